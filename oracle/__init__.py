@@ -1,0 +1,218 @@
+"""CPU checkers for the quantized-matmul path.  TEST INFRASTRUCTURE ONLY.
+
+Two implementations behind one numpy interface:
+
+* ``impl="port"``  -- the plain-C restatement in ``nnops_oracle.c`` (always available);
+* ``impl="ref"``   -- the unmodified reference CPU route compiled into ``oracle/_ref`` (available
+  when it was prebuilt and the host CPU has the VNNI flavour it needs).
+
+Only tests, ``__graft_entry__.smoke()`` and the bench's CPU-baseline legs may import this
+package; the shipped CUDA path never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import numpy as np
+
+from . import build as _build
+
+HERE = Path(__file__).resolve().parent
+OUT_KINDS = {"s32": 0, "s8": 1, "u8": 2, "f32": 3, "f16": 4}
+_OUT_NP = {"s32": np.int32, "s8": np.int8, "u8": np.uint8, "f32": np.float32, "f16": np.float16}
+Q4_1_BLOCK_BYTES = 20
+Q4_1_BLOCK_ELEMS = 32
+
+
+class GemmI8Args(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("w", C.c_void_p), ("out", C.c_void_p),
+        ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+        ("a_stride_m", C.c_int64), ("a_stride_k", C.c_int64),
+        ("w_stride_n", C.c_int64), ("w_stride_k", C.c_int64), ("ldc", C.c_int64),
+        ("a_unsigned", C.c_int32), ("out_kind", C.c_int32),
+        ("bias", C.c_void_p), ("relu", C.c_int32),
+        ("scale_a", C.c_void_p), ("scale_w", C.c_void_p), ("zp_a", C.c_void_p), ("zp_w", C.c_void_p),
+        ("scale_a_scalar", C.c_float), ("scale_w_scalar", C.c_float),
+        ("zp_a_scalar", C.c_int32), ("zp_w_scalar", C.c_int32),
+        ("out_scale", C.c_float), ("out_zp", C.c_int32),
+        ("min_clip", C.c_float), ("max_clip", C.c_float),
+    ]
+
+
+_port = None
+_ref = None
+_ref_tried = False
+
+
+def _cpu_flags() -> set[str]:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    return set(line.split(":", 1)[1].split())
+    except OSError:
+        pass
+    return set()
+
+
+def port_lib() -> C.CDLL:
+    global _port
+    if _port is None:
+        _port = C.CDLL(str(_build.build_port()))
+        _port.oracle_f16_to_f32.restype = C.c_float
+        _port.oracle_f16_to_f32.argtypes = [C.c_uint16]
+        _port.oracle_f32_to_f16.restype = C.c_uint16
+        _port.oracle_f32_to_f16.argtypes = [C.c_float]
+    return _port
+
+
+def ref_lib() -> C.CDLL | None:
+    """The compiled reference route, or None when it is not prebuilt / not runnable here."""
+    global _ref, _ref_tried
+    if _ref_tried:
+        return _ref
+    _ref_tried = True
+    flags = _cpu_flags()
+    need = {"avx2", "fma", "f16c"}
+    if not need <= flags:
+        return None
+    order = []
+    if "avx_vnni" in flags:
+        order.append("avxvnni")
+    if {"avx512_vnni", "avx512vl", "avx512bw", "avx512f"} <= flags:
+        order.append("avx512vnni")
+    for name in order:
+        p = HERE / "_ref" / f"libnnops_ref_{name}.so"
+        if p.exists():
+            try:
+                _ref = C.CDLL(str(p))
+                _ref.ref_isa = name
+                return _ref
+            except OSError:
+                continue
+    return None
+
+
+def have_ref() -> bool:
+    return ref_lib() is not None
+
+
+def ref_threads() -> int:
+    return int(os.environ.get("NNOPS_ORACLE_THREADS", os.cpu_count() or 1))
+
+
+def _ptr(x) -> int | None:
+    return None if x is None else x.ctypes.data
+
+
+def gemm_i8(a: np.ndarray, w: np.ndarray, *, out_kind: str = "s32", bias: np.ndarray | None = None,
+            relu: bool = False, scale_a=1.0, scale_w=1.0, zp_a=0, zp_w=0, out_scale: float = 1.0,
+            out_zp: int = 0, min_clip: float = -np.inf, max_clip: float = np.inf,
+            impl: str = "port", threads: int | None = None, use_linear: bool = True) -> np.ndarray:
+    """int8 matmul + fused epilogue.  ``a`` is [M,K] s8/u8 (any 2-D strides: a transposed
+    numpy view expresses MatMul's transpose_a); ``w`` is given as the LOGICAL [N,K] matrix
+    (pass ``w_kn.T`` for a weight stored [K,N]).  scale_*/zp_* are scalars or 1-D arrays
+    (per-token for A, per-channel for W)."""
+    assert a.ndim == 2 and w.ndim == 2 and a.shape[1] == w.shape[1]
+    assert a.dtype in (np.int8, np.uint8) and w.dtype == np.int8
+    m, k = a.shape
+    n = w.shape[0]
+    out = np.zeros((m, n), dtype=_OUT_NP[out_kind])
+    keep = []
+
+    def arr(v, dt):
+        if np.isscalar(v):
+            return None, dt(v)
+        v = np.ascontiguousarray(v, dtype=dt)
+        keep.append(v)
+        return v, dt(1 if dt is np.float32 else 0)
+
+    sa, sa0 = arr(scale_a, np.float32)
+    sw, sw0 = arr(scale_w, np.float32)
+    za, za0 = arr(zp_a, np.int32)
+    zw, zw0 = arr(zp_w, np.int32)
+    if bias is not None:
+        bdt = np.int32 if out_kind in ("s32", "s8", "u8") else _OUT_NP[out_kind]
+        bias = np.ascontiguousarray(bias, dtype=bdt)
+    args = GemmI8Args(
+        a=a.ctypes.data, w=w.ctypes.data, out=out.ctypes.data, m=m, n=n, k=k,
+        a_stride_m=a.strides[0], a_stride_k=a.strides[1] if k > 1 or a.strides[1] == 1 else 1,
+        w_stride_n=w.strides[0], w_stride_k=w.strides[1] if k > 1 or w.strides[1] == 1 else 1, ldc=n,
+        a_unsigned=int(a.dtype == np.uint8), out_kind=OUT_KINDS[out_kind], bias=_ptr(bias), relu=int(relu),
+        scale_a=_ptr(sa), scale_w=_ptr(sw), zp_a=_ptr(za), zp_w=_ptr(zw),
+        scale_a_scalar=float(sa0), scale_w_scalar=float(sw0), zp_a_scalar=int(za0), zp_w_scalar=int(zw0),
+        out_scale=float(out_scale), out_zp=int(out_zp), min_clip=float(min_clip), max_clip=float(max_clip))
+    if impl == "port":
+        port_lib().oracle_gemm_i8(C.byref(args))
+    else:
+        lib = ref_lib()
+        if lib is None:
+            raise RuntimeError("reference route not available on this host")
+        linear = use_linear and a.strides[1] == 1 and w.strides[1] == 1
+        st = lib.ref_gemm_i8(C.byref(args), int(linear), int(threads or ref_threads()))
+        if st != 0:
+            raise RuntimeError(f"reference op returned Status {st}")
+    return out
+
+
+def q4_1_decode(blocks: np.ndarray, count: int, impl: str = "port") -> np.ndarray:
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    out = np.zeros(count, dtype=np.float32)
+    if impl == "port":
+        port_lib().oracle_q4_1_decode_row(C.c_void_p(blocks.ctypes.data), C.c_int64(count),
+                                          C.c_void_p(out.ctypes.data))
+    else:
+        ref_lib().ref_q4_1_decode(C.c_void_p(blocks.ctypes.data), C.c_int64(count), C.c_void_p(out.ctypes.data))
+    return out
+
+
+def q4_1_quantize(src: np.ndarray, impl: str = "port") -> np.ndarray:
+    src = np.ascontiguousarray(src, dtype=np.float32).ravel()
+    nblk = (src.size + Q4_1_BLOCK_ELEMS - 1) // Q4_1_BLOCK_ELEMS
+    blocks = np.zeros(nblk * Q4_1_BLOCK_BYTES, dtype=np.uint8)
+    if impl == "port":
+        port_lib().oracle_q4_1_quantize_row(C.c_void_p(src.ctypes.data), C.c_int64(src.size),
+                                            C.c_void_p(blocks.ctypes.data))
+    else:
+        ref_lib().ref_q4_1_quantize(C.c_void_p(src.ctypes.data), C.c_int64(src.size), C.c_void_p(blocks.ctypes.data))
+    return blocks
+
+
+def q4_1_matmul(a: np.ndarray, w_blocks: np.ndarray, k: int, *, out_dtype: str = "f32",
+                w_round_f16: bool = False, bias: np.ndarray | None = None, impl: str = "port",
+                threads: int | None = None) -> np.ndarray:
+    """``a`` [M,K] f16/f32 (C-contiguous), ``w_blocks`` uint8 [N, ceil(K/32)*20].
+    port: f64 accumulation, out_dtype free.  ref: the reference Linear op, whose output dtype
+    equals the activation dtype (f16 activations x f32 output is not a reference pose)."""
+    assert a.ndim == 2 and w_blocks.ndim == 2 and w_blocks.dtype == np.uint8
+    a = np.ascontiguousarray(a)
+    w_blocks = np.ascontiguousarray(w_blocks)
+    m = a.shape[0]
+    n = w_blocks.shape[0]
+    assert a.shape[1] == k and w_blocks.shape[1] == ((k + 31) // 32) * 20
+    a_f16 = a.dtype == np.float16
+    out = np.zeros((m, n), dtype=_OUT_NP[out_dtype])
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, dtype=_OUT_NP[out_dtype])
+    if impl == "port":
+        port_lib().oracle_q4_1_matmul(
+            C.c_void_p(a.ctypes.data), C.c_int(a_f16), C.c_int64(k),
+            C.c_void_p(w_blocks.ctypes.data), C.c_int64(w_blocks.shape[1] // 20),
+            C.c_void_p(out.ctypes.data), C.c_int(out_dtype == "f16"), C.c_int64(n),
+            C.c_int64(m), C.c_int64(n), C.c_int64(k), C.c_int(w_round_f16), C.c_void_p(_ptr(bias)))
+    else:
+        lib = ref_lib()
+        if lib is None:
+            raise RuntimeError("reference route not available on this host")
+        assert (out_dtype == "f16") == a_f16, "reference pose: output dtype == activation dtype"
+        st = lib.ref_linear_q4_1(
+            C.c_void_p(a.ctypes.data), C.c_int(a_f16), C.c_int64(m), C.c_int64(k), C.c_int64(a.strides[0]),
+            C.c_void_p(w_blocks.ctypes.data), C.c_int64(n), C.c_int64(w_blocks.strides[0]),
+            C.c_void_p(_ptr(bias)), C.c_void_p(out.ctypes.data), C.c_int64(out.strides[0]),
+            C.c_int(int(threads or ref_threads())))
+        if st != 0:
+            raise RuntimeError(f"reference op returned Status {st}")
+    return out

@@ -1,0 +1,173 @@
+// C entry points around the UNMODIFIED nnops reference CPU route.  TEST INFRASTRUCTURE
+// ONLY: built by oracle/build.py into oracle/_ref/libnnops_ref_<isa>.so from the reference's
+// own sources (read in place, never copied), and used to (1) validate the plain-C
+// restatement in nnops_oracle.c, (2) generate tests/golden/ fixtures, and (3) serve as the
+// timed host-CPU baseline ("kind": "reference").  The shipped CUDA path never loads it.
+//
+// Everything here goes through the reference's public operator API exactly as a caller
+// would: Linear::create / MatMul::create(attrs, Backend::CPU) -> compute(out, inputs, ctx),
+// with an OpenMP parallel_for injected through ComputeContext::cpu.
+
+#include "nnops/core/openmp_backend.hpp"
+#include "nnops/ops/linear.hpp"
+#include "nnops/ops/matmul.hpp"
+#include "nnops/detail/q4_1.hpp"
+
+#include <cstdint>
+#include <cstring>
+
+using namespace nnops;
+
+namespace {
+
+// Field-for-field twin of oracle_gemm_i8_args in nnops_oracle.c.
+struct GemmI8Args {
+    const void* a;
+    const int8_t* w;
+    void* out;
+    int64_t m, n, k;
+    int64_t a_stride_m, a_stride_k, w_stride_n, w_stride_k, ldc;
+    int32_t a_unsigned;
+    int32_t out_kind;
+    const void* bias;
+    int32_t relu;
+    const float* scale_a;
+    const float* scale_w;
+    const int32_t* zp_a;
+    const int32_t* zp_w;
+    float scale_a_scalar, scale_w_scalar;
+    int32_t zp_a_scalar, zp_w_scalar;
+    float out_scale;
+    int32_t out_zp;
+    float min_clip, max_clip;
+};
+
+DataType out_dtype(int kind)
+{
+    switch (kind) {
+    case 0: return DataType::s32;
+    case 1: return DataType::s8;
+    case 2: return DataType::u8;
+    case 3: return DataType::f32;
+    default: return DataType::f16;
+    }
+}
+
+QuantParams make_qp(const float* s, const int32_t* z, float s0, int32_t z0, int64_t count,
+                    QuantGranularity g)
+{
+    QuantParams q;
+    q.scale = s0;
+    q.zero_point = z0;
+    if (s != nullptr || z != nullptr) {
+        q.granularity = g;
+        q.scale_data = s;
+        q.zero_point_data = z;
+        q.num_scales = count;
+    }
+    return q;
+}
+
+ComputeContext make_ctx(int threads)
+{
+    ComputeContext ctx;
+    if (threads > 1) {
+        ctx.cpu = openmp_backend(threads);
+    }
+    return ctx;
+}
+
+} // namespace
+
+extern "C" {
+
+/// int8 Linear / MatMul through the reference op.  use_linear != 0 requires the NT pose
+/// (A [M,K], W [N,K]) and calls Linear; otherwise MatMul with the transposes the strides imply.
+int ref_gemm_i8(const GemmI8Args* p, int use_linear, int threads)
+{
+    const bool ta = p->a_stride_k != 1;   // A stored [K, M]
+    const bool tb = p->w_stride_k == 1;   // W stored [N, K]
+    const int64_t a_shape[2] = {ta ? p->k : p->m, ta ? p->m : p->k};
+    const int64_t w_shape[2] = {tb ? p->n : p->k, tb ? p->k : p->n};
+    const int64_t o_shape[2] = {p->m, p->n};
+    const DataType adt = p->a_unsigned ? DataType::u8 : DataType::s8;
+    const DataType odt = out_dtype(p->out_kind);
+
+    TensorView a(a_shape, adt, const_cast<void*>(p->a), ta ? p->a_stride_k : p->a_stride_m,
+                 TensorLayout::Dense,
+                 make_qp(p->scale_a, p->zp_a, p->scale_a_scalar, p->zp_a_scalar, p->m,
+                         QuantGranularity::PerToken));
+    TensorView w(w_shape, DataType::s8, const_cast<int8_t*>(p->w), tb ? p->w_stride_n : p->w_stride_k,
+                 TensorLayout::Dense,
+                 make_qp(p->scale_w, p->zp_w, p->scale_w_scalar, p->zp_w_scalar, p->n,
+                         QuantGranularity::PerChannel));
+    QuantParams oq;
+    oq.scale = p->out_scale;
+    oq.zero_point = p->out_zp;
+    TensorView out(o_shape, odt, p->out, p->ldc * int64_t(data_type_size(odt)), TensorLayout::Dense, oq);
+
+    const int64_t b_shape[1] = {p->n};
+    const DataType bdt = p->out_kind <= 2 ? DataType::s32 : odt;
+    TensorView bias(b_shape, bdt, const_cast<void*>(p->bias));
+
+    Epilogue ep;
+    ep.type = p->relu ? EpilogueActivateType::Relu : EpilogueActivateType::None;
+    ep.min_clip = p->min_clip;
+    ep.max_clip = p->max_clip;
+
+    const ComputeContext ctx = make_ctx(threads);
+    TensorView ins[3] = {a, w, bias};
+    const std::span<const TensorView> in_span(ins, p->bias ? 3 : 2);
+
+    Status st;
+    if (use_linear) {
+        if (ta || !tb) {
+            return int(Status::invalid_argument);
+        }
+        LinearAttributes attrs;
+        attrs.output_dtype = odt;
+        attrs.epilogue = ep;
+        auto op = Linear::create(attrs, Backend::CPU);
+        st = op->compute(out, in_span, ctx, nullptr);
+    } else {
+        MatMulAttributes attrs;
+        attrs.transpose_a = ta;
+        attrs.transpose_b = tb;
+        attrs.output_dtype = odt;
+        attrs.epilogue = ep;
+        auto op = MatMul::create(attrs, Backend::CPU);
+        st = op->compute(out, in_span, ctx, nullptr);
+    }
+    return int(st);
+}
+
+/// Linear(f32|f16 activations x q4_1 weights [N,K]) through the reference op.  The output
+/// dtype equals the activation dtype (the reference's only fp pose).
+int ref_linear_q4_1(const void* x, int x_is_f16, int64_t m, int64_t k, int64_t x_pitch_bytes,
+                    const void* w_blocks, int64_t n, int64_t w_pitch_bytes, const void* bias,
+                    void* out, int64_t out_pitch_bytes, int threads)
+{
+    const DataType dt = x_is_f16 ? DataType::f16 : DataType::f32;
+    const int64_t x_shape[2] = {m, k};
+    const int64_t w_shape[2] = {n, k};
+    const int64_t o_shape[2] = {m, n};
+    const int64_t b_shape[1] = {n};
+    TensorView xv(x_shape, dt, const_cast<void*>(x), x_pitch_bytes);
+    TensorView wv(w_shape, DataType::q4_1, const_cast<void*>(w_blocks), w_pitch_bytes);
+    TensorView ov(o_shape, dt, out, out_pitch_bytes);
+    TensorView bv(b_shape, dt, const_cast<void*>(bias));
+    LinearAttributes attrs;
+    attrs.output_dtype = dt;
+    auto op = Linear::create(attrs, Backend::CPU);
+    const ComputeContext ctx = make_ctx(threads);
+    TensorView ins[3] = {xv, wv, bv};
+    return int(op->compute(ov, std::span<const TensorView>(ins, bias ? 3 : 2), ctx, nullptr));
+}
+
+/// Reference Q4_1 codec, for pinning the restated codec.
+void ref_q4_1_decode(const void* blocks, int64_t count, float* out) { pack_q4<float>(blocks, count, out); }
+void ref_q4_1_quantize(const float* src, int64_t count, void* blocks) { quantize_q4<float>(src, count, blocks); }
+
+void ref_release_scratch() { release_scratch_memory(); }
+
+} // extern "C"
