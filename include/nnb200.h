@@ -1,0 +1,188 @@
+/*
+ * nnb200 -- C ABI of the B200 (sm_100a) quantized-matmul backend for nnops.
+ *
+ * Every entry point takes plain pointers and sizes; all data pointers are DEVICE pointers
+ * of the current CUDA device unless a comment says otherwise.  Calls enqueue work on the
+ * given stream (a cudaStream_t passed as void*, NULL = default stream) and return without
+ * synchronising.  Return values use the numbering of nnops::Status
+ * (reference include/nnops/core/status.hpp:19-33).  A call that returns an error has written
+ * nothing to its outputs.
+ */
+#ifndef NNB200_H
+#define NNB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define NNB200_API __attribute__((visibility("default")))
+#else
+#define NNB200_API
+#endif
+
+#define NNB200_OK 0
+#define NNB200_INVALID_ARGUMENT 1
+#define NNB200_UNSUPPORTED 2
+#define NNB200_NOT_INITIALIZED 3
+#define NNB200_OUT_OF_MEMORY 4
+#define NNB200_INTERNAL 5
+
+/* Destination kinds of the int8 route (reference I8OutKind,
+ * src/backend/cuda/matmul/matmul_i8_common.cuh:38-58). */
+#define NNB200_OUT_S32 0
+#define NNB200_OUT_S8 1
+#define NNB200_OUT_U8 2
+#define NNB200_OUT_F32 3
+#define NNB200_OUT_F16 4
+
+/* Activation codes = nnops::EpilogueActivateType (include/nnops/core/epilogue.hpp:23-34). */
+#define NNB200_ACT_NONE 0
+#define NNB200_ACT_RELU 1
+#define NNB200_ACT_GELU 2
+#define NNB200_ACT_SIGMOID 3
+#define NNB200_ACT_TANH 4
+#define NNB200_ACT_LEAKY_RELU 5
+#define NNB200_ACT_SILU 6
+#define NNB200_ACT_HARD_SWISH 7
+#define NNB200_ACT_ELU 8
+#define NNB200_ACT_RELU6 9
+
+/* Engines, for nnb200_gemm_i8_args.force_engine and the *_engine_name queries. */
+#define NNB200_ENGINE_AUTO 0
+#define NNB200_ENGINE_UMMA 1    /* TMA + tcgen05.mma kind::i8, TMEM accumulators           */
+#define NNB200_ENGINE_NARROW 2  /* M <= 16 decode: bandwidth kernel, dp4a                   */
+#define NNB200_ENGINE_GENERIC 3 /* any pose / alignment: SIMT tile, correctness tier        */
+
+/*
+ * One int8 matmul call: out[b][m][n] = epilogue( sum_k A[b][m][k] * W[b][n][k] ).
+ * Replaces the parameter block the reference launcher takes
+ * (GemmI8Params, src/backend/cuda/matmul/matmul_i8_common.cuh:69-112, filled by
+ * linear_i8_cuda src/backend/cuda/matmul/linear.cu:27-90 and matmul_i8_cuda
+ * src/backend/cuda/matmul/matmul.cu:35-95).
+ *
+ * Strides are in ELEMENTS.  The Linear pose is a_stride_k == 1 and w_stride_k == 1
+ * (A [M,K] and W [N,K], both k-contiguous); MatMul's transposes are expressed by
+ * swapping which stride is 1.  batch_stride 0 broadcasts that operand over the batch.
+ *
+ * Integer destinations (S32/S8/U8): v = raw - zp_a*R_w[n] - zp_w*R_a[m] + K*zp_a*zp_w
+ * (+ int32 bias[n]) (Relu if relu != 0); S8/U8 then requantise with
+ * req = (scale_a[m] / out_scale) * scale_w[n], x = float(v) * req, clamp to the type's
+ * range minus out_zp, round half away from zero as trunc(x + copysign(0.5, x)), add out_zp.
+ * fp destinations (F32/F16): f = float(v) * (scale_a[m]*scale_w[n]) (+ fp bias[n] if
+ * non-zero), clamp to [min_clip, max_clip], activation.
+ *
+ * scale_a / zp_a are per row m (NULL -> the *_scalar value), scale_w / zp_w per output
+ * channel n.  For a batched call the same arrays serve every batch element.
+ *
+ * workspace: nnb200_gemm_i8_workspace_bytes() bytes of device scratch (may be NULL when
+ * that is 0).  It holds the row/column sums R_a, R_w when any zero point is non-zero and
+ * the split-K planes of the narrow engine.
+ */
+typedef struct nnb200_gemm_i8_args {
+    const void* a;
+    const void* w;
+    void* out;
+    int64_t m, n, k;
+    int64_t a_stride_m, a_stride_k;
+    int64_t w_stride_n, w_stride_k;
+    int64_t ldc;
+    int64_t batch;
+    int64_t a_batch_stride, w_batch_stride, out_batch_stride;
+    int32_t a_unsigned; /* A holds u8 instead of s8 */
+    int32_t out_kind;   /* NNB200_OUT_* */
+    const void* bias;   /* [n]: int32 for integer destinations, out type for fp ones; may be NULL */
+    int32_t relu;       /* integer destinations honour only Relu */
+    int32_t activation; /* NNB200_ACT_*, fp destinations */
+    float act_alpha, act_beta;
+    float min_clip, max_clip;
+    const float* scale_a;
+    const float* scale_w;
+    const int32_t* zp_a;
+    const int32_t* zp_w;
+    float scale_a_scalar, scale_w_scalar;
+    int32_t zp_a_scalar, zp_w_scalar;
+    int32_t zp_a_nonzero; /* caller's promise about the ARRAYS: 0 = every zp_a[] entry is 0 */
+    int32_t zp_w_nonzero; /* (lets the backend skip the R_a / R_w sweeps); scalars are checked here */
+    float out_scale;
+    int32_t out_zp;
+    void* workspace;
+    size_t workspace_bytes;
+    int32_t force_engine; /* NNB200_ENGINE_*; AUTO picks */
+} nnb200_gemm_i8_args;
+
+/* Scratch the call needs (0 for the common zero-point-free tensor-core call). */
+NNB200_API size_t nnb200_gemm_i8_workspace_bytes(const nnb200_gemm_i8_args* args);
+
+/* Enqueue the matmul.  Replaces dense_gemm_i8_status
+ * (src/backend/cuda/matmul/matmul_i8.cuh:284-446). */
+NNB200_API int nnb200_gemm_i8(const nnb200_gemm_i8_args* args, void* stream);
+
+/* Which engine nnb200_gemm_i8 would run for these arguments (NNB200_ENGINE_*). */
+NNB200_API int nnb200_gemm_i8_engine(const nnb200_gemm_i8_args* args);
+
+/*
+ * Q4_1 weight-decode product: out[m][n] = act( alpha * sum_k A[m][k] * dequant(W)[n][k]
+ * + bias[n] ), W stored as llama.cpp Q4_1 rows: ceil(k/32) blocks of 20 bytes
+ * {f16 d, f16 m, 16 nibble bytes; low nibble = value j, high nibble = value j+16; w = d*q+m}
+ * (reference include/nnops/detail/q4_1.hpp:53-79).  Replaces the CPU-only routes
+ * matmul_qblock_fused (src/backend/cpu/matmul/matmul_qblock_fused.cpp:151-197) and the packed
+ * route (src/backend/cpu/matmul/matmul.cpp:137-156); the reference has no CUDA kernel for it
+ * (src/backend/cuda/matmul/linear.cu:116-119 returns unsupported).
+ *
+ * a_f16 / out_f16: 1 = IEEE half, 0 = float.  Reference poses are f16->f16 and f32->f32;
+ * f16 activations with f32 output is accepted as an extension.  lda / ldc in elements,
+ * ldw_blocks in 20-byte blocks.
+ */
+typedef struct nnb200_q4_1_args {
+    const void* a;
+    const void* w_blocks;
+    void* out;
+    int64_t m, n, k;
+    int64_t lda, ldw_blocks, ldc;
+    int32_t a_f16, out_f16;
+    const void* bias; /* [n] in the output type; may be NULL */
+    int32_t activation;
+    float act_alpha, act_beta;
+    float min_clip, max_clip;
+    float alpha;
+    void* workspace;
+    size_t workspace_bytes;
+    int32_t force_engine; /* 0 auto, 1 tensor-core GEMM, 2 GEMV */
+} nnb200_q4_1_args;
+
+NNB200_API size_t nnb200_q4_1_workspace_bytes(const nnb200_q4_1_args* args);
+NNB200_API int nnb200_linear_q4_1(const nnb200_q4_1_args* args, void* stream);
+NNB200_API int nnb200_q4_1_engine(const nnb200_q4_1_args* args);
+
+/* Decode `rows` Q4_1 rows of `k` values into f32 (out_f16 == 0) or f16, ld in elements.
+ * Device twin of pack_q4 (include/nnops/detail/q4_1.hpp:152-184). */
+NNB200_API int nnb200_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, int64_t k, void* out,
+                       int32_t out_f16, int64_t ld_out, void* stream);
+
+/*
+ * Kernels never spin forever: a pipeline wait that runs out records a code in a per-device
+ * error word and the kernel exits.  This synchronises the device, returns that word through
+ * *code (0 = no error) and clears it.
+ */
+NNB200_API int nnb200_take_device_error(int32_t* code);
+
+/* Stage a host array into device memory on the stream (the reference launcher's per-call
+ * H2D of quantization arrays, src/backend/cuda/matmul/matmul_i8.cuh:357-376). */
+NNB200_API int nnb200_copy_h2d_async(void* dst_device, const void* src_host, size_t bytes, void* stream);
+
+/* 1 if p is device (or managed) memory usable by kernels of the current device, else 0. */
+NNB200_API int nnb200_is_device_pointer(const void* p);
+
+/* Count of kernel launches this process has enqueued through this library. */
+NNB200_API uint64_t nnb200_launch_count(void);
+
+NNB200_API const char* nnb200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNB200_H */

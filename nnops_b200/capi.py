@@ -1,0 +1,115 @@
+"""ctypes bindings of libnnb200's C ABI (include/nnb200.h).
+
+Loading fails loudly when the library has not been built: there is no CPU or PyTorch
+fallback for any call here.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "lib" / "libnnb200.so"
+
+OK, INVALID_ARGUMENT, UNSUPPORTED, NOT_INITIALIZED, OUT_OF_MEMORY, INTERNAL = range(6)
+STATUS_NAMES = ["ok", "invalid_argument", "unsupported", "not_initialized", "out_of_memory", "internal"]
+OUT_KINDS = {"s32": 0, "s8": 1, "u8": 2, "f32": 3, "f16": 4}
+ACTIVATIONS = {"none": 0, "relu": 1, "gelu": 2, "sigmoid": 3, "tanh": 4, "leaky_relu": 5, "silu": 6,
+               "hard_swish": 7, "elu": 8, "relu6": 9}
+ENGINES = {"auto": 0, "umma": 1, "narrow": 2, "generic": 3}
+ENGINE_NAMES = {v: k for k, v in ENGINES.items()}
+Q4_ENGINES = {"auto": 0, "gemm": 1, "gemv": 2}
+
+
+class GemmI8Args(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("w", C.c_void_p), ("out", C.c_void_p),
+        ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+        ("a_stride_m", C.c_int64), ("a_stride_k", C.c_int64),
+        ("w_stride_n", C.c_int64), ("w_stride_k", C.c_int64),
+        ("ldc", C.c_int64), ("batch", C.c_int64),
+        ("a_batch_stride", C.c_int64), ("w_batch_stride", C.c_int64), ("out_batch_stride", C.c_int64),
+        ("a_unsigned", C.c_int32), ("out_kind", C.c_int32),
+        ("bias", C.c_void_p),
+        ("relu", C.c_int32), ("activation", C.c_int32),
+        ("act_alpha", C.c_float), ("act_beta", C.c_float),
+        ("min_clip", C.c_float), ("max_clip", C.c_float),
+        ("scale_a", C.c_void_p), ("scale_w", C.c_void_p), ("zp_a", C.c_void_p), ("zp_w", C.c_void_p),
+        ("scale_a_scalar", C.c_float), ("scale_w_scalar", C.c_float),
+        ("zp_a_scalar", C.c_int32), ("zp_w_scalar", C.c_int32),
+        ("zp_a_nonzero", C.c_int32), ("zp_w_nonzero", C.c_int32),
+        ("out_scale", C.c_float), ("out_zp", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("force_engine", C.c_int32),
+    ]
+
+
+class Q41Args(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("w_blocks", C.c_void_p), ("out", C.c_void_p),
+        ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+        ("lda", C.c_int64), ("ldw_blocks", C.c_int64), ("ldc", C.c_int64),
+        ("a_f16", C.c_int32), ("out_f16", C.c_int32),
+        ("bias", C.c_void_p),
+        ("activation", C.c_int32),
+        ("act_alpha", C.c_float), ("act_beta", C.c_float),
+        ("min_clip", C.c_float), ("max_clip", C.c_float),
+        ("alpha", C.c_float),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("force_engine", C.c_int32),
+    ]
+
+
+# Every symbol include/nnb200.h declares: (name, restype, argtypes).
+SYMBOLS = [
+    ("nnb200_gemm_i8_workspace_bytes", C.c_size_t, [C.POINTER(GemmI8Args)]),
+    ("nnb200_gemm_i8", C.c_int, [C.POINTER(GemmI8Args), C.c_void_p]),
+    ("nnb200_gemm_i8_engine", C.c_int, [C.POINTER(GemmI8Args)]),
+    ("nnb200_q4_1_workspace_bytes", C.c_size_t, [C.POINTER(Q41Args)]),
+    ("nnb200_linear_q4_1", C.c_int, [C.POINTER(Q41Args), C.c_void_p]),
+    ("nnb200_q4_1_engine", C.c_int, [C.POINTER(Q41Args)]),
+    ("nnb200_q4_1_decode", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32,
+                                     C.c_int64, C.c_void_p]),
+    ("nnb200_take_device_error", C.c_int, [C.POINTER(C.c_int32)]),
+    ("nnb200_copy_h2d_async", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    ("nnb200_is_device_pointer", C.c_int, [C.c_void_p]),
+    ("nnb200_launch_count", C.c_uint64, []),
+    ("nnb200_version", C.c_char_p, []),
+]
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded C-ABI library.  Raises if it has not been built (python -m nnops_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m nnops_b200.build` "
+                "(the CUDA library is the only implementation; there is no fallback)")
+        l = C.CDLL(str(LIB_PATH))
+        for name, res, args in SYMBOLS:
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+class Nnb200Error(RuntimeError):
+    def __init__(self, status: int, what: str):
+        self.status = status
+        name = STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else str(status)
+        super().__init__(f"{what}: {name}")
+
+
+def check(status: int, what: str) -> None:
+    if status != OK:
+        raise Nnb200Error(status, what)
+
+
+def take_device_error() -> int:
+    code = C.c_int32(0)
+    check(lib().nnb200_take_device_error(C.byref(code)), "nnb200_take_device_error")
+    return code.value

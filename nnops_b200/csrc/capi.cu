@@ -1,0 +1,396 @@
+// extern "C" entry points of libnnb200 (declared in include/nnb200.h): argument checks,
+// engine choice, per-device state, TMA descriptor encoding.
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstring>
+#include <mutex>
+
+#include "internal.cuh"
+
+namespace nnb200 {
+
+namespace {
+
+// One error word per device; kernels reach it through DeviceInfo::error_word.
+__device__ int32_t g_error_word;
+
+std::atomic<uint64_t> g_launches{0};
+
+DeviceInfo g_devices[kMaxDevices];
+std::once_flag g_device_once[kMaxDevices];
+bool g_device_ok[kMaxDevices];
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn()
+{
+    // The driver entry point is looked up at run time so the library does not link libcuda.
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &qres) !=
+                cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess) {
+            return static_cast<EncodeTiledFn>(nullptr);
+        }
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+}  // namespace
+
+const DeviceInfo* current_device_info()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        return nullptr;
+    }
+    std::call_once(g_device_once[dev], [dev] {
+        DeviceInfo& d = g_devices[dev];
+        d.device = dev;
+        bool ok = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess;
+        ok = ok && cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess;
+        ok = ok && cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev) == cudaSuccess;
+        void* p = nullptr;
+        // The symbol's name is a host-side handle; kernels need its device address, which
+        // differs per device, so it is resolved with that device current.
+        ok = ok && cudaGetSymbolAddress(&p, g_error_word) == cudaSuccess;
+        d.error_word = static_cast<int32_t*>(p);
+        if (ok) {
+            const int32_t zero = 0;
+            ok = cudaMemcpy(d.error_word, &zero, sizeof(zero), cudaMemcpyHostToDevice) == cudaSuccess;
+        }
+        g_device_ok[dev] = ok;
+    });
+    return g_device_ok[dev] ? &g_devices[dev] : nullptr;
+}
+
+void note_launch(int n)
+{
+    g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed);
+}
+
+bool make_tma_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t cols, uint64_t rows,
+                 uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) {
+        return false;
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+namespace {
+
+bool valid_i8_args(const nnb200_gemm_i8_args* a)
+{
+    if (a == nullptr || a->m < 0 || a->n < 0 || a->k < 0 || a->batch < 0) {
+        return false;
+    }
+    if (a->out_kind < NNB200_OUT_S32 || a->out_kind > NNB200_OUT_F16) {
+        return false;
+    }
+    if (a->m == 0 || a->n == 0 || a->batch == 0) {
+        return true;
+    }
+    if (a->a == nullptr || a->w == nullptr || a->out == nullptr || a->k == 0) {
+        return false;
+    }
+    if (a->ldc < a->n) {
+        return false;
+    }
+    if ((a->a_stride_k != 1 && a->a_stride_m != 1) || (a->w_stride_k != 1 && a->w_stride_n != 1)) {
+        return false;  // one of the two strides of each operand is the contiguous one
+    }
+    return true;
+}
+
+bool needs_compensation(const nnb200_gemm_i8_args* a)
+{
+    return a->zp_a_scalar != 0 || a->zp_w_scalar != 0 || (a->zp_a != nullptr && a->zp_a_nonzero != 0) ||
+           (a->zp_w != nullptr && a->zp_w_nonzero != 0);
+}
+
+I8Problem problem_of(const nnb200_gemm_i8_args* a, int64_t b)
+{
+    I8Problem p;
+    p.a = static_cast<const uint8_t*>(a->a) + b * a->a_batch_stride;
+    p.w = static_cast<const uint8_t*>(a->w) + b * a->w_batch_stride;
+    p.m = a->m;
+    p.n = a->n;
+    p.k = a->k;
+    p.a_stride_m = a->a_stride_m;
+    p.a_stride_k = a->a_stride_k;
+    p.w_stride_n = a->w_stride_n;
+    p.w_stride_k = a->w_stride_k;
+    p.a_unsigned = a->a_unsigned;
+    return p;
+}
+
+int pick_i8_engine(const nnb200_gemm_i8_args* a, const I8Problem& p)
+{
+    if (a->force_engine == NNB200_ENGINE_GENERIC) {
+        return NNB200_ENGINE_GENERIC;
+    }
+    if (a->force_engine == NNB200_ENGINE_NARROW) {
+        return narrow_i8_supported(p) ? NNB200_ENGINE_NARROW : NNB200_ENGINE_GENERIC;
+    }
+    if (a->force_engine == NNB200_ENGINE_UMMA) {
+        return umma_i8_supported(p) ? NNB200_ENGINE_UMMA : NNB200_ENGINE_GENERIC;
+    }
+    if (narrow_i8_supported(p)) {
+        return NNB200_ENGINE_NARROW;
+    }
+    if (umma_i8_supported(p)) {
+        return NNB200_ENGINE_UMMA;
+    }
+    return NNB200_ENGINE_GENERIC;
+}
+
+size_t out_elem_bytes(int kind)
+{
+    return (kind == NNB200_OUT_S32 || kind == NNB200_OUT_F32) ? 4 : (kind == NNB200_OUT_F16 ? 2 : 1);
+}
+
+}  // namespace
+}  // namespace nnb200
+
+using namespace nnb200;
+
+extern "C" {
+
+size_t nnb200_gemm_i8_workspace_bytes(const nnb200_gemm_i8_args* a)
+{
+    if (!valid_i8_args(a) || a->m == 0 || a->n == 0 || a->batch == 0) {
+        return 0;
+    }
+    if (!needs_compensation(a)) {
+        return 0;
+    }
+    // R_a [batch][m] and R_w [batch][n], each padded to 256 bytes.
+    const size_t ra = (static_cast<size_t>(a->m) * 4 + 255) & ~size_t(255);
+    const size_t rw = (static_cast<size_t>(a->n) * 4 + 255) & ~size_t(255);
+    return static_cast<size_t>(a->batch) * (ra + rw);
+}
+
+int nnb200_gemm_i8_engine(const nnb200_gemm_i8_args* a)
+{
+    if (!valid_i8_args(a)) {
+        return -1;
+    }
+    return pick_i8_engine(a, problem_of(a, 0));
+}
+
+int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
+{
+    if (!valid_i8_args(a)) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if (a->m == 0 || a->n == 0 || a->batch == 0) {
+        return NNB200_OK;
+    }
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    if (dev->cc_major != 10) {
+        return NNB200_UNSUPPORTED;  // sm_100a only: there is no other code path
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const bool comp = needs_compensation(a);
+    const size_t need = nnb200_gemm_i8_workspace_bytes(a);
+    if (need > 0 && (a->workspace == nullptr || a->workspace_bytes < need)) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    const size_t ra_bytes = (static_cast<size_t>(a->m) * 4 + 255) & ~size_t(255);
+    const size_t rw_bytes = (static_cast<size_t>(a->n) * 4 + 255) & ~size_t(255);
+
+    for (int64_t b = 0; b < a->batch; ++b) {
+        const I8Problem p = problem_of(a, b);
+        I8Epilogue ep;
+        std::memset(&ep, 0, sizeof(ep));
+        ep.out = static_cast<uint8_t*>(a->out) + static_cast<size_t>(b * a->out_batch_stride) * out_elem_bytes(a->out_kind);
+        ep.ldc = a->ldc;
+        ep.out_kind = a->out_kind;
+        ep.bias = a->bias;
+        const bool int_out = a->out_kind <= NNB200_OUT_U8;
+        ep.relu = int_out ? (a->relu != 0) : 0;
+        ep.activation = int_out ? NNB200_ACT_NONE : a->activation;
+        ep.act_alpha = a->act_alpha;
+        ep.act_beta = a->act_beta;
+        ep.min_clip = a->min_clip;
+        ep.max_clip = a->max_clip;
+        ep.scale_a = a->scale_a;
+        ep.scale_w = a->scale_w;
+        ep.zp_a = a->zp_a;
+        ep.zp_w = a->zp_w;
+        ep.scale_a_scalar = a->scale_a_scalar;
+        ep.scale_w_scalar = a->scale_w_scalar;
+        ep.zp_a_scalar = a->zp_a_scalar;
+        ep.zp_w_scalar = a->zp_w_scalar;
+        ep.compensate = comp ? 1 : 0;
+        ep.k = static_cast<int32_t>(a->k);
+        ep.out_scale = a->out_scale;
+        ep.out_zp = a->out_zp;
+        if (comp) {
+            uint8_t* ws = static_cast<uint8_t*>(a->workspace) + static_cast<size_t>(b) * (ra_bytes + rw_bytes);
+            int32_t* r_a = reinterpret_cast<int32_t*>(ws);
+            int32_t* r_w = reinterpret_cast<int32_t*>(ws + ra_bytes);
+            const int st = launch_i8_sums(p, r_a, r_w, stream);
+            if (st != NNB200_OK) {
+                return st;
+            }
+            ep.r_a = r_a;
+            ep.r_w = r_w;
+        }
+        int st;
+        switch (pick_i8_engine(a, p)) {
+        case NNB200_ENGINE_UMMA: st = launch_gemm_i8_umma(p, ep, *dev, stream); break;
+        case NNB200_ENGINE_NARROW: st = launch_gemm_i8_narrow(p, ep, *dev, stream); break;
+        default: st = launch_gemm_i8_generic(p, ep, *dev, stream); break;
+        }
+        if (st != NNB200_OK) {
+            return st;
+        }
+    }
+    return NNB200_OK;
+}
+
+static bool valid_q4_args(const nnb200_q4_1_args* q)
+{
+    if (q == nullptr || q->m < 0 || q->n < 0 || q->k < 0) {
+        return false;
+    }
+    if (q->m == 0 || q->n == 0) {
+        return true;
+    }
+    if (q->a == nullptr || q->w_blocks == nullptr || q->out == nullptr || q->k == 0) {
+        return false;
+    }
+    const int64_t nblk = (q->k + 31) / 32;
+    return q->lda >= q->k && q->ldc >= q->n && q->ldw_blocks >= nblk;
+}
+
+size_t nnb200_q4_1_workspace_bytes(const nnb200_q4_1_args*)
+{
+    return 0;
+}
+
+int nnb200_q4_1_engine(const nnb200_q4_1_args* q)
+{
+    if (!valid_q4_args(q)) {
+        return -1;
+    }
+    if (q->force_engine == 2) {
+        return 2;
+    }
+    const bool gemm_ok = q4_1_gemm_umma_supported(*q);
+    if (q->force_engine == 1) {
+        return gemm_ok ? 1 : 2;
+    }
+    return (q->m > 8 && gemm_ok) ? 1 : 2;
+}
+
+int nnb200_linear_q4_1(const nnb200_q4_1_args* q, void* stream_v)
+{
+    if (!valid_q4_args(q)) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if (q->m == 0 || q->n == 0) {
+        return NNB200_OK;
+    }
+    if ((reinterpret_cast<uintptr_t>(q->w_blocks) & 3u) != 0) {
+        return NNB200_UNSUPPORTED;  // blocks are read as 32-bit words
+    }
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    if (dev->cc_major != 10) {
+        return NNB200_UNSUPPORTED;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (nnb200_q4_1_engine(q) == 1) {
+        return launch_q4_1_gemm_umma(*q, *dev, stream);
+    }
+    return launch_q4_1_gemv(*q, *dev, stream);
+}
+
+int nnb200_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, int64_t k, void* out, int32_t out_f16,
+                       int64_t ld_out, void* stream)
+{
+    if (rows < 0 || k < 0 || (rows > 0 && k > 0 && (w_blocks == nullptr || out == nullptr)) || ld_out < k) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if ((reinterpret_cast<uintptr_t>(w_blocks) & 3u) != 0) {
+        return NNB200_UNSUPPORTED;
+    }
+    return launch_q4_1_decode(w_blocks, ldw_blocks, rows, k, out, out_f16, ld_out, static_cast<cudaStream_t>(stream));
+}
+
+int nnb200_take_device_error(int32_t* code)
+{
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr || code == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    if (cudaDeviceSynchronize() != cudaSuccess) {
+        return NNB200_INTERNAL;
+    }
+    if (cudaMemcpy(code, dev->error_word, sizeof(int32_t), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        return NNB200_INTERNAL;
+    }
+    const int32_t zero = 0;
+    return cuda_status(cudaMemcpy(dev->error_word, &zero, sizeof(zero), cudaMemcpyHostToDevice));
+}
+
+int nnb200_copy_h2d_async(void* dst_device, const void* src_host, size_t bytes, void* stream)
+{
+    if (bytes == 0) {
+        return NNB200_OK;
+    }
+    if (dst_device == nullptr || src_host == nullptr) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    return cuda_status(
+        cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+}
+
+int nnb200_is_device_pointer(const void* p)
+{
+    if (p == nullptr) {
+        return 0;
+    }
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) ? 1 : 0;
+}
+
+uint64_t nnb200_launch_count(void)
+{
+    return g_launches.load(std::memory_order_relaxed);
+}
+
+const char* nnb200_version(void)
+{
+    return "nnb200 0.1 (sm_100a)";
+}
+
+}  // extern "C"

@@ -1,0 +1,526 @@
+// int8 GEMM for prefill-sized problems on sm_100a: out = epilogue(A[M,K] * W[N,K]^T).
+//
+// Replaces the reference's mma.sync tile engine (i8_gemm_kernel,
+// src/backend/cuda/matmul/matmul_i8_ptx.cu:22-385) with a design native to Blackwell:
+//
+//   * persistent CTAs (one per SM), each walking 128 x BN output tiles in an L2-friendly
+//     grouped order;
+//   * warp 0 streams A and W tiles (128 bytes of K per stage) into a shared-memory ring with
+//     TMA, 128-byte swizzle, out-of-range rows/columns zero-filled by the hardware;
+//   * warp 1 issues tcgen05.mma kind::i8 (M128 x N=BN x K32) into one of two TMEM
+//     accumulators and frees ring slots with tcgen05.commit;
+//   * warps 2-5 drain the other accumulator with tcgen05.ld and apply the fused epilogue
+//     (zero-point compensation, int32 bias, Relu, requantisation / dequantisation) in
+//     registers, so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Both operands are already K-major in memory ([M,K] and [N,K]), which is the layout the
+// UMMA shared-memory descriptors want, so no transposes or repacking happen anywhere.
+// Every barrier wait is bounded; a wait that runs out records an error code and the CTA
+// tears down cleanly.
+
+#include <cuda_fp16.h>
+
+#include <mutex>
+
+#include "internal.cuh"
+#include "ptx.cuh"
+
+namespace nnb200 {
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockKBytes = 128;  // one 128-byte swizzle row of K per stage
+constexpr int kUmmaK = 32;         // K per tcgen05.mma for 8-bit operands
+constexpr int kGroupM = 16;        // m-blocks per raster group
+constexpr int kNumThreads = 192;   // TMA warp, MMA warp, 4 epilogue warps
+constexpr int kEpilogueThreads = 128;
+
+template <int BN>
+struct TileConfig {
+    static constexpr int kATileBytes = kBlockM * kBlockKBytes;
+    static constexpr int kBTileBytes = BN * kBlockKBytes;
+    static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+    // Ring depth: as many stages as fit beside the epilogue staging in ~200 KB.
+    static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int kTmemCols = 2 * BN;  // two accumulators; 128..512, a power of two
+    static constexpr int kColParamBytes = 4 * 4 * BN * 4;  // 4 epilogue warps x {scale, bias, r_w, zp_w} x BN x 4 B
+    static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kColParamBytes + kBarrierBytes;
+};
+
+struct TileCoord {
+    int m_blk;
+    int n_blk;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n)
+{
+    const int group_size = kGroupM * num_n;
+    const int group = tile / group_size;
+    const int first_m = group * kGroupM;
+    const int gm = min(num_m - first_m, kGroupM);
+    const int in_group = tile - group * group_size;
+    TileCoord c;
+    c.m_blk = first_m + in_group % gm;
+    c.n_blk = in_group / gm;
+    return c;
+}
+
+// Epilogue of one 32-column chunk of one row.  `acc` holds the raw int32 sums of columns
+// n0..n0+31; col_* point at the chunk's staged per-column terms in shared memory.
+template <int KIND>
+__device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowTerms& t, const uint32_t (&acc)[32],
+                                               int64_t m, bool row_ok, int n0, int n_total,
+                                               const float* col_scale, const int32_t* col_bias,
+                                               const int32_t* col_rw, const int32_t* col_zpw, bool vec_ok)
+{
+    const bool full = n0 + 32 <= n_total;
+    const float zpf = static_cast<float>(e.out_zp);
+
+    if constexpr (KIND == NNB200_OUT_S32) {
+        int32_t o[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            o[j] = i8_int_value(e, t, static_cast<int32_t>(acc[j]), col_zpw[j], col_rw[j], col_bias[j]);
+        }
+        if (!row_ok) {
+            return;
+        }
+        int32_t* dst = static_cast<int32_t*>(e.out) + m * e.ldc + n0;
+        if (full && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                *reinterpret_cast<int4*>(dst + j) = make_int4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (n0 + j < n_total) {
+                    dst[j] = o[j];
+                }
+            }
+        }
+    } else if constexpr (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) {
+        const float lo = (KIND == NNB200_OUT_S8 ? -128.0f : 0.0f) - zpf;
+        const float hi = (KIND == NNB200_OUT_S8 ? 127.0f : 255.0f) - zpf;
+        uint32_t packed[8];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int32_t v = i8_int_value(e, t, static_cast<int32_t>(acc[j + b]), col_zpw[j + b],
+                                               col_rw[j + b], col_bias[j + b]);
+                const int32_t q = i8_requant(v, __fmul_rn(t.row_k, col_scale[j + b]), lo, hi, e.out_zp);
+                word |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * b);
+            }
+            packed[j / 4] = word;
+        }
+        if (!row_ok) {
+            return;
+        }
+        uint8_t* dst = static_cast<uint8_t*>(e.out) + m * e.ldc + n0;
+        if (full && vec_ok) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (n0 + j < n_total) {
+                    dst[j] = static_cast<uint8_t>(packed[j / 4] >> (8 * (j % 4)));
+                }
+            }
+        }
+    } else if constexpr (KIND == NNB200_OUT_F32) {
+        float o[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            o[j] = i8_fp_value(e, t, static_cast<int32_t>(acc[j]), col_zpw[j], col_rw[j], col_scale[j],
+                               __int_as_float(col_bias[j]));
+        }
+        if (!row_ok) {
+            return;
+        }
+        float* dst = static_cast<float*>(e.out) + m * e.ldc + n0;
+        if (full && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                *reinterpret_cast<float4*>(dst + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (n0 + j < n_total) {
+                    dst[j] = o[j];
+                }
+            }
+        }
+    } else {  // F16
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+            const float f0 = i8_fp_value(e, t, static_cast<int32_t>(acc[j]), col_zpw[j], col_rw[j], col_scale[j],
+                                         __int_as_float(col_bias[j]));
+            const float f1 = i8_fp_value(e, t, static_cast<int32_t>(acc[j + 1]), col_zpw[j + 1], col_rw[j + 1],
+                                         col_scale[j + 1], __int_as_float(col_bias[j + 1]));
+            packed[j / 2] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f0))) |
+                            (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f1))) << 16);
+        }
+        if (!row_ok) {
+            return;
+        }
+        uint16_t* dst = static_cast<uint16_t*>(e.out) + m * e.ldc + n0;
+        if (full && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+                *reinterpret_cast<uint4*>(dst + 2 * j) =
+                    make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (n0 + j < n_total) {
+                    dst[j] = static_cast<uint16_t>(packed[j / 2] >> (16 * (j % 2)));
+                }
+            }
+        }
+    }
+}
+
+template <int BN, int KIND>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const I8Epilogue ep, const int m_total, const int n_total, const int k_total,
+                    const uint32_t idesc, const int vec_ok, int32_t* error_word)
+{
+    using Cfg = TileConfig<BN>;
+    constexpr int kStages = Cfg::kStages;
+
+    extern __shared__ uint8_t smem_raw[];
+    // The swizzled tiles must start on a 1024-byte boundary.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* stage_base = smem;
+    // Per-column epilogue terms, one private copy per epilogue warp (no cross-warp barrier).
+    int32_t* col_params = reinterpret_cast<int32_t*>(smem + kStages * Cfg::kStageBytes);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(col_params + 4 * 4 * BN);
+    uint64_t* empty_bar = full_bar + kStages;
+    uint64_t* acc_full_bar = empty_bar + kStages;
+    uint64_t* acc_empty_bar = acc_full_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int num_m = (m_total + kBlockM - 1) / kBlockM;
+    const int num_n = (n_total + BN - 1) / BN;
+    const int num_tiles = num_m * num_n;
+    const int num_kb = (k_total + kBlockKBytes - 1) / kBlockKBytes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full_bar[a], 1);
+            mbar_init(&acc_empty_bar[a], kEpilogueThreads / 32);
+        }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t armed = 0;        // bit s: slot s has been armed at least once
+            uint32_t armed_phase = 0;  // bit s: parity of the phase slot s was last armed in
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                const TileCoord tc = tile_coord(tile, num_m, num_n);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                        atomicCAS(error_word, 0, kErrProducerWait);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* a_dst = stage_base + stage * Cfg::kStageBytes;
+                    uint8_t* b_dst = a_dst + Cfg::kATileBytes;
+                    mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+                    tma_load_2d(a_dst, &map_a, &full_bar[stage], kb * kBlockKBytes, tc.m_blk * kBlockM);
+                    tma_load_2d(b_dst, &map_w, &full_bar[stage], kb * kBlockKBytes, tc.n_blk * BN);
+                    armed |= 1u << stage;
+                    armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                // Copies already issued still land in shared memory: wait (bounded) for the
+                // armed slots so the CTA does not exit underneath them.
+                const long long t0 = clock64();
+                for (int s = 0; s < kStages; ++s) {
+                    if ((armed >> s) & 1u) {
+                        // The full barrier of the phase this slot was last armed in completes
+                        // when its bytes have landed.
+                        while (!mbar_try_wait(&full_bar[s], (armed_phase >> s) & 1u)) {
+                            if (clock64() - t0 > kWaitLimitCycles) {
+                                atomicCAS(error_word, 0, kErrDrainWait);
+                                break;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+                const int acc = local_tile & 1;
+                const uint32_t acc_phase = (local_tile >> 1) & 1u;
+                if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag)) {
+                    atomicCAS(error_word, 0, kErrAccumWait);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+                        atomicCAS(error_word, 0, kErrMmaWait);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(stage_base + stage * Cfg::kStageBytes);
+                    const uint32_t b_addr = a_addr + Cfg::kATileBytes;
+                    const uint64_t a_desc = umma_desc_sw128_kmajor(a_addr);
+                    const uint64_t b_desc = umma_desc_sw128_kmajor(b_addr);
+#pragma unroll
+                    for (int ks = 0; ks < kBlockKBytes / kUmmaK; ++ks) {
+                        // +32 bytes of K per step = +2 in the descriptor's 16-byte address units.
+                        umma_i8(d_tmem, a_desc + static_cast<uint64_t>(ks * 2), b_desc + static_cast<uint64_t>(ks * 2),
+                                idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) {
+                    umma_commit(&acc_full_bar[acc]);  // accumulator complete
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+        float* cs = reinterpret_cast<float*>(col_params + (warp - 2) * 4 * BN);
+        int32_t* cb = reinterpret_cast<int32_t*>(cs) + BN;
+        int32_t* cr = cb + BN;
+        int32_t* cz = cr + BN;
+        int local_tile = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+            const TileCoord tc = tile_coord(tile, num_m, num_n);
+            const int acc = local_tile & 1;
+            const uint32_t acc_phase = (local_tile >> 1) & 1u;
+            const int n_base = tc.n_blk * BN;
+
+            // Stage this tile's per-column terms (hidden behind the tile's main loop).
+            __syncwarp();  // previous tile's reads of the staging are done
+            for (int j = lane; j < BN; j += 32) {
+                const int n = n_base + j;
+                const bool in = n < n_total;
+                cs[j] = (in && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
+                int32_t b = 0;
+                if (in && ep.bias != nullptr) {
+                    if constexpr (KIND <= NNB200_OUT_U8) {
+                        b = static_cast<const int32_t*>(ep.bias)[n];
+                    } else if constexpr (KIND == NNB200_OUT_F32) {
+                        b = __float_as_int(static_cast<const float*>(ep.bias)[n]);
+                    } else {
+                        b = __float_as_int(__half2float(static_cast<const __half*>(ep.bias)[n]));
+                    }
+                }
+                cb[j] = b;
+                cr[j] = (in && ep.compensate) ? ep.r_w[n] : 0;
+                cz[j] = (in && ep.zp_w != nullptr) ? ep.zp_w[n] : ep.zp_w_scalar;
+            }
+            __syncwarp();
+
+            const int64_t m = static_cast<int64_t>(tc.m_blk) * kBlockM + quarter * 32 + lane;
+            const bool row_ok = m < m_total;
+            I8RowTerms rt;
+            rt.zpa = 0;
+            rt.ra = 0;
+            rt.s_a = 1.0f;
+            rt.row_k = 1.0f;
+            if (row_ok) {
+                rt = i8_row_terms(ep, m);
+            }
+
+            // Warp-uniform outcome, so no lane is left behind at a later warp sync.
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag))) {
+                atomicCAS(error_word, 0, kErrEpilogueWait);
+                break;
+            }
+            tc_fence_after_sync();
+
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int n0 = n_base + c * 32;
+                if (n0 >= n_total) {
+                    break;  // uniform across the CTA's epilogue warps
+                }
+                uint32_t v[32];
+                tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
+                tmem_ld_wait();
+                epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
+                                     cz + c * 32, vec_ok != 0);
+            }
+            // Accumulator drained: hand it back to the MMA warp.
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&acc_empty_bar[acc]);
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+template <int BN, int KIND>
+int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m, int n, int k,
+                   uint32_t idesc, int vec_ok, const DeviceInfo& dev, cudaStream_t stream)
+{
+    using Cfg = TileConfig<BN>;
+    auto kernel = gemm_i8_umma_kernel<BN, KIND>;
+    static std::once_flag once[kMaxDevices];
+    static cudaError_t attr_err[kMaxDevices];
+    std::call_once(once[dev.device], [&] {
+        attr_err[dev.device] =
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    });
+    if (attr_err[dev.device] != cudaSuccess) {
+        return NNB200_INTERNAL;
+    }
+    const int num_tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BN - 1) / BN);
+    const int grid = num_tiles < dev.sm_count ? num_tiles : dev.sm_count;
+    kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, ep, m, n, k, idesc, vec_ok,
+                                                           dev.error_word);
+    note_launch();
+    return cuda_status(cudaGetLastError());
+}
+
+template <int BN>
+int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m, int n, int k,
+              uint32_t idesc, int vec_ok, const DeviceInfo& dev, cudaStream_t stream)
+{
+    switch (kind) {
+    case NNB200_OUT_S32: return launch_variant<BN, NNB200_OUT_S32>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_S8: return launch_variant<BN, NNB200_OUT_S8>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_U8: return launch_variant<BN, NNB200_OUT_U8>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_F32: return launch_variant<BN, NNB200_OUT_F32>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_F16: return launch_variant<BN, NNB200_OUT_F16>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    default: return NNB200_UNSUPPORTED;
+    }
+}
+
+}  // namespace
+
+bool umma_i8_supported(const I8Problem& p)
+{
+    if (p.a_stride_k != 1 || p.w_stride_k != 1) {
+        return false;
+    }
+    if (p.m < 1 || p.n < 1 || p.k < 1 || p.m > INT32_MAX || p.n > INT32_MAX || p.k > INT32_MAX) {
+        return false;
+    }
+    const auto aligned16 = [](uint64_t v) { return (v & 15u) == 0; };
+    return aligned16(reinterpret_cast<uintptr_t>(p.a)) && aligned16(reinterpret_cast<uintptr_t>(p.w)) &&
+           aligned16(static_cast<uint64_t>(p.a_stride_m)) && aligned16(static_cast<uint64_t>(p.w_stride_n)) &&
+           p.a_stride_m >= p.k && p.w_stride_n >= p.k;
+}
+
+int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream)
+{
+    const int m = static_cast<int>(p.m);
+    const int n = static_cast<int>(p.n);
+    const int k = static_cast<int>(p.k);
+
+    // Tile width: the widest tile that still gives every SM work; narrow problems trade
+    // arithmetic intensity for parallelism.
+    const int num_m = (m + kBlockM - 1) / kBlockM;
+    int bn = 256;
+    if (static_cast<int64_t>(num_m) * ((n + 255) / 256) < dev.sm_count) {
+        bn = 128;
+        if (static_cast<int64_t>(num_m) * ((n + 127) / 128) < dev.sm_count) {
+            bn = 64;
+        }
+    }
+
+    CUtensorMap map_a, map_w;
+    if (!make_tma_2d(&map_a, p.a, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(m),
+                     static_cast<uint64_t>(p.a_stride_m), kBlockKBytes, kBlockM) ||
+        !make_tma_2d(&map_w, p.w, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                     static_cast<uint64_t>(p.w_stride_n), kBlockKBytes, static_cast<uint32_t>(bn))) {
+        return NNB200_INTERNAL;
+    }
+
+    // Destination vector stores need a 16-byte aligned base and row pitch.
+    const int elem = (ep.out_kind == NNB200_OUT_S32 || ep.out_kind == NNB200_OUT_F32) ? 4
+                     : (ep.out_kind == NNB200_OUT_F16)                                ? 2
+                                                                                      : 1;
+    const int vec_ok = ((reinterpret_cast<uintptr_t>(ep.out) & 15u) == 0 &&
+                        ((static_cast<uint64_t>(ep.ldc) * static_cast<uint64_t>(elem)) & 15u) == 0)
+                           ? 1
+                           : 0;
+
+    const uint32_t a_fmt = p.a_unsigned ? 0u : 1u;
+    switch (bn) {
+    case 256:
+        return launch_bn<256>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 256), vec_ok,
+                              dev, stream);
+    case 128:
+        return launch_bn<128>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 128), vec_ok,
+                              dev, stream);
+    default:
+        return launch_bn<64>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 64), vec_ok,
+                             dev, stream);
+    }
+}
+
+}  // namespace nnb200

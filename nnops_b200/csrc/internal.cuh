@@ -1,0 +1,73 @@
+// Declarations shared between the translation units of libnnb200: engine launchers, the
+// per-device state cache and the TMA descriptor helper.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/nnb200.h"
+#include "epilogue.cuh"
+
+namespace nnb200 {
+
+constexpr int kMaxDevices = 64;
+
+// Per-device facts, looked up once per device (never keyed on "the device current at first
+// call").
+struct DeviceInfo {
+    int device = -1;
+    int sm_count = 0;
+    int cc_major = 0;
+    int cc_minor = 0;
+    int32_t* error_word = nullptr;  // device address of this device's error word
+};
+
+// State of the calling thread's current device; nullptr on a CUDA error.
+const DeviceInfo* current_device_info();
+
+// Count a kernel launch (nnb200_launch_count).
+void note_launch(int n = 1);
+
+// Encode a 2-D row-major byte/half tensor [rows][cols] with row pitch `pitch_bytes` as a TMA
+// descriptor with a 128-byte-swizzled box of box_cols x box_rows elements.  elem_bytes is 1
+// or 2.  Returns false if the driver rejects it.
+bool make_tma_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t cols, uint64_t rows,
+                 uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows);
+
+// One 2-D int8 problem (a single batch element), Linear pose: A [m,k] and W [n,k] both
+// k-contiguous.  lda / ldw are row pitches in bytes.
+struct I8Problem {
+    const void* a;
+    const void* w;
+    int64_t m, n, k;
+    int64_t a_stride_m, a_stride_k, w_stride_n, w_stride_k;
+    int32_t a_unsigned;
+};
+
+// True when the tensor-core engine can take the problem: k-contiguous operands whose base
+// and row pitch are 16-byte aligned (the TMA rule).
+bool umma_i8_supported(const I8Problem& p);
+
+int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
+int launch_gemm_i8_generic(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
+int launch_gemm_i8_narrow(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
+bool narrow_i8_supported(const I8Problem& p);
+
+// R_a[m] = sum_k A[m][k] and R_w[n] = sum_k W[n][k] into int32 scratch.
+int launch_i8_sums(const I8Problem& p, int32_t* r_a, int32_t* r_w, cudaStream_t stream);
+
+int launch_q4_1_gemv(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
+int launch_q4_1_gemm_umma(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
+bool q4_1_gemm_umma_supported(const nnb200_q4_1_args& a);
+int launch_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, int64_t k, void* out, int out_f16,
+                       int64_t ld_out, cudaStream_t stream);
+
+inline int cuda_status(cudaError_t e)
+{
+    return e == cudaSuccess ? NNB200_OK : NNB200_INTERNAL;
+}
+
+}  // namespace nnb200

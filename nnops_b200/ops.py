@@ -1,0 +1,159 @@
+"""Thin torch-tensor front end over the C ABI, used by the tests, the bench and the sharded
+layer.  torch provides device memory and streams only; every computation is a libnnb200 call.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import capi
+
+_OUT_TORCH = {"s32": torch.int32, "s8": torch.int8, "u8": torch.uint8, "f32": torch.float32, "f16": torch.float16}
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _dev_array(v, dtype: torch.dtype, device: torch.device, count: int | None):
+    """Scalar -> (None, scalar); tensor/sequence -> (device tensor, neutral scalar)."""
+    if v is None:
+        return None, None
+    if isinstance(v, (int, float)):
+        return None, v
+    t = torch.as_tensor(v, dtype=dtype).to(device).contiguous()
+    if count is not None and t.numel() != count:
+        raise ValueError(f"expected {count} quantization entries, got {t.numel()}")
+    return t, None
+
+
+def gemm_i8_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, out_kind: str, bias=None, relu=False,
+                 activation="none", act_alpha=0.0, act_beta=1.0, min_clip=-math.inf, max_clip=math.inf,
+                 scale_a=1.0, scale_w=1.0, zp_a=0, zp_w=0, out_scale=1.0, out_zp=0, workspace=None,
+                 engine="auto", keep: list | None = None) -> capi.GemmI8Args:
+    """Fill the C argument block.  ``a`` is [M,K] or [B,M,K] (s8/u8), ``w`` the LOGICAL [N,K]
+    (or [B,N,K]) s8 matrix -- pass ``w_kn.transpose(-1,-2)`` for a weight stored [K,N].
+    Tensors created for quantization arrays are appended to ``keep`` so they outlive the call."""
+    keep = keep if keep is not None else []
+    dev = a.device
+    batched = a.dim() == 3 or w.dim() == 3
+    a3 = a if a.dim() == 3 else a.unsqueeze(0)
+    w3 = w if w.dim() == 3 else w.unsqueeze(0)
+    o3 = out if out.dim() == 3 else out.unsqueeze(0)
+    batch = max(a3.shape[0], w3.shape[0]) if batched else 1
+    m, k = a3.shape[1], a3.shape[2]
+    n = w3.shape[1]
+    if w3.shape[2] != k:
+        raise ValueError("K mismatch")
+    sa, sa0 = _dev_array(scale_a, torch.float32, dev, m)
+    sw, sw0 = _dev_array(scale_w, torch.float32, dev, n)
+    za, za0 = _dev_array(zp_a, torch.int32, dev, m)
+    zw, zw0 = _dev_array(zp_w, torch.int32, dev, n)
+    keep.extend(t for t in (sa, sw, za, zw) if t is not None)
+    if bias is not None:
+        bdt = torch.int32 if out_kind in ("s32", "s8", "u8") else _OUT_TORCH[out_kind]
+        bias = torch.as_tensor(bias).to(device=dev, dtype=bdt).contiguous()
+        keep.append(bias)
+
+    def stride_or_one(t, dim, size):
+        return t.stride(dim) if size > 1 else (1 if dim == 2 else t.stride(dim))
+
+    args = capi.GemmI8Args(
+        a=a3.data_ptr(), w=w3.data_ptr(), out=o3.data_ptr(), m=m, n=n, k=k,
+        a_stride_m=a3.stride(1), a_stride_k=stride_or_one(a3, 2, k),
+        w_stride_n=w3.stride(1), w_stride_k=stride_or_one(w3, 2, k),
+        ldc=o3.stride(1), batch=batch,
+        a_batch_stride=a3.stride(0) if a3.shape[0] > 1 else 0,
+        w_batch_stride=w3.stride(0) if w3.shape[0] > 1 else 0,
+        out_batch_stride=o3.stride(0) if o3.shape[0] > 1 else 0,
+        a_unsigned=int(a.dtype == torch.uint8), out_kind=capi.OUT_KINDS[out_kind],
+        bias=bias.data_ptr() if bias is not None else None,
+        relu=int(bool(relu)), activation=capi.ACTIVATIONS[activation],
+        act_alpha=act_alpha, act_beta=act_beta, min_clip=min_clip, max_clip=max_clip,
+        scale_a=sa.data_ptr() if sa is not None else None,
+        scale_w=sw.data_ptr() if sw is not None else None,
+        zp_a=za.data_ptr() if za is not None else None,
+        zp_w=zw.data_ptr() if zw is not None else None,
+        scale_a_scalar=1.0 if sa0 is None else float(sa0), scale_w_scalar=1.0 if sw0 is None else float(sw0),
+        zp_a_scalar=0 if za0 is None else int(za0), zp_w_scalar=0 if zw0 is None else int(zw0),
+        zp_a_nonzero=int(za is not None and bool((za != 0).any().item())),
+        zp_w_nonzero=int(zw is not None and bool((zw != 0).any().item())),
+        out_scale=float(out_scale), out_zp=int(out_zp),
+        workspace=None, workspace_bytes=0, force_engine=capi.ENGINES[engine])
+    need = capi.lib().nnb200_gemm_i8_workspace_bytes(C.byref(args))
+    if need:
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+            keep.append(workspace)
+        args.workspace = workspace.data_ptr()
+        args.workspace_bytes = workspace.numel()
+    return args
+
+
+def gemm_i8(a: torch.Tensor, w: torch.Tensor, *, out_kind: str = "s32", out: torch.Tensor | None = None, **kw):
+    """out = epilogue(a @ w^T) on the current CUDA stream.  Returns the output tensor."""
+    if not a.is_cuda:
+        raise RuntimeError("nnops_b200.gemm_i8 needs CUDA tensors; there is no CPU path")
+    batched = a.dim() == 3 or w.dim() == 3
+    m = a.shape[-2]
+    n = w.shape[-2]
+    if out is None:
+        shape = (max(a.shape[0] if a.dim() == 3 else 1, w.shape[0] if w.dim() == 3 else 1), m, n) if batched else (m, n)
+        out = torch.empty(shape, dtype=_OUT_TORCH[out_kind], device=a.device)
+    keep: list = []
+    args = gemm_i8_args(a, w, out, out_kind=out_kind, keep=keep, **kw)
+    with torch.cuda.device(a.device):
+        capi.check(capi.lib().nnb200_gemm_i8(C.byref(args), _stream_ptr(a.device)), "nnb200_gemm_i8")
+    return out
+
+
+def gemm_i8_engine(a, w, out, **kw) -> str:
+    args = gemm_i8_args(a, w, out, **kw)
+    return capi.ENGINE_NAMES.get(capi.lib().nnb200_gemm_i8_engine(C.byref(args)), "invalid")
+
+
+def q4_1_args(a: torch.Tensor, w_blocks: torch.Tensor, out: torch.Tensor, k: int, *, bias=None, activation="none",
+              act_alpha=0.0, act_beta=1.0, min_clip=-math.inf, max_clip=math.inf, alpha=1.0, engine="auto",
+              keep: list | None = None) -> capi.Q41Args:
+    keep = keep if keep is not None else []
+    if w_blocks.dtype != torch.uint8 or w_blocks.dim() != 2 or w_blocks.stride(1) != 1 or w_blocks.stride(0) % 20:
+        raise ValueError("w_blocks must be a uint8 [N, row_bytes] tensor whose row pitch is a multiple of 20")
+    if a.stride(1) != 1 or out.stride(1) != 1:
+        raise ValueError("activations and output must be row-major")
+    if bias is not None:
+        bias = torch.as_tensor(bias).to(device=a.device, dtype=out.dtype).contiguous()
+        keep.append(bias)
+    return capi.Q41Args(
+        a=a.data_ptr(), w_blocks=w_blocks.data_ptr(), out=out.data_ptr(),
+        m=a.shape[0], n=w_blocks.shape[0], k=k, lda=a.stride(0), ldw_blocks=w_blocks.stride(0) // 20,
+        ldc=out.stride(0), a_f16=int(a.dtype == torch.float16), out_f16=int(out.dtype == torch.float16),
+        bias=bias.data_ptr() if bias is not None else None, activation=capi.ACTIVATIONS[activation],
+        act_alpha=act_alpha, act_beta=act_beta, min_clip=min_clip, max_clip=max_clip, alpha=alpha,
+        workspace=None, workspace_bytes=0, force_engine=capi.Q4_ENGINES[engine])
+
+
+def linear_q4_1(a: torch.Tensor, w_blocks: torch.Tensor, k: int, *, out_dtype: torch.dtype | None = None,
+                out: torch.Tensor | None = None, **kw) -> torch.Tensor:
+    """out[M,N] = a[M,K] @ dequant(w_blocks)[N,K]^T.  ``w_blocks``: uint8 [N, ceil(K/32)*20]."""
+    if not a.is_cuda:
+        raise RuntimeError("nnops_b200.linear_q4_1 needs CUDA tensors; there is no CPU path")
+    if a.dtype not in (torch.float16, torch.float32):
+        raise ValueError("activations must be f16 or f32")
+    if out is None:
+        out = torch.empty((a.shape[0], w_blocks.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+    keep: list = []
+    args = q4_1_args(a, w_blocks, out, k, keep=keep, **kw)
+    with torch.cuda.device(a.device):
+        capi.check(capi.lib().nnb200_linear_q4_1(C.byref(args), _stream_ptr(a.device)), "nnb200_linear_q4_1")
+    return out
+
+
+def q4_1_decode(w_blocks: torch.Tensor, k: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    out = torch.empty((w_blocks.shape[0], k), dtype=out_dtype, device=w_blocks.device)
+    with torch.cuda.device(w_blocks.device):
+        capi.check(capi.lib().nnb200_q4_1_decode(w_blocks.data_ptr(), w_blocks.stride(0) // 20, w_blocks.shape[0], k,
+                                                 out.data_ptr(), int(out_dtype == torch.float16), out.stride(0),
+                                                 _stream_ptr(w_blocks.device)), "nnb200_q4_1_decode")
+    return out

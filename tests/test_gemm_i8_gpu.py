@@ -1,0 +1,183 @@
+"""Parity of the int8 CUDA engines with the CPU oracle, through the C ABI.
+
+Mirrors the reference's differential CUDA tests (tests/test_cuda_matmul.cpp:681-889,
+tests/test_cuda_linear.cpp:190-351): same bytes to both sides, integer outputs compared
+byte for byte; ragged M/N/K tails, odd N, per-token / per-channel parameters, all five
+destinations, both operand poses, batch broadcast -- plus pitched views with canary bytes,
+which the reference leaves untested.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from nnops_b200 import ops, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_case(dev, m, n, k, *, out_kind="s32", a_unsigned=False, relu=False, bias=True, per_token=False,
+              per_channel=False, zero_points=False, out_scale=1.0, out_zp=0, engine="auto", seed=0,
+              expect_engine=None, act="none", min_clip=-np.inf, max_clip=np.inf):
+    rng = np.random.default_rng(seed)
+    a = rng.integers(0, 256, (m, k), dtype=np.uint8) if a_unsigned else rng.integers(-127, 128, (m, k), dtype=np.int8)
+    w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    kw = {}
+    kw["scale_a"] = rng.uniform(0.01, 0.03, m).astype(np.float32) if per_token else 0.02
+    kw["scale_w"] = rng.uniform(0.001, 0.02, n).astype(np.float32) if per_channel else 0.01
+    if zero_points:
+        kw["zp_a"] = rng.integers(-9, 10, m).astype(np.int32) if per_token else (128 if a_unsigned else 3)
+        kw["zp_w"] = rng.integers(-9, 10, n).astype(np.int32) if per_channel else -2
+    int_out = out_kind in ("s32", "s8", "u8")
+    b = None
+    if bias:
+        b = rng.integers(-1000, 1001, n).astype(np.int32) if int_out else \
+            (rng.normal(size=n) * 3).astype(np.float32 if out_kind == "f32" else np.float16)
+    common = dict(out_kind=out_kind, bias=b, out_scale=out_scale, out_zp=out_zp, **kw)
+    want = oracle.gemm_i8(a, w, relu=relu, min_clip=min_clip, max_clip=max_clip, **common)
+    ta, tw = torch.from_numpy(a).to(dev), torch.from_numpy(w).to(dev)
+    if expect_engine is not None:
+        o = torch.empty((m, n), dtype=ops._OUT_TORCH[out_kind], device=dev)
+        assert ops.gemm_i8_engine(ta, tw, o, engine=engine, **common) == expect_engine
+    got = ops.gemm_i8(ta, tw, relu=relu, activation=("relu" if relu and not int_out else act), engine=engine,
+                      min_clip=min_clip, max_clip=max_clip, **common)
+    torch.cuda.synchronize()
+    got = got.cpu().numpy()
+    assert got.shape == want.shape
+    if not np.array_equal(got.view(np.uint8), want.view(np.uint8)):
+        bad = np.argwhere(got != want)
+        raise AssertionError(f"{len(bad)} mismatches of {got.size}; first {bad[:5].tolist()} "
+                             f"got {got[tuple(bad[0])]} want {want[tuple(bad[0])]}")
+
+
+@pytest.mark.parametrize("engine", ["umma", "generic"])
+def test_tiny_s32(cuda_device, nnb200_lib, engine):
+    _run_case(cuda_device, 128, 64, 128, engine=engine, bias=False)
+
+
+@pytest.mark.parametrize("engine", ["umma", "generic"])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (128, 256, 512), (256, 512, 1024), (100, 200, 300),
+                                   (129, 257, 130), (1, 16, 16), (17, 33, 48), (300, 1000, 96), (64, 4096, 64)])
+def test_s32_shapes(cuda_device, nnb200_lib, engine, shape):
+    m, n, k = shape
+    _run_case(cuda_device, m, n, k, engine=engine, seed=m + n + k)
+
+
+@pytest.mark.parametrize("out_kind", ["s32", "s8", "u8", "f32", "f16"])
+@pytest.mark.parametrize("relu", [False, True])
+def test_destinations_umma(cuda_device, nnb200_lib, out_kind, relu):
+    _run_case(cuda_device, 200, 330, 512, out_kind=out_kind, relu=relu, per_token=True, per_channel=True,
+              out_scale=1.7, out_zp=0 if out_kind == "s32" else 5, engine="umma", expect_engine="umma", seed=7)
+
+
+@pytest.mark.parametrize("out_kind", ["s32", "s8", "u8", "f32", "f16"])
+@pytest.mark.parametrize("a_unsigned", [False, True])
+def test_zero_points(cuda_device, nnb200_lib, out_kind, a_unsigned):
+    for engine in ("umma", "generic"):
+        _run_case(cuda_device, 77, 130, 272, out_kind=out_kind, a_unsigned=a_unsigned, relu=True, per_token=True,
+                  per_channel=True, zero_points=True, out_scale=2.3, out_zp=0 if out_kind == "s32" else -3,
+                  engine=engine, seed=11)
+
+
+def test_scalar_zero_points_u8(cuda_device, nnb200_lib):
+    _run_case(cuda_device, 64, 96, 160, out_kind="s8", a_unsigned=True, zero_points=True, out_scale=3.0, engine="umma")
+
+
+def test_fp_clip(cuda_device, nnb200_lib):
+    _run_case(cuda_device, 40, 100, 256, out_kind="f32", per_channel=True, min_clip=-1.5, max_clip=2.5, engine="umma")
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 16])
+def test_narrow_decode(cuda_device, nnb200_lib, m):
+    _run_case(cuda_device, m, 520, 1024, out_kind="s8", relu=True, per_channel=True, out_scale=1.1,
+              expect_engine="narrow", seed=m)
+    _run_case(cuda_device, m, 130, 4096 + 16, out_kind="s32", a_unsigned=True, zero_points=True, per_token=True,
+              per_channel=True, engine="narrow", seed=m + 50)
+
+
+def test_transposed_poses_use_generic(cuda_device, nnb200_lib):
+    rng = np.random.default_rng(5)
+    m, n, k = 70, 90, 200
+    a_km = rng.integers(-127, 128, (k, m), dtype=np.int8)   # MatMul transpose_a storage
+    w_kn = rng.integers(-127, 128, (k, n), dtype=np.int8)   # MatMul without transpose_b
+    want = oracle.gemm_i8(a_km.T, w_kn.T, out_kind="s8", out_scale=40.0)
+    ta = torch.from_numpy(a_km).to(cuda_device).t()
+    tw = torch.from_numpy(w_kn).to(cuda_device).t()
+    got = ops.gemm_i8(ta, tw, out_kind="s8", out_scale=40.0)
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_batched_and_broadcast(cuda_device, nnb200_lib):
+    rng = np.random.default_rng(6)
+    b, m, n, k = 3, 130, 140, 256
+    a = rng.integers(-127, 128, (b, m, k), dtype=np.int8)
+    w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    sw = rng.uniform(0.001, 0.02, n).astype(np.float32)
+    got = ops.gemm_i8(torch.from_numpy(a).to(cuda_device), torch.from_numpy(w).to(cuda_device), out_kind="s8",
+                      scale_w=sw, out_scale=0.5).cpu().numpy()
+    for i in range(b):
+        assert np.array_equal(got[i], oracle.gemm_i8(a[i], w, out_kind="s8", scale_w=sw, out_scale=0.5))
+
+
+@pytest.mark.parametrize("out_kind", ["s8", "s32"])
+def test_pitched_views_keep_padding(cuda_device, nnb200_lib, out_kind):
+    """Row pitches wider than the rows on every operand; padding bytes of the output stay untouched."""
+    rng = np.random.default_rng(8)
+    m, n, k = 150, 200, 260
+    a_pad = torch.from_numpy(rng.integers(-127, 128, (m, k + 28), dtype=np.int8)).to(cuda_device)
+    w_pad = torch.from_numpy(rng.integers(-127, 128, (n, k + 12), dtype=np.int8)).to(cuda_device)
+    a, w = a_pad[:, :k], w_pad[:, :k]
+    tdt = ops._OUT_TORCH[out_kind]
+    out_pad = torch.full((m, n + 24), 0x5A if out_kind == "s8" else 0x5A5A5A5A, dtype=tdt, device=cuda_device)
+    ops.gemm_i8(a, w, out_kind=out_kind, out=out_pad[:, :n], out_scale=30.0, relu=True)
+    want = oracle.gemm_i8(a.cpu().numpy(), w.cpu().numpy(), out_kind=out_kind, out_scale=30.0, relu=True)
+    got = out_pad.cpu().numpy()
+    assert np.array_equal(got[:, :n], want)
+    assert np.all(got[:, n:] == (0x5A if out_kind == "s8" else 0x5A5A5A5A))
+
+
+def test_unaligned_falls_back(cuda_device, nnb200_lib):
+    """K = 100 rows are not 16-byte pitched: the tensor-core engine must decline, result still exact."""
+    rng = np.random.default_rng(9)
+    a = torch.from_numpy(rng.integers(-127, 128, (130, 100), dtype=np.int8)).to(cuda_device)
+    w = torch.from_numpy(rng.integers(-127, 128, (140, 100), dtype=np.int8)).to(cuda_device)
+    o = torch.empty((130, 140), dtype=torch.int32, device=cuda_device)
+    assert ops.gemm_i8_engine(a, w, o, out_kind="s32") == "generic"
+    got = ops.gemm_i8(a, w, out=o)
+    assert np.array_equal(got.cpu().numpy(), oracle.gemm_i8(a.cpu().numpy(), w.cpu().numpy()))
+
+
+def test_config1_bit_exact(cuda_device, nnb200_lib):
+    c = synth.config1()
+    got = ops.gemm_i8(torch.from_numpy(c.a).to(cuda_device), torch.from_numpy(c.w).to(cuda_device), **c.kwargs())
+    assert np.array_equal(got.cpu().numpy(), oracle.gemm_i8(c.a, c.w, **c.kwargs()))
+
+
+@pytest.mark.parametrize("out_scale", [0.05, 1.6])
+def test_config2_bit_exact(cuda_device, nnb200_lib, out_scale):
+    c = synth.config2(out_scale=out_scale)
+    got = ops.gemm_i8(torch.from_numpy(c.a).to(cuda_device), torch.from_numpy(c.w).to(cuda_device), **c.kwargs())
+    want = oracle.gemm_i8(c.a, c.w, **c.kwargs())
+    got = got.cpu().numpy()
+    assert np.array_equal(got, want)
+    if out_scale > 1:
+        inside = np.count_nonzero((want > 0) & (want < 127))
+        assert inside > want.size // 4, "in-range variant must exercise the rounding path"
+
+
+def test_config5_rows_and_linearity(cuda_device, nnb200_lib):
+    """Full-size sharded shape on one GPU: a sample of rows against the oracle, plus an exact
+    size-independent property of the s32 route (additivity in A)."""
+    c = synth.config5()
+    ta, tw = torch.from_numpy(c.a).to(cuda_device), torch.from_numpy(c.w).to(cuda_device)
+    got = ops.gemm_i8(ta, tw, **c.kwargs())
+    rows = np.random.default_rng(0).choice(c.a.shape[0], 48, replace=False)
+    kw = c.kwargs()
+    want = oracle.gemm_i8(np.ascontiguousarray(c.a[rows]), c.w, **kw)
+    assert np.array_equal(got[torch.from_numpy(rows).to(cuda_device)].cpu().numpy(), want)
+    # Linearity: (A1 + A2) W^T == A1 W^T + A2 W^T exactly in int32 (values halved to stay in s8).
+    a1 = (ta // 2)
+    a2 = ta - a1
+    s = ops.gemm_i8(a1, tw) + ops.gemm_i8(a2, tw)
+    full = ops.gemm_i8(ta, tw)
+    assert torch.equal(s, full)

@@ -1,0 +1,141 @@
+"""CPU tests of the checkers: the plain-C restatement against the hand-computed vectors of the
+reference's own tests (tests/test_matmul_int8.cpp:106-285, tests/test_q4_1.cpp), against the
+committed golden fixtures produced by the compiled reference, and -- where the compiled
+reference can run on this host -- against it directly."""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+IMPLS = ["port"] + (["ref"] if oracle.have_ref() else [])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_kat_basic_s32(impl):
+    a = np.array([[1, -2, 3], [-4, 5, -6]], np.int8)
+    b = np.array([[1, 2], [3, 4], [5, 6]], np.int8)  # stored [K,N]
+    assert oracle.gemm_i8(a, b.T, impl=impl).ravel().tolist() == [10, 12, -19, -24]
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_kat_zero_points_s32(impl):
+    a = np.array([[1, 2, 3], [4, 5, 6]], np.int8)
+    w = np.array([[7, 8, 9], [10, 11, 12]], np.int8)
+    out = oracle.gemm_i8(a, w, zp_a=np.array([1, 2]), zp_w=np.array([3, 4]), scale_a=np.ones(2),
+                         scale_w=np.ones(2), impl=impl)
+    assert out.ravel().tolist() == [17, 23, 47, 65]
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_kat_u8_zero_points_s32(impl):
+    a = np.array([[130, 128, 3], [200, 255, 0]], np.uint8)
+    b = np.array([[1, -4], [2, 5], [3, -6]], np.int8)
+    out = oracle.gemm_i8(a, b.T, zp_a=np.array([128, 100]), scale_a=np.ones(2), zp_w=3, impl=impl)
+    assert out.ravel().tolist() == [-4, 1111, -355, 510]
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_kat_requant_and_clamp(impl):
+    out = oracle.gemm_i8(np.array([[4, 6]], np.int8), np.ones((2, 2), np.int8), out_kind="s8", out_scale=2.0,
+                         impl=impl)
+    assert out.ravel().tolist() == [5, 5]
+    out = oracle.gemm_i8(np.array([[100, 100]], np.int8), np.full((2, 2), 100, np.int8), out_kind="s8", impl=impl)
+    assert out.ravel().tolist() == [127, 127]
+
+
+def test_requant_rounds_half_away_from_zero():
+    # acc = +/-1, +/-3 with scale 0.5 -> +/-0.5, +/-1.5 -> +/-1, +/-2 (ties away), not ties-to-even (0, 2).
+    a = np.array([[1], [-1], [3], [-3]], np.int8)
+    w = np.array([[1]], np.int8)
+    out = oracle.gemm_i8(a, w, out_kind="s8", out_scale=2.0)
+    assert out.ravel().tolist() == [1, -1, 2, -2]
+
+
+def test_requant_f32_half_quirk():
+    # x = 0.49999997 (largest f32 below 0.5): x + 0.5 rounds to 1.0 in f32, so the result is 1.
+    x = np.nextafter(np.float32(0.5), np.float32(0))
+    out = oracle.gemm_i8(np.array([[1]], np.int8), np.array([[1]], np.int8), out_kind="s8", scale_a=float(x))
+    assert out.item() == 1
+
+
+def test_f16_conversions_match_numpy():
+    lib = oracle.port_lib()
+    rng = np.random.default_rng(1)
+    for bits in rng.integers(0, 1 << 16, 4000):
+        h = np.uint16(bits).view(np.float16)
+        if np.isnan(h):
+            continue
+        assert lib.oracle_f16_to_f32(int(bits)) == float(np.float32(h))
+    vals = np.concatenate([rng.normal(size=2000), rng.normal(size=500) * 1e-6, rng.normal(size=500) * 7e4,
+                           [0.0, 65504.0, 65519.9, 65520.0, 6e-8, 2.98e-8, 2.99e-8]]).astype(np.float32)
+    for v in vals:
+        assert lib.oracle_f32_to_f16(float(v)) == int(np.float32(v).astype(np.float16).view(np.uint16))
+
+
+def test_q4_1_block_layout():
+    # d = 0.5, m = -1; byte j = j | ((15-j) << 4): value j -> j*0.5-1, value j+16 -> (15-j)*0.5-1.
+    blk = np.zeros(20, np.uint8)
+    blk[0:2] = np.array([0.5], np.float16).view(np.uint8)
+    blk[2:4] = np.array([-1.0], np.float16).view(np.uint8)
+    blk[4:] = [j | ((15 - j) << 4) for j in range(16)]
+    out = oracle.q4_1_decode(blk, 32)
+    exp = [j * 0.5 - 1 for j in range(16)] + [(15 - j) * 0.5 - 1 for j in range(16)]
+    assert out.tolist() == exp
+    assert oracle.q4_1_decode(blk, 20).tolist() == exp[:20]  # partial block
+
+
+def test_q4_1_quantize_round_trip():
+    rng = np.random.default_rng(2)
+    x = rng.normal(size=96 + 7).astype(np.float32)
+    blocks = oracle.q4_1_quantize(x)
+    assert blocks.size == 4 * 20
+    y = oracle.q4_1_decode(blocks, x.size)
+    d = np.repeat(blocks.reshape(4, 20)[:, :2].copy().view(np.float16).astype(np.float32), 32)[: x.size]
+    assert np.all(np.abs(x - y) <= 0.5 * d + 2e-3)
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="compiled reference not runnable on this host")
+def test_port_matches_reference_random():
+    rng = np.random.default_rng(3)
+    for (m, n, k) in [(37, 53, 600), (6, 200, 33), (130, 70, 257)]:
+        a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+        w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+        kw = dict(scale_a=rng.uniform(0.01, 0.03, m).astype(np.float32),
+                  scale_w=rng.uniform(0.001, 0.02, n).astype(np.float32),
+                  zp_a=rng.integers(-5, 5, m).astype(np.int32), zp_w=rng.integers(-5, 5, n).astype(np.int32))
+        for kind in ("s32", "s8", "u8", "f32", "f16"):
+            bias = rng.integers(-1000, 1000, n)
+            b = bias.astype(np.int32) if kind in ("s32", "s8", "u8") else bias.astype(np.float32) * 0.01
+            for relu in (False, True):
+                p = oracle.gemm_i8(a, w, out_kind=kind, bias=b, relu=relu, out_scale=1.6,
+                                   out_zp=0 if kind == "s32" else 3, impl="port", **kw)
+                r = oracle.gemm_i8(a, w, out_kind=kind, bias=b, relu=relu, out_scale=1.6,
+                                   out_zp=0 if kind == "s32" else 3, impl="ref", **kw)
+                assert np.array_equal(p.view(np.uint8), r.view(np.uint8)), (m, n, k, kind, relu)
+
+
+def _golden_cases():
+    return sorted(GOLDEN.glob("*.npz"))
+
+
+@pytest.mark.parametrize("path", _golden_cases(), ids=lambda p: p.stem)
+def test_port_matches_golden(path):
+    """Fixtures written by tests/golden/make_golden.py from the compiled reference."""
+    z = np.load(path)
+    meta = json.loads(str(z["meta"]))
+    if meta["op"] == "gemm_i8":
+        kw = {k: (z[k] if k in z.files else meta["scalars"][k]) for k in meta["kw"]}
+        a = z["a"].T if meta.get("a_transposed") else z["a"]
+        w = z["w"].T if meta.get("w_kn") else z["w"]
+        out = oracle.gemm_i8(a, w, out_kind=meta["out_kind"], relu=meta["relu"], **kw)
+        assert np.array_equal(out.view(np.uint8), z["out"].view(np.uint8))
+    else:
+        out = oracle.q4_1_matmul(z["a"], z["w_blocks"], meta["k"], out_dtype=meta["out_dtype"],
+                                 w_round_f16=meta["out_dtype"] == "f16")
+        ref = z["out"].astype(np.float32)
+        tol = meta["rtol"] * np.abs(ref) + meta["rtol"] * float(np.sqrt(np.mean(ref * ref)))
+        assert np.all(np.abs(out.astype(np.float32) - ref) <= tol)

@@ -1,0 +1,97 @@
+"""Parity of the Q4_1 CUDA kernels with the CPU oracle, through the C ABI.
+
+Tolerances follow the benchmark contract: f32 output rtol 2e-3, f16 output rtol 1e-2, each
+with an absolute floor of rtol * rms(reference) (a purely relative test is unsatisfiable near
+zero).  The oracle accumulates in f64, so it is an order-free expected value like the one the
+reference's own test recomputes (tests/test_matmul_q4_1.cpp:190-224).
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from nnops_b200 import ops, synth
+
+pytestmark = pytest.mark.gpu
+
+RTOL_F32 = 2e-3
+RTOL_F16 = 1e-2
+
+
+def _close(got, ref, rtol):
+    got = got.astype(np.float32)
+    ref = ref.astype(np.float32)
+    tol = rtol * np.abs(ref) + rtol * float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    bad = np.abs(got - ref) > tol
+    assert not bad.any(), f"{bad.sum()} of {bad.size} outside tolerance; max err {np.abs(got - ref).max()}"
+
+
+def test_decode_matches_oracle_bitwise(cuda_device, nnb200_lib):
+    rng = np.random.default_rng(0)
+    for k in (32, 64, 100, 4096):
+        wb = synth.q4_1_weights(rng, 9, k)
+        got = ops.q4_1_decode(torch.from_numpy(wb).to(cuda_device), k).cpu().numpy()
+        want = np.stack([oracle.q4_1_decode(wb[i], k) for i in range(wb.shape[0])])
+        assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 11])
+@pytest.mark.parametrize("a_dtype,out_dtype", [("f16", "f32"), ("f16", "f16"), ("f32", "f32")])
+def test_gemv_small(cuda_device, nnb200_lib, m, a_dtype, out_dtype):
+    rng = np.random.default_rng(m)
+    n, k = 203, 1000   # ragged N, K not a multiple of 32
+    wb = synth.q4_1_weights(rng, n, k)
+    a = rng.standard_normal((m, k)).astype(np.float16 if a_dtype == "f16" else np.float32)
+    bias = rng.standard_normal(n).astype(np.float32 if out_dtype == "f32" else np.float16)
+    want = oracle.q4_1_matmul(a, wb, k, out_dtype=out_dtype, bias=bias)
+    got = ops.linear_q4_1(torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device), k,
+                          out_dtype=torch.float32 if out_dtype == "f32" else torch.float16, bias=bias,
+                          engine="gemv")
+    _close(got.cpu().numpy(), want, RTOL_F32 if out_dtype == "f32" else RTOL_F16)
+
+
+@pytest.mark.parametrize("m", [1, 8])
+def test_config3_gemv(cuda_device, nnb200_lib, m):
+    c = synth.config3(m)
+    want = oracle.q4_1_matmul(c.a, c.w_blocks, c.k, out_dtype="f32")
+    got = ops.linear_q4_1(torch.from_numpy(c.a).to(cuda_device), torch.from_numpy(c.w_blocks).to(cuda_device), c.k,
+                          out_dtype=torch.float32)
+    _close(got.cpu().numpy(), want, RTOL_F32)
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 64), (128, 256, 256), (130, 300, 512), (64, 1000, 160),
+                                   (300, 260, 1000), (2048, 1024, 512)])
+@pytest.mark.parametrize("out_dtype", ["f16", "f32"])
+def test_gemm_umma_shapes(cuda_device, nnb200_lib, shape, out_dtype):
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    wb = synth.q4_1_weights(rng, n, k)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    want = oracle.q4_1_matmul(a, wb, k, out_dtype=out_dtype, w_round_f16=True)
+    ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device)
+    tdt = torch.float16 if out_dtype == "f16" else torch.float32
+    o = torch.empty((m, n), dtype=tdt, device=cuda_device)
+    got = ops.linear_q4_1(ta, tw, k, out=o, engine="gemm")
+    _close(got.cpu().numpy(), want, RTOL_F16 if out_dtype == "f16" else RTOL_F32)
+
+
+def test_gemm_epilogue_bias_relu(cuda_device, nnb200_lib):
+    rng = np.random.default_rng(4)
+    m, n, k = 256, 384, 256
+    wb = synth.q4_1_weights(rng, n, k)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    bias = rng.standard_normal(n).astype(np.float16)
+    want = np.maximum(oracle.q4_1_matmul(a, wb, k, out_dtype="f32", w_round_f16=True) + bias.astype(np.float32), 0)
+    got = ops.linear_q4_1(torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device), k,
+                          out_dtype=torch.float16, bias=bias, activation="relu", engine="gemm")
+    _close(got.cpu().numpy(), want, RTOL_F16)
+
+
+def test_config4_sampled(cuda_device, nnb200_lib):
+    """Full prefill shape: sampled rows against the oracle (the CPU takes seconds per 32 rows)."""
+    c = synth.config4()
+    got = ops.linear_q4_1(torch.from_numpy(c.a).to(cuda_device), torch.from_numpy(c.w_blocks).to(cuda_device), c.k,
+                          out_dtype=torch.float16)
+    rows = np.random.default_rng(1).choice(c.a.shape[0], 24, replace=False)
+    want = oracle.q4_1_matmul(np.ascontiguousarray(c.a[rows]), c.w_blocks, c.k, out_dtype="f16", w_round_f16=True)
+    _close(got[torch.from_numpy(rows).to(cuda_device)].cpu().numpy(), want, RTOL_F16)
