@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (all N): the sharded int8 QuantLinear configuration -- A s8 [4096,8192] x W s8
+[28672,8192] -> s8 [4096,28672] with int32 bias, Relu and per-channel requantisation -- on
+seeded synthetic tensors.  At N > 1 W, scales and bias are column-sharded N/g per rank and the
+[M,N] output is reassembled on every rank (NCCL all-gather + interleave); total work is fixed,
+so scaling is "strong".  One step = one pass of that path.  Prints ONE JSON line (rank 0).
+
+``--impl reference`` times the reference's own CPU implementation of the same path
+(oracle/_ref when it was compiled, else the C restatement) on the host cores, on a bounded
+sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M, N, K = 4096, 28672, 8192
+METRIC = "int8_quantlinear_tops"
+UNIT = "TOPS"
+WORKLOAD = "sharded int8 QuantLinear s8[4096,8192] x s8[28672,8192] -> s8, bias+Relu+per-channel requant"
+
+
+def read_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # Under load = the upper half of the samples (idle samples before/after are excluded).
+        load = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_reference_run(sample_rows: int, steps: int, warmup: int):
+    """Reference CPU route (or the port) on the first ``sample_rows`` rows of A, all of W."""
+    import oracle
+    from nnops_b200 import synth
+    c = synth.config5()
+    a = np.ascontiguousarray(c.a[:sample_rows])
+    use_ref = oracle.have_ref()
+    threads = os.cpu_count() or 1
+    kw = c.kwargs()
+
+    def call():
+        if use_ref:
+            return oracle.gemm_i8(a, c.w, impl="ref", threads=threads, **kw)
+        return oracle.gemm_i8(a, c.w, impl="port", **kw)
+
+    for _ in range(warmup):
+        call()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        call()
+    dt = (time.perf_counter() - t0) / steps
+    ops_count = 2.0 * sample_rows * N * K
+    return {"value": ops_count / dt / 1e12, "unit": UNIT, "cores": threads,
+            "kind": "reference" if use_ref else "port",
+            "sample": f"first {sample_rows} of {M} activation rows x all {N} channels, K={K}; "
+                      f"{steps} timed calls after {warmup} warm-ups, wall clock",
+            "ms_per_call": dt * 1e3}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_rows = 512
+    r = cpu_reference_run(sample_rows, max(1, args.steps), max(1, args.warmup))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_call"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "sample_rows": sample_rows},
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def secondary_q4_1(torch, dev, peaks):
+    """Q4_1 decode GEMV (M=1, M=8) in HBM GB/s and the prefill GEMM in TFLOP/s, reported beside
+    the headline.  The 10 MiB weight matrix fits in L2, so the GEMV cycles over enough distinct
+    weight replicas (>= 3x L2) inside one CUDA graph that every launch streams from HBM."""
+    from nnops_b200 import ops, synth
+    out = {}
+    l2 = torch.cuda.get_device_properties(dev).L2_cache_size
+    for m in (1, 8):
+        c = synth.config3(m)
+        reps = max(8, int(3 * l2 // c.w_blocks.size) + 1)
+        w0 = torch.from_numpy(c.w_blocks).to(dev)
+        ws = [w0] + [w0.clone() for _ in range(reps - 1)]
+        a = torch.from_numpy(c.a).to(dev)
+        o = torch.empty((m, c.w_blocks.shape[0]), dtype=torch.float32, device=dev)
+        for w in ws[:3]:
+            ops.linear_q4_1(a, w, c.k, out=o)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g, stream=s):
+                for w in ws:
+                    ops.linear_q4_1(a, w, c.k, out=o)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = 20
+        e0.record()
+        for _ in range(iters):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (iters * reps)
+        gbs = c.bytes / us / 1e3
+        out[f"q4_1_gemv_m{m}"] = {"gbs": gbs, "us_per_call": us, "bytes_per_call": c.bytes,
+                                  "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "replicas": reps}
+        del ws, g
+    c = synth.config4()
+    a, w = torch.from_numpy(c.a).to(dev), torch.from_numpy(c.w_blocks).to(dev)
+    o = torch.empty((c.a.shape[0], c.w_blocks.shape[0]), dtype=torch.float16, device=dev)
+    for _ in range(3):
+        ops.linear_q4_1(a, w, c.k, out=o)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        ops.linear_q4_1(a, w, c.k, out=o)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 10
+    tf = c.flops / ms / 1e9
+    out["q4_1_gemm"] = {"tflops": tf, "ms_per_call": ms, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-secondary", action="store_true", help="skip the Q4_1 and CPU-baseline side measurements")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from nnops_b200 import build, capi, synth
+    from nnops_b200.sharded import ShardedLinearI8, shard_rows
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun for N > 1")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the CUDA library is the only implementation")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    build.build()
+    lib = capi.lib()
+    peaks = read_peaks()
+
+    # ---- inputs: identical seeded bytes on every rank; W / scales / bias sharded by rows ----
+    c = synth.config5()
+    a_host = torch.from_numpy(c.a).pin_memory()
+    a = a_host.to(dev)
+    w = torch.from_numpy(np.ascontiguousarray(shard_rows(c.w, world, rank))).to(dev)
+    layer = ShardedLinearI8(w, n_total=N, world=world, rank=rank, out_kind="s8",
+                            bias_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.bias, world, rank))).to(dev),
+                            scale_w_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.scale_w, world, rank))).to(dev),
+                            scale_a=c.scale_a, out_scale=c.out_scale, relu=True)
+    out = torch.empty((M, N), dtype=torch.int8, device=dev)
+    out_host = torch.empty((M, N), dtype=torch.int8).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing: `value` ----
+    for _ in range(max(3, args.warmup)):
+        layer.forward(a, out)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    k_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.nnb200_launch_count()
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        # Per-launch events around the GEMM itself (the dominant kernel), on the launching stream.
+        k_ev[i][0].record()
+        layer.local(a, out)
+        k_ev[i][1].record()
+        layer.reassemble(out)
+    e1.record()
+    barrier()
+    launches = lib.nnb200_launch_count() - launches0
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    kernel_ms = max_over_ranks(sum(s.elapsed_time(e) for s, e in k_ev) / args.steps)
+    if rank == 0:
+        time.sleep(0.2)
+        clocks = sampler.stop()
+    total_ops = 2.0 * M * N * K
+    value = total_ops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end: host activations in, host result out, every step ----
+    h2d = a_host.numel()
+    d2h = out_host.numel()
+    for _ in range(2):
+        a.copy_(a_host, non_blocking=True)
+        layer.forward(a, out)
+        out_host.copy_(out, non_blocking=True)
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        a.copy_(a_host, non_blocking=True)
+        layer.forward(a, out)
+        out_host.copy_(out, non_blocking=True)
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
+    e2e_value = total_ops / (e2e_ms * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel (the tcgen05 GEMM) ----
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    per_launch_ops = total_ops / world
+    achieved = per_launch_ops / (kernel_ms * 1e-3) / 1e12
+    traffic = None
+    tp = ROOT / "profiles" / "dram_traffic.json"
+    if tp.exists():
+        try:
+            traffic = json.loads(tp.read_text()).get("gemm_i8_umma_cfg5_bytes_per_launch")
+            if traffic is not None and world > 1:
+                traffic = None  # captured for the single-GPU launch only
+        except (ValueError, OSError):
+            traffic = None
+
+    err = capi.take_device_error()
+    if err != 0:
+        raise SystemExit(f"device error word = {err}")
+
+    extra = {}
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_secondary:
+        extra = secondary_q4_1(torch, dev, peaks)
+        cpu_baseline = cpu_reference_run(1024, 5, 2)
+        cpu_baseline = {k: cpu_baseline[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "shards": world,
+                       "reassembly": "none" if world == 1 else "nccl all-gather + interleave kernel",
+                       "l2": "inputs (268 MB) exceed L2 (126 MB); no flush needed"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
+                         "frac": achieved / int8_peak, "traffic": traffic,
+                         "peak_source": f"2 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s): "
+                                        "int8 tensor rate is twice the bf16 rate; nominal dense int8 is 4500",
+                         "kernel": "gemm_i8_umma_kernel<256,S8>", "kernel_ms": kernel_ms,
+                         "ops_per_launch": per_launch_ops},
+            "cpu_baseline": cpu_baseline,
+        }
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -164,6 +164,16 @@ NNB200_API int nnb200_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int6
                        int32_t out_f16, int64_t ld_out, void* stream);
 
 /*
+ * Column-sharded Linear, reassembly step: `gathered` holds `shards` dense slabs
+ * [shards][m][row_bytes_per_shard] (what an all-gather of per-rank [m, n/shards] outputs
+ * produces); writes the row-major [m][shards*row_bytes_per_shard] matrix with row pitch
+ * out_pitch_bytes.  All sizes and pointers must be 16-byte multiples.  No counterpart in the
+ * reference, which has no multi-GPU code.
+ */
+NNB200_API int nnb200_interleave_shards(const void* gathered, void* out, int64_t m, int64_t row_bytes_per_shard,
+                                        int32_t shards, int64_t out_pitch_bytes, void* stream);
+
+/*
  * Kernels never spin forever: a pipeline wait that runs out records a code in a per-device
  * error word and the kernel exits.  This synchronises the device, returns that word through
  * *code (0 = no error) and clears it.

@@ -70,6 +70,8 @@ SYMBOLS = [
     ("nnb200_q4_1_engine", C.c_int, [C.POINTER(Q41Args)]),
     ("nnb200_q4_1_decode", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32,
                                      C.c_int64, C.c_void_p]),
+    ("nnb200_interleave_shards", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64,
+                                           C.c_void_p]),
     ("nnb200_take_device_error", C.c_int, [C.POINTER(C.c_int32)]),
     ("nnb200_copy_h2d_async", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("nnb200_is_device_pointer", C.c_int, [C.c_void_p]),

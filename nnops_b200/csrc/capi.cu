@@ -342,6 +342,30 @@ int nnb200_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, i
     return launch_q4_1_decode(w_blocks, ldw_blocks, rows, k, out, out_f16, ld_out, static_cast<cudaStream_t>(stream));
 }
 
+int nnb200_interleave_shards(const void* gathered, void* out, int64_t m, int64_t row_bytes_per_shard, int32_t shards,
+                              int64_t out_pitch_bytes, void* stream)
+{
+    if (m < 0 || row_bytes_per_shard < 0 || shards < 1 || out_pitch_bytes < row_bytes_per_shard * shards) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if (m == 0 || row_bytes_per_shard == 0) {
+        return NNB200_OK;
+    }
+    if (gathered == nullptr || out == nullptr) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if ((row_bytes_per_shard & 15) != 0 || (out_pitch_bytes & 15) != 0 ||
+        (reinterpret_cast<uintptr_t>(gathered) & 15u) != 0 || (reinterpret_cast<uintptr_t>(out) & 15u) != 0) {
+        return NNB200_UNSUPPORTED;
+    }
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    return launch_interleave_shards(gathered, out, m, row_bytes_per_shard, shards, out_pitch_bytes, *dev,
+                                    static_cast<cudaStream_t>(stream));
+}
+
 int nnb200_take_device_error(int32_t* code)
 {
     const DeviceInfo* dev = current_device_info();

@@ -65,6 +65,9 @@ bool q4_1_gemm_umma_supported(const nnb200_q4_1_args& a);
 int launch_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, int64_t k, void* out, int out_f16,
                        int64_t ld_out, cudaStream_t stream);
 
+int launch_interleave_shards(const void* src, void* dst, int64_t m, int64_t row_bytes_per_shard, int g,
+                             int64_t dst_pitch_bytes, const DeviceInfo& dev, cudaStream_t stream);
+
 inline int cuda_status(cudaError_t e)
 {
     return e == cudaSuccess ? NNB200_OK : NNB200_INTERNAL;
