@@ -121,6 +121,28 @@ NNB200_API size_t nnb200_gemm_i8_workspace_bytes(const nnb200_gemm_i8_args* args
  * (src/backend/cuda/matmul/matmul_i8.cuh:284-446). */
 NNB200_API int nnb200_gemm_i8(const nnb200_gemm_i8_args* args, void* stream);
 
+/*
+ * Same computation as nnb200_gemm_i8 for callers that may not allocate device memory and so
+ * have no workspace to pass: a plugin inside an inference runtime, or any code on a
+ * latency-critical path, where cudaMalloc is off limits because it serialises the device and
+ * can fail at run time.  The scratch the zero-point-compensated call needs (the int32 row sums
+ * of A and W) is kept in a fixed array of NNB200_STATIC_SCRATCH_BYTES inside the library, in
+ * the memory of every GPU that loads it, for the life of the process.  args->workspace is
+ * ignored.  This entry point has no counterpart in the reference, whose launcher always
+ * allocates from its own pool (src/backend/cuda/matmul/gemm_common.cuh:296-340).
+ *
+ *  - Needs more than NNB200_STATIC_SCRATCH_BYTES (batch * (4*m + 4*n), each term rounded up
+ *    to 256): returns NNB200_OUT_OF_MEMORY and launches nothing.
+ *  - Never calls cudaMalloc, cudaFree or any allocating routine.
+ *  - The first call on each device looks up that device's copy of the array; make that first
+ *    call with the device current and outside any stream capture.
+ *  - All calls on a device share the one array.  Nothing in it has to be zeroed between
+ *    calls (every entry read is written first), but two calls whose kernels may overlap on
+ *    the GPU -- different streams, no ordering between them -- race on it: serialise them.
+ */
+#define NNB200_STATIC_SCRATCH_BYTES (1 << 20)
+NNB200_API int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, void* stream);
+
 /* Which engine nnb200_gemm_i8 would run for these arguments (NNB200_ENGINE_*). */
 NNB200_API int nnb200_gemm_i8_engine(const nnb200_gemm_i8_args* args);
 

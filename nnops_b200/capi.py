@@ -19,6 +19,7 @@ ACTIVATIONS = {"none": 0, "relu": 1, "gelu": 2, "sigmoid": 3, "tanh": 4, "leaky_
 ENGINES = {"auto": 0, "umma": 1, "narrow": 2, "generic": 3}
 ENGINE_NAMES = {v: k for k, v in ENGINES.items()}
 Q4_ENGINES = {"auto": 0, "gemm": 1, "gemv": 2}
+STATIC_SCRATCH_BYTES = 1 << 20
 
 
 class GemmI8Args(C.Structure):
@@ -64,6 +65,7 @@ class Q41Args(C.Structure):
 SYMBOLS = [
     ("nnb200_gemm_i8_workspace_bytes", C.c_size_t, [C.POINTER(GemmI8Args)]),
     ("nnb200_gemm_i8", C.c_int, [C.POINTER(GemmI8Args), C.c_void_p]),
+    ("nnb200_gemm_i8_static_scratch", C.c_int, [C.POINTER(GemmI8Args), C.c_void_p]),
     ("nnb200_gemm_i8_engine", C.c_int, [C.POINTER(GemmI8Args)]),
     ("nnb200_q4_1_workspace_bytes", C.c_size_t, [C.POINTER(Q41Args)]),
     ("nnb200_linear_q4_1", C.c_int, [C.POINTER(Q41Args), C.c_void_p]),

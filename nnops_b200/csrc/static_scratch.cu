@@ -1,0 +1,76 @@
+// nnb200_gemm_i8_static_scratch: the zero-point-compensated int8 matmul for callers that
+// cannot hand the library any scratch memory.
+//
+// Who needs this: an inference-engine plugin or a real-time loop that is given its input
+// and output buffers by the host framework and is not allowed to call cudaMalloc (or any
+// allocating routine) itself -- allocation takes a device-wide lock, may synchronise, and
+// can fail long after start-up.  The compensated matmul needs two small int32 vectors of
+// scratch (row sums of A and of W); nnb200_gemm_i8 takes them from the caller's workspace,
+// this entry point keeps them in a fixed array inside the library image instead.
+//
+// The array lives in device memory of every GPU that loads the library, from load until the
+// process exits, whether or not this entry point is ever called.
+
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "internal.cuh"
+
+namespace nnb200 {
+
+namespace {
+
+// Device-resident scratch, one copy per GPU.  In host code this name is only a handle for
+// the symbol; the address kernels can use is looked up per device below.
+static __device__ __align__(256) unsigned char g_static_scratch[NNB200_STATIC_SCRATCH_BYTES];
+
+void* g_scratch_ptr[kMaxDevices];
+cudaError_t g_scratch_err[kMaxDevices];
+std::once_flag g_scratch_once[kMaxDevices];
+
+// Device address of the current device's copy of the array; nullptr on failure.  Runs its
+// lookup once per device, with that device current (the caller's device is the one asked).
+void* static_scratch_for_current_device()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        return nullptr;
+    }
+    std::call_once(g_scratch_once[dev], [dev] {
+        void* p = nullptr;
+        g_scratch_err[dev] = cudaGetSymbolAddress(&p, g_static_scratch);
+        g_scratch_ptr[dev] = g_scratch_err[dev] == cudaSuccess ? p : nullptr;
+    });
+    return g_scratch_ptr[dev];
+}
+
+}  // namespace
+}  // namespace nnb200
+
+extern "C" int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, void* stream)
+{
+    using namespace nnb200;
+    if (args == nullptr) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    nnb200_gemm_i8_args local = *args;
+    local.workspace = nullptr;
+    local.workspace_bytes = 0;
+    const size_t need = nnb200_gemm_i8_workspace_bytes(&local);
+    if (need > static_cast<size_t>(NNB200_STATIC_SCRATCH_BYTES)) {
+        // Too large for the fixed array: refuse before anything is launched.
+        return NNB200_OUT_OF_MEMORY;
+    }
+    if (need > 0) {
+        void* p = static_scratch_for_current_device();
+        if (p == nullptr) {
+            return NNB200_INTERNAL;
+        }
+        local.workspace = p;
+        local.workspace_bytes = static_cast<size_t>(NNB200_STATIC_SCRATCH_BYTES);
+    }
+    // The sums kernels overwrite every entry of R_a / R_w they later read, so the previous
+    // call's contents never leak into this one and nothing has to be cleared.
+    return nnb200_gemm_i8(&local, stream);
+}
