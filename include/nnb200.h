@@ -173,8 +173,15 @@ typedef struct nnb200_q4_1_args {
     float alpha;
     void* workspace;
     size_t workspace_bytes;
-    int32_t force_engine; /* 0 auto, 1 tensor-core GEMM, 2 GEMV */
+    int32_t force_engine; /* 0 auto, 1 tensor-core GEMM, 2 GEMV (best), 3 GEMV on CUDA cores, 4 GEMV with warp MMA */
+    int32_t flags;        /* NNB200_Q4_FLAG_* */
 } nnb200_q4_1_args;
+
+/* The launch may begin while the preceding kernel of the stream is still finishing
+ * (programmatic dependent launch): its weight fetch overlaps that kernel's tail; activations
+ * are read and outputs written only after that kernel has completed.  Only set this when
+ * the preceding kernel does not write w_blocks.  Honoured by the GEMV engine. */
+#define NNB200_Q4_FLAG_OVERLAP_PREVIOUS 1
 
 NNB200_API size_t nnb200_q4_1_workspace_bytes(const nnb200_q4_1_args* args);
 NNB200_API int nnb200_linear_q4_1(const nnb200_q4_1_args* args, void* stream);

@@ -18,7 +18,7 @@ ACTIVATIONS = {"none": 0, "relu": 1, "gelu": 2, "sigmoid": 3, "tanh": 4, "leaky_
                "hard_swish": 7, "elu": 8, "relu6": 9}
 ENGINES = {"auto": 0, "umma": 1, "narrow": 2, "generic": 3}
 ENGINE_NAMES = {v: k for k, v in ENGINES.items()}
-Q4_ENGINES = {"auto": 0, "gemm": 1, "gemv": 2}
+Q4_ENGINES = {"auto": 0, "gemm": 1, "gemv": 2, "gemv_simt": 3, "gemv_mma": 4}
 STATIC_SCRATCH_BYTES = 1 << 20
 
 
@@ -57,9 +57,11 @@ class Q41Args(C.Structure):
         ("min_clip", C.c_float), ("max_clip", C.c_float),
         ("alpha", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("force_engine", C.c_int32),
+        ("force_engine", C.c_int32), ("flags", C.c_int32),
     ]
 
+
+Q4_FLAG_OVERLAP_PREVIOUS = 1
 
 # Every symbol include/nnb200.h declares: (name, restype, argtypes).
 SYMBOLS = [

@@ -77,7 +77,7 @@ void note_launch(int n)
 }
 
 bool make_tma_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t cols, uint64_t rows,
-                 uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows)
+                 uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, bool swizzle128)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) {
@@ -87,9 +87,12 @@ bool make_tma_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t co
     const cuuint64_t strides[1] = {pitch_bytes};
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t elem_strides[2] = {1, 1};
-    const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapDataType dt = elem_bytes == 1   ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_UINT32;
     const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -295,14 +298,16 @@ int nnb200_q4_1_engine(const nnb200_q4_1_args* q)
     if (!valid_q4_args(q)) {
         return -1;
     }
-    if (q->force_engine == 2) {
-        return 2;
+    // 1 = tensor-core GEMM (tcgen05), 3 = GEMV on CUDA cores, 4 = GEMV with warp-level MMA.
+    const int gemv = (q->force_engine != 3 && q4_1_gemv_mma_supported(*q)) ? 4 : 3;
+    if (q->force_engine == 2 || q->force_engine == 3 || q->force_engine == 4) {
+        return gemv;
     }
     const bool gemm_ok = q4_1_gemm_umma_supported(*q);
     if (q->force_engine == 1) {
-        return gemm_ok ? 1 : 2;
+        return gemm_ok ? 1 : gemv;
     }
-    return (q->m > 8 && gemm_ok) ? 1 : 2;
+    return (q->m > 8 && gemm_ok) ? 1 : gemv;
 }
 
 int nnb200_linear_q4_1(const nnb200_q4_1_args* q, void* stream_v)
@@ -324,10 +329,11 @@ int nnb200_linear_q4_1(const nnb200_q4_1_args* q, void* stream_v)
         return NNB200_UNSUPPORTED;
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    if (nnb200_q4_1_engine(q) == 1) {
-        return launch_q4_1_gemm_umma(*q, *dev, stream);
+    switch (nnb200_q4_1_engine(q)) {
+    case 1: return launch_q4_1_gemm_umma(*q, *dev, stream);
+    case 4: return launch_q4_1_gemv_mma(*q, *dev, stream);
+    default: return launch_q4_1_gemv(*q, *dev, stream);
     }
-    return launch_q4_1_gemv(*q, *dev, stream);
 }
 
 int nnb200_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, int64_t k, void* out, int32_t out_f16,

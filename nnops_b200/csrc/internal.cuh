@@ -33,9 +33,10 @@ void note_launch(int n = 1);
 
 // Encode a 2-D row-major byte/half tensor [rows][cols] with row pitch `pitch_bytes` as a TMA
 // descriptor with a 128-byte-swizzled box of box_cols x box_rows elements.  elem_bytes is 1
-// or 2.  Returns false if the driver rejects it.
+// 2 or 4 (4 = opaque 32-bit words).  swizzle128 = false leaves the box rows dense in shared
+// memory.  Returns false if the driver rejects it.
 bool make_tma_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t cols, uint64_t rows,
-                 uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows);
+                 uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, bool swizzle128 = true);
 
 // One 2-D int8 problem (a single batch element), Linear pose: A [m,k] and W [n,k] both
 // k-contiguous.  lda / ldw are row pitches in bytes.
@@ -60,6 +61,8 @@ bool narrow_i8_supported(const I8Problem& p);
 int launch_i8_sums(const I8Problem& p, int32_t* r_a, int32_t* r_w, cudaStream_t stream);
 
 int launch_q4_1_gemv(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
+int launch_q4_1_gemv_mma(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
+bool q4_1_gemv_mma_supported(const nnb200_q4_1_args& a);
 int launch_q4_1_gemm_umma(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
 bool q4_1_gemm_umma_supported(const nnb200_q4_1_args& a);
 int launch_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, int64_t k, void* out, int out_f16,

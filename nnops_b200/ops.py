@@ -116,7 +116,7 @@ def gemm_i8_engine(a, w, out, **kw) -> str:
 
 def q4_1_args(a: torch.Tensor, w_blocks: torch.Tensor, out: torch.Tensor, k: int, *, bias=None, activation="none",
               act_alpha=0.0, act_beta=1.0, min_clip=-math.inf, max_clip=math.inf, alpha=1.0, engine="auto",
-              keep: list | None = None) -> capi.Q41Args:
+              overlap_previous: bool = False, keep: list | None = None) -> capi.Q41Args:
     keep = keep if keep is not None else []
     if w_blocks.dtype != torch.uint8 or w_blocks.dim() != 2 or w_blocks.stride(1) != 1 or w_blocks.stride(0) % 20:
         raise ValueError("w_blocks must be a uint8 [N, row_bytes] tensor whose row pitch is a multiple of 20")
@@ -131,7 +131,8 @@ def q4_1_args(a: torch.Tensor, w_blocks: torch.Tensor, out: torch.Tensor, k: int
         ldc=out.stride(0), a_f16=int(a.dtype == torch.float16), out_f16=int(out.dtype == torch.float16),
         bias=bias.data_ptr() if bias is not None else None, activation=capi.ACTIVATIONS[activation],
         act_alpha=act_alpha, act_beta=act_beta, min_clip=min_clip, max_clip=max_clip, alpha=alpha,
-        workspace=None, workspace_bytes=0, force_engine=capi.Q4_ENGINES[engine])
+        workspace=None, workspace_bytes=0, force_engine=capi.Q4_ENGINES[engine],
+        flags=capi.Q4_FLAG_OVERLAP_PREVIOUS if overlap_previous else 0)
 
 
 def linear_q4_1(a: torch.Tensor, w_blocks: torch.Tensor, k: int, *, out_dtype: torch.dtype | None = None,
@@ -148,6 +149,14 @@ def linear_q4_1(a: torch.Tensor, w_blocks: torch.Tensor, k: int, *, out_dtype: t
     with torch.cuda.device(a.device):
         capi.check(capi.lib().nnb200_linear_q4_1(C.byref(args), _stream_ptr(a.device)), "nnb200_linear_q4_1")
     return out
+
+
+def q4_1_engine(a: torch.Tensor, w_blocks: torch.Tensor, k: int, *, out_dtype: torch.dtype = torch.float32,
+                engine: str = "auto") -> int:
+    """Engine code nnb200_linear_q4_1 would pick (1 GEMM, 3 GEMV on CUDA cores, 4 GEMV with warp MMA)."""
+    out = torch.empty((a.shape[0], w_blocks.shape[0]), dtype=out_dtype, device=a.device)
+    args = q4_1_args(a, w_blocks, out, k, engine=engine)
+    return capi.lib().nnb200_q4_1_engine(C.byref(args))
 
 
 def q4_1_decode(w_blocks: torch.Tensor, k: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:

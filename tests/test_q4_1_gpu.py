@@ -35,27 +35,62 @@ def test_decode_matches_oracle_bitwise(cuda_device, nnb200_lib):
         assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("engine", ["gemv_simt", "gemv_mma"])
 @pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 11])
 @pytest.mark.parametrize("a_dtype,out_dtype", [("f16", "f32"), ("f16", "f16"), ("f32", "f32")])
-def test_gemv_small(cuda_device, nnb200_lib, m, a_dtype, out_dtype):
+def test_gemv_small(cuda_device, nnb200_lib, m, a_dtype, out_dtype, engine):
     rng = np.random.default_rng(m)
-    n, k = 203, 1000   # ragged N, K not a multiple of 32
+    n, k = (203, 1000) if engine == "gemv_simt" else (203, 1024)   # ragged N; ragged K on the CUDA-core engine
     wb = synth.q4_1_weights(rng, n, k)
     a = rng.standard_normal((m, k)).astype(np.float16 if a_dtype == "f16" else np.float32)
     bias = rng.standard_normal(n).astype(np.float32 if out_dtype == "f32" else np.float16)
     want = oracle.q4_1_matmul(a, wb, k, out_dtype=out_dtype, bias=bias)
     got = ops.linear_q4_1(torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device), k,
                           out_dtype=torch.float32 if out_dtype == "f32" else torch.float16, bias=bias,
-                          engine="gemv")
+                          engine=engine)
     _close(got.cpu().numpy(), want, RTOL_F32 if out_dtype == "f32" else RTOL_F16)
 
 
+@pytest.mark.parametrize("shape", [(1, 16, 128), (4, 40, 384), (8, 130, 4096 + 128), (7, 17, 8192 + 256), (3, 64, 4096),
+                                   (2, 33, 12288)])
+def test_gemv_mma_edges(cuda_device, nnb200_lib, shape):
+    """Fewer block groups than K-quarter warps, K spanning several staged chunks, channel counts
+    off the 16-row tile, and a weight view whose row pitch is wider than its rows."""
+    m, n, k = shape
+    rng = np.random.default_rng(n + k)
+    nblk = k // 32
+    ld = nblk + 4                                   # padded pitch, still a multiple of 4 blocks
+    wb_dense = synth.q4_1_weights(rng, n, k)
+    wb = np.zeros((n, ld * 20), dtype=np.uint8)
+    wb[:, : nblk * 20] = wb_dense
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    ta = torch.from_numpy(a).to(cuda_device)
+    tw = torch.from_numpy(wb).to(cuda_device)[:, : nblk * 20]
+    assert ops.q4_1_engine(ta, tw, k, engine="gemv") == 4
+    got = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float32, engine="gemv")
+    _close(got.cpu().numpy(), oracle.q4_1_matmul(a, wb_dense, k, out_dtype="f32"), RTOL_F32)
+
+
+def test_gemv_falls_back_when_rows_are_not_bulk_copyable(cuda_device, nnb200_lib):
+    """K = 1000 (31.25 blocks): rows are not a whole number of 16-byte pieces, so the CUDA-core
+    GEMV must be chosen -- and still match."""
+    rng = np.random.default_rng(12)
+    m, n, k = 3, 50, 1000
+    wb = synth.q4_1_weights(rng, n, k)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device)
+    assert ops.q4_1_engine(ta, tw, k, engine="gemv") == 3
+    got = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float32)
+    _close(got.cpu().numpy(), oracle.q4_1_matmul(a, wb, k, out_dtype="f32"), RTOL_F32)
+
+
+@pytest.mark.parametrize("engine", ["gemv_simt", "gemv_mma"])
 @pytest.mark.parametrize("m", [1, 8])
-def test_config3_gemv(cuda_device, nnb200_lib, m):
+def test_config3_gemv(cuda_device, nnb200_lib, m, engine):
     c = synth.config3(m)
     want = oracle.q4_1_matmul(c.a, c.w_blocks, c.k, out_dtype="f32")
     got = ops.linear_q4_1(torch.from_numpy(c.a).to(cuda_device), torch.from_numpy(c.w_blocks).to(cuda_device), c.k,
-                          out_dtype=torch.float32)
+                          out_dtype=torch.float32, engine=engine)
     _close(got.cpu().numpy(), want, RTOL_F32)
 
 
