@@ -213,6 +213,12 @@ NNB200_API int nnb200_take_device_error(int32_t* code);
  * H2D of quantization arrays, src/backend/cuda/matmul/matmul_i8.cuh:357-376). */
 NNB200_API int nnb200_copy_h2d_async(void* dst_device, const void* src_host, size_t bytes, void* stream);
 
+/* Stream-ordered scratch from the device's default memory pool, for host glue that has to
+ * stage host-side quantization arrays itself (the reference launcher's private pool,
+ * gemm_workspace_alloc / gemm_workspace_free, src/backend/cuda/matmul/gemm_common.cuh:296-354). */
+NNB200_API int nnb200_scratch_alloc_async(void** out, size_t bytes, void* stream);
+NNB200_API int nnb200_scratch_free_async(void* p, void* stream);
+
 /* 1 if p is device (or managed) memory usable by kernels of the current device, else 0. */
 NNB200_API int nnb200_is_device_pointer(const void* p);
 

@@ -1,0 +1,330 @@
+// Stand-alone mirror of the slice of the nnops operator API that the quantized-matmul path
+// uses: the boundary types (DataType, Status, QuantParams, Epilogue, TensorDesc, TensorView,
+// ComputeContext) and the two operators (Linear, MatMul).  Names, argument meaning and error
+// behaviour follow the reference so that code written against nnops compiles against this
+// header unchanged:
+//
+//   reference                                   here
+//   include/nnops/core/data_type.hpp:23         DataType (same numbering, q4_1 = 11)
+//   include/nnops/core/status.hpp:19            Status
+//   include/nnops/core/quant_params.hpp:36      QuantParams
+//   include/nnops/core/epilogue.hpp:23-91       EpilogueActivateType, Epilogue
+//   include/nnops/core/tensor_view.hpp:38,124   TensorDesc, TensorView (pitched, non-owning)
+//   include/nnops/core/compute_context.hpp:24   ComputeContext (cuda_stream)
+//   include/nnops/core/op_base.hpp:30           OpBase
+//   include/nnops/ops/linear.hpp:41-142         LinearAttributes, Linear
+//   include/nnops/ops/matmul.hpp:37-135         MatMulAttributes, MatMul
+//
+// It is NOT a copy of those headers: only what this path needs exists, written from the
+// documented behaviour.  When the real nnops headers are available the CUDA backend glue
+// (nnops_b200/host/cuda_backend.cpp) is compiled against them instead and this file is unused.
+#pragma once
+
+#include <array>
+#include <cstddef>
+#include <cstdint>
+#include <limits>
+#include <memory>
+#include <span>
+#include <vector>
+
+namespace nnops {
+
+enum class Backend : uint8_t { CPU = 0, CUDA = 1, Vulkan = 2, Metal = 3 };
+
+enum class Status : uint8_t { ok = 0, invalid_argument, unsupported, not_initialized, out_of_memory, internal };
+constexpr bool is_ok(Status s) noexcept { return s == Status::ok; }
+const char* to_string(Status s) noexcept;
+
+enum class DataType : uint8_t { f32 = 0, f16, bf16, s8, u8, s32, s64, f8_e4m3, f8_e5m2, s4, u4, q4_1 };
+
+inline constexpr int64_t q4_1_block_elems = 32;
+inline constexpr size_t q4_1_block_bytes = 20;
+
+/// Bytes of one element; 0 for sub-byte and block-packed types.
+constexpr size_t data_type_size(DataType dt) noexcept
+{
+    switch (dt) {
+    case DataType::f32: case DataType::s32: return 4;
+    case DataType::f16: case DataType::bf16: return 2;
+    case DataType::s8: case DataType::u8: case DataType::f8_e4m3: case DataType::f8_e5m2: return 1;
+    case DataType::s64: return 8;
+    default: return 0;
+    }
+}
+/// The unit row strides are counted in: the element, or the 20-byte block for q4_1.
+constexpr size_t data_type_stride_unit(DataType dt) noexcept
+{
+    return dt == DataType::q4_1 ? q4_1_block_bytes : data_type_size(dt);
+}
+/// Bytes of a row of `cols` logical elements.
+constexpr size_t data_type_row_bytes(DataType dt, int64_t cols) noexcept
+{
+    if (cols <= 0) return 0;
+    if (dt == DataType::q4_1) return static_cast<size_t>((cols + q4_1_block_elems - 1) / q4_1_block_elems) * q4_1_block_bytes;
+    if (dt == DataType::s4 || dt == DataType::u4) return static_cast<size_t>((cols + 1) / 2);
+    return static_cast<size_t>(cols) * data_type_size(dt);
+}
+
+enum class QuantGranularity : uint8_t { PerTensor = 0, PerToken = 1, PerChannel = 2 };
+
+/// Quantization of a view.  scale_data / zero_point_data may be HOST arrays (the reference
+/// contract) or device arrays (used in place, no staging).
+struct QuantParams {
+    QuantGranularity granularity = QuantGranularity::PerTensor;
+    float scale = 1.0f;
+    int32_t zero_point = 0;
+    const float* scale_data = nullptr;
+    const int32_t* zero_point_data = nullptr;
+    int64_t num_scales = 0;
+    bool is_active() const noexcept
+    {
+        return scale_data != nullptr || zero_point_data != nullptr || scale != 1.0f || zero_point != 0;
+    }
+};
+
+enum class EpilogueActivateType : uint8_t {
+    None = 0, Relu, Gelu, Sigmoid, Tanh, LeakyRelu, Silu, HardSwish, Elu, Relu6
+};
+enum class EpilogueQuantType : uint8_t { None = 0, Requantize = 1, Dequantize = 2 };
+
+struct Epilogue {
+    EpilogueActivateType type = EpilogueActivateType::None;
+    float alpha = 0.0f;
+    float beta = 1.0f;
+    float min_clip = -std::numeric_limits<float>::infinity();
+    float max_clip = std::numeric_limits<float>::infinity();
+    EpilogueQuantType quant = EpilogueQuantType::None;
+    const float* quant_scales = nullptr;
+    const int32_t* quant_zero_points = nullptr;
+    int64_t quant_param_count = 0;
+    int64_t quant_axis = 0;
+};
+
+enum class TensorLayout : uint8_t { Dense = 0 };
+
+/// Fixed-capacity dimension list (the reference uses an inline small vector of 8).
+struct Dims {
+    std::array<int64_t, 8> v{};
+    int64_t& operator[](size_t i) noexcept { return v[i]; }
+    const int64_t& operator[](size_t i) const noexcept { return v[i]; }
+    int64_t* data() noexcept { return v.data(); }
+    const int64_t* data() const noexcept { return v.data(); }
+    void resize(size_t) noexcept {}
+};
+
+struct TensorDesc {
+    static constexpr int64_t kMaxRank = 8;
+    Dims dims;
+    int64_t rank = 0;
+    DataType dtype = DataType::f32;
+    TensorLayout layout = TensorLayout::Dense;
+    int64_t row_stride_elems = 0;
+
+    int64_t numel() const noexcept
+    {
+        int64_t n = 1;
+        for (int64_t i = 0; i < rank; ++i) n *= dims[static_cast<size_t>(i)];
+        return n;
+    }
+    /// Suggested row pitch in bytes, rounded up to `alignment`.
+    int64_t row_pitch(int64_t alignment = 32) const noexcept
+    {
+        if (rank < 2) return static_cast<int64_t>(data_type_stride_unit(dtype));
+        const int64_t bytes = static_cast<int64_t>(data_type_row_bytes(dtype, dims[static_cast<size_t>(rank - 1)]));
+        return (bytes + alignment - 1) / alignment * alignment;
+    }
+    size_t storage_bytes(int64_t alignment = 32) const noexcept
+    {
+        if (rank < 2) return data_type_row_bytes(dtype, numel());
+        int64_t rows = 1;
+        for (int64_t i = 0; i + 1 < rank; ++i) rows *= dims[static_cast<size_t>(i)];
+        return static_cast<size_t>(rows * row_pitch(alignment));
+    }
+};
+
+/// Non-owning, pitched view of a tensor: rows of the last dimension, `pitch` bytes apart; all
+/// leading dimensions are dense multiples of the row pitch.
+class TensorView {
+public:
+    static constexpr int64_t kMaxRank = 8;
+    TensorView() = default;
+    TensorView(std::span<const int64_t> shape, DataType dtype, void* data,
+               TensorLayout layout = TensorLayout::Dense, QuantParams qp = {})
+        : data_(data), dtype_(dtype), layout_(layout), qp_(qp)
+    {
+        set_shape(shape);
+        pitch_ = rank_ >= 2 ? static_cast<int64_t>(data_type_row_bytes(dtype, shape_[static_cast<size_t>(rank_ - 1)]))
+                            : (rank_ == 1 ? static_cast<int64_t>(data_type_stride_unit(dtype)) : 0);
+    }
+    TensorView(std::span<const int64_t> shape, DataType dtype, void* data, int64_t pitch,
+               TensorLayout layout = TensorLayout::Dense, QuantParams qp = {})
+        : data_(data), pitch_(pitch), dtype_(dtype), layout_(layout), qp_(qp)
+    {
+        set_shape(shape);
+    }
+
+    int64_t rank() const noexcept { return rank_; }
+    int64_t shape(int64_t d) const noexcept { return shape_[static_cast<size_t>(d)]; }
+    const int64_t* shape() const noexcept { return shape_.data(); }
+    int64_t pitch() const noexcept { return pitch_; }
+    DataType data_type() const noexcept { return dtype_; }
+    TensorLayout layout() const noexcept { return layout_; }
+    const QuantParams& quant_params() const noexcept { return qp_; }
+    bool is_empty() const noexcept { return data_ == nullptr; }
+    template <class T> T* ptr() noexcept { return static_cast<T*>(data_); }
+    template <class T> const T* ptr() const noexcept { return static_cast<const T*>(data_); }
+
+    int64_t numel() const noexcept
+    {
+        if (rank_ == 0) return data_ != nullptr ? 1 : 0;
+        int64_t n = 1;
+        for (int64_t i = 0; i < rank_; ++i) n *= shape_[static_cast<size_t>(i)];
+        return n;
+    }
+    /// Row stride in storage units (elements, or 20-byte blocks for q4_1).
+    int64_t row_stride_elems() const noexcept
+    {
+        if (rank_ < 2) return 1;
+        const int64_t unit = static_cast<int64_t>(data_type_stride_unit(dtype_));
+        return unit > 0 ? pitch_ / unit : 0;
+    }
+    int64_t stride_elems(int64_t dim) const noexcept
+    {
+        if (dim == rank_ - 1) return 1;
+        int64_t s = row_stride_elems();
+        for (int64_t i = rank_ - 2; i > dim; --i) s *= shape_[static_cast<size_t>(i)];
+        return s;
+    }
+    TensorDesc desc() const noexcept
+    {
+        TensorDesc d;
+        d.rank = rank_;
+        for (int64_t i = 0; i < rank_; ++i) d.dims[static_cast<size_t>(i)] = shape_[static_cast<size_t>(i)];
+        d.dtype = dtype_;
+        d.layout = layout_;
+        d.row_stride_elems = rank_ >= 2 ? row_stride_elems() : 0;
+        return d;
+    }
+
+private:
+    void set_shape(std::span<const int64_t> shape) noexcept
+    {
+        rank_ = static_cast<int64_t>(shape.size() <= 8 ? shape.size() : 8);
+        for (int64_t i = 0; i < rank_; ++i) shape_[static_cast<size_t>(i)] = shape[static_cast<size_t>(i)];
+    }
+    std::array<int64_t, 8> shape_{};
+    void* data_ = nullptr;
+    int64_t pitch_ = 0;
+    DataType dtype_ = DataType::f32;
+    TensorLayout layout_ = TensorLayout::Dense;
+    QuantParams qp_;
+    int64_t rank_ = 0;
+};
+
+/// Per-call execution context.  Only the CUDA stream matters on this path.
+struct ComputeContext {
+    Backend expected_backend = Backend::CPU;
+    void* cuda_stream = nullptr;  ///< cudaStream_t, opaque; nullptr = default stream
+};
+
+enum class OpType : uint8_t { Linear = 0, MatMul = 1 };
+
+class OpBase {
+public:
+    virtual ~OpBase() = default;
+    virtual std::vector<TensorDesc> getOutputTensorDesc(std::span<const TensorDesc> inputs) const = 0;
+    virtual size_t getWorkspaceSize(std::span<const TensorDesc>, std::span<const TensorDesc>) const { return 0; }
+    virtual Status validate(std::span<const TensorDesc>, std::span<const TensorDesc>) const { return Status::ok; }
+    virtual Status compute(std::span<TensorView> outputs, std::span<const TensorView> inputs,
+                           const ComputeContext& ctx = {}, void* workspace = nullptr) = 0;
+    Status compute(TensorView& output, std::span<const TensorView> inputs, const ComputeContext& ctx = {},
+                   void* workspace = nullptr)
+    {
+        TensorView outs[] = {output};
+        return compute(std::span<TensorView>(outs), inputs, ctx, workspace);
+    }
+    /// Two-step contract: an empty outputs[0] asks for the packed form's geometry; this
+    /// backend reads raw weights in place and leaves it empty ("no packed form").
+    virtual void prepackWeights(std::span<const TensorView>, std::span<TensorView>, const ComputeContext& = {}) {}
+    virtual OpType getOpType() const = 0;
+    virtual Backend getBackend() const = 0;
+};
+
+struct LinearAttributes {
+    Epilogue epilogue{};
+    bool add_to = false;
+    bool residual_pre_activation = false;
+    DataType output_dtype = DataType::f32;
+    bool gated = false;
+    EpilogueActivateType gate_activation = EpilogueActivateType::Silu;
+    float gate_alpha = 1.0f;
+    float gate_beta = 0.0f;
+    float gate_limit = std::numeric_limits<float>::infinity();
+};
+
+/// y[.., N] = epilogue(x[.., K] * W[N, K]^T + bias).  Quantized route: x s8/u8, W s8, output
+/// dtype = attributes.output_dtype; weight-decode route: x f16/f32, W q4_1.
+class Linear : public OpBase {
+public:
+    static std::unique_ptr<Linear> create(const LinearAttributes& attrs, Backend backend = Backend::CPU);
+    std::vector<TensorDesc> getOutputTensorDesc(std::span<const TensorDesc> inputs) const override;
+    Status validate(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs) const override;
+    using OpBase::compute;
+    Status compute(std::span<TensorView> outputs, std::span<const TensorView> inputs, const ComputeContext& ctx = {},
+                   void* workspace = nullptr) override;
+    OpType getOpType() const override { return OpType::Linear; }
+    Backend getBackend() const override { return backend_; }
+    const LinearAttributes& attributes() const noexcept { return attrs_; }
+
+private:
+    Linear(const LinearAttributes& a, Backend b) : attrs_(a), backend_(b) {}
+    LinearAttributes attrs_;
+    Backend backend_;
+};
+
+struct MatMulAttributes {
+    bool transpose_a = false;
+    bool transpose_b = false;
+    float alpha = 1.0f;
+    float beta = 0.0f;
+    bool residual_pre_activation = false;
+    DataType output_dtype = DataType::s32;
+    DataType act_quant_dtype = DataType::s8;
+    Epilogue epilogue{};
+};
+
+inline constexpr bool is_int8_matmul(DataType a, DataType b) noexcept
+{
+    return (a == DataType::s8 || a == DataType::u8) && b == DataType::s8;
+}
+
+/// C[.., M, N] = epilogue(op(A) * op(B) + bias) with numpy batch broadcasting.
+class MatMul : public OpBase {
+public:
+    static std::unique_ptr<MatMul> create(const MatMulAttributes& attrs = {}, Backend backend = Backend::CPU);
+    std::vector<TensorDesc> getOutputTensorDesc(std::span<const TensorDesc> inputs) const override;
+    Status validate(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs) const override;
+    using OpBase::compute;
+    Status compute(std::span<TensorView> outputs, std::span<const TensorView> inputs, const ComputeContext& ctx = {},
+                   void* workspace = nullptr) override;
+    OpType getOpType() const override { return OpType::MatMul; }
+    Backend getBackend() const override { return backend_; }
+    const MatMulAttributes& attributes() const noexcept { return attrs_; }
+
+private:
+    MatMul(const MatMulAttributes& a, Backend b) : attrs_(a), backend_(b) {}
+    MatMulAttributes attrs_;
+    Backend backend_;
+};
+
+namespace backend::cuda {
+/// The two backend entry points the operator front end dispatches to (the reference declares
+/// them at src/ops/linear.cpp:24 and src/ops/matmul.cpp:35).
+Status linear_cuda(const LinearAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
+                   const ComputeContext& ctx, void* workspace);
+Status matmul_cuda(const MatMulAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
+                   const ComputeContext& ctx, void* workspace);
+}  // namespace backend::cuda
+
+}  // namespace nnops

@@ -78,6 +78,8 @@ SYMBOLS = [
                                            C.c_void_p]),
     ("nnb200_take_device_error", C.c_int, [C.POINTER(C.c_int32)]),
     ("nnb200_copy_h2d_async", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    ("nnb200_scratch_alloc_async", C.c_int, [C.POINTER(C.c_void_p), C.c_size_t, C.c_void_p]),
+    ("nnb200_scratch_free_async", C.c_int, [C.c_void_p, C.c_void_p]),
     ("nnb200_is_device_pointer", C.c_int, [C.c_void_p]),
     ("nnb200_launch_count", C.c_uint64, []),
     ("nnb200_version", C.c_char_p, []),

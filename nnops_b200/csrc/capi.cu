@@ -400,6 +400,31 @@ int nnb200_copy_h2d_async(void* dst_device, const void* src_host, size_t bytes, 
         cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
 }
 
+int nnb200_scratch_alloc_async(void** out, size_t bytes, void* stream)
+{
+    if (out == nullptr) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    *out = nullptr;
+    if (bytes == 0) {
+        return NNB200_OK;
+    }
+    const cudaError_t e = cudaMallocAsync(out, bytes, static_cast<cudaStream_t>(stream));
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        return NNB200_OUT_OF_MEMORY;
+    }
+    return cuda_status(e);
+}
+
+int nnb200_scratch_free_async(void* p, void* stream)
+{
+    if (p == nullptr) {
+        return NNB200_OK;
+    }
+    return cuda_status(cudaFreeAsync(p, static_cast<cudaStream_t>(stream)));
+}
+
 int nnb200_is_device_pointer(const void* p)
 {
     if (p == nullptr) {

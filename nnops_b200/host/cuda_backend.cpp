@@ -1,0 +1,420 @@
+// nnops::backend::cuda::linear_cuda / matmul_cuda for the B200 backend: the host side of the
+// drop-in boundary.  C++23, no CUDA headers -- everything device-side goes through the C ABI
+// in include/nnb200.h, with the stream taken from ComputeContext.
+//
+// These are the two symbols nnops' operator front end resolves when it is built with CUDA
+// (declared at src/ops/linear.cpp:24 and src/ops/matmul.cpp:35 of the reference, dispatched by
+// src/ops/dispatch.hpp:42-96).  They replace src/backend/cuda/matmul/linear.cu:94-163 and
+// src/backend/cuda/matmul/matmul.cu:99-160 for the quantized routes:
+//
+//   * s8/u8 x s8 -> s32 | s8 | u8 | f32 | f16 with the fused epilogue (every pose, batch
+//     broadcast over up to four leading axes);
+//   * f16/f32 x q4_1 [N,K] -> f16/f32, which the reference serves on the CPU only.
+//
+// Compiled against the real nnops headers when NNB200_USE_NNOPS_HEADERS is defined (the
+// maintainer's integration), else against the stand-alone mirror.
+//
+// Semantics kept from the reference: integer destinations honour only Relu and ignore
+// alpha/beta and the clip bounds; a rejected call writes nothing; an empty output is ok;
+// QuantParams arrays may be host memory (staged per call, stream-ordered, like the reference
+// launcher does) or device memory (used in place).
+
+#ifdef NNB200_USE_NNOPS_HEADERS
+#include "nnops/ops/linear.hpp"
+#include "nnops/ops/matmul.hpp"
+#else
+#include "nnops_b200/nnops_api.hpp"
+#endif
+
+#include "nnb200.h"
+
+#include <algorithm>
+#include <array>
+#include <cstring>
+
+namespace nnops::backend::cuda {
+
+namespace {
+
+constexpr int kMaxBatchRank = 4;          // rank-6 operands: four broadcastable batch axes
+constexpr int64_t kMaxBatchCount = 65535; // the reference refuses larger flattened batches
+
+Status to_status(int code)
+{
+    return code >= 0 && code <= 5 ? static_cast<Status>(code) : Status::internal;
+}
+
+bool out_kind_of(DataType dt, int& kind)
+{
+    switch (dt) {
+    case DataType::s32: kind = NNB200_OUT_S32; return true;
+    case DataType::s8: kind = NNB200_OUT_S8; return true;
+    case DataType::u8: kind = NNB200_OUT_U8; return true;
+    case DataType::f32: kind = NNB200_OUT_F32; return true;
+    case DataType::f16: kind = NNB200_OUT_F16; return true;
+    default: return false;
+    }
+}
+
+// Batch geometry after numpy-style broadcasting of the leading axes of a and b.
+struct BatchLayout {
+    int rank = 0;
+    int64_t size[kMaxBatchRank] = {1, 1, 1, 1};
+    int64_t a_stride[kMaxBatchRank] = {0, 0, 0, 0};
+    int64_t b_stride[kMaxBatchRank] = {0, 0, 0, 0};
+    int64_t c_stride[kMaxBatchRank] = {0, 0, 0, 0};
+    int64_t count = 1;
+};
+
+bool batch_layout(const TensorView& a, const TensorView& b, const TensorView& c, BatchLayout& L)
+{
+    const int64_t al = std::max<int64_t>(a.rank() - 2, 0);
+    const int64_t bl = std::max<int64_t>(b.rank() - 2, 0);
+    const int64_t rank = std::max(al, bl);
+    if (rank > kMaxBatchRank) {
+        return false;
+    }
+    L.rank = static_cast<int>(rank);
+    for (int64_t d = 0; d < rank; ++d) {
+        const int64_t ai = al - 1 - d, bi = bl - 1 - d, ci = c.rank() - 3 - d;
+        const int64_t ad = ai >= 0 ? a.shape(ai) : 1;
+        const int64_t bd = bi >= 0 ? b.shape(bi) : 1;
+        if (ad != bd && ad != 1 && bd != 1) {
+            return false;
+        }
+        const int64_t slot = rank - 1 - d;
+        L.size[slot] = std::max(ad, bd);
+        L.a_stride[slot] = ad == 1 ? 0 : a.stride_elems(ai);
+        L.b_stride[slot] = bd == 1 ? 0 : b.stride_elems(bi);
+        L.c_stride[slot] = ci >= 0 ? c.stride_elems(ci) : 0;
+        if (L.size[slot] > kMaxBatchCount) {
+            return false;
+        }
+        L.count *= L.size[slot];
+        if (L.count > kMaxBatchCount) {
+            return false;
+        }
+    }
+    return true;
+}
+
+// One quantization array as the kernels want it: a device pointer (or null + scalar).
+struct DeviceArray {
+    const void* ptr = nullptr;
+    bool any_nonzero = true;
+};
+
+// Stream-ordered staging of host-side quantization arrays plus the kernels' own scratch.
+class Staging {
+public:
+    explicit Staging(void* stream) : stream_(stream) {}
+    ~Staging()
+    {
+        if (base_ != nullptr) {
+            nnb200_scratch_free_async(base_, stream_);
+        }
+    }
+    Staging(const Staging&) = delete;
+    Staging& operator=(const Staging&) = delete;
+
+    /// Reserve room; call for every array before allocate().
+    void reserve(const void* host, size_t bytes)
+    {
+        if (host != nullptr && nnb200_is_device_pointer(host) == 0) {
+            total_ += (bytes + 255) & ~size_t(255);
+        }
+    }
+    void reserve_raw(size_t bytes) { total_ += (bytes + 255) & ~size_t(255); }
+    int allocate() { return total_ == 0 ? NNB200_OK : nnb200_scratch_alloc_async(&base_, total_, stream_); }
+
+    /// Device address of `host` (copied if it is host memory); int32 arrays report whether any
+    /// entry is non-zero so the backend can skip the zero-point sweeps.
+    int place(const void* host, size_t bytes, bool scan_int32, DeviceArray& out)
+    {
+        out.ptr = nullptr;
+        out.any_nonzero = true;
+        if (host == nullptr) {
+            return NNB200_OK;
+        }
+        if (nnb200_is_device_pointer(host) != 0) {
+            out.ptr = host;
+            return NNB200_OK;
+        }
+        if (scan_int32) {
+            const int32_t* v = static_cast<const int32_t*>(host);
+            out.any_nonzero = std::any_of(v, v + bytes / 4, [](int32_t x) { return x != 0; });
+        }
+        void* dst = static_cast<char*>(base_) + used_;
+        used_ += (bytes + 255) & ~size_t(255);
+        out.ptr = dst;
+        return nnb200_copy_h2d_async(dst, host, bytes, stream_);
+    }
+    void* take_raw(size_t bytes)
+    {
+        void* p = static_cast<char*>(base_) + used_;
+        used_ += (bytes + 255) & ~size_t(255);
+        return p;
+    }
+
+private:
+    void* stream_;
+    void* base_ = nullptr;
+    size_t total_ = 0;
+    size_t used_ = 0;
+};
+
+struct I8Call {
+    const TensorView* a;
+    const TensorView* w;
+    const TensorView* bias;
+    TensorView* out;
+    bool transpose_a;   // A stored [K, M]
+    bool w_is_nk;       // W stored [N, K] (Linear, or MatMul with transpose_b)
+    const Epilogue* ep;
+    int kind;
+};
+
+Status run_i8(const I8Call& c, const ComputeContext& ctx)
+{
+    const TensorView& a = *c.a;
+    const TensorView& w = *c.w;
+    TensorView& out = *c.out;
+    if (a.rank() < 2 || w.rank() < 2 || out.rank() < 2) {
+        return Status::invalid_argument;
+    }
+    const int64_t M = c.transpose_a ? a.shape(a.rank() - 1) : a.shape(a.rank() - 2);
+    const int64_t Ka = c.transpose_a ? a.shape(a.rank() - 2) : a.shape(a.rank() - 1);
+    const int64_t Kb = c.w_is_nk ? w.shape(w.rank() - 1) : w.shape(w.rank() - 2);
+    const int64_t N = c.w_is_nk ? w.shape(w.rank() - 2) : w.shape(w.rank() - 1);
+    if (Ka != Kb) {
+        return Status::invalid_argument;
+    }
+    BatchLayout L;
+    if (!batch_layout(a, w, out, L)) {
+        return Status::unsupported;
+    }
+
+    nnb200_gemm_i8_args g;
+    std::memset(&g, 0, sizeof(g));
+    g.m = M;
+    g.n = N;
+    g.k = Ka;
+    g.a_stride_m = c.transpose_a ? 1 : a.row_stride_elems();
+    g.a_stride_k = c.transpose_a ? a.row_stride_elems() : 1;
+    g.w_stride_n = c.w_is_nk ? w.row_stride_elems() : 1;
+    g.w_stride_k = c.w_is_nk ? 1 : w.row_stride_elems();
+    g.ldc = out.row_stride_elems();
+    g.batch = 1;
+    g.a_unsigned = a.data_type() == DataType::u8;
+    g.out_kind = c.kind;
+    const bool int_out = c.kind <= NNB200_OUT_U8;
+    g.relu = int_out && c.ep->type == EpilogueActivateType::Relu;
+    g.activation = static_cast<int32_t>(c.ep->type);
+    g.act_alpha = c.ep->alpha;
+    g.act_beta = c.ep->beta;
+    g.min_clip = c.ep->min_clip;
+    g.max_clip = c.ep->max_clip;
+
+    const QuantParams& qa = a.quant_params();
+    const QuantParams& qw = w.quant_params();
+    g.scale_a_scalar = qa.scale;
+    g.scale_w_scalar = qw.scale;
+    g.zp_a_scalar = qa.zero_point;
+    g.zp_w_scalar = qw.zero_point;
+    g.out_scale = 1.0f;
+    if (int_out) {
+        // Output parameters are per-tensor; element 0 of an array form is read on the host.
+        const QuantParams& qc = out.quant_params();
+        if ((qc.scale_data != nullptr && nnb200_is_device_pointer(qc.scale_data)) ||
+            (qc.zero_point_data != nullptr && nnb200_is_device_pointer(qc.zero_point_data))) {
+            return Status::unsupported;
+        }
+        g.out_scale = qc.scale_data != nullptr ? qc.scale_data[0] : qc.scale;
+        g.out_zp = qc.zero_point_data != nullptr ? qc.zero_point_data[0] : qc.zero_point;
+    }
+    g.bias = c.bias != nullptr ? c.bias->ptr<void>() : nullptr;
+
+    // Stage host-side arrays, then size the kernels' scratch with the final argument block.
+    Staging st(ctx.cuda_stream);
+    const size_t m_bytes = static_cast<size_t>(M) * 4, n_bytes = static_cast<size_t>(N) * 4;
+    st.reserve(qa.scale_data, m_bytes);
+    st.reserve(qa.zero_point_data, m_bytes);
+    st.reserve(qw.scale_data, n_bytes);
+    st.reserve(qw.zero_point_data, n_bytes);
+    // Scratch for the two zero-point sweeps, only when some zero point can be non-zero.
+    if (qa.zero_point != 0 || qw.zero_point != 0 || qa.zero_point_data != nullptr || qw.zero_point_data != nullptr) {
+        st.reserve_raw(((m_bytes + 255) & ~size_t(255)) + ((n_bytes + 255) & ~size_t(255)));
+    }
+    if (const int e = st.allocate(); e != NNB200_OK) {
+        return to_status(e);
+    }
+    DeviceArray sa, za, sw, zw;
+    for (const int e : {st.place(qa.scale_data, m_bytes, false, sa), st.place(qa.zero_point_data, m_bytes, true, za),
+                        st.place(qw.scale_data, n_bytes, false, sw), st.place(qw.zero_point_data, n_bytes, true, zw)}) {
+        if (e != NNB200_OK) {
+            return to_status(e);
+        }
+    }
+    g.scale_a = static_cast<const float*>(sa.ptr);
+    g.zp_a = static_cast<const int32_t*>(za.ptr);
+    g.scale_w = static_cast<const float*>(sw.ptr);
+    g.zp_w = static_cast<const int32_t*>(zw.ptr);
+    g.zp_a_nonzero = za.ptr != nullptr && za.any_nonzero;
+    g.zp_w_nonzero = zw.ptr != nullptr && zw.any_nonzero;
+    g.a = a.ptr<void>();
+    g.w = w.ptr<void>();
+    g.out = out.ptr<void>();
+    const size_t need = nnb200_gemm_i8_workspace_bytes(&g);
+    if (need > 0) {
+        g.workspace = st.take_raw(need);
+        g.workspace_bytes = need;
+    }
+
+    // Walk the broadcast batch; each slice is one 2-D call.
+    const size_t out_elem = data_type_size(out.data_type());
+    std::array<int64_t, kMaxBatchRank> idx{};
+    for (int64_t b = 0; b < L.count; ++b) {
+        int64_t ao = 0, wo = 0, co = 0;
+        for (int d = 0; d < L.rank; ++d) {
+            ao += idx[static_cast<size_t>(d)] * L.a_stride[d];
+            wo += idx[static_cast<size_t>(d)] * L.b_stride[d];
+            co += idx[static_cast<size_t>(d)] * L.c_stride[d];
+        }
+        g.a = a.ptr<char>() + ao;  // 1-byte elements
+        g.w = w.ptr<char>() + wo;
+        g.out = out.ptr<char>() + co * static_cast<int64_t>(out_elem);
+        if (const int e = nnb200_gemm_i8(&g, ctx.cuda_stream); e != NNB200_OK) {
+            return to_status(e);
+        }
+        for (int d = L.rank - 1; d >= 0; --d) {
+            if (++idx[static_cast<size_t>(d)] < L.size[d]) {
+                break;
+            }
+            idx[static_cast<size_t>(d)] = 0;
+        }
+    }
+    return Status::ok;
+}
+
+// f16/f32 activations x q4_1 weights stored [N, K].
+Status run_q4_1(const TensorView& x, const TensorView& w, const TensorView* bias, TensorView& out, float alpha,
+                const Epilogue& ep, const ComputeContext& ctx)
+{
+    if (w.rank() != 2 || x.rank() < 2 || out.rank() < 2) {
+        return Status::unsupported;
+    }
+    const DataType xdt = x.data_type();
+    const DataType odt = out.data_type();
+    if ((xdt != DataType::f16 && xdt != DataType::f32) || (odt != DataType::f16 && odt != DataType::f32)) {
+        return Status::unsupported;
+    }
+    if (xdt == DataType::f32 && odt == DataType::f16) {
+        return Status::unsupported;  // the output is at least as wide as the activations
+    }
+    const int64_t K = x.shape(x.rank() - 1);
+    const int64_t N = w.shape(0);
+    if (w.shape(1) != K) {
+        return Status::invalid_argument;
+    }
+    if (bias != nullptr && bias->data_type() != odt) {
+        return Status::invalid_argument;
+    }
+    // Leading axes of x are rows of one tall matrix when they are densely pitched.
+    int64_t rows = 1;
+    for (int64_t d = 0; d + 1 < x.rank(); ++d) {
+        rows *= x.shape(d);
+    }
+    nnb200_q4_1_args q;
+    std::memset(&q, 0, sizeof(q));
+    q.a = x.ptr<void>();
+    q.w_blocks = w.ptr<void>();
+    q.out = out.ptr<void>();
+    q.m = rows;
+    q.n = N;
+    q.k = K;
+    q.lda = x.row_stride_elems();
+    q.ldw_blocks = w.row_stride_elems();
+    q.ldc = out.row_stride_elems();
+    q.a_f16 = xdt == DataType::f16;
+    q.out_f16 = odt == DataType::f16;
+    q.bias = bias != nullptr ? bias->ptr<void>() : nullptr;
+    q.activation = static_cast<int32_t>(ep.type);
+    q.act_alpha = ep.alpha;
+    q.act_beta = ep.beta;
+    q.min_clip = ep.min_clip;
+    q.max_clip = ep.max_clip;
+    q.alpha = alpha;
+    return to_status(nnb200_linear_q4_1(&q, ctx.cuda_stream));
+}
+
+}  // namespace
+
+Status linear_cuda(const LinearAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
+                   const ComputeContext& ctx, void*)
+{
+    const TensorView& x = inputs[0];
+    const TensorView& w = inputs[1];
+    const TensorView* bias = inputs.size() > 2 ? &inputs[2] : nullptr;
+    if (attrs.gated) {
+        return Status::unsupported;  // the gated combine has no CUDA route (reference linear.cu:102)
+    }
+    if (is_int8_matmul(x.data_type(), w.data_type())) {
+        if (output.numel() == 0) {
+            return Status::ok;
+        }
+        int kind;
+        if (!out_kind_of(output.data_type(), kind)) {
+            return Status::unsupported;
+        }
+        if (attrs.add_to) {
+            return Status::unsupported;  // no residual on the integer route (reference linear.cu:34)
+        }
+        if (w.rank() != 2) {
+            return Status::invalid_argument;
+        }
+        const I8Call call{&x, &w, bias, &output, false, true, &attrs.epilogue, kind};
+        return run_i8(call, ctx);
+    }
+    if (w.data_type() == DataType::q4_1) {
+        if (output.numel() == 0) {
+            return Status::ok;
+        }
+        if (attrs.add_to) {
+            return Status::unsupported;
+        }
+        return run_q4_1(x, w, bias, output, 1.0f, attrs.epilogue, ctx);
+    }
+    return Status::unsupported;  // dense fp Linear is outside this backend
+}
+
+Status matmul_cuda(const MatMulAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
+                   const ComputeContext& ctx, void*)
+{
+    const TensorView& a = inputs[0];
+    const TensorView& b = inputs[1];
+    const TensorView* bias = inputs.size() > 2 ? &inputs[2] : nullptr;
+    if (is_int8_matmul(a.data_type(), b.data_type())) {
+        if (output.numel() == 0) {
+            return Status::ok;
+        }
+        int kind;
+        if (!out_kind_of(output.data_type(), kind)) {
+            return Status::unsupported;
+        }
+        const I8Call call{&a, &b, bias, &output, attrs.transpose_a, attrs.transpose_b, &attrs.epilogue, kind};
+        return run_i8(call, ctx);
+    }
+    if (b.data_type() == DataType::q4_1) {
+        if (output.numel() == 0) {
+            return Status::ok;
+        }
+        // Only the [N, K] weight pose with row-major activations is served; no accumulate into C.
+        if (!attrs.transpose_b || attrs.transpose_a || attrs.beta != 0.0f) {
+            return Status::unsupported;
+        }
+        return run_q4_1(a, b, bias, output, attrs.alpha, attrs.epilogue, ctx);
+    }
+    return Status::unsupported;
+}
+
+}  // namespace nnops::backend::cuda

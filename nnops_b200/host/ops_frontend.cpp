@@ -1,0 +1,185 @@
+// Stand-alone front end of Linear and MatMul for builds without the nnops source tree:
+// create / getOutputTensorDesc / validate / compute with the reference's argument checks and
+// status codes (src/ops/linear.cpp:26-120, src/ops/matmul.cpp:36-152,
+// include/nnops/detail/validate.hpp:70-96, include/nnops/detail/shape_inference.hpp:453-526),
+// dispatching to the CUDA backend.  There is no CPU route here: an operator created for
+// another backend answers Status::unsupported.
+
+#include "nnops_b200/nnops_api.hpp"
+
+#include <algorithm>
+
+namespace nnops {
+
+const char* to_string(Status s) noexcept
+{
+    switch (s) {
+    case Status::ok: return "ok";
+    case Status::invalid_argument: return "invalid_argument";
+    case Status::unsupported: return "unsupported";
+    case Status::not_initialized: return "not_initialized";
+    case Status::out_of_memory: return "out_of_memory";
+    case Status::internal: return "internal";
+    }
+    return "unknown";
+}
+
+namespace {
+
+Status check_counts(size_t n_in, size_t n_out, size_t min_in, size_t max_in, size_t want_out)
+{
+    return (n_in >= min_in && n_in <= max_in && n_out == want_out) ? Status::ok : Status::invalid_argument;
+}
+
+// Counts, then "every view has storage": a call with a null view is rejected before any work.
+Status check_views(std::span<TensorView> outputs, std::span<const TensorView> inputs, size_t min_in, size_t max_in)
+{
+    if (check_counts(inputs.size(), outputs.size(), min_in, max_in, 1) != Status::ok) {
+        return Status::invalid_argument;
+    }
+    for (const auto& v : inputs) {
+        if (v.is_empty() && v.numel() != 0) {
+            return Status::invalid_argument;
+        }
+    }
+    for (const auto& v : outputs) {
+        if (v.is_empty() && v.numel() != 0) {
+            return Status::invalid_argument;
+        }
+    }
+    return Status::ok;
+}
+
+template <class Op>
+Status validate_views(const Op& op, std::span<TensorView> outputs, std::span<const TensorView> inputs)
+{
+    std::vector<TensorDesc> in_d, out_d;
+    for (const auto& v : inputs) in_d.push_back(v.desc());
+    for (const auto& v : outputs) out_d.push_back(v.desc());
+    return op.validate(in_d, out_d);
+}
+
+}  // namespace
+
+// ---- Linear -----------------------------------------------------------------------------
+
+std::unique_ptr<Linear> Linear::create(const LinearAttributes& attrs, Backend backend)
+{
+    return std::unique_ptr<Linear>(new Linear(attrs, backend));  // never fails
+}
+
+std::vector<TensorDesc> Linear::getOutputTensorDesc(std::span<const TensorDesc> inputs) const
+{
+    const TensorDesc& x = inputs[0];
+    const TensorDesc& w = inputs[1];
+    TensorDesc out = x;  // [.., K] -> [.., N], activation dtype
+    out.row_stride_elems = 0;
+    if (out.rank >= 1 && w.rank == 2) {
+        out.dims[static_cast<size_t>(out.rank - 1)] = attrs_.gated ? w.dims[0] / 2 : w.dims[0];
+    }
+    if (is_int8_matmul(x.dtype, w.dtype)) {
+        const DataType odt = attrs_.output_dtype;
+        const bool known = odt == DataType::f16 || odt == DataType::f32 || odt == DataType::s32 ||
+                           odt == DataType::s8 || odt == DataType::u8;
+        out.dtype = known ? odt : DataType::f32;
+    }
+    return {out};
+}
+
+Status Linear::validate(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs) const
+{
+    if (check_counts(inputs.size(), outputs.size(), 2, 3, 1) != Status::ok) {
+        return Status::invalid_argument;
+    }
+    if (backend_ == Backend::CUDA && inputs[0].rank > 6) {
+        return Status::unsupported;
+    }
+    if (attrs_.add_to && attrs_.residual_pre_activation && (attrs_.gated || backend_ != Backend::CPU)) {
+        return Status::unsupported;
+    }
+    return Status::ok;
+}
+
+Status Linear::compute(std::span<TensorView> outputs, std::span<const TensorView> inputs, const ComputeContext& ctx,
+                       void* workspace)
+{
+    if (const Status s = check_views(outputs, inputs, 2, 3); s != Status::ok) {
+        return s;
+    }
+    if (const Status s = validate_views(*this, outputs, inputs); s != Status::ok) {
+        return s;
+    }
+    if (backend_ != Backend::CUDA) {
+        return Status::unsupported;
+    }
+    return backend::cuda::linear_cuda(attrs_, outputs[0], inputs, ctx, workspace);
+}
+
+// ---- MatMul -----------------------------------------------------------------------------
+
+std::unique_ptr<MatMul> MatMul::create(const MatMulAttributes& attrs, Backend backend)
+{
+    return std::unique_ptr<MatMul>(new MatMul(attrs, backend));
+}
+
+std::vector<TensorDesc> MatMul::getOutputTensorDesc(std::span<const TensorDesc> inputs) const
+{
+    const TensorDesc& a = inputs[0];
+    const TensorDesc& b = inputs[1];
+    const int64_t ra = a.rank, rb = b.rank;
+    const int64_t M = attrs_.transpose_a ? a.dims[static_cast<size_t>(ra - 1)] : a.dims[static_cast<size_t>(ra - 2)];
+    const int64_t N = attrs_.transpose_b ? b.dims[static_cast<size_t>(rb - 2)] : b.dims[static_cast<size_t>(rb - 1)];
+    // numpy broadcast of the leading axes, right-aligned.
+    const int64_t la = ra - 2, lb = rb - 2, lr = std::max(la, lb);
+    TensorDesc out;
+    out.layout = a.layout;
+    out.dtype = is_int8_matmul(a.dtype, b.dtype) ? attrs_.output_dtype : a.dtype;
+    out.rank = lr + 2;
+    for (int64_t d = 0; d < lr; ++d) {
+        const int64_t ai = la - 1 - d, bi = lb - 1 - d;
+        const int64_t ad = ai >= 0 ? a.dims[static_cast<size_t>(ai)] : 1;
+        const int64_t bd = bi >= 0 ? b.dims[static_cast<size_t>(bi)] : 1;
+        out.dims[static_cast<size_t>(lr - 1 - d)] = std::max(ad, bd);
+    }
+    out.dims[static_cast<size_t>(lr)] = M;
+    out.dims[static_cast<size_t>(lr + 1)] = N;
+    return {out};
+}
+
+Status MatMul::validate(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs) const
+{
+    if (check_counts(inputs.size(), outputs.size(), 2, 3, 1) != Status::ok) {
+        return Status::invalid_argument;
+    }
+    if (attrs_.residual_pre_activation && backend_ != Backend::CPU) {
+        return Status::unsupported;
+    }
+    const TensorDesc& a = inputs[0];
+    const TensorDesc& b = inputs[1];
+    if (a.rank < 2 || b.rank < 2) {
+        return Status::invalid_argument;
+    }
+    if (backend_ == Backend::CUDA && (a.rank > 6 || b.rank > 6)) {
+        return Status::unsupported;
+    }
+    const int64_t k_a = attrs_.transpose_a ? a.dims[static_cast<size_t>(a.rank - 2)] : a.dims[static_cast<size_t>(a.rank - 1)];
+    const int64_t k_b = attrs_.transpose_b ? b.dims[static_cast<size_t>(b.rank - 1)] : b.dims[static_cast<size_t>(b.rank - 2)];
+    return k_a == k_b ? Status::ok : Status::invalid_argument;
+}
+
+Status MatMul::compute(std::span<TensorView> outputs, std::span<const TensorView> inputs, const ComputeContext& ctx,
+                       void* workspace)
+{
+    if (const Status s = check_views(outputs, inputs, 2, 3); s != Status::ok) {
+        return s;
+    }
+    if (const Status s = validate_views(*this, outputs, inputs); s != Status::ok) {
+        return s;
+    }
+    if (backend_ != Backend::CUDA) {
+        return Status::unsupported;
+    }
+    return backend::cuda::matmul_cuda(attrs_, outputs[0], inputs, ctx, workspace);
+}
+
+}  // namespace nnops

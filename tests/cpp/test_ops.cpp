@@ -1,0 +1,513 @@
+// Operator-level tests of the CUDA backend through the nnops API: Linear / MatMul created with
+// Backend::CUDA, pitched non-owning TensorViews over device memory, the stream in
+// ComputeContext.  The cases follow the reference's own tests -- the hand-computed vectors of
+// tests/test_matmul_int8.cpp:106-285, the differential cases of tests/test_cuda_matmul.cpp:681-889
+// and tests/test_cuda_linear.cpp:190-351, the contract cases of tests/test_status.cpp -- and read
+// like them.
+//
+// Built twice by nnops_b200/host/build.py:
+//   * against the stand-alone API mirror (expected values from the C oracle), and
+//   * with NNB200_USE_NNOPS_HEADERS against the real nnops tree, where the same operator is
+//     also run on Backend::CPU (the reference's CPU route) and compared byte for byte.
+
+#ifdef NNB200_USE_NNOPS_HEADERS
+#include "nnops/ops/linear.hpp"
+#include "nnops/ops/matmul.hpp"
+#else
+#include "nnops_b200/nnops_api.hpp"
+#endif
+
+#include <cuda_runtime_api.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <random>
+#include <string>
+#include <vector>
+
+using namespace nnops;
+
+// ---- C oracle (oracle/nnops_oracle.c) -----------------------------------------------------
+extern "C" {
+struct oracle_gemm_i8_args {
+    const void* a; const int8_t* w; void* out;
+    int64_t m, n, k;
+    int64_t a_stride_m, a_stride_k, w_stride_n, w_stride_k, ldc;
+    int32_t a_unsigned; int32_t out_kind;
+    const void* bias; int32_t relu;
+    const float* scale_a; const float* scale_w; const int32_t* zp_a; const int32_t* zp_w;
+    float scale_a_scalar, scale_w_scalar; int32_t zp_a_scalar, zp_w_scalar;
+    float out_scale; int32_t out_zp; float min_clip, max_clip;
+};
+void oracle_gemm_i8(const oracle_gemm_i8_args* p);
+void oracle_q4_1_matmul(const void* a, int a_is_f16, int64_t lda, const uint8_t* w_blocks, int64_t ldw_blocks, void* out,
+                        int out_is_f16, int64_t ldc, int64_t m, int64_t n, int64_t k, int w_round_f16, const void* bias);
+uint16_t oracle_f32_to_f16(float f);
+float oracle_f16_to_f32(uint16_t h);
+}
+
+// ---- tiny harness -------------------------------------------------------------------------
+static int g_checks = 0, g_failed = 0;
+static const char* g_case = "";
+#define EXPECT(cond)                                                                       \
+    do {                                                                                   \
+        ++g_checks;                                                                        \
+        if (!(cond)) {                                                                     \
+            ++g_failed;                                                                    \
+            std::printf("FAIL [%s] %s:%d: %s\n", g_case, __FILE__, __LINE__, #cond);      \
+        }                                                                                  \
+    } while (0)
+#define CUDA_OK(x)                                                                    \
+    do {                                                                              \
+        if ((x) != cudaSuccess) {                                                     \
+            std::printf("CUDA error at %s:%d\n", __FILE__, __LINE__);                \
+            std::exit(2);                                                             \
+        }                                                                             \
+    } while (0)
+
+struct DevBuf {
+    void* p = nullptr;
+    size_t bytes = 0;
+    explicit DevBuf(size_t n, int fill = 0) : bytes(n)
+    {
+        CUDA_OK(cudaMalloc(&p, n ? n : 1));
+        CUDA_OK(cudaMemset(p, fill, n ? n : 1));
+    }
+    DevBuf(const void* host, size_t n) : bytes(n)
+    {
+        CUDA_OK(cudaMalloc(&p, n ? n : 1));
+        CUDA_OK(cudaMemcpy(p, host, n, cudaMemcpyHostToDevice));
+    }
+    ~DevBuf() { cudaFree(p); }
+    template <class T> std::vector<T> download() const
+    {
+        std::vector<T> v(bytes / sizeof(T));
+        CUDA_OK(cudaDeviceSynchronize());
+        CUDA_OK(cudaMemcpy(v.data(), p, bytes, cudaMemcpyDeviceToHost));
+        return v;
+    }
+    DevBuf(const DevBuf&) = delete;
+    DevBuf& operator=(const DevBuf&) = delete;
+};
+
+static QuantParams per_tensor(float s, int32_t z)
+{
+    QuantParams q;
+    q.scale = s;
+    q.zero_point = z;
+    return q;
+}
+static QuantParams arrays(const float* s, const int32_t* z, int64_t n, QuantGranularity g)
+{
+    QuantParams q;
+    q.granularity = g;
+    q.scale_data = s;
+    q.zero_point_data = z;
+    q.num_scales = n;
+    return q;
+}
+template <size_t R> static TensorView view(const int64_t (&shape)[R], DataType dt, void* data, QuantParams q = {})
+{
+    return TensorView(std::span<const int64_t>(shape, R), dt, data, TensorLayout::Dense, q);
+}
+
+// ---- exact-value cases (reference tests/test_matmul_int8.cpp:106-285) ----------------------
+
+static void kat_basic_s32()
+{
+    g_case = "matmul_int8_basic_s32";
+    const int8_t a_h[6] = {1, -2, 3, -4, 5, -6};
+    const int8_t b_h[6] = {1, 2, 3, 4, 5, 6};  // [K=3, N=2]
+    DevBuf a(a_h, 6), b(b_h, 6), c(16, 0x7F);
+    const int64_t as[] = {2, 3}, bs[] = {3, 2}, cs[] = {2, 2};
+    MatMulAttributes attrs;
+    attrs.output_dtype = DataType::s32;
+    auto op = MatMul::create(attrs, Backend::CUDA);
+    const TensorDesc in_d[] = {view(as, DataType::s8, a.p).desc(), view(bs, DataType::s8, b.p).desc()};
+    const auto od = op->getOutputTensorDesc(in_d);
+    EXPECT(od[0].dtype == DataType::s32 && od[0].rank == 2 && od[0].dims[0] == 2 && od[0].dims[1] == 2);
+    TensorView out = view(cs, DataType::s32, c.p);
+    const TensorView ins[] = {view(as, DataType::s8, a.p), view(bs, DataType::s8, b.p)};
+    EXPECT(op->compute(out, ins) == Status::ok);
+    const auto r = c.download<int32_t>();
+    EXPECT(r[0] == 10 && r[1] == 12 && r[2] == -19 && r[3] == -24);
+}
+
+static void kat_zero_points()
+{
+    g_case = "matmul_int8_zeropoint_s32";
+    const int8_t a_h[6] = {1, 2, 3, 4, 5, 6}, w_h[6] = {7, 8, 9, 10, 11, 12};
+    const float ones[2] = {1.0f, 1.0f};
+    const int32_t a_zp[2] = {1, 2}, w_zp[2] = {3, 4};  // HOST arrays, as the reference passes them
+    DevBuf a(a_h, 6), w(w_h, 6), c(16);
+    const int64_t s23[] = {2, 3}, s22[] = {2, 2};
+    MatMulAttributes attrs;
+    attrs.transpose_b = true;
+    attrs.output_dtype = DataType::s32;
+    auto op = MatMul::create(attrs, Backend::CUDA);
+    TensorView out = view(s22, DataType::s32, c.p);
+    const TensorView ins[] = {view(s23, DataType::s8, a.p, arrays(ones, a_zp, 2, QuantGranularity::PerToken)),
+                              view(s23, DataType::s8, w.p, arrays(ones, w_zp, 2, QuantGranularity::PerChannel))};
+    EXPECT(op->compute(out, ins) == Status::ok);
+    const auto r = c.download<int32_t>();
+    EXPECT(r[0] == 17 && r[1] == 23 && r[2] == 47 && r[3] == 65);
+}
+
+static void kat_u8_zero_points()
+{
+    g_case = "matmul_int8_u8_zeropoint_s32";
+    const uint8_t a_h[6] = {130, 128, 3, 200, 255, 0};
+    const int8_t b_h[6] = {1, -4, 2, 5, 3, -6};
+    const float ones[2] = {1.0f, 1.0f};
+    const int32_t a_zp[2] = {128, 100};
+    DevBuf a(a_h, 6), b(b_h, 6), c(16);
+    const int64_t as[] = {2, 3}, bs[] = {3, 2}, cs[] = {2, 2};
+    MatMulAttributes attrs;
+    attrs.output_dtype = DataType::s32;
+    auto op = MatMul::create(attrs, Backend::CUDA);
+    TensorView out = view(cs, DataType::s32, c.p);
+    const TensorView ins[] = {view(as, DataType::u8, a.p, arrays(ones, a_zp, 2, QuantGranularity::PerToken)),
+                              view(bs, DataType::s8, b.p, per_tensor(1.0f, 3))};
+    EXPECT(op->compute(out, ins) == Status::ok);
+    const auto r = c.download<int32_t>();
+    EXPECT(r[0] == -4 && r[1] == 1111 && r[2] == -355 && r[3] == 510);
+}
+
+static void kat_requant()
+{
+    g_case = "matmul_int8_requant_s8";
+    {
+        const int8_t a_h[2] = {4, 6}, w_h[4] = {1, 1, 1, 1};
+        DevBuf a(a_h, 2), w(w_h, 4), c(2);
+        const int64_t as[] = {1, 2}, ws[] = {2, 2}, cs[] = {1, 2};
+        MatMulAttributes attrs;
+        attrs.transpose_b = true;
+        attrs.output_dtype = DataType::s8;
+        auto op = MatMul::create(attrs, Backend::CUDA);
+        TensorView out = view(cs, DataType::s8, c.p, per_tensor(2.0f, 0));
+        const TensorView ins[] = {view(as, DataType::s8, a.p), view(ws, DataType::s8, w.p)};
+        EXPECT(op->compute(out, ins) == Status::ok);
+        const auto r = c.download<int8_t>();
+        EXPECT(r[0] == 5 && r[1] == 5);
+    }
+    g_case = "matmul_int8_requant_clamp_s8";
+    {
+        const int8_t a_h[2] = {100, 100}, w_h[4] = {100, 100, 100, 100};
+        DevBuf a(a_h, 2), w(w_h, 4), c(2);
+        const int64_t as[] = {1, 2}, ws[] = {2, 2}, cs[] = {1, 2};
+        MatMulAttributes attrs;
+        attrs.transpose_b = true;
+        attrs.output_dtype = DataType::s8;
+        auto op = MatMul::create(attrs, Backend::CUDA);
+        TensorView out = view(cs, DataType::s8, c.p, per_tensor(1.0f, 0));
+        const TensorView ins[] = {view(as, DataType::s8, a.p), view(ws, DataType::s8, w.p)};
+        EXPECT(op->compute(out, ins) == Status::ok);
+        const auto r = c.download<int8_t>();
+        EXPECT(r[0] == 127 && r[1] == 127);
+    }
+}
+
+// ---- differential cases --------------------------------------------------------------------
+
+struct LinearCase {
+    int64_t batch, m, n, k;
+    DataType out_dt;
+    bool relu, per_token, per_channel, zero_points, device_arrays;
+    int64_t a_pad, w_pad, c_pad;  // extra bytes/elements of row pitch
+};
+
+static int kind_of(DataType dt)
+{
+    switch (dt) {
+    case DataType::s32: return 0;
+    case DataType::s8: return 1;
+    case DataType::u8: return 2;
+    case DataType::f32: return 3;
+    default: return 4;
+    }
+}
+
+static void linear_i8_case(const LinearCase& c, const char* name, cudaStream_t stream)
+{
+    g_case = name;
+    std::mt19937_64 rng(c.m * 131 + c.n * 17 + c.k);
+    const int64_t rows = c.batch * c.m;
+    const int64_t lda = c.k + c.a_pad, ldw = c.k + c.w_pad, ldc = c.n + c.c_pad;
+    const size_t osz = data_type_size(c.out_dt);
+    std::vector<int8_t> a(rows * lda), w(c.n * ldw);
+    for (auto& v : a) v = static_cast<int8_t>(static_cast<int>(rng() % 255) - 127);
+    for (auto& v : w) v = static_cast<int8_t>(static_cast<int>(rng() % 255) - 127);
+    std::vector<int32_t> bias(c.n), zpa(c.m), zpw(c.n);
+    std::vector<float> sa(c.m), sw(c.n);
+    std::uniform_real_distribution<float> us(0.001f, 0.02f), ua(0.01f, 0.03f);
+    for (auto& v : bias) v = static_cast<int32_t>(rng() % 2001) - 1000;
+    for (auto& v : sa) v = ua(rng);
+    for (auto& v : sw) v = us(rng);
+    for (auto& v : zpa) v = c.zero_points ? static_cast<int32_t>(rng() % 19) - 9 : 0;
+    for (auto& v : zpw) v = c.zero_points ? static_cast<int32_t>(rng() % 19) - 9 : 0;
+    const bool int_out = kind_of(c.out_dt) <= 2;
+    std::vector<float> bias_f(c.n);
+    std::vector<uint16_t> bias_h(c.n);
+    for (int64_t i = 0; i < c.n; ++i) {
+        bias_f[i] = 0.01f * static_cast<float>(bias[i]);
+        bias_h[i] = oracle_f32_to_f16(bias_f[i]);
+    }
+    const void* bias_host = int_out ? static_cast<const void*>(bias.data())
+                                    : (c.out_dt == DataType::f32 ? static_cast<const void*>(bias_f.data())
+                                                                 : static_cast<const void*>(bias_h.data()));
+    const size_t bias_bytes = static_cast<size_t>(c.n) * (int_out ? 4 : osz);
+    const float out_scale = 1.7f;
+    const int32_t out_zp = c.out_dt == DataType::s32 ? 0 : 3;
+
+    // Expected: the C oracle, one batch slice at a time (per-token arrays index the row inside the slice).
+    std::vector<uint8_t> want(rows * ldc * osz, 0x5A);
+    for (int64_t b = 0; b < c.batch; ++b) {
+        oracle_gemm_i8_args o{};
+        o.a = a.data() + b * c.m * lda;
+        o.w = w.data();
+        o.out = want.data() + b * c.m * ldc * osz;
+        o.m = c.m; o.n = c.n; o.k = c.k;
+        o.a_stride_m = lda; o.a_stride_k = 1; o.w_stride_n = ldw; o.w_stride_k = 1; o.ldc = ldc;
+        o.out_kind = kind_of(c.out_dt);
+        o.bias = bias_host;
+        o.relu = c.relu;
+        o.scale_a = c.per_token ? sa.data() : nullptr;
+        o.scale_w = c.per_channel ? sw.data() : nullptr;
+        o.zp_a = c.per_token && c.zero_points ? zpa.data() : nullptr;
+        o.zp_w = c.per_channel && c.zero_points ? zpw.data() : nullptr;
+        o.scale_a_scalar = c.per_token ? 1.0f : 0.02f;
+        o.scale_w_scalar = c.per_channel ? 1.0f : 0.01f;
+        o.zp_a_scalar = (!c.per_token && c.zero_points) ? 2 : 0;
+        o.zp_w_scalar = (!c.per_channel && c.zero_points) ? -3 : 0;
+        o.out_scale = out_scale; o.out_zp = out_zp;
+        o.min_clip = -INFINITY; o.max_clip = INFINITY;
+        oracle_gemm_i8(&o);
+    }
+
+    DevBuf da(a.data(), a.size()), dw(w.data(), w.size()), dbias(bias_host, bias_bytes);
+    DevBuf dout(want.size(), 0x5A);
+    DevBuf dsa(sa.data(), sa.size() * 4), dsw(sw.data(), sw.size() * 4), dza(zpa.data(), zpa.size() * 4),
+        dzw(zpw.data(), zpw.size() * 4);
+    QuantParams qa = per_tensor(0.02f, c.zero_points ? 2 : 0), qw = per_tensor(0.01f, c.zero_points ? -3 : 0);
+    if (c.per_token) {
+        qa = arrays(c.device_arrays ? static_cast<const float*>(dsa.p) : sa.data(),
+                    c.zero_points ? (c.device_arrays ? static_cast<const int32_t*>(dza.p) : zpa.data()) : nullptr, c.m,
+                    QuantGranularity::PerToken);
+    }
+    if (c.per_channel) {
+        qw = arrays(c.device_arrays ? static_cast<const float*>(dsw.p) : sw.data(),
+                    c.zero_points ? (c.device_arrays ? static_cast<const int32_t*>(dzw.p) : zpw.data()) : nullptr, c.n,
+                    QuantGranularity::PerChannel);
+    }
+    const int64_t xs3[] = {c.batch, c.m, c.k}, xs2[] = {c.m, c.k}, ws[] = {c.n, c.k}, bs[] = {c.n};
+    const int64_t os3[] = {c.batch, c.m, c.n}, os2[] = {c.m, c.n};
+    const bool b3 = c.batch > 1;
+    TensorView x = b3 ? TensorView(xs3, DataType::s8, da.p, lda, TensorLayout::Dense, qa)
+                      : TensorView(xs2, DataType::s8, da.p, lda, TensorLayout::Dense, qa);
+    TensorView wv(ws, DataType::s8, dw.p, ldw, TensorLayout::Dense, qw);
+    TensorView bv(bs, int_out ? DataType::s32 : c.out_dt, dbias.p);
+    TensorView out = b3 ? TensorView(os3, c.out_dt, dout.p, ldc * static_cast<int64_t>(osz), TensorLayout::Dense,
+                                     per_tensor(out_scale, out_zp))
+                        : TensorView(os2, c.out_dt, dout.p, ldc * static_cast<int64_t>(osz), TensorLayout::Dense,
+                                     per_tensor(out_scale, out_zp));
+
+    LinearAttributes attrs;
+    attrs.output_dtype = c.out_dt;
+    attrs.epilogue.type = c.relu ? EpilogueActivateType::Relu : EpilogueActivateType::None;
+    auto op = Linear::create(attrs, Backend::CUDA);
+    const TensorDesc in_d[] = {x.desc(), wv.desc(), bv.desc()};
+    const auto od = op->getOutputTensorDesc(in_d);
+    EXPECT(od[0].dtype == c.out_dt && od[0].dims[static_cast<size_t>(od[0].rank - 1)] == c.n);
+    const TensorDesc out_d[] = {out.desc()};
+    EXPECT(op->validate(in_d, out_d) == Status::ok);
+    ComputeContext ctx;
+    ctx.expected_backend = Backend::CUDA;
+    ctx.cuda_stream = stream;
+    const TensorView ins[] = {x, wv, bv};
+    EXPECT(op->compute(out, ins, ctx) == Status::ok);
+    const auto got = dout.download<uint8_t>();
+    EXPECT(got == want);  // byte for byte, padding canaries included
+
+#ifdef NNB200_USE_NNOPS_HEADERS
+    // The reference's own CPU route on the same bytes (host views).
+    if (!c.device_arrays) {
+        std::vector<uint8_t> cpu(want.size(), 0x5A);
+        QuantParams hqa = qa, hqw = qw;
+        TensorView hx = b3 ? TensorView(xs3, DataType::s8, a.data(), lda, TensorLayout::Dense, hqa)
+                           : TensorView(xs2, DataType::s8, a.data(), lda, TensorLayout::Dense, hqa);
+        TensorView hw(ws, DataType::s8, w.data(), ldw, TensorLayout::Dense, hqw);
+        TensorView hb(bs, int_out ? DataType::s32 : c.out_dt, const_cast<void*>(bias_host));
+        TensorView ho = b3 ? TensorView(os3, c.out_dt, cpu.data(), ldc * static_cast<int64_t>(osz), TensorLayout::Dense,
+                                        per_tensor(out_scale, out_zp))
+                           : TensorView(os2, c.out_dt, cpu.data(), ldc * static_cast<int64_t>(osz), TensorLayout::Dense,
+                                        per_tensor(out_scale, out_zp));
+        auto cpu_op = Linear::create(attrs, Backend::CPU);
+        const TensorView hins[] = {hx, hw, hb};
+        EXPECT(cpu_op->compute(ho, hins) == Status::ok);
+        EXPECT(cpu == got);
+    }
+#endif
+}
+
+static void linear_q4_1_case(int64_t m, int64_t n, int64_t k, bool out_f16, const char* name)
+{
+    g_case = name;
+    std::mt19937_64 rng(m + n + k);
+    const int64_t nblk = (k + 31) / 32;
+    std::vector<uint8_t> wb(n * nblk * 20);
+    std::uniform_real_distribution<float> ud(0.005f, 0.02f), uu(0.8f, 1.2f);
+    std::normal_distribution<float> na(0.0f, 1.0f);
+    for (int64_t i = 0; i < n * nblk; ++i) {
+        const uint16_t d = oracle_f32_to_f16(ud(rng));
+        const uint16_t mn = oracle_f32_to_f16(-8.0f * oracle_f16_to_f32(d) * uu(rng));
+        std::memcpy(&wb[i * 20], &d, 2);
+        std::memcpy(&wb[i * 20 + 2], &mn, 2);
+        for (int j = 0; j < 16; ++j) wb[i * 20 + 4 + j] = static_cast<uint8_t>(rng() & 0xFF);
+    }
+    std::vector<uint16_t> x(m * k);
+    for (auto& v : x) v = oracle_f32_to_f16(na(rng));
+    const size_t osz = out_f16 ? 2 : 4;
+    std::vector<uint8_t> want(m * n * osz);
+    oracle_q4_1_matmul(x.data(), 1, k, wb.data(), nblk, want.data(), out_f16, n, m, n, k, 1, nullptr);
+
+    DevBuf dx(x.data(), x.size() * 2), dw(wb.data(), wb.size()), dout(want.size());
+    const int64_t xs[] = {m, k}, ws[] = {n, k}, os[] = {m, n};
+    const DataType odt = out_f16 ? DataType::f16 : DataType::f32;
+    LinearAttributes attrs;
+    attrs.output_dtype = odt;
+    auto op = Linear::create(attrs, Backend::CUDA);
+    TensorView out = view(os, odt, dout.p);
+    const TensorView ins[] = {view(xs, DataType::f16, dx.p), view(ws, DataType::q4_1, dw.p)};
+    EXPECT(ins[1].row_stride_elems() == nblk);  // q4_1 strides count 20-byte blocks
+    ComputeContext ctx;
+    ctx.expected_backend = Backend::CUDA;
+    EXPECT(op->compute(out, ins, ctx) == Status::ok);
+    const auto got = dout.download<uint8_t>();
+    // rtol 1e-2 (f16 out) / 2e-3 (f32 out) with an absolute floor of rtol * rms(reference).
+    const float rtol = out_f16 ? 1e-2f : 2e-3f;
+    double sq = 0;
+    std::vector<float> gv(m * n), wv(m * n);
+    for (int64_t i = 0; i < m * n; ++i) {
+        if (out_f16) {
+            uint16_t a16, b16;
+            std::memcpy(&a16, &got[i * 2], 2);
+            std::memcpy(&b16, &want[i * 2], 2);
+            gv[i] = oracle_f16_to_f32(a16);
+            wv[i] = oracle_f16_to_f32(b16);
+        } else {
+            std::memcpy(&gv[i], &got[i * 4], 4);
+            std::memcpy(&wv[i], &want[i * 4], 4);
+        }
+        sq += double(wv[i]) * wv[i];
+    }
+    const float rms = static_cast<float>(std::sqrt(sq / double(m * n)));
+    int64_t bad = 0;
+    for (int64_t i = 0; i < m * n; ++i) {
+        if (std::fabs(gv[i] - wv[i]) > rtol * std::fabs(wv[i]) + rtol * rms) ++bad;
+    }
+    EXPECT(bad == 0);
+}
+
+// ---- contract cases (reference tests/test_status.cpp, README "errors write nothing") --------
+
+static void contract_cases()
+{
+    g_case = "status_contract";
+    const int64_t xs[] = {4, 64}, ws[] = {8, 64}, ws_bad[] = {8, 48}, os[] = {4, 8};
+    DevBuf x(4 * 64), w(8 * 64), out(4 * 8 * 4, 0x6B);
+    LinearAttributes attrs;
+    attrs.output_dtype = DataType::s32;
+    auto op = Linear::create(attrs, Backend::CUDA);
+    EXPECT(op != nullptr && op->getBackend() == Backend::CUDA);
+    TensorView o = view(os, DataType::s32, out.p);
+
+    {   // K mismatch: invalid_argument, output untouched
+        const TensorView ins[] = {view(xs, DataType::s8, x.p), view(ws_bad, DataType::s8, w.p)};
+        EXPECT(op->compute(o, ins) == Status::invalid_argument);
+    }
+    {   // wrong input count
+        const TensorView ins[] = {view(xs, DataType::s8, x.p)};
+        EXPECT(op->compute(o, std::span<const TensorView>(ins, 1)) == Status::invalid_argument);
+    }
+    {   // gated form has no CUDA route
+        LinearAttributes g = attrs;
+        g.gated = true;
+        auto gop = Linear::create(g, Backend::CUDA);
+        const TensorView ins[] = {view(xs, DataType::s8, x.p), view(ws, DataType::s8, w.p)};
+        EXPECT(gop->compute(o, ins) != Status::ok);
+    }
+    {   // rank above six
+        const int64_t x7[] = {1, 1, 1, 1, 1, 4, 64};
+        const TensorView ins[] = {view(x7, DataType::s8, x.p), view(ws, DataType::s8, w.p)};
+        const int64_t o7[] = {1, 1, 1, 1, 1, 4, 8};
+        TensorView o7v = view(o7, DataType::s32, out.p);
+        EXPECT(op->compute(o7v, ins) == Status::unsupported);
+    }
+    {   // dense fp Linear is not this backend's path
+        const TensorView ins[] = {view(xs, DataType::f32, x.p), view(ws, DataType::f32, w.p)};
+        DevBuf big(4 * 64 * 4);
+        (void)big;
+        EXPECT(op->compute(o, ins) == Status::unsupported);
+    }
+    const auto after = out.download<uint8_t>();
+    bool untouched = true;
+    for (uint8_t b : after) untouched = untouched && b == 0x6B;
+    EXPECT(untouched);  // every rejected call wrote nothing
+    {   // empty output: ok, nothing to do
+        const int64_t x0[] = {0, 64}, o0[] = {0, 8};
+        const TensorView ins[] = {view(x0, DataType::s8, x.p), view(ws, DataType::s8, w.p)};
+        TensorView o0v = view(o0, DataType::s32, out.p);
+        EXPECT(op->compute(o0v, ins) == Status::ok);
+    }
+    {   // the two-step prepack query answers "no packed form" on CUDA
+        TensorView packed;
+        const TensorView ins[] = {view(ws, DataType::s8, w.p)};
+        TensorView outs[] = {packed};
+        op->prepackWeights(ins, outs);
+        EXPECT(outs[0].is_empty());
+    }
+    EXPECT(op->getWorkspaceSize({}, {}) == 0);
+}
+
+int main()
+{
+    int dev_count = 0;
+    if (cudaGetDeviceCount(&dev_count) != cudaSuccess || dev_count == 0) {
+        std::printf("SKIP: no CUDA device\n");
+        return 77;
+    }
+    cudaStream_t stream;
+    CUDA_OK(cudaStreamCreate(&stream));
+
+    kat_basic_s32();
+    kat_zero_points();
+    kat_u8_zero_points();
+    kat_requant();
+
+    const DataType kinds[] = {DataType::s32, DataType::s8, DataType::u8, DataType::f32, DataType::f16};
+    for (DataType dt : kinds) {
+        const std::string n1 = "linear_i8_per_channel_" + std::to_string(int(dt));
+        linear_i8_case({1, 200, 330, 512, dt, true, true, true, false, false, 0, 0, 0}, n1.c_str(), nullptr);
+        const std::string n2 = "linear_i8_zero_points_" + std::to_string(int(dt));
+        linear_i8_case({1, 77, 130, 272, dt, false, true, true, true, false, 0, 0, 0}, n2.c_str(), stream);
+    }
+    linear_i8_case({1, 150, 200, 260, DataType::s8, true, false, true, false, false, 28, 12, 24}, "linear_i8_pitched", stream);
+    linear_i8_case({1, 130, 140, 100, DataType::s32, false, false, false, true, false, 0, 0, 0}, "linear_i8_unaligned_k", nullptr);
+    linear_i8_case({3, 64, 96, 128, DataType::s8, true, true, true, true, false, 0, 0, 0}, "linear_i8_batched", stream);
+    linear_i8_case({1, 8, 520, 1024, DataType::s8, true, false, true, false, false, 0, 0, 0}, "linear_i8_decode_m8", nullptr);
+    linear_i8_case({1, 256, 384, 512, DataType::s8, true, true, true, true, true, 0, 0, 0}, "linear_i8_device_arrays", stream);
+    linear_i8_case({1, 512, 1024, 1024, DataType::s8, true, false, true, false, false, 0, 0, 0}, "linear_i8_512x1024x1024", nullptr);
+
+    linear_q4_1_case(4, 260, 1024, false, "linear_q4_1_gemv_f32");
+    linear_q4_1_case(1, 512, 4096, true, "linear_q4_1_gemv_f16");
+    linear_q4_1_case(160, 384, 512, true, "linear_q4_1_gemm_f16");
+    linear_q4_1_case(130, 300, 1000, false, "linear_q4_1_gemm_f32_ragged");
+
+    contract_cases();
+
+    CUDA_OK(cudaDeviceSynchronize());
+    CUDA_OK(cudaStreamDestroy(stream));
+    std::printf("%s: %d checks, %d failed\n", g_failed == 0 ? "PASS" : "FAIL", g_checks, g_failed);
+    return g_failed == 0 ? 0 : 1;
+}
