@@ -71,7 +71,7 @@ class ShardedLinearI8:
             self._gathered = None
         elif self._slab is None or self._slab.shape[0] != m:
             self._slab = torch.empty((m, self.n_per), dtype=dt, device=a.device)
-            self._gathered = torch.empty((self.world, m, self.n_per), dtype=dt, device=a.device)
+            self._gathered = torch.empty((self.world * m, self.n_per), dtype=dt, device=a.device)  # [g][M][N/g]
         self._keep = []
         self._args = ops.gemm_i8_args(a, self.w, self._slab, out_kind=self.out_kind, keep=self._keep, **self.kw)
         self._key = (a.data_ptr(), m, out.data_ptr() if (out is not None and self.world == 1) else 0)

@@ -1,0 +1,72 @@
+"""Column-sharded int8 Linear on real GPUs: g ranks over NCCL must reproduce the single-GPU
+output byte for byte (and that one equals the oracle).  Needs at least two GPUs; skipped
+otherwise."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank: int, world: int, port: int, m: int, n: int, k: int, q):
+    import torch.distributed as dist
+    from nnops_b200 import capi, synth
+    from nnops_b200.sharded import ShardedLinearI8, shard_rows
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        c = synth.config2(m=m, n=n, k=k, out_scale=1.6)
+        layer = ShardedLinearI8(
+            torch.from_numpy(np.ascontiguousarray(shard_rows(c.w, world, rank))).to(dev), n_total=n, world=world,
+            rank=rank, out_kind="s8", relu=True, scale_a=c.scale_a, out_scale=c.out_scale,
+            bias_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.bias, world, rank))).to(dev),
+            scale_w_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.scale_w, world, rank))).to(dev))
+        a = torch.from_numpy(c.a).to(dev)
+        out = torch.full((m, n + 32), 0x5A, dtype=torch.int8, device=dev)   # pitched destination
+        for _ in range(2):                                                   # twice: buffers are reused
+            layer.forward(a, out[:, :n])
+        torch.cuda.synchronize()
+        assert capi.take_device_error() == 0
+        q.put((rank, out.cpu().numpy()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_matches_single_gpu(nnb200_lib, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    import oracle
+    from nnops_b200 import ops, synth
+    m, n, k = 512, 2048, 1024
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, m, n, k, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    c = synth.config2(m=m, n=n, k=k, out_scale=1.6)
+    dev = torch.device("cuda:0")
+    single = ops.gemm_i8(torch.from_numpy(c.a).to(dev), torch.from_numpy(c.w).to(dev), **c.kwargs()).cpu().numpy()
+    assert np.array_equal(single, oracle.gemm_i8(c.a, c.w, **c.kwargs()))
+    for r in range(world):
+        assert np.array_equal(results[r][:, :n], single), f"rank {r} differs from the single-GPU result"
+        assert np.all(results[r][:, n:] == 0x5A), "padding of the pitched output was touched"
