@@ -56,47 +56,50 @@ class ShardedLinearI8:
         self.out_kind = out_kind
         self.kw = dict(bias=bias_shard, scale_w=scale_w_shard, scale_a=scale_a, out_scale=out_scale, out_zp=out_zp,
                        relu=relu)
-        self._keep: list = []
-        self._args = None
-        self._slab = None
-        self._gathered = None
-        self._key = None
+        self._plans: dict = {}   # (a ptr, M, out ptr) -> prepared argument block + buffers
+        self._last = None
 
-    def _prepare(self, a: torch.Tensor, out: torch.Tensor | None):
+    def _plan(self, a: torch.Tensor, out: torch.Tensor | None) -> dict:
+        """Argument block and buffers for this (activations, destination) pair, built once."""
         m = a.shape[0]
-        dt = ops._OUT_TORCH[self.out_kind]
-        if self.world == 1:
-            # Single GPU: the GEMM writes the caller's output directly.
-            self._slab = out if out is not None else torch.empty((m, self.n_per), dtype=dt, device=a.device)
-            self._gathered = None
-        elif self._slab is None or self._slab.shape[0] != m:
-            self._slab = torch.empty((m, self.n_per), dtype=dt, device=a.device)
-            self._gathered = torch.empty((self.world * m, self.n_per), dtype=dt, device=a.device)  # [g][M][N/g]
-        self._keep = []
-        self._args = ops.gemm_i8_args(a, self.w, self._slab, out_kind=self.out_kind, keep=self._keep, **self.kw)
-        self._key = (a.data_ptr(), m, out.data_ptr() if (out is not None and self.world == 1) else 0)
+        key = (a.data_ptr(), m, out.data_ptr() if (out is not None and self.world == 1) else 0)
+        plan = self._plans.get(key)
+        if plan is None:
+            dt = ops._OUT_TORCH[self.out_kind]
+            if self.world == 1:
+                # Single GPU: the GEMM writes the caller's output directly.
+                slab = out if out is not None else torch.empty((m, self.n_per), dtype=dt, device=a.device)
+                gathered = None
+            else:
+                slab = torch.empty((m, self.n_per), dtype=dt, device=a.device)
+                gathered = torch.empty((self.world * m, self.n_per), dtype=dt, device=a.device)  # [g][M][N/g]
+            keep: list = []
+            args = ops.gemm_i8_args(a, self.w, slab, out_kind=self.out_kind, keep=keep, **self.kw)
+            plan = dict(args=args, keep=keep, slab=slab, gathered=gathered)
+            self._plans[key] = plan
+        return plan
 
     def local(self, a: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """This rank's [M, N/g] slab: the GEMM alone (written straight into ``out`` at g = 1)."""
-        key = (a.data_ptr(), a.shape[0], out.data_ptr() if (out is not None and self.world == 1) else 0)
-        if self._args is None or self._key != key:
-            self._prepare(a, out)
-        capi.check(capi.lib().nnb200_gemm_i8(C.byref(self._args), torch.cuda.current_stream(a.device).cuda_stream),
+        plan = self._plan(a, out)
+        capi.check(capi.lib().nnb200_gemm_i8(C.byref(plan["args"]), torch.cuda.current_stream(a.device).cuda_stream),
                    "nnb200_gemm_i8")
-        return self._slab
+        self._last = plan
+        return plan["slab"]
 
     def reassemble(self, out: torch.Tensor | None = None) -> torch.Tensor:
         """All-gather the slabs of the last ``local`` call and interleave them into [M, N]."""
-        slab = self._slab
+        plan = self._last
+        slab = plan["slab"]
         if self.world == 1:
             return slab
         m = slab.shape[0]
         if out is None:
             out = torch.empty((m, self.n_total), dtype=slab.dtype, device=slab.device)
-        dist.all_gather_into_tensor(self._gathered, slab, group=self.group)
+        dist.all_gather_into_tensor(plan["gathered"], slab, group=self.group)
         esize = slab.element_size()
         capi.check(capi.lib().nnb200_interleave_shards(
-            self._gathered.data_ptr(), out.data_ptr(), m, self.n_per * esize, self.world, out.stride(0) * esize,
+            plan["gathered"].data_ptr(), out.data_ptr(), m, self.n_per * esize, self.world, out.stride(0) * esize,
             torch.cuda.current_stream(slab.device).cuda_stream), "nnb200_interleave_shards")
         return out
 
