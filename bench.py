@@ -197,6 +197,34 @@ def secondary_q4_1(torch, dev, peaks):
     return out
 
 
+def run_kernel_only(args):
+    """Three launches of one kernel on seeded inputs and nothing else: the command the ncu
+    captures under profiles/ are taken from (`--kernel-only i8|gemv|q4gemm --shape M N K`)."""
+    import torch
+    from nnops_b200 import build, ops, synth
+    build.build()
+    m, n, k = args.shape
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(0)
+    if args.kernel_only == "i8":
+        a = torch.from_numpy(synth.s8_uniform(rng, (m, k))).to(dev)
+        w = torch.from_numpy(synth.s8_uniform(rng, (n, k))).to(dev)
+        sw = torch.from_numpy(rng.uniform(0.001, 0.02, n).astype(np.float32)).to(dev)
+        bias = torch.from_numpy(rng.integers(-1000, 1001, n).astype(np.int32)).to(dev)
+        out = torch.empty((m, n), dtype=torch.int8, device=dev)
+        for _ in range(3):
+            ops.gemm_i8(a, w, out_kind="s8", out=out, bias=bias, relu=True, scale_a=0.02, scale_w=sw, out_scale=0.05)
+    else:
+        wb = torch.from_numpy(synth.q4_1_weights(rng, n, k)).to(dev)
+        a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float16)).to(dev)
+        gemv = args.kernel_only == "gemv"
+        out = torch.empty((m, n), dtype=torch.float32 if gemv else torch.float16, device=dev)
+        for _ in range(3):
+            ops.linear_q4_1(a, wb, k, out=out, engine="gemv" if gemv else "gemm")
+    torch.cuda.synchronize()
+    print(json.dumps({"kernel_only": args.kernel_only, "shape": [m, n, k], "launches": 3}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -204,7 +232,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the Q4_1 and CPU-baseline side measurements")
+    ap.add_argument("--kernel-only", choices=["i8", "gemv", "q4gemm"], help="profiling aid: 3 launches of one kernel")
+    ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=[4096, 28672, 8192])
     args = ap.parse_args()
+    if args.kernel_only:
+        run_kernel_only(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
         return
