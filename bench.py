@@ -232,6 +232,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the Q4_1 and CPU-baseline side measurements")
+    ap.add_argument("--reassembly", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: peer-store epilogue (fused) or NCCL all-gather + interleave kernel")
     ap.add_argument("--kernel-only", choices=["i8", "gemv", "q4gemm"], help="profiling aid: 3 launches of one kernel")
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=[4096, 28672, 8192])
     args = ap.parse_args()
@@ -270,8 +272,10 @@ def main():
     layer = ShardedLinearI8(w, n_total=N, world=world, rank=rank, out_kind="s8",
                             bias_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.bias, world, rank))).to(dev),
                             scale_w_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.scale_w, world, rank))).to(dev),
-                            scale_a=c.scale_a, out_scale=c.out_scale, relu=True)
-    out = torch.empty((M, N), dtype=torch.int8, device=dev)
+                            scale_a=c.scale_a, out_scale=c.out_scale, relu=True,
+                            mode=args.reassembly if world > 1 else "nccl")
+    outs = layer.alloc_outputs(M, count=2)   # fused mode: mapped on every rank through CUDA IPC
+    out = outs[0]
     out_host = torch.empty((M, N), dtype=torch.int8).pin_memory()
 
     def barrier():
@@ -324,7 +328,7 @@ def main():
     d2h = M * N
     s_in, s_run, s_back = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     a_dev = [a, torch.empty_like(a)]
-    out_dev = [out, torch.empty_like(out)]
+    out_dev = outs
     out_hosts = [out_host, torch.empty((M, N), dtype=torch.int8).pin_memory()]
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_run = [torch.cuda.Event() for _ in range(2)]
@@ -339,7 +343,8 @@ def main():
         with torch.cuda.stream(s_run):
             s_run.wait_event(ev_in[b])
             s_run.wait_event(ev_back[b])        # the read-back that last used this output buffer
-            layer.forward(a_dev[b], out_dev[b])
+            # Another rank's previous read-back of this buffer may still be running: order the ranks first.
+            layer.forward(a_dev[b], out_dev[b], wait_for_readers=True)
             ev_run[b].record()
         with torch.cuda.stream(s_back):
             s_back.wait_event(ev_run[b])
@@ -393,7 +398,10 @@ def main():
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "s8", "data": "synthetic",
             "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "shards": world,
-                       "reassembly": "none" if world == 1 else "nccl all-gather + interleave kernel",
+                       "reassembly": "none" if world == 1 else (
+                           "fused: GEMM epilogue stores each tile into every rank's output over NVLink (P2P), "
+                           "then a 1-element all-reduce orders the ranks" if layer.mode == "fused"
+                           else "nccl all-gather + interleave kernel"),
                        "l2": "inputs (268 MB) exceed L2 (126 MB); no flush needed"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,

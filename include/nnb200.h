@@ -112,6 +112,15 @@ typedef struct nnb200_gemm_i8_args {
     void* workspace;
     size_t workspace_bytes;
     int32_t force_engine; /* NNB200_ENGINE_*; AUTO picks */
+    /* Column-sharded layers: besides `out`, write the same [m, n] window (same ldc) into up to
+     * seven more buffers -- the other GPUs' copies of the full output, mapped into this process
+     * (CUDA IPC / peer access).  The GEMM's write-back then IS the all-gather.  S8/U8
+     * destinations on the tensor-core engine only, batch 1, every pointer and ldc a multiple of
+     * 16, n a multiple of 16; otherwise NNB200_UNSUPPORTED.  The caller orders the ranks (all
+     * ranks' kernels must finish before any rank reads its buffer).  The reference has no
+     * multi-GPU path; this has no counterpart there. */
+    int32_t num_peer_outs;
+    void* peer_out[7];
 } nnb200_gemm_i8_args;
 
 /* Scratch the call needs (0 for the common zero-point-free tensor-core call). */
@@ -218,6 +227,26 @@ NNB200_API int nnb200_copy_h2d_async(void* dst_device, const void* src_host, siz
  * gemm_workspace_alloc / gemm_workspace_free, src/backend/cuda/matmul/gemm_common.cuh:296-354). */
 NNB200_API int nnb200_scratch_alloc_async(void** out, size_t bytes, void* stream);
 NNB200_API int nnb200_scratch_free_async(void* p, void* stream);
+
+/*
+ * Output buffers that other processes' GPUs can store into (the peer_out pointers of
+ * nnb200_gemm_i8_args).  alloc: plain device memory on the current device (this is the one
+ * place the library allocates on request; free it with nnb200_peer_buffer_free).  export: a
+ * 64-byte CUDA IPC handle to send to the other ranks.  open: map another rank's buffer for the
+ * CURRENT device -- call it with the device that will run the kernels current; returns
+ * NNB200_UNSUPPORTED when the two GPUs have no peer path.  close: unmap.  No counterpart in the
+ * reference.
+ */
+NNB200_API int nnb200_peer_buffer_alloc(void** ptr, size_t bytes);
+NNB200_API int nnb200_peer_buffer_free(void* ptr);
+NNB200_API int nnb200_peer_buffer_export(const void* ptr, uint8_t handle[64]);
+NNB200_API int nnb200_peer_buffer_open(const uint8_t handle[64], void** ptr);
+NNB200_API int nnb200_peer_buffer_close(void* ptr);
+
+/* Let kernels of the current device store into memory of `peer_device` (needed once per pair
+ * before nnb200_gemm_i8 is given peer_out pointers).  NNB200_UNSUPPORTED if the two GPUs have
+ * no peer path. */
+NNB200_API int nnb200_enable_peer_access(int32_t peer_device);
 
 /* 1 if p is device (or managed) memory usable by kernels of the current device, else 0. */
 NNB200_API int nnb200_is_device_pointer(const void* p);

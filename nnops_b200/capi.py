@@ -42,6 +42,7 @@ class GemmI8Args(C.Structure):
         ("out_scale", C.c_float), ("out_zp", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("force_engine", C.c_int32),
+        ("num_peer_outs", C.c_int32), ("peer_out", C.c_void_p * 7),
     ]
 
 
@@ -80,6 +81,12 @@ SYMBOLS = [
     ("nnb200_copy_h2d_async", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("nnb200_scratch_alloc_async", C.c_int, [C.POINTER(C.c_void_p), C.c_size_t, C.c_void_p]),
     ("nnb200_scratch_free_async", C.c_int, [C.c_void_p, C.c_void_p]),
+    ("nnb200_peer_buffer_alloc", C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
+    ("nnb200_peer_buffer_free", C.c_int, [C.c_void_p]),
+    ("nnb200_peer_buffer_export", C.c_int, [C.c_void_p, C.c_char_p]),
+    ("nnb200_peer_buffer_open", C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    ("nnb200_peer_buffer_close", C.c_int, [C.c_void_p]),
+    ("nnb200_enable_peer_access", C.c_int, [C.c_int32]),
     ("nnb200_is_device_pointer", C.c_int, [C.c_void_p]),
     ("nnb200_launch_count", C.c_uint64, []),
     ("nnb200_version", C.c_char_p, []),

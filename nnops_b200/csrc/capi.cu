@@ -155,7 +155,7 @@ int pick_i8_engine(const nnb200_gemm_i8_args* a, const I8Problem& p)
     if (a->force_engine == NNB200_ENGINE_UMMA) {
         return umma_i8_supported(p) ? NNB200_ENGINE_UMMA : NNB200_ENGINE_GENERIC;
     }
-    if (narrow_i8_supported(p)) {
+    if (a->num_peer_outs == 0 && narrow_i8_supported(p)) {
         return NNB200_ENGINE_NARROW;
     }
     if (umma_i8_supported(p)) {
@@ -222,6 +222,21 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
     const size_t ra_bytes = (static_cast<size_t>(a->m) * 4 + 255) & ~size_t(255);
     const size_t rw_bytes = (static_cast<size_t>(a->n) * 4 + 255) & ~size_t(255);
 
+    if (a->num_peer_outs != 0) {
+        // Sharded write-back: validated here so that a refused call has launched nothing.
+        const auto mis16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; };
+        bool ok = a->num_peer_outs > 0 && a->num_peer_outs <= 7 && a->batch == 1 &&
+                  (a->out_kind == NNB200_OUT_S8 || a->out_kind == NNB200_OUT_U8) && (a->ldc % 16) == 0 &&
+                  (a->n % 16) == 0 && !mis16(a->out) &&
+                  pick_i8_engine(a, problem_of(a, 0)) == NNB200_ENGINE_UMMA;
+        for (int i = 0; ok && i < a->num_peer_outs; ++i) {
+            ok = a->peer_out[i] != nullptr && !mis16(a->peer_out[i]);
+        }
+        if (!ok) {
+            return NNB200_UNSUPPORTED;
+        }
+    }
+
     for (int64_t b = 0; b < a->batch; ++b) {
         const I8Problem p = problem_of(a, b);
         I8Epilogue ep;
@@ -249,6 +264,10 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
         ep.k = static_cast<int32_t>(a->k);
         ep.out_scale = a->out_scale;
         ep.out_zp = a->out_zp;
+        ep.num_peers = a->num_peer_outs;
+        for (int i = 0; i < a->num_peer_outs; ++i) {
+            ep.peer_out[i] = a->peer_out[i];
+        }
         if (comp) {
             uint8_t* ws = static_cast<uint8_t*>(a->workspace) + static_cast<size_t>(b) * (ra_bytes + rw_bytes);
             int32_t* r_a = reinterpret_cast<int32_t*>(ws);
@@ -423,6 +442,87 @@ int nnb200_scratch_free_async(void* p, void* stream)
         return NNB200_OK;
     }
     return cuda_status(cudaFreeAsync(p, static_cast<cudaStream_t>(stream)));
+}
+
+int nnb200_peer_buffer_alloc(void** ptr, size_t bytes)
+{
+    if (ptr == nullptr || bytes == 0) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    *ptr = nullptr;
+    const cudaError_t e = cudaMalloc(ptr, bytes);
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        return NNB200_OUT_OF_MEMORY;
+    }
+    return cuda_status(e);
+}
+
+int nnb200_peer_buffer_free(void* ptr)
+{
+    return ptr == nullptr ? NNB200_OK : cuda_status(cudaFree(ptr));
+}
+
+int nnb200_peer_buffer_export(const void* ptr, uint8_t handle[64])
+{
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (ptr == nullptr || handle == nullptr) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(ptr));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return NNB200_INTERNAL;
+    }
+    std::memcpy(handle, &h, sizeof(h));
+    return NNB200_OK;
+}
+
+int nnb200_peer_buffer_open(const uint8_t handle[64], void** ptr)
+{
+    if (ptr == nullptr || handle == nullptr) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    *ptr = nullptr;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    // Opened with the ACCESSING device current: the driver maps the exporter's memory for this
+    // device and enables the peer path between the two GPUs.
+    const cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        *ptr = nullptr;
+        return e == cudaErrorPeerAccessUnsupported ? NNB200_UNSUPPORTED : NNB200_INTERNAL;
+    }
+    return NNB200_OK;
+}
+
+int nnb200_peer_buffer_close(void* ptr)
+{
+    return ptr == nullptr ? NNB200_OK : cuda_status(cudaIpcCloseMemHandle(ptr));
+}
+
+int nnb200_enable_peer_access(int32_t peer_device)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        return NNB200_INTERNAL;
+    }
+    if (peer_device == dev) {
+        return NNB200_OK;
+    }
+    int can = 0;
+    if (cudaDeviceCanAccessPeer(&can, dev, peer_device) != cudaSuccess || can == 0) {
+        cudaGetLastError();
+        return NNB200_UNSUPPORTED;
+    }
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();
+        return NNB200_OK;
+    }
+    return cuda_status(e);
 }
 
 int nnb200_is_device_pointer(const void* p)

@@ -36,6 +36,11 @@ struct I8Epilogue {
     int32_t k;
     float out_scale;
     int32_t out_zp;
+    // Column-sharded output written straight into every rank's full matrix: `out` is this
+    // rank's own copy, `peer_out[i]` the same window (same pitch) inside the other ranks'
+    // buffers, mapped into this process for peer-to-peer stores.  8-bit destinations only.
+    int32_t num_peers;
+    void* peer_out[7];
 };
 
 __device__ __forceinline__ float act_apply(int32_t act, float alpha, float beta, float x)

@@ -13,6 +13,12 @@
 //     (zero-point compensation, int32 bias, Relu, requantisation / dequantisation) in
 //     registers, so the epilogue of tile i overlaps the main loop of tile i+1.
 //
+// Sharded form (template flag PEERS): the epilogue of an 8-bit destination stages 32 rows x 128
+// columns per warp in shared memory and writes every 4 x 128-byte row group to this GPU's
+// output AND to the same window of each peer GPU's output with plain 16-byte stores (peer
+// pointers over NVLink) -- the all-gather is fused into the GEMM's write-back, tile by tile,
+// in contiguous 128-byte segments.  Loads never touch peer memory.
+//
 // Both operands are already K-major in memory ([M,K] and [N,K]), which is the layout the
 // UMMA shared-memory descriptors want, so no transposes or repacking happen anywhere.
 // Every barrier wait is bounded; a wait that runs out records an error code and the CTA
@@ -46,7 +52,9 @@ struct TileConfig {
     static constexpr int kTmemCols = 2 * BN;  // two accumulators; 128..512, a power of two
     static constexpr int kColParamBytes = 4 * 4 * BN * 4;  // 4 epilogue warps x {scale, bias, r_w, zp_w} x BN x 4 B
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kPeerStageBytes = 4 * 32 * 128;  // sharded form: 32 rows x 128 B per epilogue warp
     static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kColParamBytes + kBarrierBytes;
+    static constexpr int kSmemBytesPeers = kSmemBytes + kPeerStageBytes;
 };
 
 struct TileCoord {
@@ -188,7 +196,7 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
     }
 }
 
-template <int BN, int KIND>
+template <int BN, int KIND, bool PEERS>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const I8Epilogue ep, const int m_total, const int n_total, const int k_total,
@@ -209,6 +217,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* acc_empty_bar = acc_full_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint8_t* peer_stage = reinterpret_cast<uint8_t*>(tmem_slot + 4);  // 16-byte aligned; used when PEERS
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -392,17 +401,77 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(acc * BN);
+            if constexpr (PEERS && (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8)) {
+                // Sharded write-back: 128 columns at a time through a per-warp staging tile.
+                const float zpf = static_cast<float>(ep.out_zp);
+                const float lo = (KIND == NNB200_OUT_S8 ? -128.0f : 0.0f) - zpf;
+                const float hi = (KIND == NNB200_OUT_S8 ? 127.0f : 255.0f) - zpf;
+                uint8_t* stage = peer_stage + (warp - 2) * (32 * 128);
+                const int64_t row0 = static_cast<int64_t>(tc.m_blk) * kBlockM + quarter * 32;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                const int n0 = n_base + c * 32;
-                if (n0 >= n_total) {
-                    break;  // uniform across the CTA's epilogue warps
+                for (int c4 = 0; c4 < BN / 128; ++c4) {
+                    const int n128 = n_base + c4 * 128;
+                    if (n128 >= n_total) {
+                        break;  // uniform across the warp
+                    }
+#pragma unroll 1
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int c = c4 * 4 + cc;
+                        uint32_t v[32];
+                        tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
+                        tmem_ld_wait();
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            uint32_t word = 0;
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                const int col = c * 32 + j + b;
+                                const int32_t val = i8_int_value(ep, rt, static_cast<int32_t>(v[j + b]), cz[col], cr[col],
+                                                                 cb[col]);
+                                const int32_t q = i8_requant(val, __fmul_rn(rt.row_k, cs[col]), lo, hi, ep.out_zp);
+                                word |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * b);
+                            }
+                            packed[j / 4] = word;
+                        }
+                        // This lane's row: 16-byte pieces 2cc and 2cc+1, XOR-swizzled by the row.
+                        uint4* srow = reinterpret_cast<uint4*>(stage + lane * 128);
+                        srow[(2 * cc) ^ (lane & 7)] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        srow[(2 * cc + 1) ^ (lane & 7)] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    }
+                    __syncwarp();
+                    // Lane -> piece (lane % 8) of rows (lane / 8) + 4j: each store instruction
+                    // covers four rows of 128 contiguous bytes.
+                    const int piece = lane & 7;
+                    const int col = n128 + piece * 16;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int r = (lane >> 3) + 4 * j;
+                        const uint4 data = *reinterpret_cast<const uint4*>(stage + r * 128 + ((piece ^ (r & 7)) << 4));
+                        const int64_t grow = row0 + r;
+                        if (grow < m_total && col < n_total) {
+                            const int64_t off = grow * ep.ldc + col;
+                            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(ep.out) + off) = data;
+                            for (int pi = 0; pi < ep.num_peers; ++pi) {
+                                *reinterpret_cast<uint4*>(static_cast<uint8_t*>(ep.peer_out[pi]) + off) = data;
+                            }
+                        }
+                    }
+                    __syncwarp();  // staging tile free for the next 128 columns
                 }
-                uint32_t v[32];
-                tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
-                tmem_ld_wait();
-                epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
-                                     cz + c * 32, vec_ok != 0);
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int n0 = n_base + c * 32;
+                    if (n0 >= n_total) {
+                        break;  // uniform across the CTA's epilogue warps
+                    }
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
+                    tmem_ld_wait();
+                    epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
+                                         cz + c * 32, vec_ok != 0);
+                }
             }
             // Accumulator drained: hand it back to the MMA warp.
             tc_fence_before_sync();
@@ -422,25 +491,24 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-template <int BN, int KIND>
+template <int BN, int KIND, bool PEERS>
 int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m, int n, int k,
                    uint32_t idesc, int vec_ok, const DeviceInfo& dev, cudaStream_t stream)
 {
     using Cfg = TileConfig<BN>;
-    auto kernel = gemm_i8_umma_kernel<BN, KIND>;
+    auto kernel = gemm_i8_umma_kernel<BN, KIND, PEERS>;
+    constexpr int kSmem = PEERS ? Cfg::kSmemBytesPeers : Cfg::kSmemBytes;
     static std::once_flag once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
     std::call_once(once[dev.device], [&] {
-        attr_err[dev.device] =
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        attr_err[dev.device] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     });
     if (attr_err[dev.device] != cudaSuccess) {
         return NNB200_INTERNAL;
     }
     const int num_tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BN - 1) / BN);
     const int grid = num_tiles < dev.sm_count ? num_tiles : dev.sm_count;
-    kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, ep, m, n, k, idesc, vec_ok,
-                                                           dev.error_word);
+    kernel<<<grid, kNumThreads, kSmem, stream>>>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev.error_word);
     note_launch();
     return cuda_status(cudaGetLastError());
 }
@@ -449,12 +517,24 @@ template <int BN>
 int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m, int n, int k,
               uint32_t idesc, int vec_ok, const DeviceInfo& dev, cudaStream_t stream)
 {
+    if (ep.num_peers > 0) {
+        // Sharded write-back exists for the 8-bit destinations and 128-column groups.
+        if constexpr (BN >= 128) {
+            if (kind == NNB200_OUT_S8) {
+                return launch_variant<BN, NNB200_OUT_S8, true>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+            }
+            if (kind == NNB200_OUT_U8) {
+                return launch_variant<BN, NNB200_OUT_U8, true>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+            }
+        }
+        return NNB200_UNSUPPORTED;
+    }
     switch (kind) {
-    case NNB200_OUT_S32: return launch_variant<BN, NNB200_OUT_S32>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
-    case NNB200_OUT_S8: return launch_variant<BN, NNB200_OUT_S8>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
-    case NNB200_OUT_U8: return launch_variant<BN, NNB200_OUT_U8>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
-    case NNB200_OUT_F32: return launch_variant<BN, NNB200_OUT_F32>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
-    case NNB200_OUT_F16: return launch_variant<BN, NNB200_OUT_F16>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_S32: return launch_variant<BN, NNB200_OUT_S32, false>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_S8: return launch_variant<BN, NNB200_OUT_S8, false>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_U8: return launch_variant<BN, NNB200_OUT_U8, false>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_F32: return launch_variant<BN, NNB200_OUT_F32, false>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_F16: return launch_variant<BN, NNB200_OUT_F16, false>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
     default: return NNB200_UNSUPPORTED;
     }
 }
@@ -487,7 +567,7 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
     int bn = 256;
     if (static_cast<int64_t>(num_m) * ((n + 255) / 256) < dev.sm_count) {
         bn = 128;
-        if (static_cast<int64_t>(num_m) * ((n + 127) / 128) < dev.sm_count) {
+        if (static_cast<int64_t>(num_m) * ((n + 127) / 128) < dev.sm_count && ep.num_peers == 0) {
             bn = 64;
         }
     }

@@ -5,11 +5,16 @@ because W is row-major), and the matching slices of the per-channel scales and t
 Activations are replicated.  Each output element is produced by exactly one GPU from the same
 integer inputs, so the g-way result is byte-identical to the single-GPU one.
 
-Two ways to reassemble the [M,N] output on every rank:
+Two ways to put the full row-major [M,N] output on every rank:
 
-* ``mode="nccl"``   -- local GEMM into a dense [M, N/g] slab, NCCL all-gather over
-  NVLink/NVSwitch into [g][M][N/g], then the library's interleave kernel writes row-major [M,N].
-* ``mode="fused"``  -- see ``PeerOutput`` (added by later steps of the build).
+* ``mode="nccl"``  -- local GEMM into a dense [M, N/g] slab, NCCL all-gather over
+  NVLink/NVSwitch into [g][M][N/g], then the library's interleave kernel writes [M,N].
+* ``mode="fused"`` -- the outputs are allocated with ``alloc_outputs`` (every rank maps every
+  other rank's copy through CUDA IPC); the GEMM's epilogue then stores each finished tile into
+  all g copies at once with peer-to-peer stores, so the all-gather overlaps the math tile by
+  tile and no separate collective or re-layout pass runs.  Ranks are ordered by a one-element
+  NCCL all-reduce after the GEMM (and optionally before it, when a consumer of the previous
+  result may still be reading).  Kernels only ever LOAD local memory.
 
 The reference has no multi-GPU code; this layer sits above its operator API, one operator
 instance per GPU.
@@ -41,69 +46,159 @@ def shard_rows(t, world: int, rank: int):
     return t[lo:hi]
 
 
+class _DeviceBuffer:
+    """A library-allocated device buffer exposed to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, shape: tuple, kind: str):
+        self.ptr = ptr
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": "|i1" if kind == "s8" else "|u1",
+                                         "data": (ptr, False), "version": 2, "strides": None}
+
+    def __del__(self):
+        try:
+            capi.lib().nnb200_peer_buffer_free(self.ptr)
+        except Exception:
+            pass
+
+
 class ShardedLinearI8:
     """s8 x s8 Linear with the fused epilogue, N-sharded.  All tensors live on ``device``."""
 
     def __init__(self, w_shard: torch.Tensor, *, n_total: int, world: int, rank: int, group=None,
                  out_kind: str = "s8", bias_shard=None, scale_w_shard=1.0, scale_a=1.0, out_scale=1.0, out_zp=0,
-                 relu: bool = False):
+                 relu: bool = False, mode: str = "nccl"):
         lo, hi = shard_bounds(n_total, world, rank)
         if w_shard.shape[0] != hi - lo:
             raise ValueError("weight shard has the wrong number of rows")
+        if mode not in ("nccl", "fused"):
+            raise ValueError("mode must be 'nccl' or 'fused'")
+        if mode == "fused" and out_kind not in ("s8", "u8"):
+            raise ValueError("the fused write-back serves 8-bit outputs")
         self.w = w_shard
         self.n_total, self.world, self.rank, self.group = n_total, world, rank, group
-        self.n_per = hi - lo
+        self.col0, self.n_per = lo, hi - lo
         self.out_kind = out_kind
+        self.mode = mode if world > 1 else "nccl"
         self.kw = dict(bias=bias_shard, scale_w=scale_w_shard, scale_a=scale_a, out_scale=out_scale, out_zp=out_zp,
                        relu=relu)
-        self._plans: dict = {}   # (a ptr, M, out ptr) -> prepared argument block + buffers
+        self._plans: dict = {}    # (a ptr, M, out ptr) -> prepared argument block + buffers
         self._last = None
+        self._peer_ptrs: dict = {}    # local output data_ptr -> addresses of the other ranks' copies, mapped here
+        self._owners: list = []
+        self._token = None
+
+    # ---- outputs -------------------------------------------------------------------------
+
+    def alloc_outputs(self, m: int, count: int = 1) -> list[torch.Tensor]:
+        """``count`` full [M, N] outputs on this rank.  In fused mode every rank must call this
+        with the same arguments: the buffers are library allocations exported through CUDA IPC,
+        and every rank maps every other rank's copies with ITS OWN device current (that is what
+        makes them storable from its kernels)."""
+        dev = self.w.device
+        dt = ops._OUT_TORCH[self.out_kind]
+        if self.mode != "fused":
+            return [torch.empty((m, self.n_total), dtype=dt, device=dev) for _ in range(count)]
+        lib = capi.lib()
+        nbytes = m * self.n_total                    # 8-bit outputs
+        outs, handles = [], []
+        with torch.cuda.device(dev):
+            for _ in range(count):
+                ptr = C.c_void_p()
+                capi.check(lib.nnb200_peer_buffer_alloc(C.byref(ptr), nbytes), "nnb200_peer_buffer_alloc")
+                h = C.create_string_buffer(64)
+                capi.check(lib.nnb200_peer_buffer_export(ptr, h), "nnb200_peer_buffer_export")
+                owner = _DeviceBuffer(ptr.value, (m, self.n_total), self.out_kind)
+                t = torch.as_tensor(owner, device=dev)
+                self._owners.append(owner)
+                outs.append(t)
+                handles.append(h.raw)
+            everyone: list = [None] * self.world
+            dist.all_gather_object(everyone, handles, group=self.group)
+            for i, t in enumerate(outs):
+                mapped = []
+                for r in range(self.world):
+                    if r != self.rank:
+                        p = C.c_void_p()
+                        capi.check(lib.nnb200_peer_buffer_open(everyone[r][i], C.byref(p)), "nnb200_peer_buffer_open")
+                        mapped.append(p.value)
+                self._peer_ptrs[t.data_ptr()] = mapped
+        self._token = torch.zeros(1, dtype=torch.int32, device=dev)
+        dist.barrier(group=self.group)                   # every rank has mapped everything
+        return outs
+
+    def rank_barrier(self) -> None:
+        """Order the ranks on the current stream (one-element all-reduce)."""
+        if self.world > 1:
+            if self._token is None:
+                self._token = torch.zeros(1, dtype=torch.int32, device=self.w.device)
+            dist.all_reduce(self._token, group=self.group)
+
+    # ---- compute -------------------------------------------------------------------------
 
     def _plan(self, a: torch.Tensor, out: torch.Tensor | None) -> dict:
         """Argument block and buffers for this (activations, destination) pair, built once."""
         m = a.shape[0]
-        key = (a.data_ptr(), m, out.data_ptr() if (out is not None and self.world == 1) else 0)
+        fused = self.mode == "fused" and out is not None and out.data_ptr() in self._peer_ptrs
+        direct = self.world == 1 or fused
+        key = (a.data_ptr(), m, out.data_ptr() if (out is not None and direct) else 0)
         plan = self._plans.get(key)
         if plan is None:
             dt = ops._OUT_TORCH[self.out_kind]
+            gathered = None
             if self.world == 1:
                 # Single GPU: the GEMM writes the caller's output directly.
                 slab = out if out is not None else torch.empty((m, self.n_per), dtype=dt, device=a.device)
-                gathered = None
+            elif fused:
+                slab = out[:, self.col0:self.col0 + self.n_per]        # this rank's window of its own copy
             else:
                 slab = torch.empty((m, self.n_per), dtype=dt, device=a.device)
                 gathered = torch.empty((self.world * m, self.n_per), dtype=dt, device=a.device)  # [g][M][N/g]
             keep: list = []
             args = ops.gemm_i8_args(a, self.w, slab, out_kind=self.out_kind, keep=keep, **self.kw)
-            plan = dict(args=args, keep=keep, slab=slab, gathered=gathered)
+            if fused:
+                peers = self._peer_ptrs[out.data_ptr()]
+                args.num_peer_outs = len(peers)
+                for i, base in enumerate(peers):
+                    args.peer_out[i] = base + self.col0 * out.element_size()   # same window, same pitch
+            plan = dict(args=args, keep=keep, slab=slab, gathered=gathered, fused=fused)
             self._plans[key] = plan
         return plan
 
     def local(self, a: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """This rank's [M, N/g] slab: the GEMM alone (written straight into ``out`` at g = 1)."""
+        """This rank's share of the work: the GEMM alone.  At g = 1 it writes ``out`` directly; in
+        fused mode it writes this rank's column window of EVERY rank's ``out``."""
         plan = self._plan(a, out)
-        capi.check(capi.lib().nnb200_gemm_i8(C.byref(plan["args"]), torch.cuda.current_stream(a.device).cuda_stream),
-                   "nnb200_gemm_i8")
+        with torch.cuda.device(a.device):
+            capi.check(capi.lib().nnb200_gemm_i8(C.byref(plan["args"]),
+                                                 torch.cuda.current_stream(a.device).cuda_stream), "nnb200_gemm_i8")
         self._last = plan
         return plan["slab"]
 
     def reassemble(self, out: torch.Tensor | None = None) -> torch.Tensor:
-        """All-gather the slabs of the last ``local`` call and interleave them into [M, N]."""
+        """Make the full [M, N] of the last ``local`` call valid on this rank."""
         plan = self._last
         slab = plan["slab"]
         if self.world == 1:
             return slab
+        if plan["fused"]:
+            self.rank_barrier()       # every rank's tiles have landed in every copy
+            return out
         m = slab.shape[0]
         if out is None:
             out = torch.empty((m, self.n_total), dtype=slab.dtype, device=slab.device)
         dist.all_gather_into_tensor(plan["gathered"], slab, group=self.group)
         esize = slab.element_size()
-        capi.check(capi.lib().nnb200_interleave_shards(
-            plan["gathered"].data_ptr(), out.data_ptr(), m, self.n_per * esize, self.world, out.stride(0) * esize,
-            torch.cuda.current_stream(slab.device).cuda_stream), "nnb200_interleave_shards")
+        with torch.cuda.device(slab.device):
+            capi.check(capi.lib().nnb200_interleave_shards(
+                plan["gathered"].data_ptr(), out.data_ptr(), m, self.n_per * esize, self.world, out.stride(0) * esize,
+                torch.cuda.current_stream(slab.device).cuda_stream), "nnb200_interleave_shards")
         return out
 
-    def forward(self, a: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """Full row-major [M, N] output on every rank."""
+    def forward(self, a: torch.Tensor, out: torch.Tensor | None = None, *, wait_for_readers: bool = False) -> torch.Tensor:
+        """Full row-major [M, N] output on every rank.  ``wait_for_readers``: in fused mode, order
+        the ranks BEFORE the GEMM as well, for callers whose previous result in ``out`` may still
+        be read on another rank when this call starts."""
+        if wait_for_readers and self.mode == "fused":
+            self.rank_barrier()
         self.local(a, out)
         return self.reassemble(out)

@@ -181,3 +181,50 @@ def test_config5_rows_and_linearity(cuda_device, nnb200_lib):
     s = ops.gemm_i8(a1, tw) + ops.gemm_i8(a2, tw)
     full = ops.gemm_i8(ta, tw)
     assert torch.equal(s, full)
+
+
+@pytest.mark.parametrize("shape", [(512, 1024, 1024), (300, 2048 + 16, 512), (4096, 3584, 256)])
+@pytest.mark.parametrize("out_kind", ["s8", "u8"])
+def test_multi_destination_epilogue_local(cuda_device, nnb200_lib, shape, out_kind):
+    """The sharded write-back on ONE GPU: the kernel stores its [M, n] window into `out` and into
+    two more buffers that play the other ranks' copies (plain local memory here).  Every copy
+    must equal the oracle inside the window and stay untouched outside it."""
+    import ctypes as C
+    from nnops_b200 import capi
+    m, n, k = shape
+    rng = np.random.default_rng(m + n)
+    a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    kw = dict(out_kind=out_kind, bias=rng.integers(-1000, 1001, n).astype(np.int32), relu=True, scale_a=0.02,
+              scale_w=rng.uniform(0.001, 0.02, n).astype(np.float32), out_scale=1.6, out_zp=2)
+    want = oracle.gemm_i8(a, w, **kw)
+    n_full, col0 = 2 * n + 64, n + 32            # the window sits in the middle of a wider matrix
+    tdt = ops._OUT_TORCH[out_kind]
+    copies = [torch.full((m, n_full), 0x5A, dtype=tdt, device=cuda_device) for _ in range(3)]
+    ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(w).to(cuda_device)
+    keep = []
+    args = ops.gemm_i8_args(ta, tw, copies[0][:, col0:col0 + n], keep=keep, **kw)
+    args.num_peer_outs = 2
+    for i in range(2):
+        args.peer_out[i] = copies[i + 1][:, col0:col0 + n].data_ptr()
+    capi.check(nnb200_lib.nnb200_gemm_i8(C.byref(args), torch.cuda.current_stream(cuda_device).cuda_stream), "gemm")
+    torch.cuda.synchronize()
+    for c in copies:
+        got = c.cpu().numpy()
+        assert np.array_equal(got[:, col0:col0 + n], want)
+        assert np.all(got[:, :col0] == 0x5A) and np.all(got[:, col0 + n:] == 0x5A)
+
+
+def test_multi_destination_rejections(cuda_device, nnb200_lib):
+    import ctypes as C
+    from nnops_b200 import capi
+    a = torch.zeros((256, 256), dtype=torch.int8, device=cuda_device)
+    w = torch.zeros((256, 256), dtype=torch.int8, device=cuda_device)
+    o32 = torch.full((256, 256), 7, dtype=torch.int32, device=cuda_device)
+    other = torch.zeros((256, 256), dtype=torch.int32, device=cuda_device)
+    args = ops.gemm_i8_args(a, w, o32, out_kind="s32")
+    args.num_peer_outs = 1
+    args.peer_out[0] = other.data_ptr()
+    assert nnb200_lib.nnb200_gemm_i8(C.byref(args), None) == capi.UNSUPPORTED     # 8-bit destinations only
+    torch.cuda.synchronize()
+    assert bool((o32 == 7).all())

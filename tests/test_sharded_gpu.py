@@ -17,7 +17,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _rank_main(rank: int, world: int, port: int, m: int, n: int, k: int, q):
+def _rank_main(rank: int, world: int, port: int, m: int, n: int, k: int, mode: str, q):
     import torch.distributed as dist
     from nnops_b200 import capi, synth
     from nnops_b200.sharded import ShardedLinearI8, shard_rows
@@ -28,25 +28,52 @@ def _rank_main(rank: int, world: int, port: int, m: int, n: int, k: int, q):
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
+        _rank_body(rank, world, m, n, k, mode, q, dev)
+    except Exception:  # report instead of leaving the parent to time out
+        import traceback
+        q.put((rank, "ERROR: " + traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _rank_body(rank, world, m, n, k, mode, q, dev):
+    import torch.distributed as dist
+    from nnops_b200 import capi, synth
+    from nnops_b200.sharded import ShardedLinearI8, shard_rows
+    if True:
         c = synth.config2(m=m, n=n, k=k, out_scale=1.6)
         layer = ShardedLinearI8(
             torch.from_numpy(np.ascontiguousarray(shard_rows(c.w, world, rank))).to(dev), n_total=n, world=world,
             rank=rank, out_kind="s8", relu=True, scale_a=c.scale_a, out_scale=c.out_scale,
             bias_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.bias, world, rank))).to(dev),
-            scale_w_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.scale_w, world, rank))).to(dev))
+            scale_w_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.scale_w, world, rank))).to(dev),
+            mode=mode)
         a = torch.from_numpy(c.a).to(dev)
-        out = torch.full((m, n + 32), 0x5A, dtype=torch.int8, device=dev)   # pitched destination
-        for _ in range(2):                                                   # twice: buffers are reused
-            layer.forward(a, out[:, :n])
+        if mode == "fused":
+            outs = layer.alloc_outputs(m, count=2)                           # peer-mapped on every rank
+            for o in outs:
+                o.fill_(0x5A)
+            torch.cuda.synchronize()
+            dist.barrier()
+            for i in range(4):                                               # alternate buffers, reuse them
+                layer.forward(a, outs[i & 1], wait_for_readers=True)
+            torch.cuda.synchronize()
+            assert torch.equal(outs[0], outs[1])
+            result = torch.full((m, n + 32), 0x5A, dtype=torch.int8, device=dev)
+            result[:, :n] = outs[1]
+        else:
+            result = torch.full((m, n + 32), 0x5A, dtype=torch.int8, device=dev)   # pitched destination
+            for _ in range(2):                                                      # twice: buffers are reused
+                layer.forward(a, result[:, :n])
         torch.cuda.synchronize()
         assert capi.take_device_error() == 0
-        q.put((rank, out.cpu().numpy()))
-    finally:
-        dist.destroy_process_group()
+        dist.barrier()
+        q.put((rank, result.cpu().numpy()))
 
 
+@pytest.mark.parametrize("mode", ["nccl", "fused"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_sharded_matches_single_gpu(nnb200_lib, world):
+def test_sharded_matches_single_gpu(nnb200_lib, world, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
@@ -56,12 +83,15 @@ def test_sharded_matches_single_gpu(nnb200_lib, world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, m, n, k, q)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, m, n, k, mode, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = dict(q.get(timeout=300) for _ in range(world))
+    results = dict(q.get(timeout=120) for _ in range(world))
     for p in procs:
         p.join(timeout=120)
+    for r, v in results.items():
+        assert not isinstance(v, str), f"rank {r}: {v}"
+    for p in procs:
         assert p.exitcode == 0
     c = synth.config2(m=m, n=n, k=k, out_scale=1.6)
     dev = torch.device("cuda:0")
