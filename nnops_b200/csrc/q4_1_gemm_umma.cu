@@ -7,8 +7,11 @@
 // staging of a tcgen05 pipeline, so the 4.5-bit weight stream is all that ever leaves HBM:
 //
 //   * warp 0 TMA-loads 128 x 64 f16 activation tiles (128-byte swizzle) into a ring;
-//   * BN/32 dequant warps (one thread per weight row) read the raw 20-byte blocks from
-//     global memory one k-step ahead, expand the nibbles to f16 with integer tricks
+//   * the same warp TMA-loads the RAW Q4_1 stream -- W viewed as rows of 32-bit words, one box
+//     of 20 words (4 blocks = 128 k) x BN rows per two k-steps -- into a small ring; rows that
+//     TMA cannot address (pitch or base not 16-byte aligned) are read with plain loads instead;
+//   * BN/32 dequant warps (one thread per weight row) pull their row's 80 bytes from that ring
+//     with conflict-free 16-byte shared loads, expand the nibbles to f16 with integer tricks
 //     (nibble | 0x6400 = 1024 + q exactly, minus 1024, then one hfma2 q*d + m -- a single f16
 //     rounding per weight, which is what the reference's f16 route stores), and write them
 //     into the ring in the same K-major 128-byte-swizzled layout TMA would have produced;
@@ -17,6 +20,7 @@
 //
 // Every wait is bounded (see ptx.cuh).
 
+#include <cstring>
 #include <mutex>
 
 #include "internal.cuh"
@@ -32,17 +36,22 @@ constexpr int kBlockK = 64;  // halves per stage = one 128-byte swizzle row = tw
 constexpr int kUmmaKBytes = 32;
 constexpr int kGroupM = 8;
 
-template <int BN>
+constexpr int kRawSlots = 3;             // raw-block ring depth (each slot = 128 k of BN rows)
+constexpr int kRawRowBytes = 4 * kQ4BlockBytes;  // 80 B: four blocks
+
+template <int BN, bool RAW_TMA>
 struct Q4Config {
     static constexpr int kATileBytes = kBlockM * kBlockK * 2;
     static constexpr int kBTileBytes = BN * kBlockK * 2;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
-    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kRawSlotBytes = BN * kRawRowBytes;
+    static constexpr int kRawBytes = RAW_TMA ? kRawSlots * kRawSlotBytes : 0;
+    static constexpr int kStages = RAW_TMA ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6);
     static constexpr int kDequantWarps = BN / 32;
     static constexpr int kNumThreads = (6 + kDequantWarps) * 32;
     static constexpr int kTmemCols = 2 * BN;
-    static constexpr int kBarrierBytes = (3 * kStages + 4) * 8 + 16;
-    static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kBarrierBytes;
+    static constexpr int kBarrierBytes = (3 * kStages + 4 + 2 * kRawSlots) * 8 + 16;
+    static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kRawBytes + kBarrierBytes;
 };
 
 struct TileCoord {
@@ -98,25 +107,29 @@ __device__ __forceinline__ void dequant_word_pair(uint32_t w0, uint32_t w1, __ha
     hi = make_uint4(hi_out[0], hi_out[1], hi_out[2], hi_out[3]);
 }
 
-template <int BN, bool OUT_F16>
-__global__ void __launch_bounds__(Q4Config<BN>::kNumThreads, 1)
-q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* __restrict__ w,
+template <int BN, bool OUT_F16, bool RAW_TMA>
+__global__ void __launch_bounds__(Q4Config<BN, RAW_TMA>::kNumThreads, 1)
+q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                      const uint8_t* __restrict__ w,
                       const int64_t ldw_blocks, void* __restrict__ out, const int64_t ldc, const int m_total,
                       const int n_total, const int k_total, const FpEpilogue ep, const uint32_t idesc,
                       const int vec_ok, int32_t* error_word)
 {
-    using Cfg = Q4Config<BN>;
+    using Cfg = Q4Config<BN, RAW_TMA>;
     constexpr int kStages = Cfg::kStages;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_base = smem;
-    uint64_t* a_full_bar = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+    uint8_t* raw_base = smem + kStages * Cfg::kStageBytes;  // raw-block ring (RAW_TMA only)
+    uint64_t* a_full_bar = reinterpret_cast<uint64_t*>(raw_base + Cfg::kRawBytes);
     uint64_t* b_full_bar = a_full_bar + kStages;
     uint64_t* empty_bar = b_full_bar + kStages;
     uint64_t* acc_full_bar = empty_bar + kStages;
     uint64_t* acc_empty_bar = acc_full_bar + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+    uint64_t* raw_full_bar = acc_empty_bar + 2;
+    uint64_t* raw_empty_bar = raw_full_bar + kRawSlots;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_empty_bar + kRawSlots);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -138,11 +151,18 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
             mbar_init(&acc_full_bar[a], 1);
             mbar_init(&acc_empty_bar[a], 4);
         }
+        for (int rs = 0; rs < kRawSlots; ++rs) {
+            mbar_init(&raw_full_bar[rs], 1);
+            mbar_init(&raw_empty_bar[rs], Cfg::kDequantWarps);
+        }
         *abort_flag = 0;
         mbar_init_fence();
     }
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&map_a);
+        if constexpr (RAW_TMA) {
+            tma_prefetch_desc(&map_w);
+        }
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -159,10 +179,32 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
             int stage = 0;
             uint32_t phase = 0;
             uint32_t armed = 0, armed_phase = 0;
+            int rslot = 0;
+            uint32_t rphase = 0;
+            uint32_t rarmed = 0, rarmed_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 const TileCoord tc = tile_coord(tile, num_m, num_n);
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    if constexpr (RAW_TMA) {
+                        if ((kb & 1) == 0) {
+                            // Raw weights for k-steps kb and kb+1: 4 blocks of every row of the tile.
+                            if (!mbar_wait(&raw_empty_bar[rslot], rphase ^ 1u, abort_flag)) {
+                                atomicCAS(error_word, 0, kErrProducerWait);
+                                ok = false;
+                                break;
+                            }
+                            mbar_expect_tx(&raw_full_bar[rslot], Cfg::kRawSlotBytes);
+                            tma_load_2d(raw_base + rslot * Cfg::kRawSlotBytes, &map_w, &raw_full_bar[rslot],
+                                        (kb >> 1) * (kRawRowBytes / 4), tc.n_blk * BN);
+                            rarmed |= 1u << rslot;
+                            rarmed_phase = (rarmed_phase & ~(1u << rslot)) | (rphase << rslot);
+                            if (++rslot == kRawSlots) {
+                                rslot = 0;
+                                rphase ^= 1u;
+                            }
+                        }
+                    }
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         atomicCAS(error_word, 0, kErrProducerWait);
                         ok = false;
@@ -184,6 +226,16 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
                 for (int s = 0; s < kStages; ++s) {
                     if ((armed >> s) & 1u) {
                         while (!mbar_try_wait(&a_full_bar[s], (armed_phase >> s) & 1u)) {
+                            if (clock64() - t0 > kWaitLimitCycles) {
+                                atomicCAS(error_word, 0, kErrDrainWait);
+                                break;
+                            }
+                        }
+                    }
+                }
+                for (int s = 0; s < kRawSlots; ++s) {
+                    if ((rarmed >> s) & 1u) {
+                        while (!mbar_try_wait(&raw_full_bar[s], (rarmed_phase >> s) & 1u)) {
                             if (clock64() - t0 > kWaitLimitCycles) {
                                 atomicCAS(error_word, 0, kErrDrainWait);
                                 break;
@@ -357,25 +409,8 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
             }
         };
 
-        uint32_t next[10];
-        if (total_it > 0) {
-            load_raw(0, next);
-        }
-        int stage = 0;
-        uint32_t phase = 0;
-        for (int it = 0; it < total_it; ++it) {
-            uint32_t raw[10];
-#pragma unroll
-            for (int i = 0; i < 10; ++i) {
-                raw[i] = next[i];
-            }
-            if (it + 1 < total_it) {
-                load_raw(it + 1, next);
-            }
-            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag))) {
-                atomicCAS(error_word, 0, kErrDequantWait);
-                break;
-            }
+        // Dequantise blocks (5 words each) raw[0..4] and raw[5..9] of this row into B slot `stage`.
+        auto emit_stage = [&](const uint32_t* raw, int stage) {
             uint8_t* b_row = stage_base + stage * Cfg::kStageBytes + Cfg::kATileBytes + r * 128;
             const int sw = r & 7;
 #pragma unroll
@@ -397,9 +432,83 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
             if (lane == 0) {
                 mbar_arrive(&b_full_bar[stage]);
             }
-            if (++stage == kStages) {
-                stage = 0;
-                phase ^= 1u;
+        };
+
+        int stage = 0;
+        uint32_t phase = 0;
+        if constexpr (RAW_TMA) {
+            int rslot = 0;
+            uint32_t rphase = 0;
+            bool ok = true;
+            for (int t = 0; ok && t < my_tiles; ++t) {
+                for (int kb0 = 0; kb0 < num_kb; kb0 += 2) {
+                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(&raw_full_bar[rslot], rphase, abort_flag))) {
+                        atomicCAS(error_word, 0, kErrDequantWait);
+                        ok = false;
+                        break;
+                    }
+                    // This row's 80 bytes: five 16-byte shared loads, conflict-free (80-byte row stride).
+                    uint32_t raw[20];
+                    const uint4* src = reinterpret_cast<const uint4*>(raw_base + rslot * Cfg::kRawSlotBytes + r * kRawRowBytes);
+#pragma unroll
+                    for (int j = 0; j < 5; ++j) {
+                        const uint4 v = src[j];
+                        raw[4 * j] = v.x;
+                        raw[4 * j + 1] = v.y;
+                        raw[4 * j + 2] = v.z;
+                        raw[4 * j + 3] = v.w;
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&raw_empty_bar[rslot]);  // the slot can be refilled
+                    }
+                    if (++rslot == kRawSlots) {
+                        rslot = 0;
+                        rphase ^= 1u;
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (kb0 + h < num_kb) {
+                            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag))) {
+                                atomicCAS(error_word, 0, kErrDequantWait);
+                                ok = false;
+                                break;
+                            }
+                            emit_stage(raw + 10 * h, stage);
+                            if (++stage == kStages) {
+                                stage = 0;
+                                phase ^= 1u;
+                            }
+                        }
+                    }
+                    if (!ok) {
+                        break;
+                    }
+                }
+            }
+        } else {
+            uint32_t next[10];
+            if (total_it > 0) {
+                load_raw(0, next);
+            }
+            for (int it = 0; it < total_it; ++it) {
+                uint32_t raw[10];
+#pragma unroll
+                for (int i = 0; i < 10; ++i) {
+                    raw[i] = next[i];
+                }
+                if (it + 1 < total_it) {
+                    load_raw(it + 1, next);
+                }
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag))) {
+                    atomicCAS(error_word, 0, kErrDequantWait);
+                    break;
+                }
+                emit_stage(raw, stage);
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
             }
         }
     }
@@ -413,12 +522,12 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
     }
 }
 
-template <int BN, bool OUT_F16>
-int launch_variant(const nnb200_q4_1_args& q, const CUtensorMap& map_a, const FpEpilogue& ep, const DeviceInfo& dev,
-                   cudaStream_t stream)
+template <int BN, bool OUT_F16, bool RAW_TMA>
+int launch_variant(const nnb200_q4_1_args& q, const CUtensorMap& map_a, const CUtensorMap& map_w, const FpEpilogue& ep,
+                   const DeviceInfo& dev, cudaStream_t stream)
 {
-    using Cfg = Q4Config<BN>;
-    auto kernel = q4_1_gemm_umma_kernel<BN, OUT_F16>;
+    using Cfg = Q4Config<BN, RAW_TMA>;
+    auto kernel = q4_1_gemm_umma_kernel<BN, OUT_F16, RAW_TMA>;
     static std::once_flag once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
     std::call_once(once[dev.device], [&] {
@@ -437,7 +546,7 @@ int launch_variant(const nnb200_q4_1_args& q, const CUtensorMap& map_a, const Fp
                            ? 1
                            : 0;
     kernel<<<grid, Cfg::kNumThreads, Cfg::kSmemBytes, stream>>>(
-        map_a, static_cast<const uint8_t*>(q.w_blocks), q.ldw_blocks, q.out, q.ldc, m, n, k, ep,
+        map_a, map_w, static_cast<const uint8_t*>(q.w_blocks), q.ldw_blocks, q.out, q.ldc, m, n, k, ep,
         umma_idesc(1, 0, 0, kBlockM, BN), vec_ok, dev.error_word);
     note_launch();
     return cuda_status(cudaGetLastError());
@@ -471,12 +580,26 @@ int launch_q4_1_gemm_umma(const nnb200_q4_1_args& q, const DeviceInfo& dev, cuda
     }
     const int num_m = static_cast<int>((q.m + kBlockM - 1) / kBlockM);
     const bool wide = static_cast<int64_t>(num_m) * ((q.n + 255) / 256) >= dev.sm_count;
-    if (wide) {
-        return q.out_f16 ? launch_variant<256, true>(q, map_a, ep, dev, stream)
-                         : launch_variant<256, false>(q, map_a, ep, dev, stream);
+    // Raw blocks by TMA when W's rows are addressable as 16-byte aligned runs of 32-bit words.
+    const bool raw_tma = (reinterpret_cast<uintptr_t>(q.w_blocks) & 15u) == 0 && (q.ldw_blocks % 4) == 0;
+    CUtensorMap map_w;
+    std::memset(&map_w, 0, sizeof(map_w));
+    if (raw_tma) {
+        const int64_t nblk = (q.k + kQ4BlockElems - 1) / kQ4BlockElems;
+        if (!make_tma_2d(&map_w, q.w_blocks, 4, static_cast<uint64_t>(nblk * kQ4BlockWords), static_cast<uint64_t>(q.n),
+                         static_cast<uint64_t>(q.ldw_blocks) * kQ4BlockBytes, kRawRowBytes / 4, wide ? 256u : 128u,
+                         /*swizzle128=*/false)) {
+            return NNB200_INTERNAL;
+        }
     }
-    return q.out_f16 ? launch_variant<128, true>(q, map_a, ep, dev, stream)
-                     : launch_variant<128, false>(q, map_a, ep, dev, stream);
+#define NNB200_Q4_LAUNCH(BNV, F16V)                                                              \
+    (raw_tma ? launch_variant<BNV, F16V, true>(q, map_a, map_w, ep, dev, stream)                 \
+             : launch_variant<BNV, F16V, false>(q, map_a, map_w, ep, dev, stream))
+    if (wide) {
+        return q.out_f16 ? NNB200_Q4_LAUNCH(256, true) : NNB200_Q4_LAUNCH(256, false);
+    }
+    return q.out_f16 ? NNB200_Q4_LAUNCH(128, true) : NNB200_Q4_LAUNCH(128, false);
+#undef NNB200_Q4_LAUNCH
 }
 
 }  // namespace nnb200
