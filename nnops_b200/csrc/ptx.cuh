@@ -108,6 +108,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// Warp-collective wait: lane 0 polls, the result is broadcast.  Keeps the number of threads
+// hammering one barrier word at one per warp instead of thirty-two.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
+{
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    }
+    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+    return ok != 0;
+}
+
 // ---- TMA --------------------------------------------------------------------------------
 
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map)
@@ -134,6 +146,24 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
+}
+
+// 16-byte asynchronous copy global -> shared without staging registers; bytes past
+// `src_bytes` (0..16) are written as zeros.  Completion is tracked per thread in commit groups.
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, uint32_t src_bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit()
+{
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // Generic-proxy writes to shared memory -> visible to the async proxy (UMMA / TMA reads).

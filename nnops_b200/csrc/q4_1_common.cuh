@@ -7,6 +7,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cmath>
 #include <cstdint>
 
 #include "epilogue.cuh"
@@ -26,6 +27,14 @@ struct FpEpilogue {
     float act_alpha, act_beta;
     float min_clip, max_clip;
 };
+
+// True when the output arithmetic is the identity (alpha 1, no bias, no clip, no activation):
+// callers test it once per tile and skip fp_epilogue_value altogether.
+__device__ __forceinline__ bool fp_epilogue_is_identity(const FpEpilogue& e)
+{
+    return e.alpha == 1.0f && e.bias == nullptr && e.activation == NNB200_ACT_NONE && e.min_clip == -INFINITY &&
+           e.max_clip == INFINITY;
+}
 
 template <bool OUT_F16>
 __device__ __forceinline__ float fp_epilogue_value(const FpEpilogue& e, float acc, int64_t n)

@@ -7,16 +7,20 @@
 // staging of a tcgen05 pipeline, so the 4.5-bit weight stream is all that ever leaves HBM:
 //
 //   * warp 0 TMA-loads 128 x 64 f16 activation tiles (128-byte swizzle) into a ring;
-//   * the same warp TMA-loads the RAW Q4_1 stream -- W viewed as rows of 32-bit words, one box
-//     of 20 words (4 blocks = 128 k) x BN rows per two k-steps -- into a small ring; rows that
-//     TMA cannot address (pitch or base not 16-byte aligned) are read with plain loads instead;
-//   * BN/32 dequant warps (one thread per weight row) pull their row's 80 bytes from that ring
-//     with conflict-free 16-byte shared loads, expand the nibbles to f16 with integer tricks
+//   * 16 dequant warps fetch the RAW Q4_1 stream themselves, 128 k (4 blocks = 80 B per row) at
+//     a time: coalesced 16-byte global loads issued one step ahead, parked in a double-buffered
+//     shared tile, then each lane picks up "its" block -- lane (g, c) of warp w owns block c of
+//     row 8w+g, a mapping whose 32-bit shared reads are bank-conflict free (20g + 5c + i is a
+//     bijection mod 32).  (TMA was measured first for this stream: with 80-byte box rows it
+//     sustained only about one row per 17 clocks per SM and capped the whole kernel.)  Rows that
+//     cannot be read 16 bytes at a time (base or pitch unaligned) are read by each lane directly;
+//   * the lanes expand the nibbles to f16 with integer tricks
 //     (nibble | 0x6400 = 1024 + q exactly, minus 1024, then one hfma2 q*d + m -- a single f16
 //     rounding per weight, which is what the reference's f16 route stores), and write them
 //     into the ring in the same K-major 128-byte-swizzled layout TMA would have produced;
-//   * warp 1 issues tcgen05.mma kind::f16 (M128 x N=BN x K16) into one of two TMEM
-//     accumulators; warps 2-5 drain the other one and apply alpha / bias / clip / activation.
+//   * warp 1 issues tcgen05.mma kind::f16 (M128 x N128 x K16, twice per k-step when the tile
+//     stacks two 128-row activation halves over one weight tile) into one of two TMEM
+//     accumulator sets; warps 2-5 drain the other and apply alpha / bias / clip / activation.
 //
 // Every wait is bounded (see ptx.cuh).
 
@@ -31,26 +35,30 @@ namespace nnb200 {
 
 namespace {
 
-constexpr int kBlockM = 128;
+constexpr int kHalfM = 128;  // rows per UMMA instruction; a tile stacks MH of them over one weight tile
 constexpr int kBlockK = 64;  // halves per stage = one 128-byte swizzle row = two Q4_1 blocks
 constexpr int kUmmaKBytes = 32;
 constexpr int kGroupM = 8;
 
-constexpr int kRawSlots = 3;             // raw-block ring depth (each slot = 128 k of BN rows)
-constexpr int kRawRowBytes = 4 * kQ4BlockBytes;  // 80 B: four blocks
+constexpr int kRawRowBytes = 4 * kQ4BlockBytes;  // 80 B: the four blocks of one row in a 128-k super-step
+constexpr int kDequantWarps = 16;                // 8 rows x 4 blocks per warp
+constexpr int kDequantThreads = kDequantWarps * 32;
+constexpr int kTileN = 128;                      // weight rows per tile = kDequantWarps * 8
+constexpr int kRawAhead = 2;                     // super-steps of raw weights in flight (cp.async)
+constexpr int kRawBufs = kRawAhead + 1;          // ring of raw tiles in shared memory
 
-template <int BN, bool RAW_TMA>
+template <bool COOP, int MH>
 struct Q4Config {
+    static constexpr int kBlockM = kHalfM * MH;
     static constexpr int kATileBytes = kBlockM * kBlockK * 2;
-    static constexpr int kBTileBytes = BN * kBlockK * 2;
+    static constexpr int kBTileBytes = kTileN * kBlockK * 2;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
-    static constexpr int kRawSlotBytes = BN * kRawRowBytes;
-    static constexpr int kRawBytes = RAW_TMA ? kRawSlots * kRawSlotBytes : 0;
-    static constexpr int kStages = RAW_TMA ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6);
-    static constexpr int kDequantWarps = BN / 32;
+    static constexpr int kRawBufBytes = kTileN * kRawRowBytes;     // 10 240 B
+    static constexpr int kRawBytes = COOP ? kRawBufs * kRawBufBytes : 0;
+    static constexpr int kStages = (MH == 2) ? 4 : 6;
     static constexpr int kNumThreads = (6 + kDequantWarps) * 32;
-    static constexpr int kTmemCols = 2 * BN;
-    static constexpr int kBarrierBytes = (3 * kStages + 4 + 2 * kRawSlots) * 8 + 16;
+    static constexpr int kTmemCols = 2 * MH * kTileN;  // two accumulator sets of MH x 128 columns
+    static constexpr int kBarrierBytes = (3 * kStages + 4) * 8 + 16;
     static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kRawBytes + kBarrierBytes;
 };
 
@@ -107,29 +115,29 @@ __device__ __forceinline__ void dequant_word_pair(uint32_t w0, uint32_t w1, __ha
     hi = make_uint4(hi_out[0], hi_out[1], hi_out[2], hi_out[3]);
 }
 
-template <int BN, bool OUT_F16, bool RAW_TMA>
-__global__ void __launch_bounds__(Q4Config<BN, RAW_TMA>::kNumThreads, 1)
-q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                      const uint8_t* __restrict__ w,
+template <bool OUT_F16, bool COOP, int MH>
+__global__ void __launch_bounds__(Q4Config<COOP, MH>::kNumThreads, 1)
+q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* __restrict__ w,
                       const int64_t ldw_blocks, void* __restrict__ out, const int64_t ldc, const int m_total,
                       const int n_total, const int k_total, const FpEpilogue ep, const uint32_t idesc,
                       const int vec_ok, int32_t* error_word)
 {
-    using Cfg = Q4Config<BN, RAW_TMA>;
+    using Cfg = Q4Config<COOP, MH>;
+    constexpr int BN = kTileN;
     constexpr int kStages = Cfg::kStages;
+    constexpr int kBlockM = Cfg::kBlockM;
+    static_assert(Cfg::kTmemCols <= 512, "accumulators exceed TMEM");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_base = smem;
-    uint8_t* raw_base = smem + kStages * Cfg::kStageBytes;  // raw-block ring (RAW_TMA only)
+    uint8_t* raw_base = smem + kStages * Cfg::kStageBytes;  // two raw-block tiles (COOP only)
     uint64_t* a_full_bar = reinterpret_cast<uint64_t*>(raw_base + Cfg::kRawBytes);
     uint64_t* b_full_bar = a_full_bar + kStages;
     uint64_t* empty_bar = b_full_bar + kStages;
     uint64_t* acc_full_bar = empty_bar + kStages;
     uint64_t* acc_empty_bar = acc_full_bar + 2;
-    uint64_t* raw_full_bar = acc_empty_bar + 2;
-    uint64_t* raw_empty_bar = raw_full_bar + kRawSlots;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_empty_bar + kRawSlots);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -144,25 +152,18 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&a_full_bar[s], 1);
-            mbar_init(&b_full_bar[s], Cfg::kDequantWarps);
+            mbar_init(&b_full_bar[s], kDequantWarps);
             mbar_init(&empty_bar[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full_bar[a], 1);
             mbar_init(&acc_empty_bar[a], 4);
         }
-        for (int rs = 0; rs < kRawSlots; ++rs) {
-            mbar_init(&raw_full_bar[rs], 1);
-            mbar_init(&raw_empty_bar[rs], Cfg::kDequantWarps);
-        }
         *abort_flag = 0;
         mbar_init_fence();
     }
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&map_a);
-        if constexpr (RAW_TMA) {
-            tma_prefetch_desc(&map_w);
-        }
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -179,32 +180,10 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             int stage = 0;
             uint32_t phase = 0;
             uint32_t armed = 0, armed_phase = 0;
-            int rslot = 0;
-            uint32_t rphase = 0;
-            uint32_t rarmed = 0, rarmed_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 const TileCoord tc = tile_coord(tile, num_m, num_n);
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if constexpr (RAW_TMA) {
-                        if ((kb & 1) == 0) {
-                            // Raw weights for k-steps kb and kb+1: 4 blocks of every row of the tile.
-                            if (!mbar_wait(&raw_empty_bar[rslot], rphase ^ 1u, abort_flag)) {
-                                atomicCAS(error_word, 0, kErrProducerWait);
-                                ok = false;
-                                break;
-                            }
-                            mbar_expect_tx(&raw_full_bar[rslot], Cfg::kRawSlotBytes);
-                            tma_load_2d(raw_base + rslot * Cfg::kRawSlotBytes, &map_w, &raw_full_bar[rslot],
-                                        (kb >> 1) * (kRawRowBytes / 4), tc.n_blk * BN);
-                            rarmed |= 1u << rslot;
-                            rarmed_phase = (rarmed_phase & ~(1u << rslot)) | (rphase << rslot);
-                            if (++rslot == kRawSlots) {
-                                rslot = 0;
-                                rphase ^= 1u;
-                            }
-                        }
-                    }
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         atomicCAS(error_word, 0, kErrProducerWait);
                         ok = false;
@@ -222,20 +201,11 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 }
             }
             if (!ok) {
+                // Copies already issued still land in shared memory: wait (bounded) for them.
                 const long long t0 = clock64();
                 for (int s = 0; s < kStages; ++s) {
                     if ((armed >> s) & 1u) {
                         while (!mbar_try_wait(&a_full_bar[s], (armed_phase >> s) & 1u)) {
-                            if (clock64() - t0 > kWaitLimitCycles) {
-                                atomicCAS(error_word, 0, kErrDrainWait);
-                                break;
-                            }
-                        }
-                    }
-                }
-                for (int s = 0; s < kRawSlots; ++s) {
-                    if ((rarmed >> s) & 1u) {
-                        while (!mbar_try_wait(&raw_full_bar[s], (rarmed_phase >> s) & 1u)) {
                             if (clock64() - t0 > kWaitLimitCycles) {
                                 atomicCAS(error_word, 0, kErrDrainWait);
                                 break;
@@ -261,7 +231,7 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * MH * BN);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(&a_full_bar[stage], phase, abort_flag) ||
                         !mbar_wait(&b_full_bar[stage], phase, abort_flag)) {
@@ -276,8 +246,13 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     const uint64_t b_desc = umma_desc_sw128_kmajor(b_addr);
 #pragma unroll
                     for (int ks = 0; ks < (kBlockK * 2) / kUmmaKBytes; ++ks) {
-                        umma_f16(d_tmem, a_desc + static_cast<uint64_t>(ks * 2), b_desc + static_cast<uint64_t>(ks * 2),
-                                 idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+                        for (int h = 0; h < MH; ++h) {
+                            // Each 128-row half of the activation tile meets the same dequantised weights.
+                            umma_f16(d_tmem + static_cast<uint32_t>(h * BN),
+                                     a_desc + static_cast<uint64_t>(h * ((kHalfM * kBlockK * 2) >> 4) + ks * 2),
+                                     b_desc + static_cast<uint64_t>(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(&empty_bar[stage]);
                     if (++stage == kStages) {
@@ -294,28 +269,31 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     } else if (warp < 6) {
         // ---------------- epilogue warps ----------------
         const int quarter = warp & 3;
+        const bool identity = fp_epilogue_is_identity(ep);
         int local_tile = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
             const TileCoord tc = tile_coord(tile, num_m, num_n);
             const int acc = local_tile & 1;
             const uint32_t acc_phase = (local_tile >> 1) & 1u;
             const int n_base = tc.n_blk * BN;
-            const int64_t m = static_cast<int64_t>(tc.m_blk) * kBlockM + quarter * 32 + lane;
-            const bool row_ok = m < m_total;
 
             // Warp-uniform outcome, so no lane is left behind at a later warp sync.
-            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag))) {
+            if (!mbar_wait_warp(&acc_full_bar[acc], acc_phase, abort_flag)) {
                 atomicCAS(error_word, 0, kErrEpilogueWait);
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int hc = 0; hc < MH * (BN / 32); ++hc) {
+                const int h = hc / (BN / 32);
+                const int c = hc % (BN / 32);
+                const int64_t m = static_cast<int64_t>(tc.m_blk) * kBlockM + h * kHalfM + quarter * 32 + lane;
+                const bool row_ok = m < m_total;
+                const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                       static_cast<uint32_t>(acc * MH * BN + h * BN);
                 const int n0 = n_base + c * 32;
                 if (n0 >= n_total) {
-                    break;
+                    continue;  // warp-uniform
                 }
                 uint32_t v[32];
                 tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
@@ -325,9 +303,11 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     uint32_t packed[16];
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
-                        const float f0 = fp_epilogue_value<true>(ep, __uint_as_float(v[j]), min(n0 + j, n_total - 1));
-                        const float f1 =
-                            fp_epilogue_value<true>(ep, __uint_as_float(v[j + 1]), min(n0 + j + 1, n_total - 1));
+                        const float f0 = identity ? __uint_as_float(v[j])
+                                                  : fp_epilogue_value<true>(ep, __uint_as_float(v[j]), min(n0 + j, n_total - 1));
+                        const float f1 = identity ? __uint_as_float(v[j + 1])
+                                                  : fp_epilogue_value<true>(ep, __uint_as_float(v[j + 1]),
+                                                                            min(n0 + j + 1, n_total - 1));
                         packed[j / 2] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f0))) |
                                         (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f1))) << 16);
                     }
@@ -352,7 +332,8 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     float o[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        o[j] = fp_epilogue_value<false>(ep, __uint_as_float(v[j]), min(n0 + j, n_total - 1));
+                        o[j] = identity ? __uint_as_float(v[j])
+                                        : fp_epilogue_value<false>(ep, __uint_as_float(v[j]), min(n0 + j, n_total - 1));
                     }
                     if (row_ok) {
                         float* dst = static_cast<float*>(out) + m * ldc + n0;
@@ -380,136 +361,151 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
     } else {
         // ---------------- dequant warps ----------------
-        const int r = (warp - 6) * 32 + lane;  // weight row inside the tile
+        // Work unit: one Q4_1 block (32 k) of one weight row per super-step of 128 k.  Lane (g, c)
+        // of dequant warp dw owns block c of row 8*dw + g; blocks 0,1 fall in the even k-step of
+        // the super-step, blocks 2,3 in the odd one.
+        const int dw = warp - 6;
+        const int dt = dw * 32 + lane;                // 0..511
+        const int g = lane >> 2;
+        const int c = lane & 3;
+        const int parity = c >> 1;                    // which of the two k-steps this lane feeds
+        const int jblk = c & 1;                       // first or second block of that k-step
+        const int r = dw * 8 + g;                     // weight row inside the tile
+        const int sw = r & 7;
         const int my_tiles = (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                              static_cast<int>(gridDim.x);
-        const int total_it = my_tiles * num_kb;
+        const int num_ss = (num_kb + 1) / 2;
+        const int total_q = my_tiles * num_ss;        // super-steps this CTA walks through
+        const int64_t pitch = ldw_blocks * kQ4BlockBytes;
 
-        // Raw words of the two blocks of iteration `it` for this row (zeros when out of range).
-        auto load_raw = [&](int it, uint32_t (&raw)[10]) {
-            const int tile = static_cast<int>(blockIdx.x) + (it / num_kb) * static_cast<int>(gridDim.x);
-            const int kb = it % num_kb;
-            const TileCoord tc = tile_coord(tile, num_m, num_n);
-            const int64_t n = static_cast<int64_t>(tc.n_blk) * BN + r;
+        // First weight row of the tile that super-step q belongs to.
+        auto tile_row0 = [&](int q) {
+            const int tile = static_cast<int>(blockIdx.x) + (q / num_ss) * static_cast<int>(gridDim.x);
+            return static_cast<int64_t>(tile_coord(tile, num_m, num_n).n_blk) * BN;
+        };
+
+        // COOP: the raw tile of a super-step is 128 rows x 80 B = 640 pieces of 16 B; thread dt
+        // copies piece dt and (dt < 128) piece 512 + dt with cp.async, kRawAhead super-steps ahead,
+        // into a ring of kRawBufs tiles.  Pieces past N or past the row end arrive as zeros.
+        auto issue_piece = [&](int q, int piece) {
+            const int row = piece / 5;
+            const int j = piece - row * 5;
+            const int64_t n = tile_row0(q) + row;
+            const int64_t byte0 = static_cast<int64_t>(q % num_ss) * kRawRowBytes + j * 16;
+            const int64_t row_bytes = static_cast<int64_t>(nblk) * kQ4BlockBytes;
+            int64_t valid = n < n_total ? row_bytes - byte0 : 0;
+            valid = valid < 0 ? 0 : (valid > 16 ? 16 : valid);
+            const uint8_t* src = valid > 0 ? w + n * pitch + byte0 : w;
+            cp_async_16(raw_base + (q % kRawBufs) * Cfg::kRawBufBytes + piece * 16, src, static_cast<uint32_t>(valid));
+        };
+        auto issue_super_step = [&](int q) {
+            if (q < total_q) {
+                issue_piece(q, dt);
+                if (dt < 128) {
+                    issue_piece(q, 512 + dt);
+                }
+            }
+            cp_async_commit();  // one group per super-step, empty ones included, so the counts line up
+        };
+        // Plain path: this lane's own block, five 32-bit loads.
+        uint32_t next[5] = {0u, 0u, 0u, 0u, 0u};
+        auto fetch_block = [&](int q) {
+            const int64_t n = tile_row0(q) + r;
+            const int b = (q % num_ss) * 4 + c;
+            if (n < n_total && b < nblk) {
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(w + n * pitch + static_cast<int64_t>(b) * kQ4BlockBytes);
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int b = kb * 2 + j;
-                if (n < n_total && b < nblk) {
-                    const uint32_t* src = reinterpret_cast<const uint32_t*>(w + (n * ldw_blocks + b) * kQ4BlockBytes);
+                for (int i = 0; i < 5; ++i) {
+                    next[i] = __ldg(src + i);
+                }
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 5; ++i) {
-                        raw[5 * j + i] = __ldg(src + i);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 5; ++i) {
-                        raw[5 * j + i] = 0u;
-                    }
+                for (int i = 0; i < 5; ++i) {
+                    next[i] = 0u;
                 }
             }
         };
 
-        // Dequantise blocks (5 words each) raw[0..4] and raw[5..9] of this row into B slot `stage`.
-        auto emit_stage = [&](const uint32_t* raw, int stage) {
-            uint8_t* b_row = stage_base + stage * Cfg::kStageBytes + Cfg::kATileBytes + r * 128;
-            const int sw = r & 7;
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const uint32_t dm = raw[5 * j];
-                const __half2 d2 = __half2half2(__ushort_as_half(static_cast<uint16_t>(dm & 0xFFFFu)));
-                const __half2 m2 = __half2half2(__ushort_as_half(static_cast<uint16_t>(dm >> 16)));
-                uint4 lo0, hi0, lo1, hi1;
-                dequant_word_pair(raw[5 * j + 1], raw[5 * j + 2], d2, m2, lo0, hi0);  // k 0..7 and 16..23
-                dequant_word_pair(raw[5 * j + 3], raw[5 * j + 4], d2, m2, lo1, hi1);  // k 8..15 and 24..31
-                // 16-byte chunk c of the row lives at chunk (c ^ (row & 7)): the 128-byte swizzle.
-                *reinterpret_cast<uint4*>(b_row + (((4 * j + 0) ^ sw) << 4)) = lo0;
-                *reinterpret_cast<uint4*>(b_row + (((4 * j + 1) ^ sw) << 4)) = lo1;
-                *reinterpret_cast<uint4*>(b_row + (((4 * j + 2) ^ sw) << 4)) = hi0;
-                *reinterpret_cast<uint4*>(b_row + (((4 * j + 3) ^ sw) << 4)) = hi1;
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&b_full_bar[stage]);
-            }
-        };
-
-        int stage = 0;
-        uint32_t phase = 0;
-        if constexpr (RAW_TMA) {
-            int rslot = 0;
-            uint32_t rphase = 0;
-            bool ok = true;
-            for (int t = 0; ok && t < my_tiles; ++t) {
-                for (int kb0 = 0; kb0 < num_kb; kb0 += 2) {
-                    if (!__all_sync(0xFFFFFFFFu, mbar_wait(&raw_full_bar[rslot], rphase, abort_flag))) {
-                        atomicCAS(error_word, 0, kErrDequantWait);
-                        ok = false;
-                        break;
-                    }
-                    // This row's 80 bytes: five 16-byte shared loads, conflict-free (80-byte row stride).
-                    uint32_t raw[20];
-                    const uint4* src = reinterpret_cast<const uint4*>(raw_base + rslot * Cfg::kRawSlotBytes + r * kRawRowBytes);
-#pragma unroll
-                    for (int j = 0; j < 5; ++j) {
-                        const uint4 v = src[j];
-                        raw[4 * j] = v.x;
-                        raw[4 * j + 1] = v.y;
-                        raw[4 * j + 2] = v.z;
-                        raw[4 * j + 3] = v.w;
-                    }
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(&raw_empty_bar[rslot]);  // the slot can be refilled
-                    }
-                    if (++rslot == kRawSlots) {
-                        rslot = 0;
-                        rphase ^= 1u;
-                    }
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        if (kb0 + h < num_kb) {
-                            if (!__all_sync(0xFFFFFFFFu, mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag))) {
-                                atomicCAS(error_word, 0, kErrDequantWait);
-                                ok = false;
-                                break;
-                            }
-                            emit_stage(raw + 10 * h, stage);
-                            if (++stage == kStages) {
-                                stage = 0;
-                                phase ^= 1u;
-                            }
-                        }
-                    }
-                    if (!ok) {
-                        break;
-                    }
+        if (total_q > 0) {
+            if constexpr (COOP) {
+                for (int q0 = 0; q0 < kRawAhead; ++q0) {
+                    issue_super_step(q0);
                 }
+            } else {
+                fetch_block(0);
             }
-        } else {
-            uint32_t next[10];
-            if (total_it > 0) {
-                load_raw(0, next);
-            }
-            for (int it = 0; it < total_it; ++it) {
-                uint32_t raw[10];
+        }
+        int kcount = 0;     // k-steps this CTA has gone through before the current super-step
+        bool dead = false;  // a wait ran out: keep walking (the barriers below need every warp) but do nothing
+        for (int q = 0; q < total_q; ++q) {
+            uint32_t raw[5];
+            if constexpr (COOP) {
+                uint8_t* buf = raw_base + (q % kRawBufs) * Cfg::kRawBufBytes;
+                // Slot (q + kRawAhead) % kRawBufs was last read in super-step q - 1, which every warp
+                // finished before passing that step's barrier... except the readers still inside
+                // step q - 1 right now; the barrier below is what orders them, so the refill is
+                // issued after it.
+                cp_async_wait_group<kRawAhead - 1>();   // this thread's pieces of super-step q have landed
+                named_barrier_sync(1, kDequantThreads); // ... and everyone else's; step q - 1 is fully read
+                issue_super_step(q + kRawAhead);
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(buf + r * kRawRowBytes) + c * kQ4BlockWords;
 #pragma unroll
-                for (int i = 0; i < 10; ++i) {
+                for (int i = 0; i < 5; ++i) {
+                    raw[i] = src[i];
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 5; ++i) {
                     raw[i] = next[i];
                 }
-                if (it + 1 < total_it) {
-                    load_raw(it + 1, next);
-                }
-                if (!__all_sync(0xFFFFFFFFu, mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag))) {
-                    atomicCAS(error_word, 0, kErrDequantWait);
-                    break;
-                }
-                emit_stage(raw, stage);
-                if (++stage == kStages) {
-                    stage = 0;
-                    phase ^= 1u;
+                if (q + 1 < total_q) {
+                    fetch_block(q + 1);
                 }
             }
+            const int ss = q % num_ss;
+            const int steps_here = min(2, num_kb - 2 * ss);
+            const int idx_e = kcount;
+            const int idx_o = kcount + 1;
+            const int stage_e = idx_e % kStages;
+            const int stage_o = idx_o % kStages;
+            // Decode BEFORE asking for the ring slots: the wait below then only gates four shared
+            // stores, which keeps the slot's turnaround (free -> refilled) short.
+            const uint32_t dm = raw[0];
+            const __half2 d2 = __half2half2(__ushort_as_half(static_cast<uint16_t>(dm & 0xFFFFu)));
+            const __half2 m2 = __half2half2(__ushort_as_half(static_cast<uint16_t>(dm >> 16)));
+            uint4 lo0, hi0, lo1, hi1;
+            dequant_word_pair(raw[1], raw[2], d2, m2, lo0, hi0);  // k 0..7 and 16..23 of the block
+            dequant_word_pair(raw[3], raw[4], d2, m2, lo1, hi1);  // k 8..15 and 24..31
+            if (!dead) {
+                bool ok = mbar_wait_warp(&empty_bar[stage_e], (static_cast<uint32_t>(idx_e / kStages) & 1u) ^ 1u, abort_flag);
+                if (steps_here == 2) {
+                    ok = mbar_wait_warp(&empty_bar[stage_o], (static_cast<uint32_t>(idx_o / kStages) & 1u) ^ 1u, abort_flag) && ok;
+                }
+                if (!ok) {
+                    atomicCAS(error_word, 0, kErrDequantWait);
+                    dead = true;
+                }
+            }
+            if (!dead) {
+                if (parity < steps_here) {
+                    const int stage = parity == 0 ? stage_e : stage_o;
+                    uint8_t* b_row = stage_base + stage * Cfg::kStageBytes + Cfg::kATileBytes + r * 128;
+                    // 16-byte chunk ch of the row lives at chunk (ch ^ (row & 7)): the 128-byte swizzle.
+                    *reinterpret_cast<uint4*>(b_row + (((4 * jblk + 0) ^ sw) << 4)) = lo0;
+                    *reinterpret_cast<uint4*>(b_row + (((4 * jblk + 1) ^ sw) << 4)) = lo1;
+                    *reinterpret_cast<uint4*>(b_row + (((4 * jblk + 2) ^ sw) << 4)) = hi0;
+                    *reinterpret_cast<uint4*>(b_row + (((4 * jblk + 3) ^ sw) << 4)) = hi1;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&b_full_bar[stage_e]);
+                    if (steps_here == 2) {
+                        mbar_arrive(&b_full_bar[stage_o]);
+                    }
+                }
+            }
+            kcount += steps_here;
         }
     }
 
@@ -522,12 +518,13 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
 }
 
-template <int BN, bool OUT_F16, bool RAW_TMA>
-int launch_variant(const nnb200_q4_1_args& q, const CUtensorMap& map_a, const CUtensorMap& map_w, const FpEpilogue& ep,
-                   const DeviceInfo& dev, cudaStream_t stream)
+template <bool OUT_F16, bool COOP, int MH>
+int launch_variant(const nnb200_q4_1_args& q, const CUtensorMap& map_a, const FpEpilogue& ep, const DeviceInfo& dev,
+                   cudaStream_t stream)
 {
-    using Cfg = Q4Config<BN, RAW_TMA>;
-    auto kernel = q4_1_gemm_umma_kernel<BN, OUT_F16, RAW_TMA>;
+    using Cfg = Q4Config<COOP, MH>;
+    constexpr int kBlockM = Cfg::kBlockM;
+    auto kernel = q4_1_gemm_umma_kernel<OUT_F16, COOP, MH>;
     static std::once_flag once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
     std::call_once(once[dev.device], [&] {
@@ -538,7 +535,7 @@ int launch_variant(const nnb200_q4_1_args& q, const CUtensorMap& map_a, const CU
         return NNB200_INTERNAL;
     }
     const int m = static_cast<int>(q.m), n = static_cast<int>(q.n), k = static_cast<int>(q.k);
-    const int num_tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BN - 1) / BN);
+    const int num_tiles = ((m + kBlockM - 1) / kBlockM) * ((n + kTileN - 1) / kTileN);
     const int grid = num_tiles < dev.sm_count ? num_tiles : dev.sm_count;
     const int elem = OUT_F16 ? 2 : 4;
     const int vec_ok = ((reinterpret_cast<uintptr_t>(q.out) & 15u) == 0 &&
@@ -546,8 +543,8 @@ int launch_variant(const nnb200_q4_1_args& q, const CUtensorMap& map_a, const CU
                            ? 1
                            : 0;
     kernel<<<grid, Cfg::kNumThreads, Cfg::kSmemBytes, stream>>>(
-        map_a, map_w, static_cast<const uint8_t*>(q.w_blocks), q.ldw_blocks, q.out, q.ldc, m, n, k, ep,
-        umma_idesc(1, 0, 0, kBlockM, BN), vec_ok, dev.error_word);
+        map_a, static_cast<const uint8_t*>(q.w_blocks), q.ldw_blocks, q.out, q.ldc, m, n, k, ep,
+        umma_idesc(1, 0, 0, kHalfM, kTileN), vec_ok, dev.error_word);
     note_launch();
     return cuda_status(cudaGetLastError());
 }
@@ -573,32 +570,27 @@ int launch_q4_1_gemm_umma(const nnb200_q4_1_args& q, const DeviceInfo& dev, cuda
     ep.min_clip = q.min_clip;
     ep.max_clip = q.max_clip;
 
+    // Tile shape.  Tall problems stack two 128-row activation halves over one 128-channel
+    // weight tile (256 x 128): every dequantised weight then feeds twice the math.  Otherwise
+    // 128 x 128.
+    const int64_t tiles_tall = ((q.m + 255) / 256) * ((q.n + kTileN - 1) / kTileN);
+    const bool tall = q.m >= 256 && tiles_tall >= dev.sm_count;
+    const int block_m = tall ? 256 : 128;
+
     CUtensorMap map_a;
     if (!make_tma_2d(&map_a, q.a, 2, static_cast<uint64_t>(q.k), static_cast<uint64_t>(q.m),
-                     static_cast<uint64_t>(q.lda) * 2, kBlockK, kBlockM)) {
+                     static_cast<uint64_t>(q.lda) * 2, kBlockK, static_cast<uint32_t>(block_m))) {
         return NNB200_INTERNAL;
     }
-    const int num_m = static_cast<int>((q.m + kBlockM - 1) / kBlockM);
-    const bool wide = static_cast<int64_t>(num_m) * ((q.n + 255) / 256) >= dev.sm_count;
-    // Raw blocks by TMA when W's rows are addressable as 16-byte aligned runs of 32-bit words.
-    const bool raw_tma = (reinterpret_cast<uintptr_t>(q.w_blocks) & 15u) == 0 && (q.ldw_blocks % 4) == 0;
-    CUtensorMap map_w;
-    std::memset(&map_w, 0, sizeof(map_w));
-    if (raw_tma) {
-        const int64_t nblk = (q.k + kQ4BlockElems - 1) / kQ4BlockElems;
-        if (!make_tma_2d(&map_w, q.w_blocks, 4, static_cast<uint64_t>(nblk * kQ4BlockWords), static_cast<uint64_t>(q.n),
-                         static_cast<uint64_t>(q.ldw_blocks) * kQ4BlockBytes, kRawRowBytes / 4, wide ? 256u : 128u,
-                         /*swizzle128=*/false)) {
-            return NNB200_INTERNAL;
-        }
+    // 16-byte cooperative loads of the raw stream need 16-byte aligned rows.
+    const bool coop = (reinterpret_cast<uintptr_t>(q.w_blocks) & 15u) == 0 && (q.ldw_blocks % 4) == 0;
+#define NNB200_Q4_LAUNCH(F16V, MHV)                                                   \
+    (coop ? launch_variant<F16V, true, MHV>(q, map_a, ep, dev, stream)                \
+          : launch_variant<F16V, false, MHV>(q, map_a, ep, dev, stream))
+    if (tall) {
+        return q.out_f16 ? NNB200_Q4_LAUNCH(true, 2) : NNB200_Q4_LAUNCH(false, 2);
     }
-#define NNB200_Q4_LAUNCH(BNV, F16V)                                                              \
-    (raw_tma ? launch_variant<BNV, F16V, true>(q, map_a, map_w, ep, dev, stream)                 \
-             : launch_variant<BNV, F16V, false>(q, map_a, map_w, ep, dev, stream))
-    if (wide) {
-        return q.out_f16 ? NNB200_Q4_LAUNCH(256, true) : NNB200_Q4_LAUNCH(256, false);
-    }
-    return q.out_f16 ? NNB200_Q4_LAUNCH(128, true) : NNB200_Q4_LAUNCH(128, false);
+    return q.out_f16 ? NNB200_Q4_LAUNCH(true, 1) : NNB200_Q4_LAUNCH(false, 1);
 #undef NNB200_Q4_LAUNCH
 }
 

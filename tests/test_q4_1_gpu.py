@@ -95,7 +95,8 @@ def test_config3_gemv(cuda_device, nnb200_lib, m, engine):
 
 
 @pytest.mark.parametrize("shape", [(128, 128, 64), (128, 256, 256), (130, 300, 512), (64, 1000, 160),
-                                   (300, 260, 1000), (2048, 1024, 512)])
+                                   (300, 260, 1000), (2048, 1024, 512),
+                                   (1024, 4864, 256), (1000, 4810, 320), (520, 9500, 96)])  # 256-row tiles
 @pytest.mark.parametrize("out_dtype", ["f16", "f32"])
 def test_gemm_umma_shapes(cuda_device, nnb200_lib, shape, out_dtype):
     m, n, k = shape
