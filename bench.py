@@ -324,6 +324,10 @@ def main():
     # Every step copies its activations from pinned host memory, runs the layer and reads the
     # full result back.  Copies and compute run on three streams over two sets of device/host
     # buffers, so step i's read-back overlaps step i+1's upload and GEMM (PCIe is full duplex).
+    # At N > 1 rank 0 uploads the activations and broadcasts them over NVLink (the host link is
+    # shared by all GPUs of the box), and every rank reads back only the output columns it
+    # produced; together the ranks return the whole result once.
+    col_lo, col_hi = (0, N) if world == 1 else (layer.col0, layer.col0 + layer.n_per)
     h2d = a_host.numel()
     d2h = M * N
     s_in, s_run, s_back = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
@@ -338,17 +342,20 @@ def main():
         b = i & 1
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_run[b])          # the GEMM that last read this activation buffer
-            a_dev[b].copy_(a_host, non_blocking=True)
+            if rank == 0:
+                a_dev[b].copy_(a_host, non_blocking=True)
             ev_in[b].record()
         with torch.cuda.stream(s_run):
             s_run.wait_event(ev_in[b])
             s_run.wait_event(ev_back[b])        # the read-back that last used this output buffer
+            if world > 1:
+                dist.broadcast(a_dev[b], src=0)  # same stream as the layer's collectives: one communicator
             # Another rank's previous read-back of this buffer may still be running: order the ranks first.
             layer.forward(a_dev[b], out_dev[b], wait_for_readers=True)
             ev_run[b].record()
         with torch.cuda.stream(s_back):
             s_back.wait_event(ev_run[b])
-            out_hosts[b].copy_(out_dev[b], non_blocking=True)
+            out_hosts[b][:, col_lo:col_hi].copy_(out_dev[b][:, col_lo:col_hi], non_blocking=True)
             ev_back[b].record()
 
     for i in range(4):
@@ -365,7 +372,7 @@ def main():
     barrier()
     e2e_ms = max_over_ranks(t0.elapsed_time(t1) / e2e_steps)
     e2e_value = total_ops / (e2e_ms * 1e-3) / 1e12
-    e2e_check = bool(torch.equal(out_hosts[0], out_hosts[1]))
+    e2e_check = bool(torch.equal(out_hosts[0][:, col_lo:col_hi], out_hosts[1][:, col_lo:col_hi]))
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM) ----
     int8_peak = 2.0 * peaks["bf16_tflops"]
@@ -406,7 +413,9 @@ def main():
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "results_identical_across_buffers": e2e_check,
-                    "method": "3 streams, double-buffered: H2D of A, layer, D2H of the full output every step"},
+                    "method": "3 streams, double-buffered: H2D of A (rank 0, then NVLink broadcast at N > 1), the "
+                              "layer, D2H of each rank's own N/g output columns, every step; bytes are "
+                              "totals over the ranks"},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                          "frac": achieved / int8_peak, "traffic": traffic,

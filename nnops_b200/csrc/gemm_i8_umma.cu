@@ -14,10 +14,11 @@
 //     registers, so the epilogue of tile i overlaps the main loop of tile i+1.
 //
 // Sharded form (template flag PEERS): the epilogue of an 8-bit destination stages 32 rows x 128
-// columns per warp in shared memory and writes every 4 x 128-byte row group to this GPU's
-// output AND to the same window of each peer GPU's output with plain 16-byte stores (peer
-// pointers over NVLink) -- the all-gather is fused into the GEMM's write-back, tile by tile,
-// in contiguous 128-byte segments.  Loads never touch peer memory.
+// columns per warp in shared memory (128-byte swizzle) and hands each such tile to TMA, once per
+// destination: this GPU's output and the same window of every peer GPU's output (peer memory
+// over NVLink).  The all-gather is thereby fused into the GEMM's write-back, tile by tile, as
+// asynchronous bulk stores; the epilogue warps only wait for a staging buffer to be read out.
+// Loads never touch peer memory.
 //
 // Both operands are already K-major in memory ([M,K] and [N,K]), which is the layout the
 // UMMA shared-memory descriptors want, so no transposes or repacking happen anywhere.
@@ -26,6 +27,8 @@
 
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "internal.cuh"
@@ -38,23 +41,28 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockKBytes = 128;  // one 128-byte swizzle row of K per stage
 constexpr int kUmmaK = 32;         // K per tcgen05.mma for 8-bit operands
-constexpr int kGroupM = 16;        // m-blocks per raster group
 constexpr int kNumThreads = 192;   // TMA warp, MMA warp, 4 epilogue warps
 constexpr int kEpilogueThreads = 128;
 
-template <int BN>
+// TMA descriptors of the output windows the sharded form writes: [0] this GPU's, then the peers'.
+struct alignas(64) PeerMaps {
+    CUtensorMap m[8];
+};
+
+template <int BN, bool PEERS = false>
 struct TileConfig {
     static constexpr int kATileBytes = kBlockM * kBlockKBytes;
     static constexpr int kBTileBytes = BN * kBlockKBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     // Ring depth: as many stages as fit beside the epilogue staging in ~200 KB.
-    static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int kStages = PEERS ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : (BN == 128 ? 6 : 8));
     static constexpr int kTmemCols = 2 * BN;  // two accumulators; 128..512, a power of two
     static constexpr int kColParamBytes = 4 * 4 * BN * 4;  // 4 epilogue warps x {scale, bias, r_w, zp_w} x BN x 4 B
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
-    static constexpr int kPeerStageBytes = 4 * 32 * 128;  // sharded form: 32 rows x 128 B per epilogue warp
-    static constexpr int kSmemBytes = 1024 /*alignment slack*/ + kStages * kStageBytes + kColParamBytes + kBarrierBytes;
-    static constexpr int kSmemBytesPeers = kSmemBytes + kPeerStageBytes;
+    // Sharded form: two staging tiles of 32 rows x 128 B per epilogue warp (one being filled, one being stored).
+    static constexpr int kPeerStageBytes = PEERS ? 4 * 2 * 32 * 128 : 0;
+    static constexpr int kSmemBytes =
+        1024 /*alignment slack*/ + kStages * kStageBytes + kPeerStageBytes + kColParamBytes + kBarrierBytes;
 };
 
 struct TileCoord {
@@ -62,12 +70,15 @@ struct TileCoord {
     int n_blk;
 };
 
-__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n)
+// Tiles are walked m-fastest inside groups of `group_m` m-blocks, groups n-fastest: the CTAs of
+// one wave then share a band of A (kept in L2 for the whole pass over N) while W streams by once
+// per group.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int group_m)
 {
-    const int group_size = kGroupM * num_n;
+    const int group_size = group_m * num_n;
     const int group = tile / group_size;
-    const int first_m = group * kGroupM;
-    const int gm = min(num_m - first_m, kGroupM);
+    const int first_m = group * group_m;
+    const int gm = min(num_m - first_m, group_m);
     const int in_group = tile - group * group_size;
     TileCoord c;
     c.m_blk = first_m + in_group % gm;
@@ -199,10 +210,11 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
 template <int BN, int KIND, bool PEERS>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const I8Epilogue ep, const int m_total, const int n_total, const int k_total,
-                    const uint32_t idesc, const int vec_ok, int32_t* error_word)
+                    const __grid_constant__ PeerMaps peer_maps, const I8Epilogue ep, const int m_total,
+                    const int n_total, const int k_total, const uint32_t idesc, const int vec_ok, const int group_m,
+                    int32_t* error_word)
 {
-    using Cfg = TileConfig<BN>;
+    using Cfg = TileConfig<BN, PEERS>;
     constexpr int kStages = Cfg::kStages;
 
     extern __shared__ uint8_t smem_raw[];
@@ -210,14 +222,14 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_base = smem;
     // Per-column epilogue terms, one private copy per epilogue warp (no cross-warp barrier).
-    int32_t* col_params = reinterpret_cast<int32_t*>(smem + kStages * Cfg::kStageBytes);
+    uint8_t* peer_stage = smem + kStages * Cfg::kStageBytes;  // 1024-byte aligned (PEERS only)
+    int32_t* col_params = reinterpret_cast<int32_t*>(peer_stage + Cfg::kPeerStageBytes);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(col_params + 4 * 4 * BN);
     uint64_t* empty_bar = full_bar + kStages;
     uint64_t* acc_full_bar = empty_bar + kStages;
     uint64_t* acc_empty_bar = acc_full_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    uint8_t* peer_stage = reinterpret_cast<uint8_t*>(tmem_slot + 4);  // 16-byte aligned; used when PEERS
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -261,7 +273,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t armed_phase = 0;  // bit s: parity of the phase slot s was last armed in
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const TileCoord tc = tile_coord(tile, num_m, num_n);
+                const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         atomicCAS(error_word, 0, kErrProducerWait);
@@ -352,9 +364,11 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int32_t* cb = reinterpret_cast<int32_t*>(cs) + BN;
         int32_t* cr = cb + BN;
         int32_t* cz = cr + BN;
+        int stage_turn = 0;  // sharded form: which of the warp's two staging tiles is next
+        (void)stage_turn;
         int local_tile = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
-            const TileCoord tc = tile_coord(tile, num_m, num_n);
+            const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
             const int acc = local_tile & 1;
             const uint32_t acc_phase = (local_tile >> 1) & 1u;
             const int n_base = tc.n_blk * BN;
@@ -406,14 +420,23 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const float zpf = static_cast<float>(ep.out_zp);
                 const float lo = (KIND == NNB200_OUT_S8 ? -128.0f : 0.0f) - zpf;
                 const float hi = (KIND == NNB200_OUT_S8 ? 127.0f : 255.0f) - zpf;
-                uint8_t* stage = peer_stage + (warp - 2) * (32 * 128);
-                const int64_t row0 = static_cast<int64_t>(tc.m_blk) * kBlockM + quarter * 32;
+                const int row0 = tc.m_blk * kBlockM + quarter * 32;
+                const int num_dst = 1 + ep.num_peers;
 #pragma unroll 1
                 for (int c4 = 0; c4 < BN / 128; ++c4) {
                     const int n128 = n_base + c4 * 128;
                     if (n128 >= n_total) {
                         break;  // uniform across the warp
                     }
+                    // Two staging tiles per warp, used alternately: before refilling one, its
+                    // previous bulk stores must have finished READING it (they may still be in flight
+                    // on the wire).  Only lane 0 issues bulk stores, so only lane 0 has groups to wait on.
+                    uint8_t* stage = peer_stage + ((warp - 2) * 2 + (stage_turn & 1)) * (32 * 128);
+                    ++stage_turn;
+                    if (lane == 0) {
+                        bulk_wait_group_read<1>();
+                    }
+                    __syncwarp();
 #pragma unroll 1
                     for (int cc = 0; cc < 4; ++cc) {
                         const int c = c4 * 4 + cc;
@@ -434,30 +457,21 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             }
                             packed[j / 4] = word;
                         }
-                        // This lane's row: 16-byte pieces 2cc and 2cc+1, XOR-swizzled by the row.
+                        // This lane's row in the 128-byte-swizzled tile: 16-byte pieces 2cc and 2cc+1.
                         uint4* srow = reinterpret_cast<uint4*>(stage + lane * 128);
                         srow[(2 * cc) ^ (lane & 7)] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                         srow[(2 * cc + 1) ^ (lane & 7)] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                     }
+                    fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA engine
                     __syncwarp();
-                    // Lane -> piece (lane % 8) of rows (lane / 8) + 4j: each store instruction
-                    // covers four rows of 128 contiguous bytes.
-                    const int piece = lane & 7;
-                    const int col = n128 + piece * 16;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int r = (lane >> 3) + 4 * j;
-                        const uint4 data = *reinterpret_cast<const uint4*>(stage + r * 128 + ((piece ^ (r & 7)) << 4));
-                        const int64_t grow = row0 + r;
-                        if (grow < m_total && col < n_total) {
-                            const int64_t off = grow * ep.ldc + col;
-                            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(ep.out) + off) = data;
-                            for (int pi = 0; pi < ep.num_peers; ++pi) {
-                                *reinterpret_cast<uint4*>(static_cast<uint8_t*>(ep.peer_out[pi]) + off) = data;
-                            }
+                    if (lane == 0) {
+                        // One bulk store per destination; rows past M and columns past N are clipped
+                        // by the descriptor.
+                        for (int d = 0; d < num_dst; ++d) {
+                            tma_store_2d(&peer_maps.m[d], stage, n128, row0);
                         }
+                        bulk_commit_group();
                     }
-                    __syncwarp();  // staging tile free for the next 128 columns
                 }
             } else {
 #pragma unroll 1
@@ -480,6 +494,12 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 mbar_arrive(&acc_empty_bar[acc]);
             }
         }
+        if constexpr (PEERS) {
+            if (lane == 0) {
+                bulk_wait_group<0>();  // every bulk store of this warp has completed before the CTA exits
+            }
+            __syncwarp();
+        }
     }
 
     // ---------------- teardown ----------------
@@ -495,9 +515,21 @@ template <int BN, int KIND, bool PEERS>
 int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m, int n, int k,
                    uint32_t idesc, int vec_ok, const DeviceInfo& dev, cudaStream_t stream)
 {
-    using Cfg = TileConfig<BN>;
+    using Cfg = TileConfig<BN, PEERS>;
     auto kernel = gemm_i8_umma_kernel<BN, KIND, PEERS>;
-    constexpr int kSmem = PEERS ? Cfg::kSmemBytesPeers : Cfg::kSmemBytes;
+    constexpr int kSmem = Cfg::kSmemBytes;
+    PeerMaps maps;
+    std::memset(&maps, 0, sizeof(maps));
+    if constexpr (PEERS) {
+        // Output windows as 2-D byte tensors [m][n] with the caller's pitch; 128 x 32 boxes.
+        for (int d = 0; d <= ep.num_peers; ++d) {
+            const void* base = d == 0 ? ep.out : ep.peer_out[d - 1];
+            if (!make_tma_2d(&maps.m[d], base, 1, static_cast<uint64_t>(n), static_cast<uint64_t>(m),
+                             static_cast<uint64_t>(ep.ldc), 128, 32)) {
+                return NNB200_INTERNAL;
+            }
+        }
+    }
     static std::once_flag once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
     std::call_once(once[dev.device], [&] {
@@ -508,7 +540,15 @@ int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8E
     }
     const int num_tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BN - 1) / BN);
     const int grid = num_tiles < dev.sm_count ? num_tiles : dev.sm_count;
-    kernel<<<grid, kNumThreads, kSmem, stream>>>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev.error_word);
+    // Raster group: as many m-blocks as keep the group's band of A within about a third of L2
+    // (126 MB on B200), so that W is read from DRAM once per group.
+    int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(kBlockM) * (k > 0 ? k : 1)));
+    group_m = group_m < 4 ? 4 : group_m;
+    if (const char* e = getenv("NNB200_GROUP_M")) {
+        group_m = atoi(e) > 0 ? atoi(e) : group_m;
+    }
+    kernel<<<grid, kNumThreads, kSmem, stream>>>(map_a, map_w, maps, ep, m, n, k, idesc, vec_ok, group_m,
+                                                 dev.error_word);
     note_launch();
     return cuda_status(cudaGetLastError());
 }
