@@ -1,0 +1,91 @@
+"""Generate the golden fixtures of this directory from the compiled reference CPU route.
+
+    python tests/golden/make_golden.py        (needs oracle/_ref, i.e. the nnops source tree at build time)
+
+Each .npz holds seeded inputs, the reference's output and a JSON `meta` describing the call.
+The reference is driven through its public operator API (Linear / MatMul on Backend::CPU, via
+oracle/ref_shim.cpp).  tests/test_oracle.py checks the C restatement against these files, and
+tests/test_golden_gpu.py checks the CUDA path against them, so parity with the reference stays
+pinned on machines where the reference itself cannot be built.
+"""
+import json
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent.parent
+sys.path.insert(0, str(ROOT))
+import oracle  # noqa: E402
+from nnops_b200 import synth  # noqa: E402
+
+HERE = Path(__file__).resolve().parent
+
+
+def save(name, meta, **arrays):
+    np.savez_compressed(HERE / f"{name}.npz", meta=np.array(json.dumps(meta)), **arrays)
+    print("wrote", name, {k: v.shape for k, v in arrays.items()})
+
+
+def int8_case(name, m, n, k, out_kind, *, seed, relu=False, a_unsigned=False, per_token=False, per_channel=True,
+              zero_points=False, out_scale=1.0, out_zp=0, a_transposed=False, w_kn=False):
+    rng = np.random.default_rng(seed)
+    a = rng.integers(0, 256, (m, k), dtype=np.uint8) if a_unsigned else rng.integers(-127, 128, (m, k), dtype=np.int8)
+    w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    int_out = out_kind in ("s32", "s8", "u8")
+    arrays, scalars, kw = {}, {}, []
+
+    def put(key, value):
+        kw.append(key)
+        if np.isscalar(value):
+            scalars[key] = value
+        else:
+            arrays[key] = value
+
+    put("scale_a", rng.uniform(0.01, 0.03, m).astype(np.float32) if per_token else 0.02)
+    put("scale_w", rng.uniform(0.001, 0.02, n).astype(np.float32) if per_channel else 0.01)
+    if zero_points:
+        put("zp_a", rng.integers(-9, 10, m).astype(np.int32) if per_token else (128 if a_unsigned else 3))
+        put("zp_w", rng.integers(-9, 10, n).astype(np.int32) if per_channel else -2)
+    put("bias", rng.integers(-1000, 1001, n).astype(np.int32) if int_out
+        else (rng.normal(size=n) * 3).astype(np.float32 if out_kind == "f32" else np.float16))
+    put("out_scale", float(out_scale))
+    put("out_zp", int(out_zp))
+    call = {key: (arrays[key] if key in arrays else scalars[key]) for key in kw}
+    a_stored = np.ascontiguousarray(a.T) if a_transposed else a        # [K,M] storage for transpose_a
+    w_stored = np.ascontiguousarray(w.T) if w_kn else w                # [K,N] storage without transpose_b
+    a_view = a_stored.T if a_transposed else a_stored
+    w_view = w_stored.T if w_kn else w_stored
+    out = oracle.gemm_i8(a_view, w_view, out_kind=out_kind, relu=relu, impl="ref", **call)
+    meta = dict(op="gemm_i8", out_kind=out_kind, relu=relu, kw=kw, scalars=scalars, a_transposed=a_transposed, w_kn=w_kn)
+    save(name, meta, a=a_stored, w=w_stored, out=out, **arrays)
+
+
+def q4_case(name, m, n, k, dtype, *, seed):
+    rng = np.random.default_rng(seed)
+    wb = synth.q4_1_weights(rng, n, k)
+    a = rng.standard_normal((m, k)).astype(np.float16 if dtype == "f16" else np.float32)
+    out = oracle.q4_1_matmul(a, wb, k, out_dtype=dtype, impl="ref")
+    # f16: the reference's own route carries f16 round trips of partial sums at large M; 1e-2.
+    save(name, dict(op="q4_1", k=k, out_dtype=dtype, rtol=1e-2 if dtype == "f16" else 2e-3), a=a, w_blocks=wb, out=out)
+
+
+if __name__ == "__main__":
+    if not oracle.have_ref():
+        raise SystemExit("the compiled reference (oracle/_ref) is not available on this machine")
+    int8_case("i8_s32_bias", 128, 192, 256, "s32", seed=1, per_channel=False)
+    int8_case("i8_s8_relu_per_channel", 160, 272, 512, "s8", seed=2, relu=True, out_scale=1.6)
+    int8_case("i8_s8_saturating", 64, 128, 1024, "s8", seed=3, relu=True, out_scale=0.05)
+    int8_case("i8_u8_per_token_zero_points", 77, 130, 272, "u8", seed=4, per_token=True, zero_points=True,
+              out_scale=2.3, out_zp=7)
+    int8_case("i8_u8_activations_s32", 50, 96, 160, "s32", seed=5, a_unsigned=True, zero_points=True, per_token=True)
+    int8_case("i8_f32_dequant", 96, 144, 320, "f32", seed=6, per_token=True, relu=True)
+    int8_case("i8_f16_dequant_zero_points", 40, 100, 256, "f16", seed=7, per_token=True, zero_points=True)
+    int8_case("i8_transposed_poses", 70, 90, 200, "s8", seed=8, out_scale=40.0, per_channel=False, a_transposed=True,
+              w_kn=True)
+    int8_case("i8_decode_m4", 4, 520, 1024, "s8", seed=9, relu=True, out_scale=1.1)
+    q4_case("q4_1_gemv_m1_f32", 1, 256, 4096, "f32", seed=10)
+    q4_case("q4_1_gemv_m8_f32", 8, 203, 1000, "f32", seed=11)
+    q4_case("q4_1_small_m_f16", 4, 128, 1024, "f16", seed=12)
+    q4_case("q4_1_gemm_f32", 96, 160, 512, "f32", seed=13)
+    q4_case("q4_1_gemm_f16", 160, 192, 512, "f16", seed=14)
