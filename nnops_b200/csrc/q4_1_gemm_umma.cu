@@ -378,39 +378,50 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
         const int total_q = my_tiles * num_ss;        // super-steps this CTA walks through
         const int64_t pitch = ldw_blocks * kQ4BlockBytes;
 
-        // First weight row of the tile that super-step q belongs to.
-        auto tile_row0 = [&](int q) {
-            const int tile = static_cast<int>(blockIdx.x) + (q / num_ss) * static_cast<int>(gridDim.x);
+        // First weight row of local tile t.
+        auto tile_row0 = [&](int t) {
+            const int tile = static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x);
             return static_cast<int64_t>(tile_coord(tile, num_m, num_n).n_blk) * BN;
         };
 
         // COOP: the raw tile of a super-step is 128 rows x 80 B = 640 pieces of 16 B; thread dt
         // copies piece dt and (dt < 128) piece 512 + dt with cp.async, kRawAhead super-steps ahead,
         // into a ring of kRawBufs tiles.  Pieces past N or past the row end arrive as zeros.
-        auto issue_piece = [&](int q, int piece) {
-            const int row = piece / 5;
-            const int j = piece - row * 5;
-            const int64_t n = tile_row0(q) + row;
-            const int64_t byte0 = static_cast<int64_t>(q % num_ss) * kRawRowBytes + j * 16;
-            const int64_t row_bytes = static_cast<int64_t>(nblk) * kQ4BlockBytes;
-            int64_t valid = n < n_total ? row_bytes - byte0 : 0;
-            valid = valid < 0 ? 0 : (valid > 16 ? 16 : valid);
-            const uint8_t* src = valid > 0 ? w + n * pitch + byte0 : w;
-            cp_async_16(raw_base + (q % kRawBufs) * Cfg::kRawBufBytes + piece * 16, src, static_cast<uint32_t>(valid));
-        };
-        auto issue_super_step = [&](int q) {
-            if (q < total_q) {
-                issue_piece(q, dt);
-                if (dt < 128) {
-                    issue_piece(q, 512 + dt);
+        // Everything that does not change from one super-step to the next is computed here once.
+        const int64_t row_bytes = static_cast<int64_t>(nblk) * kQ4BlockBytes;
+        const int p_row[2] = {dt / 5, (512 + dt) / 5};
+        const int p_off[2] = {(dt % 5) * 16, ((512 + dt) % 5) * 16};
+        const int p_count = dt < 128 ? 2 : 1;
+        int pf_t = 0, pf_ss = 0, pf_buf = 0;        // prefetch cursor: local tile, super-step, ring slot
+        int64_t pf_row0 = my_tiles > 0 ? tile_row0(0) : 0;
+        auto issue_super_step = [&]() {
+            if (pf_t < my_tiles) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    if (i < p_count) {
+                        const int64_t n = pf_row0 + p_row[i];
+                        const int64_t byte0 = static_cast<int64_t>(pf_ss) * kRawRowBytes + p_off[i];
+                        int64_t valid = n < n_total ? row_bytes - byte0 : 0;
+                        valid = valid < 0 ? 0 : (valid > 16 ? 16 : valid);
+                        const uint8_t* src = valid > 0 ? w + n * pitch + byte0 : w;
+                        cp_async_16(raw_base + pf_buf * Cfg::kRawBufBytes + (i == 0 ? dt : 512 + dt) * 16, src,
+                                    static_cast<uint32_t>(valid));
+                    }
+                }
+                if (++pf_ss == num_ss) {
+                    pf_ss = 0;
+                    if (++pf_t < my_tiles) {
+                        pf_row0 = tile_row0(pf_t);
+                    }
                 }
             }
+            pf_buf = pf_buf + 1 == kRawBufs ? 0 : pf_buf + 1;
             cp_async_commit();  // one group per super-step, empty ones included, so the counts line up
         };
         // Plain path: this lane's own block, five 32-bit loads.
         uint32_t next[5] = {0u, 0u, 0u, 0u, 0u};
         auto fetch_block = [&](int q) {
-            const int64_t n = tile_row0(q) + r;
+            const int64_t n = tile_row0(q / num_ss) + r;
             const int b = (q % num_ss) * 4 + c;
             if (n < n_total && b < nblk) {
                 const uint32_t* src = reinterpret_cast<const uint32_t*>(w + n * pitch + static_cast<int64_t>(b) * kQ4BlockBytes);
@@ -429,7 +440,7 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
         if (total_q > 0) {
             if constexpr (COOP) {
                 for (int q0 = 0; q0 < kRawAhead; ++q0) {
-                    issue_super_step(q0);
+                    issue_super_step();
                 }
             } else {
                 fetch_block(0);
@@ -437,17 +448,22 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
         }
         int kcount = 0;     // k-steps this CTA has gone through before the current super-step
         bool dead = false;  // a wait ran out: keep walking (the barriers below need every warp) but do nothing
+        int cur_buf = 0;    // ring slot of super-step q
+        int ss = 0;         // super-step inside the current tile
+        int stage_e = 0;    // ring stage of k-step `kcount`
+        uint32_t phase_e = 0;
         for (int q = 0; q < total_q; ++q) {
             uint32_t raw[5];
             if constexpr (COOP) {
-                uint8_t* buf = raw_base + (q % kRawBufs) * Cfg::kRawBufBytes;
+                uint8_t* buf = raw_base + cur_buf * Cfg::kRawBufBytes;
+                cur_buf = cur_buf + 1 == kRawBufs ? 0 : cur_buf + 1;
                 // Slot (q + kRawAhead) % kRawBufs was last read in super-step q - 1, which every warp
                 // finished before passing that step's barrier... except the readers still inside
                 // step q - 1 right now; the barrier below is what orders them, so the refill is
                 // issued after it.
                 cp_async_wait_group<kRawAhead - 1>();   // this thread's pieces of super-step q have landed
                 named_barrier_sync(1, kDequantThreads); // ... and everyone else's; step q - 1 is fully read
-                issue_super_step(q + kRawAhead);
+                issue_super_step();
                 const uint32_t* src = reinterpret_cast<const uint32_t*>(buf + r * kRawRowBytes) + c * kQ4BlockWords;
 #pragma unroll
                 for (int i = 0; i < 5; ++i) {
@@ -462,12 +478,12 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
                     fetch_block(q + 1);
                 }
             }
-            const int ss = q % num_ss;
             const int steps_here = min(2, num_kb - 2 * ss);
-            const int idx_e = kcount;
-            const int idx_o = kcount + 1;
-            const int stage_e = idx_e % kStages;
-            const int stage_o = idx_o % kStages;
+            if (++ss == num_ss) {
+                ss = 0;
+            }
+            const int stage_o = stage_e + 1 == kStages ? 0 : stage_e + 1;
+            const uint32_t phase_o = stage_e + 1 == kStages ? phase_e ^ 1u : phase_e;
             // Decode BEFORE asking for the ring slots: the wait below then only gates four shared
             // stores, which keeps the slot's turnaround (free -> refilled) short.
             const uint32_t dm = raw[0];
@@ -477,9 +493,9 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
             dequant_word_pair(raw[1], raw[2], d2, m2, lo0, hi0);  // k 0..7 and 16..23 of the block
             dequant_word_pair(raw[3], raw[4], d2, m2, lo1, hi1);  // k 8..15 and 24..31
             if (!dead) {
-                bool ok = mbar_wait_warp(&empty_bar[stage_e], (static_cast<uint32_t>(idx_e / kStages) & 1u) ^ 1u, abort_flag);
+                bool ok = mbar_wait_warp(&empty_bar[stage_e], phase_e ^ 1u, abort_flag);
                 if (steps_here == 2) {
-                    ok = mbar_wait_warp(&empty_bar[stage_o], (static_cast<uint32_t>(idx_o / kStages) & 1u) ^ 1u, abort_flag) && ok;
+                    ok = mbar_wait_warp(&empty_bar[stage_o], phase_o ^ 1u, abort_flag) && ok;
                 }
                 if (!ok) {
                     atomicCAS(error_word, 0, kErrDequantWait);
@@ -506,7 +522,14 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
                 }
             }
             kcount += steps_here;
+            for (int adv = 0; adv < steps_here; ++adv) {
+                if (++stage_e == kStages) {
+                    stage_e = 0;
+                    phase_e ^= 1u;
+                }
+            }
         }
+        (void)kcount;
     }
 
     // ---------------- teardown ----------------
