@@ -197,6 +197,34 @@ def secondary_q4_1(torch, dev, peaks):
     return out
 
 
+def secondary_i8_decode(torch, dev, peaks, w, sw, bias):
+    """The int8 layer's token-by-token twin: M = 1, 8, 16 activation rows against the bench's
+    own weight matrix (235 MB, larger than L2, so every call streams it from HBM)."""
+    from nnops_b200 import ops
+    out = {}
+    n, k = w.shape
+    for m in (1, 8, 16):
+        a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev)
+        o = torch.empty((m, n), dtype=torch.int8, device=dev)
+        kw = dict(out_kind="s8", out=o, bias=bias, relu=True, scale_a=0.02, scale_w=sw, out_scale=0.05)
+        engine = ops.gemm_i8_engine(a, w, o, **{x: y for x, y in kw.items() if x != "out"})
+        for _ in range(3):
+            ops.gemm_i8(a, w, **kw)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = 20
+        e0.record()
+        for _ in range(iters):
+            ops.gemm_i8(a, w, **kw)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / iters
+        nbytes = n * k + m * k + m * n + 8 * n
+        gbs = nbytes / us / 1e3
+        out[f"i8_decode_m{m}"] = {"gbs": gbs, "us_per_call": us, "bytes_per_call": nbytes, "engine": engine,
+                                  "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
+    return out
+
+
 def run_kernel_only(args):
     """Three launches of one kernel on seeded inputs and nothing else: the command the ncu
     captures under profiles/ are taken from (`--kernel-only i8|gemv|q4gemm --shape M N K`)."""
@@ -396,6 +424,7 @@ def main():
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_secondary:
         extra = secondary_q4_1(torch, dev, peaks)
+        extra.update(secondary_i8_decode(torch, dev, peaks, layer.w, layer.kw["scale_w"], layer.kw["bias"]))
         cpu_baseline = cpu_reference_run(1024, 5, 2)
         cpu_baseline = {k: cpu_baseline[k] for k in ("value", "unit", "cores", "kind", "sample")}
 

@@ -54,8 +54,9 @@ extern "C" {
 /* Engines, for nnb200_gemm_i8_args.force_engine and the *_engine_name queries. */
 #define NNB200_ENGINE_AUTO 0
 #define NNB200_ENGINE_UMMA 1    /* TMA + tcgen05.mma kind::i8, TMEM accumulators           */
-#define NNB200_ENGINE_NARROW 2  /* M <= 16 decode: bandwidth kernel, dp4a                   */
+#define NNB200_ENGINE_NARROW 2  /* M <= 16 decode, any K: one warp per channel, dp4a        */
 #define NNB200_ENGINE_GENERIC 3 /* any pose / alignment: SIMT tile, correctness tier        */
+#define NNB200_ENGINE_DECODE 4  /* M <= 16, K % 64 == 0: streaming loads + warp MMA        */
 
 /*
  * One int8 matmul call: out[b][m][n] = epilogue( sum_k A[b][m][k] * W[b][n][k] ).

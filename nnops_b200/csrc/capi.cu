@@ -155,6 +155,12 @@ int pick_i8_engine(const nnb200_gemm_i8_args* a, const I8Problem& p)
     if (a->force_engine == NNB200_ENGINE_UMMA) {
         return umma_i8_supported(p) ? NNB200_ENGINE_UMMA : NNB200_ENGINE_GENERIC;
     }
+    if (a->force_engine == NNB200_ENGINE_DECODE) {
+        return decode_i8_supported(p) ? NNB200_ENGINE_DECODE : NNB200_ENGINE_GENERIC;
+    }
+    if (a->num_peer_outs == 0 && decode_i8_supported(p)) {
+        return NNB200_ENGINE_DECODE;
+    }
     if (a->num_peer_outs == 0 && narrow_i8_supported(p)) {
         return NNB200_ENGINE_NARROW;
     }
@@ -283,6 +289,7 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
         switch (pick_i8_engine(a, p)) {
         case NNB200_ENGINE_UMMA: st = launch_gemm_i8_umma(p, ep, *dev, stream); break;
         case NNB200_ENGINE_NARROW: st = launch_gemm_i8_narrow(p, ep, *dev, stream); break;
+        case NNB200_ENGINE_DECODE: st = launch_gemm_i8_decode(p, ep, *dev, stream); break;
         default: st = launch_gemm_i8_generic(p, ep, *dev, stream); break;
         }
         if (st != NNB200_OK) {

@@ -56,6 +56,8 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
 int launch_gemm_i8_generic(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
 int launch_gemm_i8_narrow(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
 bool narrow_i8_supported(const I8Problem& p);
+int launch_gemm_i8_decode(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
+bool decode_i8_supported(const I8Problem& p);
 
 // R_a[m] = sum_k A[m][k] and R_w[n] = sum_k W[n][k] into int32 scratch.
 int launch_i8_sums(const I8Problem& p, int32_t* r_a, int32_t* r_w, cudaStream_t stream);

@@ -87,12 +87,25 @@ def test_fp_clip(cuda_device, nnb200_lib):
     _run_case(cuda_device, 40, 100, 256, out_kind="f32", per_channel=True, min_clip=-1.5, max_clip=2.5, engine="umma")
 
 
-@pytest.mark.parametrize("m", [1, 2, 3, 8, 16])
-def test_narrow_decode(cuda_device, nnb200_lib, m):
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 9, 16])
+def test_decode_engines(cuda_device, nnb200_lib, m):
+    """M <= 16: the streaming warp-MMA engine when K is a multiple of 64, the dp4a engine otherwise."""
     _run_case(cuda_device, m, 520, 1024, out_kind="s8", relu=True, per_channel=True, out_scale=1.1,
-              expect_engine="narrow", seed=m)
+              expect_engine="decode", seed=m)
+    _run_case(cuda_device, m, 520, 1024, out_kind="s8", relu=True, per_channel=True, out_scale=1.1,
+              engine="narrow", expect_engine="narrow", seed=m)
     _run_case(cuda_device, m, 130, 4096 + 16, out_kind="s32", a_unsigned=True, zero_points=True, per_token=True,
-              per_channel=True, engine="narrow", seed=m + 50)
+              per_channel=True, expect_engine="narrow", seed=m + 50)
+    # ragged channel count (n % 16 != 0), u8 activations with zero points, K with a partial unroll group
+    _run_case(cuda_device, m, 1003, 64 * 37, out_kind="s32", a_unsigned=True, zero_points=True, per_token=True,
+              per_channel=True, expect_engine="decode", seed=m + 70)
+    _run_case(cuda_device, m, 48, 64, out_kind="f16", per_channel=True, expect_engine="decode", seed=m + 90)
+
+
+@pytest.mark.parametrize("out_kind", ["s32", "s8", "u8", "f32", "f16"])
+def test_decode_destinations(cuda_device, nnb200_lib, out_kind):
+    _run_case(cuda_device, 5, 700, 4096, out_kind=out_kind, relu=True, per_token=True, per_channel=True,
+              out_scale=1.9, out_zp=0 if out_kind == "s32" else 4, expect_engine="decode", seed=21)
 
 
 def test_transposed_poses_use_generic(cuda_device, nnb200_lib):
