@@ -197,6 +197,30 @@ def secondary_q4_1(torch, dev, peaks):
     return out
 
 
+def graph_time_us(torch, fn, calls_per_graph: int = 10, replays: int = 10) -> float:
+    """Average device time of one ``fn()`` call: ``calls_per_graph`` calls captured in a CUDA
+    graph (so host-side launch cost does not pace the kernels), replayed between two events."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            for _ in range(calls_per_graph):
+                fn()
+    torch.cuda.synchronize()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (replays * calls_per_graph)
+
+
 def secondary_i8_decode(torch, dev, peaks, w, sw, bias):
     """The int8 layer's token-by-token twin: M = 1, 8, 16 activation rows against the bench's
     own weight matrix (235 MB, larger than L2, so every call streams it from HBM)."""
@@ -208,20 +232,39 @@ def secondary_i8_decode(torch, dev, peaks, w, sw, bias):
         o = torch.empty((m, n), dtype=torch.int8, device=dev)
         kw = dict(out_kind="s8", out=o, bias=bias, relu=True, scale_a=0.02, scale_w=sw, out_scale=0.05)
         engine = ops.gemm_i8_engine(a, w, o, **{x: y for x, y in kw.items() if x != "out"})
-        for _ in range(3):
-            ops.gemm_i8(a, w, **kw)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        iters = 20
-        e0.record()
-        for _ in range(iters):
-            ops.gemm_i8(a, w, **kw)
-        e1.record()
-        torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / iters
+        us = graph_time_us(torch, lambda: ops.gemm_i8(a, w, **kw))
         nbytes = n * k + m * k + m * n + 8 * n
         gbs = nbytes / us / 1e3
         out[f"i8_decode_m{m}"] = {"gbs": gbs, "us_per_call": us, "bytes_per_call": nbytes, "engine": engine,
                                   "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
+    return out
+
+
+def secondary_quant_linear(torch, dev, peaks):
+    """The elementwise steps either side of the int8 layer, on the bench's own tensors:
+    QuantizeLinear of the [4096, 8192] activations (per token; f32 and f16 sources) and
+    DequantizeLinear of the [4096, 28672] result (per tensor, to f16).  Pure streaming: bytes
+    read + written over time, against the measured copy bandwidth.  All tensors exceed L2."""
+    from nnops_b200 import ops
+    out = {}
+
+    def timed(fn, nbytes, key):
+        us = graph_time_us(torch, fn)
+        out[key] = {"gbs": nbytes / us / 1e3, "us_per_call": us, "bytes_per_call": nbytes,
+                    "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"]}
+
+    scale = torch.full((M,), 0.02, dtype=torch.float32, device=dev)
+    zp = torch.zeros(M, dtype=torch.int8, device=dev)
+    for name, dt, esz in (("f32", torch.float32, 4), ("f16", torch.float16, 2)):
+        x = torch.randn((M, K), dtype=dt, device=dev)
+        q = torch.empty((M, K), dtype=torch.int8, device=dev)
+        timed(lambda: ops.quantize_linear(x, scale, zp, out=q), M * K * (esz + 1), f"quantize_{name}_per_token")
+        del x
+    y = torch.randint(-128, 128, (M, N), dtype=torch.int8, device=dev)
+    f = torch.empty((M, N), dtype=torch.float16, device=dev)
+    s1 = torch.tensor([0.05], dtype=torch.float32, device=dev)
+    z1 = torch.zeros(1, dtype=torch.int8, device=dev)
+    timed(lambda: ops.dequantize_linear(y, s1, z1, out=f), M * N * 3, "dequantize_s8_to_f16_per_tensor")
     return out
 
 
@@ -424,6 +467,7 @@ def main():
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_secondary:
         extra = secondary_q4_1(torch, dev, peaks)
+        extra.update(secondary_quant_linear(torch, dev, peaks))
         extra.update(secondary_i8_decode(torch, dev, peaks, layer.w, layer.kw["scale_w"], layer.kw["bias"]))
         cpu_baseline = cpu_reference_run(1024, 5, 2)
         cpu_baseline = {k: cpu_baseline[k] for k in ("value", "unit", "cores", "kind", "sample")}

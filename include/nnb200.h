@@ -203,6 +203,34 @@ NNB200_API int nnb200_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int6
                        int32_t out_f16, int64_t ld_out, void* stream);
 
 /*
+ * QuantizeLinear / DequantizeLinear (reference operators include/nnops/ops/quant_linear.hpp:24-141;
+ * these two calls stand where the reference's CUDA entry points quantize_linear_cuda /
+ * dequantize_linear_cuda are Status::unsupported stubs, src/backend/cuda/not_implemented.cu:28-37;
+ * the arithmetic is the one of its CPU route, src/backend/cpu/quant_linear.cpp:80-262).
+ *
+ * The dense tensor is viewed as [outer][rows][inner]; scale[r] / zero_point[r] serve row r of
+ * every outer group: per tensor = [1][1][numel], per token = [1][numel/last][last], per channel
+ * (axis a) = [prod(shape[:a])][shape[a]][prod(shape[a+1:])].  x, y, scale and zero_point are
+ * device pointers; the floating side is f32 or f16, the integer side s8 or u8, the zero point
+ * s8 or u8 on its own flag.
+ *   quantize:   y = saturate(round_half_even(fma(x, 1/scale, zero_point)))
+ *   dequantize: y = (x - zero_point) * scale   (rounded as the reference's kernels round it)
+ */
+typedef struct nnb200_quant_linear_args {
+    const void* x;
+    void* y;
+    int64_t outer, rows, inner;
+    const float* scale;     /* [rows] */
+    const void* zero_point; /* [rows], s8 or u8 */
+    int32_t zp_unsigned;
+    int32_t float_f16;      /* floating side (x of quantize, y of dequantize) is f16, else f32 */
+    int32_t int_unsigned;   /* integer side (y of quantize, x of dequantize) is u8, else s8 */
+} nnb200_quant_linear_args;
+
+NNB200_API int nnb200_quantize_linear(const nnb200_quant_linear_args* args, void* stream);
+NNB200_API int nnb200_dequantize_linear(const nnb200_quant_linear_args* args, void* stream);
+
+/*
  * Column-sharded Linear, reassembly step: `gathered` holds `shards` dense slabs
  * [shards][m][row_bytes_per_shard] (what an all-gather of per-rank [m, n/shards] outputs
  * produces); writes the row-major [m][shards*row_bytes_per_shard] matrix with row pitch

@@ -1,6 +1,7 @@
 // Stand-alone mirror of the slice of the nnops operator API that the quantized-matmul path
 // uses: the boundary types (DataType, Status, QuantParams, Epilogue, TensorDesc, TensorView,
-// ComputeContext) and the two operators (Linear, MatMul).  Names, argument meaning and error
+// ComputeContext), the two matmul operators (Linear, MatMul) and the two elementwise operators
+// either side of them in a W8A8 graph (QuantizeLinear, DequantizeLinear).  Names, argument meaning and error
 // behaviour follow the reference so that code written against nnops compiles against this
 // header unchanged:
 //
@@ -14,6 +15,7 @@
 //   include/nnops/core/op_base.hpp:30           OpBase
 //   include/nnops/ops/linear.hpp:41-142         LinearAttributes, Linear
 //   include/nnops/ops/matmul.hpp:37-135         MatMulAttributes, MatMul
+//   include/nnops/ops/quant_linear.hpp:24-141   QuantLinearAttributes, QuantizeLinear, DequantizeLinear
 //
 // It is NOT a copy of those headers: only what this path needs exists, written from the
 // documented behaviour.  When the real nnops headers are available the CUDA backend glue
@@ -228,7 +230,7 @@ struct ComputeContext {
     void* cuda_stream = nullptr;  ///< cudaStream_t, opaque; nullptr = default stream
 };
 
-enum class OpType : uint8_t { Linear = 0, MatMul = 1 };
+enum class OpType : uint8_t { Linear = 0, MatMul = 1, QuantizeLinear = 2, DequantizeLinear = 3 };
 
 class OpBase {
 public:
@@ -318,6 +320,66 @@ private:
     Backend backend_;
 };
 
+struct QuantLinearAttributes {
+    /// -1: one parameter per innermost row (per token); >= 0: one per index along `axis` (per
+    /// channel).  A one-element scale is per tensor whatever the axis.
+    int64_t axis = -1;
+    /// QuantizeLinear: s8 / u8.  DequantizeLinear: f32 / f16 (anything else means f32).
+    DataType output_dtype = DataType::s8;
+};
+
+inline QuantGranularity resolve_quant_granularity(const TensorView& scale, int64_t axis)
+{
+    if (scale.numel() <= 1) return QuantGranularity::PerTensor;
+    return axis < 0 ? QuantGranularity::PerToken : QuantGranularity::PerChannel;
+}
+
+/// inputs {x (f32/f16), y_scale (f32), y_zero_point (s8/u8)} -> y (s8/u8):
+/// y = saturate(round_half_even(x / scale) + zero_point).
+class QuantizeLinear : public OpBase {
+public:
+    static std::unique_ptr<QuantizeLinear> create(const QuantLinearAttributes& attrs = {}, Backend backend = Backend::CPU);
+    static std::unique_ptr<QuantizeLinear> create(Backend backend) { return create(QuantLinearAttributes{}, backend); }
+    std::vector<TensorDesc> getOutputTensorDesc(std::span<const TensorDesc> inputs) const override;
+    Status validate(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs) const override;
+    using OpBase::compute;
+    Status compute(std::span<TensorView> outputs, std::span<const TensorView> inputs, const ComputeContext& ctx = {},
+                   void* workspace = nullptr) override;
+    OpType getOpType() const override { return OpType::QuantizeLinear; }
+    Backend getBackend() const override { return backend_; }
+    const QuantLinearAttributes& attributes() const noexcept { return attrs_; }
+
+private:
+    QuantizeLinear(const QuantLinearAttributes& a, Backend b) : attrs_(a), backend_(b) {}
+    QuantLinearAttributes attrs_;
+    Backend backend_;
+};
+
+/// inputs {x (s8/u8), x_scale (f32), x_zero_point (s8/u8)} -> y (f32/f16): y = (x - zero_point) * scale.
+class DequantizeLinear : public OpBase {
+public:
+    static std::unique_ptr<DequantizeLinear> create(const QuantLinearAttributes& attrs = {}, Backend backend = Backend::CPU);
+    static std::unique_ptr<DequantizeLinear> create(Backend backend) { return create(QuantLinearAttributes{}, backend); }
+    std::vector<TensorDesc> getOutputTensorDesc(std::span<const TensorDesc> inputs) const override;
+    Status validate(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs) const override;
+    using OpBase::compute;
+    Status compute(std::span<TensorView> outputs, std::span<const TensorView> inputs, const ComputeContext& ctx = {},
+                   void* workspace = nullptr) override;
+    OpType getOpType() const override { return OpType::DequantizeLinear; }
+    Backend getBackend() const override { return backend_; }
+    const QuantLinearAttributes& attributes() const noexcept { return attrs_; }
+
+private:
+    DequantizeLinear(const QuantLinearAttributes& a, Backend b) : attrs_(a), backend_(b)
+    {
+        if (attrs_.output_dtype != DataType::f32 && attrs_.output_dtype != DataType::f16) {
+            attrs_.output_dtype = DataType::f32;
+        }
+    }
+    QuantLinearAttributes attrs_;
+    Backend backend_;
+};
+
 namespace backend::cuda {
 /// The two backend entry points the operator front end dispatches to (the reference declares
 /// them at src/ops/linear.cpp:24 and src/ops/matmul.cpp:35).
@@ -325,6 +387,11 @@ Status linear_cuda(const LinearAttributes& attrs, TensorView& output, std::span<
                    const ComputeContext& ctx, void* workspace);
 Status matmul_cuda(const MatMulAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
                    const ComputeContext& ctx, void* workspace);
+/// ... and the two of QuantizeLinear / DequantizeLinear (declared at src/ops/quant_linear.cpp:21-28).
+Status quantize_linear_cuda(const QuantLinearAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
+                            const ComputeContext& ctx, void* workspace);
+Status dequantize_linear_cuda(const QuantLinearAttributes& attrs, TensorView& output,
+                              std::span<const TensorView> inputs, const ComputeContext& ctx, void* workspace);
 }  // namespace backend::cuda
 
 }  // namespace nnops

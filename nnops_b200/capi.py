@@ -65,6 +65,16 @@ class Q41Args(C.Structure):
 Q4_FLAG_OVERLAP_PREVIOUS = 1
 
 # Every symbol include/nnb200.h declares: (name, restype, argtypes).
+class QuantLinearArgs(C.Structure):
+    """Mirror of nnb200_quant_linear_args."""
+    _fields_ = [
+        ("x", C.c_void_p), ("y", C.c_void_p),
+        ("outer", C.c_int64), ("rows", C.c_int64), ("inner", C.c_int64),
+        ("scale", C.c_void_p), ("zero_point", C.c_void_p),
+        ("zp_unsigned", C.c_int32), ("float_f16", C.c_int32), ("int_unsigned", C.c_int32),
+    ]
+
+
 SYMBOLS = [
     ("nnb200_gemm_i8_workspace_bytes", C.c_size_t, [C.POINTER(GemmI8Args)]),
     ("nnb200_gemm_i8", C.c_int, [C.POINTER(GemmI8Args), C.c_void_p]),
@@ -75,6 +85,8 @@ SYMBOLS = [
     ("nnb200_q4_1_engine", C.c_int, [C.POINTER(Q41Args)]),
     ("nnb200_q4_1_decode", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32,
                                      C.c_int64, C.c_void_p]),
+    ("nnb200_quantize_linear", C.c_int, [C.POINTER(QuantLinearArgs), C.c_void_p]),
+    ("nnb200_dequantize_linear", C.c_int, [C.POINTER(QuantLinearArgs), C.c_void_p]),
     ("nnb200_interleave_shards", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64,
                                            C.c_void_p]),
     ("nnb200_take_device_error", C.c_int, [C.POINTER(C.c_int32)]),

@@ -374,6 +374,42 @@ int nnb200_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, i
     return launch_q4_1_decode(w_blocks, ldw_blocks, rows, k, out, out_f16, ld_out, static_cast<cudaStream_t>(stream));
 }
 
+static int quant_linear_call(const nnb200_quant_linear_args* q, void* stream, bool quantize)
+{
+    if (q == nullptr || q->outer < 0 || q->rows < 0 || q->inner < 0) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if (q->outer == 0 || q->rows == 0 || q->inner == 0) {
+        return NNB200_OK;
+    }
+    if (q->x == nullptr || q->y == nullptr || q->scale == nullptr || q->zero_point == nullptr) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    // The element count must fit the kernels' 64-bit signed indexing.
+    if (q->outer > INT64_MAX / q->rows || q->outer * q->rows > INT64_MAX / q->inner) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    if (dev->cc_major != 10) {
+        return NNB200_UNSUPPORTED;
+    }
+    return quantize ? launch_quantize_linear(*q, *dev, static_cast<cudaStream_t>(stream))
+                    : launch_dequantize_linear(*q, *dev, static_cast<cudaStream_t>(stream));
+}
+
+int nnb200_quantize_linear(const nnb200_quant_linear_args* q, void* stream)
+{
+    return quant_linear_call(q, stream, true);
+}
+
+int nnb200_dequantize_linear(const nnb200_quant_linear_args* q, void* stream)
+{
+    return quant_linear_call(q, stream, false);
+}
+
 int nnb200_interleave_shards(const void* gathered, void* out, int64_t m, int64_t row_bytes_per_shard, int32_t shards,
                               int64_t out_pitch_bytes, void* stream)
 {

@@ -70,6 +70,9 @@ bool q4_1_gemm_umma_supported(const nnb200_q4_1_args& a);
 int launch_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, int64_t k, void* out, int out_f16,
                        int64_t ld_out, cudaStream_t stream);
 
+int launch_quantize_linear(const nnb200_quant_linear_args& q, const DeviceInfo& dev, cudaStream_t stream);
+int launch_dequantize_linear(const nnb200_quant_linear_args& q, const DeviceInfo& dev, cudaStream_t stream);
+
 int launch_interleave_shards(const void* src, void* dst, int64_t m, int64_t row_bytes_per_shard, int g,
                              int64_t dst_pitch_bytes, const DeviceInfo& dev, cudaStream_t stream);
 

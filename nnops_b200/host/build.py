@@ -4,10 +4,10 @@ programs.
     python -m nnops_b200.host.build
 
 Outputs (all git-ignored, shipped as built files):
-  nnops_b200/lib/libnnb200_host.so      Linear/MatMul front end + backend glue against the stand-alone API mirror
+  nnops_b200/lib/libnnb200_host.so      operator front end + backend glue against the stand-alone API mirror
   tests/cpp/_bin/test_ops_standalone    operator tests against that library
 and, only where the nnops source tree is present (NNOPS_REFERENCE_ROOT, default /root/reference):
-  nnops_b200/lib/libnnops_b200_dropin.so   nnops' own front end (src/ops/linear.cpp, matmul.cpp) and CPU route,
+  nnops_b200/lib/libnnops_b200_dropin.so   nnops' own front end (src/ops/linear.cpp, matmul.cpp, quant_linear.cpp) and CPU route,
                                            compiled in place with NNOPS_HAS_CUDA, linked against THIS backend
   tests/cpp/_bin/test_ops_dropin           the same tests through the real nnops API, CUDA vs nnops' CPU route
 """
@@ -34,6 +34,7 @@ REF_SOURCES = [
     "backend/cpu/matmul/matmul.cpp", "backend/cpu/matmul/matmul_i8.cpp", "backend/cpu/matmul/matmul_helper_i8.cpp",
     "backend/cpu/matmul/matmul_helper.cpp", "backend/cpu/matmul/matmul_small.cpp",
     "backend/cpu/matmul/matmul_qblock_fused.cpp", "backend/cpu/matmul/linear.cpp",
+    "ops/quant_linear.cpp", "backend/cpu/quant_linear.cpp",
 ]
 COMMON = ["-std=c++23", "-O2", "-fPIC", "-Wall", f"-I{ROOT / 'include'}"]
 
@@ -58,7 +59,7 @@ def _rpath(*dirs):
 def build_standalone(force=False) -> Path:
     lib = lib_build.build()
     out = LIB_DIR / "libnnb200_host.so"
-    srcs = [HOST / "cuda_backend.cpp", HOST / "ops_frontend.cpp"]
+    srcs = [HOST / "cuda_backend.cpp", HOST / "quant_backend.cpp", HOST / "ops_frontend.cpp"]
     deps = srcs + [ROOT / "include" / "nnops_b200" / "nnops_api.hpp", ROOT / "include" / "nnb200.h", lib]
     if force or _stale(out, deps):
         _run([CXX, *COMMON, "-shared", "-o", out, *srcs, f"-L{LIB_DIR}", "-lnnb200", *_rpath("$ORIGIN")])
@@ -72,9 +73,9 @@ def build_dropin(force=False) -> Path | None:
         return p if p.exists() else None
     lib = lib_build.build()
     out = LIB_DIR / "libnnops_b200_dropin.so"
-    glue = HOST / "cuda_backend.cpp"
+    glue = [HOST / "cuda_backend.cpp", HOST / "quant_backend.cpp"]
     srcs = [REFERENCE_ROOT / "src" / s for s in REF_SOURCES]
-    if not (force or _stale(out, [glue, lib, ROOT / "include" / "nnb200.h", *srcs])):
+    if not (force or _stale(out, [*glue, lib, ROOT / "include" / "nnb200.h", *srcs])):
         return out
     obj_dir = LIB_DIR / "obj_dropin"
     obj_dir.mkdir(exist_ok=True)
@@ -88,9 +89,10 @@ def build_dropin(force=False) -> Path | None:
         o = obj_dir / (str(s.relative_to(REFERENCE_ROOT)).replace("/", "_") + ".o")
         objs.append(o)
         jobs.append([CXX, *flags, "-c", s, "-o", o])
-    o = obj_dir / "cuda_backend.o"
-    objs.append(o)
-    jobs.append([CXX, *flags, "-DNNB200_USE_NNOPS_HEADERS=1", "-c", glue, "-o", o])
+    for g in glue:
+        o = obj_dir / (g.stem + ".o")
+        objs.append(o)
+        jobs.append([CXX, *flags, "-DNNB200_USE_NNOPS_HEADERS=1", "-c", g, "-o", o])
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as ex:
         list(ex.map(_run, jobs))
     _run([CXX, "-shared", "-fopenmp", "-o", out, *objs, f"-L{LIB_DIR}", "-lnnb200", *_rpath("$ORIGIN")])

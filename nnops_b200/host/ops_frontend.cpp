@@ -1,7 +1,8 @@
-// Stand-alone front end of Linear and MatMul for builds without the nnops source tree:
-// create / getOutputTensorDesc / validate / compute with the reference's argument checks and
-// status codes (src/ops/linear.cpp:26-120, src/ops/matmul.cpp:36-152,
-// include/nnops/detail/validate.hpp:70-96, include/nnops/detail/shape_inference.hpp:453-526),
+// Stand-alone front end of Linear, MatMul, QuantizeLinear and DequantizeLinear for builds
+// without the nnops source tree: create / getOutputTensorDesc / validate / compute with the
+// reference's argument checks and status codes (src/ops/linear.cpp:26-120,
+// src/ops/matmul.cpp:36-152, src/ops/quant_linear.cpp:54-175,
+// include/nnops/detail/validate.hpp:70-126, include/nnops/detail/shape_inference.hpp:453-526,713-742),
 // dispatching to the CUDA backend.  There is no CPU route here: an operator created for
 // another backend answers Status::unsupported.
 
@@ -180,6 +181,113 @@ Status MatMul::compute(std::span<TensorView> outputs, std::span<const TensorView
         return Status::unsupported;
     }
     return backend::cuda::matmul_cuda(attrs_, outputs[0], inputs, ctx, workspace);
+}
+
+// ---- QuantizeLinear / DequantizeLinear -----------------------------------------------------
+
+namespace {
+
+TensorDesc same_shape_as(const TensorDesc& x, DataType dt)
+{
+    TensorDesc out;
+    out.rank = x.rank;
+    out.layout = x.layout;
+    out.dtype = dt;
+    out.dims = x.dims;
+    return out;
+}
+
+bool rows_compact(const TensorDesc& d)
+{
+    return d.rank < 2 || d.row_stride_elems == 0 || d.row_stride_elems == d.dims[static_cast<size_t>(d.rank - 1)];
+}
+
+// A float side (f32/f16), an s8/u8 side, an f32 scale and an s8/u8 zero point; rows packed.
+Status check_quant_linear(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs, bool quantize)
+{
+    if (check_counts(inputs.size(), outputs.size(), 3, 3, 1) != Status::ok) {
+        return Status::invalid_argument;
+    }
+    const DataType flt = quantize ? inputs[0].dtype : outputs[0].dtype;
+    const DataType qnt = quantize ? outputs[0].dtype : inputs[0].dtype;
+    if (flt != DataType::f32 && flt != DataType::f16) {
+        return Status::unsupported;
+    }
+    if (qnt != DataType::s8 && qnt != DataType::u8) {
+        return Status::invalid_argument;
+    }
+    if (inputs[1].dtype != DataType::f32) {
+        return Status::invalid_argument;
+    }
+    if (inputs[2].dtype != DataType::s8 && inputs[2].dtype != DataType::u8) {
+        return Status::invalid_argument;
+    }
+    if (!rows_compact(inputs[0]) || !rows_compact(outputs[0])) {
+        return Status::unsupported;
+    }
+    return Status::ok;
+}
+
+}  // namespace
+
+std::unique_ptr<QuantizeLinear> QuantizeLinear::create(const QuantLinearAttributes& attrs, Backend backend)
+{
+    return std::unique_ptr<QuantizeLinear>(new QuantizeLinear(attrs, backend));
+}
+
+std::vector<TensorDesc> QuantizeLinear::getOutputTensorDesc(std::span<const TensorDesc> inputs) const
+{
+    return {same_shape_as(inputs[0], attrs_.output_dtype)};
+}
+
+Status QuantizeLinear::validate(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs) const
+{
+    return check_quant_linear(inputs, outputs, true);
+}
+
+Status QuantizeLinear::compute(std::span<TensorView> outputs, std::span<const TensorView> inputs,
+                               const ComputeContext& ctx, void* workspace)
+{
+    if (const Status s = check_views(outputs, inputs, 3, 3); s != Status::ok) {
+        return s;
+    }
+    if (const Status s = validate_views(*this, outputs, inputs); s != Status::ok) {
+        return s;
+    }
+    if (backend_ != Backend::CUDA) {
+        return Status::unsupported;
+    }
+    return backend::cuda::quantize_linear_cuda(attrs_, outputs[0], inputs, ctx, workspace);
+}
+
+std::unique_ptr<DequantizeLinear> DequantizeLinear::create(const QuantLinearAttributes& attrs, Backend backend)
+{
+    return std::unique_ptr<DequantizeLinear>(new DequantizeLinear(attrs, backend));
+}
+
+std::vector<TensorDesc> DequantizeLinear::getOutputTensorDesc(std::span<const TensorDesc> inputs) const
+{
+    return {same_shape_as(inputs[0], attrs_.output_dtype)};
+}
+
+Status DequantizeLinear::validate(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs) const
+{
+    return check_quant_linear(inputs, outputs, false);
+}
+
+Status DequantizeLinear::compute(std::span<TensorView> outputs, std::span<const TensorView> inputs,
+                                 const ComputeContext& ctx, void* workspace)
+{
+    if (const Status s = check_views(outputs, inputs, 3, 3); s != Status::ok) {
+        return s;
+    }
+    if (const Status s = validate_views(*this, outputs, inputs); s != Status::ok) {
+        return s;
+    }
+    if (backend_ != Backend::CUDA) {
+        return Status::unsupported;
+    }
+    return backend::cuda::dequantize_linear_cuda(attrs_, outputs[0], inputs, ctx, workspace);
 }
 
 }  // namespace nnops

@@ -166,3 +166,63 @@ def q4_1_decode(w_blocks: torch.Tensor, k: int, out_dtype: torch.dtype = torch.f
                                                  out.data_ptr(), int(out_dtype == torch.float16), out.stride(0),
                                                  _stream_ptr(w_blocks.device)), "nnb200_q4_1_decode")
     return out
+
+
+def _quant_view(shape, axis: int, param_count: int) -> tuple[int, int, int]:
+    """[outer][rows][inner] of a dense tensor: one parameter = per tensor; axis < 0 = one per
+    innermost row; else one per index along ``axis`` (the operator's granularity rule,
+    reference include/nnops/ops/quant_linear.hpp:38-45)."""
+    shape = tuple(int(s) for s in shape)
+    numel = math.prod(shape)
+    if param_count <= 1:
+        return 1, 1, numel
+    if axis < 0:
+        return 1, numel // shape[-1] if shape[-1] else 0, shape[-1]
+    return math.prod(shape[:axis]), shape[axis], math.prod(shape[axis + 1:])
+
+
+def _quant_params(scale, zero_point, device):
+    scale = torch.as_tensor(scale, dtype=torch.float32).reshape(-1).to(device).contiguous()
+    zero_point = torch.as_tensor(zero_point).reshape(-1).to(device).contiguous()
+    if zero_point.dtype not in (torch.int8, torch.uint8) or zero_point.numel() != scale.numel():
+        raise ValueError("zero_point must be int8/uint8 with one entry per scale")
+    return scale, zero_point
+
+
+def quantize_linear(x: torch.Tensor, scale, zero_point, *, axis: int = -1, out_dtype: torch.dtype = torch.int8,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """QuantizeLinear on the GPU: f32/f16 -> s8/u8."""
+    if x.dtype not in (torch.float32, torch.float16) or not x.is_contiguous():
+        raise ValueError("x must be a contiguous f32/f16 tensor")
+    scale, zero_point = _quant_params(scale, zero_point, x.device)
+    y = out if out is not None else torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    outer, rows, inner = _quant_view(x.shape, axis, scale.numel())
+    if rows != scale.numel():
+        raise ValueError("scale count does not match the tensor and axis")
+    args = capi.QuantLinearArgs(x=x.data_ptr(), y=y.data_ptr(), outer=outer, rows=rows, inner=inner,
+                                scale=scale.data_ptr(), zero_point=zero_point.data_ptr(),
+                                zp_unsigned=int(zero_point.dtype == torch.uint8),
+                                float_f16=int(x.dtype == torch.float16), int_unsigned=int(y.dtype == torch.uint8))
+    with torch.cuda.device(x.device):
+        capi.check(capi.lib().nnb200_quantize_linear(C.byref(args), _stream_ptr(x.device)), "nnb200_quantize_linear")
+    return y
+
+
+def dequantize_linear(x: torch.Tensor, scale, zero_point, *, axis: int = -1, out_dtype: torch.dtype = torch.float32,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """DequantizeLinear on the GPU: s8/u8 -> f32/f16."""
+    if x.dtype not in (torch.int8, torch.uint8) or not x.is_contiguous():
+        raise ValueError("x must be a contiguous int8/uint8 tensor")
+    scale, zero_point = _quant_params(scale, zero_point, x.device)
+    y = out if out is not None else torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    outer, rows, inner = _quant_view(x.shape, axis, scale.numel())
+    if rows != scale.numel():
+        raise ValueError("scale count does not match the tensor and axis")
+    args = capi.QuantLinearArgs(x=x.data_ptr(), y=y.data_ptr(), outer=outer, rows=rows, inner=inner,
+                                scale=scale.data_ptr(), zero_point=zero_point.data_ptr(),
+                                zp_unsigned=int(zero_point.dtype == torch.uint8),
+                                float_f16=int(y.dtype == torch.float16), int_unsigned=int(x.dtype == torch.uint8))
+    with torch.cuda.device(x.device):
+        capi.check(capi.lib().nnb200_dequantize_linear(C.byref(args), _stream_ptr(x.device)),
+                   "nnb200_dequantize_linear")
+    return y

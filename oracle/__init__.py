@@ -216,3 +216,80 @@ def q4_1_matmul(a: np.ndarray, w_blocks: np.ndarray, k: int, *, out_dtype: str =
         if st != 0:
             raise RuntimeError(f"reference op returned Status {st}")
     return out
+
+
+def quant_decompose(shape, axis: int, param_count: int) -> tuple[int, int, int]:
+    """[outer][rows][inner] view of a dense tensor for QuantizeLinear / DequantizeLinear:
+    one parameter -> per tensor; axis < 0 -> one per innermost row; else one per index of axis
+    (reference resolve_quant_granularity, include/nnops/ops/quant_linear.hpp:38-45)."""
+    shape = tuple(int(s) for s in shape)
+    numel = int(np.prod(shape)) if shape else 1
+    if param_count <= 1:
+        return 1, 1, numel
+    if axis < 0:
+        return 1, numel // shape[-1], shape[-1]
+    outer = int(np.prod(shape[:axis])) if axis > 0 else 1
+    inner = int(np.prod(shape[axis + 1:])) if axis + 1 < len(shape) else 1
+    return outer, shape[axis], inner
+
+
+def quantize_linear(x: np.ndarray, scale, zero_point, *, axis: int = -1, out_dtype=np.int8, impl: str = "port",
+                    threads: int | None = None, tail_fused: bool = True) -> np.ndarray:
+    """y = saturate(round_half_even(x / scale + zero_point)) with the reference's arithmetic.
+    ``scale`` f32 and ``zero_point`` s8/u8 arrays of equal length (1 = per tensor)."""
+    x = np.ascontiguousarray(x)
+    assert x.dtype in (np.float32, np.float16)
+    scale = np.ascontiguousarray(np.atleast_1d(scale), dtype=np.float32)
+    zero_point = np.ascontiguousarray(np.atleast_1d(zero_point))
+    assert zero_point.dtype in (np.int8, np.uint8) and zero_point.size == scale.size
+    y = np.zeros(x.shape, dtype=out_dtype)
+    if x.size == 0:
+        return y
+    if impl == "port":
+        outer, rows, inner = quant_decompose(x.shape, axis, scale.size)
+        assert rows == scale.size
+        port_lib().oracle_quantize_linear(
+            C.c_void_p(x.ctypes.data), C.c_int(x.dtype == np.float16), C.c_int64(outer), C.c_int64(rows),
+            C.c_int64(inner), C.c_void_p(scale.ctypes.data), C.c_void_p(zero_point.ctypes.data),
+            C.c_int(zero_point.dtype == np.uint8), C.c_void_p(y.ctypes.data), C.c_int(y.dtype == np.uint8),
+            C.c_int(int(tail_fused)))
+    else:
+        shape = (C.c_int64 * x.ndim)(*x.shape)
+        st = ref_lib().ref_quantize_linear(
+            C.c_void_p(x.ctypes.data), C.c_int(x.dtype == np.float16), shape, C.c_int(x.ndim), C.c_int64(axis),
+            C.c_void_p(scale.ctypes.data), C.c_void_p(zero_point.ctypes.data), C.c_int(zero_point.dtype == np.uint8),
+            C.c_int64(scale.size), C.c_void_p(y.ctypes.data), C.c_int(y.dtype == np.uint8),
+            C.c_int(int(threads or ref_threads())))
+        if st != 0:
+            raise RuntimeError(f"reference op returned Status {st}")
+    return y
+
+
+def dequantize_linear(x: np.ndarray, scale, zero_point, *, axis: int = -1, out_dtype=np.float32, impl: str = "port",
+                      threads: int | None = None) -> np.ndarray:
+    """y = (x - zero_point) * scale with the reference's arithmetic (see nnops_oracle.c)."""
+    x = np.ascontiguousarray(x)
+    assert x.dtype in (np.int8, np.uint8)
+    scale = np.ascontiguousarray(np.atleast_1d(scale), dtype=np.float32)
+    zero_point = np.ascontiguousarray(np.atleast_1d(zero_point))
+    assert zero_point.dtype in (np.int8, np.uint8) and zero_point.size == scale.size
+    y = np.zeros(x.shape, dtype=out_dtype)
+    if x.size == 0:
+        return y
+    if impl == "port":
+        outer, rows, inner = quant_decompose(x.shape, axis, scale.size)
+        assert rows == scale.size
+        port_lib().oracle_dequantize_linear(
+            C.c_void_p(x.ctypes.data), C.c_int(x.dtype == np.uint8), C.c_int64(outer), C.c_int64(rows),
+            C.c_int64(inner), C.c_void_p(scale.ctypes.data), C.c_void_p(zero_point.ctypes.data),
+            C.c_int(zero_point.dtype == np.uint8), C.c_void_p(y.ctypes.data), C.c_int(y.dtype == np.float16))
+    else:
+        shape = (C.c_int64 * x.ndim)(*x.shape)
+        st = ref_lib().ref_dequantize_linear(
+            C.c_void_p(x.ctypes.data), C.c_int(x.dtype == np.uint8), shape, C.c_int(x.ndim), C.c_int64(axis),
+            C.c_void_p(scale.ctypes.data), C.c_void_p(zero_point.ctypes.data), C.c_int(zero_point.dtype == np.uint8),
+            C.c_int64(scale.size), C.c_void_p(y.ctypes.data), C.c_int(y.dtype == np.float16),
+            C.c_int(int(threads or ref_threads())))
+        if st != 0:
+            raise RuntimeError(f"reference op returned Status {st}")
+    return y

@@ -36,6 +36,8 @@ REF_SOURCES = [
     "backend/cpu/matmul/matmul_small.cpp",
     "backend/cpu/matmul/matmul_qblock_fused.cpp",
     "backend/cpu/matmul/linear.cpp",
+    "ops/quant_linear.cpp",
+    "backend/cpu/quant_linear.cpp",
 ]
 
 ISA_VARIANTS = {

@@ -353,3 +353,91 @@ void oracle_q4_1_matmul(const void* a, int a_is_f16, int64_t lda,
     }
     free(arow_all);
 }
+
+/* ---- QuantizeLinear / DequantizeLinear ----------------------------------------------------
+ * The tensor is a flat row-major array seen as [outer][rows][inner]; parameter r (scale,
+ * zero point) serves every element of row r of every outer group
+ * (src/backend/cpu/quant_linear.cpp:83-118: per tensor = [1][1][numel], per token =
+ * [1][numel/last][last], per channel = [outer][shape[axis]][inner]).
+ *
+ * Arithmetic of the x86 arch kernels (src/backend/cpu/x86_64/quant.hpp:117-165, 278-325):
+ *   quantize:   inv = 1.0f / scale; v = fma(x, inv, zp) in ONE rounding; q = v rounded to
+ *               nearest-even as int32, where anything outside int32 (and NaN) becomes
+ *               INT32_MIN as cvtps2dq does; then saturate to the 8-bit range.
+ *   dequantize: first (inner - inner % 16) elements of a row:  fma(float(q), scale, -zp*scale);
+ *               the last inner % 16 elements (the scalar tail):  (float(q) - zp) * scale.
+ * f16 inputs are widened exactly, f16 outputs rounded once from the f32 result (RNE).
+ * tail_fused = 0 makes the quantize tail round the product before the add (the literal
+ * reading of the scalar tail, quant.hpp:159-164); the reference compiled with its own flags
+ * contracts it into the same fma as the vector body, which tests/test_oracle.py pins.
+ */
+static int32_t cvt_rne_x86(float v)
+{
+    if (!(v >= -2147483648.0f && v < 2147483648.0f)) {
+        return INT32_MIN;
+    }
+    return (int32_t)nearbyintf(v);
+}
+
+void oracle_quantize_linear(const void* x, int x_is_f16, int64_t outer, int64_t rows, int64_t inner,
+                            const float* scale, const void* zero_point, int zp_is_u8,
+                            void* y, int y_is_u8, int tail_fused)
+{
+    const int32_t qmin = y_is_u8 ? 0 : -128;
+    const int32_t qmax = y_is_u8 ? 255 : 127;
+    const int64_t body = inner - inner % 16;
+    for (int64_t o = 0; o < outer; ++o) {
+        for (int64_t r = 0; r < rows; ++r) {
+            const float inv = 1.0f / scale[r];
+            const float zp = zp_is_u8 ? (float)((const uint8_t*)zero_point)[r] : (float)((const int8_t*)zero_point)[r];
+            const int64_t base = (o * rows + r) * inner;
+            for (int64_t i = 0; i < inner; ++i) {
+                const float xv = x_is_f16 ? oracle_f16_to_f32(((const uint16_t*)x)[base + i]) : ((const float*)x)[base + i];
+                float v;
+                if (i < body || tail_fused) {
+                    v = fmaf(xv, inv, zp);
+                } else {
+                    const float prod = xv * inv;
+                    v = prod + zp;
+                }
+                int32_t q = cvt_rne_x86(v);
+                q = q < qmin ? qmin : (q > qmax ? qmax : q);
+                if (y_is_u8) {
+                    ((uint8_t*)y)[base + i] = (uint8_t)q;
+                } else {
+                    ((int8_t*)y)[base + i] = (int8_t)q;
+                }
+            }
+        }
+    }
+}
+
+void oracle_dequantize_linear(const void* x, int x_is_u8, int64_t outer, int64_t rows, int64_t inner,
+                              const float* scale, const void* zero_point, int zp_is_u8,
+                              void* y, int y_is_f16)
+{
+    const int64_t body = inner - inner % 16;
+    for (int64_t o = 0; o < outer; ++o) {
+        for (int64_t r = 0; r < rows; ++r) {
+            const float s = scale[r];
+            const float zp = zp_is_u8 ? (float)((const uint8_t*)zero_point)[r] : (float)((const int8_t*)zero_point)[r];
+            const float neg_zs = -zp * s;
+            const int64_t base = (o * rows + r) * inner;
+            for (int64_t i = 0; i < inner; ++i) {
+                const float q = x_is_u8 ? (float)((const uint8_t*)x)[base + i] : (float)((const int8_t*)x)[base + i];
+                float f;
+                if (i < body) {
+                    f = fmaf(q, s, neg_zs);
+                } else {
+                    const float d = q - zp;
+                    f = d * s;
+                }
+                if (y_is_f16) {
+                    ((uint16_t*)y)[base + i] = oracle_f32_to_f16(f);
+                } else {
+                    ((float*)y)[base + i] = f;
+                }
+            }
+        }
+    }
+}

@@ -11,6 +11,7 @@
 #include "nnops/core/openmp_backend.hpp"
 #include "nnops/ops/linear.hpp"
 #include "nnops/ops/matmul.hpp"
+#include "nnops/ops/quant_linear.hpp"
 #include "nnops/detail/q4_1.hpp"
 
 #include <cstdint>
@@ -167,6 +168,47 @@ int ref_linear_q4_1(const void* x, int x_is_f16, int64_t m, int64_t k, int64_t x
 /// Reference Q4_1 codec, for pinning the restated codec.
 void ref_q4_1_decode(const void* blocks, int64_t count, float* out) { pack_q4<float>(blocks, count, out); }
 void ref_q4_1_quantize(const float* src, int64_t count, void* blocks) { quantize_q4<float>(src, count, blocks); }
+
+/// QuantizeLinear / DequantizeLinear through the reference ops.  `shape`/`rank` describe the
+/// dense tensor, `axis` and `param_count` select the granularity exactly as the op does
+/// (count 1 = per tensor, axis < 0 = one parameter per innermost row, else per index of axis).
+int ref_quantize_linear(const void* x, int x_is_f16, const int64_t* shape, int rank, int64_t axis,
+                        const float* scale, const void* zero_point, int zp_is_u8, int64_t param_count,
+                        void* y, int y_is_u8, int threads)
+{
+    const std::span<const int64_t> sh(shape, size_t(rank));
+    const int64_t p_shape[1] = {param_count};
+    TensorView xv(sh, x_is_f16 ? DataType::f16 : DataType::f32, const_cast<void*>(x));
+    TensorView sv(p_shape, DataType::f32, const_cast<float*>(scale));
+    TensorView zv(p_shape, zp_is_u8 ? DataType::u8 : DataType::s8, const_cast<void*>(zero_point));
+    TensorView yv(sh, y_is_u8 ? DataType::u8 : DataType::s8, y);
+    QuantLinearAttributes attrs;
+    attrs.axis = axis;
+    attrs.output_dtype = y_is_u8 ? DataType::u8 : DataType::s8;
+    auto op = QuantizeLinear::create(attrs, Backend::CPU);
+    const ComputeContext ctx = make_ctx(threads);
+    TensorView ins[3] = {xv, sv, zv};
+    return int(op->compute(yv, std::span<const TensorView>(ins, 3), ctx, nullptr));
+}
+
+int ref_dequantize_linear(const void* x, int x_is_u8, const int64_t* shape, int rank, int64_t axis,
+                          const float* scale, const void* zero_point, int zp_is_u8, int64_t param_count,
+                          void* y, int y_is_f16, int threads)
+{
+    const std::span<const int64_t> sh(shape, size_t(rank));
+    const int64_t p_shape[1] = {param_count};
+    TensorView xv(sh, x_is_u8 ? DataType::u8 : DataType::s8, const_cast<void*>(x));
+    TensorView sv(p_shape, DataType::f32, const_cast<float*>(scale));
+    TensorView zv(p_shape, zp_is_u8 ? DataType::u8 : DataType::s8, const_cast<void*>(zero_point));
+    TensorView yv(sh, y_is_f16 ? DataType::f16 : DataType::f32, y);
+    QuantLinearAttributes attrs;
+    attrs.axis = axis;
+    attrs.output_dtype = y_is_f16 ? DataType::f16 : DataType::f32;
+    auto op = DequantizeLinear::create(attrs, Backend::CPU);
+    const ComputeContext ctx = make_ctx(threads);
+    TensorView ins[3] = {xv, sv, zv};
+    return int(op->compute(yv, std::span<const TensorView>(ins, 3), ctx, nullptr));
+}
 
 void ref_release_scratch() { release_scratch_memory(); }
 

@@ -13,6 +13,7 @@
 #ifdef NNB200_USE_NNOPS_HEADERS
 #include "nnops/ops/linear.hpp"
 #include "nnops/ops/matmul.hpp"
+#include "nnops/ops/quant_linear.hpp"
 #else
 #include "nnops_b200/nnops_api.hpp"
 #endif
@@ -43,6 +44,10 @@ struct oracle_gemm_i8_args {
 void oracle_gemm_i8(const oracle_gemm_i8_args* p);
 void oracle_q4_1_matmul(const void* a, int a_is_f16, int64_t lda, const uint8_t* w_blocks, int64_t ldw_blocks, void* out,
                         int out_is_f16, int64_t ldc, int64_t m, int64_t n, int64_t k, int w_round_f16, const void* bias);
+void oracle_quantize_linear(const void* x, int x_is_f16, int64_t outer, int64_t rows, int64_t inner, const float* scale,
+                            const void* zero_point, int zp_is_u8, void* y, int y_is_u8, int tail_fused);
+void oracle_dequantize_linear(const void* x, int x_is_u8, int64_t outer, int64_t rows, int64_t inner, const float* scale,
+                              const void* zero_point, int zp_is_u8, void* y, int y_is_f16);
 uint16_t oracle_f32_to_f16(float f);
 float oracle_f16_to_f32(uint16_t h);
 }
@@ -470,6 +475,146 @@ static void contract_cases()
     EXPECT(op->getWorkspaceSize({}, {}) == 0);
 }
 
+// ---- QuantizeLinear / DequantizeLinear ------------------------------------------------------
+
+// Known answers of the reference's operator test (tests/test_quant_linear.cpp:198-226, 439-467):
+// per-channel along axis 1 of a [2,3] tensor, with the half-to-even tie 0.5 -> 0.
+static void kat_quant_linear()
+{
+    g_case = "quantize_linear_2d_per_channel";
+    const int64_t shape[] = {2, 3}, ps[] = {3};
+    const float x_h[6] = {0.0f, 1.0f, 2.0f, 10.0f, 11.0f, 12.0f}, scale_h[3] = {1.0f, 2.0f, 3.0f};
+    const int8_t zp_h[3] = {0, 0, 0};
+    DevBuf x(x_h, sizeof(x_h)), sc(scale_h, sizeof(scale_h)), zp(zp_h, sizeof(zp_h)), y(6, 0x55);
+    QuantLinearAttributes attrs;
+    attrs.axis = 1;
+    attrs.output_dtype = DataType::s8;
+    auto op = QuantizeLinear::create(attrs, Backend::CUDA);
+    const TensorView ins[] = {view(shape, DataType::f32, x.p), view(ps, DataType::f32, sc.p), view(ps, DataType::s8, zp.p)};
+    const TensorDesc in_d[] = {ins[0].desc(), ins[1].desc(), ins[2].desc()};
+    const auto od = op->getOutputTensorDesc(in_d);
+    EXPECT(od[0].dtype == DataType::s8 && od[0].rank == 2 && od[0].dims[0] == 2 && od[0].dims[1] == 3);
+    TensorView out = view(shape, DataType::s8, y.p);
+    EXPECT(op->compute(out, ins) == Status::ok);
+    const auto q = y.download<int8_t>();
+    EXPECT(q[0] == 0 && q[1] == 0 && q[2] == 1 && q[3] == 10 && q[4] == 6 && q[5] == 4);
+
+    g_case = "dequantize_linear_2d_per_channel";
+    const int8_t xq_h[6] = {0, 0, 1, 10, 5, 4};
+    DevBuf xq(xq_h, sizeof(xq_h)), f(24);
+    attrs.output_dtype = DataType::f32;
+    auto dq = DequantizeLinear::create(attrs, Backend::CUDA);
+    const TensorView dins[] = {view(shape, DataType::s8, xq.p), view(ps, DataType::f32, sc.p), view(ps, DataType::s8, zp.p)};
+    TensorView fout = view(shape, DataType::f32, f.p);
+    EXPECT(dq->compute(fout, dins) == Status::ok);
+    const auto r = f.download<float>();
+    EXPECT(r[0] == 0.0f && r[1] == 0.0f && r[2] == 3.0f && r[3] == 10.0f && r[4] == 10.0f && r[5] == 12.0f);
+
+    g_case = "quant_linear_contract";
+    // A 64-bit float side is no dtype of this operator; a wrong scale dtype is an argument error.
+    const TensorView bad_scale[] = {view(shape, DataType::f32, x.p), view(ps, DataType::s8, sc.p), view(ps, DataType::s8, zp.p)};
+    EXPECT(op->compute(out, bad_scale) == Status::invalid_argument);
+    const TensorView two[] = {view(shape, DataType::f32, x.p), view(ps, DataType::f32, sc.p)};
+    EXPECT(op->compute(out, std::span<const TensorView>(two, 2)) == Status::invalid_argument);
+    const auto after = y.download<int8_t>();
+    EXPECT(after == q);  // rejected calls wrote nothing
+}
+
+struct QuantCase {
+    std::vector<int64_t> shape;
+    int64_t axis;
+    int64_t params;  // 1 = per tensor
+    bool f16, u8;
+};
+
+static void quant_linear_case(const QuantCase& c, const char* name, cudaStream_t stream)
+{
+    g_case = name;
+    int64_t numel = 1;
+    for (int64_t d : c.shape) numel *= d;
+    int64_t outer = 1, rows = 1, inner = numel;
+    if (c.params > 1 && c.axis < 0) {
+        inner = c.shape.back();
+        rows = numel / inner;
+    } else if (c.params > 1) {
+        inner = 1;
+        for (size_t d = 0; d < c.shape.size(); ++d) {
+            if (static_cast<int64_t>(d) < c.axis) outer *= c.shape[d];
+            if (static_cast<int64_t>(d) > c.axis) inner *= c.shape[d];
+        }
+        rows = c.shape[static_cast<size_t>(c.axis)];
+    }
+    std::mt19937_64 rng(numel * 7 + c.params);
+    std::normal_distribution<float> nd(0.0f, 60.0f);
+    std::uniform_real_distribution<float> us(0.05f, 3.0f);
+    std::vector<float> scale(c.params);
+    std::vector<uint8_t> zp(c.params);
+    for (auto& v : scale) v = us(rng);
+    for (auto& v : zp) v = static_cast<uint8_t>(rng() % 256);
+    std::vector<float> xf(numel);
+    for (int64_t i = 0; i < numel; ++i) {
+        xf[i] = (i % 5 == 0) ? (static_cast<float>(static_cast<int>(rng() % 180) - 90) + 0.5f) * scale[0] : nd(rng);
+    }
+    std::vector<uint16_t> xh(numel);
+    for (int64_t i = 0; i < numel; ++i) xh[i] = oracle_f32_to_f16(xf[i]);
+    const void* x_host = c.f16 ? static_cast<const void*>(xh.data()) : static_cast<const void*>(xf.data());
+    const size_t fsz = c.f16 ? 2 : 4;
+    const DataType fdt = c.f16 ? DataType::f16 : DataType::f32;
+    const DataType qdt = c.u8 ? DataType::u8 : DataType::s8;
+
+    std::vector<uint8_t> want_q(numel), xq(numel);
+    oracle_quantize_linear(x_host, c.f16, outer, rows, inner, scale.data(), zp.data(), c.u8, want_q.data(), c.u8, 1);
+    for (auto& v : xq) v = static_cast<uint8_t>(rng() % 256);
+    std::vector<uint8_t> want_f(numel * fsz);
+    oracle_dequantize_linear(xq.data(), c.u8, outer, rows, inner, scale.data(), zp.data(), c.u8, want_f.data(), c.f16);
+
+    DevBuf dx(x_host, numel * fsz), dsc(scale.data(), scale.size() * 4), dzp(zp.data(), zp.size()), dq(numel, 0x11);
+    DevBuf dxq(xq.data(), numel), df(numel * fsz, 0x11);
+    const std::span<const int64_t> sh(c.shape.data(), c.shape.size());
+    const int64_t ps[] = {c.params};
+    QuantLinearAttributes attrs;
+    attrs.axis = c.axis;
+    attrs.output_dtype = qdt;
+    ComputeContext ctx;
+    ctx.expected_backend = Backend::CUDA;
+    ctx.cuda_stream = stream;
+    {
+        auto op = QuantizeLinear::create(attrs, Backend::CUDA);
+        TensorView out(sh, qdt, dq.p);
+        const TensorView ins[] = {TensorView(sh, fdt, dx.p), view(ps, DataType::f32, dsc.p), view(ps, qdt, dzp.p)};
+        EXPECT(op->compute(out, ins, ctx) == Status::ok);
+        EXPECT(dq.download<uint8_t>() == want_q);
+    }
+    attrs.output_dtype = fdt;
+    {
+        auto op = DequantizeLinear::create(attrs, Backend::CUDA);
+        TensorView out(sh, fdt, df.p);
+        const TensorView ins[] = {TensorView(sh, qdt, dxq.p), view(ps, DataType::f32, dsc.p), view(ps, qdt, dzp.p)};
+        EXPECT(op->compute(out, ins, ctx) == Status::ok);
+        EXPECT(df.download<uint8_t>() == want_f);
+    }
+#ifdef NNB200_USE_NNOPS_HEADERS
+    // The reference's own CPU operators on the same bytes.
+    {
+        std::vector<uint8_t> cpu_q(numel), cpu_f(numel * fsz);
+        attrs.output_dtype = qdt;
+        auto qop = QuantizeLinear::create(attrs, Backend::CPU);
+        TensorView qo(sh, qdt, cpu_q.data());
+        const TensorView qins[] = {TensorView(sh, fdt, const_cast<void*>(x_host)), view(ps, DataType::f32, scale.data()),
+                                   view(ps, qdt, zp.data())};
+        EXPECT(qop->compute(qo, qins) == Status::ok);
+        EXPECT(cpu_q == want_q);
+        attrs.output_dtype = fdt;
+        auto dop = DequantizeLinear::create(attrs, Backend::CPU);
+        TensorView fo(sh, fdt, cpu_f.data());
+        const TensorView dins[] = {TensorView(sh, qdt, xq.data()), view(ps, DataType::f32, scale.data()),
+                                   view(ps, qdt, zp.data())};
+        EXPECT(dop->compute(fo, dins) == Status::ok);
+        EXPECT(cpu_f == want_f);
+    }
+#endif
+}
+
 int main()
 {
     int dev_count = 0;
@@ -505,6 +650,15 @@ int main()
     linear_q4_1_case(130, 300, 1000, false, "linear_q4_1_gemm_f32_ragged");
 
     contract_cases();
+
+    kat_quant_linear();
+    quant_linear_case({{64, 4096}, -1, 1, false, false}, "quant_linear_per_tensor_f32_s8", stream);
+    quant_linear_case({{70001}, -1, 1, true, true}, "quant_linear_per_tensor_ragged_f16_u8", nullptr);
+    quant_linear_case({{200, 1028}, -1, 200, false, true}, "quant_linear_per_token_f32_u8", stream);
+    quant_linear_case({{37, 75}, -1, 37, true, false}, "quant_linear_per_token_ragged_f16_s8", nullptr);
+    quant_linear_case({{5, 12, 24}, 1, 12, false, false}, "quant_linear_per_channel_axis1", stream);
+    quant_linear_case({{4, 100, 64}, 0, 4, true, true}, "quant_linear_per_channel_axis0_f16", stream);
+    quant_linear_case({{6, 50}, 1, 50, false, true}, "quant_linear_per_channel_last_axis", nullptr);
 
     CUDA_OK(cudaDeviceSynchronize());
     CUDA_OK(cudaStreamDestroy(stream));

@@ -1,6 +1,6 @@
 """Generate the golden fixtures of this directory from the compiled reference CPU route.
 
-    python tests/golden/make_golden.py        (needs oracle/_ref, i.e. the nnops source tree at build time)
+    python tests/golden/make_golden.py [name-prefix]     (needs oracle/_ref, i.e. the nnops source tree at build time)
 
 Each .npz holds seeded inputs, the reference's output and a JSON `meta` describing the call.
 The reference is driven through its public operator API (Linear / MatMul on Backend::CPU, via
@@ -20,9 +20,12 @@ import oracle  # noqa: E402
 from nnops_b200 import synth  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
+ONLY = ""   # optional name prefix given on the command line: regenerate only those fixtures
 
 
 def save(name, meta, **arrays):
+    if not name.startswith(ONLY):
+        return
     np.savez_compressed(HERE / f"{name}.npz", meta=np.array(json.dumps(meta)), **arrays)
     print("wrote", name, {k: v.shape for k, v in arrays.items()})
 
@@ -70,9 +73,31 @@ def q4_case(name, m, n, k, dtype, *, seed):
     save(name, dict(op="q4_1", k=k, out_dtype=dtype, rtol=1e-2 if dtype == "f16" else 2e-3), a=a, w_blocks=wb, out=out)
 
 
+def quant_case(name, shape, axis, per, fdt, qdt, *, seed):
+    """QuantizeLinear and DequantizeLinear of one tensor.  x carries exact .5 ties (in units of
+    its scale), infinities, a NaN and values far outside the 8-bit range."""
+    rng = np.random.default_rng(seed)
+    count = {"tensor": 1, "token": int(np.prod(shape[:-1])), "channel": shape[axis]}[per]
+    scale = rng.uniform(0.05, 3.0, count).astype(np.float32)
+    zdt = np.uint8 if qdt == "u8" else np.int8
+    zp = (rng.integers(0, 256, count) if qdt == "u8" else rng.integers(-128, 128, count)).astype(zdt)
+    x = (rng.standard_normal(shape) * 60).astype(fdt)
+    flat = x.reshape(-1)
+    flat[::5] = ((rng.integers(-90, 90, flat[::5].size) + 0.5) * scale[0]).astype(fdt)
+    flat[:3] = [np.inf, -np.inf, np.nan]
+    if fdt == np.float32:
+        flat[3:5] = [3e9, -3e9]
+    q = oracle.quantize_linear(x, scale, zp, axis=axis, out_dtype=zdt, impl="ref")
+    xq = (rng.integers(0, 256, shape) if qdt == "u8" else rng.integers(-128, 128, shape)).astype(zdt)
+    dq = oracle.dequantize_linear(xq, scale, zp, axis=axis, out_dtype=fdt, impl="ref")
+    save(name, dict(op="quant_linear", axis=axis), x=x, scale=scale, zero_point=zp, quantized=q, xq=xq,
+         dequantized=dq)
+
+
 if __name__ == "__main__":
     if not oracle.have_ref():
         raise SystemExit("the compiled reference (oracle/_ref) is not available on this machine")
+    ONLY = sys.argv[1] if len(sys.argv) > 1 else ""
     int8_case("i8_s32_bias", 128, 192, 256, "s32", seed=1, per_channel=False)
     int8_case("i8_s8_relu_per_channel", 160, 272, 512, "s8", seed=2, relu=True, out_scale=1.6)
     int8_case("i8_s8_saturating", 64, 128, 1024, "s8", seed=3, relu=True, out_scale=0.05)
@@ -89,3 +114,7 @@ if __name__ == "__main__":
     q4_case("q4_1_small_m_f16", 4, 128, 1024, "f16", seed=12)
     q4_case("q4_1_gemm_f32", 96, 160, 512, "f32", seed=13)
     q4_case("q4_1_gemm_f16", 160, 192, 512, "f16", seed=14)
+    quant_case("qdq_per_tensor_f32_s8", (7, 1003), -1, "tensor", np.float32, "s8", seed=20)
+    quant_case("qdq_per_token_f16_u8", (37, 75), -1, "token", np.float16, "u8", seed=21)
+    quant_case("qdq_per_channel_f32_u8", (5, 12, 24), 1, "channel", np.float32, "u8", seed=22)
+    quant_case("qdq_per_channel_last_axis_f16_s8", (6, 50), 1, "channel", np.float16, "s8", seed=23)

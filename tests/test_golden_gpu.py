@@ -28,6 +28,14 @@ def test_cuda_matches_golden(cuda_device, nnb200_lib, path):
         got = ops.gemm_i8(a, w, out_kind=meta["out_kind"], relu=meta["relu"],
                           activation="relu" if meta["relu"] and meta["out_kind"] in ("f32", "f16") else "none", **kw)
         assert np.array_equal(got.cpu().numpy().view(np.uint8), z["out"].view(np.uint8))
+    elif meta["op"] == "quant_linear":
+        scale, zp = torch.from_numpy(z["scale"]), torch.from_numpy(z["zero_point"])
+        q = ops.quantize_linear(torch.from_numpy(z["x"]).to(dev), scale, zp, axis=meta["axis"],
+                                out_dtype=torch.from_numpy(z["quantized"]).dtype)
+        assert np.array_equal(q.cpu().numpy(), z["quantized"])
+        dq = ops.dequantize_linear(torch.from_numpy(z["xq"]).to(dev), scale, zp, axis=meta["axis"],
+                                   out_dtype=torch.from_numpy(z["dequantized"]).dtype)
+        assert np.array_equal(dq.cpu().numpy().view(np.uint8), z["dequantized"].view(np.uint8))
     else:
         a = torch.from_numpy(z["a"]).to(dev)
         w = torch.from_numpy(z["w_blocks"]).to(dev)

@@ -133,9 +133,118 @@ def test_port_matches_golden(path):
         w = z["w"].T if meta.get("w_kn") else z["w"]
         out = oracle.gemm_i8(a, w, out_kind=meta["out_kind"], relu=meta["relu"], **kw)
         assert np.array_equal(out.view(np.uint8), z["out"].view(np.uint8))
+    elif meta["op"] == "quant_linear":
+        q = oracle.quantize_linear(z["x"], z["scale"], z["zero_point"], axis=meta["axis"],
+                                   out_dtype=z["quantized"].dtype)
+        assert np.array_equal(q, z["quantized"])
+        dq = oracle.dequantize_linear(z["xq"], z["scale"], z["zero_point"], axis=meta["axis"],
+                                      out_dtype=z["dequantized"].dtype)
+        assert np.array_equal(dq.view(np.uint8), z["dequantized"].view(np.uint8))
     else:
         out = oracle.q4_1_matmul(z["a"], z["w_blocks"], meta["k"], out_dtype=meta["out_dtype"],
                                  w_round_f16=meta["out_dtype"] == "f16")
         ref = z["out"].astype(np.float32)
         tol = meta["rtol"] * np.abs(ref) + meta["rtol"] * float(np.sqrt(np.mean(ref * ref)))
         assert np.all(np.abs(out.astype(np.float32) - ref) <= tol)
+
+
+# ---- QuantizeLinear / DequantizeLinear ------------------------------------------------------
+
+def test_quantize_known_answers():
+    """Round half to even, saturation, and the x86 conversion's out-of-range rule
+    (arithmetic: src/backend/cpu/x86_64/quant.hpp:117-165)."""
+    x = np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 1000.0, -1000.0, np.inf, -np.inf, np.nan, 3e9], dtype=np.float32)
+    q = oracle.quantize_linear(x, [1.0], np.array([0], np.int8))
+    assert q.tolist() == [0, 2, 2, 0, -2, -2, 127, -128, -128, -128, -128, -128]
+    q = oracle.quantize_linear(x, [1.0], np.array([10], np.uint8), out_dtype=np.uint8)
+    assert q.tolist() == [10, 12, 12, 10, 8, 8, 255, 0, 0, 0, 0, 0]
+    # per channel along axis 0: row r uses scale[r]
+    x2 = np.array([[1.0, 2.0], [1.0, 2.0]], dtype=np.float32)
+    q2 = oracle.quantize_linear(x2, [0.5, 0.25], np.array([1, -1], np.int8), axis=0)
+    assert q2.tolist() == [[3, 5], [3, 7]]
+
+
+def test_dequantize_known_answers():
+    q = np.array([-128, -1, 0, 1, 127], dtype=np.int8)
+    y = oracle.dequantize_linear(q, [0.5], np.array([1], np.int8))
+    assert y.tolist() == [-64.5, -1.0, -0.5, 0.0, 63.0]
+    y16 = oracle.dequantize_linear(q.view(np.uint8), [0.25], np.array([128], np.uint8), out_dtype=np.float16)
+    assert y16.dtype == np.float16 and y16.tolist() == [0.0, 31.75, -32.0, -31.75, -0.25]
+
+
+def test_dequantize_body_and_tail_round_differently():
+    """The first inner - inner % 16 elements of a row go through fma(q, s, -zp*s), the rest
+    through (q - zp) * s; with a zero point the two forms differ in the last bit for some
+    inputs, and the restatement keeps the position rule."""
+    rng = np.random.default_rng(5)
+    rows = 4000
+    q = rng.integers(-128, 128, (rows, 15)).astype(np.int8)
+    s = rng.uniform(0.001, 3, rows).astype(np.float32)
+    z = rng.integers(-128, 128, rows).astype(np.int8)
+    tail = oracle.dequantize_linear(q, s, z)                                     # 15 < 16: all tail
+    body = oracle.dequantize_linear(np.concatenate([q, q[:, :1]], axis=1), s, z)[:, :15]   # 16: all body
+    assert np.count_nonzero(tail != body) > 0
+    want_tail = (q.astype(np.float32) - z[:, None].astype(np.float32)) * s[:, None]
+    assert np.array_equal(tail, want_tail.astype(np.float32))
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="compiled reference not runnable on this host")
+def test_quant_linear_port_matches_reference():
+    rng = np.random.default_rng(9)
+    cases = [((70001,), -1, 1), ((37, 75), -1, 37), ((5, 12, 23), 1, 12), ((6, 50), 1, 50), ((4, 100, 64), 0, 4),
+             ((3000, 15), -1, 3000)]
+    for shape, axis, count in cases:
+        scale = rng.uniform(0.05, 3.0, count).astype(np.float32)
+        for fdt in (np.float32, np.float16):
+            x = (rng.standard_normal(shape) * 40).astype(fdt)
+            flat = x.reshape(-1)
+            flat[::7] = ((rng.integers(-300, 300, flat[::7].size) + 0.5) * scale[0]).astype(fdt)
+            flat[:3] = [np.inf, -np.inf, np.nan]
+            for qdt in (np.int8, np.uint8):
+                zp = (rng.integers(-20, 20, count) if qdt == np.int8 else rng.integers(0, 255, count)).astype(qdt)
+                assert np.array_equal(oracle.quantize_linear(x, scale, zp, axis=axis, out_dtype=qdt),
+                                      oracle.quantize_linear(x, scale, zp, axis=axis, out_dtype=qdt, impl="ref"))
+                xq = (rng.integers(-128, 128, shape) if qdt == np.int8 else rng.integers(0, 256, shape)).astype(qdt)
+                p = oracle.dequantize_linear(xq, scale, zp, axis=axis, out_dtype=fdt)
+                r = oracle.dequantize_linear(xq, scale, zp, axis=axis, out_dtype=fdt, impl="ref")
+                assert np.array_equal(p.view(np.uint8), r.view(np.uint8)), (shape, axis, fdt, qdt)
+
+
+# Known-answer cases of the reference's own operator test (tests/test_quant_linear.cpp:35-300 for
+# QuantizeLinear, :361-500 for DequantizeLinear): (x, scale, zero point, axis, expected).
+_REF_QUANTIZE_KATS = [
+    ([0.0, 1.0, 2.0], [1.0], np.array([0], np.int8), -1, [0, 1, 2]),
+    ([0.0, 2.0, 4.0], [2.0], np.array([0], np.int8), -1, [0, 1, 2]),
+    ([0.0, 1.0, 2.0], [1.0], np.array([100], np.int8), -1, [100, 101, 102]),
+    ([-1.0, 0.0, 1.0, 300.0], [1.0], np.array([0], np.uint8), -1, [0, 0, 1, 255]),
+    ([0.0, 1.0, -1.0], [1.0], np.array([128], np.uint8), -1, [128, 129, 127]),
+    ([[0.0, 1.0, 2.0], [10.0, 11.0, 12.0]], [1.0, 2.0, 3.0], np.zeros(3, np.int8), 1, [[0, 0, 1], [10, 6, 4]]),
+    ([[0.0, 1.0, 2.0], [10.0, 20.0, 30.0]], [1.0, 10.0], np.zeros(2, np.int8), -1, [[0, 1, 2], [1, 2, 3]]),
+    ([[[0.0, 1.0], [2.0, 4.0]], [[10.0, 20.0], [30.0, 40.0]]], [1.0, 2.0, 5.0, 10.0], np.zeros(4, np.int8), -1,
+     [[[0, 1], [1, 2]], [[2, 4], [3, 4]]]),
+]
+_REF_DEQUANTIZE_KATS = [
+    (np.array([0, 1, -1], np.int8), [1.0], np.array([0], np.int8), -1, [0.0, 1.0, -1.0]),
+    (np.array([100, 101, 102], np.int8), [2.0], np.array([100], np.int8), -1, [0.0, 2.0, 4.0]),
+    (np.array([128, 129, 127], np.uint8), [0.5], np.array([128], np.uint8), -1, [0.0, 0.5, -0.5]),
+    (np.array([[0, 0, 1], [10, 5, 4]], np.int8), [1.0, 2.0, 3.0], np.zeros(3, np.int8), 1,
+     [[0.0, 0.0, 3.0], [10.0, 10.0, 12.0]]),
+    (np.array([[1, 2, 3], [4, 5, 6]], np.int8), [0.5, 2.0], np.zeros(2, np.int8), -1,
+     [[0.5, 1.0, 1.5], [8.0, 10.0, 12.0]]),
+]
+
+
+@pytest.mark.parametrize("case", range(len(_REF_QUANTIZE_KATS)))
+def test_quantize_reference_kats(case):
+    x, scale, zp, axis, want = _REF_QUANTIZE_KATS[case]
+    got = oracle.quantize_linear(np.array(x, np.float32), scale, zp, axis=axis, out_dtype=zp.dtype)
+    assert got.tolist() == want
+    got16 = oracle.quantize_linear(np.array(x, np.float16), scale, zp, axis=axis, out_dtype=zp.dtype)
+    assert got16.tolist() == want
+
+
+@pytest.mark.parametrize("case", range(len(_REF_DEQUANTIZE_KATS)))
+def test_dequantize_reference_kats(case):
+    x, scale, zp, axis, want = _REF_DEQUANTIZE_KATS[case]
+    assert oracle.dequantize_linear(x, scale, zp, axis=axis).tolist() == want
+    assert oracle.dequantize_linear(x, scale, zp, axis=axis, out_dtype=np.float16).tolist() == want
