@@ -212,17 +212,21 @@ NNB200_API int nnb200_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int6
  * every outer group: per tensor = [1][1][numel], per token = [1][numel/last][last], per channel
  * (axis a) = [prod(shape[:a])][shape[a]][prod(shape[a+1:])].  x, y, scale and zero_point are
  * device pointers; the floating side is f32 or f16, the integer side s8 or u8, the zero point
- * s8 or u8 on its own flag.
+ * s8, u8 or int32 on its own flag.
  *   quantize:   y = saturate(round_half_even(fma(x, 1/scale, zero_point)))
  *   dequantize: y = (x - zero_point) * scale   (rounded as the reference's kernels round it)
  */
+#define NNB200_ZP_S8 0
+#define NNB200_ZP_U8 1
+#define NNB200_ZP_S32 2 /* the int32 zero points of a view's QuantParams (fp-activation route) */
+
 typedef struct nnb200_quant_linear_args {
     const void* x;
     void* y;
     int64_t outer, rows, inner;
     const float* scale;     /* [rows] */
     const void* zero_point; /* [rows], s8 or u8 */
-    int32_t zp_unsigned;
+    int32_t zp_unsigned;    /* NNB200_ZP_*: storage type of zero_point */
     int32_t float_f16;      /* floating side (x of quantize, y of dequantize) is f16, else f32 */
     int32_t int_unsigned;   /* integer side (y of quantize, x of dequantize) is u8, else s8 */
 } nnb200_quant_linear_args;

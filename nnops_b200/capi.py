@@ -65,6 +65,9 @@ class Q41Args(C.Structure):
 Q4_FLAG_OVERLAP_PREVIOUS = 1
 
 # Every symbol include/nnb200.h declares: (name, restype, argtypes).
+ZP_S8, ZP_U8, ZP_S32 = 0, 1, 2   # nnb200_quant_linear_args.zp_unsigned: storage type of the zero points
+
+
 class QuantLinearArgs(C.Structure):
     """Mirror of nnb200_quant_linear_args."""
     _fields_ = [

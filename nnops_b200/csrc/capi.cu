@@ -382,7 +382,11 @@ static int quant_linear_call(const nnb200_quant_linear_args* q, void* stream, bo
     if (q->outer == 0 || q->rows == 0 || q->inner == 0) {
         return NNB200_OK;
     }
-    if (q->x == nullptr || q->y == nullptr || q->scale == nullptr || q->zero_point == nullptr) {
+    if (q->x == nullptr || q->y == nullptr || q->scale == nullptr || q->zero_point == nullptr ||
+        q->zp_unsigned < NNB200_ZP_S8 || q->zp_unsigned > NNB200_ZP_S32) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if (q->zp_unsigned == NNB200_ZP_S32 && (reinterpret_cast<uintptr_t>(q->zero_point) & 3u) != 0) {
         return NNB200_INVALID_ARGUMENT;
     }
     // The element count must fit the kernels' 64-bit signed indexing.

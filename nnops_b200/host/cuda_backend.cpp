@@ -9,7 +9,10 @@
 //
 //   * s8/u8 x s8 -> s32 | s8 | u8 | f32 | f16 with the fused epilogue (every pose, batch
 //     broadcast over up to four leading axes);
-//   * f16/f32 x q4_1 [N,K] -> f16/f32, which the reference serves on the CPU only.
+//   * f16/f32 x q4_1 [N,K] -> f16/f32, which the reference serves on the CPU only;
+//   * f16/f32 activations carrying QuantParams x s8 weights -> the activation dtype: quantize
+//     on the fly, int8 GEMM, dequantizing epilogue (CPU-only in the reference,
+//     src/backend/cpu/matmul/matmul_i8.cpp:389-464).
 //
 // Compiled against the real nnops headers when NNB200_USE_NNOPS_HEADERS is defined (the
 // maintainer's integration), else against the stand-alone mirror.
@@ -31,6 +34,7 @@
 #include <algorithm>
 #include <array>
 #include <cstring>
+#include <vector>
 
 namespace nnops::backend::cuda {
 
@@ -296,6 +300,119 @@ Status run_i8(const I8Call& c, const ComputeContext& ctx)
     return Status::ok;
 }
 
+// f32/f16 activations with active per-tensor / per-token QuantParams x s8 weights: A is
+// quantised with ITS parameters (fma(x, 1/scale, zp), round-half-even, saturate to
+// act_dtype -- the QuantizeLinear arithmetic), the int8 GEMM runs on the result and its
+// dequantizing epilogue writes A's dtype.  Per-token arrays are indexed by the global row over
+// all leading axes, as the reference's dequantizing route does (matmul_tile_impl.h:454-463).
+Status run_dq_from_fp(const TensorView& a, const TensorView& w, const TensorView* bias, TensorView& out,
+                      bool transpose_a, bool w_is_nk, DataType act_dtype, const Epilogue& ep,
+                      const ComputeContext& ctx)
+{
+    const QuantParams& qp = a.quant_params();
+    const bool quantized = qp.is_active() && (qp.granularity == QuantGranularity::PerTensor ||
+                                              qp.granularity == QuantGranularity::PerToken);
+    if (!quantized) {
+        return Status::invalid_argument;  // a float A without parameters is not a quantized tensor
+    }
+    if (transpose_a || out.data_type() != a.data_type()) {
+        return Status::unsupported;
+    }
+    if (act_dtype != DataType::s8 && act_dtype != DataType::u8) {
+        return Status::unsupported;
+    }
+    if (a.rank() < 2 || w.rank() != 2 || out.rank() != a.rank()) {
+        return Status::unsupported;  // batched weights are not served on this route
+    }
+    const int64_t K = a.shape(a.rank() - 1);
+    const int64_t rows = K > 0 ? a.numel() / K : 0;
+    if (a.row_stride_elems() != K) {
+        return Status::unsupported;  // the quantising pass walks A as one dense array
+    }
+    const bool per_token = qp.scale_data != nullptr || qp.zero_point_data != nullptr;
+    const int64_t count = per_token ? rows : 1;
+
+    // Scratch: A_q, then scale / zero-point arrays when they are not already on the device.
+    Staging st(ctx.cuda_stream);
+    st.reserve_raw(static_cast<size_t>(rows * K));
+    const size_t p_bytes = static_cast<size_t>(count) * 4;
+    const bool scale_dev = qp.scale_data != nullptr && nnb200_is_device_pointer(qp.scale_data) != 0;
+    const bool zp_dev = qp.zero_point_data != nullptr && nnb200_is_device_pointer(qp.zero_point_data) != 0;
+    if (!scale_dev) {
+        st.reserve_raw(p_bytes);
+    }
+    if (!zp_dev) {
+        st.reserve_raw(p_bytes);
+    }
+    if (const int e = st.allocate(); e != NNB200_OK) {
+        return to_status(e);
+    }
+    void* aq = st.take_raw(static_cast<size_t>(rows * K));
+    std::vector<float> scale_h;
+    std::vector<int32_t> zp_h;
+    const float* scale_d = qp.scale_data;
+    const void* zp_d = qp.zero_point_data;
+    if (!scale_dev) {
+        if (qp.scale_data != nullptr) {
+            scale_h.assign(qp.scale_data, qp.scale_data + count);
+        } else {
+            scale_h.assign(static_cast<size_t>(count), qp.scale);
+        }
+        void* d = st.take_raw(p_bytes);
+        if (const int e = nnb200_copy_h2d_async(d, scale_h.data(), p_bytes, ctx.cuda_stream); e != NNB200_OK) {
+            return to_status(e);
+        }
+        scale_d = static_cast<const float*>(d);
+    }
+    if (!zp_dev) {
+        if (qp.zero_point_data != nullptr) {
+            zp_h.assign(qp.zero_point_data, qp.zero_point_data + count);
+        } else {
+            zp_h.assign(static_cast<size_t>(count), qp.zero_point);
+        }
+        void* d = st.take_raw(p_bytes);
+        if (const int e = nnb200_copy_h2d_async(d, zp_h.data(), p_bytes, ctx.cuda_stream); e != NNB200_OK) {
+            return to_status(e);
+        }
+        zp_d = d;
+    }
+    // The staged host vectors are pageable memory: the copies above have completed from the
+    // host's point of view when the calls return (pageable cudaMemcpyAsync stages first).
+
+    nnb200_quant_linear_args q;
+    std::memset(&q, 0, sizeof(q));
+    q.x = a.ptr<void>();
+    q.y = aq;
+    q.outer = 1;
+    q.rows = per_token ? rows : 1;
+    q.inner = per_token ? K : rows * K;
+    q.scale = scale_d;
+    q.zero_point = zp_d;
+    q.zp_unsigned = NNB200_ZP_S32;
+    q.float_f16 = a.data_type() == DataType::f16;
+    q.int_unsigned = act_dtype == DataType::u8;
+    if (const int e = nnb200_quantize_linear(&q, ctx.cuda_stream); e != NNB200_OK) {
+        return to_status(e);
+    }
+
+    // The int8 GEMM over A_q as one tall [rows, K] matrix with A's parameters.
+    const int64_t a2[] = {rows, K};
+    const int64_t o2[] = {rows, out.shape(out.rank() - 1)};
+    QuantParams aq_qp = qp;
+    if (per_token) {
+        aq_qp.scale_data = qp.scale_data != nullptr ? scale_d : nullptr;
+        aq_qp.zero_point_data = qp.zero_point_data != nullptr ? static_cast<const int32_t*>(zp_d) : nullptr;
+    }
+    TensorView aq_view(a2, act_dtype, aq, TensorLayout::Dense, aq_qp);
+    TensorView out2(o2, out.data_type(), out.ptr<void>(), out.pitch(), TensorLayout::Dense, out.quant_params());
+    int kind;
+    if (!out_kind_of(out.data_type(), kind)) {
+        return Status::unsupported;
+    }
+    const I8Call call{&aq_view, &w, bias, &out2, false, w_is_nk, &ep, kind};
+    return run_i8(call, ctx);
+}
+
 // f16/f32 activations x q4_1 weights stored [N, K].
 Status run_q4_1(const TensorView& x, const TensorView& w, const TensorView* bias, TensorView& out, float alpha,
                 const Epilogue& ep, const ComputeContext& ctx)
@@ -384,6 +501,15 @@ Status linear_cuda(const LinearAttributes& attrs, TensorView& output, std::span<
         }
         return run_q4_1(x, w, bias, output, 1.0f, attrs.epilogue, ctx);
     }
+    if ((x.data_type() == DataType::f32 || x.data_type() == DataType::f16) && w.data_type() == DataType::s8) {
+        if (output.numel() == 0) {
+            return Status::ok;
+        }
+        if (attrs.add_to) {
+            return Status::unsupported;
+        }
+        return run_dq_from_fp(x, w, bias, output, false, true, DataType::s8, attrs.epilogue, ctx);
+    }
     return Status::unsupported;  // dense fp Linear is outside this backend
 }
 
@@ -413,6 +539,16 @@ Status matmul_cuda(const MatMulAttributes& attrs, TensorView& output, std::span<
             return Status::unsupported;
         }
         return run_q4_1(a, b, bias, output, attrs.alpha, attrs.epilogue, ctx);
+    }
+    if ((a.data_type() == DataType::f32 || a.data_type() == DataType::f16) && b.data_type() == DataType::s8) {
+        if (output.numel() == 0) {
+            return Status::ok;
+        }
+        if (attrs.beta != 0.0f) {
+            return Status::unsupported;
+        }
+        return run_dq_from_fp(a, b, bias, output, attrs.transpose_a, attrs.transpose_b, attrs.act_quant_dtype,
+                              attrs.epilogue, ctx);
     }
     return Status::unsupported;
 }

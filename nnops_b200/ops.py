@@ -226,3 +226,27 @@ def dequantize_linear(x: torch.Tensor, scale, zero_point, *, axis: int = -1, out
         capi.check(capi.lib().nnb200_dequantize_linear(C.byref(args), _stream_ptr(x.device)),
                    "nnb200_dequantize_linear")
     return y
+
+
+def linear_fp_act(a: torch.Tensor, w: torch.Tensor, *, scale_a, zp_a=0, act_dtype: torch.dtype = torch.int8, **kw):
+    """f32/f16 activations carrying quantization parameters x s8 weights [N,K] -> a's dtype:
+    the same two C-ABI calls the C++ backend glue makes for this route (quantise A with its
+    per-tensor / per-token scale and int32 zero point, then the int8 matmul with the
+    dequantizing epilogue).  ``scale_a`` / ``zp_a`` are scalars or per-row arrays."""
+    if a.dim() != 2 or a.dtype not in (torch.float32, torch.float16) or not a.is_contiguous():
+        raise ValueError("a must be a contiguous 2-D f32/f16 tensor")
+    m, k = a.shape
+    per_token = not (isinstance(scale_a, (int, float)) and isinstance(zp_a, int))
+    count = m if per_token else 1
+    scale = torch.as_tensor(scale_a, dtype=torch.float32).reshape(-1).to(a.device).expand(count).contiguous()
+    zp = torch.as_tensor(zp_a, dtype=torch.int32).reshape(-1).to(a.device).expand(count).contiguous()
+    aq = torch.empty((m, k), dtype=act_dtype, device=a.device)
+    outer, rows, inner = (1, m, k) if per_token else (1, 1, m * k)
+    args = capi.QuantLinearArgs(x=a.data_ptr(), y=aq.data_ptr(), outer=outer, rows=rows, inner=inner,
+                                scale=scale.data_ptr(), zero_point=zp.data_ptr(), zp_unsigned=capi.ZP_S32,
+                                float_f16=int(a.dtype == torch.float16), int_unsigned=int(act_dtype == torch.uint8))
+    with torch.cuda.device(a.device):
+        capi.check(capi.lib().nnb200_quantize_linear(C.byref(args), _stream_ptr(a.device)), "nnb200_quantize_linear")
+    out_kind = "f32" if a.dtype == torch.float32 else "f16"
+    return gemm_i8(aq, w, out_kind=out_kind, scale_a=scale if per_token else float(scale_a),
+                   zp_a=zp if per_token else int(zp_a), **kw)

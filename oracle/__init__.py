@@ -293,3 +293,60 @@ def dequantize_linear(x: np.ndarray, scale, zero_point, *, axis: int = -1, out_d
         if st != 0:
             raise RuntimeError(f"reference op returned Status {st}")
     return y
+
+
+def linear_fp_act(a: np.ndarray, w: np.ndarray, *, scale_a, zp_a=0, act_dtype=np.int8, bias: np.ndarray | None = None,
+                  relu: bool = False, scale_w=1.0, zp_w=0, min_clip: float = -np.inf, max_clip: float = np.inf,
+                  impl: str = "port", threads: int | None = None) -> np.ndarray:
+    """f32/f16 activations carrying quantization parameters x s8 weights [N,K] -> a's dtype:
+    quantise A on the fly (QuantizeLinear arithmetic with A's per-tensor / per-token scale and
+    int32 zero point), int8 matmul, dequantizing epilogue
+    (reference src/backend/cpu/matmul/matmul_i8.cpp:389-464)."""
+    assert a.ndim == 2 and a.dtype in (np.float32, np.float16) and w.dtype == np.int8
+    a = np.ascontiguousarray(a)
+    m, k = a.shape
+    out_kind = "f32" if a.dtype == np.float32 else "f16"
+    if impl == "port":
+        per_token = not (np.isscalar(scale_a) and np.isscalar(zp_a))
+        count = m if per_token else 1
+        s = np.ascontiguousarray(np.broadcast_to(np.asarray(scale_a, dtype=np.float32), (count,)))
+        z = np.ascontiguousarray(np.broadcast_to(np.asarray(zp_a, dtype=np.int32), (count,)))
+        aq = np.zeros((m, k), dtype=act_dtype)
+        outer, rows, inner = (1, m, k) if per_token else (1, 1, m * k)
+        port_lib().oracle_quantize_linear(
+            C.c_void_p(a.ctypes.data), C.c_int(a.dtype == np.float16), C.c_int64(outer), C.c_int64(rows),
+            C.c_int64(inner), C.c_void_p(s.ctypes.data), C.c_void_p(z.ctypes.data), C.c_int(2),
+            C.c_void_p(aq.ctypes.data), C.c_int(aq.dtype == np.uint8), C.c_int(1))
+        return gemm_i8(aq, w, out_kind=out_kind, bias=bias, relu=relu, scale_a=scale_a, scale_w=scale_w, zp_a=zp_a,
+                       zp_w=zp_w, min_clip=min_clip, max_clip=max_clip)
+    lib = ref_lib()
+    if lib is None:
+        raise RuntimeError("reference route not available on this host")
+    assert act_dtype == np.int8, "the reference Linear quantises activations to s8"
+    n = w.shape[0]
+    out = np.zeros((m, n), dtype=_OUT_NP[out_kind])
+    keep = []
+
+    def arr(v, dt):
+        if np.isscalar(v):
+            return None, dt(v)
+        v = np.ascontiguousarray(v, dtype=dt)
+        keep.append(v)
+        return v, dt(1 if dt is np.float32 else 0)
+
+    sa, sa0 = arr(scale_a, np.float32)
+    sw, sw0 = arr(scale_w, np.float32)
+    za, za0 = arr(zp_a, np.int32)
+    zw, zw0 = arr(zp_w, np.int32)
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, dtype=_OUT_NP[out_kind])
+    args = GemmI8Args(
+        a=a.ctypes.data, w=w.ctypes.data, out=out.ctypes.data, m=m, n=n, k=k, a_stride_m=k, a_stride_k=1,
+        w_stride_n=w.strides[0], w_stride_k=1, ldc=n, a_unsigned=2 if a.dtype == np.float32 else 3,
+        out_kind=OUT_KINDS[out_kind], bias=_ptr(bias), relu=int(relu), scale_a=_ptr(sa), scale_w=_ptr(sw),
+        zp_a=_ptr(za), zp_w=_ptr(zw), scale_a_scalar=float(sa0), scale_w_scalar=float(sw0), zp_a_scalar=int(za0),
+        zp_w_scalar=int(zw0), out_scale=1.0, out_zp=0, min_clip=float(min_clip), max_clip=float(max_clip))
+    st = lib.ref_gemm_i8(C.byref(args), 1, int(threads or ref_threads()))
+    if st != 0:
+        raise RuntimeError(f"reference op returned Status {st}")
+    return out

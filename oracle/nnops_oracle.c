@@ -371,6 +371,15 @@ void oracle_q4_1_matmul(const void* a, int a_is_f16, int64_t lda,
  * reading of the scalar tail, quant.hpp:159-164); the reference compiled with its own flags
  * contracts it into the same fma as the vector body, which tests/test_oracle.py pins.
  */
+/* zp_kind: 0 = s8, 1 = u8, 2 = int32 storage. */
+static float load_zero_point(const void* zero_point, int zp_kind, int64_t r)
+{
+    if (zp_kind == 2) {
+        return (float)((const int32_t*)zero_point)[r];
+    }
+    return zp_kind == 1 ? (float)((const uint8_t*)zero_point)[r] : (float)((const int8_t*)zero_point)[r];
+}
+
 static int32_t cvt_rne_x86(float v)
 {
     if (!(v >= -2147483648.0f && v < 2147483648.0f)) {
@@ -380,7 +389,7 @@ static int32_t cvt_rne_x86(float v)
 }
 
 void oracle_quantize_linear(const void* x, int x_is_f16, int64_t outer, int64_t rows, int64_t inner,
-                            const float* scale, const void* zero_point, int zp_is_u8,
+                            const float* scale, const void* zero_point, int zp_kind,
                             void* y, int y_is_u8, int tail_fused)
 {
     const int32_t qmin = y_is_u8 ? 0 : -128;
@@ -389,7 +398,7 @@ void oracle_quantize_linear(const void* x, int x_is_f16, int64_t outer, int64_t 
     for (int64_t o = 0; o < outer; ++o) {
         for (int64_t r = 0; r < rows; ++r) {
             const float inv = 1.0f / scale[r];
-            const float zp = zp_is_u8 ? (float)((const uint8_t*)zero_point)[r] : (float)((const int8_t*)zero_point)[r];
+            const float zp = load_zero_point(zero_point, zp_kind, r);
             const int64_t base = (o * rows + r) * inner;
             for (int64_t i = 0; i < inner; ++i) {
                 const float xv = x_is_f16 ? oracle_f16_to_f32(((const uint16_t*)x)[base + i]) : ((const float*)x)[base + i];
@@ -413,14 +422,14 @@ void oracle_quantize_linear(const void* x, int x_is_f16, int64_t outer, int64_t 
 }
 
 void oracle_dequantize_linear(const void* x, int x_is_u8, int64_t outer, int64_t rows, int64_t inner,
-                              const float* scale, const void* zero_point, int zp_is_u8,
+                              const float* scale, const void* zero_point, int zp_kind,
                               void* y, int y_is_f16)
 {
     const int64_t body = inner - inner % 16;
     for (int64_t o = 0; o < outer; ++o) {
         for (int64_t r = 0; r < rows; ++r) {
             const float s = scale[r];
-            const float zp = zp_is_u8 ? (float)((const uint8_t*)zero_point)[r] : (float)((const int8_t*)zero_point)[r];
+            const float zp = load_zero_point(zero_point, zp_kind, r);
             const float neg_zs = -zp * s;
             const int64_t base = (o * rows + r) * inner;
             for (int64_t i = 0; i < inner; ++i) {

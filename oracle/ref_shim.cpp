@@ -91,10 +91,16 @@ int ref_gemm_i8(const GemmI8Args* p, int use_linear, int threads)
     const int64_t a_shape[2] = {ta ? p->k : p->m, ta ? p->m : p->k};
     const int64_t w_shape[2] = {tb ? p->n : p->k, tb ? p->k : p->n};
     const int64_t o_shape[2] = {p->m, p->n};
-    const DataType adt = p->a_unsigned ? DataType::u8 : DataType::s8;
+    // a_unsigned doubles as the activation dtype selector: 0 = s8, 1 = u8, 2 = f32, 3 = f16 (the
+    // fp-activation route: A is quantised on the fly with the parameters given for A).
+    const DataType adt = p->a_unsigned == 3 ? DataType::f16
+                         : p->a_unsigned == 2 ? DataType::f32
+                         : p->a_unsigned == 1 ? DataType::u8
+                                              : DataType::s8;
+    const int64_t a_elem = int64_t(data_type_size(adt));
     const DataType odt = out_dtype(p->out_kind);
 
-    TensorView a(a_shape, adt, const_cast<void*>(p->a), ta ? p->a_stride_k : p->a_stride_m,
+    TensorView a(a_shape, adt, const_cast<void*>(p->a), (ta ? p->a_stride_k : p->a_stride_m) * a_elem,
                  TensorLayout::Dense,
                  make_qp(p->scale_a, p->zp_a, p->scale_a_scalar, p->zp_a_scalar, p->m,
                          QuantGranularity::PerToken));

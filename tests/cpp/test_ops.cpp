@@ -475,6 +475,114 @@ static void contract_cases()
     EXPECT(op->getWorkspaceSize({}, {}) == 0);
 }
 
+// ---- f32/f16 activations carrying QuantParams x s8 weights ---------------------------------
+// (the reference's CPU-only quantize-on-the-fly route, src/backend/cpu/matmul/matmul_i8.cpp:389-464)
+
+static void linear_fp_act_case(int64_t batch, int64_t m, int64_t n, int64_t k, bool f16, bool per_token, bool zero_points,
+                               bool relu, const char* name, cudaStream_t stream)
+{
+    g_case = name;
+    const int64_t rows = batch * m;
+    std::mt19937_64 rng(m * 31 + n * 7 + k);
+    std::normal_distribution<float> nd(0.0f, 2.0f);
+    std::uniform_real_distribution<float> us(0.001f, 0.02f), ua(0.01f, 0.05f);
+    std::vector<float> xf(rows * k), sa(rows), sw(n), bias_f(n);
+    std::vector<uint16_t> xh(rows * k), bias_h(n);
+    std::vector<int8_t> w(n * k);
+    std::vector<int32_t> za(rows);
+    for (auto& v : xf) v = nd(rng);
+    for (int64_t i = 0; i < rows * k; ++i) {
+        xh[i] = oracle_f32_to_f16(xf[i]);
+        if (f16) xf[i] = oracle_f16_to_f32(xh[i]);
+    }
+    for (auto& v : w) v = static_cast<int8_t>(static_cast<int>(rng() % 255) - 127);
+    for (auto& v : sa) v = ua(rng);
+    for (auto& v : sw) v = us(rng);
+    for (auto& v : za) v = zero_points ? static_cast<int32_t>(rng() % 19) - 9 : 0;
+    for (int64_t i = 0; i < n; ++i) {
+        bias_f[i] = 0.01f * static_cast<float>(static_cast<int>(rng() % 2001) - 1000);
+        bias_h[i] = oracle_f32_to_f16(bias_f[i]);
+    }
+    const float sa0 = 0.03f;
+    const int32_t za0 = zero_points ? 3 : 0;
+    const void* x_host = f16 ? static_cast<const void*>(xh.data()) : static_cast<const void*>(xf.data());
+    const void* bias_host = f16 ? static_cast<const void*>(bias_h.data()) : static_cast<const void*>(bias_f.data());
+    const size_t fsz = f16 ? 2 : 4;
+    const DataType fdt = f16 ? DataType::f16 : DataType::f32;
+
+    // Expected: quantise with the oracle, then its int8 matmul with the dequantizing epilogue.
+    std::vector<int8_t> aq(rows * k);
+    const float s1[1] = {sa0};
+    const int32_t z1[1] = {za0};
+    oracle_quantize_linear(x_host, f16, 1, per_token ? rows : 1, per_token ? k : rows * k, per_token ? sa.data() : s1,
+                           per_token ? static_cast<const void*>(za.data()) : static_cast<const void*>(z1), 2, aq.data(),
+                           0, 1);
+    std::vector<uint8_t> want(rows * n * fsz);
+    oracle_gemm_i8_args o{};
+    o.a = aq.data(); o.w = w.data(); o.out = want.data();
+    o.m = rows; o.n = n; o.k = k;
+    o.a_stride_m = k; o.a_stride_k = 1; o.w_stride_n = k; o.w_stride_k = 1; o.ldc = n;
+    o.out_kind = f16 ? 4 : 3;
+    o.bias = bias_host;
+    o.relu = relu;
+    o.scale_a = per_token ? sa.data() : nullptr;
+    o.zp_a = per_token && zero_points ? za.data() : nullptr;
+    o.scale_w = sw.data();
+    o.scale_a_scalar = per_token ? 1.0f : sa0;
+    o.scale_w_scalar = 1.0f;
+    o.zp_a_scalar = per_token ? 0 : za0;
+    o.out_scale = 1.0f;
+    o.min_clip = -INFINITY; o.max_clip = INFINITY;
+    oracle_gemm_i8(&o);
+
+    DevBuf dx(x_host, rows * k * fsz), dw(w.data(), w.size()), dbias(bias_host, n * fsz), dout(want.size(), 0x5A);
+    QuantParams qa = per_token ? arrays(sa.data(), zero_points ? za.data() : nullptr, rows, QuantGranularity::PerToken)
+                               : per_tensor(sa0, za0);
+    QuantParams qw = arrays(sw.data(), nullptr, n, QuantGranularity::PerChannel);
+    const int64_t xs3[] = {batch, m, k}, xs2[] = {m, k}, ws[] = {n, k}, bs[] = {n}, os3[] = {batch, m, n}, os2[] = {m, n};
+    const bool b3 = batch > 1;
+    TensorView x = b3 ? TensorView(xs3, fdt, dx.p, TensorLayout::Dense, qa) : TensorView(xs2, fdt, dx.p, TensorLayout::Dense, qa);
+    TensorView wv(ws, DataType::s8, dw.p, TensorLayout::Dense, qw);
+    TensorView bv(bs, fdt, dbias.p);
+    TensorView out = b3 ? TensorView(os3, fdt, dout.p) : TensorView(os2, fdt, dout.p);
+    LinearAttributes attrs;
+    attrs.epilogue.type = relu ? EpilogueActivateType::Relu : EpilogueActivateType::None;
+    auto op = Linear::create(attrs, Backend::CUDA);
+    const TensorDesc in_d[] = {x.desc(), wv.desc(), bv.desc()};
+    EXPECT(op->getOutputTensorDesc(in_d)[0].dtype == fdt);
+    ComputeContext ctx;
+    ctx.expected_backend = Backend::CUDA;
+    ctx.cuda_stream = stream;
+    const TensorView ins[] = {x, wv, bv};
+    EXPECT(op->compute(out, ins, ctx) == Status::ok);
+    const auto got = dout.download<uint8_t>();
+    EXPECT(got == want);
+    {   // without parameters a float A is not a quantized tensor: rejected, nothing written
+        DevBuf canary(want.size(), 0x3C);
+        TensorView plain = b3 ? TensorView(xs3, fdt, dx.p) : TensorView(xs2, fdt, dx.p);
+        TensorView o2v = b3 ? TensorView(os3, fdt, canary.p) : TensorView(os2, fdt, canary.p);
+        const TensorView bad[] = {plain, wv, bv};
+        EXPECT(op->compute(o2v, bad, ctx) == Status::invalid_argument);
+        bool untouched = true;
+        for (uint8_t b : canary.download<uint8_t>()) untouched = untouched && b == 0x3C;
+        EXPECT(untouched);
+    }
+#ifdef NNB200_USE_NNOPS_HEADERS
+    {   // the reference's CPU route on the same bytes
+        std::vector<uint8_t> cpu(want.size());
+        TensorView hx = b3 ? TensorView(xs3, fdt, const_cast<void*>(x_host), TensorLayout::Dense, qa)
+                           : TensorView(xs2, fdt, const_cast<void*>(x_host), TensorLayout::Dense, qa);
+        TensorView hw(ws, DataType::s8, w.data(), TensorLayout::Dense, qw);
+        TensorView hb(bs, fdt, const_cast<void*>(bias_host));
+        TensorView ho = b3 ? TensorView(os3, fdt, cpu.data()) : TensorView(os2, fdt, cpu.data());
+        auto cpu_op = Linear::create(attrs, Backend::CPU);
+        const TensorView hins[] = {hx, hw, hb};
+        EXPECT(cpu_op->compute(ho, hins) == Status::ok);
+        EXPECT(cpu == got);
+    }
+#endif
+}
+
 // ---- QuantizeLinear / DequantizeLinear ------------------------------------------------------
 
 // Known answers of the reference's operator test (tests/test_quant_linear.cpp:198-226, 439-467):
@@ -650,6 +758,12 @@ int main()
     linear_q4_1_case(130, 300, 1000, false, "linear_q4_1_gemm_f32_ragged");
 
     contract_cases();
+
+    linear_fp_act_case(1, 200, 330, 512, false, true, true, true, "linear_fp_act_f32_per_token_zp", stream);
+    linear_fp_act_case(1, 77, 130, 272, true, false, true, false, "linear_fp_act_f16_per_tensor_zp", nullptr);
+    linear_fp_act_case(1, 8, 520, 1024, true, true, false, true, "linear_fp_act_f16_decode_m8", stream);
+    linear_fp_act_case(3, 64, 96, 128, false, true, true, false, "linear_fp_act_f32_batched_per_token", stream);
+    linear_fp_act_case(1, 130, 140, 100, false, false, false, true, "linear_fp_act_f32_unaligned_k", nullptr);
 
     kat_quant_linear();
     quant_linear_case({{64, 4096}, -1, 1, false, false}, "quant_linear_per_tensor_f32_s8", stream);

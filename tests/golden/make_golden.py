@@ -73,6 +73,21 @@ def q4_case(name, m, n, k, dtype, *, seed):
     save(name, dict(op="q4_1", k=k, out_dtype=dtype, rtol=1e-2 if dtype == "f16" else 2e-3), a=a, w_blocks=wb, out=out)
 
 
+def fp_act_case(name, m, n, k, fdt, *, seed, per_token, relu):
+    """f32/f16 activations with quantization parameters x s8 weights (quantize on the fly)."""
+    rng = np.random.default_rng(seed)
+    w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    a = (rng.standard_normal((m, k)) * 2).astype(fdt)
+    scale_w = rng.uniform(0.001, 0.02, n).astype(np.float32)
+    bias = (rng.normal(size=n) * 3).astype(fdt)
+    scale_a = rng.uniform(0.01, 0.05, m).astype(np.float32) if per_token else np.float32(0.03)
+    zp_a = rng.integers(-9, 10, m).astype(np.int32) if per_token else np.int32(3)
+    out = oracle.linear_fp_act(a, w, scale_a=scale_a if per_token else float(scale_a),
+                               zp_a=zp_a if per_token else int(zp_a), bias=bias, relu=relu, scale_w=scale_w, impl="ref")
+    save(name, dict(op="fp_act", relu=relu, per_token=per_token), a=a, w=w, scale_a=np.atleast_1d(scale_a),
+         zp_a=np.atleast_1d(zp_a), scale_w=scale_w, bias=bias, out=out)
+
+
 def quant_case(name, shape, axis, per, fdt, qdt, *, seed):
     """QuantizeLinear and DequantizeLinear of one tensor.  x carries exact .5 ties (in units of
     its scale), infinities, a NaN and values far outside the 8-bit range."""
@@ -118,3 +133,5 @@ if __name__ == "__main__":
     quant_case("qdq_per_token_f16_u8", (37, 75), -1, "token", np.float16, "u8", seed=21)
     quant_case("qdq_per_channel_f32_u8", (5, 12, 24), 1, "channel", np.float32, "u8", seed=22)
     quant_case("qdq_per_channel_last_axis_f16_s8", (6, 50), 1, "channel", np.float16, "s8", seed=23)
+    fp_act_case("fp_act_f32_per_token", 96, 144, 320, np.float32, seed=30, per_token=True, relu=True)
+    fp_act_case("fp_act_f16_per_tensor", 40, 100, 256, np.float16, seed=31, per_token=False, relu=False)

@@ -28,6 +28,14 @@ def test_cuda_matches_golden(cuda_device, nnb200_lib, path):
         got = ops.gemm_i8(a, w, out_kind=meta["out_kind"], relu=meta["relu"],
                           activation="relu" if meta["relu"] and meta["out_kind"] in ("f32", "f16") else "none", **kw)
         assert np.array_equal(got.cpu().numpy().view(np.uint8), z["out"].view(np.uint8))
+    elif meta["op"] == "fp_act":
+        pt = meta["per_token"]
+        got = ops.linear_fp_act(torch.from_numpy(z["a"]).to(dev), torch.from_numpy(z["w"]).to(dev),
+                                scale_a=torch.from_numpy(z["scale_a"]) if pt else float(z["scale_a"][0]),
+                                zp_a=torch.from_numpy(z["zp_a"]) if pt else int(z["zp_a"][0]),
+                                bias=torch.from_numpy(z["bias"]), relu=meta["relu"],
+                                activation="relu" if meta["relu"] else "none", scale_w=torch.from_numpy(z["scale_w"]))
+        assert np.array_equal(got.cpu().numpy().view(np.uint8), z["out"].view(np.uint8))
     elif meta["op"] == "quant_linear":
         scale, zp = torch.from_numpy(z["scale"]), torch.from_numpy(z["zero_point"])
         q = ops.quantize_linear(torch.from_numpy(z["x"]).to(dev), scale, zp, axis=meta["axis"],

@@ -133,6 +133,12 @@ def test_port_matches_golden(path):
         w = z["w"].T if meta.get("w_kn") else z["w"]
         out = oracle.gemm_i8(a, w, out_kind=meta["out_kind"], relu=meta["relu"], **kw)
         assert np.array_equal(out.view(np.uint8), z["out"].view(np.uint8))
+    elif meta["op"] == "fp_act":
+        pt = meta["per_token"]
+        out = oracle.linear_fp_act(z["a"], z["w"], scale_a=z["scale_a"] if pt else float(z["scale_a"][0]),
+                                   zp_a=z["zp_a"] if pt else int(z["zp_a"][0]), bias=z["bias"], relu=meta["relu"],
+                                   scale_w=z["scale_w"])
+        assert np.array_equal(out.view(np.uint8), z["out"].view(np.uint8))
     elif meta["op"] == "quant_linear":
         q = oracle.quantize_linear(z["x"], z["scale"], z["zero_point"], axis=meta["axis"],
                                    out_dtype=z["quantized"].dtype)
@@ -248,3 +254,22 @@ def test_dequantize_reference_kats(case):
     x, scale, zp, axis, want = _REF_DEQUANTIZE_KATS[case]
     assert oracle.dequantize_linear(x, scale, zp, axis=axis).tolist() == want
     assert oracle.dequantize_linear(x, scale, zp, axis=axis, out_dtype=np.float16).tolist() == want
+
+
+@pytest.mark.skipif(not oracle.have_ref(), reason="compiled reference not runnable on this host")
+def test_fp_activation_route_port_matches_reference():
+    """f32/f16 activations with per-tensor / per-token parameters x s8 weights: quantise, int8
+    matmul, dequantize -- the composed restatement equals the reference Linear bit for bit."""
+    rng = np.random.default_rng(12)
+    for (m, n, k) in [(37, 53, 600), (6, 200, 64), (130, 70, 257)]:
+        w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+        sw = rng.uniform(0.001, 0.02, n).astype(np.float32)
+        for fdt in (np.float32, np.float16):
+            a = (rng.standard_normal((m, k)) * 2).astype(fdt)
+            bias = (rng.normal(size=n) * 3).astype(fdt)
+            for sa, za in ((0.03, 0), (0.03, 3), (rng.uniform(0.01, 0.05, m).astype(np.float32), 0),
+                           (rng.uniform(0.01, 0.05, m).astype(np.float32), rng.integers(-9, 10, m).astype(np.int32))):
+                for relu in (False, True):
+                    p = oracle.linear_fp_act(a, w, scale_a=sa, zp_a=za, bias=bias, relu=relu, scale_w=sw)
+                    r = oracle.linear_fp_act(a, w, scale_a=sa, zp_a=za, bias=bias, relu=relu, scale_w=sw, impl="ref")
+                    assert np.array_equal(p.view(np.uint8), r.view(np.uint8)), (m, n, k, fdt, relu)

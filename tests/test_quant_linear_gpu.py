@@ -17,7 +17,8 @@ CASES = [
     ((70001,), -1, "tensor"),            # scalar kernel (length not a multiple of 4)
     ((64, 4096), -1, "tensor"),
     ((37, 75), -1, "token"),             # scalar kernel
-    ((200, 1028), -1, "token"),          # vector kernel with a 4-element CPU-tail region per row
+    ((200, 1028), -1, "token"),          # f32: vector kernel with a 4-element CPU-tail region per row
+    ((50, 1032), -1, "token"),           # f32 and f16 vector kernels, 8-element CPU-tail region per row
     ((5, 12, 24), 1, "channel"),
     ((6, 50), 1, "channel"),             # channel = last axis: inner 1
     ((4, 100, 64), 0, "channel"),
