@@ -183,17 +183,21 @@ def secondary_q4_1(torch, dev, peaks):
     c = synth.config4()
     a, w = torch.from_numpy(c.a).to(dev), torch.from_numpy(c.w_blocks).to(dev)
     o = torch.empty((c.a.shape[0], c.w_blocks.shape[0]), dtype=torch.float16, device=dev)
-    for _ in range(3):
-        ops.linear_q4_1(a, w, c.k, out=o)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(10):
-        ops.linear_q4_1(a, w, c.k, out=o)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / 10
-    tf = c.flops / ms / 1e9
-    out["q4_1_gemm"] = {"tflops": tf, "ms_per_call": ms, "frac_of_bf16_peak": tf / peaks["bf16_tflops"]}
+    # The whole call (auto picks the two-pass form here: expansion of W + dense GEMM), and the
+    # fused single-kernel form beside it.
+    for key, engine in (("q4_1_gemm", "auto"), ("q4_1_gemm_fused", "gemm")):
+        for _ in range(3):
+            ops.linear_q4_1(a, w, c.k, out=o, engine=engine)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            ops.linear_q4_1(a, w, c.k, out=o, engine=engine)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 10
+        tf = c.flops / ms / 1e9
+        out[key] = {"tflops": tf, "ms_per_call": ms, "frac_of_bf16_peak": tf / peaks["bf16_tflops"],
+                    "engine": ops.q4_1_engine(a, w, c.k, out_dtype=torch.float16, engine=engine)}
     return out
 
 
@@ -270,7 +274,7 @@ def secondary_quant_linear(torch, dev, peaks):
 
 def run_kernel_only(args):
     """Three launches of one kernel on seeded inputs and nothing else: the command the ncu
-    captures under profiles/ are taken from (`--kernel-only i8|gemv|q4gemm --shape M N K`)."""
+    captures under profiles/ are taken from (`--kernel-only i8|gemv|q4gemm|q4gemm2 --shape M N K`)."""
     import torch
     from nnops_b200 import build, ops, synth
     build.build()
@@ -291,7 +295,8 @@ def run_kernel_only(args):
         gemv = args.kernel_only == "gemv"
         out = torch.empty((m, n), dtype=torch.float32 if gemv else torch.float16, device=dev)
         for _ in range(3):
-            ops.linear_q4_1(a, wb, k, out=out, engine="gemv" if gemv else "gemm")
+            ops.linear_q4_1(a, wb, k, out=out, engine="gemv" if gemv else
+                            ("gemm_two_pass" if args.kernel_only == "q4gemm2" else "gemm"))
     torch.cuda.synchronize()
     print(json.dumps({"kernel_only": args.kernel_only, "shape": [m, n, k], "launches": 3}))
 
@@ -305,7 +310,8 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the Q4_1 and CPU-baseline side measurements")
     ap.add_argument("--reassembly", default="fused", choices=["fused", "nccl"],
                     help="N > 1: peer-store epilogue (fused) or NCCL all-gather + interleave kernel")
-    ap.add_argument("--kernel-only", choices=["i8", "gemv", "q4gemm"], help="profiling aid: 3 launches of one kernel")
+    ap.add_argument("--kernel-only", choices=["i8", "gemv", "q4gemm", "q4gemm2"],
+                    help="profiling aid: 3 launches of one kernel (q4gemm = fused form, q4gemm2 = two-pass form)")
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=[4096, 28672, 8192])
     args = ap.parse_args()
     if args.kernel_only:

@@ -183,7 +183,8 @@ typedef struct nnb200_q4_1_args {
     float alpha;
     void* workspace;
     size_t workspace_bytes;
-    int32_t force_engine; /* 0 auto, 1 tensor-core GEMM, 2 GEMV (best), 3 GEMV on CUDA cores, 4 GEMV with warp MMA */
+    int32_t force_engine; /* 0 auto, 1 fused tensor-core GEMM, 2 GEMV (best), 3 GEMV on CUDA cores, 4 GEMV with
+                             warp MMA, 5 two-pass GEMM (needs the workspace) */
     int32_t flags;        /* NNB200_Q4_FLAG_* */
 } nnb200_q4_1_args;
 
@@ -193,6 +194,11 @@ typedef struct nnb200_q4_1_args {
  * the preceding kernel does not write w_blocks.  Honoured by the GEMV engine. */
 #define NNB200_Q4_FLAG_OVERLAP_PREVIOUS 1
 
+/* Optional device scratch (16-byte aligned).  Non-zero for tall f16 problems (m >= 256): given
+ * that many bytes, the call expands the weights to f16 once into the scratch and runs a dense
+ * tensor-core GEMM over them, which is faster than decoding inside the GEMM; without it (NULL or
+ * too small) the same call runs the fused kernel.  The scratch is dead when the call's work has
+ * completed on the stream. */
 NNB200_API size_t nnb200_q4_1_workspace_bytes(const nnb200_q4_1_args* args);
 NNB200_API int nnb200_linear_q4_1(const nnb200_q4_1_args* args, void* stream);
 NNB200_API int nnb200_q4_1_engine(const nnb200_q4_1_args* args);

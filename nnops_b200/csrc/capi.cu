@@ -314,9 +314,19 @@ static bool valid_q4_args(const nnb200_q4_1_args* q)
     return q->lda >= q->k && q->ldc >= q->n && q->ldw_blocks >= nblk;
 }
 
-size_t nnb200_q4_1_workspace_bytes(const nnb200_q4_1_args*)
+// Rows of activations from which expanding the weights once and running a dense GEMM beats
+// decoding them inside the GEMM (measured on config 4's weights: equal at 128 rows, 64 us
+// against 100 us at 256).
+static constexpr int64_t kTwoPassMinRows = 256;
+
+size_t nnb200_q4_1_workspace_bytes(const nnb200_q4_1_args* q)
 {
-    return 0;
+    if (!valid_q4_args(q) || q->m == 0 || q->n == 0) {
+        return 0;
+    }
+    // Optional: without it a tall call runs the fused kernel.
+    const bool wanted = q->force_engine == 5 || (q->force_engine == 0 && q->m >= kTwoPassMinRows);
+    return (wanted && q->a_f16 != 0) ? q4_1_two_pass_scratch_bytes(*q) : 0;
 }
 
 int nnb200_q4_1_engine(const nnb200_q4_1_args* q)
@@ -324,14 +334,22 @@ int nnb200_q4_1_engine(const nnb200_q4_1_args* q)
     if (!valid_q4_args(q)) {
         return -1;
     }
-    // 1 = tensor-core GEMM (tcgen05), 3 = GEMV on CUDA cores, 4 = GEMV with warp-level MMA.
+    // 1 = fused tensor-core GEMM (tcgen05), 3 = GEMV on CUDA cores, 4 = GEMV with warp-level MMA,
+    // 5 = two-pass GEMM (expand to f16 scratch, dense tcgen05 GEMM).
     const int gemv = (q->force_engine != 3 && q4_1_gemv_mma_supported(*q)) ? 4 : 3;
     if (q->force_engine == 2 || q->force_engine == 3 || q->force_engine == 4) {
         return gemv;
     }
     const bool gemm_ok = q4_1_gemm_umma_supported(*q);
+    const bool two_pass_ok = q4_1_two_pass_supported(*q);
+    if (q->force_engine == 5) {
+        return two_pass_ok ? 5 : (gemm_ok ? 1 : gemv);
+    }
     if (q->force_engine == 1) {
         return gemm_ok ? 1 : gemv;
+    }
+    if (q->m >= kTwoPassMinRows && two_pass_ok) {
+        return 5;
     }
     return (q->m > 8 && gemm_ok) ? 1 : gemv;
 }
@@ -357,6 +375,7 @@ int nnb200_linear_q4_1(const nnb200_q4_1_args* q, void* stream_v)
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     switch (nnb200_q4_1_engine(q)) {
     case 1: return launch_q4_1_gemm_umma(*q, *dev, stream);
+    case 5: return launch_q4_1_two_pass(*q, *dev, stream);
     case 4: return launch_q4_1_gemv_mma(*q, *dev, stream);
     default: return launch_q4_1_gemv(*q, *dev, stream);
     }

@@ -55,8 +55,9 @@ struct TileConfig {
     static constexpr int kBTileBytes = BN * kBlockKBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     // Ring depth: as many stages as fit beside the epilogue staging in ~200 KB.
-    static constexpr int kStages = PEERS ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : (BN == 128 ? 6 : 8));
-    static constexpr int kTmemCols = 2 * BN;  // two accumulators; 128..512, a power of two
+    static constexpr int kStages = PEERS ? ((BN == 256) ? 3 : 5) : ((BN > 128) ? 4 : (BN == 128 ? 6 : 8));
+    // Two accumulators BN columns apart; the allocation is a power of two of at least 2 * BN.
+    static constexpr int kTmemCols = BN > 128 ? 512 : 2 * BN;
     static constexpr int kColParamBytes = 4 * 4 * BN * 4;  // 4 epilogue warps x {scale, bias, r_w, zp_w} x BN x 4 B
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
     // Sharded form: two staging tiles of 32 rows x 128 B per epilogue warp (one being filled, one being stored).
@@ -559,7 +560,7 @@ int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, cons
 {
     if (ep.num_peers > 0) {
         // Sharded write-back exists for the 8-bit destinations and 128-column groups.
-        if constexpr (BN >= 128) {
+        if constexpr (BN == 256 || BN == 128) {
             if (kind == NNB200_OUT_S8) {
                 return launch_variant<BN, NNB200_OUT_S8, true>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
             }
@@ -601,14 +602,35 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
     const int n = static_cast<int>(p.n);
     const int k = static_cast<int>(p.k);
 
-    // Tile width: the widest tile that still gives every SM work; narrow problems trade
-    // arithmetic intensity for parallelism.
+    // Tile width.  When even the widest tile gives every SM work, take the width with the least
+    // padded work over whole waves (waves x width; ties to the wider tile); narrow problems
+    // trade arithmetic intensity for parallelism.
     const int num_m = (m + kBlockM - 1) / kBlockM;
     int bn = 256;
     if (static_cast<int64_t>(num_m) * ((n + 255) / 256) < dev.sm_count) {
         bn = 128;
         if (static_cast<int64_t>(num_m) * ((n + 127) / 128) < dev.sm_count && ep.num_peers == 0) {
             bn = 64;
+        }
+    } else if (ep.num_peers == 0) {
+        const auto padded_work = [&](int width) {
+            const int64_t tiles = static_cast<int64_t>(num_m) * ((n + width - 1) / width);
+            return (tiles + dev.sm_count - 1) / dev.sm_count * width;
+        };
+        int64_t best_cost = padded_work(256);
+        for (const int cand : {224, 192}) {
+            // A narrower tile moves more operand bytes per multiply-add (measured: about 8 % slower
+            // per unit of work at 224): it has to save more than that.
+            if (padded_work(cand) * 100 < best_cost * 92) {
+                best_cost = padded_work(cand);
+                bn = cand;
+            }
+        }
+    }
+    if (const char* e = getenv("NNB200_I8_BN")) {  // measurement aid
+        const int v = atoi(e);
+        if (v == 256 || v == 224 || v == 192 || v == 128 || v == 64) {
+            bn = v;
         }
     }
 
@@ -633,6 +655,12 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
     switch (bn) {
     case 256:
         return launch_bn<256>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 256), vec_ok,
+                              dev, stream);
+    case 224:
+        return launch_bn<224>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 224), vec_ok,
+                              dev, stream);
+    case 192:
+        return launch_bn<192>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 192), vec_ok,
                               dev, stream);
     case 128:
         return launch_bn<128>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 128), vec_ok,

@@ -67,6 +67,9 @@ int launch_q4_1_gemv_mma(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaS
 bool q4_1_gemv_mma_supported(const nnb200_q4_1_args& a);
 int launch_q4_1_gemm_umma(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
 bool q4_1_gemm_umma_supported(const nnb200_q4_1_args& a);
+int launch_q4_1_two_pass(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
+bool q4_1_two_pass_supported(const nnb200_q4_1_args& a);
+size_t q4_1_two_pass_scratch_bytes(const nnb200_q4_1_args& a);
 int launch_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, int64_t k, void* out, int out_f16,
                        int64_t ld_out, cudaStream_t stream);
 

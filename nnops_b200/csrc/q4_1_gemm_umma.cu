@@ -80,41 +80,6 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n)
     return c;
 }
 
-// Two nibble-carrying words (8 bytes of qs) -> 8 consecutive f16 weights of the low nibbles
-// and 8 of the high nibbles, each as a uint4 of four half2.
-__device__ __forceinline__ void dequant_word_pair(uint32_t w0, uint32_t w1, __half2 d2, __half2 m2, uint4& lo,
-                                                  uint4& hi)
-{
-    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-    const uint32_t magic = 0x64646464u;
-    uint32_t lo_out[4], hi_out[4];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const uint32_t w = i == 0 ? w0 : w1;
-        const uint32_t x = w & 0x0F0F0F0Fu;
-        const uint32_t y = (w >> 4) & 0x0F0F0F0Fu;
-        // bytes (n0, 0x64, n1, 0x64) = half2(1024 + n0, 1024 + n1)
-        const uint32_t x01 = __byte_perm(x, magic, 0x4140);
-        const uint32_t x23 = __byte_perm(x, magic, 0x4342);
-        const uint32_t y01 = __byte_perm(y, magic, 0x4140);
-        const uint32_t y23 = __byte_perm(y, magic, 0x4342);
-        const __half2 q0 = __hsub2(*reinterpret_cast<const __half2*>(&x01), k1024);
-        const __half2 q1 = __hsub2(*reinterpret_cast<const __half2*>(&x23), k1024);
-        const __half2 q2 = __hsub2(*reinterpret_cast<const __half2*>(&y01), k1024);
-        const __half2 q3 = __hsub2(*reinterpret_cast<const __half2*>(&y23), k1024);
-        const __half2 r0 = __hfma2(q0, d2, m2);
-        const __half2 r1 = __hfma2(q1, d2, m2);
-        const __half2 r2 = __hfma2(q2, d2, m2);
-        const __half2 r3 = __hfma2(q3, d2, m2);
-        lo_out[2 * i] = *reinterpret_cast<const uint32_t*>(&r0);
-        lo_out[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&r1);
-        hi_out[2 * i] = *reinterpret_cast<const uint32_t*>(&r2);
-        hi_out[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&r3);
-    }
-    lo = make_uint4(lo_out[0], lo_out[1], lo_out[2], lo_out[3]);
-    hi = make_uint4(hi_out[0], hi_out[1], hi_out[2], hi_out[3]);
-}
-
 template <bool OUT_F16, bool COOP, int MH>
 __global__ void __launch_bounds__(Q4Config<COOP, MH>::kNumThreads, 1)
 q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* __restrict__ w,

@@ -461,6 +461,16 @@ Status run_q4_1(const TensorView& x, const TensorView& w, const TensorView* bias
     q.min_clip = ep.min_clip;
     q.max_clip = ep.max_clip;
     q.alpha = alpha;
+    // Tall problems run faster with scratch for the expanded weights (stream-ordered, freed
+    // right after the launch is enqueued).
+    Staging st(ctx.cuda_stream);
+    if (const size_t need = nnb200_q4_1_workspace_bytes(&q); need > 0) {
+        st.reserve_raw(need);
+        if (st.allocate() == NNB200_OK) {
+            q.workspace = st.take_raw(need);
+            q.workspace_bytes = need;
+        }
+    }
     return to_status(nnb200_linear_q4_1(&q, ctx.cuda_stream));
 }
 

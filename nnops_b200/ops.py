@@ -146,6 +146,14 @@ def linear_q4_1(a: torch.Tensor, w_blocks: torch.Tensor, k: int, *, out_dtype: t
         out = torch.empty((a.shape[0], w_blocks.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
     keep: list = []
     args = q4_1_args(a, w_blocks, out, k, keep=keep, **kw)
+    need = capi.lib().nnb200_q4_1_workspace_bytes(C.byref(args))
+    if need > 0:
+        # Scratch for the expanded weights of the two-pass form; torch's allocator is
+        # stream-ordered, so letting it go after the call is safe.
+        scratch = torch.empty(need, dtype=torch.uint8, device=a.device)
+        keep.append(scratch)
+        args.workspace = scratch.data_ptr()
+        args.workspace_bytes = need
     with torch.cuda.device(a.device):
         capi.check(capi.lib().nnb200_linear_q4_1(C.byref(args), _stream_ptr(a.device)), "nnb200_linear_q4_1")
     return out
@@ -153,9 +161,15 @@ def linear_q4_1(a: torch.Tensor, w_blocks: torch.Tensor, k: int, *, out_dtype: t
 
 def q4_1_engine(a: torch.Tensor, w_blocks: torch.Tensor, k: int, *, out_dtype: torch.dtype = torch.float32,
                 engine: str = "auto") -> int:
-    """Engine code nnb200_linear_q4_1 would pick (1 GEMM, 3 GEMV on CUDA cores, 4 GEMV with warp MMA)."""
+    """Engine code nnb200_linear_q4_1 would pick (1 fused GEMM, 3 GEMV on CUDA cores, 4 GEMV with warp
+    MMA, 5 two-pass GEMM) when given the scratch it asks for."""
     out = torch.empty((a.shape[0], w_blocks.shape[0]), dtype=out_dtype, device=a.device)
     args = q4_1_args(a, w_blocks, out, k, engine=engine)
+    need = capi.lib().nnb200_q4_1_workspace_bytes(C.byref(args))
+    if need > 0:
+        scratch = torch.empty(need, dtype=torch.uint8, device=a.device)
+        args.workspace = scratch.data_ptr()
+        args.workspace_bytes = need
     return capi.lib().nnb200_q4_1_engine(C.byref(args))
 
 

@@ -111,6 +111,43 @@ def test_gemm_umma_shapes(cuda_device, nnb200_lib, shape, out_dtype):
     _close(got.cpu().numpy(), want, RTOL_F16 if out_dtype == "f16" else RTOL_F32)
 
 
+@pytest.mark.parametrize("shape", [(128, 128, 64), (130, 300, 512), (64, 1000, 160), (300, 260, 1000),
+                                   (2048, 1024, 512), (1000, 4810, 320), (520, 9500, 96), (640, 7168, 128)])
+@pytest.mark.parametrize("out_dtype", ["f16", "f32"])
+def test_gemm_two_pass_shapes(cuda_device, nnb200_lib, shape, out_dtype):
+    """Expand-then-dense-GEMM form: ragged M / N / K, every tile width the picker can choose."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k + 1)
+    wb = synth.q4_1_weights(rng, n, k)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    want = oracle.q4_1_matmul(a, wb, k, out_dtype=out_dtype, w_round_f16=True)
+    ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device)
+    tdt = torch.float16 if out_dtype == "f16" else torch.float32
+    assert ops.q4_1_engine(ta, tw, k, out_dtype=tdt, engine="gemm_two_pass") == 5
+    assert ops.q4_1_engine(ta, tw, k, out_dtype=tdt) == (5 if m >= 256 else 1)
+    o = torch.empty((m, n), dtype=tdt, device=cuda_device)
+    got = ops.linear_q4_1(ta, tw, k, out=o, engine="gemm_two_pass")
+    _close(got.cpu().numpy(), want, RTOL_F16 if out_dtype == "f16" else RTOL_F32)
+
+
+def test_gemm_two_pass_needs_its_scratch(cuda_device, nnb200_lib):
+    """Without the scratch the same call runs the fused kernel: same result within tolerance."""
+    import ctypes as C
+    from nnops_b200 import capi
+    rng = np.random.default_rng(8)
+    m, n, k = 600, 512, 256
+    wb = synth.q4_1_weights(rng, n, k)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device)
+    o = torch.empty((m, n), dtype=torch.float16, device=cuda_device)
+    args = ops.q4_1_args(ta, tw, o, k)                       # no workspace set
+    assert capi.lib().nnb200_q4_1_workspace_bytes(C.byref(args)) == n * k * 2
+    assert capi.lib().nnb200_q4_1_engine(C.byref(args)) == 1
+    capi.check(capi.lib().nnb200_linear_q4_1(C.byref(args), torch.cuda.current_stream().cuda_stream), "q4_1")
+    want = oracle.q4_1_matmul(a, wb, k, out_dtype="f16", w_round_f16=True)
+    _close(o.cpu().numpy(), want, RTOL_F16)
+
+
 def test_gemm_epilogue_bias_relu(cuda_device, nnb200_lib):
     rng = np.random.default_rng(4)
     m, n, k = 256, 384, 256
@@ -118,9 +155,10 @@ def test_gemm_epilogue_bias_relu(cuda_device, nnb200_lib):
     a = rng.standard_normal((m, k)).astype(np.float16)
     bias = rng.standard_normal(n).astype(np.float16)
     want = np.maximum(oracle.q4_1_matmul(a, wb, k, out_dtype="f32", w_round_f16=True) + bias.astype(np.float32), 0)
-    got = ops.linear_q4_1(torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device), k,
-                          out_dtype=torch.float16, bias=bias, activation="relu", engine="gemm")
-    _close(got.cpu().numpy(), want, RTOL_F16)
+    for engine in ("gemm", "gemm_two_pass"):
+        got = ops.linear_q4_1(torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device), k,
+                              out_dtype=torch.float16, bias=bias, activation="relu", engine=engine)
+        _close(got.cpu().numpy(), want, RTOL_F16)
 
 
 def test_config4_sampled(cuda_device, nnb200_lib):
