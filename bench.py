@@ -281,7 +281,16 @@ def run_kernel_only(args):
     m, n, k = args.shape
     dev = torch.device("cuda:0")
     rng = np.random.default_rng(0)
-    if args.kernel_only == "i8":
+    if args.kernel_only == "quant":
+        x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(dev)
+        scale = torch.full((m,), 0.02, dtype=torch.float32, device=dev)
+        zp = torch.zeros(m, dtype=torch.int8, device=dev)
+        q = torch.empty((m, k), dtype=torch.int8, device=dev)
+        y = torch.empty_like(x)
+        for _ in range(3):
+            ops.quantize_linear(x, scale, zp, out=q)
+            ops.dequantize_linear(q, scale, zp, out=y)
+    elif args.kernel_only == "i8":
         a = torch.from_numpy(synth.s8_uniform(rng, (m, k))).to(dev)
         w = torch.from_numpy(synth.s8_uniform(rng, (n, k))).to(dev)
         sw = torch.from_numpy(rng.uniform(0.001, 0.02, n).astype(np.float32)).to(dev)
@@ -310,8 +319,9 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the Q4_1 and CPU-baseline side measurements")
     ap.add_argument("--reassembly", default="fused", choices=["fused", "nccl"],
                     help="N > 1: peer-store epilogue (fused) or NCCL all-gather + interleave kernel")
-    ap.add_argument("--kernel-only", choices=["i8", "gemv", "q4gemm", "q4gemm2"],
-                    help="profiling aid: 3 launches of one kernel (q4gemm = fused form, q4gemm2 = two-pass form)")
+    ap.add_argument("--kernel-only", choices=["i8", "gemv", "q4gemm", "q4gemm2", "quant"],
+                    help="profiling aid: 3 launches of one kernel (q4gemm = fused form, q4gemm2 = two-pass form, "
+                         "quant = QuantizeLinear then DequantizeLinear of an [M, K] f32 tensor, per token; N unused)")
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=[4096, 28672, 8192])
     args = ap.parse_args()
     if args.kernel_only:

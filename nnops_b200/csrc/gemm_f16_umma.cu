@@ -78,28 +78,44 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
 // Lane pair (2b, 2b+1) of a warp owns one block: half h = lane & 1 decodes qs bytes 8h..8h+7,
 // i.e. weights k 8h..8h+7 (low nibbles) and 16+8h..16+8h+7 (high nibbles), and stores them as
 // two 16-byte pieces; a pair thereby completes the 32-byte sectors [k 0..15] and [k 16..31].
+// A CTA walks whole rows (no index division anywhere); every thread has the loads of two rows in
+// flight before it decodes either.
 __global__ void __launch_bounds__(256) q4_1_expand_f16_kernel(const uint8_t* __restrict__ w, const int64_t ldw_blocks,
-                                                              const int64_t rows, const int64_t nblk,
+                                                              const int rows, const int nblk,
                                                               __half* __restrict__ out, const int64_t ld_out)
 {
-    const int64_t total = rows * nblk * 2;  // half-blocks
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t blk = i >> 1;
-        const int h = static_cast<int>(i & 1);
-        const int64_t r = blk / nblk;
-        const int64_t b = blk - r * nblk;
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(w + (r * ldw_blocks + b) * kQ4BlockBytes);
-        const uint32_t dm = __ldg(src);
-        const uint32_t q0 = __ldg(src + 1 + 2 * h);
-        const uint32_t q1 = __ldg(src + 2 + 2 * h);
-        const __half2 d2 = __half2half2(__ushort_as_half(static_cast<uint16_t>(dm & 0xFFFFu)));
-        const __half2 m2 = __half2half2(__ushort_as_half(static_cast<uint16_t>(dm >> 16)));
-        uint4 lo, hi;
-        dequant_word_pair(q0, q1, d2, m2, lo, hi);
-        __half* dst = out + r * ld_out + b * kQ4BlockElems + 8 * h;
-        *reinterpret_cast<uint4*>(dst) = lo;
-        *reinterpret_cast<uint4*>(dst + 16) = hi;
+    const int half_blocks = 2 * nblk;
+    const int64_t pitch = ldw_blocks * kQ4BlockBytes;
+    for (int r0 = blockIdx.x; r0 < rows; r0 += 2 * gridDim.x) {
+        const int r1 = r0 + gridDim.x;
+        for (int hb = threadIdx.x; hb < half_blocks; hb += blockDim.x) {
+            const int b = hb >> 1;
+            const int h = hb & 1;
+            uint32_t dm[2], q0[2], q1[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int r = u == 0 ? r0 : r1;
+                if (r < rows) {
+                    const uint32_t* src = reinterpret_cast<const uint32_t*>(w + r * pitch + b * kQ4BlockBytes);
+                    dm[u] = __ldg(src);
+                    q0[u] = __ldg(src + 1 + 2 * h);
+                    q1[u] = __ldg(src + 2 + 2 * h);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int r = u == 0 ? r0 : r1;
+                if (r < rows) {
+                    const __half2 d2 = __half2half2(__ushort_as_half(static_cast<uint16_t>(dm[u] & 0xFFFFu)));
+                    const __half2 m2 = __half2half2(__ushort_as_half(static_cast<uint16_t>(dm[u] >> 16)));
+                    uint4 lo, hi;
+                    dequant_word_pair(q0[u], q1[u], d2, m2, lo, hi);
+                    __half* dst = out + r * ld_out + b * kQ4BlockElems + 8 * h;
+                    __stcg(reinterpret_cast<uint4*>(dst), lo);
+                    __stcg(reinterpret_cast<uint4*>(dst + 16), hi);
+                }
+            }
+        }
     }
 }
 
@@ -446,12 +462,12 @@ int launch_q4_1_two_pass(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
     const int64_t ldw = nblk * kQ4BlockElems;
     __half* w_f16 = static_cast<__half*>(q.workspace);
     {
-        const int64_t half_blocks = q.n * nblk * 2;
-        const int64_t want = (half_blocks + 255) / 256;
-        const int64_t cap = static_cast<int64_t>(dev.sm_count) * 32;
+        // One CTA per pair of rows, capped at a few waves; the kernel strides.
+        const int64_t want = (q.n + 1) / 2;
+        const int64_t cap = static_cast<int64_t>(dev.sm_count) * 16;
         const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
-        q4_1_expand_f16_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(q.w_blocks), q.ldw_blocks, q.n,
-                                                         nblk, w_f16, ldw);
+        q4_1_expand_f16_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(q.w_blocks), q.ldw_blocks,
+                                                         static_cast<int>(q.n), static_cast<int>(nblk), w_f16, ldw);
         note_launch();
         if (cudaGetLastError() != cudaSuccess) {
             return NNB200_INTERNAL;

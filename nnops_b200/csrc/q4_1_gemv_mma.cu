@@ -72,39 +72,79 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c)
 // (BIAS + q) pairs -> d*q + m, rounded once to f16.  BIAS is the half bit pattern the nibble
 // was or-ed into: 0x6400 (1024, nibble in mantissa bits 0-3) or 0x5400 (64, nibble in bits 4-7).
 template <uint16_t BIAS>
-__device__ __forceinline__ uint32_t scale_pair(uint32_t biased, __half2 d2, __half2 m2)
+__device__ __forceinline__ uint32_t scale_pair(uint32_t biased, uint32_t d, uint32_t m)
 {
     constexpr uint32_t kb = (static_cast<uint32_t>(BIAS) << 16) | BIAS;
-    const uint32_t d = *reinterpret_cast<const uint32_t*>(&d2);
-    const uint32_t m = *reinterpret_cast<const uint32_t*>(&m2);
     uint32_t q, r;
     asm("sub.f16x2 %0, %1, %2;" : "=r"(q) : "r"(biased), "r"(kb));
     asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(q), "r"(d), "r"(m));
     return r;
 }
 
-// 32 halves of activation row slice starting at k0 (zeros when the lane's row is past M).
-__device__ __forceinline__ void load_act_block(const __half* a_row, int k0, bool row_live, bool vec_ok, uint4 (&av)[4])
+// The 32 activations of one block for this lane's MMA column (activation row g), as four uint4.
+// Lanes whose row does not exist keep the zeros they were initialised with: no work per step.
+__device__ __forceinline__ void load_act_block(const __half* a_blk, bool vec_ok, uint4 (&av)[4])
 {
-    if (row_live) {
-        if (vec_ok) {
-            const uint4* src = reinterpret_cast<const uint4*>(a_row + k0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                av[j] = __ldg(src + j);
-            }
-        } else {
-            uint32_t* dst = reinterpret_cast<uint32_t*>(av);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                dst[j] = static_cast<uint32_t>(__half_as_ushort(a_row[k0 + 2 * j])) |
-                         (static_cast<uint32_t>(__half_as_ushort(a_row[k0 + 2 * j + 1])) << 16);
-            }
-        }
-    } else {
+    if (vec_ok) {
+        const uint4* src = reinterpret_cast<const uint4*>(a_blk);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            av[j] = make_uint4(0u, 0u, 0u, 0u);
+            av[j] = __ldg(src + j);
+        }
+    } else {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(av);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            dst[j] = static_cast<uint32_t>(__half_as_ushort(a_blk[2 * j])) |
+                     (static_cast<uint32_t>(__half_as_ushort(a_blk[2 * j + 1])) << 16);
+        }
+    }
+}
+
+// Low half / high half of a word duplicated into both halves (f16 scale and min of a block).
+__device__ __forceinline__ uint32_t dup_lo16(uint32_t w) { return __byte_perm(w, w, 0x1010); }
+__device__ __forceinline__ uint32_t dup_hi16(uint32_t w) { return __byte_perm(w, w, 0x3232); }
+
+// One block group: 16 rows x 32 k against the activation fragment `av`.  s_lo / s_hi point at
+// this lane's block in rows g and g + 8 of the shared slice.
+__device__ __forceinline__ void mma_block(const uint32_t* s_lo, const uint32_t* s_hi, const uint4 (&av)[4],
+                                          float (&acc0)[4], float (&acc1)[4])
+{
+    uint32_t w_lo[5], w_hi[5];
+#pragma unroll
+    for (int j = 0; j < 5; ++j) {
+        w_lo[j] = s_lo[j];
+        w_hi[j] = s_hi[j];
+    }
+    const uint32_t d_lo = dup_lo16(w_lo[0]), m_lo = dup_hi16(w_lo[0]);
+    const uint32_t d_hi = dup_lo16(w_hi[0]), m_hi = dup_hi16(w_hi[0]);
+    const uint32_t* avw = reinterpret_cast<const uint32_t*>(av);
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+        const uint32_t x = w_lo[1 + wi];  // row g:     bytes 4wi..4wi+3
+        const uint32_t y = w_hi[1 + wi];  // row g + 8
+        const uint32_t x8 = x >> 8;
+        const uint32_t y8 = y >> 8;
+        // Low nibbles (k 4wi..4wi+3): nibble | 0x6400 = 1024 + q.  Pair A = bytes 0, 2
+        // -> (k+0, k+2); pair B = bytes 1, 3 -> (k+1, k+3).
+        {
+            const uint32_t r0 = avw[2 * wi];
+            const uint32_t r1 = avw[2 * wi + 1];
+            mma_m16n8k16(acc0, scale_pair<0x6400>(and_or(x, 0x000F000Fu, 0x64006400u), d_lo, m_lo),
+                         scale_pair<0x6400>(and_or(y, 0x000F000Fu, 0x64006400u), d_hi, m_hi),
+                         scale_pair<0x6400>(and_or(x8, 0x000F000Fu, 0x64006400u), d_lo, m_lo),
+                         scale_pair<0x6400>(and_or(y8, 0x000F000Fu, 0x64006400u), d_hi, m_hi),
+                         __byte_perm(r0, r1, 0x5410), __byte_perm(r0, r1, 0x7632));
+        }
+        // High nibbles (k 16+4wi..): left in place, (nibble << 4) | 0x5400 = 64 + q.
+        {
+            const uint32_t r0 = avw[8 + 2 * wi];
+            const uint32_t r1 = avw[8 + 2 * wi + 1];
+            mma_m16n8k16(acc1, scale_pair<0x5400>(and_or(x, 0x00F000F0u, 0x54005400u), d_lo, m_lo),
+                         scale_pair<0x5400>(and_or(y, 0x00F000F0u, 0x54005400u), d_hi, m_hi),
+                         scale_pair<0x5400>(and_or(x8, 0x00F000F0u, 0x54005400u), d_lo, m_lo),
+                         scale_pair<0x5400>(and_or(y8, 0x00F000F0u, 0x54005400u), d_hi, m_hi),
+                         __byte_perm(r0, r1, 0x5410), __byte_perm(r0, r1, 0x7632));
         }
     }
 }
@@ -186,7 +226,16 @@ q4_1_gemv_mma_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes,
     float acc0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     float acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const bool row_live = g < m_count;  // activation row this lane feeds as MMA column g
-    const __half* a_row = a + static_cast<int64_t>(g) * lda;
+    const bool vec_ok = a_vec_ok != 0;
+    // This lane's activations: row g, starting at its block c of the first group.
+    const __half* a_lane = a + static_cast<int64_t>(row_live ? g : 0) * lda + c * kQ4BlockElems;
+    // Two fragment register sets, used alternately; lanes without a row keep zeros throughout.
+    uint4 av0[4], av1[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        av0[j] = make_uint4(0u, 0u, 0u, 0u);
+        av1[j] = make_uint4(0u, 0u, 0u, 0u);
+    }
 
     for (int ch = 0; ch < num_chunks; ++ch) {
         const int buf = ch % num_bufs;
@@ -195,71 +244,33 @@ q4_1_gemv_mma_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes,
         slice_of(ch, sb, snb);
         if (snb > 0) {
             const int groups = snb / 4;
+            const __half* a_grp = a_lane + static_cast<int64_t>(sb) * kQ4BlockElems;  // group 0 of this slice
             // First group's activations are fetched while the weights are still landing.
-            uint4 av[4];
-            load_act_block(a_row, (sb + c) * kQ4BlockElems, row_live, a_vec_ok != 0, av);
-
+            if (row_live) {
+                load_act_block(a_grp, vec_ok, av0);
+            }
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(&bars[warp][buf], phase, &abort_word))) {
                 atomicCAS(error_word, 0, kErrMmaWait);
                 break;
             }
             const uint8_t* base = slices + (warp * num_bufs + buf) * kSliceBufBytes;
-            for (int gi = 0; gi < groups; ++gi) {
-                const int blk_local = gi * 4 + c;  // the block this lane decodes
-                uint4 av_next[4];
-                if (gi + 1 < groups) {
-                    load_act_block(a_row, (sb + blk_local + 4) * kQ4BlockElems, row_live, a_vec_ok != 0, av_next);
+            const uint32_t* s_lo = reinterpret_cast<const uint32_t*>(base + g * kSliceStride) + c * kQ4BlockWords;
+            const uint32_t* s_hi = reinterpret_cast<const uint32_t*>(base + (g + 8) * kSliceStride) + c * kQ4BlockWords;
+            constexpr int kGroupWords = 4 * kQ4BlockWords;   // four blocks further along the row
+            constexpr int kGroupElems = 4 * kQ4BlockElems;
+            int gi = 0;
+            for (; gi + 2 <= groups; gi += 2) {
+                if (row_live) {
+                    load_act_block(a_grp + (gi + 1) * kGroupElems, vec_ok, av1);
                 }
-                const uint32_t* s_lo = reinterpret_cast<const uint32_t*>(base + g * kSliceStride) +
-                                       blk_local * kQ4BlockWords;
-                const uint32_t* s_hi = reinterpret_cast<const uint32_t*>(base + (g + 8) * kSliceStride) +
-                                       blk_local * kQ4BlockWords;
-                uint32_t w_lo[5], w_hi[5];
-#pragma unroll
-                for (int j = 0; j < 5; ++j) {
-                    w_lo[j] = s_lo[j];
-                    w_hi[j] = s_hi[j];
+                mma_block(s_lo + gi * kGroupWords, s_hi + gi * kGroupWords, av0, acc0, acc1);
+                if (row_live && gi + 2 < groups) {
+                    load_act_block(a_grp + (gi + 2) * kGroupElems, vec_ok, av0);
                 }
-                const __half2 d_lo = __half2half2(__ushort_as_half(static_cast<uint16_t>(w_lo[0] & 0xFFFFu)));
-                const __half2 m_lo = __half2half2(__ushort_as_half(static_cast<uint16_t>(w_lo[0] >> 16)));
-                const __half2 d_hi = __half2half2(__ushort_as_half(static_cast<uint16_t>(w_hi[0] & 0xFFFFu)));
-                const __half2 m_hi = __half2half2(__ushort_as_half(static_cast<uint16_t>(w_hi[0] >> 16)));
-
-                const uint32_t* avw = reinterpret_cast<const uint32_t*>(av);
-#pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-                    const uint32_t x = w_lo[1 + wi];  // row g:     bytes 4wi..4wi+3
-                    const uint32_t y = w_hi[1 + wi];  // row g + 8
-                    const uint32_t x8 = x >> 8;
-                    const uint32_t y8 = y >> 8;
-                    // Low nibbles (k 4wi..4wi+3): nibble | 0x6400 = 1024 + q.  Pair A = bytes 0, 2
-                    // -> (k+0, k+2); pair B = bytes 1, 3 -> (k+1, k+3).
-                    {
-                        const uint32_t r0 = avw[2 * wi];
-                        const uint32_t r1 = avw[2 * wi + 1];
-                        mma_m16n8k16(acc0, scale_pair<0x6400>(and_or(x, 0x000F000Fu, 0x64006400u), d_lo, m_lo),
-                                     scale_pair<0x6400>(and_or(y, 0x000F000Fu, 0x64006400u), d_hi, m_hi),
-                                     scale_pair<0x6400>(and_or(x8, 0x000F000Fu, 0x64006400u), d_lo, m_lo),
-                                     scale_pair<0x6400>(and_or(y8, 0x000F000Fu, 0x64006400u), d_hi, m_hi),
-                                     __byte_perm(r0, r1, 0x5410), __byte_perm(r0, r1, 0x7632));
-                    }
-                    // High nibbles (k 16+4wi..): left in place, (nibble << 4) | 0x5400 = 64 + q.
-                    {
-                        const uint32_t r0 = avw[8 + 2 * wi];
-                        const uint32_t r1 = avw[8 + 2 * wi + 1];
-                        mma_m16n8k16(acc1, scale_pair<0x5400>(and_or(x, 0x00F000F0u, 0x54005400u), d_lo, m_lo),
-                                     scale_pair<0x5400>(and_or(y, 0x00F000F0u, 0x54005400u), d_hi, m_hi),
-                                     scale_pair<0x5400>(and_or(x8, 0x00F000F0u, 0x54005400u), d_lo, m_lo),
-                                     scale_pair<0x5400>(and_or(y8, 0x00F000F0u, 0x54005400u), d_hi, m_hi),
-                                     __byte_perm(r0, r1, 0x5410), __byte_perm(r0, r1, 0x7632));
-                    }
-                }
-                if (gi + 1 < groups) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        av[j] = av_next[j];
-                    }
-                }
+                mma_block(s_lo + (gi + 1) * kGroupWords, s_hi + (gi + 1) * kGroupWords, av1, acc0, acc1);
+            }
+            if (gi < groups) {
+                mma_block(s_lo + gi * kGroupWords, s_hi + gi * kGroupWords, av0, acc0, acc1);
             }
         }
         if (ch + num_bufs < num_chunks) {
