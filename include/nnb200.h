@@ -122,6 +122,10 @@ typedef struct nnb200_gemm_i8_args {
      * multi-GPU path; this has no counterpart there. */
     int32_t num_peer_outs;
     void* peer_out[7];
+    /* Optional: sum_k W[n][k] per channel, already on the device (the r_w section of a packed
+     * weight, see nnb200_i8_pack).  A call that needs zero-point compensation then skips its
+     * sweep over W.  Single-batch weights only (w_batch_stride == 0 or batch == 1). */
+    const int32_t* r_w;
 } nnb200_gemm_i8_args;
 
 /* Scratch the call needs (0 for the common zero-point-free tensor-core call). */
@@ -207,6 +211,32 @@ NNB200_API int nnb200_q4_1_engine(const nnb200_q4_1_args* args);
  * Device twin of pack_q4 (include/nnops/detail/q4_1.hpp:152-184). */
 NNB200_API int nnb200_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, int64_t k, void* out,
                        int32_t out_f16, int64_t ld_out, void* stream);
+
+/*
+ * Prepacked int8 weights -- the device blob behind the operators' two-step prepackWeights
+ * contract (reference include/nnops/core/op_base.hpp:72-80).  The reference's CUDA operators
+ * answer "no packed form" (src/ops/linear.cpp:125-128); with a blob a call stages no per-channel
+ * array and, when activation zero points are in play, does not sweep W a second time.
+ *
+ * Blob = nnb200_i8_pack_bytes(n, k) = n * (pitch + 12) bytes, pitch = k rounded up to 16:
+ * W as [n][pitch] s8 k-contiguous and zero padded (whatever pose the source had), then scale_w[n]
+ * f32, zp_w[n] s32, r_w[n] s32 (sum_k W[n][k]).  nnb200_i8_packed_view only does the pointer
+ * arithmetic.  w is device memory; scale_w / zp_w may be host or device arrays or NULL (then the
+ * scalar fills the section).  blob must be 16-byte aligned device memory.
+ */
+typedef struct nnb200_i8_packed {
+    const void* w;        /* [n][pitch] s8; use with w_stride_n = pitch, w_stride_k = 1 */
+    int64_t pitch;
+    const float* scale_w; /* [n] */
+    const int32_t* zp_w;  /* [n] */
+    const int32_t* r_w;   /* [n] */
+} nnb200_i8_packed;
+
+NNB200_API size_t nnb200_i8_pack_bytes(int64_t n, int64_t k);
+NNB200_API int nnb200_i8_pack(const void* w, int64_t n, int64_t k, int64_t w_stride_n, int64_t w_stride_k,
+                              const float* scale_w, float scale_w_scalar, const int32_t* zp_w, int32_t zp_w_scalar,
+                              void* blob, size_t blob_bytes, void* stream);
+NNB200_API int nnb200_i8_packed_view(const void* blob, int64_t n, int64_t k, nnb200_i8_packed* view);
 
 /*
  * QuantizeLinear / DequantizeLinear (reference operators include/nnops/ops/quant_linear.hpp:24-141;

@@ -103,7 +103,10 @@ struct Epilogue {
     int64_t quant_axis = 0;
 };
 
-enum class TensorLayout : uint8_t { Dense = 0 };
+/// Dense, plus this backend's packed int8 weight (nnb200_i8_pack's blob).  The reference numbers
+/// its layout tags append-only and 15 is its highest (include/nnops/core/tensor_layout.hpp:100-118);
+/// 16 is the next free value.
+enum class TensorLayout : uint8_t { Dense = 0, PackedI8B200 = 16 };
 
 /// Fixed-capacity dimension list (the reference uses an inline small vector of 8).
 struct Dims {
@@ -275,6 +278,11 @@ public:
     using OpBase::compute;
     Status compute(std::span<TensorView> outputs, std::span<const TensorView> inputs, const ComputeContext& ctx = {},
                    void* workspace = nullptr) override;
+    /// int8 weights on CUDA: the query answers a [N, K] s8 view tagged TensorLayout::PackedI8B200
+    /// whose pitch makes N * pitch the blob size; the second call fills it.  compute() accepts
+    /// the packed view in place of W.  Other weights answer "no packed form".
+    void prepackWeights(std::span<const TensorView> inputs, std::span<TensorView> outputs,
+                        const ComputeContext& ctx = {}) override;
     OpType getOpType() const override { return OpType::Linear; }
     Backend getBackend() const override { return backend_; }
     const LinearAttributes& attributes() const noexcept { return attrs_; }
@@ -310,6 +318,10 @@ public:
     using OpBase::compute;
     Status compute(std::span<TensorView> outputs, std::span<const TensorView> inputs, const ComputeContext& ctx = {},
                    void* workspace = nullptr) override;
+    /// As Linear::prepackWeights, for a 2-D B operand in either pose; the packed view stands for
+    /// the [N, K] form, so compute() reads it as if transpose_b were set.
+    void prepackWeights(std::span<const TensorView> inputs, std::span<TensorView> outputs,
+                        const ComputeContext& ctx = {}) override;
     OpType getOpType() const override { return OpType::MatMul; }
     Backend getBackend() const override { return backend_; }
     const MatMulAttributes& attributes() const noexcept { return attrs_; }
@@ -387,6 +399,8 @@ Status linear_cuda(const LinearAttributes& attrs, TensorView& output, std::span<
                    const ComputeContext& ctx, void* workspace);
 Status matmul_cuda(const MatMulAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
                    const ComputeContext& ctx, void* workspace);
+/// Two-step prepack of a 2-D int8 weight (w_is_nk: stored [N, K], else [K, N]); see Linear::prepackWeights.
+void prepack_i8_cuda(const TensorView& weight, bool w_is_nk, TensorView& packed, const ComputeContext& ctx);
 /// ... and the two of QuantizeLinear / DequantizeLinear (declared at src/ops/quant_linear.cpp:21-28).
 Status quantize_linear_cuda(const QuantLinearAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
                             const ComputeContext& ctx, void* workspace);

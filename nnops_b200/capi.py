@@ -43,6 +43,7 @@ class GemmI8Args(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("force_engine", C.c_int32),
         ("num_peer_outs", C.c_int32), ("peer_out", C.c_void_p * 7),
+        ("r_w", C.c_void_p),
     ]
 
 
@@ -68,6 +69,12 @@ Q4_FLAG_OVERLAP_PREVIOUS = 1
 ZP_S8, ZP_U8, ZP_S32 = 0, 1, 2   # nnb200_quant_linear_args.zp_unsigned: storage type of the zero points
 
 
+class I8Packed(C.Structure):
+    """Mirror of nnb200_i8_packed: the sections of a packed int8 weight."""
+    _fields_ = [("w", C.c_void_p), ("pitch", C.c_int64), ("scale_w", C.c_void_p), ("zp_w", C.c_void_p),
+                ("r_w", C.c_void_p)]
+
+
 class QuantLinearArgs(C.Structure):
     """Mirror of nnb200_quant_linear_args."""
     _fields_ = [
@@ -88,6 +95,10 @@ SYMBOLS = [
     ("nnb200_q4_1_engine", C.c_int, [C.POINTER(Q41Args)]),
     ("nnb200_q4_1_decode", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32,
                                      C.c_int64, C.c_void_p]),
+    ("nnb200_i8_pack_bytes", C.c_size_t, [C.c_int64, C.c_int64]),
+    ("nnb200_i8_pack", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_float,
+                                 C.c_void_p, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p]),
+    ("nnb200_i8_packed_view", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.POINTER(I8Packed)]),
     ("nnb200_quantize_linear", C.c_int, [C.POINTER(QuantLinearArgs), C.c_void_p]),
     ("nnb200_dequantize_linear", C.c_int, [C.POINTER(QuantLinearArgs), C.c_void_p]),
     ("nnb200_interleave_shards", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64,

@@ -278,12 +278,13 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
             uint8_t* ws = static_cast<uint8_t*>(a->workspace) + static_cast<size_t>(b) * (ra_bytes + rw_bytes);
             int32_t* r_a = reinterpret_cast<int32_t*>(ws);
             int32_t* r_w = reinterpret_cast<int32_t*>(ws + ra_bytes);
-            const int st = launch_i8_sums(p, r_a, r_w, stream);
+            const bool have_rw = a->r_w != nullptr && (a->batch == 1 || a->w_batch_stride == 0);
+            const int st = launch_i8_sums(p, r_a, have_rw ? nullptr : r_w, stream);
             if (st != NNB200_OK) {
                 return st;
             }
             ep.r_a = r_a;
-            ep.r_w = r_w;
+            ep.r_w = have_rw ? a->r_w : r_w;
         }
         int st;
         switch (pick_i8_engine(a, p)) {
@@ -391,6 +392,54 @@ int nnb200_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, i
         return NNB200_UNSUPPORTED;
     }
     return launch_q4_1_decode(w_blocks, ldw_blocks, rows, k, out, out_f16, ld_out, static_cast<cudaStream_t>(stream));
+}
+
+size_t nnb200_i8_pack_bytes(int64_t n, int64_t k)
+{
+    if (n <= 0 || k <= 0) {
+        return 0;
+    }
+    return static_cast<size_t>(n) * static_cast<size_t>(i8_pack_pitch(k) + 12);
+}
+
+int nnb200_i8_packed_view(const void* blob, int64_t n, int64_t k, nnb200_i8_packed* view)
+{
+    if (blob == nullptr || view == nullptr || n <= 0 || k <= 0) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    const uint8_t* base = static_cast<const uint8_t*>(blob);
+    const int64_t pitch = i8_pack_pitch(k);
+    view->w = base;
+    view->pitch = pitch;
+    view->scale_w = reinterpret_cast<const float*>(base + n * pitch);
+    view->zp_w = reinterpret_cast<const int32_t*>(base + n * pitch + n * 4);
+    view->r_w = reinterpret_cast<const int32_t*>(base + n * pitch + n * 8);
+    return NNB200_OK;
+}
+
+int nnb200_i8_pack(const void* w, int64_t n, int64_t k, int64_t w_stride_n, int64_t w_stride_k, const float* scale_w,
+                   float scale_w_scalar, const int32_t* zp_w, int32_t zp_w_scalar, void* blob, size_t blob_bytes,
+                   void* stream)
+{
+    if (n < 0 || k < 0) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if (n == 0 || k == 0) {
+        return NNB200_OK;
+    }
+    if (w == nullptr || blob == nullptr || blob_bytes < nnb200_i8_pack_bytes(n, k) ||
+        (reinterpret_cast<uintptr_t>(blob) & 15u) != 0 || (w_stride_n != 1 && w_stride_k != 1)) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    if (dev->cc_major != 10) {
+        return NNB200_UNSUPPORTED;
+    }
+    return launch_i8_pack(w, n, k, w_stride_n, w_stride_k, scale_w, scale_w_scalar, zp_w, zp_w_scalar, blob,
+                          static_cast<cudaStream_t>(stream));
 }
 
 static int quant_linear_call(const nnb200_quant_linear_args* q, void* stream, bool quantize)

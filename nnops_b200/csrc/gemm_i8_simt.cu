@@ -263,8 +263,10 @@ int launch_i8_sums(const I8Problem& p, int32_t* r_a, int32_t* r_w, cudaStream_t 
     } else {
         i8_sums_kernel<false><<<static_cast<unsigned>(p.m), 128, 0, stream>>>(a, p.m, p.k, p.a_stride_m, p.a_stride_k, r_a);
     }
-    i8_sums_kernel<false><<<static_cast<unsigned>(p.n), 128, 0, stream>>>(w, p.n, p.k, p.w_stride_n, p.w_stride_k, r_w);
-    note_launch(2);
+    if (r_w != nullptr) {
+        i8_sums_kernel<false><<<static_cast<unsigned>(p.n), 128, 0, stream>>>(w, p.n, p.k, p.w_stride_n, p.w_stride_k, r_w);
+    }
+    note_launch(r_w != nullptr ? 2 : 1);
     return cuda_status(cudaGetLastError());
 }
 

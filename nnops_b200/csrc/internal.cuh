@@ -59,7 +59,8 @@ bool narrow_i8_supported(const I8Problem& p);
 int launch_gemm_i8_decode(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
 bool decode_i8_supported(const I8Problem& p);
 
-// R_a[m] = sum_k A[m][k] and R_w[n] = sum_k W[n][k] into int32 scratch.
+// R_a[m] = sum_k A[m][k] and R_w[n] = sum_k W[n][k] into int32 scratch; r_w == nullptr skips the
+// sweep over W (the caller has the sums already).
 int launch_i8_sums(const I8Problem& p, int32_t* r_a, int32_t* r_w, cudaStream_t stream);
 
 int launch_q4_1_gemv(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
@@ -75,6 +76,10 @@ int launch_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, i
 
 int launch_quantize_linear(const nnb200_quant_linear_args& q, const DeviceInfo& dev, cudaStream_t stream);
 int launch_dequantize_linear(const nnb200_quant_linear_args& q, const DeviceInfo& dev, cudaStream_t stream);
+
+int64_t i8_pack_pitch(int64_t k);
+int launch_i8_pack(const void* w, int64_t n, int64_t k, int64_t stride_n, int64_t stride_k, const float* scale_w,
+                   float scale_scalar, const int32_t* zp_w, int32_t zp_scalar, void* blob, cudaStream_t stream);
 
 int launch_interleave_shards(const void* src, void* dst, int64_t m, int64_t row_bytes_per_shard, int g,
                              int64_t dst_pitch_bytes, const DeviceInfo& dev, cudaStream_t stream);

@@ -102,6 +102,18 @@ bool batch_layout(const TensorView& a, const TensorView& b, const TensorView& c,
     return true;
 }
 
+// True for a weight view that holds nnb200_i8_pack's blob (stand-alone API only: the reference's
+// layout enumeration has no such tag, and its CUDA operators answer "no packed form").
+bool is_packed_i8(const TensorView& w)
+{
+#ifdef NNB200_USE_NNOPS_HEADERS
+    (void)w;
+    return false;
+#else
+    return w.layout() == TensorLayout::PackedI8B200;
+#endif
+}
+
 // One quantization array as the kernels want it: a device pointer (or null + scalar).
 struct DeviceArray {
     const void* ptr = nullptr;
@@ -207,6 +219,17 @@ Status run_i8(const I8Call& c, const ComputeContext& ctx)
     g.a_stride_k = c.transpose_a ? a.row_stride_elems() : 1;
     g.w_stride_n = c.w_is_nk ? w.row_stride_elems() : 1;
     g.w_stride_k = c.w_is_nk ? 1 : w.row_stride_elems();
+    nnb200_i8_packed pk{};
+    const bool packed = is_packed_i8(w);
+    if (packed) {
+        // The blob holds W as [N][pitch], its per-channel arrays and its row sums on the device.
+        if (nnb200_i8_packed_view(w.ptr<void>(), N, Ka, &pk) != NNB200_OK) {
+            return Status::invalid_argument;
+        }
+        g.w_stride_n = pk.pitch;
+        g.w_stride_k = 1;
+        g.r_w = pk.r_w;
+    }
     g.ldc = out.row_stride_elems();
     g.batch = 1;
     g.a_unsigned = a.data_type() == DataType::u8;
@@ -243,8 +266,10 @@ Status run_i8(const I8Call& c, const ComputeContext& ctx)
     const size_t m_bytes = static_cast<size_t>(M) * 4, n_bytes = static_cast<size_t>(N) * 4;
     st.reserve(qa.scale_data, m_bytes);
     st.reserve(qa.zero_point_data, m_bytes);
-    st.reserve(qw.scale_data, n_bytes);
-    st.reserve(qw.zero_point_data, n_bytes);
+    if (!packed) {
+        st.reserve(qw.scale_data, n_bytes);
+        st.reserve(qw.zero_point_data, n_bytes);
+    }
     // Scratch for the two zero-point sweeps, only when some zero point can be non-zero.
     if (qa.zero_point != 0 || qw.zero_point != 0 || qa.zero_point_data != nullptr || qw.zero_point_data != nullptr) {
         st.reserve_raw(((m_bytes + 255) & ~size_t(255)) + ((n_bytes + 255) & ~size_t(255)));
@@ -253,10 +278,27 @@ Status run_i8(const I8Call& c, const ComputeContext& ctx)
         return to_status(e);
     }
     DeviceArray sa, za, sw, zw;
-    for (const int e : {st.place(qa.scale_data, m_bytes, false, sa), st.place(qa.zero_point_data, m_bytes, true, za),
-                        st.place(qw.scale_data, n_bytes, false, sw), st.place(qw.zero_point_data, n_bytes, true, zw)}) {
+    for (const int e : {st.place(qa.scale_data, m_bytes, false, sa), st.place(qa.zero_point_data, m_bytes, true, za)}) {
         if (e != NNB200_OK) {
             return to_status(e);
+        }
+    }
+    if (packed) {
+        // Per-channel arrays were copied into the blob at pack time; the view's own (host) arrays
+        // only tell which of them are in use, and whether any zero point is non-zero.
+        if (qw.scale_data != nullptr) {
+            sw.ptr = pk.scale_w;
+        }
+        if (qw.zero_point_data != nullptr) {
+            zw.ptr = pk.zp_w;
+            zw.any_nonzero = nnb200_is_device_pointer(qw.zero_point_data) != 0 ||
+                             std::any_of(qw.zero_point_data, qw.zero_point_data + N, [](int32_t x) { return x != 0; });
+        }
+    } else {
+        for (const int e : {st.place(qw.scale_data, n_bytes, false, sw), st.place(qw.zero_point_data, n_bytes, true, zw)}) {
+            if (e != NNB200_OK) {
+                return to_status(e);
+            }
         }
     }
     g.scale_a = static_cast<const float*>(sa.ptr);
@@ -268,6 +310,7 @@ Status run_i8(const I8Call& c, const ComputeContext& ctx)
     g.a = a.ptr<void>();
     g.w = w.ptr<void>();
     g.out = out.ptr<void>();
+    // Zero-point scratch is sized from the argument block; reserve it now that the block is final.
     const size_t need = nnb200_gemm_i8_workspace_bytes(&g);
     if (need > 0) {
         g.workspace = st.take_raw(need);
@@ -523,6 +566,38 @@ Status linear_cuda(const LinearAttributes& attrs, TensorView& output, std::span<
     return Status::unsupported;  // dense fp Linear is outside this backend
 }
 
+#ifndef NNB200_USE_NNOPS_HEADERS
+// Two-step prepack of a 2-D s8 weight: an empty `packed` is set to the geometry of the blob (a
+// [N, K] s8 view tagged PackedI8B200 whose pitch gives N * pitch = the blob's bytes, carrying the
+// weight's QuantParams); a populated one is filled on the stream.  Anything else answers
+// "no packed form" by leaving `packed` alone.
+void prepack_i8_cuda(const TensorView& weight, bool w_is_nk, TensorView& packed, const ComputeContext& ctx)
+{
+    if (weight.data_type() != DataType::s8 || weight.rank() != 2) {
+        return;
+    }
+    const int64_t n = w_is_nk ? weight.shape(0) : weight.shape(1);
+    const int64_t k = w_is_nk ? weight.shape(1) : weight.shape(0);
+    if (n <= 0 || k <= 0) {
+        return;
+    }
+    const int64_t pitch = static_cast<int64_t>(nnb200_i8_pack_bytes(n, k)) / n;
+    const int64_t shape[2] = {n, k};
+    if (packed.is_empty()) {
+        packed = TensorView(shape, DataType::s8, nullptr, pitch, TensorLayout::PackedI8B200, weight.quant_params());
+        return;
+    }
+    if (packed.layout() != TensorLayout::PackedI8B200 || packed.rank() != 2 || packed.shape(0) != n ||
+        packed.shape(1) != k || packed.pitch() != pitch) {
+        return;  // not the geometry the query gave
+    }
+    const QuantParams& q = weight.quant_params();
+    nnb200_i8_pack(weight.ptr<void>(), n, k, w_is_nk ? weight.row_stride_elems() : 1,
+                   w_is_nk ? 1 : weight.row_stride_elems(), q.scale_data, q.scale, q.zero_point_data, q.zero_point,
+                   packed.ptr<void>(), static_cast<size_t>(n * pitch), ctx.cuda_stream);
+}
+#endif
+
 Status matmul_cuda(const MatMulAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
                    const ComputeContext& ctx, void*)
 {
@@ -537,7 +612,8 @@ Status matmul_cuda(const MatMulAttributes& attrs, TensorView& output, std::span<
         if (!out_kind_of(output.data_type(), kind)) {
             return Status::unsupported;
         }
-        const I8Call call{&a, &b, bias, &output, attrs.transpose_a, attrs.transpose_b, &attrs.epilogue, kind};
+        const I8Call call{&a, &b, bias, &output, attrs.transpose_a, attrs.transpose_b || is_packed_i8(b), &attrs.epilogue,
+                          kind};
         return run_i8(call, ctx);
     }
     if (b.data_type() == DataType::q4_1) {

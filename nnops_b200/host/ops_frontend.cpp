@@ -116,6 +116,15 @@ Status Linear::compute(std::span<TensorView> outputs, std::span<const TensorView
     return backend::cuda::linear_cuda(attrs_, outputs[0], inputs, ctx, workspace);
 }
 
+void Linear::prepackWeights(std::span<const TensorView> inputs, std::span<TensorView> outputs,
+                            const ComputeContext& ctx)
+{
+    if (backend_ != Backend::CUDA || inputs.empty() || outputs.empty()) {
+        return;
+    }
+    backend::cuda::prepack_i8_cuda(inputs[0], true, outputs[0], ctx);
+}
+
 // ---- MatMul -----------------------------------------------------------------------------
 
 std::unique_ptr<MatMul> MatMul::create(const MatMulAttributes& attrs, Backend backend)
@@ -128,8 +137,9 @@ std::vector<TensorDesc> MatMul::getOutputTensorDesc(std::span<const TensorDesc> 
     const TensorDesc& a = inputs[0];
     const TensorDesc& b = inputs[1];
     const int64_t ra = a.rank, rb = b.rank;
+    const bool b_is_nk = attrs_.transpose_b || b.layout == TensorLayout::PackedI8B200;  // a packed B stands for [N, K]
     const int64_t M = attrs_.transpose_a ? a.dims[static_cast<size_t>(ra - 1)] : a.dims[static_cast<size_t>(ra - 2)];
-    const int64_t N = attrs_.transpose_b ? b.dims[static_cast<size_t>(rb - 2)] : b.dims[static_cast<size_t>(rb - 1)];
+    const int64_t N = b_is_nk ? b.dims[static_cast<size_t>(rb - 2)] : b.dims[static_cast<size_t>(rb - 1)];
     // numpy broadcast of the leading axes, right-aligned.
     const int64_t la = ra - 2, lb = rb - 2, lr = std::max(la, lb);
     TensorDesc out;
@@ -164,7 +174,8 @@ Status MatMul::validate(std::span<const TensorDesc> inputs, std::span<const Tens
         return Status::unsupported;
     }
     const int64_t k_a = attrs_.transpose_a ? a.dims[static_cast<size_t>(a.rank - 2)] : a.dims[static_cast<size_t>(a.rank - 1)];
-    const int64_t k_b = attrs_.transpose_b ? b.dims[static_cast<size_t>(b.rank - 1)] : b.dims[static_cast<size_t>(b.rank - 2)];
+    const bool b_is_nk = attrs_.transpose_b || b.layout == TensorLayout::PackedI8B200;
+    const int64_t k_b = b_is_nk ? b.dims[static_cast<size_t>(b.rank - 1)] : b.dims[static_cast<size_t>(b.rank - 2)];
     return k_a == k_b ? Status::ok : Status::invalid_argument;
 }
 
@@ -181,6 +192,15 @@ Status MatMul::compute(std::span<TensorView> outputs, std::span<const TensorView
         return Status::unsupported;
     }
     return backend::cuda::matmul_cuda(attrs_, outputs[0], inputs, ctx, workspace);
+}
+
+void MatMul::prepackWeights(std::span<const TensorView> inputs, std::span<TensorView> outputs,
+                            const ComputeContext& ctx)
+{
+    if (backend_ != Backend::CUDA || inputs.empty() || outputs.empty()) {
+        return;
+    }
+    backend::cuda::prepack_i8_cuda(inputs[0], attrs_.transpose_b, outputs[0], ctx);
 }
 
 // ---- QuantizeLinear / DequantizeLinear -----------------------------------------------------

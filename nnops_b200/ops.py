@@ -32,7 +32,7 @@ def _dev_array(v, dtype: torch.dtype, device: torch.device, count: int | None):
 def gemm_i8_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, out_kind: str, bias=None, relu=False,
                  activation="none", act_alpha=0.0, act_beta=1.0, min_clip=-math.inf, max_clip=math.inf,
                  scale_a=1.0, scale_w=1.0, zp_a=0, zp_w=0, out_scale=1.0, out_zp=0, workspace=None,
-                 engine="auto", keep: list | None = None) -> capi.GemmI8Args:
+                 engine="auto", r_w: torch.Tensor | None = None, keep: list | None = None) -> capi.GemmI8Args:
     """Fill the C argument block.  ``a`` is [M,K] or [B,M,K] (s8/u8), ``w`` the LOGICAL [N,K]
     (or [B,N,K]) s8 matrix -- pass ``w_kn.transpose(-1,-2)`` for a weight stored [K,N].
     Tensors created for quantization arrays are appended to ``keep`` so they outlive the call."""
@@ -81,7 +81,8 @@ def gemm_i8_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, out_kin
         zp_a_nonzero=int(za is not None and bool((za != 0).any().item())),
         zp_w_nonzero=int(zw is not None and bool((zw != 0).any().item())),
         out_scale=float(out_scale), out_zp=int(out_zp),
-        workspace=None, workspace_bytes=0, force_engine=capi.ENGINES[engine])
+        workspace=None, workspace_bytes=0, force_engine=capi.ENGINES[engine],
+        r_w=r_w.data_ptr() if r_w is not None else None)
     need = capi.lib().nnb200_gemm_i8_workspace_bytes(C.byref(args))
     if need:
         if workspace is None:
@@ -107,6 +108,60 @@ def gemm_i8(a: torch.Tensor, w: torch.Tensor, *, out_kind: str = "s32", out: tor
     with torch.cuda.device(a.device):
         capi.check(capi.lib().nnb200_gemm_i8(C.byref(args), _stream_ptr(a.device)), "nnb200_gemm_i8")
     return out
+
+
+class PackedI8:
+    """A prepacked int8 weight: one device blob holding W as [N][pitch] k-contiguous plus the
+    per-channel scale, zero point and row-sum sections (see nnb200_i8_pack in nnb200.h)."""
+
+    def __init__(self, blob: torch.Tensor, n: int, k: int, zp_nonzero: bool):
+        self.blob, self.n, self.k, self.zp_nonzero = blob, n, k, zp_nonzero
+        view = capi.I8Packed()
+        capi.check(capi.lib().nnb200_i8_packed_view(blob.data_ptr(), n, k, C.byref(view)), "nnb200_i8_packed_view")
+        pitch = view.pitch
+        self.w = blob[: n * pitch].view(torch.int8).view(n, pitch)[:, :k]          # [N, K] view with the packed pitch
+        self.scale_w = blob[n * pitch: n * pitch + 4 * n].view(torch.float32)
+        self.zp_w = blob[n * pitch + 4 * n: n * pitch + 8 * n].view(torch.int32)
+        self.r_w = blob[n * pitch + 8 * n: n * pitch + 12 * n].view(torch.int32)
+
+
+def prepack_i8(w: torch.Tensor, *, scale_w=1.0, zp_w=0) -> PackedI8:
+    """Pack the LOGICAL [N, K] s8 weight ``w`` (any strides: pass ``w_kn.t()`` for [K, N] storage)
+    with its per-channel or per-tensor parameters (host or device arrays, or scalars)."""
+    if w.dim() != 2 or w.dtype != torch.int8 or not w.is_cuda:
+        raise ValueError("w must be a 2-D int8 CUDA tensor")
+    n, k = w.shape
+    if w.stride(0) != 1 and w.stride(1) != 1:
+        raise ValueError("one of the weight's strides must be 1")
+    blob = torch.empty(capi.lib().nnb200_i8_pack_bytes(n, k), dtype=torch.uint8, device=w.device)
+    keep = []
+
+    def arr(v, dt):
+        if isinstance(v, (int, float)):
+            return None, v
+        t = torch.as_tensor(v, dtype=dt).contiguous()       # stays where it is: host or device
+        if t.numel() != n:
+            raise ValueError(f"expected {n} per-channel entries")
+        keep.append(t)
+        return t, (1.0 if dt is torch.float32 else 0)
+
+    s, s0 = arr(scale_w, torch.float32)
+    z, z0 = arr(zp_w, torch.int32)
+    with torch.cuda.device(w.device):
+        capi.check(capi.lib().nnb200_i8_pack(
+            w.data_ptr(), n, k, w.stride(0) if n > 1 or w.stride(0) == 1 else k, w.stride(1) if k > 1 else 1,
+            s.data_ptr() if s is not None else None, float(s0), z.data_ptr() if z is not None else None, int(z0),
+            blob.data_ptr(), blob.numel(), _stream_ptr(w.device)), "nnb200_i8_pack")
+        if any(not t.is_cuda for t in keep):
+            torch.cuda.current_stream(w.device).synchronize()   # host arrays must outlive the copies
+    zp_nonzero = bool((z != 0).any().item()) if z is not None else int(z0) != 0
+    return PackedI8(blob, n, k, zp_nonzero)
+
+
+def gemm_i8_packed(a: torch.Tensor, packed: PackedI8, **kw):
+    """gemm_i8 against a prepacked weight: per-channel arrays and row sums come from the blob."""
+    return gemm_i8(a, packed.w, scale_w=packed.scale_w, zp_w=packed.zp_w if packed.zp_nonzero else 0,
+                   r_w=packed.r_w, **kw)
 
 
 def gemm_i8_engine(a, w, out, **kw) -> str:

@@ -465,12 +465,22 @@ static void contract_cases()
         TensorView o0v = view(o0, DataType::s32, out.p);
         EXPECT(op->compute(o0v, ins) == Status::ok);
     }
-    {   // the two-step prepack query answers "no packed form" on CUDA
+    {   // the two-step prepack query
         TensorView packed;
         const TensorView ins[] = {view(ws, DataType::s8, w.p)};
         TensorView outs[] = {packed};
         op->prepackWeights(ins, outs);
-        EXPECT(outs[0].is_empty());
+#ifdef NNB200_USE_NNOPS_HEADERS
+        EXPECT(outs[0].is_empty());  // the reference's CUDA front end: "no packed form"
+#else
+        EXPECT(outs[0].is_empty() && outs[0].rank() == 2 && outs[0].layout() == TensorLayout::PackedI8B200);
+        const int64_t f32s[] = {8, 64};
+        TensorView none;
+        const TensorView fp[] = {view(f32s, DataType::f32, w.p)};
+        TensorView fouts[] = {none};
+        op->prepackWeights(fp, fouts);
+        EXPECT(fouts[0].rank() == 0);  // other weights: no packed form
+#endif
     }
     EXPECT(op->getWorkspaceSize({}, {}) == 0);
 }
@@ -582,6 +592,86 @@ static void linear_fp_act_case(int64_t batch, int64_t m, int64_t n, int64_t k, b
     }
 #endif
 }
+
+// ---- prepacked int8 weights (stand-alone API; the reference's CUDA operators have no packed form) ----
+#ifndef NNB200_USE_NNOPS_HEADERS
+static void prepack_case(bool matmul_kn, int64_t m, int64_t n, int64_t k, const char* name, cudaStream_t stream)
+{
+    g_case = name;
+    std::mt19937_64 rng(m * 13 + n * 5 + k);
+    std::vector<uint8_t> a(m * k);
+    std::vector<int8_t> w(n * k), w_kn(k * n);
+    for (auto& v : a) v = static_cast<uint8_t>(rng() % 256);
+    for (auto& v : w) v = static_cast<int8_t>(static_cast<int>(rng() % 255) - 127);
+    for (int64_t i = 0; i < n; ++i) {
+        for (int64_t j = 0; j < k; ++j) w_kn[j * n + i] = w[i * k + j];
+    }
+    std::vector<float> sa(m), sw(n);
+    std::vector<int32_t> za(m), zw(n), bias(n);
+    std::uniform_real_distribution<float> us(0.001f, 0.02f), ua(0.01f, 0.03f);
+    for (auto& v : sa) v = ua(rng);
+    for (auto& v : sw) v = us(rng);
+    for (auto& v : za) v = 100 + static_cast<int32_t>(rng() % 40);
+    for (auto& v : zw) v = static_cast<int32_t>(rng() % 19) - 9;
+    for (auto& v : bias) v = static_cast<int32_t>(rng() % 2001) - 1000;
+
+    std::vector<int8_t> want(m * n);
+    oracle_gemm_i8_args o{};
+    o.a = a.data(); o.w = w.data(); o.out = want.data();
+    o.m = m; o.n = n; o.k = k;
+    o.a_stride_m = k; o.a_stride_k = 1; o.w_stride_n = k; o.w_stride_k = 1; o.ldc = n;
+    o.a_unsigned = 1; o.out_kind = 1; o.bias = bias.data(); o.relu = 1;
+    o.scale_a = sa.data(); o.scale_w = sw.data(); o.zp_a = za.data(); o.zp_w = zw.data();
+    o.scale_a_scalar = 1.0f; o.scale_w_scalar = 1.0f;
+    o.out_scale = 2.3f; o.out_zp = -3;
+    o.min_clip = -INFINITY; o.max_clip = INFINITY;
+    oracle_gemm_i8(&o);
+
+    DevBuf da(a.data(), a.size()), dw(matmul_kn ? w_kn.data() : w.data(), w.size()), dbias(bias.data(), n * 4), dout(m * n, 0x5A);
+    const int64_t as[] = {m, k}, ws_nk[] = {n, k}, ws_kn[] = {k, n}, bs[] = {n}, os[] = {m, n};
+    const QuantParams qa = arrays(sa.data(), za.data(), m, QuantGranularity::PerToken);
+    const QuantParams qw = arrays(sw.data(), zw.data(), n, QuantGranularity::PerChannel);
+    TensorView wv = matmul_kn ? TensorView(ws_kn, DataType::s8, dw.p, TensorLayout::Dense, qw)
+                              : TensorView(ws_nk, DataType::s8, dw.p, TensorLayout::Dense, qw);
+    ComputeContext ctx;
+    ctx.expected_backend = Backend::CUDA;
+    ctx.cuda_stream = stream;
+    LinearAttributes la;
+    la.output_dtype = DataType::s8;
+    la.epilogue.type = EpilogueActivateType::Relu;
+    MatMulAttributes ma;
+    ma.output_dtype = DataType::s8;
+    ma.epilogue.type = EpilogueActivateType::Relu;
+    auto lin = Linear::create(la, Backend::CUDA);
+    auto mm = MatMul::create(ma, Backend::CUDA);
+    OpBase* op = matmul_kn ? static_cast<OpBase*>(mm.get()) : static_cast<OpBase*>(lin.get());
+
+    // Step 1: the query describes the blob.  Step 2: allocate that much and pack.
+    TensorView packed;
+    {
+        const TensorView ins[] = {wv};
+        TensorView outs[] = {packed};
+        op->prepackWeights(ins, outs, ctx);
+        packed = outs[0];
+    }
+    EXPECT(packed.is_empty() && packed.layout() == TensorLayout::PackedI8B200 && packed.shape(0) == n && packed.shape(1) == k);
+    const size_t blob_bytes = static_cast<size_t>(packed.shape(0) * packed.pitch());
+    EXPECT(blob_bytes == static_cast<size_t>(n) * static_cast<size_t>((k + 15) / 16 * 16 + 12));
+    DevBuf blob(blob_bytes);
+    TensorView filled(std::span<const int64_t>(packed.shape(), 2), DataType::s8, blob.p, packed.pitch(),
+                      TensorLayout::PackedI8B200, packed.quant_params());
+    {
+        const TensorView ins[] = {wv};
+        TensorView outs[] = {filled};
+        op->prepackWeights(ins, outs, ctx);
+    }
+    TensorView out = TensorView(os, DataType::s8, dout.p, TensorLayout::Dense, per_tensor(2.3f, -3));
+    const TensorView ins[] = {TensorView(as, DataType::u8, da.p, TensorLayout::Dense, qa), filled,
+                              TensorView(bs, DataType::s32, dbias.p)};
+    EXPECT(op->compute(out, ins, ctx) == Status::ok);
+    EXPECT(dout.download<int8_t>() == want);
+}
+#endif
 
 // ---- QuantizeLinear / DequantizeLinear ------------------------------------------------------
 
@@ -764,6 +854,12 @@ int main()
     linear_fp_act_case(1, 8, 520, 1024, true, true, false, true, "linear_fp_act_f16_decode_m8", stream);
     linear_fp_act_case(3, 64, 96, 128, false, true, true, false, "linear_fp_act_f32_batched_per_token", stream);
     linear_fp_act_case(1, 130, 140, 100, false, false, false, true, "linear_fp_act_f32_unaligned_k", nullptr);
+
+#ifndef NNB200_USE_NNOPS_HEADERS
+    prepack_case(false, 77, 130, 272, "prepack_linear_nk", stream);
+    prepack_case(true, 200, 330, 1000, "prepack_matmul_kn_storage", stream);
+    prepack_case(false, 4, 520, 1024, "prepack_linear_decode", nullptr);
+#endif
 
     kat_quant_linear();
     quant_linear_case({{64, 4096}, -1, 1, false, false}, "quant_linear_per_tensor_f32_s8", stream);
