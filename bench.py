@@ -272,6 +272,28 @@ def secondary_quant_linear(torch, dev, peaks):
     return out
 
 
+def secondary_i8_config2(torch, dev, peaks):
+    """The Llama-7B MLP shape of the benchmark's second configuration (M=512, N=11008, K=4096,
+    s8 out, per-channel requant, ReLU), cycling over enough weight copies to exceed L2."""
+    from nnops_b200 import ops, synth
+    c = synth.config2()
+    a = torch.from_numpy(c.a).to(dev)
+    w0 = torch.from_numpy(c.w).to(dev)
+    ws = [w0] + [w0.clone() for _ in range(5)]
+    o = torch.empty((c.a.shape[0], c.w.shape[0]), dtype=torch.int8, device=dev)
+    kw = {k: (torch.from_numpy(v).to(dev) if isinstance(v, np.ndarray) else v) for k, v in c.kwargs().items()}
+    kw.pop("out_kind", None)
+
+    def fn():
+        for w in ws:
+            ops.gemm_i8(a, w, out_kind="s8", out=o, **kw)
+
+    us = graph_time_us(torch, fn, calls_per_graph=2) / len(ws)
+    ops_count = 2.0 * c.a.shape[0] * c.w.shape[0] * c.a.shape[1]
+    tops = ops_count / us / 1e6
+    return {"i8_config2": {"tops": tops, "us_per_call": us, "frac_of_int8_peak": tops / (2.0 * peaks["bf16_tflops"])}}
+
+
 def run_kernel_only(args):
     """Three launches of one kernel on seeded inputs and nothing else: the command the ncu
     captures under profiles/ are taken from (`--kernel-only i8|gemv|q4gemm|q4gemm2 --shape M N K`)."""
@@ -490,6 +512,7 @@ def main():
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_secondary:
         extra = secondary_q4_1(torch, dev, peaks)
+        extra.update(secondary_i8_config2(torch, dev, peaks))
         extra.update(secondary_quant_linear(torch, dev, peaks))
         extra.update(secondary_i8_decode(torch, dev, peaks, layer.w, layer.kw["scale_w"], layer.kw["bias"]))
         cpu_baseline = cpu_reference_run(1024, 5, 2)

@@ -51,12 +51,18 @@ struct alignas(64) PeerMaps {
 
 template <int BN, bool PEERS = false>
 struct TileConfig {
+    // Tiles wider than 256 columns (single-wave form, see launch_gemm_i8_umma) are issued as two
+    // MMAs of BN / 2 columns over one A tile and keep ONE accumulator: a CTA owns exactly one tile.
+    static constexpr int kNSplit = BN > 256 ? 2 : 1;
+    static constexpr int kMmaN = BN / kNSplit;
     static constexpr int kATileBytes = kBlockM * kBlockKBytes;
     static constexpr int kBTileBytes = BN * kBlockKBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     // Ring depth: as many stages as fit beside the epilogue staging in ~200 KB.
-    static constexpr int kStages = PEERS ? ((BN == 256) ? 3 : 5) : ((BN > 128) ? 4 : (BN == 128 ? 6 : 8));
-    // Two accumulators BN columns apart; the allocation is a power of two of at least 2 * BN.
+    static constexpr int kStages = PEERS ? ((BN == 256) ? 3 : 5)
+                                   : (BN > 256) ? (BN > 384 ? 2 : 3)
+                                                : ((BN > 128) ? 4 : (BN == 128 ? 6 : 8));
+    // Two accumulators BN columns apart (one when BN > 256); a power of two of at least that.
     static constexpr int kTmemCols = BN > 128 ? 512 : 2 * BN;
     static constexpr int kColParamBytes = 4 * 4 * BN * 4;  // 4 epilogue warps x {scale, bias, r_w, zp_w} x BN x 4 B
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
@@ -285,7 +291,11 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     uint8_t* b_dst = a_dst + Cfg::kATileBytes;
                     mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
                     tma_load_2d(a_dst, &map_a, &full_bar[stage], kb * kBlockKBytes, tc.m_blk * kBlockM);
-                    tma_load_2d(b_dst, &map_w, &full_bar[stage], kb * kBlockKBytes, tc.n_blk * BN);
+#pragma unroll
+                    for (int h = 0; h < Cfg::kNSplit; ++h) {  // TMA boxes hold at most 256 rows
+                        tma_load_2d(b_dst + h * Cfg::kMmaN * kBlockKBytes, &map_w, &full_bar[stage], kb * kBlockKBytes,
+                                    tc.n_blk * BN + h * Cfg::kMmaN);
+                    }
                     armed |= 1u << stage;
                     armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
                     if (++stage == kStages) {
@@ -321,8 +331,8 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int local_tile = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
-                const int acc = local_tile & 1;
-                const uint32_t acc_phase = (local_tile >> 1) & 1u;
+                const int acc = Cfg::kNSplit > 1 ? 0 : (local_tile & 1);
+                const uint32_t acc_phase = Cfg::kNSplit > 1 ? (local_tile & 1u) : ((local_tile >> 1) & 1u);
                 if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag)) {
                     atomicCAS(error_word, 0, kErrAccumWait);
                     break;
@@ -343,8 +353,15 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int ks = 0; ks < kBlockKBytes / kUmmaK; ++ks) {
                         // +32 bytes of K per step = +2 in the descriptor's 16-byte address units.
-                        umma_i8(d_tmem, a_desc + static_cast<uint64_t>(ks * 2), b_desc + static_cast<uint64_t>(ks * 2),
-                                idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+                        for (int h = 0; h < Cfg::kNSplit; ++h) {
+                            // Second half of a wide tile: kMmaN rows further down the W tile (16-byte
+                            // descriptor units), kMmaN columns further along the accumulator.
+                            umma_i8(d_tmem + static_cast<uint32_t>(h * Cfg::kMmaN),
+                                    a_desc + static_cast<uint64_t>(ks * 2),
+                                    b_desc + static_cast<uint64_t>(ks * 2 + h * (Cfg::kMmaN * kBlockKBytes / 16)), idesc,
+                                    (kb > 0 || ks > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
                     if (++stage == kStages) {
@@ -370,8 +387,8 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int local_tile = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
             const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
-            const int acc = local_tile & 1;
-            const uint32_t acc_phase = (local_tile >> 1) & 1u;
+            const int acc = Cfg::kNSplit > 1 ? 0 : (local_tile & 1);
+            const uint32_t acc_phase = Cfg::kNSplit > 1 ? (local_tile & 1u) : ((local_tile >> 1) & 1u);
             const int n_base = tc.n_blk * BN;
 
             // Stage this tile's per-column terms (hidden behind the tile's main loop).
@@ -626,10 +643,22 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
                 bn = cand;
             }
         }
+        // Single-wave form: when the problem needs a second, mostly empty wave, a tile wide enough
+        // to give every CTA exactly one tile (two MMAs of BN / 2 columns per k-step) ends sooner.
+        for (const int wide : {320, 384, 448, 512}) {
+            const int64_t tiles = static_cast<int64_t>(num_m) * ((n + wide - 1) / wide);
+            if (tiles <= dev.sm_count) {
+                if (static_cast<int64_t>(wide) * 100 < best_cost * 92) {
+                    best_cost = wide;
+                    bn = wide;
+                }
+                break;  // wider ones only add padding
+            }
+        }
     }
     if (const char* e = getenv("NNB200_I8_BN")) {  // measurement aid
         const int v = atoi(e);
-        if (v == 256 || v == 224 || v == 192 || v == 128 || v == 64) {
+        if (v == 512 || v == 448 || v == 384 || v == 320 || v == 256 || v == 224 || v == 192 || v == 128 || v == 64) {
             bn = v;
         }
     }
@@ -638,7 +667,7 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
     if (!make_tma_2d(&map_a, p.a, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(m),
                      static_cast<uint64_t>(p.a_stride_m), kBlockKBytes, kBlockM) ||
         !make_tma_2d(&map_w, p.w, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
-                     static_cast<uint64_t>(p.w_stride_n), kBlockKBytes, static_cast<uint32_t>(bn))) {
+                     static_cast<uint64_t>(p.w_stride_n), kBlockKBytes, static_cast<uint32_t>(bn > 256 ? bn / 2 : bn))) {
         return NNB200_INTERNAL;
     }
 
@@ -653,6 +682,18 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
 
     const uint32_t a_fmt = p.a_unsigned ? 0u : 1u;
     switch (bn) {
+    case 512:
+        return launch_bn<512>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 256), vec_ok,
+                              dev, stream);
+    case 448:
+        return launch_bn<448>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 224), vec_ok,
+                              dev, stream);
+    case 384:
+        return launch_bn<384>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 192), vec_ok,
+                              dev, stream);
+    case 320:
+        return launch_bn<320>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 160), vec_ok,
+                              dev, stream);
     case 256:
         return launch_bn<256>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 256), vec_ok,
                               dev, stream);

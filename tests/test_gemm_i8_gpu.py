@@ -108,6 +108,17 @@ def test_decode_destinations(cuda_device, nnb200_lib, out_kind):
               out_scale=1.9, out_zp=0 if out_kind == "s32" else 4, expect_engine="decode", seed=21)
 
 
+@pytest.mark.parametrize("bn", [320, 384, 448, 512])
+def test_wide_single_wave_tiles(cuda_device, nnb200_lib, bn, monkeypatch):
+    """Tiles wider than 256 columns (two MMAs per k-step, one accumulator): forced through the
+    measurement override, once with one tile per CTA and once with several per CTA."""
+    monkeypatch.setenv("NNB200_I8_BN", str(bn))
+    _run_case(cuda_device, 300, 1500, 512, out_kind="s8", relu=True, per_token=True, per_channel=True,
+              zero_points=True, out_scale=1.9, out_zp=2, engine="umma", seed=bn)
+    _run_case(cuda_device, 1100, 4000 + bn, 256, out_kind="s32", per_channel=True, engine="umma", seed=bn + 1)
+    _run_case(cuda_device, 2048, 8192, 128, out_kind="f16", per_channel=True, engine="umma", seed=bn + 2)
+
+
 def test_transposed_poses_use_generic(cuda_device, nnb200_lib):
     rng = np.random.default_rng(5)
     m, n, k = 70, 90, 200
