@@ -33,6 +33,7 @@
 
 #include "internal.cuh"
 #include "ptx.cuh"
+#include "ptx_pair.cuh"
 
 namespace nnb200 {
 
@@ -529,6 +530,321 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+
+// ---- CTA-pair form ---------------------------------------------------------------------------
+// Two CTAs (a cluster of two, on neighbouring SMs) share one 256 x BN output tile: each loads its
+// own 128 rows of A and HALF of the tile's W rows, the pair leader issues tcgen05.mma with
+// cta_group::2 (M = 256 over both SMs' tensor cores and TMEM), and each CTA drains its own 128
+// accumulator rows through the same epilogue.  Per multiply-add the pair moves two thirds of the
+// operand bytes, and -- what pays -- its 32 KB stages give a six-deep ring where the single-CTA
+// form has room for four (a three-deep ring measured 7 % slower than four on the same problem).
+//
+// Signalling: TMA loads of both CTAs report their bytes to the LEADER's full barrier; the
+// leader's commits arrive on BOTH CTAs' empty / accumulator-full barriers (one plain commit per
+// destination); the epilogue warps of both CTAs arrive on the leader's accumulator-empty
+// barrier.  A cluster barrier brackets the kernel so neither CTA initialises late or exits early.
+template <int BN>
+struct PairTileConfig {
+    static constexpr int kATileBytes = kBlockM * kBlockKBytes;   // this CTA's 128 rows of A
+    static constexpr int kBTileBytes = (BN / 2) * kBlockKBytes;  // this CTA's half of the W rows
+    static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+    static constexpr int kColParamBytes = 4 * 4 * BN * 4;
+    static constexpr int kStages = (208 * 1024 - kColParamBytes) / kStageBytes;  // 256: 6, 224: 6, 192: 7
+    static constexpr int kTmemCols = 512;
+    static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kColParamBytes + kBarrierBytes;
+};
+
+template <int BN, int KIND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         const I8Epilogue ep, const int m_total, const int n_total, const int k_total,
+                         const uint32_t idesc, const int vec_ok, const int group_m, int32_t* error_word)
+{
+    using Cfg = PairTileConfig<BN>;
+    constexpr int kStages = Cfg::kStages;
+    constexpr int kPairM = 2 * kBlockM;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* stage_base = smem;
+    int32_t* col_params = reinterpret_cast<int32_t*>(smem + kStages * Cfg::kStageBytes);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(col_params + 4 * 4 * BN);
+    uint64_t* empty_bar = full_bar + kStages;
+    uint64_t* acc_full_bar = empty_bar + kStages;
+    uint64_t* acc_empty_bar = acc_full_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();  // 0 = pair leader
+    const int pair = static_cast<int>(blockIdx.x >> 1);
+    const int num_pairs = static_cast<int>(gridDim.x >> 1);
+    const int num_m = (m_total + kPairM - 1) / kPairM;
+    const int num_n = (n_total + BN - 1) / BN;
+    const int num_tiles = num_m * num_n;
+    const int num_kb = (k_total + kBlockKBytes - 1) / kBlockKBytes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 1);   // the leader's: its own expect-tx arrival; bytes come from both CTAs
+            mbar_init(&empty_bar[s], 1);  // one commit from the leader
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full_bar[a], 1);
+            mbar_init(&acc_empty_bar[a], 2 * kEpilogueThreads / 32);  // the leader's: 4 warps of each CTA
+        }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_w);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    cluster_sync_all();  // both CTAs' barriers and TMEM exist before anything is signalled across
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (each CTA loads its own halves) ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
+                const int m0 = tc.m_blk * kPairM + static_cast<int>(rank) * kBlockM;
+                const int n0 = tc.n_blk * BN + static_cast<int>(rank) * (BN / 2);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                        atomicCAS(error_word, 0, kErrProducerWait);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* a_dst = stage_base + stage * Cfg::kStageBytes;
+                    uint8_t* b_dst = a_dst + Cfg::kATileBytes;
+                    if (rank == 0) {
+                        mbar_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+                    }
+                    const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                    tma_load_2d_pair(a_dst, &map_a, leader_full, kb * kBlockKBytes, m0);
+                    tma_load_2d_pair(b_dst, &map_w, leader_full, kb * kBlockKBytes, n0);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (pair leader only) ----------------
+        if (lane == 0 && rank == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int local_tile = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
+                const int acc = local_tile & 1;
+                const uint32_t acc_phase = (local_tile >> 1) & 1u;
+                if (!mbar_wait_cluster(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag)) {
+                    atomicCAS(error_word, 0, kErrAccumWait);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 256);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_cluster(&full_bar[stage], phase, abort_flag)) {
+                        atomicCAS(error_word, 0, kErrMmaWait);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(stage_base + stage * Cfg::kStageBytes);
+                    const uint32_t b_addr = a_addr + Cfg::kATileBytes;
+                    const uint64_t a_desc = umma_desc_sw128_kmajor(a_addr);
+                    const uint64_t b_desc = umma_desc_sw128_kmajor(b_addr);
+#pragma unroll
+                    for (int ks = 0; ks < kBlockKBytes / kUmmaK; ++ks) {
+                        umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>(ks * 2),
+                                     b_desc + static_cast<uint64_t>(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    // The slot is free in BOTH CTAs once these MMAs have read it.
+                    const uint32_t e = smem_u32(&empty_bar[stage]);
+                    umma_commit_pair(map_to_cta(e, 0));
+                    umma_commit_pair(map_to_cta(e, 1));
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) {
+                    const uint32_t f = smem_u32(&acc_full_bar[acc]);
+                    umma_commit_pair(map_to_cta(f, 0));
+                    umma_commit_pair(map_to_cta(f, 1));
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue warps (each CTA drains its own 128 rows) ----------------
+        const int quarter = warp & 3;
+        float* cs = reinterpret_cast<float*>(col_params + (warp - 2) * 4 * BN);
+        int32_t* cb = reinterpret_cast<int32_t*>(cs) + BN;
+        int32_t* cr = cb + BN;
+        int32_t* cz = cr + BN;
+        int local_tile = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
+            const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
+            const int acc = local_tile & 1;
+            const uint32_t acc_phase = (local_tile >> 1) & 1u;
+            const int n_base = tc.n_blk * BN;
+
+            // Stage this tile's per-column terms (hidden behind the tile's main loop).
+            __syncwarp();
+            for (int j = lane; j < BN; j += 32) {
+                const int n = n_base + j;
+                const bool in = n < n_total;
+                cs[j] = (in && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
+                int32_t b = 0;
+                if (in && ep.bias != nullptr) {
+                    if constexpr (KIND <= NNB200_OUT_U8) {
+                        b = static_cast<const int32_t*>(ep.bias)[n];
+                    } else if constexpr (KIND == NNB200_OUT_F32) {
+                        b = __float_as_int(static_cast<const float*>(ep.bias)[n]);
+                    } else {
+                        b = __float_as_int(__half2float(static_cast<const __half*>(ep.bias)[n]));
+                    }
+                }
+                cb[j] = b;
+                cr[j] = (in && ep.compensate) ? ep.r_w[n] : 0;
+                cz[j] = (in && ep.zp_w != nullptr) ? ep.zp_w[n] : ep.zp_w_scalar;
+            }
+            __syncwarp();
+
+            const int64_t m = static_cast<int64_t>(tc.m_blk) * kPairM + static_cast<int64_t>(rank) * kBlockM +
+                              quarter * 32 + lane;
+            const bool row_ok = m < m_total;
+            I8RowTerms rt;
+            rt.zpa = 0;
+            rt.ra = 0;
+            rt.s_a = 1.0f;
+            rt.row_k = 1.0f;
+            if (row_ok) {
+                rt = i8_row_terms(ep, m);
+            }
+
+            int ok = 1;
+            if (lane == 0) {
+                ok = mbar_wait_cluster(&acc_full_bar[acc], acc_phase, abort_flag) ? 1 : 0;
+            }
+            ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+            if (!ok) {
+                atomicCAS(error_word, 0, kErrEpilogueWait);
+                break;
+            }
+            tc_fence_after_sync();
+
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(acc * 256);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int n0 = n_base + c * 32;
+                if (n0 >= n_total) {
+                    break;  // uniform across the CTA's epilogue warps
+                }
+                uint32_t v[32];
+                tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
+                tmem_ld_wait();
+                epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
+                                     cz + c * 32, vec_ok != 0);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[acc]), 0));
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before_sync();
+    cluster_sync_all();  // the peer has stopped signalling into / reading from this CTA
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// CTA-pair launch: 256 x BN tiles, two CTAs per tile.  NNB200_UNSUPPORTED when the device cannot
+// co-schedule a single pair (the caller then uses the single-CTA form).
+template <int BN, int KIND>
+int launch_pair_variant(const I8Problem& p, const I8Epilogue& ep, int m, int n, int k, uint32_t a_fmt, int vec_ok,
+                        const DeviceInfo& dev, cudaStream_t stream)
+{
+    using Cfg = PairTileConfig<BN>;
+    auto kernel = gemm_i8_umma_pair_kernel<BN, KIND>;
+    static std::once_flag once[kMaxDevices];
+    static cudaError_t attr_err[kMaxDevices];
+    static int max_pairs[kMaxDevices];
+    std::call_once(once[dev.device], [&] {
+        attr_err[dev.device] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        max_pairs[dev.device] = 0;
+        if (attr_err[dev.device] == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(static_cast<unsigned>(dev.sm_count & ~1));
+            cfg.blockDim = dim3(kNumThreads);
+            cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+            int count = 0;
+            if (cudaOccupancyMaxActiveClusters(&count, kernel, &cfg) == cudaSuccess) {
+                max_pairs[dev.device] = count;
+            }
+        }
+    });
+    if (attr_err[dev.device] != cudaSuccess) {
+        return NNB200_INTERNAL;
+    }
+    if (max_pairs[dev.device] < 1) {
+        return NNB200_UNSUPPORTED;
+    }
+    CUtensorMap map_a, map_w;
+    if (!make_tma_2d(&map_a, p.a, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(m),
+                     static_cast<uint64_t>(p.a_stride_m), kBlockKBytes, kBlockM) ||
+        !make_tma_2d(&map_w, p.w, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                     static_cast<uint64_t>(p.w_stride_n), kBlockKBytes, BN / 2)) {
+        return NNB200_INTERNAL;
+    }
+    const int num_tiles = ((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + BN - 1) / BN);
+    const int pairs = num_tiles < max_pairs[dev.device] ? num_tiles : max_pairs[dev.device];
+    int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(2 * kBlockM) * (k > 0 ? k : 1)));
+    group_m = group_m < 2 ? 2 : group_m;
+    kernel<<<2 * pairs, kNumThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, ep, m, n, k,
+                                                               umma_idesc(2, a_fmt, 1, 2 * kBlockM, BN), vec_ok, group_m,
+                                                               dev.error_word);
+    note_launch();
+    return cuda_status(cudaGetLastError());
+}
+
+template <int BN>
+int launch_pair_bn(const I8Problem& p, const I8Epilogue& ep, int m, int n, int k, uint32_t a_fmt, int vec_ok,
+                   const DeviceInfo& dev, cudaStream_t stream)
+{
+    switch (ep.out_kind) {
+    case NNB200_OUT_S32: return launch_pair_variant<BN, NNB200_OUT_S32>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_S8: return launch_pair_variant<BN, NNB200_OUT_S8>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_U8: return launch_pair_variant<BN, NNB200_OUT_U8>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_F32: return launch_pair_variant<BN, NNB200_OUT_F32>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_F16: return launch_pair_variant<BN, NNB200_OUT_F16>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    default: return NNB200_UNSUPPORTED;
+    }
+}
+
 template <int BN, int KIND, bool PEERS>
 int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m, int n, int k,
                    uint32_t idesc, int vec_ok, const DeviceInfo& dev, cudaStream_t stream)
@@ -681,6 +997,20 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
                            : 0;
 
     const uint32_t a_fmt = p.a_unsigned ? 0u : 1u;
+
+    // CTA-pair form for tall problems with at least a full wave of 256-row tiles.
+    // NNB200_I8_PAIR=0 turns it off, =2 makes a device that cannot co-schedule pairs an error.
+    {
+        const char* pe = getenv("NNB200_I8_PAIR");
+        const char pair_mode = pe != nullptr ? pe[0] : '0';
+        const int64_t pair_tiles = static_cast<int64_t>((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + 255) / 256);
+        if (pair_mode != '0' && ep.num_peers == 0 && m >= 4 * kBlockM && pair_tiles >= dev.sm_count / 2 && bn == 256) {
+            const int st = launch_pair_bn<256>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+            if (st != NNB200_UNSUPPORTED || pair_mode == '2') {
+                return st;
+            }
+        }
+    }
     switch (bn) {
     case 512:
         return launch_bn<512>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 256), vec_ok,

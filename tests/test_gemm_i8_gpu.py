@@ -119,6 +119,17 @@ def test_wide_single_wave_tiles(cuda_device, nnb200_lib, bn, monkeypatch):
     _run_case(cuda_device, 2048, 8192, 128, out_kind="f16", per_channel=True, engine="umma", seed=bn + 2)
 
 
+@pytest.mark.parametrize("case", [(1100, 9000, 512, "s8"), (2048, 9472, 256, "s32"), (777, 19000, 384, "f16"),
+                                  (4096, 4736, 640, "u8"), (600, 20000, 96, "f32")])
+def test_cta_pair_form(cuda_device, nnb200_lib, case, monkeypatch):
+    """256-row tiles over clusters of two CTAs (tcgen05.mma cta_group::2): forced ("2" = the pair
+    form or an error), ragged M / N / K, every destination."""
+    m, n, k, kind = case
+    monkeypatch.setenv("NNB200_I8_PAIR", "2")
+    _run_case(cuda_device, m, n, k, out_kind=kind, relu=True, per_token=True, per_channel=True, zero_points=True,
+              out_scale=0.9, out_zp=0 if kind == "s32" else 3, engine="umma", seed=m + n)
+
+
 def test_transposed_poses_use_generic(cuda_device, nnb200_lib):
     rng = np.random.default_rng(5)
     m, n, k = 70, 90, 200
