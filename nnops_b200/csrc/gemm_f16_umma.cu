@@ -154,7 +154,13 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_row, int64_t m, boo
             }
             if (row_ok) {
                 uint16_t* dst = static_cast<uint16_t*>(out) + m * ldc + n0;
-                if (full && vec_ok) {
+                if (full && (vec_ok & 2)) {
+                    // 64 bytes per lane: two whole 32-byte sectors, one 256-bit store each.
+                    st_global_32(dst, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6],
+                                 packed[7]);
+                    st_global_32(dst + 16, packed[8], packed[9], packed[10], packed[11], packed[12], packed[13],
+                                 packed[14], packed[15]);
+                } else if (full && (vec_ok & 1)) {
 #pragma unroll
                     for (int j = 0; j < 16; j += 4) {
                         *reinterpret_cast<uint4*>(dst + 2 * j) =
@@ -178,7 +184,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_row, int64_t m, boo
             }
             if (row_ok) {
                 float* dst = static_cast<float*>(out) + m * ldc + n0;
-                if (full && vec_ok) {
+                if (full && (vec_ok & 1)) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         *reinterpret_cast<float4*>(dst + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
@@ -609,10 +615,10 @@ int launch_f16_variant(const nnb200_q4_1_args& q, const __half* w_f16, int64_t l
     const int num_tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BN - 1) / BN);
     const int grid = num_tiles < dev.sm_count ? num_tiles : dev.sm_count;
     const int elem = OUT_F16 ? 2 : 4;
-    const int vec_ok = ((reinterpret_cast<uintptr_t>(q.out) & 15u) == 0 &&
-                        ((static_cast<uint64_t>(q.ldc) * elem) & 15u) == 0)
-                           ? 1
-                           : 0;
+    // Destination vector stores: bit 0 = 16-byte aligned base and row pitch, bit 1 = 32-byte.
+    const uint64_t out_pitch = static_cast<uint64_t>(q.ldc) * elem;
+    const int vec_ok = (((reinterpret_cast<uintptr_t>(q.out) & 15u) == 0 && (out_pitch & 15u) == 0) ? 1 : 0) |
+                       (((reinterpret_cast<uintptr_t>(q.out) & 31u) == 0 && (out_pitch & 31u) == 0) ? 2 : 0);
     // Raster group: m-blocks whose band of A (128 x K halves each) stays within ~40 MB of L2.
     int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(kBlockM) * 2 * (k > 0 ? k : 1)));
     group_m = group_m < 4 ? 4 : group_m;
@@ -667,10 +673,10 @@ int launch_f16_pair_variant(const nnb200_q4_1_args& q, const __half* w_f16, int6
     const int num_tiles = ((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + BN - 1) / BN);
     const int pairs = num_tiles < max_pairs[dev.device] ? num_tiles : max_pairs[dev.device];
     const int elem = OUT_F16 ? 2 : 4;
-    const int vec_ok = ((reinterpret_cast<uintptr_t>(q.out) & 15u) == 0 &&
-                        ((static_cast<uint64_t>(q.ldc) * elem) & 15u) == 0)
-                           ? 1
-                           : 0;
+    // Destination vector stores: bit 0 = 16-byte aligned base and row pitch, bit 1 = 32-byte.
+    const uint64_t out_pitch = static_cast<uint64_t>(q.ldc) * elem;
+    const int vec_ok = (((reinterpret_cast<uintptr_t>(q.out) & 15u) == 0 && (out_pitch & 15u) == 0) ? 1 : 0) |
+                       (((reinterpret_cast<uintptr_t>(q.out) & 31u) == 0 && (out_pitch & 31u) == 0) ? 2 : 0);
     int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(2 * kBlockM) * 2 * (k > 0 ? k : 1)));
     group_m = group_m < 2 ? 2 : group_m;
     kernel<<<2 * pairs, kNumThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, q.out, q.ldc, m, n, k, ep,

@@ -100,8 +100,11 @@ template <int KIND>
 __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowTerms& t, const uint32_t (&acc)[32],
                                                int64_t m, bool row_ok, int n0, int n_total,
                                                const float* col_scale, const int32_t* col_bias,
-                                               const int32_t* col_rw, const int32_t* col_zpw, bool vec_ok)
+                                               const int32_t* col_rw, const int32_t* col_zpw, int vec)
 {
+    // vec: bit 0 = the destination takes 16-byte stores, bit 1 = 32-byte stores as well.
+    const bool vec_ok = (vec & 1) != 0;
+    const bool vec32 = (vec & 2) != 0;
     const bool full = n0 + 32 <= n_total;
     const float zpf = static_cast<float>(e.out_zp);
 
@@ -148,7 +151,10 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
             return;
         }
         uint8_t* dst = static_cast<uint8_t*>(e.out) + m * e.ldc + n0;
-        if (full && vec_ok) {
+        if (full && vec32) {
+            // The lane's 32 values are exactly one 32-byte sector of its row.
+            st_global_32(dst, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
+        } else if (full && vec_ok) {
             *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
         } else {
@@ -198,7 +204,11 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
             return;
         }
         uint16_t* dst = static_cast<uint16_t*>(e.out) + m * e.ldc + n0;
-        if (full && vec_ok) {
+        if (full && vec32) {
+            st_global_32(dst, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
+            st_global_32(dst + 16, packed[8], packed[9], packed[10], packed[11], packed[12], packed[13], packed[14],
+                         packed[15]);
+        } else if (full && vec_ok) {
 #pragma unroll
             for (int j = 0; j < 16; j += 4) {
                 *reinterpret_cast<uint4*>(dst + 2 * j) =
@@ -503,7 +513,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                     tmem_ld_wait();
                     epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
-                                         cz + c * 32, vec_ok != 0);
+                                         cz + c * 32, vec_ok);
                 }
             }
             // Accumulator drained: hand it back to the MMA warp.
@@ -763,7 +773,7 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                 tmem_ld_wait();
                 epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
-                                     cz + c * 32, vec_ok != 0);
+                                     cz + c * 32, vec_ok);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -991,10 +1001,10 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
     const int elem = (ep.out_kind == NNB200_OUT_S32 || ep.out_kind == NNB200_OUT_F32) ? 4
                      : (ep.out_kind == NNB200_OUT_F16)                                ? 2
                                                                                       : 1;
-    const int vec_ok = ((reinterpret_cast<uintptr_t>(ep.out) & 15u) == 0 &&
-                        ((static_cast<uint64_t>(ep.ldc) * static_cast<uint64_t>(elem)) & 15u) == 0)
-                           ? 1
-                           : 0;
+    // Destination vector stores: bit 0 = 16-byte aligned base and row pitch, bit 1 = 32-byte.
+    const uint64_t pitch_bytes = static_cast<uint64_t>(ep.ldc) * static_cast<uint64_t>(elem);
+    const int vec_ok = (((reinterpret_cast<uintptr_t>(ep.out) & 15u) == 0 && (pitch_bytes & 15u) == 0) ? 1 : 0) |
+                       (((reinterpret_cast<uintptr_t>(ep.out) & 31u) == 0 && (pitch_bytes & 31u) == 0) ? 2 : 0);
 
     const uint32_t a_fmt = p.a_unsigned ? 0u : 1u;
 

@@ -308,6 +308,15 @@ __device__ __forceinline__ void tmem_ld_wait()
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// One 256-bit store (sm_100): a full 32-byte sector per lane.  `p` must be 32-byte aligned.
+__device__ __forceinline__ void st_global_32(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e,
+                                             uint32_t f, uint32_t g, uint32_t h)
+{
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d),
+                 "r"(e), "r"(f), "r"(g), "r"(h)
+                 : "memory");
+}
+
 // Named barrier over a subset of the CTA's warps.
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads)
 {
