@@ -100,7 +100,8 @@ template <int KIND>
 __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowTerms& t, const uint32_t (&acc)[32],
                                                int64_t m, bool row_ok, int n0, int n_total,
                                                const float* col_scale, const int32_t* col_bias,
-                                               const int32_t* col_rw, const int32_t* col_zpw, int vec)
+                                               const int32_t* col_rw, const int32_t* col_zpw, int vec,
+                                               bool scale_folded = false)
 {
     // vec: bit 0 = the destination takes 16-byte stores, bit 1 = 32-byte stores as well.
     const bool vec_ok = (vec & 1) != 0;
@@ -135,17 +136,39 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
         const float lo = (KIND == NNB200_OUT_S8 ? -128.0f : 0.0f) - zpf;
         const float hi = (KIND == NNB200_OUT_S8 ? 127.0f : 255.0f) - zpf;
         uint32_t packed[8];
+        if (!e.compensate) {
+            // Common case (every zero point 0): no compensation terms to fetch; with a per-tensor
+            // activation scale the staged column scales already carry (s_a / s_out) * s_w[n].
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-            uint32_t word = 0;
+            for (int j = 0; j < 32; j += 4) {
+                uint32_t word = 0;
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const int32_t v = i8_int_value(e, t, static_cast<int32_t>(acc[j + b]), col_zpw[j + b],
-                                               col_rw[j + b], col_bias[j + b]);
-                const int32_t q = i8_requant(v, __fmul_rn(t.row_k, col_scale[j + b]), lo, hi, e.out_zp);
-                word |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * b);
+                for (int b = 0; b < 4; ++b) {
+                    int32_t v = static_cast<int32_t>(static_cast<uint32_t>(acc[j + b]) +
+                                                     static_cast<uint32_t>(col_bias[j + b]));
+                    if (e.relu && v < 0) {
+                        v = 0;
+                    }
+                    const float req = scale_folded ? col_scale[j + b] : __fmul_rn(t.row_k, col_scale[j + b]);
+                    const int32_t q = i8_requant(v, req, lo, hi, e.out_zp);
+                    word |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * b);
+                }
+                packed[j / 4] = word;
             }
-            packed[j / 4] = word;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int32_t v = i8_int_value(e, t, static_cast<int32_t>(acc[j + b]), col_zpw[j + b],
+                                                   col_rw[j + b], col_bias[j + b]);
+                    const float req = scale_folded ? col_scale[j + b] : __fmul_rn(t.row_k, col_scale[j + b]);
+                    const int32_t q = i8_requant(v, req, lo, hi, e.out_zp);
+                    word |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * b);
+                }
+                packed[j / 4] = word;
+            }
         }
         if (!row_ok) {
             return;
@@ -389,6 +412,11 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ---------------- epilogue warps ----------------
         const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+        // 8-bit destinations with a per-tensor activation scale: the row factor s_a / s_out is the
+        // same for every row, so it is folded into the staged column scales (same two roundings,
+        // once per column instead of once per element).  The sharded form keeps the plain scales.
+        const bool fold_scale = !PEERS && (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) && ep.scale_a == nullptr;
+        const float folded_row_k = __fdiv_rn(ep.scale_a_scalar, ep.out_scale);
         float* cs = reinterpret_cast<float*>(col_params + (warp - 2) * 4 * BN);
         int32_t* cb = reinterpret_cast<int32_t*>(cs) + BN;
         int32_t* cr = cb + BN;
@@ -407,7 +435,8 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int j = lane; j < BN; j += 32) {
                 const int n = n_base + j;
                 const bool in = n < n_total;
-                cs[j] = (in && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
+                const float s_w = (in && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
+                cs[j] = fold_scale ? __fmul_rn(folded_row_k, s_w) : s_w;
                 int32_t b = 0;
                 if (in && ep.bias != nullptr) {
                     if constexpr (KIND <= NNB200_OUT_U8) {
@@ -513,7 +542,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                     tmem_ld_wait();
                     epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
-                                         cz + c * 32, vec_ok);
+                                         cz + c * 32, vec_ok, fold_scale);
                 }
             }
             // Accumulator drained: hand it back to the MMA warp.
@@ -705,6 +734,8 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     } else {
         // ---------------- epilogue warps (each CTA drains its own 128 rows) ----------------
         const int quarter = warp & 3;
+        const bool fold_scale = (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) && ep.scale_a == nullptr;
+        const float folded_row_k = __fdiv_rn(ep.scale_a_scalar, ep.out_scale);
         float* cs = reinterpret_cast<float*>(col_params + (warp - 2) * 4 * BN);
         int32_t* cb = reinterpret_cast<int32_t*>(cs) + BN;
         int32_t* cr = cb + BN;
@@ -721,7 +752,8 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             for (int j = lane; j < BN; j += 32) {
                 const int n = n_base + j;
                 const bool in = n < n_total;
-                cs[j] = (in && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
+                const float s_w = (in && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
+                cs[j] = fold_scale ? __fmul_rn(folded_row_k, s_w) : s_w;
                 int32_t b = 0;
                 if (in && ep.bias != nullptr) {
                     if constexpr (KIND <= NNB200_OUT_U8) {
@@ -773,7 +805,7 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                 tmem_ld_wait();
                 epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
-                                     cz + c * 32, vec_ok);
+                                     cz + c * 32, vec_ok, fold_scale);
             }
             tc_fence_before_sync();
             __syncwarp();
