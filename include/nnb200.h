@@ -198,10 +198,11 @@ typedef struct nnb200_q4_1_args {
  * the preceding kernel does not write w_blocks.  Honoured by the GEMV engine. */
 #define NNB200_Q4_FLAG_OVERLAP_PREVIOUS 1
 
-/* Optional device scratch (16-byte aligned).  Non-zero for tall f16 problems (m >= 256): given
- * that many bytes, the call expands the weights to f16 once into the scratch and runs a dense
- * tensor-core GEMM over them, which is faster than decoding inside the GEMM; without it (NULL or
- * too small) the same call runs the fused kernel.  The scratch is dead when the call's work has
+/* Optional device scratch (16-byte aligned).  Non-zero for tall problems (f16 activations: m >= 256;
+ * f32 activations: m >= 17): given that many bytes, the call expands the weights to f16 once into
+ * the scratch (and splits f32 activations into [hi | lo] f16 halves there) and runs a dense
+ * tensor-core GEMM over them; without it (NULL or too small) the same call runs the fused kernel
+ * (f16) or the GEMV engine tile by tile (f32).  The scratch is dead when the call's work has
  * completed on the stream. */
 NNB200_API size_t nnb200_q4_1_workspace_bytes(const nnb200_q4_1_args* args);
 NNB200_API int nnb200_linear_q4_1(const nnb200_q4_1_args* args, void* stream);

@@ -319,6 +319,14 @@ static bool valid_q4_args(const nnb200_q4_1_args* q)
 // decoding them inside the GEMM (measured on config 4's weights: equal at 128 rows, 64 us
 // against 100 us at 256).
 static constexpr int64_t kTwoPassMinRows = 256;
+// f32 activations have no fused tensor-core form (their only other route walks the weights once
+// per 8 rows): the two-pass form, with the activations split into [hi | lo] f16, serves them from here up.
+static constexpr int64_t kTwoPassMinRowsF32 = 17;
+
+static int64_t two_pass_min_rows(const nnb200_q4_1_args* q)
+{
+    return q->a_f16 != 0 ? kTwoPassMinRows : kTwoPassMinRowsF32;
+}
 
 size_t nnb200_q4_1_workspace_bytes(const nnb200_q4_1_args* q)
 {
@@ -326,8 +334,8 @@ size_t nnb200_q4_1_workspace_bytes(const nnb200_q4_1_args* q)
         return 0;
     }
     // Optional: without it a tall call runs the fused kernel.
-    const bool wanted = q->force_engine == 5 || (q->force_engine == 0 && q->m >= kTwoPassMinRows);
-    return (wanted && q->a_f16 != 0) ? q4_1_two_pass_scratch_bytes(*q) : 0;
+    const bool wanted = q->force_engine == 5 || (q->force_engine == 0 && q->m >= two_pass_min_rows(q));
+    return wanted ? q4_1_two_pass_scratch_bytes(*q) : 0;
 }
 
 int nnb200_q4_1_engine(const nnb200_q4_1_args* q)
@@ -349,7 +357,7 @@ int nnb200_q4_1_engine(const nnb200_q4_1_args* q)
     if (q->force_engine == 1) {
         return gemm_ok ? 1 : gemv;
     }
-    if (q->m >= kTwoPassMinRows && two_pass_ok) {
+    if (q->m >= two_pass_min_rows(q) && two_pass_ok) {
         return 5;
     }
     return (q->m > 8 && gemm_ok) ? 1 : gemv;

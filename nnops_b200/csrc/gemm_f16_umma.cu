@@ -123,6 +123,31 @@ __global__ void __launch_bounds__(256) q4_1_expand_f16_kernel(const uint8_t* __r
     }
 }
 
+// ---- pass 1b: f32 activations -> [hi | lo] f16 ------------------------------------------------
+// a = hi + lo with hi = f16(a), lo = f16(a - hi): the pair carries 22 mantissa bits, so the dense
+// GEMM over [hi | lo] (weights repeating along K) reproduces an f32-activation product to f32
+// accuracy.  Row m of `out` is [hi(0..kp) | lo(0..kp)], kp = K rounded up to 64, zeros past K.
+// Values beyond the f16 range (|a| > 65504) become infinities, as in any f16 activation pipeline.
+__global__ void __launch_bounds__(256) split_f32_to_f16_kernel(const float* __restrict__ a, const int64_t lda,
+                                                               const int m, const int k, const int kp,
+                                                               __half* __restrict__ out)
+{
+    const int64_t total = static_cast<int64_t>(m) * kp;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t r = i / kp;
+        const int c = static_cast<int>(i - r * kp);
+        float v = 0.0f;
+        if (c < k) {
+            v = a[r * lda + c];
+        }
+        const __half hi = __float2half_rn(v);
+        const __half lo = __float2half_rn(v - __half2float(hi));
+        out[r * 2 * kp + c] = hi;
+        out[r * 2 * kp + kp + c] = lo;
+    }
+}
+
 // ---- pass 2: dense f16 GEMM ------------------------------------------------------------------
 // Drain one accumulator (this warp's 32 rows x BN columns) through the fp epilogue into `out`.
 template <int BN, bool OUT_F16>
@@ -206,8 +231,8 @@ template <int BN, bool OUT_F16>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_f16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      void* __restrict__ out, const int64_t ldc, const int m_total, const int n_total,
-                     const int k_total, const FpEpilogue ep, const uint32_t idesc, const int vec_ok,
-                     const int group_m, int32_t* error_word)
+                     const int k_total, const int w_wrap_k, const FpEpilogue ep, const uint32_t idesc,
+                     const int vec_ok, const int group_m, int32_t* error_word)
 {
     using Cfg = F16Config<BN>;
     constexpr int kStages = Cfg::kStages;
@@ -274,8 +299,10 @@ gemm_f16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     uint8_t* b_dst = a_dst + Cfg::kATileBytes;
                     mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
                     // x coordinates are in elements: kb * 64 halves = a multiple of 128 bytes.
+                    // With split activations ([hi | lo] along K) the weights repeat every w_wrap_k.
+                    const int wk = w_wrap_k > 0 ? (kb * kBlockK) % w_wrap_k : kb * kBlockK;
                     tma_load_2d(a_dst, &map_a, &full_bar[stage], kb * kBlockK, tc.m_blk * kBlockM);
-                    tma_load_2d(b_dst, &map_w, &full_bar[stage], kb * kBlockK, tc.n_blk * BN);
+                    tma_load_2d(b_dst, &map_w, &full_bar[stage], wk, tc.n_blk * BN);
                     armed |= 1u << stage;
                     armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
                     if (++stage == kStages) {
@@ -414,8 +441,8 @@ template <int BN, bool OUT_F16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_f16_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                           void* __restrict__ out, const int64_t ldc, const int m_total, const int n_total,
-                          const int k_total, const FpEpilogue ep, const uint32_t idesc, const int vec_ok,
-                          const int group_m, int32_t* error_word)
+                          const int k_total, const int w_wrap_k, const FpEpilogue ep, const uint32_t idesc,
+                          const int vec_ok, const int group_m, int32_t* error_word)
 {
     using Cfg = PairConfig<BN>;
     constexpr int kStages = Cfg::kStages;
@@ -488,8 +515,9 @@ gemm_f16_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                         mbar_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
                     }
                     const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                    const int wk = w_wrap_k > 0 ? (kb * kBlockK) % w_wrap_k : kb * kBlockK;
                     tma_load_2d_pair(a_dst, &map_a, leader_full, kb * kBlockK, m0);
-                    tma_load_2d_pair(b_dst, &map_w, leader_full, kb * kBlockK, n0);
+                    tma_load_2d_pair(b_dst, &map_w, leader_full, wk, n0);
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -590,8 +618,20 @@ gemm_f16_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     }
 }
 
+// The dense GEMM's operands: A as f16 [m][k_loop] (the caller's activations, or their [hi | lo]
+// split) and the expanded weights [n][k_w]; w_wrap_k > 0 makes the weights' k index wrap.
+struct F16Operands {
+    const __half* a;
+    int64_t lda;
+    int k_loop;
+    const __half* w;
+    int64_t ldw;
+    int k_w;
+    int w_wrap_k;
+};
+
 template <int BN, bool OUT_F16>
-int launch_f16_variant(const nnb200_q4_1_args& q, const __half* w_f16, int64_t ldw, const FpEpilogue& ep,
+int launch_f16_variant(const nnb200_q4_1_args& q, const F16Operands& op, const FpEpilogue& ep,
                        const DeviceInfo& dev, cudaStream_t stream)
 {
     using Cfg = F16Config<BN>;
@@ -604,12 +644,12 @@ int launch_f16_variant(const nnb200_q4_1_args& q, const __half* w_f16, int64_t l
     if (attr_err[dev.device] != cudaSuccess) {
         return NNB200_INTERNAL;
     }
-    const int m = static_cast<int>(q.m), n = static_cast<int>(q.n), k = static_cast<int>(q.k);
+    const int m = static_cast<int>(q.m), n = static_cast<int>(q.n), k = op.k_loop;
     CUtensorMap map_a, map_w;
-    if (!make_tma_2d(&map_a, q.a, 2, static_cast<uint64_t>(k), static_cast<uint64_t>(m),
-                     static_cast<uint64_t>(q.lda) * 2, kBlockK, kBlockM) ||
-        !make_tma_2d(&map_w, w_f16, 2, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
-                     static_cast<uint64_t>(ldw) * 2, kBlockK, BN)) {
+    if (!make_tma_2d(&map_a, op.a, 2, static_cast<uint64_t>(op.k_loop), static_cast<uint64_t>(m),
+                     static_cast<uint64_t>(op.lda) * 2, kBlockK, kBlockM) ||
+        !make_tma_2d(&map_w, op.w, 2, static_cast<uint64_t>(op.k_w), static_cast<uint64_t>(n),
+                     static_cast<uint64_t>(op.ldw) * 2, kBlockK, BN)) {
         return NNB200_INTERNAL;
     }
     const int num_tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BN - 1) / BN);
@@ -622,7 +662,7 @@ int launch_f16_variant(const nnb200_q4_1_args& q, const __half* w_f16, int64_t l
     // Raster group: m-blocks whose band of A (128 x K halves each) stays within ~40 MB of L2.
     int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(kBlockM) * 2 * (k > 0 ? k : 1)));
     group_m = group_m < 4 ? 4 : group_m;
-    kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, q.out, q.ldc, m, n, k, ep,
+    kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, q.out, q.ldc, m, n, k, op.w_wrap_k, ep,
                                                            umma_idesc(1, 0, 0, kBlockM, BN), vec_ok, group_m,
                                                            dev.error_word);
     note_launch();
@@ -633,7 +673,7 @@ int launch_f16_variant(const nnb200_q4_1_args& q, const __half* w_f16, int64_t l
 // CTA-pair launch: 256 x BN tiles, two CTAs per tile.  Returns NNB200_UNSUPPORTED when the device
 // cannot co-schedule a single pair (the caller then uses the single-CTA form).
 template <int BN, bool OUT_F16>
-int launch_f16_pair_variant(const nnb200_q4_1_args& q, const __half* w_f16, int64_t ldw, const FpEpilogue& ep,
+int launch_f16_pair_variant(const nnb200_q4_1_args& q, const F16Operands& op, const FpEpilogue& ep,
                             const DeviceInfo& dev, cudaStream_t stream)
 {
     using Cfg = PairConfig<BN>;
@@ -662,12 +702,12 @@ int launch_f16_pair_variant(const nnb200_q4_1_args& q, const __half* w_f16, int6
     if (max_pairs[dev.device] < 1) {
         return NNB200_UNSUPPORTED;
     }
-    const int m = static_cast<int>(q.m), n = static_cast<int>(q.n), k = static_cast<int>(q.k);
+    const int m = static_cast<int>(q.m), n = static_cast<int>(q.n), k = op.k_loop;
     CUtensorMap map_a, map_w;
-    if (!make_tma_2d(&map_a, q.a, 2, static_cast<uint64_t>(k), static_cast<uint64_t>(m),
-                     static_cast<uint64_t>(q.lda) * 2, kBlockK, kBlockM) ||
-        !make_tma_2d(&map_w, w_f16, 2, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
-                     static_cast<uint64_t>(ldw) * 2, kBlockK, BN / 2)) {
+    if (!make_tma_2d(&map_a, op.a, 2, static_cast<uint64_t>(op.k_loop), static_cast<uint64_t>(m),
+                     static_cast<uint64_t>(op.lda) * 2, kBlockK, kBlockM) ||
+        !make_tma_2d(&map_w, op.w, 2, static_cast<uint64_t>(op.k_w), static_cast<uint64_t>(n),
+                     static_cast<uint64_t>(op.ldw) * 2, kBlockK, BN / 2)) {
         return NNB200_INTERNAL;
     }
     const int num_tiles = ((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + BN - 1) / BN);
@@ -679,7 +719,7 @@ int launch_f16_pair_variant(const nnb200_q4_1_args& q, const __half* w_f16, int6
                        (((reinterpret_cast<uintptr_t>(q.out) & 31u) == 0 && (out_pitch & 31u) == 0) ? 2 : 0);
     int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(2 * kBlockM) * 2 * (k > 0 ? k : 1)));
     group_m = group_m < 2 ? 2 : group_m;
-    kernel<<<2 * pairs, kNumThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, q.out, q.ldc, m, n, k, ep,
+    kernel<<<2 * pairs, kNumThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, q.out, q.ldc, m, n, k, op.w_wrap_k, ep,
                                                                umma_idesc(1, 0, 0, 2 * kBlockM, BN), vec_ok, group_m,
                                                                dev.error_word);
     note_launch();
@@ -709,21 +749,34 @@ int pick_bn(int m, int n, int sm_count)
 
 }  // namespace
 
-// Scratch the two-pass form needs: N rows of ceil(K/32)*32 halves.
-size_t q4_1_two_pass_scratch_bytes(const nnb200_q4_1_args& q)
+// Scratch the two-pass form needs: N rows of ceil(K/32)*32 halves for the expanded weights and, for
+// f32 activations, M rows of 2 * kp halves (kp = K rounded up to 64) for their [hi | lo] split.
+static size_t weights_scratch_bytes(const nnb200_q4_1_args& q)
 {
     const int64_t nblk = (q.k + kQ4BlockElems - 1) / kQ4BlockElems;
-    return static_cast<size_t>(q.n) * static_cast<size_t>(nblk) * kQ4BlockElems * sizeof(__half);
+    const size_t bytes = static_cast<size_t>(q.n) * static_cast<size_t>(nblk) * kQ4BlockElems * sizeof(__half);
+    return (bytes + 255) & ~size_t(255);
 }
 
-// f16 activations movable by TMA, whole problem in 32-bit tile arithmetic, 4-byte aligned blocks,
-// scratch 16-byte aligned (its pitch is a multiple of 64 bytes by construction).
+size_t q4_1_two_pass_scratch_bytes(const nnb200_q4_1_args& q)
+{
+    size_t bytes = weights_scratch_bytes(q);
+    if (q.a_f16 == 0) {
+        const int64_t kp = (q.k + 63) / 64 * 64;
+        bytes += static_cast<size_t>(q.m) * static_cast<size_t>(2 * kp) * sizeof(__half);
+    }
+    return bytes;
+}
+
+// Activations movable by TMA (f16: 16-byte aligned base and pitch; f32 ones are re-laid into the
+// scratch), whole problem in 32-bit tile arithmetic, 4-byte aligned blocks, scratch 16-byte aligned.
 bool q4_1_two_pass_supported(const nnb200_q4_1_args& q)
 {
-    return q.a_f16 != 0 && q.m >= 1 && q.n >= 1 && q.k >= 1 && q.m <= INT32_MAX && q.n <= INT32_MAX &&
-           q.k <= INT32_MAX - 64 && (reinterpret_cast<uintptr_t>(q.a) & 15u) == 0 && ((q.lda * 2) & 15) == 0 &&
-           q.lda >= q.k && (reinterpret_cast<uintptr_t>(q.w_blocks) & 3u) == 0 && q.workspace != nullptr &&
-           (reinterpret_cast<uintptr_t>(q.workspace) & 15u) == 0 &&
+    const bool a_ok = q.a_f16 != 0 ? ((reinterpret_cast<uintptr_t>(q.a) & 15u) == 0 && ((q.lda * 2) & 15) == 0)
+                                   : (reinterpret_cast<uintptr_t>(q.a) & 3u) == 0;
+    return a_ok && q.m >= 1 && q.n >= 1 && q.k >= 1 && q.m <= INT32_MAX && q.n <= INT32_MAX &&
+           q.k <= (INT32_MAX - 128) / 2 && q.lda >= q.k && (reinterpret_cast<uintptr_t>(q.w_blocks) & 3u) == 0 &&
+           q.workspace != nullptr && (reinterpret_cast<uintptr_t>(q.workspace) & 15u) == 0 &&
            q.workspace_bytes >= q4_1_two_pass_scratch_bytes(q);
 }
 
@@ -753,6 +806,32 @@ int launch_q4_1_two_pass(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
             return NNB200_INTERNAL;
         }
     }
+    F16Operands op;
+    op.w = w_f16;
+    op.ldw = ldw;
+    op.k_w = static_cast<int>(q.k);
+    if (q.a_f16 != 0) {
+        op.a = static_cast<const __half*>(q.a);
+        op.lda = q.lda;
+        op.k_loop = static_cast<int>(q.k);
+        op.w_wrap_k = 0;
+    } else {
+        const int kp = static_cast<int>((q.k + 63) / 64 * 64);
+        __half* a16 = reinterpret_cast<__half*>(static_cast<uint8_t*>(q.workspace) + weights_scratch_bytes(q));
+        const int64_t total = q.m * kp;
+        const int64_t want = (total + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(dev.sm_count) * 16;
+        split_f32_to_f16_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, stream>>>(
+            static_cast<const float*>(q.a), q.lda, static_cast<int>(q.m), static_cast<int>(q.k), kp, a16);
+        note_launch();
+        if (cudaGetLastError() != cudaSuccess) {
+            return NNB200_INTERNAL;
+        }
+        op.a = a16;
+        op.lda = 2 * static_cast<int64_t>(kp);
+        op.k_loop = 2 * kp;
+        op.w_wrap_k = kp;
+    }
     // CTA-pair form (256-row tiles over two SMs) for tall problems; measured 1.2 % faster than the
     // single-CTA form on M=2048, N=14336, K=4096 (208.5 us against 211 us for the whole call).
     // NNB200_F16_PAIR=0 turns it off, =2 makes a device that cannot co-schedule pairs an error.
@@ -763,8 +842,8 @@ int launch_q4_1_two_pass(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
         const int bn2 = pick_bn((static_cast<int>(q.m) + 1) / 2, static_cast<int>(q.n), dev.sm_count / 2);
         int st = NNB200_UNSUPPORTED;
 #define NNB200_F16_PAIR_LAUNCH(BNV) \
-    (q.out_f16 ? launch_f16_pair_variant<BNV, true>(q, w_f16, ldw, ep, dev, stream) \
-               : launch_f16_pair_variant<BNV, false>(q, w_f16, ldw, ep, dev, stream))
+    (q.out_f16 ? launch_f16_pair_variant<BNV, true>(q, op, ep, dev, stream) \
+               : launch_f16_pair_variant<BNV, false>(q, op, ep, dev, stream))
         if (bn2 >= 256) {
             st = NNB200_F16_PAIR_LAUNCH(256);
         } else if (bn2 >= 224) {
@@ -779,8 +858,8 @@ int launch_q4_1_two_pass(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
     }
     const int bn = pick_bn(static_cast<int>(q.m), static_cast<int>(q.n), dev.sm_count);
 #define NNB200_F16_LAUNCH(BNV) \
-    (q.out_f16 ? launch_f16_variant<BNV, true>(q, w_f16, ldw, ep, dev, stream) \
-               : launch_f16_variant<BNV, false>(q, w_f16, ldw, ep, dev, stream))
+    (q.out_f16 ? launch_f16_variant<BNV, true>(q, op, ep, dev, stream) \
+               : launch_f16_variant<BNV, false>(q, op, ep, dev, stream))
     switch (bn) {
     case 256: return NNB200_F16_LAUNCH(256);
     case 224: return NNB200_F16_LAUNCH(224);

@@ -130,6 +130,27 @@ def test_gemm_two_pass_shapes(cuda_device, nnb200_lib, shape, out_dtype):
     _close(got.cpu().numpy(), want, RTOL_F16 if out_dtype == "f16" else RTOL_F32)
 
 
+@pytest.mark.parametrize("shape", [(96, 160, 512), (130, 300, 1000), (600, 1100, 320), (2048, 1024, 96)])
+@pytest.mark.parametrize("out_dtype", ["f32", "f16"])
+def test_gemm_two_pass_f32_activations(cuda_device, nnb200_lib, shape, out_dtype):
+    """f32 activations (the reference's f32 -> f32 pose) at GEMM sizes: split into [hi | lo] f16 in
+    the scratch, dense GEMM over 2K with the weights repeating.  Held to the f32 tolerance."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k + 2)
+    wb = synth.q4_1_weights(rng, n, k)
+    a = (rng.standard_normal((m, k)) * 3).astype(np.float32)
+    want = oracle.q4_1_matmul(a, wb, k, out_dtype=out_dtype, w_round_f16=True)
+    ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device)
+    tdt = torch.float16 if out_dtype == "f16" else torch.float32
+    assert ops.q4_1_engine(ta, tw, k, out_dtype=tdt) == 5
+    got = ops.linear_q4_1(ta, tw, k, out_dtype=tdt)
+    _close(got.cpu().numpy(), want, RTOL_F16 if out_dtype == "f16" else RTOL_F32)
+    if out_dtype == "f32":   # the split carries 22 mantissa bits: far inside the tolerance
+        ref64 = oracle.q4_1_matmul(a, wb, k, out_dtype="f32", w_round_f16=True).astype(np.float64)
+        err = np.abs(got.cpu().numpy().astype(np.float64) - ref64).max() / np.sqrt(np.mean(ref64 ** 2))
+        assert err < 2e-5, err
+
+
 def test_gemm_two_pass_needs_its_scratch(cuda_device, nnb200_lib):
     """Without the scratch the same call runs the fused kernel: same result within tolerance."""
     import ctypes as C
