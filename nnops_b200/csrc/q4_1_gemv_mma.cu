@@ -33,6 +33,7 @@
 // CPU twin: mma_qblock_trans (src/backend/cpu/x86_64/mma_qblock.hpp:144-291).
 
 #include <mutex>
+#include <type_traits>
 
 #include "internal.cuh"
 #include "ptx.cuh"
@@ -101,6 +102,33 @@ __device__ __forceinline__ void load_act_block(const __half* a_blk, bool vec_ok,
     }
 }
 
+// f32 activations: the 32 values of one block as f16, either their high parts hi = f16(a) or the
+// remainders lo = f16(a - hi).  An MMA column fed with hi and another fed with lo, summed, give
+// the product to f32 accuracy (the pair carries 22 mantissa bits).
+__device__ __forceinline__ void load_act_block_f32(const float* a_blk, bool vec_ok, bool want_lo, uint4 (&av)[4])
+{
+    uint32_t* dst = reinterpret_cast<uint32_t*>(av);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float4 v;
+        if (vec_ok) {
+            v = __ldg(reinterpret_cast<const float4*>(a_blk) + j);
+        } else {
+            v = make_float4(a_blk[4 * j], a_blk[4 * j + 1], a_blk[4 * j + 2], a_blk[4 * j + 3]);
+        }
+        __half2 h01 = __floats2half2_rn(v.x, v.y);
+        __half2 h23 = __floats2half2_rn(v.z, v.w);
+        if (want_lo) {
+            const float2 f01 = __half22float2(h01);
+            const float2 f23 = __half22float2(h23);
+            h01 = __floats2half2_rn(v.x - f01.x, v.y - f01.y);
+            h23 = __floats2half2_rn(v.z - f23.x, v.w - f23.y);
+        }
+        dst[2 * j] = *reinterpret_cast<const uint32_t*>(&h01);
+        dst[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+    }
+}
+
 // Low half / high half of a word duplicated into both halves (f16 scale and min of a block).
 __device__ __forceinline__ uint32_t dup_lo16(uint32_t w) { return __byte_perm(w, w, 0x1010); }
 __device__ __forceinline__ uint32_t dup_hi16(uint32_t w) { return __byte_perm(w, w, 0x3232); }
@@ -149,9 +177,11 @@ __device__ __forceinline__ void mma_block(const uint32_t* s_lo, const uint32_t* 
     }
 }
 
-template <bool OUT_F16>
+// A_F32: activations are f32; MMA columns 0..m_count-1 carry their hi parts and columns
+// m_count..2*m_count-1 their lo parts (so m_count <= 4), summed in the final reduction.
+template <bool OUT_F16, bool A_F32>
 __global__ void __launch_bounds__(kWarps * 32, 2)
-q4_1_gemv_mma_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes, const __half* __restrict__ a,
+q4_1_gemv_mma_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes, const void* __restrict__ a_v,
                      const int64_t lda, void* __restrict__ out, const int64_t ldc, const int m_count,
                      const int n_total, const int k_total, const int num_bufs, const FpEpilogue ep,
                      const int a_vec_ok, int32_t* error_word)
@@ -225,10 +255,22 @@ q4_1_gemv_mma_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes,
 
     float acc0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     float acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    const bool row_live = g < m_count;  // activation row this lane feeds as MMA column g
+    // Activation row this lane feeds as MMA column g (f32: column g carries the hi part of row g
+    // for g < m_count and the lo part of row g - m_count after that).
+    const bool row_live = A_F32 ? g < 2 * m_count : g < m_count;
+    const bool want_lo = A_F32 && g >= m_count;
+    const int a_row = row_live ? (want_lo ? g - m_count : g) : 0;
     const bool vec_ok = a_vec_ok != 0;
-    // This lane's activations: row g, starting at its block c of the first group.
-    const __half* a_lane = a + static_cast<int64_t>(row_live ? g : 0) * lda + c * kQ4BlockElems;
+    using ActT = typename std::conditional<A_F32, float, __half>::type;
+    // This lane's activations: its row, starting at its block c of the first group.
+    const ActT* a_lane = static_cast<const ActT*>(a_v) + static_cast<int64_t>(a_row) * lda + c * kQ4BlockElems;
+    const auto load_act = [&](const ActT* blk, uint4 (&av)[4]) {
+        if constexpr (A_F32) {
+            load_act_block_f32(blk, vec_ok, want_lo, av);
+        } else {
+            load_act_block(blk, vec_ok, av);
+        }
+    };
     // Two fragment register sets, used alternately; lanes without a row keep zeros throughout.
     uint4 av0[4], av1[4];
 #pragma unroll
@@ -244,10 +286,10 @@ q4_1_gemv_mma_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes,
         slice_of(ch, sb, snb);
         if (snb > 0) {
             const int groups = snb / 4;
-            const __half* a_grp = a_lane + static_cast<int64_t>(sb) * kQ4BlockElems;  // group 0 of this slice
+            const ActT* a_grp = a_lane + static_cast<int64_t>(sb) * kQ4BlockElems;  // group 0 of this slice
             // First group's activations are fetched while the weights are still landing.
             if (row_live) {
-                load_act_block(a_grp, vec_ok, av0);
+                load_act(a_grp, av0);
             }
             if (!__all_sync(0xFFFFFFFFu, mbar_wait(&bars[warp][buf], phase, &abort_word))) {
                 atomicCAS(error_word, 0, kErrMmaWait);
@@ -261,11 +303,11 @@ q4_1_gemv_mma_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes,
             int gi = 0;
             for (; gi + 2 <= groups; gi += 2) {
                 if (row_live) {
-                    load_act_block(a_grp + (gi + 1) * kGroupElems, vec_ok, av1);
+                    load_act(a_grp + (gi + 1) * kGroupElems, av1);
                 }
                 mma_block(s_lo + gi * kGroupWords, s_hi + gi * kGroupWords, av0, acc0, acc1);
                 if (row_live && gi + 2 < groups) {
-                    load_act_block(a_grp + (gi + 2) * kGroupElems, vec_ok, av0);
+                    load_act(a_grp + (gi + 2) * kGroupElems, av0);
                 }
                 mma_block(s_lo + (gi + 1) * kGroupWords, s_hi + (gi + 1) * kGroupWords, av1, acc0, acc1);
             }
@@ -292,7 +334,20 @@ q4_1_gemv_mma_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes,
             s.w += p.w;
         }
         // Fragment layout: (x, y) = channel n0+g, activation rows 2c and 2c+1; (z, w) = channel n0+g+8.
-        const float vals[4] = {s.x, s.y, s.z, s.w};
+        float vals[4] = {s.x, s.y, s.z, s.w};
+        if constexpr (A_F32) {
+            // Column col holds the hi product of row col; its lo product sits m_count columns on,
+            // i.e. in lane (g, (col + m_count) / 2), component (col + m_count) % 2 of the same quad.
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int col = 2 * c + (j & 1);
+                const int pcol = (col + m_count) & 7;
+                const int src_lane = (lane & ~3) | (pcol >> 1);
+                const float even = __shfl_sync(0xFFFFFFFFu, j < 2 ? s.x : s.z, src_lane);
+                const float odd = __shfl_sync(0xFFFFFFFFu, j < 2 ? s.y : s.w, src_lane);
+                vals[j] += (pcol & 1) ? odd : even;
+            }
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + g + (j >= 2 ? 8 : 0);
@@ -309,9 +364,9 @@ q4_1_gemv_mma_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes,
     }
 }
 
-template <bool OUT_F16>
+template <bool OUT_F16, bool A_F32>
 cudaError_t launch_one(unsigned grid, bool overlap, cudaStream_t stream, const uint8_t* w, int64_t pitch,
-                       const __half* a, int64_t lda, void* out, int64_t ldc, int m_count, int n, int k, int num_bufs,
+                       const void* a, int64_t lda, void* out, int64_t ldc, int m_count, int n, int k, int num_bufs,
                        const FpEpilogue& ep, int a_vec_ok, int32_t* error_word)
 {
     cudaLaunchConfig_t cfg = {};
@@ -324,7 +379,7 @@ cudaError_t launch_one(unsigned grid, bool overlap, cudaStream_t stream, const u
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = overlap ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, q4_1_gemv_mma_kernel<OUT_F16>, w, pitch, a, lda, out, ldc, m_count, n, k,
+    return cudaLaunchKernelEx(&cfg, q4_1_gemv_mma_kernel<OUT_F16, A_F32>, w, pitch, a, lda, out, ldc, m_count, n, k,
                               num_bufs, ep, a_vec_ok, error_word);
 }
 
@@ -332,9 +387,9 @@ cudaError_t launch_one(unsigned grid, bool overlap, cudaStream_t stream, const u
 
 bool q4_1_gemv_mma_supported(const nnb200_q4_1_args& q)
 {
-    // f16 activations; weight rows movable by 16-byte bulk copies: 16-byte aligned base and
+    // f16 or f32 activations; weight rows movable by 16-byte bulk copies: 16-byte aligned base and
     // pitch, whole rows a multiple of 4 blocks (K % 128 == 0).
-    return q.a_f16 != 0 && q.n <= INT32_MAX && q.k <= INT32_MAX - 128 && (q.k % 128) == 0 &&
+    return q.n <= INT32_MAX && q.k <= INT32_MAX - 128 && (q.k % 128) == 0 &&
            (reinterpret_cast<uintptr_t>(q.w_blocks) & 15u) == 0 && (q.ldw_blocks % 4) == 0;
 }
 
@@ -353,11 +408,16 @@ int launch_q4_1_gemv_mma(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
     static cudaError_t attr_err[kMaxDevices];
     std::call_once(once[dev.device], [&] {
         const int max_smem = kWarps * kBufs * kSliceBufBytes;
-        cudaError_t e = cudaFuncSetAttribute(q4_1_gemv_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             max_smem);
-        if (e == cudaSuccess) {
-            e = cudaFuncSetAttribute(q4_1_gemv_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        }
+        cudaError_t e = cudaSuccess;
+        const auto raise = [&](auto kernel) {
+            if (e == cudaSuccess) {
+                e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+            }
+        };
+        raise(q4_1_gemv_mma_kernel<false, false>);
+        raise(q4_1_gemv_mma_kernel<true, false>);
+        raise(q4_1_gemv_mma_kernel<false, true>);
+        raise(q4_1_gemv_mma_kernel<true, true>);
         attr_err[dev.device] = e;
     });
     if (attr_err[dev.device] != cudaSuccess) {
@@ -366,22 +426,32 @@ int launch_q4_1_gemv_mma(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
     const int chunks = static_cast<int>((q.k / kQ4BlockElems + kMaxChunkBlocks - 1) / kMaxChunkBlocks);
     const int num_bufs = chunks < kBufs ? chunks : kBufs;
     const unsigned grid = static_cast<unsigned>((q.n + kRows - 1) / kRows);
-    const int a_vec_ok = ((reinterpret_cast<uintptr_t>(q.a) & 15u) == 0 && (q.lda % 8) == 0) ? 1 : 0;
+    const bool a_f32 = q.a_f16 == 0;
+    // 16-byte activation loads: aligned base and a row pitch that keeps every block aligned.
+    const int a_vec_ok = ((reinterpret_cast<uintptr_t>(q.a) & 15u) == 0 && (q.lda % (a_f32 ? 4 : 8)) == 0) ? 1 : 0;
     const uint8_t* w = static_cast<const uint8_t*>(q.w_blocks);
     const int64_t pitch = q.ldw_blocks * kQ4BlockBytes;
     const bool overlap = (q.flags & NNB200_Q4_FLAG_OVERLAP_PREVIOUS) != 0;
-    for (int64_t m0 = 0; m0 < q.m; m0 += 8) {
-        const int m_count = static_cast<int>(q.m - m0 < 8 ? q.m - m0 : 8);
-        const __half* a = static_cast<const __half*>(q.a) + m0 * q.lda;
+    const int64_t a_elem = a_f32 ? 4 : 2;
+    const int64_t out_elem = q.out_f16 ? 2 : 4;
+    // Activation rows per launch: the MMA has 8 columns; f32 rows take two of them (hi and lo).
+    const int rows_per_pass = a_f32 ? 4 : 8;
+    for (int64_t m0 = 0; m0 < q.m; m0 += rows_per_pass) {
+        const int m_count = static_cast<int>(q.m - m0 < rows_per_pass ? q.m - m0 : rows_per_pass);
+        const void* a = static_cast<const uint8_t*>(q.a) + m0 * q.lda * a_elem;
+        void* out = static_cast<uint8_t*>(q.out) + m0 * q.ldc * out_elem;
+        const int n = static_cast<int>(q.n), k = static_cast<int>(q.k);
         cudaError_t e;
-        if (q.out_f16) {
-            e = launch_one<true>(grid, overlap, stream, w, pitch, a, q.lda, static_cast<__half*>(q.out) + m0 * q.ldc,
-                                 q.ldc, m_count, static_cast<int>(q.n), static_cast<int>(q.k), num_bufs, ep, a_vec_ok,
-                                 dev.error_word);
+        if (a_f32) {
+            e = q.out_f16 ? launch_one<true, true>(grid, overlap, stream, w, pitch, a, q.lda, out, q.ldc, m_count, n, k,
+                                                   num_bufs, ep, a_vec_ok, dev.error_word)
+                          : launch_one<false, true>(grid, overlap, stream, w, pitch, a, q.lda, out, q.ldc, m_count, n, k,
+                                                    num_bufs, ep, a_vec_ok, dev.error_word);
         } else {
-            e = launch_one<false>(grid, overlap, stream, w, pitch, a, q.lda, static_cast<float*>(q.out) + m0 * q.ldc,
-                                  q.ldc, m_count, static_cast<int>(q.n), static_cast<int>(q.k), num_bufs, ep, a_vec_ok,
-                                  dev.error_word);
+            e = q.out_f16 ? launch_one<true, false>(grid, overlap, stream, w, pitch, a, q.lda, out, q.ldc, m_count, n, k,
+                                                    num_bufs, ep, a_vec_ok, dev.error_word)
+                          : launch_one<false, false>(grid, overlap, stream, w, pitch, a, q.lda, out, q.ldc, m_count, n,
+                                                     k, num_bufs, ep, a_vec_ok, dev.error_word);
         }
         note_launch();
         if (e != cudaSuccess) {

@@ -71,6 +71,27 @@ def test_gemv_mma_edges(cuda_device, nnb200_lib, shape):
     _close(got.cpu().numpy(), oracle.q4_1_matmul(a, wb_dense, k, out_dtype="f32"), RTOL_F32)
 
 
+@pytest.mark.parametrize("m", [1, 4, 7])
+@pytest.mark.parametrize("aligned", [True, False])
+def test_gemv_mma_f32_activations(cuda_device, nnb200_lib, m, aligned):
+    """f32 activations on the warp-MMA engine: each row feeds two MMA columns (hi and lo f16
+    parts), four rows per pass; accuracy stays at f32 level."""
+    rng = np.random.default_rng(m + 40)
+    n, k = 300, 4096
+    wb = synth.q4_1_weights(rng, n, k)
+    a = (rng.standard_normal((m, k)) * 5).astype(np.float32)
+    if aligned:
+        ta = torch.from_numpy(a).to(cuda_device)
+    else:
+        ta = torch.from_numpy(np.pad(a, ((0, 0), (1, 2)))).to(cuda_device)[:, 1:k + 1]   # 4-byte aligned rows only
+    tw = torch.from_numpy(wb).to(cuda_device)
+    assert ops.q4_1_engine(ta, tw, k, engine="gemv") == 4
+    got = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float32, engine="gemv").cpu().numpy()
+    want = oracle.q4_1_matmul(a, wb, k, out_dtype="f32", w_round_f16=True).astype(np.float64)
+    err = np.abs(got.astype(np.float64) - want).max() / np.sqrt(np.mean(want ** 2))
+    assert err < 2e-5, err
+
+
 def test_gemv_falls_back_when_rows_are_not_bulk_copyable(cuda_device, nnb200_lib):
     """K = 1000 (31.25 blocks): rows are not a whole number of 16-byte pieces, so the CUDA-core
     GEMV must be chosen -- and still match."""
