@@ -57,6 +57,7 @@ extern "C" {
 #define NNB200_ENGINE_NARROW 2  /* M <= 16 decode, any K: one warp per channel, dp4a        */
 #define NNB200_ENGINE_GENERIC 3 /* any pose / alignment: SIMT tile, correctness tier        */
 #define NNB200_ENGINE_DECODE 4  /* M <= 16, K % 64 == 0: streaming loads + warp MMA        */
+#define NNB200_ENGINE_SKINNY 5  /* M <= 128: tcgen05 with the weights as the 128-row operand */
 
 /*
  * One int8 matmul call: out[b][m][n] = epilogue( sum_k A[b][m][k] * W[b][n][k] ).

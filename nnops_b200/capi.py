@@ -16,7 +16,7 @@ STATUS_NAMES = ["ok", "invalid_argument", "unsupported", "not_initialized", "out
 OUT_KINDS = {"s32": 0, "s8": 1, "u8": 2, "f32": 3, "f16": 4}
 ACTIVATIONS = {"none": 0, "relu": 1, "gelu": 2, "sigmoid": 3, "tanh": 4, "leaky_relu": 5, "silu": 6,
                "hard_swish": 7, "elu": 8, "relu6": 9}
-ENGINES = {"auto": 0, "umma": 1, "narrow": 2, "generic": 3, "decode": 4}
+ENGINES = {"auto": 0, "umma": 1, "narrow": 2, "generic": 3, "decode": 4, "skinny": 5}
 ENGINE_NAMES = {v: k for k, v in ENGINES.items()}
 Q4_ENGINES = {"auto": 0, "gemm": 1, "gemv": 2, "gemv_simt": 3, "gemv_mma": 4, "gemm_two_pass": 5}
 STATIC_SCRATCH_BYTES = 1 << 20

@@ -158,8 +158,27 @@ int pick_i8_engine(const nnb200_gemm_i8_args* a, const I8Problem& p)
     if (a->force_engine == NNB200_ENGINE_DECODE) {
         return decode_i8_supported(p) ? NNB200_ENGINE_DECODE : NNB200_ENGINE_GENERIC;
     }
-    if (a->num_peer_outs == 0 && decode_i8_supported(p)) {
-        return NNB200_ENGINE_DECODE;
+    if (a->force_engine == NNB200_ENGINE_SKINNY) {
+        return (a->num_peer_outs == 0 && skinny_i8_supported(p)) ? NNB200_ENGINE_SKINNY : NNB200_ENGINE_GENERIC;
+    }
+    // Few activation rows: the cost is streaming W once.  Measured on N=28672,K=8192 / N=11008,K=4096:
+    // up to 8 rows the streaming warp-MMA engine wins (0.82-0.90 / 0.57-0.64 of HBM speed); from 9
+    // rows the tensor-core engine with the weights as the 128-row operand does (0.73-0.76 / 0.44-0.47
+    // up to 32 rows), until the square engine's wider tiles pay again: above 64 rows when the
+    // layer has enough 256-channel tiles for half the SMs.
+    if (a->num_peer_outs == 0) {
+        const bool decode_ok = decode_i8_supported(p);
+        const bool skinny_ok = skinny_i8_supported(p);
+        if (decode_ok && (p.m <= 8 || !skinny_ok)) {
+            return NNB200_ENGINE_DECODE;
+        }
+        if (skinny_ok) {
+            const DeviceInfo* dev = current_device_info();
+            const int64_t sms = dev != nullptr ? dev->sm_count : 148;
+            if (p.m <= 64 || (p.n + 255) / 256 < sms / 2) {
+                return NNB200_ENGINE_SKINNY;
+            }
+        }
     }
     if (a->num_peer_outs == 0 && narrow_i8_supported(p)) {
         return NNB200_ENGINE_NARROW;
@@ -291,6 +310,7 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
         case NNB200_ENGINE_UMMA: st = launch_gemm_i8_umma(p, ep, *dev, stream); break;
         case NNB200_ENGINE_NARROW: st = launch_gemm_i8_narrow(p, ep, *dev, stream); break;
         case NNB200_ENGINE_DECODE: st = launch_gemm_i8_decode(p, ep, *dev, stream); break;
+        case NNB200_ENGINE_SKINNY: st = launch_gemm_i8_skinny(p, ep, *dev, stream); break;
         default: st = launch_gemm_i8_generic(p, ep, *dev, stream); break;
         }
         if (st != NNB200_OK) {

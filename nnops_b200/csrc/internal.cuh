@@ -58,6 +58,8 @@ int launch_gemm_i8_narrow(const I8Problem& p, const I8Epilogue& ep, const Device
 bool narrow_i8_supported(const I8Problem& p);
 int launch_gemm_i8_decode(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
 bool decode_i8_supported(const I8Problem& p);
+int launch_gemm_i8_skinny(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
+bool skinny_i8_supported(const I8Problem& p);
 
 // R_a[m] = sum_k A[m][k] and R_w[n] = sum_k W[n][k] into int32 scratch; r_w == nullptr skips the
 // sweep over W (the caller has the sums already).

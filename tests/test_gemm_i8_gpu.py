@@ -89,17 +89,44 @@ def test_fp_clip(cuda_device, nnb200_lib):
 
 @pytest.mark.parametrize("m", [1, 2, 3, 8, 9, 16])
 def test_decode_engines(cuda_device, nnb200_lib, m):
-    """M <= 16: the streaming warp-MMA engine when K is a multiple of 64, the dp4a engine otherwise."""
+    """M <= 16: up to 8 rows the streaming warp-MMA engine (K a multiple of 64), from 9 rows -- or
+    for any other K -- the tensor-core engine with the weights as the 128-row operand; the dp4a
+    engine on request."""
+    few = "decode" if m <= 8 else "skinny"
     _run_case(cuda_device, m, 520, 1024, out_kind="s8", relu=True, per_channel=True, out_scale=1.1,
-              expect_engine="decode", seed=m)
+              expect_engine=few, seed=m)
+    _run_case(cuda_device, m, 520, 1024, out_kind="s8", relu=True, per_channel=True, out_scale=1.1,
+              engine="decode", expect_engine="decode", seed=m)
     _run_case(cuda_device, m, 520, 1024, out_kind="s8", relu=True, per_channel=True, out_scale=1.1,
               engine="narrow", expect_engine="narrow", seed=m)
+    # K not a multiple of 64
     _run_case(cuda_device, m, 130, 4096 + 16, out_kind="s32", a_unsigned=True, zero_points=True, per_token=True,
-              per_channel=True, expect_engine="narrow", seed=m + 50)
+              per_channel=True, expect_engine="skinny", seed=m + 50)
+    _run_case(cuda_device, m, 130, 4096 + 16, out_kind="s32", a_unsigned=True, zero_points=True, per_token=True,
+              per_channel=True, engine="narrow", expect_engine="narrow", seed=m + 50)
     # ragged channel count (n % 16 != 0), u8 activations with zero points, K with a partial unroll group
     _run_case(cuda_device, m, 1003, 64 * 37, out_kind="s32", a_unsigned=True, zero_points=True, per_token=True,
-              per_channel=True, expect_engine="decode", seed=m + 70)
-    _run_case(cuda_device, m, 48, 64, out_kind="f16", per_channel=True, expect_engine="decode", seed=m + 90)
+              per_channel=True, engine="decode", expect_engine="decode", seed=m + 70)
+    _run_case(cuda_device, m, 48, 64, out_kind="f16", per_channel=True, engine="decode", expect_engine="decode",
+              seed=m + 90)
+
+
+@pytest.mark.parametrize("m", [17, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("out_kind", ["s32", "s8", "u8", "f32", "f16"])
+def test_skinny_engine(cuda_device, nnb200_lib, m, out_kind):
+    """17..128 activation rows: the weights are the MMA's 128-row operand, the accumulator comes
+    out transposed.  Ragged N and K, u8 activations, zero points, every destination."""
+    _run_case(cuda_device, m, 1003, 528, out_kind=out_kind, a_unsigned=(m % 2 == 0), relu=True, per_token=True,
+              per_channel=True, zero_points=True, out_scale=1.9, out_zp=0 if out_kind == "s32" else 4,
+              expect_engine="skinny", seed=m)
+    _run_case(cuda_device, m, 4096, 4096, out_kind=out_kind, relu=True, per_channel=True, out_scale=1.3,
+              expect_engine="skinny", seed=m + 1)
+
+
+def test_skinny_engine_small_m_on_request(cuda_device, nnb200_lib):
+    for m in (1, 5, 16):
+        _run_case(cuda_device, m, 520, 1024, out_kind="s8", relu=True, per_channel=True, out_scale=1.1,
+                  engine="skinny", expect_engine="skinny", seed=m)
 
 
 @pytest.mark.parametrize("out_kind", ["s32", "s8", "u8", "f32", "f16"])
