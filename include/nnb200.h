@@ -80,9 +80,13 @@ extern "C" {
  * scale_a / zp_a are per row m (NULL -> the *_scalar value), scale_w / zp_w per output
  * channel n.  For a batched call the same arrays serve every batch element.
  *
- * workspace: nnb200_gemm_i8_workspace_bytes() bytes of device scratch (may be NULL when
- * that is 0).  It holds the row/column sums R_a, R_w when any zero point is non-zero and
- * the split-K planes of the narrow engine.
+ * workspace: nnb200_gemm_i8_workspace_bytes() bytes of 16-byte aligned device scratch (may be
+ * NULL when that is 0).  It holds the row/column sums R_a, R_w when any zero point is non-zero
+ * and, for calls of up to 128 activation rows that the weights-as-rows tensor-core engine
+ * serves, the partial sums and arrival counters with which that engine shares K evenly among
+ * all SMs.  Only the first part is required: a workspace of at least
+ * nnb200_gemm_i8_min_workspace_bytes() is accepted, and the call then runs with whole tiles
+ * per SM (same results, slower when N / 128 does not fill the SMs evenly).
  */
 typedef struct nnb200_gemm_i8_args {
     const void* a;
@@ -129,8 +133,10 @@ typedef struct nnb200_gemm_i8_args {
     const int32_t* r_w;
 } nnb200_gemm_i8_args;
 
-/* Scratch the call needs (0 for the common zero-point-free tensor-core call). */
+/* Scratch the call runs fastest with (0 for the common zero-point-free tensor-core call), and
+ * the least it accepts. */
 NNB200_API size_t nnb200_gemm_i8_workspace_bytes(const nnb200_gemm_i8_args* args);
+NNB200_API size_t nnb200_gemm_i8_min_workspace_bytes(const nnb200_gemm_i8_args* args);
 
 /* Enqueue the matmul.  Replaces dense_gemm_i8_status
  * (src/backend/cuda/matmul/matmul_i8.cuh:284-446). */
@@ -288,6 +294,15 @@ NNB200_API int nnb200_interleave_shards(const void* gathered, void* out, int64_t
  * *code (0 = no error) and clears it.
  */
 NNB200_API int nnb200_take_device_error(int32_t* code);
+
+/*
+ * Exercises that mechanism without disturbing anything: launches one thread that waits, for
+ * at most limit_cycles SM clock cycles (1 .. 2e8), on a barrier nothing arrives at.  The wait
+ * runs out, the kernel records NNB200_DEVICE_ERROR_SELFTEST (7) in the error word and returns
+ * normally; the context stays usable.  The next nnb200_take_device_error reports the code.
+ */
+#define NNB200_DEVICE_ERROR_SELFTEST 7
+NNB200_API int nnb200_selftest_wait_limit(int64_t limit_cycles, void* stream);
 
 /* Stage a host array into device memory on the stream (the reference launcher's per-call
  * H2D of quantization arrays, src/backend/cuda/matmul/matmul_i8.cuh:357-376). */

@@ -87,6 +87,7 @@ class QuantLinearArgs(C.Structure):
 
 SYMBOLS = [
     ("nnb200_gemm_i8_workspace_bytes", C.c_size_t, [C.POINTER(GemmI8Args)]),
+    ("nnb200_gemm_i8_min_workspace_bytes", C.c_size_t, [C.POINTER(GemmI8Args)]),
     ("nnb200_gemm_i8", C.c_int, [C.POINTER(GemmI8Args), C.c_void_p]),
     ("nnb200_gemm_i8_static_scratch", C.c_int, [C.POINTER(GemmI8Args), C.c_void_p]),
     ("nnb200_gemm_i8_engine", C.c_int, [C.POINTER(GemmI8Args)]),
@@ -104,6 +105,7 @@ SYMBOLS = [
     ("nnb200_interleave_shards", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64,
                                            C.c_void_p]),
     ("nnb200_take_device_error", C.c_int, [C.POINTER(C.c_int32)]),
+    ("nnb200_selftest_wait_limit", C.c_int, [C.c_int64, C.c_void_p]),
     ("nnb200_copy_h2d_async", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("nnb200_scratch_alloc_async", C.c_int, [C.POINTER(C.c_void_p), C.c_size_t, C.c_void_p]),
     ("nnb200_scratch_free_async", C.c_int, [C.c_void_p, C.c_void_p]),
@@ -154,3 +156,11 @@ def take_device_error() -> int:
     code = C.c_int32(0)
     check(lib().nnb200_take_device_error(C.byref(code)), "nnb200_take_device_error")
     return code.value
+
+
+DEVICE_ERROR_SELFTEST = 7
+
+
+def selftest_wait_limit(limit_cycles: int = 2_000_000, stream=None) -> None:
+    """Launch the wait self-test: its barrier wait runs out and records DEVICE_ERROR_SELFTEST."""
+    check(lib().nnb200_selftest_wait_limit(int(limit_cycles), stream), "nnb200_selftest_wait_limit")

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "internal.cuh"
+#include "ptx.cuh"
 
 namespace nnb200 {
 
@@ -194,6 +195,23 @@ size_t out_elem_bytes(int kind)
     return (kind == NNB200_OUT_S32 || kind == NNB200_OUT_F32) ? 4 : (kind == NNB200_OUT_F16 ? 2 : 1);
 }
 
+// Self-test of the bounded pipeline waits: one thread waits on a barrier nothing ever arrives
+// at.  The wait has to run out after `limit_cycles`, raise the CTA's abort flag and record
+// kErrSelfTest in the device's error word; the kernel then returns normally.
+__global__ void wait_selftest_kernel(long long limit_cycles, int32_t* error_word)
+{
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&bar, 1);
+        mbar_init_fence();
+        if (!mbar_wait(&bar, 0, &abort_flag, limit_cycles)) {
+            atomicCAS(error_word, 0, kErrSelfTest);
+        }
+    }
+}
+
 }  // namespace
 }  // namespace nnb200
 
@@ -201,7 +219,7 @@ using namespace nnb200;
 
 extern "C" {
 
-size_t nnb200_gemm_i8_workspace_bytes(const nnb200_gemm_i8_args* a)
+size_t nnb200_gemm_i8_min_workspace_bytes(const nnb200_gemm_i8_args* a)
 {
     if (!valid_i8_args(a) || a->m == 0 || a->n == 0 || a->batch == 0) {
         return 0;
@@ -213,6 +231,31 @@ size_t nnb200_gemm_i8_workspace_bytes(const nnb200_gemm_i8_args* a)
     const size_t ra = (static_cast<size_t>(a->m) * 4 + 255) & ~size_t(255);
     const size_t rw = (static_cast<size_t>(a->n) * 4 + 255) & ~size_t(255);
     return static_cast<size_t>(a->batch) * (ra + rw);
+}
+
+// Scratch that lets the few-row tensor-core engine split K evenly over all SMs (optional).
+static size_t i8_split_bytes(const nnb200_gemm_i8_args* a)
+{
+    if (a->batch != 1 || a->num_peer_outs != 0) {
+        return 0;
+    }
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr) {
+        return 0;
+    }
+    const I8Problem p = problem_of(a, 0);
+    if (pick_i8_engine(a, p) != NNB200_ENGINE_SKINNY) {
+        return 0;
+    }
+    return skinny_i8_split_bytes(p, *dev);
+}
+
+size_t nnb200_gemm_i8_workspace_bytes(const nnb200_gemm_i8_args* a)
+{
+    if (!valid_i8_args(a) || a->m == 0 || a->n == 0 || a->batch == 0) {
+        return 0;
+    }
+    return nnb200_gemm_i8_min_workspace_bytes(a) + i8_split_bytes(a);
 }
 
 int nnb200_gemm_i8_engine(const nnb200_gemm_i8_args* a)
@@ -240,9 +283,16 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const bool comp = needs_compensation(a);
-    const size_t need = nnb200_gemm_i8_workspace_bytes(a);
+    const size_t need = nnb200_gemm_i8_min_workspace_bytes(a);
     if (need > 0 && (a->workspace == nullptr || a->workspace_bytes < need)) {
         return NNB200_INVALID_ARGUMENT;
+    }
+    // The rest of the workspace, when there is enough of it, lets the few-row engine split K.
+    const size_t split_bytes = i8_split_bytes(a);
+    void* split_scratch = nullptr;
+    if (split_bytes > 0 && a->workspace != nullptr && a->workspace_bytes >= need + split_bytes &&
+        ((reinterpret_cast<uintptr_t>(a->workspace) + need) & 15u) == 0) {
+        split_scratch = static_cast<uint8_t*>(a->workspace) + need;
     }
     const size_t ra_bytes = (static_cast<size_t>(a->m) * 4 + 255) & ~size_t(255);
     const size_t rw_bytes = (static_cast<size_t>(a->n) * 4 + 255) & ~size_t(255);
@@ -310,7 +360,7 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
         case NNB200_ENGINE_UMMA: st = launch_gemm_i8_umma(p, ep, *dev, stream); break;
         case NNB200_ENGINE_NARROW: st = launch_gemm_i8_narrow(p, ep, *dev, stream); break;
         case NNB200_ENGINE_DECODE: st = launch_gemm_i8_decode(p, ep, *dev, stream); break;
-        case NNB200_ENGINE_SKINNY: st = launch_gemm_i8_skinny(p, ep, *dev, stream); break;
+        case NNB200_ENGINE_SKINNY: st = launch_gemm_i8_skinny(p, ep, *dev, split_scratch, stream); break;
         default: st = launch_gemm_i8_generic(p, ep, *dev, stream); break;
         }
         if (st != NNB200_OK) {
@@ -548,6 +598,20 @@ int nnb200_take_device_error(int32_t* code)
     }
     const int32_t zero = 0;
     return cuda_status(cudaMemcpy(dev->error_word, &zero, sizeof(zero), cudaMemcpyHostToDevice));
+}
+
+int nnb200_selftest_wait_limit(int64_t limit_cycles, void* stream)
+{
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    if (limit_cycles < 1 || limit_cycles > 200'000'000) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_cycles, dev->error_word);
+    note_launch();
+    return cuda_status(cudaGetLastError());
 }
 
 int nnb200_copy_h2d_async(void* dst_device, const void* src_host, size_t bytes, void* stream)

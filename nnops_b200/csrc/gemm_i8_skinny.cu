@@ -18,7 +18,21 @@
 // Same pipeline skeleton as the square engine (TMA warp, MMA warp, four epilogue warps, two
 // TMEM accumulators, bounded waits), same epilogue arithmetic (epilogue.cuh): results are
 // bit-identical to every other int8 engine.
+//
+// Work split.  The unit of work is one 128-byte K block of one tile; tile t owns units
+// [t * num_kb, (t + 1) * num_kb).  Every CTA takes one contiguous range of units:
+//   * whole tiles only (CTA c gets tiles [c T / G, (c + 1) T / G)) when no scratch is given;
+//   * an equal share of ALL units (CTA c gets [c U / G, (c + 1) U / G)) when the caller gave
+//     scratch: a range then starts and ends in the middle of tiles, so that every SM streams
+//     the same number of weight bytes whatever N / 128 is (224 tiles on 148 SMs would otherwise
+//     run as two waves, the second half empty).  A CTA that holds only part of a tile's K range
+//     writes its int32 partial sums to its own slot of the scratch and counts itself in on the
+//     tile's counter; whichever warp counts in last adds the other parts to its own and runs
+//     the epilogue.  Nobody waits for anybody, and integer addition makes the result
+//     independent of who came last.  The protocol runs per warp (a warp owns 32 channels of the
+//     tile in every CTA), so it needs no CTA-wide barrier.
 
+#include <cstdlib>
 #include <mutex>
 
 #include "internal.cuh"
@@ -46,11 +60,108 @@ struct SkinnyConfig {
     static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kRowTermBytes + kBarrierBytes;
 };
 
+// First unit of CTA c's range (c = G gives the end of the last range).
+__device__ __forceinline__ int64_t range_begin(int c, int grid, int num_tiles, int num_kb, bool split)
+{
+    if (split) {
+        return static_cast<int64_t>(c) * (static_cast<int64_t>(num_tiles) * num_kb) / grid;
+    }
+    return (static_cast<int64_t>(c) * num_tiles / grid) * num_kb;
+}
+
+// The CTA whose range contains unit u under the equal-share split.
+__device__ __forceinline__ int cta_of_unit(int64_t u, int grid, int64_t total_units)
+{
+    return static_cast<int>(((u + 1) * grid - 1) / total_units);
+}
+
+// Bytes of the per-tile, per-warp arrival counters at the head of the split scratch.
+__host__ __device__ inline size_t split_counter_bytes(int num_tiles)
+{
+    return (static_cast<size_t>(num_tiles) * 4 * sizeof(int32_t) + 255) & ~size_t(255);
+}
+
+// One piece of a CTA's range: K blocks [kb0, kb1) of `tile`.
+struct Segment {
+    int tile, kb0, kb1;
+};
+
+// A CTA's range [u_begin, u_end) cut at tile boundaries, in the order it is worked through:
+// the part of a tile that somebody else started (head), the part of a tile that somebody else
+// finishes (tail), then the whole tiles.  Parts go first so that they are published early and
+// the exchange with the neighbours hides behind the whole tiles that follow.
+struct SegmentList {
+    int64_t head0, head1, tail0, tail1;
+    int tile0, tile1;
+    int num_kb;
+
+    __device__ __forceinline__ SegmentList(int64_t u_begin, int64_t u_end, int nkb) : num_kb(nkb)
+    {
+        const int64_t first_full = (u_begin + nkb - 1) / nkb * nkb;
+        const int64_t last_full_end = u_end / nkb * nkb;
+        head0 = u_begin;
+        head1 = first_full < u_end ? first_full : u_end;
+        if (last_full_end >= first_full && last_full_end < u_end) {
+            tail0 = last_full_end;
+            tail1 = u_end;
+        } else {
+            tail0 = tail1 = 0;
+        }
+        tile0 = static_cast<int>(first_full / nkb);
+        tile1 = last_full_end > first_full ? static_cast<int>(last_full_end / nkb) : tile0;
+    }
+    __device__ __forceinline__ int count() const
+    {
+        return (head1 > head0 ? 1 : 0) + (tail1 > tail0 ? 1 : 0) + (tile1 - tile0);
+    }
+    __device__ __forceinline__ Segment at(int i) const
+    {
+        Segment s;
+        if (head1 > head0) {
+            if (i == 0) {
+                s.tile = static_cast<int>(head0 / num_kb);
+                s.kb0 = static_cast<int>(head0 - static_cast<int64_t>(s.tile) * num_kb);
+                s.kb1 = s.kb0 + static_cast<int>(head1 - head0);
+                return s;
+            }
+            --i;
+        }
+        if (tail1 > tail0) {
+            if (i == 0) {
+                s.tile = static_cast<int>(tail0 / num_kb);
+                s.kb0 = 0;
+                s.kb1 = static_cast<int>(tail1 - tail0);
+                return s;
+            }
+            --i;
+        }
+        s.tile = tile0 + i;
+        s.kb0 = 0;
+        s.kb1 = num_kb;
+        return s;
+    }
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int32_t* p)
+{
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void zero_words_kernel(int32_t* p, int n)
+{
+    const int i = static_cast<int>(blockIdx.x * blockDim.x + threadIdx.x);
+    if (i < n) {
+        p[i] = 0;
+    }
+}
+
 template <int MP, int KIND>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                       const I8Epilogue ep, const int m_total, const int n_total, const int k_total,
-                      const uint32_t idesc, int32_t* error_word)
+                      const uint32_t idesc, int32_t* error_word, int32_t* split_counters, int32_t* split_slots)
 {
     using Cfg = SkinnyConfig<MP>;
     constexpr int kStages = Cfg::kStages;
@@ -70,6 +181,12 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const int lane = threadIdx.x & 31;
     const int num_tiles = (n_total + kBlockN - 1) / kBlockN;
     const int num_kb = (k_total + kBlockKBytes - 1) / kBlockKBytes;
+    const bool split = split_counters != nullptr;
+    const int grid = static_cast<int>(gridDim.x);
+    const int64_t u_begin = range_begin(static_cast<int>(blockIdx.x), grid, num_tiles, num_kb, split);
+    const int64_t u_end = range_begin(static_cast<int>(blockIdx.x) + 1, grid, num_tiles, num_kb, split);
+    const SegmentList segments(u_begin, u_end, num_kb);
+    const int num_segments = segments.count();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -111,8 +228,10 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             uint32_t armed = 0;
             uint32_t armed_phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                for (int kb = 0; kb < num_kb; ++kb) {
+            for (int si = 0; ok && si < num_segments; ++si) {
+                const Segment seg = segments.at(si);
+                const int tile = seg.tile;
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         atomicCAS(error_word, 0, kErrProducerWait);
                         ok = false;
@@ -152,18 +271,19 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            int local_tile = 0;
+            int local_seg = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
-                const int acc = local_tile & 1;
-                const uint32_t acc_phase = (local_tile >> 1) & 1u;
+            for (; ok && local_seg < num_segments; ++local_seg) {
+                const Segment seg = segments.at(local_seg);
+                const int acc = local_seg & 1;
+                const uint32_t acc_phase = (local_seg >> 1) & 1u;
                 if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag)) {
                     atomicCAS(error_word, 0, kErrAccumWait);
                     break;
                 }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * MP);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = seg.kb0; kb < seg.kb1; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
                         atomicCAS(error_word, 0, kErrMmaWait);
                         ok = false;
@@ -177,7 +297,7 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 #pragma unroll
                     for (int ks = 0; ks < kBlockKBytes / kUmmaK; ++ks) {
                         umma_i8(d_tmem, w_desc + static_cast<uint64_t>(ks * 2), a_desc + static_cast<uint64_t>(ks * 2),
-                                idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                                idesc, (kb > seg.kb0 || ks > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty_bar[stage]);
                     if (++stage == kStages) {
@@ -197,11 +317,20 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         const float zpf = static_cast<float>(ep.out_zp);
         const float lo = (KIND == NNB200_OUT_S8 ? -128.0f : 0.0f) - zpf;
         const float hi = (KIND == NNB200_OUT_S8 ? 127.0f : 255.0f) - zpf;
-        int local_tile = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
-            const int acc = local_tile & 1;
-            const uint32_t acc_phase = (local_tile >> 1) & 1u;
-            const int64_t n = static_cast<int64_t>(tile) * kBlockN + quarter * 32 + lane;
+        if (split) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // the counters' zeroing kernel
+        }
+        const int ch = quarter * 32 + lane;  // this thread's channel within the tile
+        const int64_t total_units = static_cast<int64_t>(num_tiles) * num_kb;
+        const size_t slot_elems = static_cast<size_t>(kBlockN) * static_cast<size_t>(m_total);
+        int local_seg = 0;
+        for (; local_seg < num_segments; ++local_seg) {
+            const Segment seg = segments.at(local_seg);
+            const int tile = seg.tile;
+            const int acc = local_seg & 1;
+            const uint32_t acc_phase = (local_seg >> 1) & 1u;
+            const bool partial = seg.kb0 != 0 || seg.kb1 != num_kb;  // only under the equal-share split
+            const int64_t n = static_cast<int64_t>(tile) * kBlockN + ch;
             const bool n_ok = n < n_total;
             // This channel's terms, in registers for the whole tile.
             const int32_t zpw = (n_ok && ep.zp_w != nullptr) ? ep.zp_w[n] : ep.zp_w_scalar;
@@ -226,14 +355,83 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             tc_fence_after_sync();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(acc * MP);
+            // Part of a tile: publish this warp's 32 channels, count in, and carry on only if every
+            // other part of the tile has been published already.
+            int first_cta = 0, last_cta = -1;
+            bool finish = true;
+            bool publish = partial;
+            if (partial) {
+                first_cta = cta_of_unit(static_cast<int64_t>(tile) * num_kb, grid, total_units);
+                last_cta = cta_of_unit(static_cast<int64_t>(tile + 1) * num_kb - 1, grid, total_units);
+                // Everybody else already in?  Then this warp finishes the tile and has nothing to publish.
+                int seen = 0;
+                if (lane == 0) {
+                    seen = ld_acquire_gpu(&split_counters[tile * 4 + quarter]);
+                }
+                seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
+                publish = seen != last_cta - first_cta;
+                if (!publish) {
+                    __threadfence();  // every lane's reads of the others' slots come after lane 0's look
+                }
+            }
+            if (publish) {
+                int32_t* mine = split_slots +
+                                (2 * static_cast<size_t>(blockIdx.x) + (seg.kb0 == 0 ? 1u : 0u)) * slot_elems + ch;
+#pragma unroll 1
+                for (int c = 0; c < MP / 32; ++c) {
+                    if (c * 32 >= m_total) {
+                        break;  // uniform
+                    }
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (c * 32 + j < m_total) {
+                            __stcg(mine + static_cast<size_t>(c * 32 + j) * kBlockN, static_cast<int32_t>(v[j]));
+                        }
+                    }
+                }
+                __threadfence();
+                __syncwarp();
+                int ticket = 0;
+                if (lane == 0) {
+                    ticket = atomicAdd(&split_counters[tile * 4 + quarter], 1);
+                }
+                ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+                finish = ticket == last_cta - first_cta;
+                if (finish) {
+                    __threadfence();
+                }
+            }
 #pragma unroll 1
             for (int c = 0; c < MP / 32; ++c) {
-                if (c * 32 >= m_total) {
+                if (c * 32 >= m_total || !finish) {
                     break;  // uniform
                 }
                 uint32_t v[32];
                 tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                 tmem_ld_wait();
+                if (partial) {
+                    for (int other = first_cta; other <= last_cta; ++other) {
+                        if (other == static_cast<int>(blockIdx.x)) {
+                            continue;
+                        }
+                        const int32_t* theirs = split_slots +
+                                                (2 * static_cast<size_t>(other) + (other == first_cta ? 1u : 0u)) * slot_elems +
+                                                ch;
+                        // All loads first, then the additions: one L2 round trip per part, not per row.
+                        int32_t part[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            part[j] = (c * 32 + j < m_total) ? __ldcg(theirs + static_cast<size_t>(c * 32 + j) * kBlockN) : 0;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            v[j] += static_cast<uint32_t>(part[j]);
+                        }
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int m = c * 32 + j;
@@ -278,7 +476,8 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 }
 
 template <int MP, int KIND>
-int launch_skinny_variant(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream)
+int launch_skinny_variant(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, void* split_scratch,
+                          cudaStream_t stream)
 {
     using Cfg = SkinnyConfig<MP>;
     auto kernel = gemm_i8_skinny_kernel<MP, KIND>;
@@ -299,23 +498,47 @@ int launch_skinny_variant(const I8Problem& p, const I8Epilogue& ep, const Device
         return NNB200_INTERNAL;
     }
     const int num_tiles = (n + kBlockN - 1) / kBlockN;
-    const int grid = num_tiles < dev.sm_count ? num_tiles : dev.sm_count;
+    int grid = num_tiles < dev.sm_count ? num_tiles : dev.sm_count;
+    int32_t* counters = nullptr;
+    int32_t* slots = nullptr;
+    if (split_scratch != nullptr) {
+        // Equal shares of all K blocks over every SM; the tiles' counters start from zero.
+        grid = dev.sm_count;
+        counters = static_cast<int32_t*>(split_scratch);
+        slots = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(split_scratch) + split_counter_bytes(num_tiles));
+        zero_words_kernel<<<(num_tiles * 4 + 255) / 256, 256, 0, stream>>>(counters, num_tiles * 4);
+        note_launch();
+    }
     // 128-row operand = weights (s8), N operand = activations (s8 or u8).
     const uint32_t idesc = umma_idesc(2, 1, p.a_unsigned ? 0u : 1u, kBlockN, MP);
-    kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(map_w, map_a, ep, m, n, k, idesc, dev.error_word);
+    // With the split, the GEMM may start while the zeroing kernel drains: only its epilogue
+    // warps touch the counters, and they wait for that kernel first.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(kNumThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = counters != nullptr ? 1 : 0;
+    const cudaError_t e =
+        cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, ep, m, n, k, idesc, dev.error_word, counters, slots);
     note_launch();
-    return cuda_status(cudaGetLastError());
+    return cuda_status(e != cudaSuccess ? e : cudaGetLastError());
 }
 
 template <int MP>
-int launch_skinny_mp(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream)
+int launch_skinny_mp(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, void* split_scratch,
+                     cudaStream_t stream)
 {
     switch (ep.out_kind) {
-    case NNB200_OUT_S32: return launch_skinny_variant<MP, NNB200_OUT_S32>(p, ep, dev, stream);
-    case NNB200_OUT_S8: return launch_skinny_variant<MP, NNB200_OUT_S8>(p, ep, dev, stream);
-    case NNB200_OUT_U8: return launch_skinny_variant<MP, NNB200_OUT_U8>(p, ep, dev, stream);
-    case NNB200_OUT_F32: return launch_skinny_variant<MP, NNB200_OUT_F32>(p, ep, dev, stream);
-    case NNB200_OUT_F16: return launch_skinny_variant<MP, NNB200_OUT_F16>(p, ep, dev, stream);
+    case NNB200_OUT_S32: return launch_skinny_variant<MP, NNB200_OUT_S32>(p, ep, dev, split_scratch, stream);
+    case NNB200_OUT_S8: return launch_skinny_variant<MP, NNB200_OUT_S8>(p, ep, dev, split_scratch, stream);
+    case NNB200_OUT_U8: return launch_skinny_variant<MP, NNB200_OUT_U8>(p, ep, dev, split_scratch, stream);
+    case NNB200_OUT_F32: return launch_skinny_variant<MP, NNB200_OUT_F32>(p, ep, dev, split_scratch, stream);
+    case NNB200_OUT_F16: return launch_skinny_variant<MP, NNB200_OUT_F16>(p, ep, dev, split_scratch, stream);
     default: return NNB200_UNSUPPORTED;
     }
 }
@@ -328,15 +551,49 @@ bool skinny_i8_supported(const I8Problem& p)
     return p.m >= 1 && p.m <= 128 && umma_i8_supported(p);
 }
 
-int launch_gemm_i8_skinny(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream)
+// Scratch for the equal-share split of K over all SMs, or 0 when whole tiles already fill
+// them evenly (within a tenth) or a share is too short to pay for the exchange: publishing a
+// part, counting in and collecting the others' costs a few microseconds at the end of the
+// kernel, which only a long stream (from about 48 K blocks = 768 KB of weights per SM) buys back
+// (measured: N=28672, K=8192, 16 rows 50.4 -> 46.9 us; N=11008, K=4096, 16 rows 16.0 -> 21.2 us).
+// NNB200_I8_SHARE_K=0 turns the split off; =2 offers it from 8 K blocks per SM (measurement, tests).
+size_t skinny_i8_split_bytes(const I8Problem& p, const DeviceInfo& dev)
+{
+    if (!skinny_i8_supported(p)) {
+        return 0;
+    }
+    const char* e = getenv("NNB200_I8_SHARE_K");
+    const char mode = e != nullptr ? e[0] : '1';
+    if (mode == '0') {
+        return 0;
+    }
+    const int64_t tiles = (p.n + kBlockN - 1) / kBlockN;
+    const int64_t num_kb = (p.k + kBlockKBytes - 1) / kBlockKBytes;
+    const int64_t sms = dev.sm_count;
+    const int64_t waves = (tiles + sms - 1) / sms;
+    const int64_t min_share = mode == '2' ? 8 : 48;
+    if (tiles * 10 >= waves * sms * 9 || tiles * num_kb < min_share * sms) {
+        return 0;
+    }
+    if (mode != '2' && p.m > 64) {
+        return 0;  // the int32 parts grow with m: from 65 rows they cost more than the even split saves
+    }
+    // Two slots per CTA (the tile it finishes for someone and the tile it leaves to someone),
+    // each 128 channels x m int32.
+    return split_counter_bytes(static_cast<int>(tiles)) +
+           2 * static_cast<size_t>(sms) * kBlockN * static_cast<size_t>(p.m) * sizeof(int32_t);
+}
+
+int launch_gemm_i8_skinny(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, void* split_scratch,
+                          cudaStream_t stream)
 {
     if (p.m <= 32) {
-        return launch_skinny_mp<32>(p, ep, dev, stream);
+        return launch_skinny_mp<32>(p, ep, dev, split_scratch, stream);
     }
     if (p.m <= 64) {
-        return launch_skinny_mp<64>(p, ep, dev, stream);
+        return launch_skinny_mp<64>(p, ep, dev, split_scratch, stream);
     }
-    return launch_skinny_mp<128>(p, ep, dev, stream);
+    return launch_skinny_mp<128>(p, ep, dev, split_scratch, stream);
 }
 
 }  // namespace nnb200

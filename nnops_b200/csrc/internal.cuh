@@ -58,7 +58,10 @@ int launch_gemm_i8_narrow(const I8Problem& p, const I8Epilogue& ep, const Device
 bool narrow_i8_supported(const I8Problem& p);
 int launch_gemm_i8_decode(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
 bool decode_i8_supported(const I8Problem& p);
-int launch_gemm_i8_skinny(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
+// split_scratch: skinny_i8_split_bytes() bytes for the equal-share split of K over all SMs, or null.
+int launch_gemm_i8_skinny(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, void* split_scratch,
+                          cudaStream_t stream);
+size_t skinny_i8_split_bytes(const I8Problem& p, const DeviceInfo& dev);
 bool skinny_i8_supported(const I8Problem& p);
 
 // R_a[m] = sum_k A[m][k] and R_w[n] = sum_k W[n][k] into int32 scratch; r_w == nullptr skips the

@@ -19,6 +19,7 @@ enum DeviceError : int32_t {
     kErrAccumWait = 4,     // MMA issuer timed out waiting for a free accumulator
     kErrDequantWait = 5,   // Q4_1 dequant warps timed out
     kErrDrainWait = 6,     // teardown timed out waiting for copies in flight
+    kErrSelfTest = 7,      // the wait self-test's barrier ran out, as it must
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
@@ -85,7 +86,8 @@ constexpr long long kWaitLimitCycles = 4'000'000'000LL;
 
 // Wait for `parity` on `bar`.  Returns false if the wait ran out or another role already
 // aborted (`*abort_flag` != 0); on running out it raises the flag itself.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit_cycles = kWaitLimitCycles)
 {
     if (mbar_try_wait(bar, parity)) {
         return true;
@@ -100,7 +102,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             if (*abort_flag != 0) {
                 return false;
             }
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit_cycles) {
                 *abort_flag = 1;
                 return false;
             }

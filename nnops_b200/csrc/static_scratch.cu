@@ -57,7 +57,7 @@ extern "C" int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, vo
     nnb200_gemm_i8_args local = *args;
     local.workspace = nullptr;
     local.workspace_bytes = 0;
-    const size_t need = nnb200_gemm_i8_workspace_bytes(&local);
+    const size_t need = nnb200_gemm_i8_min_workspace_bytes(&local);
     if (need > static_cast<size_t>(NNB200_STATIC_SCRATCH_BYTES)) {
         // Too large for the fixed array: refuse before anything is launched.
         return NNB200_OUT_OF_MEMORY;

@@ -165,10 +165,15 @@ public:
         out.ptr = dst;
         return nnb200_copy_h2d_async(dst, host, bytes, stream_);
     }
+    // Null when the request exceeds what was reserved.
     void* take_raw(size_t bytes)
     {
+        const size_t padded = (bytes + 255) & ~size_t(255);
+        if (base_ == nullptr || used_ + padded > total_) {
+            return nullptr;
+        }
         void* p = static_cast<char*>(base_) + used_;
-        used_ += (bytes + 255) & ~size_t(255);
+        used_ += padded;
         return p;
     }
 
@@ -274,6 +279,13 @@ Status run_i8(const I8Call& c, const ComputeContext& ctx)
     if (qa.zero_point != 0 || qw.zero_point != 0 || qa.zero_point_data != nullptr || qw.zero_point_data != nullptr) {
         st.reserve_raw(((m_bytes + 255) & ~size_t(255)) + ((n_bytes + 255) & ~size_t(255)));
     }
+    // Optional scratch with which the few-row engine shares K evenly among the SMs.  The library
+    // sizes it from shapes and pointers alone (zero points do not enter), so the block as filled
+    // so far is enough to ask.
+    g.a = a.ptr<void>();
+    g.w = w.ptr<void>();
+    g.out = out.ptr<void>();
+    st.reserve_raw(nnb200_gemm_i8_workspace_bytes(&g) - nnb200_gemm_i8_min_workspace_bytes(&g));
     if (const int e = st.allocate(); e != NNB200_OK) {
         return to_status(e);
     }
@@ -315,6 +327,9 @@ Status run_i8(const I8Call& c, const ComputeContext& ctx)
     if (need > 0) {
         g.workspace = st.take_raw(need);
         g.workspace_bytes = need;
+        if (g.workspace == nullptr) {
+            return Status::internal;
+        }
     }
 
     // Walk the broadcast batch; each slice is one 2-D call.

@@ -32,7 +32,8 @@ def _dev_array(v, dtype: torch.dtype, device: torch.device, count: int | None):
 def gemm_i8_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, out_kind: str, bias=None, relu=False,
                  activation="none", act_alpha=0.0, act_beta=1.0, min_clip=-math.inf, max_clip=math.inf,
                  scale_a=1.0, scale_w=1.0, zp_a=0, zp_w=0, out_scale=1.0, out_zp=0, workspace=None,
-                 engine="auto", r_w: torch.Tensor | None = None, keep: list | None = None) -> capi.GemmI8Args:
+                 engine="auto", r_w: torch.Tensor | None = None, min_workspace: bool = False,
+                 keep: list | None = None) -> capi.GemmI8Args:
     """Fill the C argument block.  ``a`` is [M,K] or [B,M,K] (s8/u8), ``w`` the LOGICAL [N,K]
     (or [B,N,K]) s8 matrix -- pass ``w_kn.transpose(-1,-2)`` for a weight stored [K,N].
     Tensors created for quantization arrays are appended to ``keep`` so they outlive the call."""
@@ -83,7 +84,9 @@ def gemm_i8_args(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, out_kin
         out_scale=float(out_scale), out_zp=int(out_zp),
         workspace=None, workspace_bytes=0, force_engine=capi.ENGINES[engine],
         r_w=r_w.data_ptr() if r_w is not None else None)
-    need = capi.lib().nnb200_gemm_i8_workspace_bytes(C.byref(args))
+    # min_workspace: only what the call cannot do without (no scratch for sharing K among SMs).
+    size_fn = capi.lib().nnb200_gemm_i8_min_workspace_bytes if min_workspace else capi.lib().nnb200_gemm_i8_workspace_bytes
+    need = size_fn(C.byref(args))
     if need:
         if workspace is None:
             workspace = torch.empty(need, dtype=torch.uint8, device=dev)

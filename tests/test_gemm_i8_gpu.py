@@ -18,7 +18,8 @@ pytestmark = pytest.mark.gpu
 
 def _run_case(dev, m, n, k, *, out_kind="s32", a_unsigned=False, relu=False, bias=True, per_token=False,
               per_channel=False, zero_points=False, out_scale=1.0, out_zp=0, engine="auto", seed=0,
-              expect_engine=None, act="none", min_clip=-np.inf, max_clip=np.inf):
+              expect_engine=None, act="none", min_clip=-np.inf, max_clip=np.inf, min_workspace=False,
+              expect_shared_k=None):
     rng = np.random.default_rng(seed)
     a = rng.integers(0, 256, (m, k), dtype=np.uint8) if a_unsigned else rng.integers(-127, 128, (m, k), dtype=np.int8)
     w = rng.integers(-127, 128, (n, k), dtype=np.int8)
@@ -39,8 +40,17 @@ def _run_case(dev, m, n, k, *, out_kind="s32", a_unsigned=False, relu=False, bia
     if expect_engine is not None:
         o = torch.empty((m, n), dtype=ops._OUT_TORCH[out_kind], device=dev)
         assert ops.gemm_i8_engine(ta, tw, o, engine=engine, **common) == expect_engine
+    if expect_shared_k is not None:
+        # The scratch for sharing K among the SMs is what the full workspace has over the minimum.
+        import ctypes
+        from nnops_b200 import capi
+        o = torch.empty((m, n), dtype=ops._OUT_TORCH[out_kind], device=dev)
+        probe = ops.gemm_i8_args(ta, tw, o, engine=engine, min_workspace=True, **common)
+        full = capi.lib().nnb200_gemm_i8_workspace_bytes(ctypes.byref(probe))
+        least = capi.lib().nnb200_gemm_i8_min_workspace_bytes(ctypes.byref(probe))
+        assert (full > least) == expect_shared_k
     got = ops.gemm_i8(ta, tw, relu=relu, activation=("relu" if relu and not int_out else act), engine=engine,
-                      min_clip=min_clip, max_clip=max_clip, **common)
+                      min_clip=min_clip, max_clip=max_clip, min_workspace=min_workspace, **common)
     torch.cuda.synchronize()
     got = got.cpu().numpy()
     assert got.shape == want.shape
@@ -121,6 +131,40 @@ def test_skinny_engine(cuda_device, nnb200_lib, m, out_kind):
               expect_engine="skinny", seed=m)
     _run_case(cuda_device, m, 4096, 4096, out_kind=out_kind, relu=True, per_channel=True, out_scale=1.3,
               expect_engine="skinny", seed=m + 1)
+
+
+@pytest.mark.parametrize("shape", [(1280, 16384), (11008, 4096), (28672, 1024), (2999, 8192 + 48), (19000, 2048)])
+@pytest.mark.parametrize("m", [9, 16, 33, 64, 100, 128])
+def test_skinny_engine_shared_k(cuda_device, nnb200_lib, monkeypatch, m, shape):
+    """Layers whose 128-channel tiles do not fill the SMs evenly: every SM takes an equal share
+    of all K blocks, tiles are finished by whichever part arrives last.  Few tiles with a long K
+    (a tile in a dozen parts), ragged N and K, zero points (both halves of the workspace in use),
+    and the same call with the minimum workspace (whole tiles per SM)."""
+    monkeypatch.setenv("NNB200_I8_SHARE_K", "2")   # offer the split for short shares too
+    n, k = shape
+    kinds = ["s32", "s8", "u8", "f32", "f16"]
+    out_kind = kinds[(m + n) % 5]
+    zp = (m + n // 7) % 2 == 0
+    for least in (False, True):
+        _run_case(cuda_device, m, n, k, out_kind=out_kind, a_unsigned=(m % 2 == 0), relu=True, per_token=True,
+                  per_channel=True, zero_points=zp, out_scale=90.0, out_zp=0 if out_kind == "s32" else 4,
+                  engine="skinny", expect_engine="skinny", seed=m + n, min_workspace=least, expect_shared_k=True)
+
+
+def test_skinny_engine_shared_k_by_default_on_long_streams(cuda_device, nnb200_lib):
+    _run_case(cuda_device, 12, 28672, 8192, out_kind="s8", per_channel=True, out_scale=90.0, expect_engine="skinny",
+              expect_shared_k=True, seed=5)
+    _run_case(cuda_device, 12, 11008, 4096, out_kind="s8", per_channel=True, out_scale=90.0, expect_engine="skinny",
+              expect_shared_k=False, seed=6)
+
+
+def test_skinny_engine_shared_k_not_offered_when_tiles_fill_the_sms(cuda_device, nnb200_lib, monkeypatch):
+    monkeypatch.setenv("NNB200_I8_SHARE_K", "2")
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    _run_case(cuda_device, 24, 128 * sms, 2048, out_kind="s8", per_channel=True, out_scale=40.0, engine="skinny",
+              expect_engine="skinny", expect_shared_k=False)
+    _run_case(cuda_device, 24, 640, 512, out_kind="s8", per_channel=True, out_scale=40.0, engine="skinny",
+              expect_engine="skinny", expect_shared_k=False)
 
 
 def test_skinny_engine_small_m_on_request(cuda_device, nnb200_lib):
