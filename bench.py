@@ -526,7 +526,7 @@ def main():
             "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "shards": world,
                        "reassembly": "none" if world == 1 else (
                            "fused: GEMM epilogue stores each tile into every rank's output over NVLink (P2P), "
-                           "then a 1-element all-reduce orders the ranks" if layer.mode == "fused"
+                           "then a device-side flag barrier over peer memory orders the ranks" if layer.mode == "fused"
                            else "nccl all-gather + interleave kernel"),
                        "l2": "inputs (268 MB) exceed L2 (126 MB); no flush needed"},
             "clocks": clocks,

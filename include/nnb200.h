@@ -289,6 +289,24 @@ NNB200_API int nnb200_interleave_shards(const void* gathered, void* out, int64_t
                                         int32_t shards, int64_t out_pitch_bytes, void* stream);
 
 /*
+ * Device-side barrier among the GPUs of one node, for ordering the ranks after the sharded
+ * write-back without a collective: flags_by_rank[r] is rank r's flag array -- NNB200_RANK_FLAG_BYTES
+ * bytes from nnb200_peer_buffer_alloc, zeroed once, rank r's own for r == rank and the mapping
+ * from nnb200_peer_buffer_open for the others.  The kernel (one warp) advances this rank's
+ * epoch, which lives in its flag array so that a captured launch stays valid on replay, writes
+ * it into every other rank's array and polls its own array until every other rank has done the
+ * same.  Every rank must call it the same number of times.  Work enqueued on the stream after
+ * it sees everything the other ranks' streams had completed before their call.  The wait is
+ * bounded by limit_cycles SM clock cycles (0 = the library's default, about two seconds): when
+ * it runs out the kernel records code 8 in the error word (nnb200_take_device_error) and
+ * returns.  world <= 8.  No counterpart in the reference, which has no multi-GPU code.
+ */
+#define NNB200_RANK_FLAG_BYTES 64
+#define NNB200_DEVICE_ERROR_PEER_WAIT 8
+NNB200_API int nnb200_rank_barrier(int32_t* const* flags_by_rank, int32_t world, int32_t rank, int64_t limit_cycles,
+                                   void* stream);
+
+/*
  * Kernels never spin forever: a pipeline wait that runs out records a code in a per-device
  * error word and the kernel exits.  This synchronises the device, returns that word through
  * *code (0 = no error) and clears it.

@@ -104,6 +104,7 @@ SYMBOLS = [
     ("nnb200_dequantize_linear", C.c_int, [C.POINTER(QuantLinearArgs), C.c_void_p]),
     ("nnb200_interleave_shards", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64,
                                            C.c_void_p]),
+    ("nnb200_rank_barrier", C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int64, C.c_void_p]),
     ("nnb200_take_device_error", C.c_int, [C.POINTER(C.c_int32)]),
     ("nnb200_selftest_wait_limit", C.c_int, [C.c_int64, C.c_void_p]),
     ("nnb200_copy_h2d_async", C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
@@ -159,6 +160,8 @@ def take_device_error() -> int:
 
 
 DEVICE_ERROR_SELFTEST = 7
+DEVICE_ERROR_PEER_WAIT = 8
+RANK_FLAG_BYTES = 64
 
 
 def selftest_wait_limit(limit_cycles: int = 2_000_000, stream=None) -> None:

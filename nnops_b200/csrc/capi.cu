@@ -584,6 +584,23 @@ int nnb200_interleave_shards(const void* gathered, void* out, int64_t m, int64_t
                                     static_cast<cudaStream_t>(stream));
 }
 
+int nnb200_rank_barrier(int32_t* const* flags_by_rank, int32_t world, int32_t rank, int64_t limit_cycles, void* stream)
+{
+    if (flags_by_rank == nullptr || world < 1 || world > 8 || rank < 0 || rank >= world || limit_cycles < 0) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    for (int r = 0; r < world; ++r) {
+        if (flags_by_rank[r] == nullptr || (reinterpret_cast<uintptr_t>(flags_by_rank[r]) & 3u) != 0) {
+            return NNB200_INVALID_ARGUMENT;
+        }
+    }
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    return launch_rank_barrier(flags_by_rank, world, rank, limit_cycles, *dev, static_cast<cudaStream_t>(stream));
+}
+
 int nnb200_take_device_error(int32_t* code)
 {
     const DeviceInfo* dev = current_device_info();

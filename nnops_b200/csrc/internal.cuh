@@ -86,6 +86,10 @@ int64_t i8_pack_pitch(int64_t k);
 int launch_i8_pack(const void* w, int64_t n, int64_t k, int64_t stride_n, int64_t stride_k, const float* scale_w,
                    float scale_scalar, const int32_t* zp_w, int32_t zp_scalar, void* blob, cudaStream_t stream);
 
+// Device-side barrier among up to 8 GPUs: flags_by_rank[r] is rank r's flag array (int32[16],
+// zeroed once), mapped into this process; limit_cycles <= 0 means the default wait limit.
+int launch_rank_barrier(int32_t* const* flags_by_rank, int world, int rank, long long limit_cycles,
+                        const DeviceInfo& dev, cudaStream_t stream);
 int launch_interleave_shards(const void* src, void* dst, int64_t m, int64_t row_bytes_per_shard, int g,
                              int64_t dst_pitch_bytes, const DeviceInfo& dev, cudaStream_t stream);
 

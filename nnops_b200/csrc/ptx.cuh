@@ -20,6 +20,7 @@ enum DeviceError : int32_t {
     kErrDequantWait = 5,   // Q4_1 dequant warps timed out
     kErrDrainWait = 6,     // teardown timed out waiting for copies in flight
     kErrSelfTest = 7,      // the wait self-test's barrier ran out, as it must
+    kErrPeerWait = 8,      // the device-side rank barrier timed out waiting for another GPU's flag
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)

@@ -7,6 +7,7 @@
 // (The reference has no multi-GPU code; this sits above its operator API.)
 
 #include "internal.cuh"
+#include "ptx.cuh"
 
 namespace nnb200 {
 
@@ -27,7 +28,68 @@ __global__ void __launch_bounds__(256) interleave_shards_kernel(const uint4* __r
     }
 }
 
+// Flags of one rank: slot r holds the last epoch rank r announced here, slot kEpochSlot this
+// rank's own call count.
+constexpr int kEpochSlot = 8;
+
+struct RankFlags {
+    int32_t* by_rank[8];
+};
+
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v)
+{
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p)
+{
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One warp per GPU.  Lane 0 advances this rank's epoch; lane r (r != rank) announces it in rank
+// r's flag array and then polls the local slot r until rank r has announced the same epoch.
+// The epoch lives in device memory, so a captured launch stays valid on replay.  The wait is
+// bounded: on expiry the lane records kErrPeerWait and the kernel returns.
+__global__ void rank_barrier_kernel(const RankFlags flags, const int world, const int rank, const long long limit_cycles,
+                                    int32_t* error_word)
+{
+    const int lane = static_cast<int>(threadIdx.x);
+    int32_t* mine = flags.by_rank[rank];
+    int32_t epoch = 0;
+    if (lane == 0) {
+        epoch = mine[kEpochSlot] + 1;
+        mine[kEpochSlot] = epoch;
+    }
+    epoch = __shfl_sync(0xFFFFFFFFu, epoch, 0);
+    if (lane < world && lane != rank) {
+        st_release_sys(flags.by_rank[lane] + rank, epoch);
+        const long long t0 = clock64();
+        uint32_t spins = 0;
+        while (static_cast<int32_t>(static_cast<uint32_t>(ld_acquire_sys(mine + lane)) - static_cast<uint32_t>(epoch)) < 0) {
+            if ((++spins & 0x3Fu) == 0 && clock64() - t0 > limit_cycles) {
+                atomicCAS(error_word, 0, kErrPeerWait);
+                break;
+            }
+        }
+    }
+}
+
 }  // namespace
+
+int launch_rank_barrier(int32_t* const* flags_by_rank, int world, int rank, long long limit_cycles,
+                        const DeviceInfo& dev, cudaStream_t stream)
+{
+    RankFlags f;
+    for (int r = 0; r < 8; ++r) {
+        f.by_rank[r] = r < world ? flags_by_rank[r] : nullptr;
+    }
+    rank_barrier_kernel<<<1, 32, 0, stream>>>(f, world, rank, limit_cycles > 0 ? limit_cycles : kWaitLimitCycles,
+                                              dev.error_word);
+    note_launch();
+    return cuda_status(cudaGetLastError());
+}
 
 int launch_interleave_shards(const void* src, void* dst, int64_t m, int64_t row_bytes_per_shard, int g,
                              int64_t dst_pitch_bytes, const DeviceInfo& dev, cudaStream_t stream)

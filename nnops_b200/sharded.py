@@ -12,9 +12,11 @@ Two ways to put the full row-major [M,N] output on every rank:
 * ``mode="fused"`` -- the outputs are allocated with ``alloc_outputs`` (every rank maps every
   other rank's copy through CUDA IPC); the GEMM's epilogue then stores each finished tile into
   all g copies at once with peer-to-peer stores, so the all-gather overlaps the math tile by
-  tile and no separate collective or re-layout pass runs.  Ranks are ordered by a one-element
-  NCCL all-reduce after the GEMM (and optionally before it, when a consumer of the previous
-  result may still be reading).  Kernels only ever LOAD local memory.
+  tile and no separate collective or re-layout pass runs.  Ranks are ordered after the GEMM
+  (and optionally before it, when a consumer of the previous result may still be reading) by
+  the library's device-side barrier -- every rank writes an epoch into every other rank's flag
+  array and polls its own, with a bounded wait -- or, with ``rank_order="nccl"``, by a
+  one-element all-reduce.  Kernels only ever LOAD local memory, except for that flag polling.
 
 The reference has no multi-GPU code; this layer sits above its operator API, one operator
 instance per GPU.
@@ -66,7 +68,7 @@ class ShardedLinearI8:
 
     def __init__(self, w_shard: torch.Tensor, *, n_total: int, world: int, rank: int, group=None,
                  out_kind: str = "s8", bias_shard=None, scale_w_shard=1.0, scale_a=1.0, out_scale=1.0, out_zp=0,
-                 relu: bool = False, mode: str = "nccl"):
+                 relu: bool = False, mode: str = "nccl", rank_order: str = "device"):
         lo, hi = shard_bounds(n_total, world, rank)
         if w_shard.shape[0] != hi - lo:
             raise ValueError("weight shard has the wrong number of rows")
@@ -86,6 +88,10 @@ class ShardedLinearI8:
         self._peer_ptrs: dict = {}    # local output data_ptr -> addresses of the other ranks' copies, mapped here
         self._owners: list = []
         self._token = None
+        if rank_order not in ("device", "nccl"):
+            raise ValueError("rank_order must be 'device' or 'nccl'")
+        self.rank_order = rank_order     # how fused mode orders the ranks after the write-back
+        self._flags = None
 
     # ---- outputs -------------------------------------------------------------------------
 
@@ -123,15 +129,51 @@ class ShardedLinearI8:
                         mapped.append(p.value)
                 self._peer_ptrs[t.data_ptr()] = mapped
         self._token = torch.zeros(1, dtype=torch.int32, device=dev)
+        if self.rank_order == "device" and self._flags is None:
+            self._map_flags()
         dist.barrier(group=self.group)                   # every rank has mapped everything
         return outs
 
+    def _map_flags(self) -> None:
+        """Flag arrays of the device-side rank barrier: one per rank, zeroed, mapped by every rank."""
+        dev = self.w.device
+        lib = capi.lib()
+        ptr = C.c_void_p()
+        capi.check(lib.nnb200_peer_buffer_alloc(C.byref(ptr), capi.RANK_FLAG_BYTES), "nnb200_peer_buffer_alloc")
+        owner = _DeviceBuffer(ptr.value, (capi.RANK_FLAG_BYTES,), "u8")
+        torch.as_tensor(owner, device=dev).zero_()
+        torch.cuda.synchronize(dev)
+        self._owners.append(owner)
+        h = C.create_string_buffer(64)
+        capi.check(lib.nnb200_peer_buffer_export(ptr, h), "nnb200_peer_buffer_export")
+        everyone: list = [None] * self.world
+        dist.all_gather_object(everyone, h.raw, group=self.group)
+        table = (C.c_void_p * self.world)()
+        for r in range(self.world):
+            if r == self.rank:
+                table[r] = ptr.value
+            else:
+                p = C.c_void_p()
+                capi.check(lib.nnb200_peer_buffer_open(everyone[r], C.byref(p)), "nnb200_peer_buffer_open")
+                table[r] = p.value
+        self._flags = table
+
     def rank_barrier(self) -> None:
-        """Order the ranks on the current stream (one-element all-reduce)."""
-        if self.world > 1:
-            if self._token is None:
-                self._token = torch.zeros(1, dtype=torch.int32, device=self.w.device)
-            dist.all_reduce(self._token, group=self.group)
+        """Order the ranks on the current stream: the library's device-side barrier (flags written
+        into each other's memory) once ``alloc_outputs`` has mapped the flag arrays, else a
+        one-element all-reduce."""
+        if self.world <= 1:
+            return
+        if self._flags is not None:
+            dev = self.w.device
+            with torch.cuda.device(dev):
+                capi.check(capi.lib().nnb200_rank_barrier(self._flags, self.world, self.rank, 0,
+                                                          torch.cuda.current_stream(dev).cuda_stream),
+                           "nnb200_rank_barrier")
+            return
+        if self._token is None:
+            self._token = torch.zeros(1, dtype=torch.int32, device=self.w.device)
+        dist.all_reduce(self._token, group=self.group)
 
     # ---- compute -------------------------------------------------------------------------
 

@@ -47,15 +47,18 @@ def _rank_body(rank, world, m, n, k, mode, q, dev):
             rank=rank, out_kind="s8", relu=True, scale_a=c.scale_a, out_scale=c.out_scale,
             bias_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.bias, world, rank))).to(dev),
             scale_w_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.scale_w, world, rank))).to(dev),
-            mode=mode)
+            mode="fused" if mode.startswith("fused") else mode,
+            rank_order="nccl" if mode == "fused-nccl-order" else "device")
         a = torch.from_numpy(c.a).to(dev)
-        if mode == "fused":
+        if mode.startswith("fused"):
             outs = layer.alloc_outputs(m, count=2)                           # peer-mapped on every rank
             for o in outs:
                 o.fill_(0x5A)
             torch.cuda.synchronize()
             dist.barrier()
-            for i in range(4):                                               # alternate buffers, reuse them
+            for i in range(12):                                              # alternate buffers, reuse them
+                if rank == i % world:
+                    torch.cuda._sleep(2_000_000)                             # a different straggler every round
                 layer.forward(a, outs[i & 1], wait_for_readers=True)
             torch.cuda.synchronize()
             assert torch.equal(outs[0], outs[1])
@@ -71,7 +74,7 @@ def _rank_body(rank, world, m, n, k, mode, q, dev):
         q.put((rank, result.cpu().numpy()))
 
 
-@pytest.mark.parametrize("mode", ["nccl", "fused"])
+@pytest.mark.parametrize("mode", ["nccl", "fused", "fused-nccl-order"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_sharded_matches_single_gpu(nnb200_lib, world, mode):
     if torch.cuda.device_count() < world:

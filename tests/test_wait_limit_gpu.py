@@ -41,3 +41,55 @@ def test_wait_limit_argument_checked(nnb200_lib):
         with pytest.raises(capi.Nnb200Error):
             capi.selftest_wait_limit(bad, None)
     assert capi.take_device_error() == 0
+
+
+def _flag_arrays(dev, count):
+    import ctypes as C
+    from nnops_b200 import capi
+    arrays = [torch.zeros(capi.RANK_FLAG_BYTES // 4, dtype=torch.int32, device=dev) for _ in range(count)]
+    table = (C.c_void_p * count)(*[t.data_ptr() for t in arrays])
+    return arrays, table
+
+
+def test_rank_barrier_protocol_on_one_gpu(nnb200_lib):
+    """The device-side rank barrier, two ranks' flag arrays on one GPU, launches strictly one
+    after the other (kernels that wait for each other never run side by side on one GPU):
+    rank 1 announces epoch 1 and, with nobody answering, gives up after a millisecond with code
+    8; rank 0 then finds rank 1's epoch already there and passes at once; so does rank 1's
+    second call, because rank 0 is now one epoch ahead of what it needs."""
+    from nnops_b200 import capi
+
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    arrays, table = _flag_arrays(dev, 2)
+    lib = capi.lib()
+    short = 2_000_000
+
+    capi.check(lib.nnb200_rank_barrier(table, 2, 1, short, stream), "nnb200_rank_barrier")
+    assert capi.take_device_error() == capi.DEVICE_ERROR_PEER_WAIT
+    assert arrays[0][1].item() == 1 and arrays[1][8].item() == 1     # announced at rank 0; own epoch advanced
+
+    capi.check(lib.nnb200_rank_barrier(table, 2, 0, short, stream), "nnb200_rank_barrier")
+    assert capi.take_device_error() == 0
+    assert arrays[1][0].item() == 1 and arrays[0][8].item() == 1
+
+    capi.check(lib.nnb200_rank_barrier(table, 2, 0, short, stream), "nnb200_rank_barrier")   # rank 0: epoch 2, alone
+    assert capi.take_device_error() == capi.DEVICE_ERROR_PEER_WAIT
+    capi.check(lib.nnb200_rank_barrier(table, 2, 1, short, stream), "nnb200_rank_barrier")   # rank 1: epoch 2, answered
+    assert capi.take_device_error() == 0
+
+    # A world of one has nobody to wait for.
+    solo, solo_table = _flag_arrays(dev, 1)
+    capi.check(lib.nnb200_rank_barrier(solo_table, 1, 0, short, stream), "nnb200_rank_barrier")
+    assert capi.take_device_error() == 0 and solo[0][8].item() == 1
+
+
+def test_rank_barrier_arguments_checked(nnb200_lib):
+    from nnops_b200 import capi
+
+    dev = torch.device("cuda:0")
+    _, table = _flag_arrays(dev, 2)
+    lib = capi.lib()
+    for world, rank in ((0, 0), (9, 0), (2, 2), (2, -1)):
+        assert lib.nnb200_rank_barrier(table, world, rank, 0, None) != capi.OK
+    assert capi.take_device_error() == 0
