@@ -162,21 +162,29 @@ int pick_i8_engine(const nnb200_gemm_i8_args* a, const I8Problem& p)
     if (a->force_engine == NNB200_ENGINE_SKINNY) {
         return (a->num_peer_outs == 0 && skinny_i8_supported(p)) ? NNB200_ENGINE_SKINNY : NNB200_ENGINE_GENERIC;
     }
-    // Few activation rows: the cost is streaming W once.  Measured on N=28672,K=8192 / N=11008,K=4096:
-    // up to 8 rows the streaming warp-MMA engine wins (0.82-0.90 / 0.57-0.64 of HBM speed); from 9
-    // rows the tensor-core engine with the weights as the 128-row operand does (0.73-0.76 / 0.44-0.47
-    // up to 32 rows), until the square engine's wider tiles pay again: above 64 rows when the
-    // layer has enough 256-channel tiles for half the SMs.
+    // Few activation rows: the cost is streaming W once, and what decides is how evenly an engine
+    // spreads that stream over the SMs.  Measured (us) on N=28672,K=8192 / 14336,4096 / 11008,4096 /
+    // 4096,4096:
+    //   * up to 8 rows the streaming warp-MMA engine (16 channels per CTA) wins everywhere;
+    //   * 9..16 rows: it still wins while the layer has at most 96 tiles of 128 channels
+    //     (14.9 against 16.0 / 7.8 against 15.1 on the last two), beyond that the tensor-core engine
+    //     with the weights as the 128-row operand does (16.7 against 20.7 / 46.9 against 58);
+    //   * 17..128 rows: a layer with so few channels that even 64-wide tiles of the square engine
+    //     leave SMs idle is served best by exactly those (4096 channels: 13.5 against 15.9..22.7);
+    //     otherwise weights-as-rows up to 64 rows, and above while the layer has 256-channel tiles
+    //     for less than half the SMs.
     if (a->num_peer_outs == 0) {
         const bool decode_ok = decode_i8_supported(p);
         const bool skinny_ok = skinny_i8_supported(p);
-        if (decode_ok && (p.m <= 8 || !skinny_ok)) {
+        const DeviceInfo* dev = current_device_info();
+        const int64_t sms = dev != nullptr ? dev->sm_count : 148;
+        const int64_t tiles128 = (p.n + 127) / 128;
+        if (decode_ok && (p.m <= 8 || !skinny_ok || tiles128 <= 96)) {
             return NNB200_ENGINE_DECODE;
         }
         if (skinny_ok) {
-            const DeviceInfo* dev = current_device_info();
-            const int64_t sms = dev != nullptr ? dev->sm_count : 148;
-            if (p.m <= 64 || (p.n + 255) / 256 < sms / 2) {
+            const bool narrow_layer = p.m > 16 && (p.n + 63) / 64 <= sms;
+            if (!narrow_layer && (p.m <= 64 || (p.n + 255) / 256 < sms / 2)) {
                 return NNB200_ENGINE_SKINNY;
             }
         }

@@ -99,10 +99,10 @@ def test_fp_clip(cuda_device, nnb200_lib):
 
 @pytest.mark.parametrize("m", [1, 2, 3, 8, 9, 16])
 def test_decode_engines(cuda_device, nnb200_lib, m):
-    """M <= 16: up to 8 rows the streaming warp-MMA engine (K a multiple of 64), from 9 rows -- or
-    for any other K -- the tensor-core engine with the weights as the 128-row operand; the dp4a
-    engine on request."""
-    few = "decode" if m <= 8 else "skinny"
+    """M <= 16 on a layer of modest width: the streaming warp-MMA engine (K a multiple of 64); for
+    any other K the tensor-core engine with the weights as the 128-row operand; the dp4a engine
+    on request."""
+    few = "decode"
     _run_case(cuda_device, m, 520, 1024, out_kind="s8", relu=True, per_channel=True, out_scale=1.1,
               expect_engine=few, seed=m)
     _run_case(cuda_device, m, 520, 1024, out_kind="s8", relu=True, per_channel=True, out_scale=1.1,
@@ -128,9 +128,9 @@ def test_skinny_engine(cuda_device, nnb200_lib, m, out_kind):
     out transposed.  Ragged N and K, u8 activations, zero points, every destination."""
     _run_case(cuda_device, m, 1003, 528, out_kind=out_kind, a_unsigned=(m % 2 == 0), relu=True, per_token=True,
               per_channel=True, zero_points=True, out_scale=1.9, out_zp=0 if out_kind == "s32" else 4,
-              expect_engine="skinny", seed=m)
+              engine="skinny", expect_engine="skinny", seed=m)
     _run_case(cuda_device, m, 4096, 4096, out_kind=out_kind, relu=True, per_channel=True, out_scale=1.3,
-              expect_engine="skinny", seed=m + 1)
+              engine="skinny", expect_engine="skinny", seed=m + 1)
 
 
 @pytest.mark.parametrize("shape", [(1280, 16384), (11008, 4096), (28672, 1024), (2999, 8192 + 48), (19000, 2048)])
@@ -154,8 +154,8 @@ def test_skinny_engine_shared_k(cuda_device, nnb200_lib, monkeypatch, m, shape):
 def test_skinny_engine_shared_k_by_default_on_long_streams(cuda_device, nnb200_lib):
     _run_case(cuda_device, 12, 28672, 8192, out_kind="s8", per_channel=True, out_scale=90.0, expect_engine="skinny",
               expect_shared_k=True, seed=5)
-    _run_case(cuda_device, 12, 11008, 4096, out_kind="s8", per_channel=True, out_scale=90.0, expect_engine="skinny",
-              expect_shared_k=False, seed=6)
+    _run_case(cuda_device, 12, 11008, 4096, out_kind="s8", per_channel=True, out_scale=90.0, engine="skinny",
+              expect_engine="skinny", expect_shared_k=False, seed=6)
 
 
 def test_skinny_engine_shared_k_not_offered_when_tiles_fill_the_sms(cuda_device, nnb200_lib, monkeypatch):
@@ -165,6 +165,16 @@ def test_skinny_engine_shared_k_not_offered_when_tiles_fill_the_sms(cuda_device,
               expect_engine="skinny", expect_shared_k=False)
     _run_case(cuda_device, 24, 640, 512, out_kind="s8", per_channel=True, out_scale=40.0, engine="skinny",
               expect_engine="skinny", expect_shared_k=False)
+
+
+@pytest.mark.parametrize("case", [(8, 28672, 1024, "decode"), (12, 4096, 1024, "decode"), (16, 12288, 512, "decode"),
+                                  (12, 14336, 512, "skinny"), (16, 28672, 512, "skinny"), (24, 4096, 1024, "umma"),
+                                  (100, 9472, 512, "umma"), (24, 11008, 512, "skinny"), (64, 28672, 512, "skinny"),
+                                  (100, 11008, 512, "skinny"), (100, 28672, 512, "umma"), (129, 11008, 512, "umma")])
+def test_few_row_engine_choice(cuda_device, nnb200_lib, case):
+    """The measured crossovers between the streaming engine, weights-as-rows and the square engine."""
+    m, n, k, want = case
+    _run_case(cuda_device, m, n, k, out_kind="s8", per_channel=True, out_scale=30.0, expect_engine=want, seed=m + n)
 
 
 def test_skinny_engine_small_m_on_request(cuda_device, nnb200_lib):

@@ -40,38 +40,37 @@ def _rank_body(rank, world, m, n, k, mode, q, dev):
     import torch.distributed as dist
     from nnops_b200 import capi, synth
     from nnops_b200.sharded import ShardedLinearI8, shard_rows
-    if True:
-        c = synth.config2(m=m, n=n, k=k, out_scale=1.6)
-        layer = ShardedLinearI8(
-            torch.from_numpy(np.ascontiguousarray(shard_rows(c.w, world, rank))).to(dev), n_total=n, world=world,
-            rank=rank, out_kind="s8", relu=True, scale_a=c.scale_a, out_scale=c.out_scale,
-            bias_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.bias, world, rank))).to(dev),
-            scale_w_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.scale_w, world, rank))).to(dev),
-            mode="fused" if mode.startswith("fused") else mode,
-            rank_order="nccl" if mode == "fused-nccl-order" else "device")
-        a = torch.from_numpy(c.a).to(dev)
-        if mode.startswith("fused"):
-            outs = layer.alloc_outputs(m, count=2)                           # peer-mapped on every rank
-            for o in outs:
-                o.fill_(0x5A)
-            torch.cuda.synchronize()
-            dist.barrier()
-            for i in range(12):                                              # alternate buffers, reuse them
-                if rank == i % world:
-                    torch.cuda._sleep(2_000_000)                             # a different straggler every round
-                layer.forward(a, outs[i & 1], wait_for_readers=True)
-            torch.cuda.synchronize()
-            assert torch.equal(outs[0], outs[1])
-            result = torch.full((m, n + 32), 0x5A, dtype=torch.int8, device=dev)
-            result[:, :n] = outs[1]
-        else:
-            result = torch.full((m, n + 32), 0x5A, dtype=torch.int8, device=dev)   # pitched destination
-            for _ in range(2):                                                      # twice: buffers are reused
-                layer.forward(a, result[:, :n])
+    c = synth.config2(m=m, n=n, k=k, out_scale=1.6)
+    layer = ShardedLinearI8(
+        torch.from_numpy(np.ascontiguousarray(shard_rows(c.w, world, rank))).to(dev), n_total=n, world=world,
+        rank=rank, out_kind="s8", relu=True, scale_a=c.scale_a, out_scale=c.out_scale,
+        bias_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.bias, world, rank))).to(dev),
+        scale_w_shard=torch.from_numpy(np.ascontiguousarray(shard_rows(c.scale_w, world, rank))).to(dev),
+        mode="fused" if mode.startswith("fused") else mode,
+        rank_order="nccl" if mode == "fused-nccl-order" else "device")
+    a = torch.from_numpy(c.a).to(dev)
+    if mode.startswith("fused"):
+        outs = layer.alloc_outputs(m, count=2)                           # peer-mapped on every rank
+        for o in outs:
+            o.fill_(0x5A)
         torch.cuda.synchronize()
-        assert capi.take_device_error() == 0
         dist.barrier()
-        q.put((rank, result.cpu().numpy()))
+        for i in range(12):                                              # alternate buffers, reuse them
+            if rank == i % world:
+                torch.cuda._sleep(2_000_000)                             # a different straggler every round
+            layer.forward(a, outs[i & 1], wait_for_readers=True)
+        torch.cuda.synchronize()
+        assert torch.equal(outs[0], outs[1])
+        result = torch.full((m, n + 32), 0x5A, dtype=torch.int8, device=dev)
+        result[:, :n] = outs[1]
+    else:
+        result = torch.full((m, n + 32), 0x5A, dtype=torch.int8, device=dev)   # pitched destination
+        for _ in range(2):                                                      # twice: buffers are reused
+            layer.forward(a, result[:, :n])
+    torch.cuda.synchronize()
+    assert capi.take_device_error() == 0
+    dist.barrier()
+    q.put((rank, result.cpu().numpy()))
 
 
 @pytest.mark.parametrize("mode", ["nccl", "fused", "fused-nccl-order"])
