@@ -241,21 +241,58 @@ size_t nnb200_gemm_i8_min_workspace_bytes(const nnb200_gemm_i8_args* a)
     return static_cast<size_t>(a->batch) * (ra + rw);
 }
 
-// Scratch that lets the few-row tensor-core engine split K evenly over all SMs (optional).
-static size_t i8_split_bytes(const nnb200_gemm_i8_args* a)
+// Scratch that lets the few-row tensor-core engine share K evenly among all SMs (optional), and
+// whether having it changes the engine: on a layer with so few channels that the square engine
+// was chosen for its narrow tiles (17..128 rows), weights-as-rows with shared K is faster still
+// when K is long (N=4096, K=14336, 24 rows: 24.4 against 35.9 us) -- but only with the scratch.
+struct I8SplitPlan {
+    size_t bytes;         // scratch wanted beyond the required minimum (0 = no use for it)
+    bool switches_engine; // with the scratch the call runs on the weights-as-rows engine instead
+};
+
+static I8SplitPlan i8_split_plan(const nnb200_gemm_i8_args* a)
 {
+    I8SplitPlan plan{0, false};
     if (a->batch != 1 || a->num_peer_outs != 0) {
-        return 0;
+        return plan;
     }
     const DeviceInfo* dev = current_device_info();
     if (dev == nullptr) {
-        return 0;
+        return plan;
     }
     const I8Problem p = problem_of(a, 0);
-    if (pick_i8_engine(a, p) != NNB200_ENGINE_SKINNY) {
-        return 0;
+    const int engine = pick_i8_engine(a, p);
+    if (engine == NNB200_ENGINE_SKINNY) {
+        plan.bytes = skinny_i8_split_bytes(p, *dev);
+    } else if (engine == NNB200_ENGINE_UMMA && a->force_engine == NNB200_ENGINE_AUTO && p.m >= 17 && p.m <= 128) {
+        plan.bytes = skinny_i8_split_bytes(p, *dev);  // 0 unless weights-as-rows is supported and the split pays
+        plan.switches_engine = plan.bytes > 0;
     }
-    return skinny_i8_split_bytes(p, *dev);
+    return plan;
+}
+
+// The part of the caller's workspace that serves the split, or null when it is absent, too small or misaligned.
+static void* i8_split_scratch(const nnb200_gemm_i8_args* a, size_t required, size_t split_bytes)
+{
+    if (split_bytes == 0 || a->workspace == nullptr || a->workspace_bytes < required + split_bytes ||
+        ((reinterpret_cast<uintptr_t>(a->workspace) + required) & 15u) != 0) {
+        return nullptr;
+    }
+    return static_cast<uint8_t*>(a->workspace) + required;
+}
+
+// Engine of batch element 0 given the workspace the block carries.
+static int i8_engine_with_workspace(const nnb200_gemm_i8_args* a, void** split_scratch)
+{
+    const I8SplitPlan plan = i8_split_plan(a);
+    void* scratch = i8_split_scratch(a, nnb200_gemm_i8_min_workspace_bytes(a), plan.bytes);
+    if (split_scratch != nullptr) {
+        *split_scratch = scratch;
+    }
+    if (plan.switches_engine && scratch != nullptr) {
+        return NNB200_ENGINE_SKINNY;
+    }
+    return pick_i8_engine(a, problem_of(a, 0));
 }
 
 size_t nnb200_gemm_i8_workspace_bytes(const nnb200_gemm_i8_args* a)
@@ -263,7 +300,7 @@ size_t nnb200_gemm_i8_workspace_bytes(const nnb200_gemm_i8_args* a)
     if (!valid_i8_args(a) || a->m == 0 || a->n == 0 || a->batch == 0) {
         return 0;
     }
-    return nnb200_gemm_i8_min_workspace_bytes(a) + i8_split_bytes(a);
+    return nnb200_gemm_i8_min_workspace_bytes(a) + i8_split_plan(a).bytes;
 }
 
 int nnb200_gemm_i8_engine(const nnb200_gemm_i8_args* a)
@@ -271,7 +308,10 @@ int nnb200_gemm_i8_engine(const nnb200_gemm_i8_args* a)
     if (!valid_i8_args(a)) {
         return -1;
     }
-    return pick_i8_engine(a, problem_of(a, 0));
+    if (a->m == 0 || a->n == 0 || a->batch == 0) {
+        return pick_i8_engine(a, problem_of(a, 0));
+    }
+    return i8_engine_with_workspace(a, nullptr);
 }
 
 int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
@@ -295,13 +335,10 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
     if (need > 0 && (a->workspace == nullptr || a->workspace_bytes < need)) {
         return NNB200_INVALID_ARGUMENT;
     }
-    // The rest of the workspace, when there is enough of it, lets the few-row engine split K.
-    const size_t split_bytes = i8_split_bytes(a);
+    // The rest of the workspace, when there is enough of it, lets the few-row engine share K
+    // among the SMs (and on narrow layers with a long K makes it the engine of choice).
     void* split_scratch = nullptr;
-    if (split_bytes > 0 && a->workspace != nullptr && a->workspace_bytes >= need + split_bytes &&
-        ((reinterpret_cast<uintptr_t>(a->workspace) + need) & 15u) == 0) {
-        split_scratch = static_cast<uint8_t*>(a->workspace) + need;
-    }
+    const int engine0 = i8_engine_with_workspace(a, &split_scratch);
     const size_t ra_bytes = (static_cast<size_t>(a->m) * 4 + 255) & ~size_t(255);
     const size_t rw_bytes = (static_cast<size_t>(a->n) * 4 + 255) & ~size_t(255);
 
@@ -364,7 +401,7 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
             ep.r_w = have_rw ? a->r_w : r_w;
         }
         int st;
-        switch (pick_i8_engine(a, p)) {
+        switch (a->batch == 1 ? engine0 : pick_i8_engine(a, p)) {
         case NNB200_ENGINE_UMMA: st = launch_gemm_i8_umma(p, ep, *dev, stream); break;
         case NNB200_ENGINE_NARROW: st = launch_gemm_i8_narrow(p, ep, *dev, stream); break;
         case NNB200_ENGINE_DECODE: st = launch_gemm_i8_decode(p, ep, *dev, stream); break;

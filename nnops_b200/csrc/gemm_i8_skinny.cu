@@ -32,6 +32,8 @@
 //     independent of who came last.  The protocol runs per warp (a warp owns 32 channels of the
 //     tile in every CTA), so it needs no CTA-wide barrier.
 
+#include <atomic>
+#include <chrono>
 #include <cstdlib>
 #include <mutex>
 
@@ -75,10 +77,10 @@ __device__ __forceinline__ int cta_of_unit(int64_t u, int grid, int64_t total_un
     return static_cast<int>(((u + 1) * grid - 1) / total_units);
 }
 
-// Bytes of the per-tile, per-warp arrival counters at the head of the split scratch.
+// Bytes of the per-tile, per-warp arrival words at the head of the split scratch.
 __host__ __device__ inline size_t split_counter_bytes(int num_tiles)
 {
-    return (static_cast<size_t>(num_tiles) * 4 * sizeof(int32_t) + 255) & ~size_t(255);
+    return (static_cast<size_t>(num_tiles) * 4 * sizeof(unsigned long long) + 255) & ~size_t(255);
 }
 
 // One piece of a CTA's range: K blocks [kb0, kb1) of `tile`.
@@ -142,26 +144,43 @@ struct SegmentList {
     }
 };
 
-__device__ __forceinline__ int ld_acquire_gpu(const int32_t* p)
+// Arrival words.  The scratch arrives with arbitrary contents and nothing clears it: a word is
+// (call tag << 8) | count, the tag unique to this launch, and a word carrying any other tag
+// counts as zero.  The warp that finishes a tile writes (tag << 8) | 0 back, so that a replay of
+// a captured launch -- same tag -- starts from zero as well.
+__device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned long long* p)
 {
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
 
-__global__ void zero_words_kernel(int32_t* p, int n)
+__device__ __forceinline__ int arrivals_of(unsigned long long word, unsigned long long tag)
 {
-    const int i = static_cast<int>(blockIdx.x * blockDim.x + threadIdx.x);
-    if (i < n) {
-        p[i] = 0;
+    return (word >> 8) == tag ? static_cast<int>(word & 0xFFu) : 0;
+}
+
+// Count this part in; returns how many parts had arrived before it (-1 if the bounded retry ran out).
+__device__ __forceinline__ int arrive(unsigned long long* p, unsigned long long tag)
+{
+    unsigned long long old = ld_acquire_gpu_u64(p);
+    for (int tries = 0; tries < 1024; ++tries) {
+        const int before = arrivals_of(old, tag);
+        const unsigned long long prev = atomicCAS(p, old, (tag << 8) | static_cast<unsigned long long>(before + 1));
+        if (prev == old) {
+            return before;
+        }
+        old = prev;
     }
+    return -1;
 }
 
 template <int MP, int KIND>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                       const I8Epilogue ep, const int m_total, const int n_total, const int k_total,
-                      const uint32_t idesc, int32_t* error_word, int32_t* split_counters, int32_t* split_slots)
+                      const uint32_t idesc, int32_t* error_word, unsigned long long* split_counters,
+                      int32_t* split_slots, const unsigned long long split_tag)
 {
     using Cfg = SkinnyConfig<MP>;
     constexpr int kStages = Cfg::kStages;
@@ -317,9 +336,6 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         const float zpf = static_cast<float>(ep.out_zp);
         const float lo = (KIND == NNB200_OUT_S8 ? -128.0f : 0.0f) - zpf;
         const float hi = (KIND == NNB200_OUT_S8 ? 127.0f : 255.0f) - zpf;
-        if (split) {
-            asm volatile("griddepcontrol.wait;" ::: "memory");  // the counters' zeroing kernel
-        }
         const int ch = quarter * 32 + lane;  // this thread's channel within the tile
         const int64_t total_units = static_cast<int64_t>(num_tiles) * num_kb;
         const size_t slot_elems = static_cast<size_t>(kBlockN) * static_cast<size_t>(m_total);
@@ -366,7 +382,7 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 // Everybody else already in?  Then this warp finishes the tile and has nothing to publish.
                 int seen = 0;
                 if (lane == 0) {
-                    seen = ld_acquire_gpu(&split_counters[tile * 4 + quarter]);
+                    seen = arrivals_of(ld_acquire_gpu_u64(&split_counters[tile * 4 + quarter]), split_tag);
                 }
                 seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
                 publish = seen != last_cta - first_cta;
@@ -396,13 +412,19 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 __syncwarp();
                 int ticket = 0;
                 if (lane == 0) {
-                    ticket = atomicAdd(&split_counters[tile * 4 + quarter], 1);
+                    ticket = arrive(&split_counters[tile * 4 + quarter], split_tag);
                 }
                 ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+                if (ticket < 0) {
+                    atomicCAS(error_word, 0, kErrEpilogueWait);  // cannot happen with at most 148 parts per word
+                }
                 finish = ticket == last_cta - first_cta;
                 if (finish) {
                     __threadfence();
                 }
+            }
+            if (partial && finish && lane == 0) {
+                split_counters[tile * 4 + quarter] = split_tag << 8;  // nobody else touches it in this launch
             }
 #pragma unroll 1
             for (int c = 0; c < MP / 32; ++c) {
@@ -475,6 +497,20 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     }
 }
 
+// A 56-bit tag no earlier launch of this process has used, never zero; the sequence starts at
+// a point derived from the clock so that words left in recycled memory by another process do
+// not match either.
+unsigned long long next_split_tag()
+{
+    static std::atomic<unsigned long long> counter{
+        static_cast<unsigned long long>(std::chrono::steady_clock::now().time_since_epoch().count()) * 0x9E3779B97F4A7C15ull};
+    unsigned long long t;
+    do {
+        t = counter.fetch_add(1, std::memory_order_relaxed) & ((1ull << 56) - 1);
+    } while (t == 0);
+    return t;
+}
+
 template <int MP, int KIND>
 int launch_skinny_variant(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, void* split_scratch,
                           cudaStream_t stream)
@@ -499,34 +535,22 @@ int launch_skinny_variant(const I8Problem& p, const I8Epilogue& ep, const Device
     }
     const int num_tiles = (n + kBlockN - 1) / kBlockN;
     int grid = num_tiles < dev.sm_count ? num_tiles : dev.sm_count;
-    int32_t* counters = nullptr;
+    unsigned long long* counters = nullptr;
     int32_t* slots = nullptr;
+    unsigned long long tag = 0;
     if (split_scratch != nullptr) {
-        // Equal shares of all K blocks over every SM; the tiles' counters start from zero.
+        // Equal shares of all K blocks over every SM.
         grid = dev.sm_count;
-        counters = static_cast<int32_t*>(split_scratch);
+        counters = static_cast<unsigned long long*>(split_scratch);
         slots = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(split_scratch) + split_counter_bytes(num_tiles));
-        zero_words_kernel<<<(num_tiles * 4 + 255) / 256, 256, 0, stream>>>(counters, num_tiles * 4);
-        note_launch();
+        tag = next_split_tag();
     }
     // 128-row operand = weights (s8), N operand = activations (s8 or u8).
     const uint32_t idesc = umma_idesc(2, 1, p.a_unsigned ? 0u : 1u, kBlockN, MP);
-    // With the split, the GEMM may start while the zeroing kernel drains: only its epilogue
-    // warps touch the counters, and they wait for that kernel first.
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(grid));
-    cfg.blockDim = dim3(kNumThreads);
-    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = counters != nullptr ? 1 : 0;
-    const cudaError_t e =
-        cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, ep, m, n, k, idesc, dev.error_word, counters, slots);
+    kernel<<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(map_w, map_a, ep, m, n, k, idesc, dev.error_word, counters,
+                                                             slots, tag);
     note_launch();
-    return cuda_status(e != cudaSuccess ? e : cudaGetLastError());
+    return cuda_status(cudaGetLastError());
 }
 
 template <int MP>
@@ -551,11 +575,16 @@ bool skinny_i8_supported(const I8Problem& p)
     return p.m >= 1 && p.m <= 128 && umma_i8_supported(p);
 }
 
-// Scratch for the equal-share split of K over all SMs, or 0 when whole tiles already fill
-// them evenly (within a tenth) or a share is too short to pay for the exchange: publishing a
-// part, counting in and collecting the others' costs a few microseconds at the end of the
-// kernel, which only a long stream (from about 48 K blocks = 768 KB of weights per SM) buys back
-// (measured: N=28672, K=8192, 16 rows 50.4 -> 46.9 us; N=11008, K=4096, 16 rows 16.0 -> 21.2 us).
+// Scratch for the equal-share split of K over all SMs, or 0 when it would not pay.  Publishing a
+// part, counting in and collecting the others' parts costs about 10 us at the end of the kernel
+// plus ~0.1 us per activation row, against ~0.3 us per 128-byte K block that the busiest CTA no
+// longer has to stream.  Measured, 24 rows, whole tiles -> shared K (us):
+//   one wave of tiles:  N=4096,K=28672 70.1 -> 31.6;  N=4096,K=14336 38.4 -> 24.4;  N=8192,K=8192
+//   25.2 -> 24.5;  N=14336,K=8192 26.5 -> 32.6;  N=11008,K=4096 16.3 -> 21.8;
+//   two waves, the second half empty:  N=28672,K=8192 51.5 -> 47.0 (48 rows 54.6 -> 52.1).
+// Hence: with one wave, share when the busiest CTA sheds at least 45 K blocks, plus 0.5 per row
+// above 12; with several waves, when the last one is less than 9/10 full, a share is at least 48
+// K blocks and there are at most 64 rows.
 // NNB200_I8_SHARE_K=0 turns the split off; =2 offers it from 8 K blocks per SM (measurement, tests).
 size_t skinny_i8_split_bytes(const I8Problem& p, const DeviceInfo& dev)
 {
@@ -571,12 +600,19 @@ size_t skinny_i8_split_bytes(const I8Problem& p, const DeviceInfo& dev)
     const int64_t num_kb = (p.k + kBlockKBytes - 1) / kBlockKBytes;
     const int64_t sms = dev.sm_count;
     const int64_t waves = (tiles + sms - 1) / sms;
-    const int64_t min_share = mode == '2' ? 8 : 48;
-    if (tiles * 10 >= waves * sms * 9 || tiles * num_kb < min_share * sms) {
-        return 0;
+    const int64_t share = (tiles * num_kb + sms - 1) / sms;
+    if (tiles * 10 >= waves * sms * 9 || share < 8) {
+        return 0;  // whole tiles already fill the SMs, or there is next to nothing to share
     }
-    if (mode != '2' && p.m > 64) {
-        return 0;  // the int32 parts grow with m: from 65 rows they cost more than the even split saves
+    if (mode != '2') {
+        if (waves == 1) {
+            const int64_t rows_over = p.m > 12 ? p.m - 12 : 0;
+            if ((num_kb - share) * 10 < 450 + 5 * rows_over) {
+                return 0;
+            }
+        } else if (share < 48 || p.m > 64) {
+            return 0;
+        }
     }
     // Two slots per CTA (the tile it finishes for someone and the tile it leaves to someone),
     // each 128 channels x m int32.

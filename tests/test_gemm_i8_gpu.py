@@ -177,6 +177,24 @@ def test_few_row_engine_choice(cuda_device, nnb200_lib, case):
     _run_case(cuda_device, m, n, k, out_kind="s8", per_channel=True, out_scale=30.0, expect_engine=want, seed=m + n)
 
 
+def test_narrow_layer_with_long_k_depends_on_the_workspace(cuda_device, nnb200_lib):
+    """4096 channels, K = 14336, 24 rows: with the full workspace the weights-as-rows engine
+    shares K among all SMs; with the minimum one the call stays on the square engine.  Same bytes."""
+    m, n, k = 24, 4096, 14336
+    rng = np.random.default_rng(77)
+    a = torch.from_numpy(rng.integers(-127, 128, (m, k), dtype=np.int8)).to(cuda_device)
+    w = torch.from_numpy(rng.integers(-127, 128, (n, k), dtype=np.int8)).to(cuda_device)
+    sw = rng.uniform(0.001, 0.02, n).astype(np.float32)
+    kw = dict(out_kind="s8", scale_a=0.02, scale_w=sw, out_scale=150.0, relu=True)
+    o = torch.empty((m, n), dtype=torch.int8, device=cuda_device)
+    assert ops.gemm_i8_engine(a, w, o, **kw) == "skinny"
+    assert ops.gemm_i8_engine(a, w, o, min_workspace=True, **kw) == "umma"
+    full = ops.gemm_i8(a, w, **kw).cpu().numpy()
+    least = ops.gemm_i8(a, w, min_workspace=True, **kw).cpu().numpy()
+    want = oracle.gemm_i8(a.cpu().numpy(), w.cpu().numpy(), **kw)
+    assert np.array_equal(full, want) and np.array_equal(least, want)
+
+
 def test_skinny_engine_small_m_on_request(cuda_device, nnb200_lib):
     for m in (1, 5, 16):
         _run_case(cuda_device, m, 520, 1024, out_kind="s8", relu=True, per_channel=True, out_scale=1.1,
