@@ -15,9 +15,9 @@
 //     per tile into registers, and for each activation row the warp stores 32 consecutive
 //     channels of that output row.
 //
-// Same pipeline skeleton as the square engine (TMA warp, MMA warp, four epilogue warps, two
-// TMEM accumulators, bounded waits), same epilogue arithmetic (epilogue.cuh): results are
-// bit-identical to every other int8 engine.
+// Same pipeline skeleton as the square engine (TMA warp, MMA warp, epilogue warps, two TMEM
+// accumulators, bounded waits) except that each accumulator has its own four epilogue warps;
+// same epilogue arithmetic (epilogue.cuh): results are bit-identical to every other int8 engine.
 //
 // Work split.  The unit of work is one 128-byte K block of one tile; tile t owns units
 // [t * num_kb, (t + 1) * num_kb).  Every CTA takes one contiguous range of units:
@@ -47,8 +47,11 @@ namespace {
 constexpr int kBlockN = 128;       // channels per tile = rows of the MMA's 128-row operand
 constexpr int kBlockKBytes = 128;  // one 128-byte swizzle row of K per stage
 constexpr int kUmmaK = 32;
-constexpr int kNumThreads = 192;   // TMA warp, MMA warp, 4 epilogue warps
-constexpr int kEpilogueThreads = 128;
+// TMA warp, MMA warp and two groups of four epilogue warps.  Group g drains accumulator g, i.e.
+// every second piece of the CTA's range, so the drains (and, with shared K, the exchanges of
+// partial sums, each a chain of L2 round trips) of consecutive pieces run side by side.
+constexpr int kNumThreads = 320;
+constexpr int kEpilogueThreads = 128;  // per group
 
 template <int MP>
 struct SkinnyConfig {
@@ -160,10 +163,10 @@ __device__ __forceinline__ int arrivals_of(unsigned long long word, unsigned lon
     return (word >> 8) == tag ? static_cast<int>(word & 0xFFu) : 0;
 }
 
-// Count this part in; returns how many parts had arrived before it (-1 if the bounded retry ran out).
-__device__ __forceinline__ int arrive(unsigned long long* p, unsigned long long tag)
+// Count this part in, starting from the word as last seen; returns how many parts had arrived
+// before it (-1 if the bounded retry ran out).
+__device__ __forceinline__ int arrive(unsigned long long* p, unsigned long long tag, unsigned long long old)
 {
-    unsigned long long old = ld_acquire_gpu_u64(p);
     for (int tries = 0; tries < 1024; ++tries) {
         const int before = arrivals_of(old, tag);
         const unsigned long long prev = atomicCAS(p, old, (tag << 8) | static_cast<unsigned long long>(before + 1));
@@ -173,6 +176,32 @@ __device__ __forceinline__ int arrive(unsigned long long* p, unsigned long long 
         old = prev;
     }
     return -1;
+}
+
+// Sum over the other CTAs' published parts of one tile, rows [row0, row0 + 32) of this thread's
+// channel.  All loads of a part are issued before any is used: one L2 round trip per part.
+__device__ __forceinline__ void collect_parts(int32_t (&sum)[32], const int32_t* split_slots, size_t slot_elems, int ch,
+                                              int first_cta, int last_cta, int self, int row0, int m_total)
+{
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        sum[j] = 0;
+    }
+    for (int other = first_cta; other <= last_cta; ++other) {
+        if (other == self) {
+            continue;
+        }
+        const int32_t* theirs = split_slots + (2 * static_cast<size_t>(other) + (other == first_cta ? 1u : 0u)) * slot_elems + ch;
+        int32_t part[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            part[j] = (row0 + j < m_total) ? __ldcg(theirs + static_cast<size_t>(row0 + j) * kBlockN) : 0;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            sum[j] += part[j];
+        }
+    }
 }
 
 template <int MP, int KIND>
@@ -339,8 +368,9 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         const int ch = quarter * 32 + lane;  // this thread's channel within the tile
         const int64_t total_units = static_cast<int64_t>(num_tiles) * num_kb;
         const size_t slot_elems = static_cast<size_t>(kBlockN) * static_cast<size_t>(m_total);
-        int local_seg = 0;
-        for (; local_seg < num_segments; ++local_seg) {
+        const int group = (warp - 2) >> 2;
+        int local_seg = group;
+        for (; local_seg < num_segments; local_seg += 2) {
             const Segment seg = segments.at(local_seg);
             const int tile = seg.tile;
             const int acc = local_seg & 1;
@@ -364,6 +394,30 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 }
             }
 
+            // Part of a tile.  While this piece's MMAs are still running, look whether everybody else
+            // has published already; if so this warp will finish the tile and fetches the others'
+            // sums for the first 32 rows now, off the critical path.
+            int first_cta = 0, last_cta = -1;
+            bool early = false;
+            int32_t early_sum[32];
+            if (partial) {
+                first_cta = cta_of_unit(static_cast<int64_t>(tile) * num_kb, grid, total_units);
+                last_cta = cta_of_unit(static_cast<int64_t>(tile + 1) * num_kb - 1, grid, total_units);
+                int seen = 0;
+                if (MP == 32 && lane == 0) {
+                    seen = arrivals_of(ld_acquire_gpu_u64(&split_counters[tile * 4 + quarter]), split_tag);
+                }
+                seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
+                // Only where 32 rows are all there is: with more rows the early fetch covers a part of
+                // the work and measured slower than none.
+                early = MP == 32 && seen == last_cta - first_cta;
+                if (early) {
+                    __threadfence();  // every lane's reads of the others' slots come after lane 0's look
+                    collect_parts(early_sum, split_slots, slot_elems, ch, first_cta, last_cta, static_cast<int>(blockIdx.x),
+                                  0, m_total);
+                }
+            }
+
             if (!mbar_wait_warp(&acc_full_bar[acc], acc_phase, abort_flag)) {
                 atomicCAS(error_word, 0, kErrEpilogueWait);
                 break;
@@ -371,18 +425,17 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             tc_fence_after_sync();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(acc * MP);
-            // Part of a tile: publish this warp's 32 channels, count in, and carry on only if every
-            // other part of the tile has been published already.
-            int first_cta = 0, last_cta = -1;
+            // Otherwise: publish this warp's 32 channels, count in, and carry on only if every other
+            // part of the tile has been published by then.
             bool finish = true;
-            bool publish = partial;
-            if (partial) {
-                first_cta = cta_of_unit(static_cast<int64_t>(tile) * num_kb, grid, total_units);
-                last_cta = cta_of_unit(static_cast<int64_t>(tile + 1) * num_kb - 1, grid, total_units);
-                // Everybody else already in?  Then this warp finishes the tile and has nothing to publish.
+            bool publish = partial && !early;
+            unsigned long long seen_word = 0;  // lane 0's last look at the tile's arrival word
+            if (publish) {
+                // Everybody else in by now?  Then this warp finishes the tile and has nothing to publish.
                 int seen = 0;
                 if (lane == 0) {
-                    seen = arrivals_of(ld_acquire_gpu_u64(&split_counters[tile * 4 + quarter]), split_tag);
+                    seen_word = ld_acquire_gpu_u64(&split_counters[tile * 4 + quarter]);
+                    seen = arrivals_of(seen_word, split_tag);
                 }
                 seen = __shfl_sync(0xFFFFFFFFu, seen, 0);
                 publish = seen != last_cta - first_cta;
@@ -412,7 +465,7 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 __syncwarp();
                 int ticket = 0;
                 if (lane == 0) {
-                    ticket = arrive(&split_counters[tile * 4 + quarter], split_tag);
+                    ticket = arrive(&split_counters[tile * 4 + quarter], split_tag, seen_word);
                 }
                 ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
                 if (ticket < 0) {
@@ -435,23 +488,13 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                 tmem_ld_wait();
                 if (partial) {
-                    for (int other = first_cta; other <= last_cta; ++other) {
-                        if (other == static_cast<int>(blockIdx.x)) {
-                            continue;
-                        }
-                        const int32_t* theirs = split_slots +
-                                                (2 * static_cast<size_t>(other) + (other == first_cta ? 1u : 0u)) * slot_elems +
-                                                ch;
-                        // All loads first, then the additions: one L2 round trip per part, not per row.
-                        int32_t part[32];
+                    if (!(early && c == 0)) {
+                        collect_parts(early_sum, split_slots, slot_elems, ch, first_cta, last_cta,
+                                      static_cast<int>(blockIdx.x), c * 32, m_total);
+                    }
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            part[j] = (c * 32 + j < m_total) ? __ldcg(theirs + static_cast<size_t>(c * 32 + j) * kBlockN) : 0;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            v[j] += static_cast<uint32_t>(part[j]);
-                        }
+                    for (int j = 0; j < 32; ++j) {
+                        v[j] += static_cast<uint32_t>(early_sum[j]);
                     }
                 }
 #pragma unroll
@@ -576,13 +619,14 @@ bool skinny_i8_supported(const I8Problem& p)
 }
 
 // Scratch for the equal-share split of K over all SMs, or 0 when it would not pay.  Publishing a
-// part, counting in and collecting the others' parts costs about 10 us at the end of the kernel
-// plus ~0.1 us per activation row, against ~0.3 us per 128-byte K block that the busiest CTA no
-// longer has to stream.  Measured, 24 rows, whole tiles -> shared K (us):
-//   one wave of tiles:  N=4096,K=28672 70.1 -> 31.6;  N=4096,K=14336 38.4 -> 24.4;  N=8192,K=8192
-//   25.2 -> 24.5;  N=14336,K=8192 26.5 -> 32.6;  N=11008,K=4096 16.3 -> 21.8;
-//   two waves, the second half empty:  N=28672,K=8192 51.5 -> 47.0 (48 rows 54.6 -> 52.1).
-// Hence: with one wave, share when the busiest CTA sheds at least 45 K blocks, plus 0.5 per row
+// part, counting in and collecting the others' parts is a chain of L2 round trips at the end of
+// the kernel, each well over a microsecond while every SM is streaming: about 6 us in all plus
+// ~0.1 us per activation row, against ~0.3 us per 128-byte K block that the busiest CTA no longer
+// has to stream.  Measured, 24 rows, whole tiles -> shared K (us):
+//   one wave of tiles:  N=4096,K=28672 70.1 -> 31.6;  N=4096,K=14336 38.5 -> 22.2;  N=8192,K=8192
+//   25.3 -> 22.2;  N=14336,K=8192 28.1 -> 29.5;  N=11008,K=4096 16.5 -> 18.3;
+//   two waves, the second half empty:  N=28672,K=8192 52.0 -> 47.6 (48 rows 54.9 -> 51.8).
+// Hence: with one wave, share when the busiest CTA sheds at least 30 K blocks, plus 0.7 per row
 // above 12; with several waves, when the last one is less than 9/10 full, a share is at least 48
 // K blocks and there are at most 64 rows.
 // NNB200_I8_SHARE_K=0 turns the split off; =2 offers it from 8 K blocks per SM (measurement, tests).
@@ -607,7 +651,7 @@ size_t skinny_i8_split_bytes(const I8Problem& p, const DeviceInfo& dev)
     if (mode != '2') {
         if (waves == 1) {
             const int64_t rows_over = p.m > 12 ? p.m - 12 : 0;
-            if ((num_kb - share) * 10 < 450 + 5 * rows_over) {
+            if ((num_kb - share) * 10 < 300 + 7 * rows_over) {
                 return 0;
             }
         } else if (share < 48 || p.m > 64) {
