@@ -68,7 +68,7 @@ extern "C" int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, vo
             return NNB200_INTERNAL;
         }
         local.workspace = p;
-        local.workspace_bytes = static_cast<size_t>(NNB200_STATIC_SCRATCH_BYTES);
+        local.workspace_bytes = need;  // exactly the sums' share: the optional K-sharing scratch is not offered here
     }
     // The sums kernels overwrite every entry of R_a / R_w they later read, so the previous
     // call's contents never leak into this one and nothing has to be cleared.
