@@ -45,6 +45,64 @@ def read_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+class NvmlSampler:
+    """SM clock and clock-event reasons read through NVML from a thread of this process, every
+    couple of milliseconds, while the timed region runs (read-only queries)."""
+
+    def __init__(self, gpu_index: int, uuid: str | None = None):
+        import threading
+        import pynvml
+        self.nv = pynvml
+        pynvml.nvmlInit()
+        handle = None
+        if uuid:
+            try:
+                handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+            except pynvml.NVMLError:
+                handle = None
+        self.h = handle if handle is not None else pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        self.sm, self.mask, self.power = [], 0, []
+        self.smax = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+            except nv.NVMLError:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        self._thread.join(timeout=2)
+        nv = self.nv
+        names = (("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown),
+                 ("hw_thermal_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown),
+                 ("sw_thermal_slowdown", nv.nvmlClocksEventReasonSwThermalSlowdown),
+                 ("sw_power_cap", nv.nvmlClocksEventReasonSwPowerCap))
+        reasons = sorted(n for n, bit in names if self.mask & bit)
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": float(self.smax),
+                "samples": len(self.sm), "reasons": reasons, "source": "nvml, 2 ms period, timed region only",
+                "power_w": round(statistics.median(self.power), 1) if self.power else None}
+
+
+def make_clock_sampler(gpu_index: int, uuid: str | None = None):
+    """(sampler, tight): the in-process NVML sampler when NVML is usable -- it brackets the timed
+    region tightly -- else the nvidia-smi subprocess, which needs slack before and after."""
+    try:
+        return NvmlSampler(gpu_index, uuid), True
+    except Exception:
+        return ClockSampler(gpu_index), False
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -402,14 +460,17 @@ def main():
     for _ in range(max(3, args.warmup)):
         layer.forward(a, out)
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
+    uuid = getattr(torch.cuda.get_device_properties(dev), "uuid", None)
+    sampler, tight = make_clock_sampler(local_rank, str(uuid) if uuid is not None else None) if rank == 0 else (None, True)
+    if rank == 0 and not tight:
         sampler.start()
         time.sleep(0.3)
     k_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = lib.nnb200_launch_count()
     barrier()
+    if rank == 0 and tight:
+        sampler.start()
     e0.record()
     for i in range(args.steps):
         # Per-launch events around the GEMM itself (the dominant kernel), on the launching stream.
@@ -419,10 +480,12 @@ def main():
         layer.reassemble(out)
     e1.record()
     barrier()
+    if rank == 0 and tight:
+        clocks = sampler.stop()
     launches = lib.nnb200_launch_count() - launches0
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     kernel_ms = max_over_ranks(sum(s.elapsed_time(e) for s, e in k_ev) / args.steps)
-    if rank == 0:
+    if rank == 0 and not tight:
         time.sleep(0.2)
         clocks = sampler.stop()
     total_ops = 2.0 * M * N * K
