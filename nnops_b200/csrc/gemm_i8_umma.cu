@@ -50,7 +50,7 @@ struct alignas(64) PeerMaps {
     CUtensorMap m[8];
 };
 
-template <int BN, bool PEERS = false>
+template <int BN, int PEERS = 0>
 struct TileConfig {
     // Tiles wider than 256 columns (single-wave form, see launch_gemm_i8_umma) are issued as two
     // MMAs of BN / 2 columns over one A tile and keep ONE accumulator: a CTA owns exactly one tile.
@@ -60,15 +60,19 @@ struct TileConfig {
     static constexpr int kBTileBytes = BN * kBlockKBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     // Ring depth: as many stages as fit beside the epilogue staging in ~200 KB.
-    static constexpr int kStages = PEERS ? ((BN == 256) ? 3 : 5)
+    static constexpr int kStages = PEERS ? ((BN == 256) ? (PEERS == 1 ? 4 : 3) : 5)
                                    : (BN > 256) ? (BN > 384 ? 2 : 3)
                                                 : ((BN > 128) ? 4 : (BN == 128 ? 6 : 8));
     // Two accumulators BN columns apart (one when BN > 256); a power of two of at least that.
     static constexpr int kTmemCols = BN > 128 ? 512 : 2 * BN;
     static constexpr int kColParamBytes = 4 * 4 * BN * 4;  // 4 epilogue warps x {scale, bias, r_w, zp_w} x BN x 4 B
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
-    // Sharded form: two staging tiles of 32 rows x 128 B per epilogue warp (one being filled, one being stored).
-    static constexpr int kPeerStageBytes = PEERS ? 4 * 2 * 32 * 128 : 0;
+    // Sharded form (PEERS = 2): two staging tiles of 32 rows x 128 B per epilogue warp, one being
+    // filled while the other is being stored.  With a single peer (PEERS = 1) the stores are far
+    // from saturating the link and the main loop decides: one staging tile per warp, and the
+    // shared memory that frees keeps the ring at four stages.
+    static constexpr int kStageTiles = PEERS == 1 ? 1 : 2;
+    static constexpr int kPeerStageBytes = PEERS ? 4 * kStageTiles * 32 * 128 : 0;
     static constexpr int kSmemBytes =
         1024 /*alignment slack*/ + kStages * kStageBytes + kPeerStageBytes + kColParamBytes + kBarrierBytes;
 };
@@ -248,7 +252,7 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
     }
 }
 
-template <int BN, int KIND, bool PEERS>
+template <int BN, int KIND, int PEERS>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ PeerMaps peer_maps, const I8Epilogue ep, const int m_total,
@@ -489,10 +493,10 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     // Two staging tiles per warp, used alternately: before refilling one, its
                     // previous bulk stores must have finished READING it (they may still be in flight
                     // on the wire).  Only lane 0 issues bulk stores, so only lane 0 has groups to wait on.
-                    uint8_t* stage = peer_stage + ((warp - 2) * 2 + (stage_turn & 1)) * (32 * 128);
+                    uint8_t* stage = peer_stage + ((warp - 2) * Cfg::kStageTiles + (stage_turn % Cfg::kStageTiles)) * (32 * 128);
                     ++stage_turn;
                     if (lane == 0) {
-                        bulk_wait_group_read<1>();
+                        bulk_wait_group_read<Cfg::kStageTiles - 1>();
                     }
                     __syncwarp();
 #pragma unroll 1
@@ -887,7 +891,7 @@ int launch_pair_bn(const I8Problem& p, const I8Epilogue& ep, int m, int n, int k
     }
 }
 
-template <int BN, int KIND, bool PEERS>
+template <int BN, int KIND, int PEERS>
 int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m, int n, int k,
                    uint32_t idesc, int vec_ok, const DeviceInfo& dev, cudaStream_t stream)
 {
@@ -937,20 +941,24 @@ int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, cons
         // Sharded write-back exists for the 8-bit destinations and 128-column groups.
         if constexpr (BN == 256 || BN == 128) {
             if (kind == NNB200_OUT_S8) {
-                return launch_variant<BN, NNB200_OUT_S8, true>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+                return ep.num_peers == 1
+                           ? launch_variant<BN, NNB200_OUT_S8, 1>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream)
+                           : launch_variant<BN, NNB200_OUT_S8, 2>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
             }
             if (kind == NNB200_OUT_U8) {
-                return launch_variant<BN, NNB200_OUT_U8, true>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+                return ep.num_peers == 1
+                           ? launch_variant<BN, NNB200_OUT_U8, 1>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream)
+                           : launch_variant<BN, NNB200_OUT_U8, 2>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
             }
         }
         return NNB200_UNSUPPORTED;
     }
     switch (kind) {
-    case NNB200_OUT_S32: return launch_variant<BN, NNB200_OUT_S32, false>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
-    case NNB200_OUT_S8: return launch_variant<BN, NNB200_OUT_S8, false>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
-    case NNB200_OUT_U8: return launch_variant<BN, NNB200_OUT_U8, false>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
-    case NNB200_OUT_F32: return launch_variant<BN, NNB200_OUT_F32, false>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
-    case NNB200_OUT_F16: return launch_variant<BN, NNB200_OUT_F16, false>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_S32: return launch_variant<BN, NNB200_OUT_S32, 0>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_S8: return launch_variant<BN, NNB200_OUT_S8, 0>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_U8: return launch_variant<BN, NNB200_OUT_U8, 0>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_F32: return launch_variant<BN, NNB200_OUT_F32, 0>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+    case NNB200_OUT_F16: return launch_variant<BN, NNB200_OUT_F16, 0>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
     default: return NNB200_UNSUPPORTED;
     }
 }
