@@ -939,14 +939,19 @@ int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, cons
 {
     if (ep.num_peers > 0) {
         // Sharded write-back exists for the 8-bit destinations and 128-column groups.
+        // NNB200_I8_PEER_STAGING=1 / 2 forces the staging depth (measurement aid).
+        bool single = ep.num_peers == 1;
+        if (const char* e = getenv("NNB200_I8_PEER_STAGING")) {
+            single = e[0] == '1' ? true : (e[0] == '2' ? false : single);
+        }
         if constexpr (BN == 256 || BN == 128) {
             if (kind == NNB200_OUT_S8) {
-                return ep.num_peers == 1
+                return single
                            ? launch_variant<BN, NNB200_OUT_S8, 1>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream)
                            : launch_variant<BN, NNB200_OUT_S8, 2>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
             }
             if (kind == NNB200_OUT_U8) {
-                return ep.num_peers == 1
+                return single
                            ? launch_variant<BN, NNB200_OUT_U8, 1>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream)
                            : launch_variant<BN, NNB200_OUT_U8, 2>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
             }
