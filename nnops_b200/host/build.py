@@ -6,7 +6,7 @@ programs.
 Outputs (all git-ignored, shipped as built files):
   nnops_b200/lib/libnnb200_host.so      operator front end + backend glue against the stand-alone API mirror
   tests/cpp/_bin/test_ops_standalone    operator tests against that library
-and, only where the nnops source tree is present (NNOPS_REFERENCE_ROOT, default /root/reference):
+and, only where the nnops source tree is present (the directory NNOPS_REFERENCE_ROOT names, else the default below):
   nnops_b200/lib/libnnops_b200_dropin.so   nnops' own front end (src/ops/linear.cpp, matmul.cpp, quant_linear.cpp) and CPU route,
                                            compiled in place with NNOPS_HAS_CUDA, linked against THIS backend
   tests/cpp/_bin/test_ops_dropin           the same tests through the real nnops API, CUDA vs nnops' CPU route

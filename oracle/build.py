@@ -4,7 +4,7 @@
                                   # and, when the reference tree is present, oracle/_ref/*.so
 
 The reference route is compiled from the reference's own source files where they lie
-(REFERENCE_ROOT, default /root/reference) with plain g++ -- its build system is not run --
+(REFERENCE_ROOT: the directory NNOPS_REFERENCE_ROOT names, else the default below) with plain g++ -- its build system is not run --
 plus oracle/ref_shim.cpp.  Outputs go only into oracle/_ref/ (git-ignored).  Two ISA variants
 are produced because the int8 micro-kernel needs vpdpbusd: AVX-VNNI (the reference's default
 flags) and AVX512-VNNI+VL; the loader picks the one the host CPU supports.
