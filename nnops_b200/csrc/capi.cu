@@ -267,6 +267,13 @@ static I8SplitPlan i8_split_plan(const nnb200_gemm_i8_args* a)
     } else if (engine == NNB200_ENGINE_UMMA && a->force_engine == NNB200_ENGINE_AUTO && p.m >= 17 && p.m <= 128) {
         plan.bytes = skinny_i8_split_bytes(p, *dev);  // 0 unless weights-as-rows is supported and the split pays
         plan.switches_engine = plan.bytes > 0;
+    } else if (engine == NNB200_ENGINE_DECODE && a->force_engine == NNB200_ENGINE_AUTO && p.m > 8 &&
+               p.n * p.k >= (int64_t{80} << 20)) {
+        // 9..16 rows on a layer of modest width: the streaming engine costs ~0.23 us per MB of weights,
+        // weights-as-rows with shared K ~0.16 us per MB plus 5 us more up front; from about 80 MB the
+        // latter wins (N=4096, K=28672, 12 rows: 30.5 against 33.6 us).
+        plan.bytes = skinny_i8_split_bytes(p, *dev);
+        plan.switches_engine = plan.bytes > 0;
     }
     return plan;
 }

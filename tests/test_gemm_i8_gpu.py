@@ -170,7 +170,8 @@ def test_skinny_engine_shared_k_not_offered_when_tiles_fill_the_sms(cuda_device,
 @pytest.mark.parametrize("case", [(8, 28672, 1024, "decode"), (12, 4096, 1024, "decode"), (16, 12288, 512, "decode"),
                                   (12, 14336, 512, "skinny"), (16, 28672, 512, "skinny"), (24, 4096, 1024, "umma"),
                                   (100, 9472, 512, "umma"), (24, 11008, 512, "skinny"), (64, 28672, 512, "skinny"),
-                                  (100, 11008, 512, "skinny"), (100, 28672, 512, "umma"), (129, 11008, 512, "umma")])
+                                  (100, 11008, 512, "skinny"), (100, 28672, 512, "umma"), (129, 11008, 512, "umma"),
+                                  (12, 4096, 28672, "skinny"), (8, 4096, 28672, "decode")])
 def test_few_row_engine_choice(cuda_device, nnb200_lib, case):
     """The measured crossovers between the streaming engine, weights-as-rows and the square engine."""
     m, n, k, want = case
