@@ -320,10 +320,12 @@ def test_config5_rows_and_linearity(cuda_device, nnb200_lib):
 
 @pytest.mark.parametrize("shape", [(512, 1024, 1024), (300, 2048 + 16, 512), (4096, 3584, 256)])
 @pytest.mark.parametrize("out_kind", ["s8", "u8"])
-def test_multi_destination_epilogue_local(cuda_device, nnb200_lib, shape, out_kind):
+@pytest.mark.parametrize("peers", [1, 2, 7])
+def test_multi_destination_epilogue_local(cuda_device, nnb200_lib, shape, out_kind, peers):
     """The sharded write-back on ONE GPU: the kernel stores its [M, n] window into `out` and into
-    two more buffers that play the other ranks' copies (plain local memory here).  Every copy
-    must equal the oracle inside the window and stay untouched outside it."""
+    `peers` more buffers that play the other ranks' copies (plain local memory here).  Every copy
+    must equal the oracle inside the window and stay untouched outside it.  One peer takes the
+    variant with a single staging tile per warp and the deeper ring, more take the other."""
     import ctypes as C
     from nnops_b200 import capi
     m, n, k = shape
@@ -335,12 +337,12 @@ def test_multi_destination_epilogue_local(cuda_device, nnb200_lib, shape, out_ki
     want = oracle.gemm_i8(a, w, **kw)
     n_full, col0 = 2 * n + 64, n + 32            # the window sits in the middle of a wider matrix
     tdt = ops._OUT_TORCH[out_kind]
-    copies = [torch.full((m, n_full), 0x5A, dtype=tdt, device=cuda_device) for _ in range(3)]
+    copies = [torch.full((m, n_full), 0x5A, dtype=tdt, device=cuda_device) for _ in range(1 + peers)]
     ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(w).to(cuda_device)
     keep = []
     args = ops.gemm_i8_args(ta, tw, copies[0][:, col0:col0 + n], keep=keep, **kw)
-    args.num_peer_outs = 2
-    for i in range(2):
+    args.num_peer_outs = peers
+    for i in range(peers):
         args.peer_out[i] = copies[i + 1][:, col0:col0 + n].data_ptr()
     capi.check(nnb200_lib.nnb200_gemm_i8(C.byref(args), torch.cuda.current_stream(cuda_device).cuda_stream), "gemm")
     torch.cuda.synchronize()
