@@ -164,7 +164,8 @@ NNB200_API int nnb200_gemm_i8(const nnb200_gemm_i8_args* args, void* stream);
 #define NNB200_STATIC_SCRATCH_BYTES (1 << 20)
 NNB200_API int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, void* stream);
 
-/* Which engine nnb200_gemm_i8 would run for these arguments (NNB200_ENGINE_*). */
+/* Which engine nnb200_gemm_i8 would run for these arguments (NNB200_ENGINE_*), the workspace the
+ * block carries included: with enough of it some few-row calls move to the weights-as-rows engine. */
 NNB200_API int nnb200_gemm_i8_engine(const nnb200_gemm_i8_args* args);
 
 /*
