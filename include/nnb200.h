@@ -5,8 +5,12 @@
  * of the current CUDA device unless a comment says otherwise.  Calls enqueue work on the
  * given stream (a cudaStream_t passed as void*, NULL = default stream) and return without
  * synchronising.  Return values use the numbering of nnops::Status
- * (reference include/nnops/core/status.hpp:19-33).  A call that returns an error has written
- * nothing to its outputs.
+ * (reference include/nnops/core/status.hpp:19-33).  A call refused for its arguments
+ * (INVALID_ARGUMENT, UNSUPPORTED, OUT_OF_MEMORY) has launched nothing and written nothing to its
+ * outputs.  INTERNAL reports a CUDA launch failure; with batch > 1 earlier batch elements may
+ * have been enqueued by then.  Pointers must be naturally aligned for what they point at
+ * (4 bytes for int32 / float arrays, 2 for f16, 16 for a workspace); a misaligned one is
+ * INVALID_ARGUMENT.
  */
 #ifndef NNB200_H
 #define NNB200_H
@@ -164,6 +168,32 @@ NNB200_API int nnb200_gemm_i8(const nnb200_gemm_i8_args* args, void* stream);
 #define NNB200_STATIC_SCRATCH_BYTES (1 << 20)
 NNB200_API int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, void* stream);
 
+/*
+ * Measurement and test switches: process-wide integers, in the manner of the reference's bench
+ * knobs (src/detail/bench_knobs.hpp:15-38).  They only select among code paths that give
+ * identical results; production code leaves them alone.  A negative value means "default".
+ * The environment is never read.  nnb200_set_knob returns the previous value (or
+ * INT32_MIN for an unknown knob).
+ *   GROUP_M          raster group (m-blocks) of the int8 tensor-core GEMM
+ *   I8_BN            force its tile width: 64, 128, 192, 224, 256, 320, 384, 448 or 512
+ *   I8_PAIR          0 single-CTA form (default), 1 CTA-pair form where it applies, 2 pair form or an error
+ *   I8_PEER_STAGING  1 / 2 staging tiles per epilogue warp in the sharded write-back
+ *   F16_PAIR         as I8_PAIR for the dense f16 GEMM of the Q4_1 two-pass form (default 1)
+ *   I8_SHARE_K       0 never share K among SMs in the few-row engine, 2 offer it from 8 K blocks per SM
+ *   Q4_GEMV          Q4_1 GEMV engine of the automatic choice: 0 deferred-scaling kernel (default), 1 the
+ *                    per-weight-dequantising warp-MMA kernel
+ */
+#define NNB200_KNOB_GROUP_M 0
+#define NNB200_KNOB_I8_BN 1
+#define NNB200_KNOB_I8_PAIR 2
+#define NNB200_KNOB_I8_PEER_STAGING 3
+#define NNB200_KNOB_F16_PAIR 4
+#define NNB200_KNOB_I8_SHARE_K 5
+#define NNB200_KNOB_Q4_GEMV 6
+#define NNB200_KNOB_COUNT 7
+NNB200_API int nnb200_set_knob(int knob, int value);
+NNB200_API int nnb200_get_knob(int knob);
+
 /* Which engine nnb200_gemm_i8 would run for these arguments (NNB200_ENGINE_*), the workspace the
  * block carries included: with enough of it some few-row calls move to the weights-as-rows engine. */
 NNB200_API int nnb200_gemm_i8_engine(const nnb200_gemm_i8_args* args);
@@ -298,9 +328,16 @@ NNB200_API int nnb200_interleave_shards(const void* gathered, void* out, int64_t
  * it into every other rank's array and polls its own array until every other rank has done the
  * same.  Every rank must call it the same number of times.  Work enqueued on the stream after
  * it sees everything the other ranks' streams had completed before their call.  The wait is
- * bounded by limit_cycles SM clock cycles (0 = the library's default, about two seconds): when
- * it runs out the kernel records code 8 in the error word (nnb200_take_device_error) and
- * returns.  world <= 8.  No counterpart in the reference, which has no multi-GPU code.
+ * bounded by limit_cycles SM clock cycles (0 = the library's default, about half a minute:
+ * ranks of one job drift apart by seconds for ordinary reasons): when it runs out the kernel
+ * records code 8 in the error word and sets a sticky host-visible flag for this device, and
+ * returns.  From then on the outputs gathered on this device are not to be trusted, and every
+ * later nnb200_rank_barrier, and every nnb200_gemm_i8 with peer outputs, on this device returns
+ * NNB200_INTERNAL without launching anything, until nnb200_take_device_error has been called
+ * (it reports code 8 and clears the flag).  A sharded output is valid only if the error word
+ * read after it is 0.  The first call on a device allocates 64 bytes of pinned host memory
+ * for that flag: make it outside any stream capture.  world <= 8.  No counterpart in the
+ * reference, which has no multi-GPU code.
  */
 #define NNB200_RANK_FLAG_BYTES 64
 #define NNB200_DEVICE_ERROR_PEER_WAIT 8

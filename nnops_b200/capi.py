@@ -20,6 +20,8 @@ ENGINES = {"auto": 0, "umma": 1, "narrow": 2, "generic": 3, "decode": 4, "skinny
 ENGINE_NAMES = {v: k for k, v in ENGINES.items()}
 Q4_ENGINES = {"auto": 0, "gemm": 1, "gemv": 2, "gemv_simt": 3, "gemv_mma": 4, "gemm_two_pass": 5}
 STATIC_SCRATCH_BYTES = 1 << 20
+# Measurement / test switches (NNB200_KNOB_* in nnb200.h); process-wide, negative = default.
+KNOBS = {"group_m": 0, "i8_bn": 1, "i8_pair": 2, "i8_peer_staging": 3, "f16_pair": 4, "i8_share_k": 5, "q4_gemv": 6}
 
 
 class GemmI8Args(C.Structure):
@@ -117,6 +119,8 @@ SYMBOLS = [
     ("nnb200_peer_buffer_close", C.c_int, [C.c_void_p]),
     ("nnb200_enable_peer_access", C.c_int, [C.c_int32]),
     ("nnb200_is_device_pointer", C.c_int, [C.c_void_p]),
+    ("nnb200_set_knob", C.c_int, [C.c_int, C.c_int]),
+    ("nnb200_get_knob", C.c_int, [C.c_int]),
     ("nnb200_launch_count", C.c_uint64, []),
     ("nnb200_version", C.c_char_p, []),
 ]
@@ -151,6 +155,11 @@ class Nnb200Error(RuntimeError):
 def check(status: int, what: str) -> None:
     if status != OK:
         raise Nnb200Error(status, what)
+
+
+def set_knob(name: str, value: int) -> int:
+    """Set a measurement switch; returns the previous value (-1 = default)."""
+    return lib().nnb200_set_knob(KNOBS[name], int(value))
 
 
 def take_device_error() -> int:

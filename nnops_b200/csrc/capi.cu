@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdint>
 #include <cstring>
 #include <mutex>
 
@@ -21,8 +22,8 @@ __device__ int32_t g_error_word;
 std::atomic<uint64_t> g_launches{0};
 
 DeviceInfo g_devices[kMaxDevices];
-std::once_flag g_device_once[kMaxDevices];
-bool g_device_ok[kMaxDevices];
+std::mutex g_device_mutex;
+std::atomic<bool> g_device_ok[kMaxDevices];
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -52,24 +53,77 @@ const DeviceInfo* current_device_info()
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
         return nullptr;
     }
-    std::call_once(g_device_once[dev], [dev] {
-        DeviceInfo& d = g_devices[dev];
-        d.device = dev;
-        bool ok = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess;
-        ok = ok && cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess;
-        ok = ok && cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev) == cudaSuccess;
-        void* p = nullptr;
-        // The symbol's name is a host-side handle; kernels need its device address, which
-        // differs per device, so it is resolved with that device current.
-        ok = ok && cudaGetSymbolAddress(&p, g_error_word) == cudaSuccess;
-        d.error_word = static_cast<int32_t*>(p);
-        if (ok) {
-            const int32_t zero = 0;
-            ok = cudaMemcpy(d.error_word, &zero, sizeof(zero), cudaMemcpyHostToDevice) == cudaSuccess;
+    // Only a successful look-up is remembered: one that failed (the device not usable yet, a
+    // call made during stream capture) clears the CUDA error it raised and is tried again by
+    // the next call.
+    if (g_device_ok[dev].load(std::memory_order_acquire)) {
+        return &g_devices[dev];
+    }
+    std::lock_guard<std::mutex> lock(g_device_mutex);
+    if (g_device_ok[dev].load(std::memory_order_relaxed)) {
+        return &g_devices[dev];
+    }
+    DeviceInfo d;
+    d.device = dev;
+    bool ok = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess;
+    ok = ok && cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess;
+    ok = ok && cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev) == cudaSuccess;
+    void* p = nullptr;
+    // The symbol's name is a host-side handle; kernels need its device address, which
+    // differs per device, so it is resolved with that device current.
+    ok = ok && cudaGetSymbolAddress(&p, g_error_word) == cudaSuccess;
+    d.error_word = static_cast<int32_t*>(p);
+    if (ok) {
+        const int32_t zero = 0;
+        ok = cudaMemcpy(d.error_word, &zero, sizeof(zero), cudaMemcpyHostToDevice) == cudaSuccess;
+    }
+    if (!ok) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    g_devices[dev] = d;
+    g_device_ok[dev].store(true, std::memory_order_release);
+    return &g_devices[dev];
+}
+
+namespace {
+std::mutex g_poison_mutex;
+PeerPoison g_poison[kMaxDevices];
+}
+
+PeerPoison peer_poison_for_current_device(bool create)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        return PeerPoison{};
+    }
+    std::lock_guard<std::mutex> lock(g_poison_mutex);
+    if (g_poison[dev].host == nullptr && create) {
+        void* h = nullptr;
+        void* d = nullptr;
+        if (cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return PeerPoison{};
         }
-        g_device_ok[dev] = ok;
-    });
-    return g_device_ok[dev] ? &g_devices[dev] : nullptr;
+        std::memset(h, 0, 64);
+        if (cudaHostGetDevicePointer(&d, h, 0) != cudaSuccess) {
+            (void)cudaGetLastError();
+            cudaFreeHost(h);
+            return PeerPoison{};
+        }
+        g_poison[dev].host = static_cast<volatile int32_t*>(h);
+        g_poison[dev].device = static_cast<int32_t*>(d);
+    }
+    return g_poison[dev];
+}
+
+namespace {
+std::atomic<int> g_knobs[NNB200_KNOB_COUNT] = {{-1}, {-1}, {-1}, {-1}, {-1}, {-1}, {-1}};
+}
+
+int knob(int id)
+{
+    return (id >= 0 && id < NNB200_KNOB_COUNT) ? g_knobs[id].load(std::memory_order_relaxed) : -1;
 }
 
 void note_launch(int n)
@@ -119,6 +173,17 @@ bool valid_i8_args(const nnb200_gemm_i8_args* a)
     }
     if ((a->a_stride_k != 1 && a->a_stride_m != 1) || (a->w_stride_k != 1 && a->w_stride_n != 1)) {
         return false;  // one of the two strides of each operand is the contiguous one
+    }
+    // Natural alignment of everything a kernel reads or writes as 2- or 4-byte words, and the
+    // workspace's 16 bytes: a misaligned pointer is refused here instead of faulting on the GPU.
+    const auto misaligned = [](const void* p, uintptr_t to) { return (reinterpret_cast<uintptr_t>(p) & (to - 1)) != 0; };
+    const uintptr_t out_align = a->out_kind == NNB200_OUT_S32 || a->out_kind == NNB200_OUT_F32 ? 4
+                              : a->out_kind == NNB200_OUT_F16 ? 2 : 1;
+    const uintptr_t bias_align = a->out_kind == NNB200_OUT_F16 ? 2 : 4;
+    if (misaligned(a->out, out_align) || misaligned(a->bias, bias_align) || misaligned(a->scale_a, 4) ||
+        misaligned(a->scale_w, 4) || misaligned(a->zp_a, 4) || misaligned(a->zp_w, 4) || misaligned(a->r_w, 4) ||
+        misaligned(a->workspace, 16)) {
+        return false;
     }
     return true;
 }
@@ -350,6 +415,11 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
     const size_t rw_bytes = (static_cast<size_t>(a->n) * 4 + 255) & ~size_t(255);
 
     if (a->num_peer_outs != 0) {
+        // A rank barrier that ran out of time earlier leaves the gathered outputs suspect.
+        const PeerPoison poison = peer_poison_for_current_device(false);
+        if (poison.host != nullptr && *poison.host != 0) {
+            return NNB200_INTERNAL;
+        }
         // Sharded write-back: validated here so that a refused call has launched nothing.
         const auto mis16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; };
         bool ok = a->num_peer_outs > 0 && a->num_peer_outs <= 7 && a->batch == 1 &&
@@ -360,6 +430,15 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
             ok = a->peer_out[i] != nullptr && !mis16(a->peer_out[i]);
         }
         if (!ok) {
+            return NNB200_UNSUPPORTED;
+        }
+    }
+
+    // Launchability of every batch element is settled before the first launch, so that a
+    // refusal leaves the outputs untouched: the generic engine's grid has 65535 rows of 32.
+    for (int64_t b = 0; b < a->batch; ++b) {
+        const int e = a->batch == 1 ? engine0 : pick_i8_engine(a, problem_of(a, b));
+        if (e == NNB200_ENGINE_GENERIC && (a->m + 31) / 32 > 65535) {
             return NNB200_UNSUPPORTED;
         }
     }
@@ -650,7 +729,18 @@ int nnb200_rank_barrier(int32_t* const* flags_by_rank, int32_t world, int32_t ra
     if (dev == nullptr) {
         return NNB200_INTERNAL;
     }
-    return launch_rank_barrier(flags_by_rank, world, rank, limit_cycles, *dev, static_cast<cudaStream_t>(stream));
+    // An earlier barrier on this device ran out of time: some rank's tiles may never have
+    // landed, so every later sharded call is refused until nnb200_take_device_error has been
+    // called (which reports code 8 and clears the state).
+    const PeerPoison poison = peer_poison_for_current_device(true);
+    if (poison.host == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    if (*poison.host != 0) {
+        return NNB200_INTERNAL;
+    }
+    return launch_rank_barrier(flags_by_rank, world, rank, limit_cycles, poison.device, *dev,
+                               static_cast<cudaStream_t>(stream));
 }
 
 int nnb200_take_device_error(int32_t* code)
@@ -664,6 +754,10 @@ int nnb200_take_device_error(int32_t* code)
     }
     if (cudaMemcpy(code, dev->error_word, sizeof(int32_t), cudaMemcpyDeviceToHost) != cudaSuccess) {
         return NNB200_INTERNAL;
+    }
+    const PeerPoison poison = peer_poison_for_current_device(false);
+    if (poison.host != nullptr) {
+        *poison.host = 0;
     }
     const int32_t zero = 0;
     return cuda_status(cudaMemcpy(dev->error_word, &zero, sizeof(zero), cudaMemcpyHostToDevice));
@@ -817,6 +911,19 @@ int nnb200_is_device_pointer(const void* p)
 uint64_t nnb200_launch_count(void)
 {
     return g_launches.load(std::memory_order_relaxed);
+}
+
+int nnb200_set_knob(int id, int value)
+{
+    if (id < 0 || id >= NNB200_KNOB_COUNT) {
+        return INT32_MIN;
+    }
+    return g_knobs[id].exchange(value < 0 ? -1 : value, std::memory_order_relaxed);
+}
+
+int nnb200_get_knob(int id)
+{
+    return (id >= 0 && id < NNB200_KNOB_COUNT) ? knob(id) : INT32_MIN;
 }
 
 const char* nnb200_version(void)

@@ -834,9 +834,9 @@ int launch_q4_1_two_pass(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
     }
     // CTA-pair form (256-row tiles over two SMs) for tall problems; measured 1.2 % faster than the
     // single-CTA form on M=2048, N=14336, K=4096 (208.5 us against 211 us for the whole call).
-    // NNB200_F16_PAIR=0 turns it off, =2 makes a device that cannot co-schedule pairs an error.
-    const char* e = getenv("NNB200_F16_PAIR");
-    const char pair_mode = e != nullptr ? e[0] : '1';
+    // Knob F16_PAIR = 0 turns it off, 2 makes a device that cannot co-schedule pairs an error.
+    const int pair_knob = knob(NNB200_KNOB_F16_PAIR);
+    const char pair_mode = pair_knob < 0 ? '1' : static_cast<char>('0' + (pair_knob > 2 ? 1 : pair_knob));
     if (pair_mode != '0' && q.m >= 4 * kBlockM) {
         // Same width rule with 256-row tiles over sm_count / 2 pairs.
         const int bn2 = pick_bn((static_cast<int>(q.m) + 1) / 2, static_cast<int>(q.n), dev.sm_count / 2);

@@ -629,14 +629,14 @@ bool skinny_i8_supported(const I8Problem& p)
 // Hence: with one wave, share when the busiest CTA sheds at least 30 K blocks, plus 0.7 per row
 // above 12; with several waves, when the last one is less than 9/10 full, a share is at least 48
 // K blocks and there are at most 64 rows.
-// NNB200_I8_SHARE_K=0 turns the split off; =2 offers it from 8 K blocks per SM (measurement, tests).
+// Knob I8_SHARE_K = 0 turns the split off; 2 offers it from 8 K blocks per SM (measurement, tests).
 size_t skinny_i8_split_bytes(const I8Problem& p, const DeviceInfo& dev)
 {
     if (!skinny_i8_supported(p)) {
         return 0;
     }
-    const char* e = getenv("NNB200_I8_SHARE_K");
-    const char mode = e != nullptr ? e[0] : '1';
+    const int share_knob = knob(NNB200_KNOB_I8_SHARE_K);
+    const char mode = share_knob < 0 ? '1' : static_cast<char>('0' + (share_knob > 2 ? 1 : share_knob));
     if (mode == '0') {
         return 0;
     }

@@ -924,8 +924,8 @@ int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8E
     // (126 MB on B200), so that W is read from DRAM once per group.
     int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(kBlockM) * (k > 0 ? k : 1)));
     group_m = group_m < 4 ? 4 : group_m;
-    if (const char* e = getenv("NNB200_GROUP_M")) {
-        group_m = atoi(e) > 0 ? atoi(e) : group_m;
+    if (knob(NNB200_KNOB_GROUP_M) > 0) {
+        group_m = knob(NNB200_KNOB_GROUP_M);
     }
     kernel<<<grid, kNumThreads, kSmem, stream>>>(map_a, map_w, maps, ep, m, n, k, idesc, vec_ok, group_m,
                                                  dev.error_word);
@@ -939,12 +939,12 @@ int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, cons
 {
     if (ep.num_peers > 0) {
         // Sharded write-back exists for the 8-bit destinations and 128-column groups.
-        // NNB200_I8_PEER_STAGING=1 / 2 forces the staging depth (measurement aid).
+        // knob I8_PEER_STAGING = 1 / 2 forces the staging depth (measurement aid).
         // Up to three peers (measured at one and three: 0.380 -> 0.346 and 0.262 -> 0.237 ms per step) the
         // deeper ring pays; from four on the stores dominate and the measured form, two staging tiles, stays.
         bool single = ep.num_peers <= 3;
-        if (const char* e = getenv("NNB200_I8_PEER_STAGING")) {
-            single = e[0] == '1' ? true : (e[0] == '2' ? false : single);
+        if (const int staging = knob(NNB200_KNOB_I8_PEER_STAGING); staging == 1 || staging == 2) {
+            single = staging == 1;
         }
         if constexpr (BN == 256 || BN == 128) {
             if (kind == NNB200_OUT_S8) {
@@ -1029,8 +1029,7 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
             }
         }
     }
-    if (const char* e = getenv("NNB200_I8_BN")) {  // measurement aid
-        const int v = atoi(e);
+    if (const int v = knob(NNB200_KNOB_I8_BN); v > 0) {  // measurement aid
         if (v == 512 || v == 448 || v == 384 || v == 320 || v == 256 || v == 224 || v == 192 || v == 128 || v == 64) {
             bn = v;
         }
@@ -1056,10 +1055,10 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
     const uint32_t a_fmt = p.a_unsigned ? 0u : 1u;
 
     // CTA-pair form for tall problems with at least a full wave of 256-row tiles.
-    // NNB200_I8_PAIR=0 turns it off, =2 makes a device that cannot co-schedule pairs an error.
+    // Knob I8_PAIR = 0 turns it off, 2 makes a device that cannot co-schedule pairs an error.
     {
-        const char* pe = getenv("NNB200_I8_PAIR");
-        const char pair_mode = pe != nullptr ? pe[0] : '0';
+        const int pair_knob = knob(NNB200_KNOB_I8_PAIR);
+        const char pair_mode = pair_knob < 0 ? '0' : static_cast<char>('0' + (pair_knob > 2 ? 1 : pair_knob));
         const int64_t pair_tiles = static_cast<int64_t>((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + 255) / 256);
         if (pair_mode != '0' && ep.num_peers == 0 && m >= 4 * kBlockM && pair_tiles >= dev.sm_count / 2 && bn == 256) {
             const int st = launch_pair_bn<256>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);

@@ -28,6 +28,19 @@ struct DeviceInfo {
 // State of the calling thread's current device; nullptr on a CUDA error.
 const DeviceInfo* current_device_info();
 
+// Value of a measurement switch (NNB200_KNOB_*); negative = default.
+int knob(int id);
+
+// Sticky "a rank-barrier wait ran out" word of the current device: one int32 in pinned host
+// memory that the barrier kernel sets through its device alias and the host reads without
+// synchronising.  Created on first use (a set-up step: it allocates pinned memory once per
+// device).  Both null on failure.
+struct PeerPoison {
+    volatile int32_t* host = nullptr;
+    int32_t* device = nullptr;
+};
+PeerPoison peer_poison_for_current_device(bool create);
+
 // Count a kernel launch (nnb200_launch_count).
 void note_launch(int n = 1);
 
@@ -89,7 +102,7 @@ int launch_i8_pack(const void* w, int64_t n, int64_t k, int64_t stride_n, int64_
 // Device-side barrier among up to 8 GPUs: flags_by_rank[r] is rank r's flag array (int32[16],
 // zeroed once), mapped into this process; limit_cycles <= 0 means the default wait limit.
 int launch_rank_barrier(int32_t* const* flags_by_rank, int world, int rank, long long limit_cycles,
-                        const DeviceInfo& dev, cudaStream_t stream);
+                        int32_t* poison, const DeviceInfo& dev, cudaStream_t stream);
 int launch_interleave_shards(const void* src, void* dst, int64_t m, int64_t row_bytes_per_shard, int g,
                              int64_t dst_pitch_bytes, const DeviceInfo& dev, cudaStream_t stream);
 

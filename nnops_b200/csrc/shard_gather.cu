@@ -51,9 +51,12 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p)
 // One warp per GPU.  Lane 0 advances this rank's epoch; lane r (r != rank) announces it in rank
 // r's flag array and then polls the local slot r until rank r has announced the same epoch.
 // The epoch lives in device memory, so a captured launch stays valid on replay.  The wait is
-// bounded: on expiry the lane records kErrPeerWait and the kernel returns.
+// bounded: on expiry the lane records kErrPeerWait, sets the host-visible poison word (so that
+// the host refuses the next sharded call without having to synchronise) and the kernel
+// returns.  A rank that finds the poison already set does not wait at all: its output is
+// already suspect, and skipping keeps a poisoned pipeline from stalling one limit per step.
 __global__ void rank_barrier_kernel(const RankFlags flags, const int world, const int rank, const long long limit_cycles,
-                                    int32_t* error_word)
+                                    int32_t* error_word, int32_t* poison)
 {
     const int lane = static_cast<int>(threadIdx.x);
     int32_t* mine = flags.by_rank[rank];
@@ -63,13 +66,22 @@ __global__ void rank_barrier_kernel(const RankFlags flags, const int world, cons
         mine[kEpochSlot] = epoch;
     }
     epoch = __shfl_sync(0xFFFFFFFFu, epoch, 0);
+    const bool poisoned = poison != nullptr && *reinterpret_cast<volatile int32_t*>(poison) != 0;
     if (lane < world && lane != rank) {
         st_release_sys(flags.by_rank[lane] + rank, epoch);
+        if (poisoned) {
+            atomicCAS(error_word, 0, kErrPeerWait);
+            return;
+        }
         const long long t0 = clock64();
         uint32_t spins = 0;
         while (static_cast<int32_t>(static_cast<uint32_t>(ld_acquire_sys(mine + lane)) - static_cast<uint32_t>(epoch)) < 0) {
             if ((++spins & 0x3Fu) == 0 && clock64() - t0 > limit_cycles) {
                 atomicCAS(error_word, 0, kErrPeerWait);
+                if (poison != nullptr) {
+                    *reinterpret_cast<volatile int32_t*>(poison) = 1;
+                    __threadfence_system();
+                }
                 break;
             }
         }
@@ -79,14 +91,18 @@ __global__ void rank_barrier_kernel(const RankFlags flags, const int world, cons
 }  // namespace
 
 int launch_rank_barrier(int32_t* const* flags_by_rank, int world, int rank, long long limit_cycles,
-                        const DeviceInfo& dev, cudaStream_t stream)
+                        int32_t* poison, const DeviceInfo& dev, cudaStream_t stream)
 {
     RankFlags f;
     for (int r = 0; r < 8; ++r) {
         f.by_rank[r] = r < world ? flags_by_rank[r] : nullptr;
     }
-    rank_barrier_kernel<<<1, 32, 0, stream>>>(f, world, rank, limit_cycles > 0 ? limit_cycles : kWaitLimitCycles,
-                                              dev.error_word);
+    // Ranks of one job drift apart by far more than a pipeline stage ever waits (a lazy module
+    // load, a collector pause, a data loader on one rank), so the default limit here is about
+    // half a minute of SM clocks, not the two seconds of the in-kernel pipeline waits.
+    constexpr long long kRankBarrierLimitCycles = 60'000'000'000LL;
+    rank_barrier_kernel<<<1, 32, 0, stream>>>(f, world, rank, limit_cycles > 0 ? limit_cycles : kRankBarrierLimitCycles,
+                                              dev.error_word, poison);
     note_launch();
     return cuda_status(cudaGetLastError());
 }

@@ -8,8 +8,10 @@
 // scratch (row sums of A and of W); nnb200_gemm_i8 takes them from the caller's workspace,
 // this entry point keeps them in a fixed array inside the library image instead.
 //
-// The array lives in device memory of every GPU that loads the library, from load until the
-// process exits, whether or not this entry point is ever called.
+// Every GPU on which the library's device code gets loaded holds its own copy of the array
+// until the process exits (with lazy module loading that is from the first use of a kernel or
+// symbol of this file on that GPU, otherwise from library load).  All calls on one GPU share
+// that copy: two calls that overlap on the GPU race on it, so the caller serialises them.
 
 #include <cuda_runtime.h>
 
@@ -25,23 +27,28 @@ namespace {
 // the symbol; the address kernels can use is looked up per device below.
 static __device__ __align__(256) unsigned char g_static_scratch[NNB200_STATIC_SCRATCH_BYTES];
 
-void* g_scratch_ptr[kMaxDevices];
-cudaError_t g_scratch_err[kMaxDevices];
-std::once_flag g_scratch_once[kMaxDevices];
+std::mutex g_scratch_mutex;
+void* g_scratch_ptr[kMaxDevices];   // non-null once the lookup has succeeded on that device
 
-// Device address of the current device's copy of the array; nullptr on failure.  Runs its
-// lookup once per device, with that device current (the caller's device is the one asked).
+// Device address of the current device's copy of the array; nullptr on failure.  The lookup
+// runs with the caller's device current and is remembered only when it succeeds: a first call
+// made too early (during stream capture, say) fails, clears the CUDA error it raised, and a
+// later call tries again.
 void* static_scratch_for_current_device()
 {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
         return nullptr;
     }
-    std::call_once(g_scratch_once[dev], [dev] {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_ptr[dev] == nullptr) {
         void* p = nullptr;
-        g_scratch_err[dev] = cudaGetSymbolAddress(&p, g_static_scratch);
-        g_scratch_ptr[dev] = g_scratch_err[dev] == cudaSuccess ? p : nullptr;
-    });
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        g_scratch_ptr[dev] = p;
+    }
     return g_scratch_ptr[dev];
 }
 
@@ -63,6 +70,10 @@ extern "C" int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, vo
         return NNB200_OUT_OF_MEMORY;
     }
     if (need > 0) {
+        const DeviceInfo* info = current_device_info();
+        if (info != nullptr && info->cc_major != 10) {
+            return NNB200_UNSUPPORTED;  // the library image only holds sm_100a code, this array included
+        }
         void* p = static_scratch_for_current_device();
         if (p == nullptr) {
             return NNB200_INTERNAL;

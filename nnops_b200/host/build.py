@@ -24,7 +24,8 @@ HOST = Path(__file__).resolve().parent
 ROOT = HOST.parent.parent
 LIB_DIR = HOST.parent / "lib"
 BIN_DIR = ROOT / "tests" / "cpp" / "_bin"
-REFERENCE_ROOT = Path(os.environ.get("NNOPS_REFERENCE_ROOT", "/root/reference"))
+# The nnops source tree: NNOPS_REFERENCE_ROOT, or a checkout named "reference" beside this repository.
+REFERENCE_ROOT = Path(os.environ.get("NNOPS_REFERENCE_ROOT", str(ROOT.parent / "reference")))
 CXX = os.environ.get("NNB200_CXX", "/usr/bin/g++")
 CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
 

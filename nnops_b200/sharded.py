@@ -68,7 +68,8 @@ class ShardedLinearI8:
 
     def __init__(self, w_shard: torch.Tensor, *, n_total: int, world: int, rank: int, group=None,
                  out_kind: str = "s8", bias_shard=None, scale_w_shard=1.0, scale_a=1.0, out_scale=1.0, out_zp=0,
-                 relu: bool = False, mode: str = "nccl", rank_order: str = "device"):
+                 relu: bool = False, mode: str = "nccl", rank_order: str = "device",
+                 barrier_limit_cycles: int = 0):
         lo, hi = shard_bounds(n_total, world, rank)
         if w_shard.shape[0] != hi - lo:
             raise ValueError("weight shard has the wrong number of rows")
@@ -91,6 +92,10 @@ class ShardedLinearI8:
         if rank_order not in ("device", "nccl"):
             raise ValueError("rank_order must be 'device' or 'nccl'")
         self.rank_order = rank_order     # how fused mode orders the ranks after the write-back
+        # Wait limit of the device-side rank barrier in SM clock cycles; 0 = the library's default
+        # (about half a minute: far longer than the pipeline waits inside a kernel, because ranks
+        # drift apart by seconds for ordinary reasons).
+        self.barrier_limit_cycles = int(barrier_limit_cycles)
         self._flags = None
 
     # ---- outputs -------------------------------------------------------------------------
@@ -167,13 +172,24 @@ class ShardedLinearI8:
         if self._flags is not None:
             dev = self.w.device
             with torch.cuda.device(dev):
-                capi.check(capi.lib().nnb200_rank_barrier(self._flags, self.world, self.rank, 0,
+                capi.check(capi.lib().nnb200_rank_barrier(self._flags, self.world, self.rank, self.barrier_limit_cycles,
                                                           torch.cuda.current_stream(dev).cuda_stream),
                            "nnb200_rank_barrier")
             return
         if self._token is None:
             self._token = torch.zeros(1, dtype=torch.int32, device=self.w.device)
         dist.all_reduce(self._token, group=self.group)
+
+    def check(self) -> None:
+        """Synchronise this rank's device and raise if a bounded wait ran out since the last
+        check: the outputs gathered since then are valid only if this passes.  (Without calling
+        it, a barrier that timed out still makes the NEXT ``forward`` / ``rank_barrier`` on this
+        rank fail with status ``internal`` -- the library keeps a sticky flag the host reads
+        without synchronising.)"""
+        with torch.cuda.device(self.w.device):
+            code = capi.take_device_error()
+        if code != 0:
+            raise capi.Nnb200Error(capi.INTERNAL, f"device error word = {code}")
 
     # ---- compute -------------------------------------------------------------------------
 

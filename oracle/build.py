@@ -18,7 +18,8 @@ from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REFERENCE_ROOT = Path(os.environ.get("NNOPS_REFERENCE_ROOT", "/root/reference"))
+# The nnops source tree: NNOPS_REFERENCE_ROOT, or a checkout named "reference" beside this repository.
+REFERENCE_ROOT = Path(os.environ.get("NNOPS_REFERENCE_ROOT", str(HERE.parent.parent / "reference")))
 CXX = os.environ.get("NNOPS_ORACLE_CXX", "/usr/bin/g++")
 CC = os.environ.get("NNOPS_ORACLE_CC", "/usr/bin/gcc")
 

@@ -36,3 +36,18 @@ def _no_device_error(request):
     if request.node.get_closest_marker("gpu") is not None:
         from nnops_b200 import capi
         assert capi.take_device_error() == 0
+
+
+@pytest.fixture
+def knobs(nnb200_lib):
+    """Set measurement switches of the library for one test; every one is restored afterwards."""
+    from nnops_b200 import capi
+    saved = {}
+
+    def set_(name, value):
+        prev = capi.set_knob(name, value)
+        saved.setdefault(name, prev)
+
+    yield set_
+    for name, prev in saved.items():
+        capi.set_knob(name, prev)

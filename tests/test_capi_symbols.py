@@ -41,3 +41,42 @@ def test_argument_validation_without_gpu(nnb200_lib):
     q = capi.Q41Args()
     q.m, q.n, q.k = 1, 4, 64
     assert nnb200_lib.nnb200_linear_q4_1(C.byref(q), None) == capi.INVALID_ARGUMENT  # null pointers
+
+
+def test_misaligned_pointers_are_refused_before_any_launch(nnb200_lib):
+    """Arrays read as 4-byte words (bias, scales, zero points, row sums), f16 bias and the
+    16-byte workspace: a misaligned pointer is INVALID_ARGUMENT, not a device fault."""
+    from nnops_b200 import capi
+    base = 0x7000_0000_1000            # never dereferenced: validation comes first
+
+    def block():
+        a = capi.GemmI8Args()
+        a.a, a.w, a.out = base, base + 0x1000, base + 0x2000
+        a.m, a.n, a.k, a.batch = 4, 4, 16, 1
+        a.a_stride_m, a.a_stride_k, a.w_stride_n, a.w_stride_k, a.ldc = 16, 1, 16, 1, 4
+        a.scale_a_scalar = a.scale_w_scalar = a.out_scale = 1.0
+        return a
+
+    before = nnb200_lib.nnb200_launch_count()
+    for field, off in [("bias", 2), ("scale_a", 1), ("scale_w", 2), ("zp_a", 3), ("zp_w", 2), ("r_w", 1),
+                       ("workspace", 8), ("out", 2)]:
+        a = block()
+        setattr(a, field, base + 0x3000 + off)
+        assert nnb200_lib.nnb200_gemm_i8(C.byref(a), None) == capi.INVALID_ARGUMENT, field
+        if field != "workspace":       # the allocation-free entry ignores the caller's workspace
+            assert nnb200_lib.nnb200_gemm_i8_static_scratch(C.byref(a), None) == capi.INVALID_ARGUMENT, field
+    a = block()
+    a.out_kind = capi.OUT_KINDS["f16"]
+    a.bias = base + 0x3001             # f16 bias: 2-byte alignment
+    assert nnb200_lib.nnb200_gemm_i8(C.byref(a), None) == capi.INVALID_ARGUMENT
+    assert nnb200_lib.nnb200_launch_count() == before
+
+
+def test_knobs_round_trip(nnb200_lib):
+    from nnops_b200 import capi
+    assert nnb200_lib.nnb200_get_knob(capi.KNOBS["i8_bn"]) == -1
+    assert capi.set_knob("i8_bn", 192) == -1
+    assert nnb200_lib.nnb200_get_knob(capi.KNOBS["i8_bn"]) == 192
+    assert capi.set_knob("i8_bn", -5) == 192
+    assert nnb200_lib.nnb200_get_knob(capi.KNOBS["i8_bn"]) == -1
+    assert nnb200_lib.nnb200_set_knob(99, 1) == -(2 ** 31)

@@ -135,12 +135,12 @@ def test_skinny_engine(cuda_device, nnb200_lib, m, out_kind):
 
 @pytest.mark.parametrize("shape", [(1280, 16384), (11008, 4096), (28672, 1024), (2999, 8192 + 48), (19000, 2048)])
 @pytest.mark.parametrize("m", [9, 16, 33, 64, 100, 128])
-def test_skinny_engine_shared_k(cuda_device, nnb200_lib, monkeypatch, m, shape):
+def test_skinny_engine_shared_k(cuda_device, nnb200_lib, knobs, m, shape):
     """Layers whose 128-channel tiles do not fill the SMs evenly: every SM takes an equal share
     of all K blocks, tiles are finished by whichever part arrives last.  Few tiles with a long K
     (a tile in a dozen parts), ragged N and K, zero points (both halves of the workspace in use),
     and the same call with the minimum workspace (whole tiles per SM)."""
-    monkeypatch.setenv("NNB200_I8_SHARE_K", "2")   # offer the split for short shares too
+    knobs("i8_share_k", 2)   # offer the split for short shares too
     n, k = shape
     kinds = ["s32", "s8", "u8", "f32", "f16"]
     out_kind = kinds[(m + n) % 5]
@@ -158,8 +158,8 @@ def test_skinny_engine_shared_k_by_default_on_long_streams(cuda_device, nnb200_l
               expect_engine="skinny", expect_shared_k=False, seed=6)
 
 
-def test_skinny_engine_shared_k_not_offered_when_tiles_fill_the_sms(cuda_device, nnb200_lib, monkeypatch):
-    monkeypatch.setenv("NNB200_I8_SHARE_K", "2")
+def test_skinny_engine_shared_k_not_offered_when_tiles_fill_the_sms(cuda_device, nnb200_lib, knobs):
+    knobs("i8_share_k", 2)
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     _run_case(cuda_device, 24, 128 * sms, 2048, out_kind="s8", per_channel=True, out_scale=40.0, engine="skinny",
               expect_engine="skinny", expect_shared_k=False)
@@ -209,10 +209,10 @@ def test_decode_destinations(cuda_device, nnb200_lib, out_kind):
 
 
 @pytest.mark.parametrize("bn", [320, 384, 448, 512])
-def test_wide_single_wave_tiles(cuda_device, nnb200_lib, bn, monkeypatch):
+def test_wide_single_wave_tiles(cuda_device, nnb200_lib, bn, knobs):
     """Tiles wider than 256 columns (two MMAs per k-step, one accumulator): forced through the
     measurement override, once with one tile per CTA and once with several per CTA."""
-    monkeypatch.setenv("NNB200_I8_BN", str(bn))
+    knobs("i8_bn", bn)
     _run_case(cuda_device, 300, 1500, 512, out_kind="s8", relu=True, per_token=True, per_channel=True,
               zero_points=True, out_scale=1.9, out_zp=2, engine="umma", seed=bn)
     _run_case(cuda_device, 1100, 4000 + bn, 256, out_kind="s32", per_channel=True, engine="umma", seed=bn + 1)
@@ -221,11 +221,11 @@ def test_wide_single_wave_tiles(cuda_device, nnb200_lib, bn, monkeypatch):
 
 @pytest.mark.parametrize("case", [(1100, 9000, 512, "s8"), (2048, 9472, 256, "s32"), (777, 19000, 384, "f16"),
                                   (4096, 4736, 640, "u8"), (600, 20000, 96, "f32")])
-def test_cta_pair_form(cuda_device, nnb200_lib, case, monkeypatch):
+def test_cta_pair_form(cuda_device, nnb200_lib, case, knobs):
     """256-row tiles over clusters of two CTAs (tcgen05.mma cta_group::2): forced ("2" = the pair
     form or an error), ragged M / N / K, every destination."""
     m, n, k, kind = case
-    monkeypatch.setenv("NNB200_I8_PAIR", "2")
+    knobs("i8_pair", 2)
     _run_case(cuda_device, m, n, k, out_kind=kind, relu=True, per_token=True, per_channel=True, zero_points=True,
               out_scale=0.9, out_zp=0 if kind == "s32" else 3, engine="umma", seed=m + n)
 
@@ -300,16 +300,30 @@ def test_config2_bit_exact(cuda_device, nnb200_lib, out_scale):
         assert inside > want.size // 4, "in-range variant must exercise the rounding path"
 
 
-def test_config5_rows_and_linearity(cuda_device, nnb200_lib):
-    """Full-size sharded shape on one GPU: a sample of rows against the oracle, plus an exact
-    size-independent property of the s32 route (additivity in A)."""
-    c = synth.config5()
-    ta, tw = torch.from_numpy(c.a).to(cuda_device), torch.from_numpy(c.w).to(cuda_device)
-    got = ops.gemm_i8(ta, tw, **c.kwargs())
-    rows = np.random.default_rng(0).choice(c.a.shape[0], 48, replace=False)
-    kw = c.kwargs()
-    want = oracle.gemm_i8(np.ascontiguousarray(c.a[rows]), c.w, **kw)
-    assert np.array_equal(got[torch.from_numpy(rows).to(cuda_device)].cpu().numpy(), want)
+def test_config5_whole_output_and_linearity(cuda_device, nnb200_lib):
+    """Full-size sharded shape on one GPU: every one of the 4096 x 28672 output bytes against the
+    compiled reference CPU route (the reference's own CUDA tests memcmp whole outputs the same
+    way, tests/test_cuda_linear.cpp:190-351), in-range variant included so that the rounding
+    path is exercised on every tile; then an exact size-independent property of the s32 route
+    (additivity in A).  Without the compiled reference (no VNNI on the host) the C restatement
+    checks a sample of rows instead."""
+    for out_scale in (0.05, 1.6):
+        c = synth.config5(out_scale=out_scale)
+        ta, tw = torch.from_numpy(c.a).to(cuda_device), torch.from_numpy(c.w).to(cuda_device)
+        got = ops.gemm_i8(ta, tw, **c.kwargs())
+        kw = c.kwargs()
+        if oracle.have_ref():
+            want = oracle.gemm_i8(c.a, c.w, impl="ref", **kw)
+            got_h = got.cpu().numpy()
+            if not np.array_equal(got_h, want):
+                bad = np.argwhere(got_h != want)
+                raise AssertionError(f"{len(bad)} of {want.size} bytes differ; first {bad[:5].tolist()}")
+            if out_scale > 1:
+                assert np.count_nonzero((want > 0) & (want < 127)) > want.size // 4
+        else:
+            rows = np.random.default_rng(0).choice(c.a.shape[0], 48, replace=False)
+            want = oracle.gemm_i8(np.ascontiguousarray(c.a[rows]), c.w, **kw)
+            assert np.array_equal(got[torch.from_numpy(rows).to(cuda_device)].cpu().numpy(), want)
     # Linearity: (A1 + A2) W^T == A1 W^T + A2 W^T exactly in int32 (values halved to stay in s8).
     a1 = (ta // 2)
     a2 = ta - a1

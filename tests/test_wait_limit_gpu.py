@@ -84,6 +84,40 @@ def test_rank_barrier_protocol_on_one_gpu(nnb200_lib):
     assert capi.take_device_error() == 0 and solo[0][8].item() == 1
 
 
+def test_rank_barrier_timeout_is_sticky_on_the_host(nnb200_lib):
+    """A barrier that ran out of time must not pass silently: until the error word has been
+    read, the next barrier and the next sharded GEMM on the device are refused on the host,
+    with nothing launched."""
+    import ctypes as C
+    from nnops_b200 import capi, ops
+
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    arrays, table = _flag_arrays(dev, 2)
+    lib = capi.lib()
+    assert capi.take_device_error() == 0
+    capi.check(lib.nnb200_rank_barrier(table, 2, 0, 2_000_000, stream), "nnb200_rank_barrier")   # nobody answers
+    torch.cuda.synchronize(dev)
+    before = lib.nnb200_launch_count()
+    assert lib.nnb200_rank_barrier(table, 2, 0, 2_000_000, stream) == capi.INTERNAL
+    a = torch.zeros((256, 256), dtype=torch.int8, device=dev)
+    w = torch.zeros((256, 256), dtype=torch.int8, device=dev)
+    out = torch.full((256, 512), 9, dtype=torch.int8, device=dev)
+    other = torch.full((256, 512), 9, dtype=torch.int8, device=dev)
+    args = ops.gemm_i8_args(a, w, out[:, :256], out_kind="s8")
+    args.num_peer_outs = 1
+    args.peer_out[0] = other.data_ptr()
+    assert lib.nnb200_gemm_i8(C.byref(args), stream) == capi.INTERNAL
+    assert lib.nnb200_launch_count() == before
+    torch.cuda.synchronize(dev)
+    assert bool((out == 9).all()) and bool((other == 9).all())
+    assert capi.take_device_error() == capi.DEVICE_ERROR_PEER_WAIT          # reading it clears the state
+    capi.check(lib.nnb200_gemm_i8(C.byref(args), stream), "nnb200_gemm_i8")  # accepted again
+    torch.cuda.synchronize(dev)
+    assert bool((out[:, :256] == 0).all()) and bool((other[:, :256] == 0).all())
+    assert capi.take_device_error() == 0
+
+
 def test_rank_barrier_arguments_checked(nnb200_lib):
     from nnops_b200 import capi
 

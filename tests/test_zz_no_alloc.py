@@ -5,7 +5,9 @@ allocate device memory themselves (a plugin inside an inference runtime, a laten
 loop): its scratch is a fixed array inside the library.  Here it is driven through the C ABI on
 two different problems in a row -- the second smaller than the first, so stale contents of the
 shared array would show -- and each result must equal, byte for byte, what nnb200_gemm_i8
-produces with a caller-provided workspace.  Collected last on purpose.
+produces with a caller-provided workspace AND what the CPU oracle computes from the same
+bytes.  A batched call and a call that brings the weights' row sums with it (a packed weight)
+follow.  Collected last on purpose.
 """
 import ctypes as C
 
@@ -13,6 +15,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from nnops_b200 import capi, ops
 
 pytestmark = pytest.mark.gpu
@@ -44,6 +47,44 @@ def test_static_scratch_matches_workspace_entry(cuda_device, nnb200_lib):
         capi.check(nnb200_lib.nnb200_gemm_i8_static_scratch(C.byref(args), stream), "static_scratch")
         torch.cuda.synchronize()
         assert torch.equal(got, want)
+        kw_np = {key: (v.copy() if isinstance(v, np.ndarray) else v) for key, v in kw.items()}
+        expect = oracle.gemm_i8(a.cpu().numpy(), w.cpu().numpy(), **kw_np)
+        assert np.array_equal(got.cpu().numpy(), expect), "differs from the CPU oracle"
+
+
+def test_static_scratch_batched_and_packed_row_sums(cuda_device, nnb200_lib):
+    """Two more uses of the fixed array: a batch of two (each batch element has its own slice of
+    the scratch) and a call whose weight row sums come precomputed from a packed blob."""
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    rng = np.random.default_rng(11)
+    m, n, k = 90, 200, 256
+    a = torch.from_numpy(rng.integers(0, 256, (2, m, k), dtype=np.uint8)).to(cuda_device)
+    w = torch.from_numpy(rng.integers(-127, 128, (n, k), dtype=np.int8)).to(cuda_device)
+    kw = dict(out_kind="s8", out_scale=3.0, out_zp=-3, scale_a=0.02, zp_a=128,
+              scale_w=rng.uniform(0.001, 0.02, n).astype(np.float32), zp_w=rng.integers(-9, 10, n).astype(np.int32))
+    want = ops.gemm_i8(a, w, **kw)
+    got = torch.empty_like(want)
+    keep = []
+    args = ops.gemm_i8_args(a, w, got, keep=keep, **kw)
+    assert args.batch == 2 and args.workspace_bytes > 0
+    args.workspace, args.workspace_bytes = None, 0
+    capi.check(nnb200_lib.nnb200_gemm_i8_static_scratch(C.byref(args), stream), "static_scratch batch")
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    for b in range(2):
+        expect = oracle.gemm_i8(a[b].cpu().numpy(), w.cpu().numpy(), **kw)
+        assert np.array_equal(got[b].cpu().numpy(), expect)
+
+    packed = ops.prepack_i8(w, scale_w=kw["scale_w"], zp_w=kw["zp_w"])
+    kw2 = dict(kw, scale_w=packed.scale_w, zp_w=packed.zp_w)
+    want2 = ops.gemm_i8(a[0], packed.w, r_w=packed.r_w, **kw2)
+    got2 = torch.empty_like(want2)
+    args = ops.gemm_i8_args(a[0], packed.w, got2, keep=keep, r_w=packed.r_w, **kw2)
+    args.workspace, args.workspace_bytes = None, 0
+    capi.check(nnb200_lib.nnb200_gemm_i8_static_scratch(C.byref(args), stream), "static_scratch packed")
+    torch.cuda.synchronize()
+    assert torch.equal(got2, want2)
+    assert np.array_equal(got2.cpu().numpy(), oracle.gemm_i8(a[0].cpu().numpy(), w.cpu().numpy(), **kw))
 
 
 def test_static_scratch_rejects_oversize(cuda_device, nnb200_lib):
