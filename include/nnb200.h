@@ -226,7 +226,8 @@ typedef struct nnb200_q4_1_args {
     void* workspace;
     size_t workspace_bytes;
     int32_t force_engine; /* 0 auto, 1 fused tensor-core GEMM, 2 GEMV (best), 3 GEMV on CUDA cores, 4 GEMV with
-                             warp MMA, 5 two-pass GEMM (needs the workspace) */
+                             warp MMA after per-weight dequantisation, 5 two-pass GEMM (needs the workspace),
+                             6 GEMV with warp MMA on raw nibbles, scale and minimum applied per block afterwards */
     int32_t flags;        /* NNB200_Q4_FLAG_* */
 } nnb200_q4_1_args;
 

@@ -544,10 +544,19 @@ int nnb200_q4_1_engine(const nnb200_q4_1_args* q)
     if (!valid_q4_args(q)) {
         return -1;
     }
-    // 1 = fused tensor-core GEMM (tcgen05), 3 = GEMV on CUDA cores, 4 = GEMV with warp-level MMA,
-    // 5 = two-pass GEMM (expand to f16 scratch, dense tcgen05 GEMM).
-    const int gemv = (q->force_engine != 3 && q4_1_gemv_mma_supported(*q)) ? 4 : 3;
-    if (q->force_engine == 2 || q->force_engine == 3 || q->force_engine == 4) {
+    // 1 = fused tensor-core GEMM (tcgen05), 3 = GEMV on CUDA cores, 4 = GEMV with warp-level MMA
+    // after per-weight dequantisation, 5 = two-pass GEMM (expand to f16 scratch, dense tcgen05
+    // GEMM), 6 = GEMV with warp-level MMA on raw nibbles and deferred scaling.
+    int gemv = 3;
+    if (q->force_engine != 3) {
+        const bool prefer_dsq = q->force_engine == 6 || (q->force_engine != 4 && knob(NNB200_KNOB_Q4_GEMV) != 1);
+        if (prefer_dsq && q4_1_gemv_dsq_supported(*q)) {
+            gemv = 6;
+        } else if (q4_1_gemv_mma_supported(*q)) {
+            gemv = 4;
+        }
+    }
+    if (q->force_engine == 2 || q->force_engine == 3 || q->force_engine == 4 || q->force_engine == 6) {
         return gemv;
     }
     const bool gemm_ok = q4_1_gemm_umma_supported(*q);
@@ -587,6 +596,7 @@ int nnb200_linear_q4_1(const nnb200_q4_1_args* q, void* stream_v)
     case 1: return launch_q4_1_gemm_umma(*q, *dev, stream);
     case 5: return launch_q4_1_two_pass(*q, *dev, stream);
     case 4: return launch_q4_1_gemv_mma(*q, *dev, stream);
+    case 6: return launch_q4_1_gemv_dsq(*q, *dev, stream);
     default: return launch_q4_1_gemv(*q, *dev, stream);
     }
 }

@@ -84,6 +84,8 @@ int launch_i8_sums(const I8Problem& p, int32_t* r_a, int32_t* r_w, cudaStream_t 
 int launch_q4_1_gemv(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
 int launch_q4_1_gemv_mma(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
 bool q4_1_gemv_mma_supported(const nnb200_q4_1_args& a);
+int launch_q4_1_gemv_dsq(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
+bool q4_1_gemv_dsq_supported(const nnb200_q4_1_args& a);
 int launch_q4_1_gemm_umma(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);
 bool q4_1_gemm_umma_supported(const nnb200_q4_1_args& a);
 int launch_q4_1_two_pass(const nnb200_q4_1_args& a, const DeviceInfo& dev, cudaStream_t stream);

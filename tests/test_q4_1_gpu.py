@@ -35,7 +35,7 @@ def test_decode_matches_oracle_bitwise(cuda_device, nnb200_lib):
         assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("engine", ["gemv_simt", "gemv_mma"])
+@pytest.mark.parametrize("engine", ["gemv_simt", "gemv_mma", "gemv_dsq"])
 @pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 11])
 @pytest.mark.parametrize("a_dtype,out_dtype", [("f16", "f32"), ("f16", "f16"), ("f32", "f32")])
 def test_gemv_small(cuda_device, nnb200_lib, m, a_dtype, out_dtype, engine):
@@ -51,9 +51,13 @@ def test_gemv_small(cuda_device, nnb200_lib, m, a_dtype, out_dtype, engine):
     _close(got.cpu().numpy(), want, RTOL_F32 if out_dtype == "f32" else RTOL_F16)
 
 
+ENGINE_IDS = {"gemv_mma": 4, "gemv_dsq": 6}
+
+
+@pytest.mark.parametrize("engine", ["gemv_mma", "gemv_dsq"])
 @pytest.mark.parametrize("shape", [(1, 16, 128), (4, 40, 384), (8, 130, 4096 + 128), (7, 17, 8192 + 256), (3, 64, 4096),
-                                   (2, 33, 12288)])
-def test_gemv_mma_edges(cuda_device, nnb200_lib, shape):
+                                   (2, 33, 12288), (1, 5000, 2048 + 128), (1, 37, 32768), (2, 2400, 640)])
+def test_gemv_mma_edges(cuda_device, nnb200_lib, shape, engine):
     """Fewer block groups than K-quarter warps, K spanning several staged chunks, channel counts
     off the 16-row tile, and a weight view whose row pitch is wider than its rows."""
     m, n, k = shape
@@ -66,14 +70,20 @@ def test_gemv_mma_edges(cuda_device, nnb200_lib, shape):
     a = rng.standard_normal((m, k)).astype(np.float16)
     ta = torch.from_numpy(a).to(cuda_device)
     tw = torch.from_numpy(wb).to(cuda_device)[:, : nblk * 20]
-    assert ops.q4_1_engine(ta, tw, k, engine="gemv") == 4
-    got = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float32, engine="gemv")
+    # The deferred-scaling engine stages one pass's activations whole in shared memory (64 KB).
+    mp = 1 if m == 1 else (2 if m == 2 else (4 if m <= 4 else 8))      # MMA columns per block
+    fits = mp * (-(-nblk // 8) * 8) * 64 <= 64 * 1024
+    want_id = ENGINE_IDS[engine] if (engine == "gemv_mma" or fits) else 4
+    assert ops.q4_1_engine(ta, tw, k, engine=engine) == want_id
+    assert ops.q4_1_engine(ta, tw, k, engine="gemv") == (6 if fits else 4)
+    got = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float32, engine=engine)
     _close(got.cpu().numpy(), oracle.q4_1_matmul(a, wb_dense, k, out_dtype="f32"), RTOL_F32)
 
 
+@pytest.mark.parametrize("engine", ["gemv_mma", "gemv_dsq"])
 @pytest.mark.parametrize("m", [1, 4, 7])
 @pytest.mark.parametrize("aligned", [True, False])
-def test_gemv_mma_f32_activations(cuda_device, nnb200_lib, m, aligned):
+def test_gemv_mma_f32_activations(cuda_device, nnb200_lib, m, aligned, engine):
     """f32 activations on the warp-MMA engine: each row feeds two MMA columns (hi and lo f16
     parts), four rows per pass; accuracy stays at f32 level."""
     rng = np.random.default_rng(m + 40)
@@ -85,9 +95,11 @@ def test_gemv_mma_f32_activations(cuda_device, nnb200_lib, m, aligned):
     else:
         ta = torch.from_numpy(np.pad(a, ((0, 0), (1, 2)))).to(cuda_device)[:, 1:k + 1]   # 4-byte aligned rows only
     tw = torch.from_numpy(wb).to(cuda_device)
-    assert ops.q4_1_engine(ta, tw, k, engine="gemv") == 4
-    got = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float32, engine="gemv").cpu().numpy()
-    want = oracle.q4_1_matmul(a, wb, k, out_dtype="f32", w_round_f16=True).astype(np.float64)
+    assert ops.q4_1_engine(ta, tw, k, engine=engine) == ENGINE_IDS[engine]
+    got = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float32, engine=engine).cpu().numpy()
+    # The per-weight-dequantising engine rounds each weight to f16 (like the reference's f16
+    # route); the deferred-scaling engine multiplies exact nibbles and scales in f32.
+    want = oracle.q4_1_matmul(a, wb, k, out_dtype="f32", w_round_f16=(engine == "gemv_mma")).astype(np.float64)
     err = np.abs(got.astype(np.float64) - want).max() / np.sqrt(np.mean(want ** 2))
     assert err < 2e-5, err
 
@@ -105,14 +117,33 @@ def test_gemv_falls_back_when_rows_are_not_bulk_copyable(cuda_device, nnb200_lib
     _close(got.cpu().numpy(), oracle.q4_1_matmul(a, wb, k, out_dtype="f32"), RTOL_F32)
 
 
-@pytest.mark.parametrize("engine", ["gemv_simt", "gemv_mma"])
+@pytest.mark.parametrize("engine", ["gemv_simt", "gemv_mma", "gemv_dsq"])
 @pytest.mark.parametrize("m", [1, 8])
 def test_config3_gemv(cuda_device, nnb200_lib, m, engine):
     c = synth.config3(m)
     want = oracle.q4_1_matmul(c.a, c.w_blocks, c.k, out_dtype="f32")
     got = ops.linear_q4_1(torch.from_numpy(c.a).to(cuda_device), torch.from_numpy(c.w_blocks).to(cuda_device), c.k,
-                          out_dtype=torch.float32, engine=engine)
-    _close(got.cpu().numpy(), want, RTOL_F32)
+                          out_dtype=torch.float32, engine=engine).cpu().numpy()
+    _close(got, want, RTOL_F32)
+    if engine == "gemv_dsq":
+        # Exact nibbles, exact products, f32 sums: the only error left is f32 accumulation.
+        err = np.abs(got.astype(np.float64) - want.astype(np.float64)).max() / np.sqrt(np.mean(want.astype(np.float64) ** 2))
+        assert err < 2e-5, err
+
+
+def test_gemv_dsq_subnormal_and_large_activations(cuda_device, nnb200_lib):
+    """The nibbles enter the MMA as f16 subnormals (q * 2^-24): activations from the smallest
+    normal f16 magnitudes to the largest must still give exact products."""
+    rng = np.random.default_rng(77)
+    n, k = 96, 1024
+    wb = synth.q4_1_weights(rng, n, k)
+    for scale in (1e-4, 1.0, 3e3):
+        a = (rng.standard_normal((2, k)) * scale).astype(np.float16)
+        want = oracle.q4_1_matmul(a, wb, k, out_dtype="f32").astype(np.float64)
+        got = ops.linear_q4_1(torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device), k,
+                              out_dtype=torch.float32, engine="gemv_dsq").cpu().numpy().astype(np.float64)
+        err = np.abs(got - want).max() / np.sqrt(np.mean(want ** 2))
+        assert err < 2e-5, (scale, err)
 
 
 @pytest.mark.parametrize("shape", [(128, 128, 64), (128, 256, 256), (130, 300, 512), (64, 1000, 160),
