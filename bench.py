@@ -10,8 +10,8 @@ seeded synthetic tensors.  At N > 1 W, scales and bias are column-sharded N/g pe
 so scaling is "strong".  One step = one pass of that path.  Prints ONE JSON line (rank 0).
 
 ``--impl reference`` times the reference's own CPU implementation of the same path
-(oracle/_ref when it was compiled, else the C restatement) on the host cores, on a bounded
-sample of the same workload.
+(oracle/_ref when it was compiled, else the C restatement) on the host cores, on the same
+whole configuration.
 """
 from __future__ import annotations
 
@@ -149,14 +149,47 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_reference_run(sample_rows: int, steps: int, warmup: int):
-    """Reference CPU route (or the port) on the first ``sample_rows`` rows of A, all of W."""
+def host_cores() -> dict:
+    """Logical CPUs this process may use, and the physical cores / SMT width behind them as
+    /proc/cpuinfo describes them (None where it does not say)."""
+    logical = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    cores, siblings, per_pkg = set(), None, None
+    try:
+        phys = core = None
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                key, _, val = line.partition(":")
+                key, val = key.strip(), val.strip()
+                if key == "physical id":
+                    phys = val
+                elif key == "core id":
+                    core = val
+                elif key == "siblings":
+                    siblings = int(val)
+                elif key == "cpu cores":
+                    per_pkg = int(val)
+                elif key == "" and phys is not None and core is not None:
+                    cores.add((phys, core))
+                    phys = core = None
+    except (OSError, ValueError):
+        pass
+    smt = (siblings // per_pkg) if siblings and per_pkg else None
+    physical = len(cores) if cores else None
+    if physical and smt and physical * smt < logical:
+        physical = None      # a container that hides part of the topology: do not guess
+    return {"logical": logical, "physical": physical, "smt": smt}
+
+
+def cpu_reference_run(rows: int, steps: int, warmup: int, keep_output: bool = False):
+    """Reference CPU route (or the C restatement when it is not runnable here) on the first
+    ``rows`` rows of A against all of W, with all the host threads it can use."""
     import oracle
     from nnops_b200 import synth
     c = synth.config5()
-    a = np.ascontiguousarray(c.a[:sample_rows])
+    a = c.a if rows >= M else np.ascontiguousarray(c.a[:rows])
     use_ref = oracle.have_ref()
-    threads = os.cpu_count() or 1
+    hc = host_cores()
+    threads = hc["logical"]
     kw = c.kwargs()
 
     def call():
@@ -164,38 +197,77 @@ def cpu_reference_run(sample_rows: int, steps: int, warmup: int):
             return oracle.gemm_i8(a, c.w, impl="ref", threads=threads, **kw)
         return oracle.gemm_i8(a, c.w, impl="port", **kw)
 
+    out = None
     for _ in range(warmup):
-        call()
+        out = call()
     t0 = time.perf_counter()
     for _ in range(steps):
-        call()
+        out = call()
     dt = (time.perf_counter() - t0) / steps
-    ops_count = 2.0 * sample_rows * N * K
-    return {"value": ops_count / dt / 1e12, "unit": UNIT, "cores": threads,
-            "kind": "reference" if use_ref else "port",
-            "sample": f"first {sample_rows} of {M} activation rows x all {N} channels, K={K}; "
-                      f"{steps} timed calls after {warmup} warm-ups, wall clock",
-            "ms_per_call": dt * 1e3}
+    ops_count = 2.0 * a.shape[0] * N * K
+    what = f"all {M} activation rows" if a.shape[0] >= M else f"first {a.shape[0]} of {M} activation rows"
+    r = {"value": ops_count / dt / 1e12, "unit": UNIT, "cores": threads if use_ref else 1,
+         "physical_cores": hc["physical"], "smt": hc["smt"],
+         "kind": "reference" if use_ref else "port",
+         "sample": f"{what} x all {N} channels, K={K}; {steps} timed calls after {warmup} warm-ups, wall clock",
+         "ms_per_call": dt * 1e3, "rows": int(a.shape[0])}
+    if keep_output:
+        r["output"] = out
+    return r
+
+
+def cpu_q4_1_baseline() -> dict:
+    """The Q4_1 half of the metric on the host: the reference's Linear(f32 x q4_1, Backend::CPU)
+    on the decode-step configuration (M = 1 and 8, K = N = 4096), in GB/s of the same algorithmic
+    bytes the GPU figure counts, with all host threads and with one.  Method of the reference's
+    operator bench (tests/bench_linear.cpp:127-163): 3 warm-ups, then rounds of at least 8 calls
+    and 100 ms; the median of 3 rounds."""
+    import oracle
+    from nnops_b200 import synth
+    hc = host_cores()
+    if not oracle.have_ref():
+        return {"unavailable": "compiled reference route not runnable on this host"}
+    out = {"unit": "GB/s", "kind": "reference", "cores": hc["logical"], "physical_cores": hc["physical"],
+           "smt": hc["smt"],
+           "method": "Linear(f32 x q4_1, Backend::CPU), f32 activations holding the f16 values; 3 warm-ups, "
+                     "median of 3 rounds of >= 8 calls and >= 100 ms; bytes = the GPU figure's algorithmic bytes"}
+    for m in (1, 8):
+        c = synth.config3(m)
+        a32 = c.a.astype(np.float32)
+        for label, threads in (("all_cores", hc["logical"]), ("one_thread", 1)):
+            def call():
+                oracle.q4_1_matmul(a32, c.w_blocks, c.k, out_dtype="f32", impl="ref", threads=threads)
+            for _ in range(3):
+                call()
+            rounds = []
+            for _ in range(3):
+                n_calls, t0 = 0, time.perf_counter()
+                while n_calls < 8 or time.perf_counter() - t0 < 0.1:
+                    call()
+                    n_calls += 1
+                rounds.append((time.perf_counter() - t0) / n_calls)
+            out[f"m{m}_{label}"] = c.bytes / statistics.median(rounds) / 1e9
+    return out
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample_rows = 512
-    r = cpu_reference_run(sample_rows, max(1, args.steps), max(1, args.warmup))
+    # The whole configuration, every step: one call is well under two seconds of CPU time.
+    r = cpu_reference_run(M, max(1, args.steps), max(1, args.warmup))
     line = {
         "impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_call"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "s8", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "sample_rows": sample_rows},
-        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K},
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "physical_cores", "smt", "kind", "sample")},
         "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def secondary_q4_1(torch, dev, peaks):
+def secondary_q4_1(torch, dev, peaks, gemv_only: bool = False):
     """Q4_1 decode GEMV (M=1, M=8) in HBM GB/s and the prefill GEMM in TFLOP/s, reported beside
     the headline.  The 10 MiB weight matrix fits in L2, so the GEMV cycles over enough distinct
     weight replicas (>= 3x L2) inside one CUDA graph that every launch streams from HBM."""
@@ -238,6 +310,8 @@ def secondary_q4_1(torch, dev, peaks):
                                   "method": "CUDA graph of one launch per weight replica (replicas >= 3x L2), "
                                             "launches chained with programmatic dependent launch"}
         del ws, g
+    if gemv_only:
+        return out
     c = synth.config4()
     a, w = torch.from_numpy(c.a).to(dev), torch.from_numpy(c.w_blocks).to(dev)
     o = torch.empty((c.a.shape[0], c.w_blocks.shape[0]), dtype=torch.float16, device=dev)
@@ -350,6 +424,95 @@ def secondary_i8_config2(torch, dev, peaks):
     ops_count = 2.0 * c.a.shape[0] * c.w.shape[0] * c.a.shape[1]
     tops = ops_count / us / 1e6
     return {"i8_config2": {"tops": tops, "us_per_call": us, "frac_of_int8_peak": tops / (2.0 * peaks["bf16_tflops"])}}
+
+
+def measured_i8_peak(torch, lib, dev, sampler_factory):
+    """The part's int8 tensor rate from the library's issue-bound probe (tcgen05.mma kind::i8 on
+    shared-memory-resident tiles): best of five short launches (burst) and a loop of long
+    launches lasting about two seconds (sustained, SM clock sampled inside it)."""
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ops = C.c_double(0.0)
+
+    def one(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        st = lib.nnb200_measure_i8_mma_peak(iters, C.byref(ops), stream)
+        e1.record()
+        if st != 0:
+            raise RuntimeError(f"nnb200_measure_i8_mma_peak: status {st}")
+        torch.cuda.synchronize()
+        return ops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12
+
+    one(2048)
+    burst = max(one(8192) for _ in range(5))
+    sampler = sampler_factory()
+    if sampler is not None:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches, iters = 24, 1 << 18
+    e0.record()
+    for _ in range(launches):
+        lib.nnb200_measure_i8_mma_peak(iters, C.byref(ops), stream)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler is not None else None
+    secs = e0.elapsed_time(e1) * 1e-3
+    return {"burst_tops": burst, "sustained_tops": ops.value * launches / secs / 1e12, "sustained_seconds": secs,
+            "sustained_clocks": clocks,
+            "method": "one CTA per SM issuing tcgen05.mma.kind::i8 M128xN256xK32 back to back on zero-filled "
+                      "shared-memory tiles, two alternating TMEM accumulators; no loads, no epilogue"}
+
+
+def sustained_gemm(torch, layer, a, out, total_ops, sampler_factory, seconds: float = 2.5):
+    """The headline GEMM back to back for a couple of seconds: what it holds under the power cap."""
+    for _ in range(3):
+        layer.local(a, out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = sampler_factory()
+    if sampler is not None:
+        sampler.start()
+    launches = 0
+    t_end = time.perf_counter() + seconds
+    e0.record()
+    while time.perf_counter() < t_end:
+        # Chunks of 200 launches (~0.1 s) with one synchronisation each, so that the host clock
+        # that ends the loop and the device stay together; the gap per chunk is microseconds.
+        for _ in range(200):
+            layer.local(a, out)
+        launches += 200
+        torch.cuda.synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler is not None else None
+    secs = e0.elapsed_time(e1) * 1e-3
+    tops = total_ops * launches / secs / 1e12
+    r = {"tops": tops, "seconds": secs, "launches": launches, "clocks": clocks}
+    if clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz"):
+        r["tops_at_max_clock"] = tops * clocks["sm_max_mhz"] / clocks["sm_mhz"]
+    return r
+
+
+def operator_level_bench(steps: int, warmup: int):
+    """The same layer driven from C++ through Linear::create(attrs, Backend::CUDA)->compute() with
+    the weight scales as HOST arrays (tests/cpp/bench_linear_op.cpp): the drop-in build when it
+    exists, else the stand-alone front end."""
+    bin_dir = ROOT / "tests" / "cpp" / "_bin"
+    for name in ("bench_linear_op_dropin", "bench_linear_op_standalone"):
+        exe = bin_dir / name
+        if exe.exists():
+            try:
+                r = subprocess.run([str(exe), str(M), str(N), str(K), str(steps), str(warmup)], capture_output=True,
+                                   text=True, timeout=300)
+                line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+                if r.returncode == 0 and line:
+                    d = json.loads(line[-1])
+                    d["binary"] = name
+                    return d
+                return {"unavailable": f"{name} exited {r.returncode}: {(r.stdout + r.stderr)[-200:]}"}
+            except (OSError, subprocess.TimeoutExpired, ValueError) as e:
+                return {"unavailable": f"{name}: {e}"}
+    return {"unavailable": "tests/cpp/_bin/bench_linear_op_* not built (python -m nnops_b200.host.build)"}
 
 
 def run_kernel_only(args):
@@ -491,18 +654,54 @@ def main():
     total_ops = 2.0 * M * N * K
     value = total_ops / (ms_step * 1e-3) / 1e12
 
+    # ---- correctness of what was timed: every rank's assembled [M, N] output ----
+    # Each rank hashes its own copy; all hashes must agree, and rank 0 compares its copy byte
+    # for byte with the reference's CPU route run on the same seeded inputs (all 4096 rows: one
+    # call costs the host about a second).
+    import hashlib
+    out_host_full = out.cpu().numpy()
+    my_hash = hashlib.sha256(out_host_full.tobytes()).hexdigest()
+    hashes = [my_hash]
+    if world > 1:
+        hashes = [None] * world
+        dist.all_gather_object(hashes, my_hash)
+    parity = None
+    cpu_full = None
+    if rank == 0:
+        import oracle
+        if oracle.have_ref():
+            cpu_full = cpu_reference_run(M, 1, 0, keep_output=True)
+            want = cpu_full.pop("output")
+            parity = {"rows_checked": M, "equal": bool(np.array_equal(out_host_full, want)),
+                      "against": "reference CPU route (oracle/_ref), whole output",
+                      "ref_sha256": hashlib.sha256(want.tobytes()).hexdigest()}
+        else:
+            rows = np.random.default_rng(0).choice(M, 64, replace=False)
+            want = oracle.gemm_i8(np.ascontiguousarray(c.a[rows]), c.w, **c.kwargs())
+            parity = {"rows_checked": 64, "equal": bool(np.array_equal(out_host_full[rows], want)),
+                      "against": "C restatement of the reference arithmetic, sampled rows"}
+        parity["ranks_agree"] = len(set(hashes)) == 1
+        if not (parity["equal"] and parity["ranks_agree"]):
+            raise SystemExit(f"parity failure: {parity}, hashes {hashes}")
+    del out_host_full
+
     # ---- end to end: host activations in, host result out, every step ----
     # Every step copies its activations from pinned host memory, runs the layer and reads the
     # full result back.  Copies and compute run on three streams over two sets of device/host
     # buffers, so step i's read-back overlaps step i+1's upload and GEMM (PCIe is full duplex).
-    # At N > 1 rank 0 uploads the activations and broadcasts them over NVLink (the host link is
-    # shared by all GPUs of the box), and every rank reads back only the output columns it
-    # produced; together the ranks return the whole result once.
+    # At N > 1 every rank uploads M/g rows of the activations over its own host link and the
+    # ranks all-gather the slices over NVLink; every rank reads back only the output columns it
+    # produced; together the ranks move the whole input and the whole result once.
     col_lo, col_hi = (0, N) if world == 1 else (layer.col0, layer.col0 + layer.n_per)
     h2d = a_host.numel()
     d2h = M * N
     s_in, s_run, s_back = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     a_dev = [a, torch.empty_like(a)]
+    # N > 1: every rank uploads its own M/g rows of the activations over its own host link, then
+    # the ranks exchange the slices over NVLink (all-gather in place).
+    rows_per = M // world
+    row_lo = rank * rows_per
+    a_host_slice = a_host[row_lo:row_lo + rows_per] if world > 1 else a_host
     out_dev = outs
     # Each rank's host copy holds only its own columns, densely: a strided pinned destination
     # would make torch fall back to a synchronous host-side copy.
@@ -517,14 +716,18 @@ def main():
         b = i & 1
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_run[b])          # the GEMM that last read this activation buffer
-            if rank == 0:
+            if world == 1:
                 a_dev[b].copy_(a_host, non_blocking=True)
+            else:
+                a_dev[b][row_lo:row_lo + rows_per].copy_(a_host_slice, non_blocking=True)
             ev_in[b].record()
         with torch.cuda.stream(s_run):
             s_run.wait_event(ev_in[b])
             s_run.wait_event(ev_back[b])        # the read-back that last used this output buffer
             if world > 1:
-                dist.broadcast(a_dev[b], src=0)  # same stream as the layer's collectives: one communicator
+                # Same stream as the layer's collectives: one communicator.  In place: each rank's
+                # input is its own slice of the output.
+                dist.all_gather_into_tensor(a_dev[b], a_dev[b][row_lo:row_lo + rows_per])
             # Another rank's previous read-back of this buffer may still be running: order the ranks first.
             layer.forward(a_dev[b], out_dev[b], wait_for_readers=True)
             ev_run[b].record()
@@ -553,17 +756,22 @@ def main():
     e2e_value = total_ops / (e2e_ms * 1e-3) / 1e12
     e2e_check = bool(torch.equal(out_hosts[0], out_hosts[1]))
 
+    e2e_matches_resident = None
+    if world == 1:
+        e2e_matches_resident = hashlib.sha256(out_hosts[0].numpy().tobytes()).hexdigest() == my_hash
+
     # ---- roofline of the dominant kernel (the tcgen05 GEMM) ----
-    int8_peak = 2.0 * peaks["bf16_tflops"]
+    derived_peak = 2.0 * peaks["bf16_tflops"]
     per_launch_ops = total_ops / world
     achieved = per_launch_ops / (kernel_ms * 1e-3) / 1e12
-    traffic = None
+    traffic, traffic_source = None, None
     tp = ROOT / "profiles" / "dram_traffic.json"
-    if tp.exists():
+    if tp.exists() and world == 1:      # captured for the single-GPU launch only
         try:
             traffic = json.loads(tp.read_text()).get("gemm_i8_umma_cfg5_bytes_per_launch")
-            if traffic is not None and world > 1:
-                traffic = None  # captured for the single-GPU launch only
+            traffic_source = ("profiles/dram_traffic.json: dram__bytes_read.sum + dram__bytes_write.sum of one ncu "
+                              "capture of this kernel on this workload (profiles/gemm_i8_umma_config5.md); not "
+                              "re-measured by this run")
         except (ValueError, OSError):
             traffic = None
 
@@ -571,15 +779,62 @@ def main():
     if err != 0:
         raise SystemExit(f"device error word = {err}")
 
+    def sampler_factory():
+        try:
+            return make_clock_sampler(local_rank, str(uuid) if uuid is not None else None)[0]
+        except Exception:
+            return None
+
     extra = {}
     cpu_baseline = None
+    i8_peak = None
     if rank == 0 and world == 1 and not args.no_secondary:
-        extra = secondary_q4_1(torch, dev, peaks)
+        i8_peak = measured_i8_peak(torch, lib, dev, sampler_factory)
+        extra["int8_mma_peak"] = i8_peak
+        sus = sustained_gemm(torch, layer, a, out, total_ops, sampler_factory)
+        sus["frac_of_sustained_int8_peak"] = sus["tops"] / i8_peak["sustained_tops"]
+        sus["frac_of_2x_bf16_sustained"] = sus["tops"] / (2.0 * peaks["bf16_tflops_sustained"])
+        sus["frac_of_nominal_4500"] = sus["tops"] / 4500.0
+        extra["sustained"] = sus
+        extra.update(secondary_q4_1(torch, dev, peaks))
         extra.update(secondary_i8_config2(torch, dev, peaks))
         extra.update(secondary_quant_linear(torch, dev, peaks))
         extra.update(secondary_i8_decode(torch, dev, peaks, layer.w, layer.kw["scale_w"], layer.kw["bias"]))
-        cpu_baseline = cpu_reference_run(1024, 5, 2)
-        cpu_baseline = {k: cpu_baseline[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        extra["e2e_op"] = operator_level_bench(10, 3)
+        extra["cpu_baseline_q4_1"] = cpu_q4_1_baseline()
+        cb = cpu_reference_run(M, 3, 1)
+        cpu_baseline = {k: cb[k] for k in ("value", "unit", "cores", "physical_cores", "smt", "kind", "sample")}
+        one = None
+        try:
+            import oracle
+            if oracle.have_ref():
+                t0 = time.perf_counter()
+                oracle.gemm_i8(np.ascontiguousarray(c.a[:256]), c.w, impl="ref", threads=1, **c.kwargs())
+                one = 2.0 * 256 * N * K / (time.perf_counter() - t0) / 1e12
+        except Exception:
+            one = None
+        cpu_baseline["one_thread_value"] = one
+        cpu_baseline["one_thread_sample"] = "first 256 rows, one call, one thread"
+    elif rank == 0 and cpu_full is not None:
+        cpu_baseline = {k: cpu_full[k] for k in ("value", "unit", "cores", "physical_cores", "smt", "kind", "sample")}
+    if world > 1 and not args.no_secondary:
+        # The Q4_1 decode GEMV does not shard in this build: at N > 1 every GPU runs its own
+        # replica of the layer (independent requests), and the aggregate is the sum.
+        rep = secondary_q4_1(torch, dev, peaks, gemv_only=True)
+        mine = [rep["q4_1_gemv_m1"]["gbs"], rep["q4_1_gemv_m8"]["gbs"]]
+        allv = [None] * world
+        dist.all_gather_object(allv, mine)
+        if rank == 0:
+            for i, key in enumerate(("q4_1_gemv_m1", "q4_1_gemv_m8")):
+                extra[key] = {"gbs": float(sum(v[i] for v in allv)), "per_gpu_gbs": [float(v[i]) for v in allv],
+                              "mode": "replicas: one independent GEMV stream per GPU, no exchange",
+                              "bytes_per_call": rep[key]["bytes_per_call"]}
+
+    peak = i8_peak["burst_tops"] if i8_peak is not None else derived_peak
+    peak_source = ("measured: tcgen05.mma kind::i8 issue-bound probe on this GPU (burst); 2 x measured dense bf16 burst "
+                   f"would be {derived_peak:.1f}; nominal dense int8 is 4500") if i8_peak is not None else (
+                   f"2 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s): int8 tensor rate is twice "
+                   "the bf16 rate; nominal dense int8 is 4500 (the issue-bound probe runs at N = 1 only)")
 
     if rank == 0:
         line = {
@@ -595,16 +850,18 @@ def main():
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "results_identical_across_buffers": e2e_check,
-                    "method": "3 streams, double-buffered: H2D of A (rank 0, then NVLink broadcast at N > 1), the "
-                              "layer, D2H of each rank's own N/g output columns, every step; bytes are "
-                              "totals over the ranks"},
+                    "result_equals_device_resident_run": e2e_matches_resident,
+                    "method": "3 streams, double-buffered: H2D of A (at N > 1 each rank uploads M/g rows, then an "
+                              "NVLink all-gather), the layer, D2H of each rank's own N/g output columns, every "
+                              "step; bytes are totals over the ranks"},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
-                         "frac": achieved / int8_peak, "traffic": traffic,
-                         "peak_source": f"2 x {peaks['source']} dense bf16 burst ({peaks['bf16_tflops']} TFLOP/s): "
-                                        "int8 tensor rate is twice the bf16 rate; nominal dense int8 is 4500",
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s",
+                         "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_source,
+                         "peak_source": peak_source, "frac_of_2x_bf16_burst": achieved / derived_peak,
+                         "frac_of_nominal_4500": achieved / 4500.0,
                          "kernel": "gemm_i8_umma_kernel<256,S8>", "kernel_ms": kernel_ms,
                          "ops_per_launch": per_launch_ops},
+            "out_sha256": my_hash, "parity": parity,
             "cpu_baseline": cpu_baseline,
         }
         line.update(extra)

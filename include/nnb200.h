@@ -169,6 +169,16 @@ NNB200_API int nnb200_gemm_i8(const nnb200_gemm_i8_args* args, void* stream);
 NNB200_API int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, void* stream);
 
 /*
+ * Measurement aid: the int8 tensor rate of this GPU.  Enqueues one launch in which every SM
+ * issues iters groups of four tcgen05.mma kind::i8 M128 x N256 x K32 (the int8 GEMM's own
+ * instruction) on operand tiles resident in shared memory, with no loads, stores or epilogue;
+ * *ops receives the integer operations the launch performs (2 per multiply-add).  The caller
+ * times the launch with events on the stream: ops / time is the denominator the GEMM's
+ * roofline fraction is quoted against.  1 <= iters <= 2^21.  No counterpart in the reference.
+ */
+NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, double* ops, void* stream);
+
+/*
  * Measurement and test switches: process-wide integers, in the manner of the reference's bench
  * knobs (src/detail/bench_knobs.hpp:15-38).  They only select among code paths that give
  * identical results; production code leaves them alone.  A negative value means "default".
@@ -180,8 +190,8 @@ NNB200_API int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, vo
  *   I8_PEER_STAGING  1 / 2 staging tiles per epilogue warp in the sharded write-back
  *   F16_PAIR         as I8_PAIR for the dense f16 GEMM of the Q4_1 two-pass form (default 1)
  *   I8_SHARE_K       0 never share K among SMs in the few-row engine, 2 offer it from 8 K blocks per SM
- *   Q4_GEMV          Q4_1 GEMV engine of the automatic choice: 0 deferred-scaling kernel (default), 1 the
- *                    per-weight-dequantising warp-MMA kernel
+ *   Q4_GEMV          Q4_1 GEMV engine of the automatic choice: 1 never the deferred-scaling kernel, 2 that
+ *                    kernel whenever it can run (default: for a single activation row)
  */
 #define NNB200_KNOB_GROUP_M 0
 #define NNB200_KNOB_I8_BN 1

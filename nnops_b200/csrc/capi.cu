@@ -549,7 +549,13 @@ int nnb200_q4_1_engine(const nnb200_q4_1_args* q)
     // GEMM), 6 = GEMV with warp-level MMA on raw nibbles and deferred scaling.
     int gemv = 3;
     if (q->force_engine != 3) {
-        const bool prefer_dsq = q->force_engine == 6 || (q->force_engine != 4 && knob(NNB200_KNOB_Q4_GEMV) != 1);
+        // Deferred scaling pays one fix-up per (channel, block, activation column), so it wins where
+        // the columns are few: one f16 row (4.6 against 4.7 us on a 10 MB matrix, 33 against 51 us on
+        // 147 MB) and one f32 row (two columns); from two f16 rows on the per-weight form is faster
+        // (M = 8 on 10 MB: 6.0 against 9.7 us).  Knob Q4_GEMV: 1 never, 2 whenever it can run.
+        const int kn = knob(NNB200_KNOB_Q4_GEMV);
+        const bool few_columns = q->m == 1;
+        const bool prefer_dsq = q->force_engine == 6 || (q->force_engine != 4 && kn != 1 && (kn == 2 || few_columns));
         if (prefer_dsq && q4_1_gemv_dsq_supported(*q)) {
             gemv = 6;
         } else if (q4_1_gemv_mma_supported(*q)) {
@@ -921,6 +927,21 @@ int nnb200_is_device_pointer(const void* p)
 uint64_t nnb200_launch_count(void)
 {
     return g_launches.load(std::memory_order_relaxed);
+}
+
+int nnb200_measure_i8_mma_peak(int32_t iters, double* ops, void* stream)
+{
+    if (iters < 1 || iters > (1 << 21)) {
+        return NNB200_INVALID_ARGUMENT;   // the upper bound keeps the launch well inside the bounded wait
+    }
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    if (dev->cc_major != 10) {
+        return NNB200_UNSUPPORTED;
+    }
+    return launch_mma_i8_peak(iters, ops, *dev, static_cast<cudaStream_t>(stream));
 }
 
 int nnb200_set_knob(int id, int value)

@@ -28,7 +28,10 @@
 //   * Launched with programmatic stream serialization when the caller allows it
 //     (NNB200_Q4_FLAG_OVERLAP_PREVIOUS): the weight copies are issued before
 //     griddepcontrol.wait, so they overlap the tail of the preceding kernel in the stream;
-//     activations are read and outputs written only after it.
+//     activations are read and outputs written only after it.  Such a launch begins before the
+//     kernel that produces the activations has finished, so no kernel boundary has invalidated
+//     this SM's L1 since an earlier step may have read the same buffer: the vector loads of the
+//     activations therefore go to L2 (ld.global.cg), never through the non-coherent path.
 //
 // CPU twin: mma_qblock_trans (src/backend/cpu/x86_64/mma_qblock.hpp:144-291).
 
@@ -90,14 +93,14 @@ __device__ __forceinline__ void load_act_block(const __half* a_blk, bool vec_ok,
         const uint4* src = reinterpret_cast<const uint4*>(a_blk);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            av[j] = __ldg(src + j);
+            av[j] = __ldcg(src + j);   // L2, not the non-coherent path: see the launch note below
         }
     } else {
         uint32_t* dst = reinterpret_cast<uint32_t*>(av);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            dst[j] = static_cast<uint32_t>(__half_as_ushort(a_blk[2 * j])) |
-                     (static_cast<uint32_t>(__half_as_ushort(a_blk[2 * j + 1])) << 16);
+            const unsigned short* u = reinterpret_cast<const unsigned short*>(a_blk);
+            dst[j] = static_cast<uint32_t>(__ldcg(u + 2 * j)) | (static_cast<uint32_t>(__ldcg(u + 2 * j + 1)) << 16);
         }
     }
 }
@@ -112,9 +115,9 @@ __device__ __forceinline__ void load_act_block_f32(const float* a_blk, bool vec_
     for (int j = 0; j < 8; ++j) {
         float4 v;
         if (vec_ok) {
-            v = __ldg(reinterpret_cast<const float4*>(a_blk) + j);
+            v = __ldcg(reinterpret_cast<const float4*>(a_blk) + j);
         } else {
-            v = make_float4(a_blk[4 * j], a_blk[4 * j + 1], a_blk[4 * j + 2], a_blk[4 * j + 3]);
+            v = make_float4(__ldcg(a_blk + 4 * j), __ldcg(a_blk + 4 * j + 1), __ldcg(a_blk + 4 * j + 2), __ldcg(a_blk + 4 * j + 3));
         }
         __half2 h01 = __floats2half2_rn(v.x, v.y);
         __half2 h23 = __floats2half2_rn(v.z, v.w);

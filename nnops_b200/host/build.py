@@ -116,6 +116,12 @@ def build_tests(force=False) -> list[Path]:
         _run([CXX, *COMMON, "-o", out, src, f"-L{LIB_DIR}", "-lnnb200_host", "-lnnb200", f"-L{oracle_lib.parent}",
               "-lnnops_oracle", *cuda, *_rpath(LIB_DIR, oracle_lib.parent, CUDA_HOME / "lib64")])
     outs.append(out)
+    bench_src = ROOT / "tests" / "cpp" / "bench_linear_op.cpp"
+    out = BIN_DIR / "bench_linear_op_standalone"
+    if force or _stale(out, [bench_src, host_lib]):
+        _run([CXX, *COMMON, "-o", out, bench_src, f"-L{LIB_DIR}", "-lnnb200_host", "-lnnb200", *cuda,
+              *_rpath(LIB_DIR, CUDA_HOME / "lib64")])
+    outs.append(out)
     dropin = build_dropin(force)
     if dropin is not None and (REFERENCE_ROOT / "include").exists():
         out = BIN_DIR / "test_ops_dropin"
@@ -125,8 +131,16 @@ def build_tests(force=False) -> list[Path]:
                   "-lnnops_b200_dropin", "-lnnb200", f"-L{oracle_lib.parent}", "-lnnops_oracle", "-fopenmp", *cuda,
                   *_rpath(LIB_DIR, oracle_lib.parent, CUDA_HOME / "lib64")])
         outs.append(out)
-    elif (BIN_DIR / "test_ops_dropin").exists():
-        outs.append(BIN_DIR / "test_ops_dropin")
+        out = BIN_DIR / "bench_linear_op_dropin"
+        if force or _stale(out, [bench_src, dropin]):
+            _run([CXX, "-std=c++23", "-O2", "-include", "limits", "-DNNB200_USE_NNOPS_HEADERS=1", "-DNNOPS_HAS_CUDA=1",
+                  f"-I{REFERENCE_ROOT / 'include'}", f"-I{ROOT / 'include'}", "-o", out, bench_src, f"-L{LIB_DIR}",
+                  "-lnnops_b200_dropin", "-lnnb200", "-fopenmp", *cuda, *_rpath(LIB_DIR, CUDA_HOME / "lib64")])
+        outs.append(out)
+    else:
+        for name in ("test_ops_dropin", "bench_linear_op_dropin"):
+            if (BIN_DIR / name).exists():
+                outs.append(BIN_DIR / name)
     return outs
 
 
