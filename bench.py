@@ -428,39 +428,43 @@ def secondary_i8_config2(torch, dev, peaks):
 
 def measured_i8_peak(torch, lib, dev, sampler_factory):
     """The part's int8 tensor rate from the library's issue-bound probe (tcgen05.mma kind::i8 on
-    shared-memory-resident tiles): best of five short launches (burst) and a loop of long
-    launches lasting about two seconds (sustained, SM clock sampled inside it)."""
+    shared-memory-resident tiles).  Zero operands give the pipe's issue rate (best of five short
+    launches); pseudo-random operands, in a loop of about two seconds with the SM clock sampled
+    inside it, give what the same instruction stream holds under the power cap."""
     stream = torch.cuda.current_stream(dev).cuda_stream
     ops = C.c_double(0.0)
 
-    def one(iters):
+    def one(iters, pattern):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        st = lib.nnb200_measure_i8_mma_peak(iters, C.byref(ops), stream)
+        st = lib.nnb200_measure_i8_mma_peak(iters, pattern, C.byref(ops), stream)
         e1.record()
         if st != 0:
             raise RuntimeError(f"nnb200_measure_i8_mma_peak: status {st}")
         torch.cuda.synchronize()
         return ops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12
 
-    one(2048)
-    burst = max(one(8192) for _ in range(5))
-    sampler = sampler_factory()
-    if sampler is not None:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches, iters = 24, 1 << 18
-    e0.record()
-    for _ in range(launches):
-        lib.nnb200_measure_i8_mma_peak(iters, C.byref(ops), stream)
-    e1.record()
-    torch.cuda.synchronize()
-    clocks = sampler.stop() if sampler is not None else None
-    secs = e0.elapsed_time(e1) * 1e-3
-    return {"burst_tops": burst, "sustained_tops": ops.value * launches / secs / 1e12, "sustained_seconds": secs,
-            "sustained_clocks": clocks,
-            "method": "one CTA per SM issuing tcgen05.mma.kind::i8 M128xN256xK32 back to back on zero-filled "
-                      "shared-memory tiles, two alternating TMEM accumulators; no loads, no epilogue"}
+    def loop(pattern, launches, iters):
+        sampler = sampler_factory()
+        if sampler is not None:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(launches):
+            lib.nnb200_measure_i8_mma_peak(iters, pattern, C.byref(ops), stream)
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if sampler is not None else None
+        secs = e0.elapsed_time(e1) * 1e-3
+        return {"tops": ops.value * launches / secs / 1e12, "seconds": secs, "clocks": clocks}
+
+    one(2048, 0)
+    burst = max(one(8192, 0) for _ in range(5))
+    burst_random = max(one(8192, 1) for _ in range(5))
+    return {"burst_tops": burst, "burst_tops_random_operands": burst_random,
+            "sustained_zero_operands": loop(0, 8, 1 << 18), "sustained_random_operands": loop(1, 24, 1 << 18),
+            "method": "one CTA per SM issuing tcgen05.mma.kind::i8 M128xN256xK32 back to back on shared-memory "
+                      "tiles (zeros / pseudo-random bytes), two alternating TMEM accumulators; no loads, no epilogue"}
 
 
 def sustained_gemm(torch, layer, a, out, total_ops, sampler_factory, seconds: float = 2.5):
@@ -560,8 +564,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the Q4_1 and CPU-baseline side measurements")
-    ap.add_argument("--reassembly", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: peer-store epilogue (fused) or NCCL all-gather + interleave kernel")
+    ap.add_argument("--reassembly", default="multicast", choices=["multicast", "fused", "nccl"],
+                    help="N > 1: the GEMM epilogue stores every tile once through an NVSwitch multicast mapping "
+                         "(multicast; falls back to fused where the fabric has none), or into every rank's output "
+                         "with one peer store per rank (fused), or NCCL all-gather + interleave kernel (nccl)")
     ap.add_argument("--kernel-only", choices=["i8", "gemv", "q4gemm", "q4gemm2", "quant"],
                     help="profiling aid: 3 launches of one kernel (q4gemm = fused form, q4gemm2 = two-pass form, "
                          "quant = QuantizeLinear then DequantizeLinear of an [M, K] f32 tensor, per token; N unused)")
@@ -681,9 +687,20 @@ def main():
             parity = {"rows_checked": 64, "equal": bool(np.array_equal(out_host_full[rows], want)),
                       "against": "C restatement of the reference arithmetic, sampled rows"}
         parity["ranks_agree"] = len(set(hashes)) == 1
-        if not (parity["equal"] and parity["ranks_agree"]):
-            raise SystemExit(f"parity failure: {parity}, hashes {hashes}")
     del out_host_full
+    # All ranks learn the verdict and leave together (their buffers are mapped into each other).
+    verdict = torch.tensor([1 if (rank != 0 or (parity["equal"] and parity["ranks_agree"])) else 0],
+                           dtype=torch.int32, device=dev)
+    if world > 1:
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+    if int(verdict.item()) == 0:
+        if rank == 0:
+            print(json.dumps({"error": "parity failure", "parity": parity, "hashes": hashes}), file=sys.stderr, flush=True)
+        del out, outs
+        layer.close()
+        if world > 1:
+            dist.destroy_process_group()
+        raise SystemExit(1)
 
     # ---- end to end: host activations in, host result out, every step ----
     # Every step copies its activations from pinned host memory, runs the layer and reads the
@@ -776,7 +793,15 @@ def main():
             traffic = None
 
     err = capi.take_device_error()
+    if world > 1:
+        et = torch.tensor([err], dtype=torch.int32, device=dev)
+        dist.all_reduce(et, op=dist.ReduceOp.MAX)
+        err = int(et.item())
     if err != 0:
+        if world > 1:        # every rank leaves, together
+            del out, outs, out_dev, a_dev
+            layer.close()
+            dist.destroy_process_group()
         raise SystemExit(f"device error word = {err}")
 
     def sampler_factory():
@@ -792,7 +817,7 @@ def main():
         i8_peak = measured_i8_peak(torch, lib, dev, sampler_factory)
         extra["int8_mma_peak"] = i8_peak
         sus = sustained_gemm(torch, layer, a, out, total_ops, sampler_factory)
-        sus["frac_of_sustained_int8_peak"] = sus["tops"] / i8_peak["sustained_tops"]
+        sus["frac_of_sustained_int8_peak_random_operands"] = sus["tops"] / i8_peak["sustained_random_operands"]["tops"]
         sus["frac_of_2x_bf16_sustained"] = sus["tops"] / (2.0 * peaks["bf16_tflops_sustained"])
         sus["frac_of_nominal_4500"] = sus["tops"] / 4500.0
         extra["sustained"] = sus
@@ -843,9 +868,12 @@ def main():
             "vs_baseline": None, "dtype": "s8", "data": "synthetic",
             "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "shards": world,
                        "reassembly": "none" if world == 1 else (
-                           "fused: GEMM epilogue stores each tile into every rank's output over NVLink (P2P), "
-                           "then a device-side flag barrier over peer memory orders the ranks" if layer.mode == "fused"
-                           else "nccl all-gather + interleave kernel"),
+                           "multicast: GEMM epilogue stores each tile once with multimem.st, the NVSwitch writes it "
+                           "into every rank's output; then a device-side flag barrier over peer memory orders the ranks"
+                           if layer.multicast_active else (
+                               "fused: GEMM epilogue stores each tile into every rank's output over NVLink (P2P), "
+                               "then a device-side flag barrier over peer memory orders the ranks"
+                               if layer.mode in ("fused", "multicast") else "nccl all-gather + interleave kernel")),
                        "l2": "inputs (268 MB) exceed L2 (126 MB); no flush needed"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
@@ -867,6 +895,9 @@ def main():
         line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
+        # Release the mapped / multicast-bound buffers while every rank is alive.
+        del out, outs, out_dev, a_dev
+        layer.close()
         dist.destroy_process_group()
 
 

@@ -135,6 +135,16 @@ typedef struct nnb200_gemm_i8_args {
      * weight, see nnb200_i8_pack).  A call that needs zero-point compensation then skips its
      * sweep over W.  Single-batch weights only (w_batch_stride == 0 or batch == 1). */
     const int32_t* r_w;
+    /* Optional, column-sharded layers on GPUs behind an NVSwitch: the address of this call's
+     * [m, n] output window (same ldc) inside a MULTICAST mapping that is bound to every rank's
+     * copy of the full output, this rank's included.  Each finished tile is then stored once
+     * with multimem.st and the switch replicates it to all copies, instead of one store per
+     * destination: `out` and peer_out[] are not written (num_peer_outs must be 0; `out` must
+     * still name this rank's own window, it decides alignment and pitch).  Same conditions as
+     * peer_out.  The address must come from a multicast object (cuMulticastCreate /
+     * cuMulticastBindMem, or a library that wraps them): anything else is not a valid operand
+     * of the instruction.  No counterpart in the reference. */
+    void* multicast_out;
 } nnb200_gemm_i8_args;
 
 /* Scratch the call runs fastest with (0 for the common zero-point-free tensor-core call), and
@@ -172,11 +182,13 @@ NNB200_API int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, vo
  * Measurement aid: the int8 tensor rate of this GPU.  Enqueues one launch in which every SM
  * issues iters groups of four tcgen05.mma kind::i8 M128 x N256 x K32 (the int8 GEMM's own
  * instruction) on operand tiles resident in shared memory, with no loads, stores or epilogue;
- * *ops receives the integer operations the launch performs (2 per multiply-add).  The caller
- * times the launch with events on the stream: ops / time is the denominator the GEMM's
- * roofline fraction is quoted against.  1 <= iters <= 2^21.  No counterpart in the reference.
+ * pattern 0 fills the tiles with zeros (the pipe's issue rate), 1 with pseudo-random bytes (the
+ * rate the power cap allows once the operands toggle).  *ops receives the integer operations
+ * the launch performs (2 per multiply-add).  The caller times the launch with events on the
+ * stream: ops / time is the denominator the GEMM's roofline fraction is quoted against.
+ * 1 <= iters <= 2^21.  No counterpart in the reference.
  */
-NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, double* ops, void* stream);
+NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double* ops, void* stream);
 
 /*
  * Measurement and test switches: process-wide integers, in the manner of the reference's bench

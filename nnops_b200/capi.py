@@ -46,6 +46,7 @@ class GemmI8Args(C.Structure):
         ("force_engine", C.c_int32),
         ("num_peer_outs", C.c_int32), ("peer_out", C.c_void_p * 7),
         ("r_w", C.c_void_p),
+        ("multicast_out", C.c_void_p),
     ]
 
 
@@ -119,7 +120,7 @@ SYMBOLS = [
     ("nnb200_peer_buffer_close", C.c_int, [C.c_void_p]),
     ("nnb200_enable_peer_access", C.c_int, [C.c_int32]),
     ("nnb200_is_device_pointer", C.c_int, [C.c_void_p]),
-    ("nnb200_measure_i8_mma_peak", C.c_int, [C.c_int32, C.POINTER(C.c_double), C.c_void_p]),
+    ("nnb200_measure_i8_mma_peak", C.c_int, [C.c_int32, C.c_int32, C.POINTER(C.c_double), C.c_void_p]),
     ("nnb200_set_knob", C.c_int, [C.c_int, C.c_int]),
     ("nnb200_get_knob", C.c_int, [C.c_int]),
     ("nnb200_launch_count", C.c_uint64, []),

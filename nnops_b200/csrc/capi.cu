@@ -210,6 +210,12 @@ I8Problem problem_of(const nnb200_gemm_i8_args* a, int64_t b)
     return p;
 }
 
+// The call writes a column window of a sharded output (peer stores or multicast stores).
+bool sharded_out(const nnb200_gemm_i8_args* a)
+{
+    return a->num_peer_outs != 0 || a->multicast_out != nullptr;
+}
+
 int pick_i8_engine(const nnb200_gemm_i8_args* a, const I8Problem& p)
 {
     if (a->force_engine == NNB200_ENGINE_GENERIC) {
@@ -225,7 +231,7 @@ int pick_i8_engine(const nnb200_gemm_i8_args* a, const I8Problem& p)
         return decode_i8_supported(p) ? NNB200_ENGINE_DECODE : NNB200_ENGINE_GENERIC;
     }
     if (a->force_engine == NNB200_ENGINE_SKINNY) {
-        return (a->num_peer_outs == 0 && skinny_i8_supported(p)) ? NNB200_ENGINE_SKINNY : NNB200_ENGINE_GENERIC;
+        return (!sharded_out(a) && skinny_i8_supported(p)) ? NNB200_ENGINE_SKINNY : NNB200_ENGINE_GENERIC;
     }
     // Few activation rows: the cost is streaming W once, and what decides is how evenly an engine
     // spreads that stream over the SMs.  Measured (us) on N=28672,K=8192 / 14336,4096 / 11008,4096 /
@@ -238,7 +244,7 @@ int pick_i8_engine(const nnb200_gemm_i8_args* a, const I8Problem& p)
     //     leave SMs idle is served best by exactly those (4096 channels: 13.5 against 15.9..22.7);
     //     otherwise weights-as-rows up to 64 rows, and above while the layer has 256-channel tiles
     //     for less than half the SMs.
-    if (a->num_peer_outs == 0) {
+    if (!sharded_out(a)) {
         const bool decode_ok = decode_i8_supported(p);
         const bool skinny_ok = skinny_i8_supported(p);
         const DeviceInfo* dev = current_device_info();
@@ -254,7 +260,7 @@ int pick_i8_engine(const nnb200_gemm_i8_args* a, const I8Problem& p)
             }
         }
     }
-    if (a->num_peer_outs == 0 && narrow_i8_supported(p)) {
+    if (!sharded_out(a) && narrow_i8_supported(p)) {
         return NNB200_ENGINE_NARROW;
     }
     if (umma_i8_supported(p)) {
@@ -318,7 +324,7 @@ struct I8SplitPlan {
 static I8SplitPlan i8_split_plan(const nnb200_gemm_i8_args* a)
 {
     I8SplitPlan plan{0, false};
-    if (a->batch != 1 || a->num_peer_outs != 0) {
+    if (a->batch != 1 || sharded_out(a)) {
         return plan;
     }
     const DeviceInfo* dev = current_device_info();
@@ -414,7 +420,7 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
     const size_t ra_bytes = (static_cast<size_t>(a->m) * 4 + 255) & ~size_t(255);
     const size_t rw_bytes = (static_cast<size_t>(a->n) * 4 + 255) & ~size_t(255);
 
-    if (a->num_peer_outs != 0) {
+    if (sharded_out(a)) {
         // A rank barrier that ran out of time earlier leaves the gathered outputs suspect.
         const PeerPoison poison = peer_poison_for_current_device(false);
         if (poison.host != nullptr && *poison.host != 0) {
@@ -422,12 +428,15 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
         }
         // Sharded write-back: validated here so that a refused call has launched nothing.
         const auto mis16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; };
-        bool ok = a->num_peer_outs > 0 && a->num_peer_outs <= 7 && a->batch == 1 &&
+        bool ok = a->num_peer_outs >= 0 && a->num_peer_outs <= 7 && a->batch == 1 &&
                   (a->out_kind == NNB200_OUT_S8 || a->out_kind == NNB200_OUT_U8) && (a->ldc % 16) == 0 &&
                   (a->n % 16) == 0 && !mis16(a->out) &&
                   pick_i8_engine(a, problem_of(a, 0)) == NNB200_ENGINE_UMMA;
         for (int i = 0; ok && i < a->num_peer_outs; ++i) {
             ok = a->peer_out[i] != nullptr && !mis16(a->peer_out[i]);
+        }
+        if (a->multicast_out != nullptr) {
+            ok = ok && a->num_peer_outs == 0 && !mis16(a->multicast_out);
         }
         if (!ok) {
             return NNB200_UNSUPPORTED;
@@ -470,6 +479,7 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
         ep.k = static_cast<int32_t>(a->k);
         ep.out_scale = a->out_scale;
         ep.out_zp = a->out_zp;
+        ep.mc_out = a->multicast_out;
         ep.num_peers = a->num_peer_outs;
         for (int i = 0; i < a->num_peer_outs; ++i) {
             ep.peer_out[i] = a->peer_out[i];
@@ -805,6 +815,45 @@ int nnb200_copy_h2d_async(void* dst_device, const void* src_host, size_t bytes, 
         cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
 }
 
+namespace {
+// Stream-ordered scratch comes from a private pool per device that keeps its memory between
+// calls (release threshold: never).  The device's default pool hands freed memory back to the
+// driver at every synchronisation, which made each staged call pay for fresh physical memory
+// (0.4 ms per int8 Linear with host-side scale arrays).  The reference does the same
+// (src/backend/cuda/matmul/gemm_common.cuh:296-318).
+std::mutex g_pool_mutex;
+cudaMemPool_t g_pool[nnb200::kMaxDevices];
+bool g_pool_ready[nnb200::kMaxDevices];
+
+cudaMemPool_t scratch_pool_for_current_device()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= nnb200::kMaxDevices) {
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    if (!g_pool_ready[dev]) {
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        cudaMemPool_t pool = nullptr;
+        if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        uint64_t keep = UINT64_MAX;
+        if (cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep) != cudaSuccess) {
+            (void)cudaGetLastError();
+        }
+        g_pool[dev] = pool;
+        g_pool_ready[dev] = true;
+    }
+    return g_pool[dev];
+}
+}  // namespace
+
 int nnb200_scratch_alloc_async(void** out, size_t bytes, void* stream)
 {
     if (out == nullptr) {
@@ -814,7 +863,9 @@ int nnb200_scratch_alloc_async(void** out, size_t bytes, void* stream)
     if (bytes == 0) {
         return NNB200_OK;
     }
-    const cudaError_t e = cudaMallocAsync(out, bytes, static_cast<cudaStream_t>(stream));
+    cudaMemPool_t pool = scratch_pool_for_current_device();
+    const cudaError_t e = pool != nullptr ? cudaMallocFromPoolAsync(out, bytes, pool, static_cast<cudaStream_t>(stream))
+                                          : cudaMallocAsync(out, bytes, static_cast<cudaStream_t>(stream));
     if (e == cudaErrorMemoryAllocation) {
         cudaGetLastError();
         return NNB200_OUT_OF_MEMORY;
@@ -929,9 +980,9 @@ uint64_t nnb200_launch_count(void)
     return g_launches.load(std::memory_order_relaxed);
 }
 
-int nnb200_measure_i8_mma_peak(int32_t iters, double* ops, void* stream)
+int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double* ops, void* stream)
 {
-    if (iters < 1 || iters > (1 << 21)) {
+    if (iters < 1 || iters > (1 << 21) || pattern < 0 || pattern > 1) {
         return NNB200_INVALID_ARGUMENT;   // the upper bound keeps the launch well inside the bounded wait
     }
     const DeviceInfo* dev = current_device_info();
@@ -941,7 +992,7 @@ int nnb200_measure_i8_mma_peak(int32_t iters, double* ops, void* stream)
     if (dev->cc_major != 10) {
         return NNB200_UNSUPPORTED;
     }
-    return launch_mma_i8_peak(iters, ops, *dev, static_cast<cudaStream_t>(stream));
+    return launch_mma_i8_peak(iters, pattern, ops, *dev, static_cast<cudaStream_t>(stream));
 }
 
 int nnb200_set_knob(int id, int value)

@@ -41,6 +41,9 @@ struct I8Epilogue {
     // buffers, mapped into this process for peer-to-peer stores.  8-bit destinations only.
     int32_t num_peers;
     void* peer_out[7];
+    // The same window inside a multicast mapping bound to every rank's copy (this rank's too):
+    // tiles are stored once with multimem.st and replicated by the switch; peer_out is unused.
+    void* mc_out;
 };
 
 __device__ __forceinline__ float act_apply(int32_t act, float alpha, float beta, float x)

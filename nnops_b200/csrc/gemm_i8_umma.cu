@@ -60,7 +60,7 @@ struct TileConfig {
     static constexpr int kBTileBytes = BN * kBlockKBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     // Ring depth: as many stages as fit beside the epilogue staging in ~200 KB.
-    static constexpr int kStages = PEERS ? ((BN == 256) ? (PEERS == 1 ? 4 : 3) : 5)
+    static constexpr int kStages = PEERS ? ((BN == 256) ? (PEERS == 1 ? 4 : 3) : (BN == 224 ? 4 : 5))
                                    : (BN > 256) ? (BN > 384 ? 2 : 3)
                                                 : ((BN > 128) ? 4 : (BN == 128 ? 6 : 8));
     // Two accumulators BN columns apart (one when BN > 256); a power of two of at least that.
@@ -484,8 +484,9 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const float hi = (KIND == NNB200_OUT_S8 ? 127.0f : 255.0f) - zpf;
                 const int row0 = tc.m_blk * kBlockM + quarter * 32;
                 const int num_dst = 1 + ep.num_peers;
+                const bool multicast = ep.mc_out != nullptr;
 #pragma unroll 1
-                for (int c4 = 0; c4 < BN / 128; ++c4) {
+                for (int c4 = 0; c4 < (BN + 127) / 128; ++c4) {
                     const int n128 = n_base + c4 * 128;
                     if (n128 >= n_total) {
                         break;  // uniform across the warp
@@ -502,6 +503,9 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll 1
                     for (int cc = 0; cc < 4; ++cc) {
                         const int c = c4 * 4 + cc;
+                        if (c >= BN / 32) {
+                            break;  // a 224-wide tile ends inside its second 128-column group
+                        }
                         uint32_t v[32];
                         tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                         tmem_ld_wait();
@@ -523,6 +527,25 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         uint4* srow = reinterpret_cast<uint4*>(stage + lane * 128);
                         srow[(2 * cc) ^ (lane & 7)] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                         srow[(2 * cc + 1) ^ (lane & 7)] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    }
+                    if (multicast) {
+                        // One store per tile for all ranks: the staged rows go out as 16-byte
+                        // multimem stores, eight lanes covering one 128-byte row, four rows per
+                        // pass, and the switch replicates them into every rank's copy.
+                        __syncwarp();
+                        const int piece = lane & 7;
+                        const int cols_here = min(min(128, BN - c4 * 128), n_total - n128);
+#pragma unroll 1
+                        for (int pass = 0; pass < 8; ++pass) {
+                            const int r = pass * 4 + (lane >> 3);
+                            const int64_t grow = static_cast<int64_t>(row0) + r;
+                            if (grow < m_total && piece * 16 < cols_here) {
+                                const uint4 q = *reinterpret_cast<const uint4*>(stage + r * 128 + ((piece ^ (r & 7)) * 16));
+                                multimem_st_16(static_cast<uint8_t*>(ep.mc_out) + grow * ep.ldc + n128 + piece * 16, q);
+                            }
+                        }
+                        __syncwarp();  // the staging tile may be refilled
+                        continue;
                     }
                     fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA engine
                     __syncwarp();
@@ -557,6 +580,9 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
         if constexpr (PEERS) {
+            if (ep.mc_out != nullptr) {
+                __threadfence_system();  // this warp's multicast stores are performed before the kernel completes
+            }
             if (lane == 0) {
                 bulk_wait_group<0>();  // every bulk store of this warp has completed before the CTA exits
             }
@@ -937,11 +963,13 @@ template <int BN>
 int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m, int n, int k,
               uint32_t idesc, int vec_ok, const DeviceInfo& dev, cudaStream_t stream)
 {
-    if (ep.num_peers > 0) {
-        // Sharded write-back exists for the 8-bit destinations and 128-column groups.
+    if (ep.num_peers > 0 || ep.mc_out != nullptr) {
+        // Sharded write-back exists for the 8-bit destinations: 256- and 128-wide tiles, and --
+        // multicast stores only, whose pieces need not be whole 128-byte boxes -- 224-wide ones.
         // knob I8_PEER_STAGING = 1 / 2 forces the staging depth (measurement aid).
         // Up to three peers (measured at one and three: 0.380 -> 0.346 and 0.262 -> 0.237 ms per step) the
         // deeper ring pays; from four on the stores dominate and the measured form, two staging tiles, stays.
+        // Multicast stores leave the SM as ordinary stores: one staging tile per warp is all they need.
         bool single = ep.num_peers <= 3;
         if (const int staging = knob(NNB200_KNOB_I8_PEER_STAGING); staging == 1 || staging == 2) {
             single = staging == 1;
@@ -956,6 +984,14 @@ int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, cons
                 return single
                            ? launch_variant<BN, NNB200_OUT_U8, 1>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream)
                            : launch_variant<BN, NNB200_OUT_U8, 2>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+            }
+        }
+        if constexpr (BN == 224) {
+            if (ep.mc_out != nullptr && kind == NNB200_OUT_S8) {
+                return launch_variant<BN, NNB200_OUT_S8, 1>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+            }
+            if (ep.mc_out != nullptr && kind == NNB200_OUT_U8) {
+                return launch_variant<BN, NNB200_OUT_U8, 1>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
             }
         }
         return NNB200_UNSUPPORTED;
@@ -996,13 +1032,25 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
     // padded work over whole waves (waves x width; ties to the wider tile); narrow problems
     // trade arithmetic intensity for parallelism.
     const int num_m = (m + kBlockM - 1) / kBlockM;
+    const bool sharded = ep.num_peers > 0 || ep.mc_out != nullptr;
     int bn = 256;
     if (static_cast<int64_t>(num_m) * ((n + 255) / 256) < dev.sm_count) {
         bn = 128;
-        if (static_cast<int64_t>(num_m) * ((n + 127) / 128) < dev.sm_count && ep.num_peers == 0) {
+        if (static_cast<int64_t>(num_m) * ((n + 127) / 128) < dev.sm_count && !sharded) {
             bn = 64;
         }
-    } else if (ep.num_peers == 0) {
+    } else if (sharded) {
+        // A shard of a wide layer often ends a little past a whole number of waves (N / 8 = 3584:
+        // 448 tiles of 256 columns on 148 SMs = 3.03 waves).  With multicast stores the 224-wide
+        // tile is available: 512 tiles = 3.46 waves, an eighth less padded work.
+        const auto padded_work = [&](int width) {
+            const int64_t tiles = static_cast<int64_t>(num_m) * ((n + width - 1) / width);
+            return (tiles + dev.sm_count - 1) / dev.sm_count * width;
+        };
+        if (ep.mc_out != nullptr && padded_work(224) * 100 < padded_work(256) * 92) {
+            bn = 224;
+        }
+    } else {
         const auto padded_work = [&](int width) {
             const int64_t tiles = static_cast<int64_t>(num_m) * ((n + width - 1) / width);
             return (tiles + dev.sm_count - 1) / dev.sm_count * width;
@@ -1060,7 +1108,7 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
         const int pair_knob = knob(NNB200_KNOB_I8_PAIR);
         const char pair_mode = pair_knob < 0 ? '0' : static_cast<char>('0' + (pair_knob > 2 ? 1 : pair_knob));
         const int64_t pair_tiles = static_cast<int64_t>((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + 255) / 256);
-        if (pair_mode != '0' && ep.num_peers == 0 && m >= 4 * kBlockM && pair_tiles >= dev.sm_count / 2 && bn == 256) {
+        if (pair_mode != '0' && !sharded && m >= 4 * kBlockM && pair_tiles >= dev.sm_count / 2 && bn == 256) {
             const int st = launch_pair_bn<256>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
             if (st != NNB200_UNSUPPORTED || pair_mode == '2') {
                 return st;

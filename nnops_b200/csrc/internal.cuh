@@ -97,7 +97,7 @@ int launch_q4_1_decode(const void* w_blocks, int64_t ldw_blocks, int64_t rows, i
 int launch_quantize_linear(const nnb200_quant_linear_args& q, const DeviceInfo& dev, cudaStream_t stream);
 int launch_dequantize_linear(const nnb200_quant_linear_args& q, const DeviceInfo& dev, cudaStream_t stream);
 
-int launch_mma_i8_peak(int iters, double* ops_out, const DeviceInfo& dev, cudaStream_t stream);
+int launch_mma_i8_peak(int iters, int pattern, double* ops_out, const DeviceInfo& dev, cudaStream_t stream);
 
 int64_t i8_pack_pitch(int64_t k);
 int launch_i8_pack(const void* w, int64_t n, int64_t k, int64_t stride_n, int64_t stride_k, const float* scale_w,

@@ -3,7 +3,7 @@
 //
 // The roofline of the int8 GEMM needs a denominator that is a property of the part, not of a
 // library: one CTA per SM holds one 128 x 128-byte A tile and one 256 x 128-byte W tile in shared
-// memory (zero-filled, in the 128-byte-swizzled K-major layout the GEMM uses), and a single
+// memory (zero-filled or pseudo-random, in the 128-byte-swizzled K-major layout the GEMM uses), and a single
 // thread issues `iters` groups of four M128 x N256 x K32 MMAs -- exactly the instruction, shape,
 // descriptors and two alternating TMEM accumulators of gemm_i8_umma_kernel -- with nothing to
 // wait for: no TMA, no epilogue, no global traffic.  What limits it is the tensor pipe and the
@@ -25,7 +25,8 @@ constexpr int kPeakBTile = kPeakN * kPeakKBytes;        // 32 KB
 constexpr int kPeakSmem = kPeakATile + kPeakBTile + 1024;   // + alignment slack
 constexpr int kPeakTmemCols = 512;                      // two 256-column accumulators
 
-__global__ void __launch_bounds__(128, 1) mma_i8_peak_kernel(const int iters, const uint32_t idesc, int32_t* error_word)
+__global__ void __launch_bounds__(128, 1) mma_i8_peak_kernel(const int iters, const int pattern, const uint32_t idesc,
+                                                             int32_t* error_word)
 {
     extern __shared__ __align__(1024) uint8_t peak_smem[];
     __shared__ __align__(8) uint64_t done_bar;
@@ -33,8 +34,17 @@ __global__ void __launch_bounds__(128, 1) mma_i8_peak_kernel(const int iters, co
     __shared__ int abort_word;
 
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(peak_smem) + 1023) & ~uintptr_t(1023));
+    // pattern 0: zeros (the pipe's issue rate, next to no switching power); 1: pseudo-random
+    // bytes (what the same instruction stream holds once the operands toggle and the power cap
+    // sets the clock).
     for (int i = threadIdx.x; i < (kPeakATile + kPeakBTile) / 16; i += blockDim.x) {
-        reinterpret_cast<uint4*>(tiles)[i] = make_uint4(0u, 0u, 0u, 0u);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (pattern != 0) {
+            uint32_t h = static_cast<uint32_t>(i) * 2654435761u + blockIdx.x * 40503u + 0x9E3779B9u;
+            h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+            v = make_uint4(h, h * 3266489917u + 1u, (h ^ 0xA5A5A5A5u) * 668265263u, h * 374761393u + 7u);
+        }
+        reinterpret_cast<uint4*>(tiles)[i] = v;
     }
     const int warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) {
@@ -80,7 +90,7 @@ __global__ void __launch_bounds__(128, 1) mma_i8_peak_kernel(const int iters, co
 
 // Launch the probe on every SM.  *ops_out = integer operations (2 per multiply-add) the launch
 // performs; the caller divides by the time between its events.
-int launch_mma_i8_peak(int iters, double* ops_out, const DeviceInfo& dev, cudaStream_t stream)
+int launch_mma_i8_peak(int iters, int pattern, double* ops_out, const DeviceInfo& dev, cudaStream_t stream)
 {
     static bool attr_done[kMaxDevices];
     if (!attr_done[dev.device]) {
@@ -91,7 +101,7 @@ int launch_mma_i8_peak(int iters, double* ops_out, const DeviceInfo& dev, cudaSt
         attr_done[dev.device] = true;
     }
     const uint32_t idesc = umma_idesc(2, 1, 1, kPeakM, kPeakN);   // s32 accumulate, s8 x s8
-    mma_i8_peak_kernel<<<dev.sm_count, 128, kPeakSmem, stream>>>(iters, idesc, dev.error_word);
+    mma_i8_peak_kernel<<<dev.sm_count, 128, kPeakSmem, stream>>>(iters, pattern, idesc, dev.error_word);
     note_launch();
     if (ops_out != nullptr) {
         *ops_out = 2.0 * kPeakM * kPeakN * 32.0 * 4.0 * static_cast<double>(iters) * dev.sm_count;

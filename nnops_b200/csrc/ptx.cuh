@@ -320,6 +320,15 @@ __device__ __forceinline__ void st_global_32(void* p, uint32_t a, uint32_t b, ui
                  : "memory");
 }
 
+// 16-byte store to a MULTICAST address (a mapping of a multicast object bound to one buffer per
+// GPU): the NVSwitch writes the bytes into every bound buffer.  Only valid on such addresses.
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, uint4 v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
 // Named barrier over a subset of the CTA's warps.
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads)
 {

@@ -9,6 +9,11 @@ Two ways to put the full row-major [M,N] output on every rank:
 
 * ``mode="nccl"``  -- local GEMM into a dense [M, N/g] slab, NCCL all-gather over
   NVLink/NVSwitch into [g][M][N/g], then the library's interleave kernel writes [M,N].
+* ``mode="multicast"`` -- like ``fused``, but the outputs are symmetric-memory allocations bound
+  to one NVSwitch multicast object (``torch.distributed._symmetric_memory``: plumbing only), and
+  the epilogue stores each tile ONCE with ``multimem.st``; the switch replicates it into every
+  rank's copy.  A GPU then sends N/g columns instead of (g-1) times that.  Where the fabric
+  offers no multicast the layer falls back to ``fused`` over the same allocations.
 * ``mode="fused"`` -- the outputs are allocated with ``alloc_outputs`` (every rank maps every
   other rank's copy through CUDA IPC); the GEMM's epilogue then stores each finished tile into
   all g copies at once with peer-to-peer stores, so the all-gather overlaps the math tile by
@@ -73,9 +78,9 @@ class ShardedLinearI8:
         lo, hi = shard_bounds(n_total, world, rank)
         if w_shard.shape[0] != hi - lo:
             raise ValueError("weight shard has the wrong number of rows")
-        if mode not in ("nccl", "fused"):
-            raise ValueError("mode must be 'nccl' or 'fused'")
-        if mode == "fused" and out_kind not in ("s8", "u8"):
+        if mode not in ("nccl", "fused", "multicast"):
+            raise ValueError("mode must be 'nccl', 'fused' or 'multicast'")
+        if mode in ("fused", "multicast") and out_kind not in ("s8", "u8"):
             raise ValueError("the fused write-back serves 8-bit outputs")
         self.w = w_shard
         self.n_total, self.world, self.rank, self.group = n_total, world, rank, group
@@ -87,6 +92,8 @@ class ShardedLinearI8:
         self._plans: dict = {}    # (a ptr, M, out ptr) -> prepared argument block + buffers
         self._last = None
         self._peer_ptrs: dict = {}    # local output data_ptr -> addresses of the other ranks' copies, mapped here
+        self._mc_ptrs: dict = {}      # local output data_ptr -> address of the same buffer in the multicast mapping
+        self.multicast_active = False
         self._owners: list = []
         self._token = None
         if rank_order not in ("device", "nccl"):
@@ -107,8 +114,10 @@ class ShardedLinearI8:
         makes them storable from its kernels)."""
         dev = self.w.device
         dt = ops._OUT_TORCH[self.out_kind]
-        if self.mode != "fused":
+        if self.mode == "nccl":
             return [torch.empty((m, self.n_total), dtype=dt, device=dev) for _ in range(count)]
+        if self.mode == "multicast":
+            return self._alloc_symmetric(m, count)
         lib = capi.lib()
         nbytes = m * self.n_total                    # 8-bit outputs
         outs, handles = [], []
@@ -138,6 +147,57 @@ class ShardedLinearI8:
             self._map_flags()
         dist.barrier(group=self.group)                   # every rank has mapped everything
         return outs
+
+    def _alloc_symmetric(self, m: int, count: int) -> list[torch.Tensor]:
+        """Outputs from torch's symmetric-memory allocator: every rank's buffer is mapped on every
+        rank, and -- where the fabric supports it -- all of them are bound to one multicast
+        object whose mapping ``multimem.st`` can store to."""
+        import torch.distributed._symmetric_memory as symm_mem
+        dev = self.w.device
+        dt = ops._OUT_TORCH[self.out_kind]
+        group = self.group if self.group is not None else dist.group.WORLD
+        outs = []
+        with torch.cuda.device(dev):
+            for _ in range(count):
+                t = symm_mem.empty((m, self.n_total), dtype=dt, device=dev)
+                hdl = symm_mem.rendezvous(t, group)
+                self._owners.append((t, hdl))
+                mc = int(getattr(hdl, "multicast_ptr", 0) or 0)     # 0 where the fabric has no multicast
+                if mc:
+                    self._mc_ptrs[t.data_ptr()] = mc
+                else:
+                    self._peer_ptrs[t.data_ptr()] = [int(p) for r, p in enumerate(hdl.buffer_ptrs) if r != self.rank]
+                outs.append(t)
+        # Every rank must take the same path: multicast only if all of them have it.
+        have = torch.tensor([1 if self._mc_ptrs else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(have, op=dist.ReduceOp.MIN, group=self.group)
+        self.multicast_active = bool(have.item())
+        if not self.multicast_active and self._mc_ptrs:
+            for (t, hdl) in [o for o in self._owners if isinstance(o, tuple)]:
+                self._peer_ptrs[t.data_ptr()] = [int(p) for r, p in enumerate(hdl.buffer_ptrs) if r != self.rank]
+            self._mc_ptrs.clear()
+        self._token = torch.zeros(1, dtype=torch.int32, device=dev)
+        if self.rank_order == "device" and self._flags is None:
+            self._map_flags()
+        dist.barrier(group=self.group)
+        return outs
+
+    def close(self) -> None:
+        """Release the mapped and multicast-bound buffers while every rank is still alive: the
+        ranks meet, each drops its allocations, and they meet again.  Call before the process
+        group is destroyed."""
+        if self.world > 1:
+            torch.cuda.synchronize(self.w.device)
+            dist.barrier(group=self.group)
+        self._plans.clear()
+        self._last = None
+        self._peer_ptrs.clear()
+        self._mc_ptrs.clear()
+        self._owners.clear()
+        self._flags = None
+        if self.world > 1:
+            torch.cuda.synchronize(self.w.device)
+            dist.barrier(group=self.group)
 
     def _map_flags(self) -> None:
         """Flag arrays of the device-side rank barrier: one per rank, zeroed, mapped by every rank."""
@@ -196,7 +256,8 @@ class ShardedLinearI8:
     def _plan(self, a: torch.Tensor, out: torch.Tensor | None) -> dict:
         """Argument block and buffers for this (activations, destination) pair, built once."""
         m = a.shape[0]
-        fused = self.mode == "fused" and out is not None and out.data_ptr() in self._peer_ptrs
+        fused = self.mode in ("fused", "multicast") and out is not None and (
+            out.data_ptr() in self._peer_ptrs or out.data_ptr() in self._mc_ptrs)
         direct = self.world == 1 or fused
         key = (a.data_ptr(), m, out.data_ptr() if (out is not None and direct) else 0)
         plan = self._plans.get(key)
@@ -213,7 +274,9 @@ class ShardedLinearI8:
                 gathered = torch.empty((self.world * m, self.n_per), dtype=dt, device=a.device)  # [g][M][N/g]
             keep: list = []
             args = ops.gemm_i8_args(a, self.w, slab, out_kind=self.out_kind, keep=keep, **self.kw)
-            if fused:
+            if fused and out.data_ptr() in self._mc_ptrs:
+                args.multicast_out = self._mc_ptrs[out.data_ptr()] + self.col0 * out.element_size()
+            elif fused:
                 peers = self._peer_ptrs[out.data_ptr()]
                 args.num_peer_outs = len(peers)
                 for i, base in enumerate(peers):
@@ -256,7 +319,7 @@ class ShardedLinearI8:
         """Full row-major [M, N] output on every rank.  ``wait_for_readers``: in fused mode, order
         the ranks BEFORE the GEMM as well, for callers whose previous result in ``out`` may still
         be read on another rank when this call starts."""
-        if wait_for_readers and self.mode == "fused":
+        if wait_for_readers and self.mode in ("fused", "multicast"):
             self.rank_barrier()
         self.local(a, out)
         return self.reassemble(out)
