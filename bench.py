@@ -519,6 +519,25 @@ def operator_level_bench(steps: int, warmup: int):
     return {"unavailable": "tests/cpp/_bin/bench_linear_op_* not built (python -m nnops_b200.host.build)"}
 
 
+def secondary_i8_poses(torch, dev):
+    """MatMul's four operand poses at 4096^3, s8 x s8 -> s32 (the reference quotes its own tile
+    kernel on this shape, src/backend/cuda/matmul/matmul_i8_ptx.cu:474-479): 'nn' is MatMul's
+    default, A [M, K] x B [K, N]; 'nt' is Linear's pose."""
+    from nnops_b200 import ops
+    size = 4096
+    out = {}
+    o = torch.empty((size, size), dtype=torch.int32, device=dev)
+    for pose in ("nt", "nn", "tn", "tt"):
+        a_store = torch.randint(-127, 128, (size, size), dtype=torch.int8, device=dev)
+        b_store = torch.randint(-127, 128, (size, size), dtype=torch.int8, device=dev)
+        a = a_store.t() if pose[0] == "t" else a_store
+        w = b_store if pose[1] == "t" else b_store.t()
+        engine = ops.gemm_i8_engine(a, w, o, out_kind="s32")
+        us = graph_time_us(torch, lambda: ops.gemm_i8(a, w, out_kind="s32", out=o))
+        out[f"i8_matmul_{pose}_4096"] = {"tops": 2.0 * size ** 3 / us / 1e6, "us_per_call": us, "engine": engine}
+    return out
+
+
 def run_kernel_only(args):
     """Three launches of one kernel on seeded inputs and nothing else: the command the ncu
     captures under profiles/ are taken from (`--kernel-only i8|gemv|q4gemm|q4gemm2 --shape M N K`)."""
@@ -823,6 +842,7 @@ def main():
         extra["sustained"] = sus
         extra.update(secondary_q4_1(torch, dev, peaks))
         extra.update(secondary_i8_config2(torch, dev, peaks))
+        extra.update(secondary_i8_poses(torch, dev))
         extra.update(secondary_quant_linear(torch, dev, peaks))
         extra.update(secondary_i8_decode(torch, dev, peaks, layer.w, layer.kw["scale_w"], layer.kw["bias"]))
         extra["e2e_op"] = operator_level_bench(10, 3)

@@ -278,6 +278,9 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // Operand poses ride in bits 4-5 of vec_ok: bit 4 = A stored [K][M], bit 5 = W stored [K][N]
+    // (MN-major operands: the tensor maps, the descriptors and the K step change, nothing else).
+    const int pose = (vec_ok >> 4) & 3;
 
     const int num_m = (m_total + kBlockM - 1) / kBlockM;
     const int num_n = (n_total + BN - 1) / BN;
@@ -328,11 +331,25 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     uint8_t* a_dst = stage_base + stage * Cfg::kStageBytes;
                     uint8_t* b_dst = a_dst + Cfg::kATileBytes;
                     mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-                    tma_load_2d(a_dst, &map_a, &full_bar[stage], kb * kBlockKBytes, tc.m_blk * kBlockM);
+                    if (pose & 1) {
+                        // A stored [K][M]: the box is 128 k-rows of 128 m-bytes.
+                        tma_load_2d(a_dst, &map_a, &full_bar[stage], tc.m_blk * kBlockM, kb * kBlockKBytes);
+                    } else {
+                        tma_load_2d(a_dst, &map_a, &full_bar[stage], kb * kBlockKBytes, tc.m_blk * kBlockM);
+                    }
+                    if (pose & 2) {
+                        // W stored [K][N]: one box of 128 k-rows x 128 n-bytes per 128 columns of the tile.
 #pragma unroll
-                    for (int h = 0; h < Cfg::kNSplit; ++h) {  // TMA boxes hold at most 256 rows
-                        tma_load_2d(b_dst + h * Cfg::kMmaN * kBlockKBytes, &map_w, &full_bar[stage], kb * kBlockKBytes,
-                                    tc.n_blk * BN + h * Cfg::kMmaN);
+                        for (int blk = 0; blk < BN / 128; ++blk) {
+                            tma_load_2d(b_dst + blk * (128 * kBlockKBytes), &map_w, &full_bar[stage],
+                                        tc.n_blk * BN + blk * 128, kb * kBlockKBytes);
+                        }
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < Cfg::kNSplit; ++h) {  // TMA boxes hold at most 256 rows
+                            tma_load_2d(b_dst + h * Cfg::kMmaN * kBlockKBytes, &map_w, &full_bar[stage], kb * kBlockKBytes,
+                                        tc.n_blk * BN + h * Cfg::kMmaN);
+                        }
                     }
                     armed |= 1u << stage;
                     armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
@@ -386,19 +403,25 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(stage_base + stage * Cfg::kStageBytes);
                     const uint32_t b_addr = a_addr + Cfg::kATileBytes;
-                    const uint64_t a_desc = umma_desc_sw128_kmajor(a_addr);
-                    const uint64_t b_desc = umma_desc_sw128_kmajor(b_addr);
+                    // K-major tiles step 32 bytes along their 128-byte rows per MMA (+2 in the
+                    // descriptor's 16-byte units); MN-major tiles step 32 k-rows of 128 bytes (+256).
+                    const uint64_t a_desc = (pose & 1) ? umma_desc_sw128_mnmajor(a_addr, 128 * kBlockKBytes)
+                                                       : umma_desc_sw128_kmajor(a_addr);
+                    const uint64_t b_desc = (pose & 2) ? umma_desc_sw128_mnmajor(b_addr, 128 * kBlockKBytes)
+                                                       : umma_desc_sw128_kmajor(b_addr);
+                    const uint64_t a_step = (pose & 1) ? 256u : 2u;
+                    const uint64_t b_step = (pose & 2) ? 256u : 2u;
 #pragma unroll
                     for (int ks = 0; ks < kBlockKBytes / kUmmaK; ++ks) {
-                        // +32 bytes of K per step = +2 in the descriptor's 16-byte address units.
 #pragma unroll
                         for (int h = 0; h < Cfg::kNSplit; ++h) {
                             // Second half of a wide tile: kMmaN rows further down the W tile (16-byte
                             // descriptor units), kMmaN columns further along the accumulator.
                             umma_i8(d_tmem + static_cast<uint32_t>(h * Cfg::kMmaN),
-                                    a_desc + static_cast<uint64_t>(ks * 2),
-                                    b_desc + static_cast<uint64_t>(ks * 2 + h * (Cfg::kMmaN * kBlockKBytes / 16)), idesc,
-                                    (kb > 0 || ks > 0) ? 1u : 0u);
+                                    a_desc + static_cast<uint64_t>(ks) * a_step,
+                                    b_desc + static_cast<uint64_t>(ks) * b_step +
+                                        static_cast<uint64_t>(h * (Cfg::kMmaN * kBlockKBytes / 16)),
+                                    idesc, (kb > 0 || ks > 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(&empty_bar[stage]);  // slot is free once these MMAs have read it
@@ -1010,16 +1033,22 @@ int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, cons
 
 bool umma_i8_supported(const I8Problem& p)
 {
-    if (p.a_stride_k != 1 || p.w_stride_k != 1) {
-        return false;
-    }
     if (p.m < 1 || p.n < 1 || p.k < 1 || p.m > INT32_MAX || p.n > INT32_MAX || p.k > INT32_MAX) {
         return false;
     }
+    // Each operand in either pose, as long as TMA can address it: the contiguous index has
+    // stride 1, the other a pitch that is a multiple of 16 bytes and covers a row; 16-byte base.
     const auto aligned16 = [](uint64_t v) { return (v & 15u) == 0; };
-    return aligned16(reinterpret_cast<uintptr_t>(p.a)) && aligned16(reinterpret_cast<uintptr_t>(p.w)) &&
-           aligned16(static_cast<uint64_t>(p.a_stride_m)) && aligned16(static_cast<uint64_t>(p.w_stride_n)) &&
-           p.a_stride_m >= p.k && p.w_stride_n >= p.k;
+    const auto operand_ok = [&](const void* base, int64_t stride_mn, int64_t stride_k, int64_t mn, int64_t k) {
+        if (!aligned16(reinterpret_cast<uintptr_t>(base))) {
+            return false;
+        }
+        if (stride_k == 1) {   // K-major: rows of k bytes
+            return aligned16(static_cast<uint64_t>(stride_mn)) && stride_mn >= k;
+        }
+        return stride_mn == 1 && aligned16(static_cast<uint64_t>(stride_k)) && stride_k >= mn;   // MN-major
+    };
+    return operand_ok(p.a, p.a_stride_m, p.a_stride_k, p.m, p.k) && operand_ok(p.w, p.w_stride_n, p.w_stride_k, p.n, p.k);
 }
 
 int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream)
@@ -1082,12 +1111,29 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
             bn = v;
         }
     }
+    // Operand poses: MN-major means the operand's M / N index is the contiguous one in memory
+    // (MatMul's transpose_a, and its default [K, N] weights).  An MN-major W tile is brought in as
+    // whole 128-column blocks, so its width is 256 or 128.
+    const bool a_mn = p.a_stride_k != 1;
+    const bool w_mn = p.w_stride_k != 1;
+    if (w_mn && bn != 256 && bn != 128) {
+        bn = (bn > 256 || static_cast<int64_t>(num_m) * ((n + 255) / 256) >= dev.sm_count) ? 256 : 128;
+    }
+    const uint32_t major_bits = (a_mn ? kUmmaAMajorMN : 0u) | (w_mn ? kUmmaBMajorMN : 0u);
+    const auto idesc_of = [&](int mma_n) { return umma_idesc(2, p.a_unsigned ? 0u : 1u, 1, kBlockM, mma_n) | major_bits; };
 
     CUtensorMap map_a, map_w;
-    if (!make_tma_2d(&map_a, p.a, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(m),
-                     static_cast<uint64_t>(p.a_stride_m), kBlockKBytes, kBlockM) ||
-        !make_tma_2d(&map_w, p.w, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
-                     static_cast<uint64_t>(p.w_stride_n), kBlockKBytes, static_cast<uint32_t>(bn > 256 ? bn / 2 : bn))) {
+    const bool map_a_ok =
+        a_mn ? make_tma_2d(&map_a, p.a, 1, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
+                           static_cast<uint64_t>(p.a_stride_k), kBlockM, kBlockKBytes)
+             : make_tma_2d(&map_a, p.a, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(m),
+                           static_cast<uint64_t>(p.a_stride_m), kBlockKBytes, kBlockM);
+    const bool map_w_ok =
+        w_mn ? make_tma_2d(&map_w, p.w, 1, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
+                           static_cast<uint64_t>(p.w_stride_k), 128, kBlockKBytes)
+             : make_tma_2d(&map_w, p.w, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                           static_cast<uint64_t>(p.w_stride_n), kBlockKBytes, static_cast<uint32_t>(bn > 256 ? bn / 2 : bn));
+    if (!map_a_ok || !map_w_ok) {
         return NNB200_INTERNAL;
     }
 
@@ -1098,7 +1144,8 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
     // Destination vector stores: bit 0 = 16-byte aligned base and row pitch, bit 1 = 32-byte.
     const uint64_t pitch_bytes = static_cast<uint64_t>(ep.ldc) * static_cast<uint64_t>(elem);
     const int vec_ok = (((reinterpret_cast<uintptr_t>(ep.out) & 15u) == 0 && (pitch_bytes & 15u) == 0) ? 1 : 0) |
-                       (((reinterpret_cast<uintptr_t>(ep.out) & 31u) == 0 && (pitch_bytes & 31u) == 0) ? 2 : 0);
+                       (((reinterpret_cast<uintptr_t>(ep.out) & 31u) == 0 && (pitch_bytes & 31u) == 0) ? 2 : 0) |
+                       (a_mn ? 16 : 0) | (w_mn ? 32 : 0);   // bits 4-5: operand poses, read by the kernel
 
     const uint32_t a_fmt = p.a_unsigned ? 0u : 1u;
 
@@ -1108,7 +1155,7 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
         const int pair_knob = knob(NNB200_KNOB_I8_PAIR);
         const char pair_mode = pair_knob < 0 ? '0' : static_cast<char>('0' + (pair_knob > 2 ? 1 : pair_knob));
         const int64_t pair_tiles = static_cast<int64_t>((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + 255) / 256);
-        if (pair_mode != '0' && !sharded && m >= 4 * kBlockM && pair_tiles >= dev.sm_count / 2 && bn == 256) {
+        if (pair_mode != '0' && !sharded && !a_mn && !w_mn && m >= 4 * kBlockM && pair_tiles >= dev.sm_count / 2 && bn == 256) {
             const int st = launch_pair_bn<256>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
             if (st != NNB200_UNSUPPORTED || pair_mode == '2') {
                 return st;
@@ -1117,31 +1164,31 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
     }
     switch (bn) {
     case 512:
-        return launch_bn<512>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 256), vec_ok,
+        return launch_bn<512>(ep.out_kind, map_a, map_w, ep, m, n, k, idesc_of(256), vec_ok,
                               dev, stream);
     case 448:
-        return launch_bn<448>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 224), vec_ok,
+        return launch_bn<448>(ep.out_kind, map_a, map_w, ep, m, n, k, idesc_of(224), vec_ok,
                               dev, stream);
     case 384:
-        return launch_bn<384>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 192), vec_ok,
+        return launch_bn<384>(ep.out_kind, map_a, map_w, ep, m, n, k, idesc_of(192), vec_ok,
                               dev, stream);
     case 320:
-        return launch_bn<320>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 160), vec_ok,
+        return launch_bn<320>(ep.out_kind, map_a, map_w, ep, m, n, k, idesc_of(160), vec_ok,
                               dev, stream);
     case 256:
-        return launch_bn<256>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 256), vec_ok,
+        return launch_bn<256>(ep.out_kind, map_a, map_w, ep, m, n, k, idesc_of(256), vec_ok,
                               dev, stream);
     case 224:
-        return launch_bn<224>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 224), vec_ok,
+        return launch_bn<224>(ep.out_kind, map_a, map_w, ep, m, n, k, idesc_of(224), vec_ok,
                               dev, stream);
     case 192:
-        return launch_bn<192>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 192), vec_ok,
+        return launch_bn<192>(ep.out_kind, map_a, map_w, ep, m, n, k, idesc_of(192), vec_ok,
                               dev, stream);
     case 128:
-        return launch_bn<128>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 128), vec_ok,
+        return launch_bn<128>(ep.out_kind, map_a, map_w, ep, m, n, k, idesc_of(128), vec_ok,
                               dev, stream);
     default:
-        return launch_bn<64>(ep.out_kind, map_a, map_w, ep, m, n, k, umma_idesc(2, a_fmt, 1, kBlockM, 64), vec_ok,
+        return launch_bn<64>(ep.out_kind, map_a, map_w, ep, m, n, k, idesc_of(64), vec_ok,
                              dev, stream);
     }
 }

@@ -255,6 +255,27 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_kmajor(uint32_t smem_addr)
     return d;
 }
 
+// Shared-memory matrix descriptor for an MN-major operand tile (the operand's M or N index is
+// the contiguous one in memory: A stored [K][M], W stored [K][N]) written by TMA with the
+// 128-byte swizzle: rows of 128 bytes along M/N, one row per k, eight k-rows per 1024-byte
+// swizzle group (stride byte offset), and `block_bytes` between consecutive 128-byte column
+// blocks of a tile wider than 128 (leading byte offset).  Stepping along K by 32 rows adds
+// 32 * 128 bytes to the start address.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mnmajor(uint32_t smem_addr, uint32_t block_bytes)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+    d |= static_cast<uint64_t>((block_bytes >> 4) & 0x3FFFu) << 16;  // leading byte offset: next 128-byte block
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset: 8 k-rows * 128 B
+    d |= static_cast<uint64_t>(1) << 46;                      // descriptor version (sm_100)
+    d |= static_cast<uint64_t>(2) << 61;                      // layout: 128-byte swizzle
+    return d;
+}
+
+// Instruction-descriptor bits that declare an operand MN-major instead of K-major.
+constexpr uint32_t kUmmaAMajorMN = 1u << 15;
+constexpr uint32_t kUmmaBMajorMN = 1u << 16;
+
 // Instruction descriptor, dense, both operands K-major.
 //   d_fmt: 0 = f16, 1 = f32, 2 = s32;  a_fmt / b_fmt: kind::i8 0 = u8, 1 = s8; kind::f16 0 = f16, 1 = bf16.
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t d_fmt, uint32_t a_fmt, uint32_t b_fmt, uint32_t m,

@@ -230,7 +230,9 @@ def test_cta_pair_form(cuda_device, nnb200_lib, case, knobs):
               out_scale=0.9, out_zp=0 if kind == "s32" else 3, engine="umma", seed=m + n)
 
 
-def test_transposed_poses_use_generic(cuda_device, nnb200_lib):
+def test_transposed_poses_off_the_tma_rule_use_generic(cuda_device, nnb200_lib):
+    """[K, M] activations and [K, N] weights whose row pitch is not a multiple of 16 bytes cannot
+    be addressed by TMA: the generic engine serves them."""
     rng = np.random.default_rng(5)
     m, n, k = 70, 90, 200
     a_km = rng.integers(-127, 128, (k, m), dtype=np.int8)   # MatMul transpose_a storage
@@ -238,7 +240,55 @@ def test_transposed_poses_use_generic(cuda_device, nnb200_lib):
     want = oracle.gemm_i8(a_km.T, w_kn.T, out_kind="s8", out_scale=40.0)
     ta = torch.from_numpy(a_km).to(cuda_device).t()
     tw = torch.from_numpy(w_kn).to(cuda_device).t()
+    o = torch.empty((m, n), dtype=torch.int8, device=cuda_device)
+    assert ops.gemm_i8_engine(ta, tw, o, out_kind="s8", out_scale=40.0) == "generic"
     got = ops.gemm_i8(ta, tw, out_kind="s8", out_scale=40.0)
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("pose", ["nn", "tn", "tt", "nt"])          # (transpose_a, transpose_b) of MatMul: n = no, t = yes
+@pytest.mark.parametrize("shape", [(256, 512, 384), (144, 272, 208), (1008, 4112, 96), (2048, 9008, 640), (144, 144, 144)])
+@pytest.mark.parametrize("out_kind", ["s32", "s8", "f16"])
+def test_matmul_poses_on_the_tensor_core_engine(cuda_device, nnb200_lib, pose, shape, out_kind):
+    """MatMul's four operand poses on the tcgen05 engine (reference: one tile kernel templated on
+    TransA / TransB, src/backend/cuda/matmul/matmul_i8_ptx.cu:22-24).  'nn' is MatMul's default:
+    A [M, K], B [K, N].  M / N / K off the tile sizes (multiples of 16, as TMA's pitch rule asks), u8 and
+    s8 activations, zero points, every kind of destination."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k + len(pose))
+    a_unsigned = (m + n) % 2 == 0
+    a_t, b_t = pose[0] == "t", pose[1] == "t"
+    # Storage: A as [M, K] or (transpose_a) [K, M]; B as [K, N] or (transpose_b) [N, K].
+    a_store = rng.integers(0, 256, (k, m) if a_t else (m, k), dtype=np.uint8) if a_unsigned else \
+        rng.integers(-127, 128, (k, m) if a_t else (m, k), dtype=np.int8)
+    b_store = rng.integers(-127, 128, (n, k) if b_t else (k, n), dtype=np.int8)
+    a_log = a_store.T if a_t else a_store              # logical [M, K]
+    w_log = b_store if b_t else b_store.T              # logical [N, K]
+    kw = dict(out_kind=out_kind, scale_a=rng.uniform(0.01, 0.03, m).astype(np.float32),
+              scale_w=rng.uniform(0.001, 0.02, n).astype(np.float32), zp_a=128 if a_unsigned else 3,
+              zp_w=rng.integers(-9, 10, n).astype(np.int32), out_scale=2.3, out_zp=0 if out_kind == "s32" else 4)
+    want = oracle.gemm_i8(a_log, w_log, **kw)
+    ta = torch.from_numpy(a_store).to(cuda_device)
+    tb = torch.from_numpy(b_store).to(cuda_device)
+    ta = ta.t() if a_t else ta
+    tw = tb if b_t else tb.t()
+    o = torch.empty((m, n), dtype=ops._OUT_TORCH[out_kind], device=cuda_device)
+    assert ops.gemm_i8_engine(ta, tw, o, engine="umma", **kw) == "umma"
+    got = ops.gemm_i8(ta, tw, engine="umma", **kw).cpu().numpy()
+    if not np.array_equal(got.view(np.uint8), want.view(np.uint8)):
+        bad = np.argwhere(got != want)
+        raise AssertionError(f"{len(bad)} mismatches of {got.size}; first {bad[:5].tolist()}")
+
+
+def test_matmul_default_pose_takes_the_tensor_core_engine_by_itself(cuda_device, nnb200_lib):
+    """MatMul::create({}, Backend::CUDA) on s8 [M, K] x [K, N] must not fall to the SIMT engine."""
+    m = n = k = 1024
+    a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=cuda_device)
+    b_kn = torch.randint(-127, 128, (k, n), dtype=torch.int8, device=cuda_device)
+    o = torch.empty((m, n), dtype=torch.int32, device=cuda_device)
+    assert ops.gemm_i8_engine(a, b_kn.t(), o, out_kind="s32") == "umma"
+    got = ops.gemm_i8(a, b_kn.t(), out=o)
+    want = oracle.gemm_i8(a.cpu().numpy(), b_kn.cpu().numpy().T)
     assert np.array_equal(got.cpu().numpy(), want)
 
 
