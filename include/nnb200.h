@@ -251,6 +251,13 @@ typedef struct nnb200_q4_1_args {
                              warp MMA after per-weight dequantisation, 5 two-pass GEMM (needs the workspace),
                              6 GEMV with warp MMA on raw nibbles, scale and minimum applied per block afterwards */
     int32_t flags;        /* NNB200_Q4_FLAG_* */
+    /* Prepacked weights (nnb200_q4_1_pack): when w_dm is not NULL, w_blocks points at the nibble
+     * plane -- 16 bytes per block, ldw_blocks still counted in blocks -- and w_dm at the plane of
+     * (f16 d, f16 m) pairs, 4 bytes per block, rows ld_dm blocks apart.  Served by the GEMV
+     * engine with deferred scaling and by the two-pass GEMM; other shapes of call answer
+     * NNB200_UNSUPPORTED. */
+    const void* w_dm;
+    int64_t ld_dm;
 } nnb200_q4_1_args;
 
 /* The launch may begin while the preceding kernel of the stream is still finishing
@@ -299,6 +306,30 @@ NNB200_API int nnb200_i8_pack(const void* w, int64_t n, int64_t k, int64_t w_str
                               const float* scale_w, float scale_w_scalar, const int32_t* zp_w, int32_t zp_w_scalar,
                               void* blob, size_t blob_bytes, void* stream);
 NNB200_API int nnb200_i8_packed_view(const void* blob, int64_t n, int64_t k, nnb200_i8_packed* view);
+
+/*
+ * Prepacked Q4_1 weights: the raw llama.cpp stream interleaves a 4-byte (d, m) header with 16
+ * nibble bytes, so a block is only 4-byte aligned and no load wider than 32 bits can be aimed
+ * at it.  The packed form separates the two: a nibble plane [n][row of ceil(k/32) 16-byte
+ * entries] whose every block is 16-byte aligned, then a (d, m) plane [n][ceil(k/32) 4-byte
+ * entries]; both row pitches are rounded up to 16 bytes.  Same 20 bytes per block in total, so
+ * the bytes a product moves are unchanged.  This is the "Q4_1 repacked into separated scale
+ * and nibble planes" form of the operators' two-step prepackWeights contract (reference
+ * include/nnops/core/op_base.hpp:72-80; its CUDA front end answers "no packed form",
+ * src/ops/linear.cpp:125-128).  One-time cost, a pure re-layout: decoding the planes gives the
+ * same values bit for bit.
+ */
+typedef struct nnb200_q4_1_packed {
+    const void* qs;     /* nibble plane */
+    int64_t qs_pitch;   /* its row pitch in 16-byte blocks */
+    const void* dm;     /* (d, m) plane */
+    int64_t dm_pitch;   /* its row pitch in 4-byte entries */
+} nnb200_q4_1_packed;
+
+NNB200_API size_t nnb200_q4_1_pack_bytes(int64_t n, int64_t k);
+NNB200_API int nnb200_q4_1_pack(const void* w_blocks, int64_t ldw_blocks, int64_t n, int64_t k, void* blob,
+                                size_t blob_bytes, void* stream);
+NNB200_API int nnb200_q4_1_packed_view(const void* blob, int64_t n, int64_t k, nnb200_q4_1_packed* view);
 
 /*
  * QuantizeLinear / DequantizeLinear (reference operators include/nnops/ops/quant_linear.hpp:24-141;

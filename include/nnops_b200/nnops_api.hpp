@@ -106,7 +106,7 @@ struct Epilogue {
 /// Dense, plus this backend's packed int8 weight (nnb200_i8_pack's blob).  The reference numbers
 /// its layout tags append-only and 15 is its highest (include/nnops/core/tensor_layout.hpp:100-118);
 /// 16 is the next free value.
-enum class TensorLayout : uint8_t { Dense = 0, PackedI8B200 = 16 };
+enum class TensorLayout : uint8_t { Dense = 0, PackedI8B200 = 16, PackedQ4_1B200 = 17 };
 
 /// Fixed-capacity dimension list (the reference uses an inline small vector of 8).
 struct Dims {
@@ -280,7 +280,9 @@ public:
                    void* workspace = nullptr) override;
     /// int8 weights on CUDA: the query answers a [N, K] s8 view tagged TensorLayout::PackedI8B200
     /// whose pitch makes N * pitch the blob size; the second call fills it.  compute() accepts
-    /// the packed view in place of W.  Other weights answer "no packed form".
+    /// the packed view in place of W.  q4_1 weights: a [N, K] q4_1 view tagged
+    /// TensorLayout::PackedQ4_1B200 (separate nibble and (d, m) planes), same two steps.  Other
+    /// weights answer "no packed form".
     void prepackWeights(std::span<const TensorView> inputs, std::span<TensorView> outputs,
                         const ComputeContext& ctx = {}) override;
     OpType getOpType() const override { return OpType::Linear; }
@@ -401,6 +403,8 @@ Status matmul_cuda(const MatMulAttributes& attrs, TensorView& output, std::span<
                    const ComputeContext& ctx, void* workspace);
 /// Two-step prepack of a 2-D int8 weight (w_is_nk: stored [N, K], else [K, N]); see Linear::prepackWeights.
 void prepack_i8_cuda(const TensorView& weight, bool w_is_nk, TensorView& packed, const ComputeContext& ctx);
+/// Two-step prepack of a 2-D q4_1 weight stored [N, K] into separated nibble and (d, m) planes.
+void prepack_q4_1_cuda(const TensorView& weight, TensorView& packed, const ComputeContext& ctx);
 /// ... and the two of QuantizeLinear / DequantizeLinear (declared at src/ops/quant_linear.cpp:21-28).
 Status quantize_linear_cuda(const QuantLinearAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
                             const ComputeContext& ctx, void* workspace);

@@ -63,6 +63,7 @@ class Q41Args(C.Structure):
         ("alpha", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("force_engine", C.c_int32), ("flags", C.c_int32),
+        ("w_dm", C.c_void_p), ("ld_dm", C.c_int64),
     ]
 
 
@@ -76,6 +77,11 @@ class I8Packed(C.Structure):
     """Mirror of nnb200_i8_packed: the sections of a packed int8 weight."""
     _fields_ = [("w", C.c_void_p), ("pitch", C.c_int64), ("scale_w", C.c_void_p), ("zp_w", C.c_void_p),
                 ("r_w", C.c_void_p)]
+
+
+class Q41Packed(C.Structure):
+    """Mirror of nnb200_q4_1_packed: the two planes of a packed Q4_1 weight."""
+    _fields_ = [("qs", C.c_void_p), ("qs_pitch", C.c_int64), ("dm", C.c_void_p), ("dm_pitch", C.c_int64)]
 
 
 class QuantLinearArgs(C.Structure):
@@ -103,6 +109,9 @@ SYMBOLS = [
     ("nnb200_i8_pack", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_float,
                                  C.c_void_p, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("nnb200_i8_packed_view", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.POINTER(I8Packed)]),
+    ("nnb200_q4_1_pack_bytes", C.c_size_t, [C.c_int64, C.c_int64]),
+    ("nnb200_q4_1_pack", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]),
+    ("nnb200_q4_1_packed_view", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.POINTER(Q41Packed)]),
     ("nnb200_quantize_linear", C.c_int, [C.POINTER(QuantLinearArgs), C.c_void_p]),
     ("nnb200_dequantize_linear", C.c_int, [C.POINTER(QuantLinearArgs), C.c_void_p]),
     ("nnb200_interleave_shards", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64,

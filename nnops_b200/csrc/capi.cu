@@ -523,6 +523,11 @@ static bool valid_q4_args(const nnb200_q4_1_args* q)
         return false;
     }
     const int64_t nblk = (q->k + 31) / 32;
+    if (q->w_dm != nullptr &&
+        (q->ld_dm < nblk || (reinterpret_cast<uintptr_t>(q->w_dm) & 15u) != 0 ||
+         (reinterpret_cast<uintptr_t>(q->w_blocks) & 15u) != 0 || (q->ld_dm % 4) != 0)) {
+        return false;   // the planes of a packed weight are 16-byte aligned, rows included
+    }
     return q->lda >= q->k && q->ldc >= q->n && q->ldw_blocks >= nblk;
 }
 
@@ -552,6 +557,19 @@ size_t nnb200_q4_1_workspace_bytes(const nnb200_q4_1_args* q)
 int nnb200_q4_1_engine(const nnb200_q4_1_args* q)
 {
     if (!valid_q4_args(q)) {
+        return -1;
+    }
+    if (q->w_dm != nullptr) {
+        // Packed weights (separate nibble and (d, m) planes): the two-pass GEMM for tall calls that
+        // bring its scratch, else the deferred-scaling GEMV; -1 when neither can take the call.
+        if (q->force_engine == 0 || q->force_engine == 5) {
+            if (q->m >= two_pass_min_rows(q) && q4_1_two_pass_supported(*q)) {
+                return 5;
+            }
+        }
+        if (q->force_engine == 0 || q->force_engine == 2 || q->force_engine == 6) {
+            return q4_1_gemv_dsq_supported(*q) ? 6 : -1;
+        }
         return -1;
     }
     // 1 = fused tensor-core GEMM (tcgen05), 3 = GEMV on CUDA cores, 4 = GEMV with warp-level MMA
@@ -609,6 +627,7 @@ int nnb200_linear_q4_1(const nnb200_q4_1_args* q, void* stream_v)
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     switch (nnb200_q4_1_engine(q)) {
+    case -1: return NNB200_UNSUPPORTED;   // packed weights in a shape no engine takes them in
     case 1: return launch_q4_1_gemm_umma(*q, *dev, stream);
     case 5: return launch_q4_1_two_pass(*q, *dev, stream);
     case 4: return launch_q4_1_gemv_mma(*q, *dev, stream);
@@ -635,6 +654,48 @@ size_t nnb200_i8_pack_bytes(int64_t n, int64_t k)
         return 0;
     }
     return static_cast<size_t>(n) * static_cast<size_t>(i8_pack_pitch(k) + 12);
+}
+
+size_t nnb200_q4_1_pack_bytes(int64_t n, int64_t k)
+{
+    if (n <= 0 || k <= 0) {
+        return 0;
+    }
+    return static_cast<size_t>(n) * (static_cast<size_t>(q4_1_pack_qs_pitch(k)) * 16 + static_cast<size_t>(q4_1_pack_dm_pitch(k)) * 4);
+}
+
+int nnb200_q4_1_packed_view(const void* blob, int64_t n, int64_t k, nnb200_q4_1_packed* view)
+{
+    if (blob == nullptr || view == nullptr || n <= 0 || k <= 0) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    const uint8_t* base = static_cast<const uint8_t*>(blob);
+    view->qs = base;
+    view->qs_pitch = q4_1_pack_qs_pitch(k);
+    view->dm = base + static_cast<size_t>(n) * static_cast<size_t>(view->qs_pitch) * 16;
+    view->dm_pitch = q4_1_pack_dm_pitch(k);
+    return NNB200_OK;
+}
+
+int nnb200_q4_1_pack(const void* w_blocks, int64_t ldw_blocks, int64_t n, int64_t k, void* blob, size_t blob_bytes,
+                     void* stream)
+{
+    if (n < 0 || k < 0) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if (n == 0 || k == 0) {
+        return NNB200_OK;
+    }
+    if (w_blocks == nullptr || blob == nullptr || ldw_blocks < (k + 31) / 32 ||
+        (reinterpret_cast<uintptr_t>(w_blocks) & 3u) != 0 || (reinterpret_cast<uintptr_t>(blob) & 15u) != 0 ||
+        blob_bytes < nnb200_q4_1_pack_bytes(n, k)) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    const DeviceInfo* dev = current_device_info();
+    if (dev == nullptr) {
+        return NNB200_INTERNAL;
+    }
+    return launch_q4_1_pack(w_blocks, ldw_blocks, n, k, blob, static_cast<cudaStream_t>(stream));
 }
 
 int nnb200_i8_packed_view(const void* blob, int64_t n, int64_t k, nnb200_i8_packed* view)

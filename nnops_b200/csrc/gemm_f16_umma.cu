@@ -84,12 +84,16 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
 // two 16-byte pieces; a pair thereby completes the 32-byte sectors [k 0..15] and [k 16..31].
 // A CTA walks whole rows (no index division anywhere); every thread has the loads of two rows in
 // flight before it decodes either.
+// dm_plane != nullptr: the weights are packed (nnb200_q4_1_pack) -- `w` is then the nibble plane,
+// 16 bytes per block, and dm_plane the (d, m) plane with rows ld_dm entries apart.
 __global__ void __launch_bounds__(256) q4_1_expand_f16_kernel(const uint8_t* __restrict__ w, const int64_t ldw_blocks,
+                                                              const uint32_t* __restrict__ dm_plane, const int64_t ld_dm,
                                                               const int rows, const int nblk,
                                                               __half* __restrict__ out, const int64_t ld_out)
 {
     const int half_blocks = 2 * nblk;
-    const int64_t pitch = ldw_blocks * kQ4BlockBytes;
+    const bool planes = dm_plane != nullptr;
+    const int64_t pitch = ldw_blocks * (planes ? 16 : kQ4BlockBytes);
     for (int r0 = blockIdx.x; r0 < rows; r0 += 2 * gridDim.x) {
         const int r1 = r0 + gridDim.x;
         for (int hb = threadIdx.x; hb < half_blocks; hb += blockDim.x) {
@@ -100,10 +104,17 @@ __global__ void __launch_bounds__(256) q4_1_expand_f16_kernel(const uint8_t* __r
             for (int u = 0; u < 2; ++u) {
                 const int r = u == 0 ? r0 : r1;
                 if (r < rows) {
-                    const uint32_t* src = reinterpret_cast<const uint32_t*>(w + r * pitch + b * kQ4BlockBytes);
-                    dm[u] = __ldg(src);
-                    q0[u] = __ldg(src + 1 + 2 * h);
-                    q1[u] = __ldg(src + 2 + 2 * h);
+                    if (planes) {
+                        const uint32_t* src = reinterpret_cast<const uint32_t*>(w + r * pitch + b * 16);
+                        dm[u] = __ldg(dm_plane + r * ld_dm + b);
+                        q0[u] = __ldg(src + 2 * h);
+                        q1[u] = __ldg(src + 1 + 2 * h);
+                    } else {
+                        const uint32_t* src = reinterpret_cast<const uint32_t*>(w + r * pitch + b * kQ4BlockBytes);
+                        dm[u] = __ldg(src);
+                        q0[u] = __ldg(src + 1 + 2 * h);
+                        q1[u] = __ldg(src + 2 + 2 * h);
+                    }
                 }
             }
 #pragma unroll
@@ -800,6 +811,7 @@ int launch_q4_1_two_pass(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
         const int64_t cap = static_cast<int64_t>(dev.sm_count) * 16;
         const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
         q4_1_expand_f16_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(q.w_blocks), q.ldw_blocks,
+                                                         static_cast<const uint32_t*>(q.w_dm), q.ld_dm,
                                                          static_cast<int>(q.n), static_cast<int>(nblk), w_f16, ldw);
         note_launch();
         if (cudaGetLastError() != cudaSuccess) {

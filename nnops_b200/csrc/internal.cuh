@@ -100,6 +100,9 @@ int launch_dequantize_linear(const nnb200_quant_linear_args& q, const DeviceInfo
 int launch_mma_i8_peak(int iters, int pattern, double* ops_out, const DeviceInfo& dev, cudaStream_t stream);
 
 int64_t i8_pack_pitch(int64_t k);
+int64_t q4_1_pack_qs_pitch(int64_t k);
+int64_t q4_1_pack_dm_pitch(int64_t k);
+int launch_q4_1_pack(const void* w_blocks, int64_t ldw_blocks, int64_t n, int64_t k, void* blob, cudaStream_t stream);
 int launch_i8_pack(const void* w, int64_t n, int64_t k, int64_t stride_n, int64_t stride_k, const float* scale_w,
                    float scale_scalar, const int32_t* zp_w, int32_t zp_scalar, void* blob, cudaStream_t stream);
 

@@ -134,4 +134,54 @@ int launch_i8_pack(const void* w, int64_t n, int64_t k, int64_t stride_n, int64_
     return cuda_status(cudaGetLastError());
 }
 
+// ---- Q4_1: (d, m) plane and nibble plane ------------------------------------------------------
+// One thread per block: five 4-byte reads of the raw stream, one 16-byte and one 4-byte store.
+namespace {
+
+__global__ void __launch_bounds__(256) pack_q4_1_kernel(const uint32_t* __restrict__ w, const int64_t ldw_words,
+                                                        const int64_t n, const int64_t nblk,
+                                                        uint4* __restrict__ qs, const int64_t qs_pitch,
+                                                        uint32_t* __restrict__ dm, const int64_t dm_pitch)
+{
+    const int64_t total = n * nblk;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t row = i / nblk;
+        const int64_t b = i - row * nblk;
+        const uint32_t* src = w + row * ldw_words + b * 5;
+        dm[row * dm_pitch + b] = src[0];
+        qs[row * qs_pitch + b] = make_uint4(src[1], src[2], src[3], src[4]);
+    }
+}
+
+}  // namespace
+
+int64_t q4_1_pack_qs_pitch(int64_t k) { return (k + 31) / 32; }                    // in 16-byte blocks
+int64_t q4_1_pack_dm_pitch(int64_t k) { return (((k + 31) / 32) + 3) / 4 * 4; }    // in 4-byte entries: 16-byte rows
+
+int launch_q4_1_pack(const void* w_blocks, int64_t ldw_blocks, int64_t n, int64_t k, void* blob, cudaStream_t stream)
+{
+    const int64_t nblk = (k + 31) / 32;
+    if (n == 0 || nblk == 0) {
+        return NNB200_OK;
+    }
+    const int64_t qs_pitch = q4_1_pack_qs_pitch(k);
+    const int64_t dm_pitch = q4_1_pack_dm_pitch(k);
+    uint8_t* base = static_cast<uint8_t*>(blob);
+    uint4* qs = reinterpret_cast<uint4*>(base);
+    uint32_t* dm = reinterpret_cast<uint32_t*>(base + static_cast<size_t>(n) * qs_pitch * 16);
+    // The pad entries of the (d, m) rows are never read; clear them anyway so the blob is reproducible.
+    if (dm_pitch != nblk) {
+        if (cudaMemsetAsync(dm, 0, static_cast<size_t>(n) * dm_pitch * 4, stream) != cudaSuccess) {
+            return NNB200_INTERNAL;
+        }
+    }
+    const int64_t total = n * nblk;
+    const unsigned grid = static_cast<unsigned>(total / 256 + 1 > 4096 ? 4096 : total / 256 + 1);
+    pack_q4_1_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(w_blocks), ldw_blocks * 5, n, nblk, qs, qs_pitch,
+                                               dm, dm_pitch);
+    note_launch();
+    return cuda_status(cudaGetLastError());
+}
+
 }  // namespace nnb200

@@ -60,7 +60,9 @@ struct DsqLayout {
     int kc_blocks;        // blocks of k per ring stage (multiple of 8)
     int stages;           // ring depth
     int row_stride;       // bytes between the 16 channel rows of a stage (16-byte multiple, padded)
-    int stage_bytes;      // 16 * row_stride
+    int dm_off;           // packed weights: where the stage's 16 rows of (d, m) entries start
+    int dm_stride;        // packed weights: bytes between those rows
+    int stage_bytes;      // 16 * row_stride (+ 16 * dm_stride)
     int nblk_pad;         // K / 32 rounded up to a multiple of 8
     int off_pairs;        // permuted activation pairs: [nblk_pad][Mp][16] u32
     int off_sums;         // per-block activation sums:  [nblk_pad][Mp] f32
@@ -233,21 +235,26 @@ struct DsqLane {
 
 // One group of G = 8 / MP blocks x 16 channels: 2 G MMAs, then the fix-up into acc.
 //   wlo / whi   shared addresses of this lane's channel rows g and g + 8 at the group's first block
+//   dlo / dhi   packed weights only: the same for the rows of (d, m) entries
 //   b0_at/b1_at shared addresses of the activation pairs for the lane's two operand halves (or of
 //               zeros, in lanes whose columns belong to another block)
 //   sums_at     shared address of the two per-block activation sums of columns 2c and 2c + 1
 //   blocks_left blocks from the group's first one to the end of K (>= 1; < G only in a row's last group)
-template <int MP>
-__device__ __forceinline__ void dsq_group(uint32_t wlo, uint32_t whi, uint32_t b0_at, uint32_t b1_at, uint32_t sums_at,
-                                          int blocks_left, int c, float (&acc)[4])
+template <int MP, bool PACKED>
+__device__ __forceinline__ void dsq_group(uint32_t wlo, uint32_t whi, uint32_t dlo, uint32_t dhi, uint32_t b0_at,
+                                          uint32_t b1_at, uint32_t sums_at, int blocks_left, int c, float (&acc)[4])
 {
     constexpr int G = 8 / MP;
     constexpr uint32_t kLo = 0x000F000Fu;   // low nibbles of bytes 0 and 2: q * 2^-24 as f16 subnormals
     constexpr uint32_t kHi = 0x00F000F0u;   // high nibbles, in place: q * 2^-20
+    // Raw stream: a block is 20 bytes, its nibble words 1..4.  Packed: 16 bytes, words 0..3, and
+    // 16-byte aligned, so a lane that walks a whole block takes it in one load.
+    constexpr uint32_t kBlk = PACKED ? 16u : 20u;
+    constexpr uint32_t kFirst = PACKED ? 0u : 4u;
     float dl[2][4], dh[2][4];               // two accumulator chains per nibble kind
     if constexpr (MP == 8) {
-        const uint32_t x = lds32(wlo + 4u * (1 + c));
-        const uint32_t y = lds32(whi + 4u * (1 + c));
+        const uint32_t x = lds32(wlo + kFirst + 4u * c);
+        const uint32_t y = lds32(whi + kFirst + 4u * c);
         const uint4 b = lds128(b0_at);
         const uint32_t xs = x >> 8;
         const uint32_t ys = y >> 8;
@@ -255,14 +262,33 @@ __device__ __forceinline__ void dsq_group(uint32_t wlo, uint32_t whi, uint32_t b
         mma_m16n8k16_first(dh[0], x & kHi, y & kHi, xs & kHi, ys & kHi, b.z, b.w);
     } else {
         using L = DsqLane<MP>;
-        const uint32_t at0 = 20u * L::block_of(c, 0) + 4u * (1 + L::word_of(c, 0));
-        const uint32_t at1 = 20u * L::block_of(c, 1) + 4u * (1 + L::word_of(c, 1));
+        const uint32_t at0 = kBlk * L::block_of(c, 0) + kFirst + 4u * L::word_of(c, 0);
+        const uint32_t at1 = kBlk * L::block_of(c, 1) + kFirst + 4u * L::word_of(c, 1);
+        uint32_t xw0[L::kWords], yw0[L::kWords], xw1[L::kWords], yw1[L::kWords];
+        if constexpr (PACKED && MP == 1) {
+            // Whole blocks: four 16-byte loads instead of sixteen 4-byte ones.
+            const uint4 a = lds128(wlo + at0), b = lds128(whi + at0), cc = lds128(wlo + at1), d = lds128(whi + at1);
+            xw0[0] = a.x; xw0[1] = a.y; xw0[2] = a.z; xw0[3] = a.w;
+            yw0[0] = b.x; yw0[1] = b.y; yw0[2] = b.z; yw0[3] = b.w;
+            xw1[0] = cc.x; xw1[1] = cc.y; xw1[2] = cc.z; xw1[3] = cc.w;
+            yw1[0] = d.x; yw1[1] = d.y; yw1[2] = d.z; yw1[3] = d.w;
+        } else if constexpr (PACKED && MP == 2) {
+            // Both halves walk the same block (words 0-1 and 2-3): one 16-byte load per channel.
+            const uint4 a = lds128(wlo + at0), b = lds128(whi + at0);
+            xw0[0] = a.x; xw0[1] = a.y; xw1[0] = a.z; xw1[1] = a.w;
+            yw0[0] = b.x; yw0[1] = b.y; yw1[0] = b.z; yw1[1] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < L::kWords; ++i) {
+                xw0[i] = lds32(wlo + at0 + 4u * i);
+                yw0[i] = lds32(whi + at0 + 4u * i);
+                xw1[i] = lds32(wlo + at1 + 4u * i);
+                yw1[i] = lds32(whi + at1 + 4u * i);
+            }
+        }
 #pragma unroll
         for (int i = 0; i < L::kWords; ++i) {
-            const uint32_t x0 = lds32(wlo + at0 + 4u * i);
-            const uint32_t y0 = lds32(whi + at0 + 4u * i);
-            const uint32_t x1 = lds32(wlo + at1 + 4u * i);
-            const uint32_t y1 = lds32(whi + at1 + 4u * i);
+            const uint32_t x0 = xw0[i], y0 = yw0[i], x1 = xw1[i], y1 = yw1[i];
             const uint4 p0 = lds128(b0_at + 16u * i);
             const uint4 p1 = lds128(b1_at + 16u * i);
             const uint32_t x0s = x0 >> 8, y0s = y0 >> 8, x1s = x1 >> 8, y1s = y1 >> 8;
@@ -288,7 +314,8 @@ __device__ __forceinline__ void dsq_group(uint32_t wlo, uint32_t whi, uint32_t b
 #pragma unroll
         for (int q = 0; q < kBlocksPerLane; ++q) {
             const int jb = MP == 1 ? 2 * c + q : (2 * c) / MP;
-            dm[half][q] = lds32((half == 0 ? wlo : whi) + 20u * jb);
+            // Raw stream: word 0 of the block; packed: entry jb of the (d, m) row.
+            dm[half][q] = PACKED ? lds32((half == 0 ? dlo : dhi) + 4u * jb) : lds32((half == 0 ? wlo : whi) + 20u * jb);
         }
     }
     const float2 t = lds_f2(sums_at);
@@ -318,9 +345,12 @@ __device__ __forceinline__ void dsq_group(uint32_t wlo, uint32_t whi, uint32_t b
 }
 
 // MP: MMA columns per block (activation rows padded to 1, 2, 4 or 8; f32 rows count twice).
-template <int MP, bool OUT_F16, bool A_F32, int NC>
+// PACKED: `w` is the nibble plane of a packed weight (16 bytes per block) and `w_dm` its (d, m)
+// plane with rows dm_pitch_bytes apart; otherwise `w` is the raw 20-byte-block stream.
+template <int MP, bool OUT_F16, bool A_F32, int NC, bool PACKED>
 __global__ void __launch_bounds__((NC + 2) * 32, NC == 8 ? 2 : 1)
-q4_1_gemv_dsq_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes, const void* __restrict__ a_v,
+q4_1_gemv_dsq_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes, const uint8_t* __restrict__ w_dm,
+                     const int64_t dm_pitch_bytes, const void* __restrict__ a_v,
                      const int64_t lda, void* __restrict__ out, const int64_t ldc, const int m_count,
                      const int n_total, const int k_total, const DsqLayout lay, const FpEpilogue ep,
                      const int a_vec_ok, int32_t* error_word)
@@ -382,14 +412,21 @@ q4_1_gemv_dsq_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes,
                     ok = false;
                     break;
                 }
-                const uint32_t bytes = static_cast<uint32_t>(min(lay.kc_blocks, nblk - b0)) * kQ4BlockBytes;
+                const uint32_t nb = static_cast<uint32_t>(min(lay.kc_blocks, nblk - b0));
+                const uint32_t bytes = nb * (PACKED ? 16u : static_cast<uint32_t>(kQ4BlockBytes));
                 if (lane == 0) {
-                    mbar_expect_tx(&full[slot], bytes * static_cast<uint32_t>(valid));
+                    mbar_expect_tx(&full[slot], (bytes + (PACKED ? nb * 4u : 0u)) * static_cast<uint32_t>(valid));
                 }
                 __syncwarp();
                 if (lane < valid) {
-                    bulk_load_1d(smem + static_cast<size_t>(slot) * lay.stage_bytes + lane * lay.row_stride,
-                                 src + static_cast<int64_t>(b0) * kQ4BlockBytes, bytes, &full[slot]);
+                    uint8_t* dst = smem + static_cast<size_t>(slot) * lay.stage_bytes;
+                    bulk_load_1d(dst + lane * lay.row_stride, src + static_cast<int64_t>(b0) * (PACKED ? 16 : kQ4BlockBytes),
+                                 bytes, &full[slot]);
+                    if constexpr (PACKED) {
+                        bulk_load_1d(dst + lay.dm_off + lane * lay.dm_stride,
+                                     w_dm + static_cast<int64_t>(r0 + lane) * dm_pitch_bytes + static_cast<int64_t>(b0) * 4,
+                                     nb * 4u, &full[slot]);
+                    }
                 }
                 if (++slot == lay.stages) {
                     slot = 0;
@@ -532,12 +569,16 @@ q4_1_gemv_dsq_kernel(const uint8_t* __restrict__ w, const int64_t w_pitch_bytes,
             const uint32_t base = smem_base + static_cast<uint32_t>(slot * lay.stage_bytes);
             const uint32_t wlo = base + static_cast<uint32_t>(g * lay.row_stride);
             const uint32_t whi = base + static_cast<uint32_t>((g + 8) * lay.row_stride);
+            const uint32_t dlo = base + static_cast<uint32_t>(lay.dm_off + g * lay.dm_stride);
+            const uint32_t dhi = base + static_cast<uint32_t>(lay.dm_off + (g + 8) * lay.dm_stride);
             const int nb = min(lay.kc_blocks, nblk - b0);
+            constexpr uint32_t kBlk = PACKED ? 16u : 20u;
             for (int ul = warp * G; ul < nb; ul += kConsumers * G) {
                 const int ub = b0 + ul;   // the group's first block, counted inside the row
-                dsq_group<MP>(wlo + 20u * ul, whi + 20u * ul, b_base[0] + static_cast<uint32_t>(ub) * b_stride[0],
-                              b_base[1] + static_cast<uint32_t>(ub) * b_stride[1],
-                              sums_base + static_cast<uint32_t>(ub) * (MP * 4u), nblk - ub, c, acc);
+                dsq_group<MP, PACKED>(wlo + kBlk * ul, whi + kBlk * ul, dlo + 4u * ul, dhi + 4u * ul,
+                                      b_base[0] + static_cast<uint32_t>(ub) * b_stride[0],
+                                      b_base[1] + static_cast<uint32_t>(ub) * b_stride[1],
+                                      sums_base + static_cast<uint32_t>(ub) * (MP * 4u), nblk - ub, c, acc);
             }
             __syncwarp();   // every lane has finished reading the stage
             if (lane == 0) {
@@ -605,7 +646,7 @@ int columns_per_block(int rows, bool a_f32)
 // programmatically chained sequence fits beside this one) with at least ~40 KB of weights in
 // flight; otherwise take what one CTA per SM can have.  Returns false when the staged
 // activations alone are too large.
-bool plan_layout(int mp, int64_t k, int consumers, DsqLayout* out)
+bool plan_layout(int mp, int64_t k, int consumers, bool packed, DsqLayout* out)
 {
     DsqLayout l = {};
     const int nblk = static_cast<int>(k / kQ4BlockElems);
@@ -633,8 +674,13 @@ bool plan_layout(int mp, int64_t k, int consumers, DsqLayout* out)
         int best_flight = 0, best_kc = 0, best_stages = 0;
         for (int kc = 128; kc >= 16; kc /= 2) {
             const int kcb = kc < l.nblk_pad ? kc : l.nblk_pad;
-            const int stride = kcb * kQ4BlockBytes + 16;   // 5 * kcb + 4 words: 4 * odd (mod 32) for kcb % 8 == 0
-            const int stage = kTileRows * stride;
+            // Raw stream: 5 * kcb + 4 words per row = 4 * odd (mod 32) for kcb % 8 == 0, which spreads
+            // the eight channels a lane group reads over all banks.  Packed: nibble rows of
+            // 16 * kcb + 64 bytes (two rows fill the 128-byte bank span of a quarter-warp's 16-byte
+            // loads) and (d, m) rows of 4 * kcb + 32 bytes.
+            const int stride = packed ? kcb * 16 + 64 : kcb * kQ4BlockBytes + 16;
+            const int dm_stride = packed ? kcb * 4 + 32 : 0;
+            const int stage = kTileRows * (stride + dm_stride);
             int stages = (budgets[pass] - fixed) / stage;
             stages = stages > kMaxStages ? kMaxStages : stages;
             if (stages >= 2 && stages * stage > best_flight) {
@@ -646,8 +692,10 @@ bool plan_layout(int mp, int64_t k, int consumers, DsqLayout* out)
         if (best_stages >= 2 && (best_flight >= 40 * 1024 || pass == 1)) {
             l.kc_blocks = best_kc;
             l.stages = best_stages;
-            l.row_stride = best_kc * kQ4BlockBytes + 16;
-            l.stage_bytes = kTileRows * l.row_stride;
+            l.row_stride = packed ? best_kc * 16 + 64 : best_kc * kQ4BlockBytes + 16;
+            l.dm_stride = packed ? best_kc * 4 + 32 : 0;
+            l.dm_off = kTileRows * l.row_stride;
+            l.stage_bytes = kTileRows * (l.row_stride + l.dm_stride);
             // The ring sits in front; everything else follows it.
             const int ring = round_up(l.stages * l.stage_bytes, 128);
             l.off_pairs += ring;
@@ -663,30 +711,30 @@ bool plan_layout(int mp, int64_t k, int consumers, DsqLayout* out)
     return false;
 }
 
-using DsqKernel = void (*)(const uint8_t*, int64_t, const void*, int64_t, void*, int64_t, int, int, int, DsqLayout,
-                           FpEpilogue, int, int32_t*);
+using DsqKernel = void (*)(const uint8_t*, int64_t, const uint8_t*, int64_t, const void*, int64_t, void*, int64_t, int, int,
+                           int, DsqLayout, FpEpilogue, int, int32_t*);
 
-template <int MP, int NC>
+template <int MP, int NC, bool PACKED>
 DsqKernel pick_kernel(bool out_f16, bool a_f32)
 {
     if (a_f32) {
         if constexpr (MP >= 2) {
-            return out_f16 ? q4_1_gemv_dsq_kernel<MP, true, true, NC> : q4_1_gemv_dsq_kernel<MP, false, true, NC>;
+            return out_f16 ? q4_1_gemv_dsq_kernel<MP, true, true, NC, PACKED> : q4_1_gemv_dsq_kernel<MP, false, true, NC, PACKED>;
         } else {
             return nullptr;
         }
     }
-    return out_f16 ? q4_1_gemv_dsq_kernel<MP, true, false, NC> : q4_1_gemv_dsq_kernel<MP, false, false, NC>;
+    return out_f16 ? q4_1_gemv_dsq_kernel<MP, true, false, NC, PACKED> : q4_1_gemv_dsq_kernel<MP, false, false, NC, PACKED>;
 }
 
-template <int NC>
+template <bool PACKED>
 DsqKernel pick_kernel(int mp, bool out_f16, bool a_f32)
 {
     switch (mp) {
-    case 1: return pick_kernel<1, NC>(out_f16, a_f32);
-    case 2: return pick_kernel<2, NC>(out_f16, a_f32);
-    case 4: return pick_kernel<4, NC>(out_f16, a_f32);
-    default: return pick_kernel<8, NC>(out_f16, a_f32);
+    case 1: return pick_kernel<1, 8, PACKED>(out_f16, a_f32);
+    case 2: return pick_kernel<2, 8, PACKED>(out_f16, a_f32);
+    case 4: return pick_kernel<4, 8, PACKED>(out_f16, a_f32);
+    default: return pick_kernel<8, 8, PACKED>(out_f16, a_f32);
     }
 }
 
@@ -702,16 +750,19 @@ int consumer_warps()
 bool q4_1_gemv_dsq_supported(const nnb200_q4_1_args& q)
 {
     // Weight rows movable by 16-byte bulk copies (aligned base and pitch, K % 128 == 0) and one
-    // pass's activations small enough to stage whole in shared memory.
+    // pass's activations small enough to stage whole in shared memory.  The planes of a packed
+    // weight are 16-byte aligned by construction; their (d, m) rows need ld_dm % 4 == 0.
+    const bool packed = q.w_dm != nullptr;
     if (!(q.n <= INT32_MAX && q.k <= INT32_MAX - 128 && (q.k % 128) == 0 &&
-          (reinterpret_cast<uintptr_t>(q.w_blocks) & 15u) == 0 && (q.ldw_blocks % 4) == 0)) {
+          (reinterpret_cast<uintptr_t>(q.w_blocks) & 15u) == 0 && (packed || (q.ldw_blocks % 4) == 0) &&
+          (!packed || ((reinterpret_cast<uintptr_t>(q.w_dm) & 15u) == 0 && (q.ld_dm % 4) == 0)))) {
         return false;
     }
     const bool a_f32 = q.a_f16 == 0;
     const int rows_per_pass = a_f32 ? 4 : 8;
     const int first = static_cast<int>(q.m < rows_per_pass ? q.m : rows_per_pass);
     DsqLayout l;
-    return plan_layout(columns_per_block(first, a_f32), q.k, consumer_warps(), &l);
+    return plan_layout(columns_per_block(first, a_f32), q.k, consumer_warps(), packed, &l);
 }
 
 int launch_q4_1_gemv_dsq(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaStream_t stream)
@@ -733,31 +784,34 @@ int launch_q4_1_gemv_dsq(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
     const int n = static_cast<int>(q.n), k = static_cast<int>(q.k);
     // Vector loads of the activations: 8-byte (f16) / 16-byte (f32) aligned groups of four.
     const int a_vec_ok = ((reinterpret_cast<uintptr_t>(q.a) & (a_f32 ? 15u : 7u)) == 0 && (q.lda % 4) == 0) ? 1 : 0;
+    const bool packed = q.w_dm != nullptr;
     const uint8_t* w = static_cast<const uint8_t*>(q.w_blocks);
-    const int64_t pitch = q.ldw_blocks * kQ4BlockBytes;
+    const int64_t pitch = q.ldw_blocks * (packed ? 16 : kQ4BlockBytes);
+    const uint8_t* w_dm = static_cast<const uint8_t*>(q.w_dm);
+    const int64_t dm_pitch = q.ld_dm * 4;
     const bool overlap = (q.flags & NNB200_Q4_FLAG_OVERLAP_PREVIOUS) != 0;
     const int tiles = (n + kTileRows - 1) / kTileRows;
 
     // Opt-in to large dynamic shared memory once per device and kernel variant.
     static std::mutex attr_mutex;
-    static bool attr_done[kMaxDevices][4][2][2][2];
+    static bool attr_done[kMaxDevices][4][2][2][2];   // [device][columns][out f16][a f32][packed]
     const int consumers = consumer_warps();
 
     for (int64_t m0 = 0; m0 < q.m; m0 += rows_per_pass) {
         const int m_count = static_cast<int>(q.m - m0 < rows_per_pass ? q.m - m0 : rows_per_pass);
         const int mp = columns_per_block(m_count, a_f32);
         DsqLayout lay;
-        if (!plan_layout(mp, k, consumers, &lay)) {
+        if (!plan_layout(mp, k, consumers, packed, &lay)) {
             return NNB200_UNSUPPORTED;
         }
-        DsqKernel kernel = consumers == 16 ? pick_kernel<16>(mp, out_f16, a_f32) : pick_kernel<8>(mp, out_f16, a_f32);
+        DsqKernel kernel = packed ? pick_kernel<true>(mp, out_f16, a_f32) : pick_kernel<false>(mp, out_f16, a_f32);
         if (kernel == nullptr) {
             return NNB200_INTERNAL;
         }
         const int mp_idx = mp == 1 ? 0 : (mp == 2 ? 1 : (mp == 4 ? 2 : 3));
         {
             std::lock_guard<std::mutex> lock(attr_mutex);
-            bool& done = attr_done[dev.device][mp_idx][out_f16 ? 1 : 0][a_f32 ? 1 : 0][consumers == 16 ? 1 : 0];
+            bool& done = attr_done[dev.device][mp_idx][out_f16 ? 1 : 0][a_f32 ? 1 : 0][packed ? 1 : 0];
             if (!done) {
                 if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024) != cudaSuccess) {
                     (void)cudaGetLastError();
@@ -782,7 +836,7 @@ int launch_q4_1_gemv_dsq(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = overlap ? 1 : 0;
-        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, w, pitch, a, q.lda, out, q.ldc, m_count, n, k, lay, ep,
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, w, pitch, w_dm, dm_pitch, a, q.lda, out, q.ldc, m_count, n, k, lay, ep,
                                                  a_vec_ok, dev.error_word);
         note_launch();
         if (e != cudaSuccess) {

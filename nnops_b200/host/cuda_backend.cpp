@@ -509,6 +509,19 @@ Status run_q4_1(const TensorView& x, const TensorView& w, const TensorView* bias
     q.k = K;
     q.lda = x.row_stride_elems();
     q.ldw_blocks = w.row_stride_elems();
+#ifndef NNB200_USE_NNOPS_HEADERS
+    if (w.layout() == TensorLayout::PackedQ4_1B200) {
+        // A prepacked weight: the view's data is nnb200_q4_1_pack's blob.
+        nnb200_q4_1_packed planes;
+        if (nnb200_q4_1_packed_view(w.ptr<void>(), N, K, &planes) != NNB200_OK) {
+            return Status::invalid_argument;
+        }
+        q.w_blocks = planes.qs;
+        q.ldw_blocks = planes.qs_pitch;
+        q.w_dm = planes.dm;
+        q.ld_dm = planes.dm_pitch;
+    }
+#endif
     q.ldc = out.row_stride_elems();
     q.a_f16 = xdt == DataType::f16;
     q.out_f16 = odt == DataType::f16;
@@ -610,6 +623,36 @@ void prepack_i8_cuda(const TensorView& weight, bool w_is_nk, TensorView& packed,
     nnb200_i8_pack(weight.ptr<void>(), n, k, w_is_nk ? weight.row_stride_elems() : 1,
                    w_is_nk ? 1 : weight.row_stride_elems(), q.scale_data, q.scale, q.zero_point_data, q.zero_point,
                    packed.ptr<void>(), static_cast<size_t>(n * pitch), ctx.cuda_stream);
+}
+#endif
+
+#ifndef NNB200_USE_NNOPS_HEADERS
+// Two-step prepack of a 2-D q4_1 weight stored [N, K]: an empty `packed` is set to the geometry of
+// the blob (a [N, K] q4_1 view tagged PackedQ4_1B200 whose pitch, a whole number of 20-byte
+// units, makes N * pitch cover the blob); a populated one is filled on the stream.
+void prepack_q4_1_cuda(const TensorView& weight, TensorView& packed, const ComputeContext& ctx)
+{
+    if (weight.data_type() != DataType::q4_1 || weight.rank() != 2) {
+        return;
+    }
+    const int64_t n = weight.shape(0), k = weight.shape(1);
+    if (n <= 0 || k <= 0) {
+        return;
+    }
+    const size_t bytes = nnb200_q4_1_pack_bytes(n, k);
+    const int64_t per_row = static_cast<int64_t>(bytes / static_cast<size_t>(n));
+    const int64_t pitch = (per_row + 19) / 20 * 20;
+    const int64_t shape[2] = {n, k};
+    if (packed.is_empty()) {
+        packed = TensorView(shape, DataType::q4_1, nullptr, pitch, TensorLayout::PackedQ4_1B200, QuantParams{});
+        return;
+    }
+    if (packed.layout() != TensorLayout::PackedQ4_1B200 || packed.rank() != 2 || packed.shape(0) != n ||
+        packed.shape(1) != k || packed.pitch() != pitch) {
+        return;  // not the geometry the query gave
+    }
+    nnb200_q4_1_pack(weight.ptr<void>(), weight.row_stride_elems(), n, k, packed.ptr<void>(),
+                     static_cast<size_t>(n * pitch), ctx.cuda_stream);
 }
 #endif
 

@@ -122,6 +122,10 @@ void Linear::prepackWeights(std::span<const TensorView> inputs, std::span<Tensor
     if (backend_ != Backend::CUDA || inputs.empty() || outputs.empty()) {
         return;
     }
+    if (inputs[0].data_type() == DataType::q4_1) {
+        backend::cuda::prepack_q4_1_cuda(inputs[0], outputs[0], ctx);
+        return;
+    }
     backend::cuda::prepack_i8_cuda(inputs[0], true, outputs[0], ctx);
 }
 

@@ -172,10 +172,51 @@ def gemm_i8_engine(a, w, out, **kw) -> str:
     return capi.ENGINE_NAMES.get(capi.lib().nnb200_gemm_i8_engine(C.byref(args)), "invalid")
 
 
-def q4_1_args(a: torch.Tensor, w_blocks: torch.Tensor, out: torch.Tensor, k: int, *, bias=None, activation="none",
+class PackedQ41:
+    """A prepacked Q4_1 weight: one device blob holding the nibble plane (16 bytes per block, every
+    block 16-byte aligned) and the plane of (f16 d, f16 m) pairs (see nnb200_q4_1_pack)."""
+
+    def __init__(self, blob: torch.Tensor, n: int, k: int):
+        self.blob, self.n, self.k = blob, n, k
+        view = capi.Q41Packed()
+        capi.check(capi.lib().nnb200_q4_1_packed_view(blob.data_ptr(), n, k, C.byref(view)), "nnb200_q4_1_packed_view")
+        self.qs_ptr, self.qs_pitch, self.dm_ptr, self.dm_pitch = view.qs, view.qs_pitch, view.dm, view.dm_pitch
+        nblk = (k + 31) // 32
+        self.qs = blob[: n * self.qs_pitch * 16].view(n, self.qs_pitch * 16)[:, : nblk * 16]
+        self.dm = blob[n * self.qs_pitch * 16:].view(n, self.dm_pitch * 4)[:, : nblk * 4]
+
+
+def prepack_q4_1(w_blocks: torch.Tensor, k: int) -> PackedQ41:
+    """Repack raw Q4_1 rows (uint8 [N, ceil(K/32)*20], any 20-byte-multiple pitch) into planes."""
+    if w_blocks.dtype != torch.uint8 or w_blocks.dim() != 2 or w_blocks.stride(1) != 1 or w_blocks.stride(0) % 20:
+        raise ValueError("w_blocks must be a uint8 [N, row_bytes] tensor whose row pitch is a multiple of 20")
+    n = w_blocks.shape[0]
+    blob = torch.empty(capi.lib().nnb200_q4_1_pack_bytes(n, k), dtype=torch.uint8, device=w_blocks.device)
+    with torch.cuda.device(w_blocks.device):
+        capi.check(capi.lib().nnb200_q4_1_pack(w_blocks.data_ptr(), w_blocks.stride(0) // 20, n, k, blob.data_ptr(),
+                                               blob.numel(), _stream_ptr(w_blocks.device)), "nnb200_q4_1_pack")
+    return PackedQ41(blob, n, k)
+
+
+def q4_1_args(a: torch.Tensor, w_blocks, out: torch.Tensor, k: int, *, bias=None, activation="none",
               act_alpha=0.0, act_beta=1.0, min_clip=-math.inf, max_clip=math.inf, alpha=1.0, engine="auto",
               overlap_previous: bool = False, keep: list | None = None) -> capi.Q41Args:
+    """``w_blocks``: raw rows (uint8 [N, ceil(K/32)*20]) or a PackedQ41."""
     keep = keep if keep is not None else []
+    if isinstance(w_blocks, PackedQ41):
+        pk = w_blocks
+        if a.stride(1) != 1 or out.stride(1) != 1:
+            raise ValueError("activations and output must be row-major")
+        if bias is not None:
+            bias = torch.as_tensor(bias).to(device=a.device, dtype=out.dtype).contiguous()
+            keep.append(bias)
+        return capi.Q41Args(
+            a=a.data_ptr(), w_blocks=pk.qs_ptr, out=out.data_ptr(), m=a.shape[0], n=pk.n, k=k, lda=a.stride(0),
+            ldw_blocks=pk.qs_pitch, ldc=out.stride(0), a_f16=int(a.dtype == torch.float16),
+            out_f16=int(out.dtype == torch.float16), bias=bias.data_ptr() if bias is not None else None,
+            activation=capi.ACTIVATIONS[activation], act_alpha=act_alpha, act_beta=act_beta, min_clip=min_clip,
+            max_clip=max_clip, alpha=alpha, workspace=None, workspace_bytes=0, force_engine=capi.Q4_ENGINES[engine],
+            flags=capi.Q4_FLAG_OVERLAP_PREVIOUS if overlap_previous else 0, w_dm=pk.dm_ptr, ld_dm=pk.dm_pitch)
     if w_blocks.dtype != torch.uint8 or w_blocks.dim() != 2 or w_blocks.stride(1) != 1 or w_blocks.stride(0) % 20:
         raise ValueError("w_blocks must be a uint8 [N, row_bytes] tensor whose row pitch is a multiple of 20")
     if a.stride(1) != 1 or out.stride(1) != 1:
@@ -200,8 +241,9 @@ def linear_q4_1(a: torch.Tensor, w_blocks: torch.Tensor, k: int, *, out_dtype: t
         raise RuntimeError("nnops_b200.linear_q4_1 needs CUDA tensors; there is no CPU path")
     if a.dtype not in (torch.float16, torch.float32):
         raise ValueError("activations must be f16 or f32")
+    n_out = w_blocks.n if isinstance(w_blocks, PackedQ41) else w_blocks.shape[0]
     if out is None:
-        out = torch.empty((a.shape[0], w_blocks.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+        out = torch.empty((a.shape[0], n_out), dtype=out_dtype or a.dtype, device=a.device)
     keep: list = []
     args = q4_1_args(a, w_blocks, out, k, keep=keep, **kw)
     need = capi.lib().nnb200_q4_1_workspace_bytes(C.byref(args))
@@ -221,7 +263,8 @@ def q4_1_engine(a: torch.Tensor, w_blocks: torch.Tensor, k: int, *, out_dtype: t
                 engine: str = "auto") -> int:
     """Engine code nnb200_linear_q4_1 would pick (1 fused GEMM, 3 GEMV on CUDA cores, 4 GEMV with warp
     MMA, 5 two-pass GEMM) when given the scratch it asks for."""
-    out = torch.empty((a.shape[0], w_blocks.shape[0]), dtype=out_dtype, device=a.device)
+    n_out = w_blocks.n if isinstance(w_blocks, PackedQ41) else w_blocks.shape[0]
+    out = torch.empty((a.shape[0], n_out), dtype=out_dtype, device=a.device)
     args = q4_1_args(a, w_blocks, out, k, engine=engine)
     need = capi.lib().nnb200_q4_1_workspace_bytes(C.byref(args))
     if need > 0:

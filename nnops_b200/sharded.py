@@ -53,6 +53,61 @@ def shard_rows(t, world: int, rank: int):
     return t[lo:hi]
 
 
+class RankLost(RuntimeError):
+    """Another rank of the sharded layer has left, or has not been heard from in time."""
+
+    def __init__(self, rank: int, why: str):
+        self.rank, self.why = rank, why
+        super().__init__(f"rank {rank} {why}")
+
+
+class RankMonitor:
+    """Host-side liveness of the ranks of a sharded layer, through a key-value store every rank
+    can reach (``torch.distributed.TCPStore`` or any object with ``set`` / ``get`` / ``check``).
+
+    The device-side barrier and the collectives assume every rank takes part; a rank that has
+    died would leave the others waiting until a bounded wait runs out.  Before each step every
+    rank therefore (1) publishes the step it is about to run and (2) waits until every other
+    rank has published the same step: a rank that announced it is leaving instead (``leave``: a
+    clean exit between steps) or that does not publish within ``timeout_s`` raises ``RankLost``
+    on the host, BEFORE anything is launched, so no kernel or collective of the survivors is
+    left in flight.  It costs a few store round trips per step, so it is opt-in.  The reference
+    has no multi-GPU code; this sits above its operator API."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 30.0, prefix: str = "nnb200"):
+        self.store, self.rank, self.world, self.timeout_s, self.prefix = store, rank, world, float(timeout_s), prefix
+        self.step = 0
+        self.store.set(self._key("step", rank), "0")
+
+    def _key(self, what: str, rank: int) -> str:
+        return f"{self.prefix}/{what}/{rank}"
+
+    def leave(self) -> None:
+        """Tell the others this rank will run no further step (call between steps, nothing in flight)."""
+        self.store.set(self._key("left", self.rank), "1")
+
+    def begin_step(self) -> int:
+        """Publish the next step and wait until every other rank has published it too.
+        Returns the step number; raises RankLost otherwise."""
+        import time
+        self.step += 1
+        self.store.set(self._key("step", self.rank), str(self.step))
+        deadline = time.monotonic() + self.timeout_s
+        for peer in range(self.world):
+            if peer == self.rank:
+                continue
+            while True:
+                seen = int(self.store.get(self._key("step", peer))) if self.store.check([self._key("step", peer)]) else -1
+                if seen >= self.step:
+                    break
+                if self.store.check([self._key("left", peer)]):
+                    raise RankLost(peer, "has left")
+                if time.monotonic() > deadline:
+                    raise RankLost(peer, f"has not reached step {self.step} within {self.timeout_s} s (last seen {seen})")
+                time.sleep(0.002)
+        return self.step
+
+
 class _DeviceBuffer:
     """A library-allocated device buffer exposed to torch through __cuda_array_interface__."""
 
@@ -315,10 +370,14 @@ class ShardedLinearI8:
                 torch.cuda.current_stream(slab.device).cuda_stream), "nnb200_interleave_shards")
         return out
 
-    def forward(self, a: torch.Tensor, out: torch.Tensor | None = None, *, wait_for_readers: bool = False) -> torch.Tensor:
+    def forward(self, a: torch.Tensor, out: torch.Tensor | None = None, *, wait_for_readers: bool = False,
+                monitor: "RankMonitor | None" = None) -> torch.Tensor:
         """Full row-major [M, N] output on every rank.  ``wait_for_readers``: in fused mode, order
         the ranks BEFORE the GEMM as well, for callers whose previous result in ``out`` may still
-        be read on another rank when this call starts."""
+        be read on another rank when this call starts.  ``monitor``: check on the host that every
+        rank is still there before anything is launched (raises RankLost)."""
+        if monitor is not None and self.world > 1:
+            monitor.begin_step()
         if wait_for_readers and self.mode in ("fused", "multicast"):
             self.rank_barrier()
         self.local(a, out)

@@ -673,6 +673,76 @@ static void prepack_case(bool matmul_kn, int64_t m, int64_t n, int64_t k, const 
 }
 #endif
 
+// ---- prepacked Q4_1 weights (stand-alone API): separated nibble and (d, m) planes ---------------
+#ifndef NNB200_USE_NNOPS_HEADERS
+static void prepack_q4_1_case(int64_t m, int64_t n, int64_t k, bool out_f16, const char* name, cudaStream_t stream)
+{
+    g_case = name;
+    std::mt19937_64 rng(m * 7 + n + k);
+    const int64_t nblk = (k + 31) / 32;
+    std::vector<uint8_t> wb(n * nblk * 20);
+    std::uniform_real_distribution<float> ud(0.005f, 0.02f), uu(0.8f, 1.2f);
+    std::normal_distribution<float> na(0.0f, 1.0f);
+    for (int64_t i = 0; i < n * nblk; ++i) {
+        const uint16_t d = oracle_f32_to_f16(ud(rng));
+        const uint16_t mn = oracle_f32_to_f16(-8.0f * oracle_f16_to_f32(d) * uu(rng));
+        std::memcpy(&wb[i * 20], &d, 2);
+        std::memcpy(&wb[i * 20 + 2], &mn, 2);
+        for (int j = 0; j < 16; ++j) wb[i * 20 + 4 + j] = static_cast<uint8_t>(rng() & 0xFF);
+    }
+    std::vector<uint16_t> x(m * k);
+    for (auto& v : x) v = oracle_f32_to_f16(na(rng));
+    const size_t osz = out_f16 ? 2 : 4;
+    DevBuf dx(x.data(), x.size() * 2), dw(wb.data(), wb.size()), d_raw(m * n * osz), d_packed(m * n * osz);
+    const int64_t xs[] = {m, k}, ws[] = {n, k}, os[] = {m, n};
+    const DataType odt = out_f16 ? DataType::f16 : DataType::f32;
+    ComputeContext ctx;
+    ctx.expected_backend = Backend::CUDA;
+    ctx.cuda_stream = stream;
+    auto op = Linear::create(LinearAttributes{}, Backend::CUDA);
+    TensorView wv = view(ws, DataType::q4_1, dw.p);
+
+    TensorView packed;
+    {
+        const TensorView ins[] = {wv};
+        TensorView outs[] = {packed};
+        op->prepackWeights(ins, outs, ctx);
+        packed = outs[0];
+    }
+    EXPECT(packed.is_empty() && packed.layout() == TensorLayout::PackedQ4_1B200 && packed.shape(0) == n && packed.shape(1) == k);
+    const size_t blob_bytes = static_cast<size_t>(packed.shape(0) * packed.pitch());
+    EXPECT(blob_bytes >= static_cast<size_t>(n * nblk * 20) && packed.pitch() % 20 == 0);
+    DevBuf blob(blob_bytes);
+    TensorView filled(std::span<const int64_t>(packed.shape(), 2), DataType::q4_1, blob.p, packed.pitch(),
+                      TensorLayout::PackedQ4_1B200, QuantParams{});
+    {
+        const TensorView ins[] = {wv};
+        TensorView outs[] = {filled};
+        op->prepackWeights(ins, outs, ctx);
+    }
+    TensorView out_raw = view(os, odt, d_raw.p), out_packed = view(os, odt, d_packed.p);
+    const TensorView raw_ins[] = {view(xs, DataType::f16, dx.p), wv};
+    const TensorView packed_ins[] = {view(xs, DataType::f16, dx.p), filled};
+    EXPECT(op->compute(out_raw, raw_ins, ctx) == Status::ok);
+    EXPECT(op->compute(out_packed, packed_ins, ctx) == Status::ok);
+    // Same arithmetic on both forms wherever one engine serves both; everywhere within tolerance of the oracle.
+    std::vector<uint8_t> want(m * n * osz);
+    oracle_q4_1_matmul(x.data(), 1, k, wb.data(), nblk, want.data(), out_f16, n, m, n, k, 0, nullptr);
+    const auto got = d_packed.download<uint8_t>();
+    double rms = 0.0, worst = 0.0;
+    for (int64_t i = 0; i < m * n; ++i) {
+        const float w_ = out_f16 ? oracle_f16_to_f32(reinterpret_cast<const uint16_t*>(want.data())[i])
+                                 : reinterpret_cast<const float*>(want.data())[i];
+        const float g_ = out_f16 ? oracle_f16_to_f32(reinterpret_cast<const uint16_t*>(got.data())[i])
+                                 : reinterpret_cast<const float*>(got.data())[i];
+        rms += static_cast<double>(w_) * w_;
+        worst = std::max(worst, static_cast<double>(std::fabs(g_ - w_)));
+    }
+    rms = std::sqrt(rms / static_cast<double>(m * n));
+    EXPECT(worst <= (out_f16 ? 2e-2 : 4e-3) * rms);
+}
+#endif
+
 // ---- QuantizeLinear / DequantizeLinear ------------------------------------------------------
 
 // Known answers of the reference's operator test (tests/test_quant_linear.cpp:198-226, 439-467):
@@ -859,6 +929,9 @@ int main()
     prepack_case(false, 77, 130, 272, "prepack_linear_nk", stream);
     prepack_case(true, 200, 330, 1000, "prepack_matmul_kn_storage", stream);
     prepack_case(false, 4, 520, 1024, "prepack_linear_decode", nullptr);
+    prepack_q4_1_case(1, 520, 4096, false, "prepack_q4_1_gemv_f32", stream);
+    prepack_q4_1_case(3, 260, 1024, true, "prepack_q4_1_gemv_f16", nullptr);
+    prepack_q4_1_case(300, 384, 512, true, "prepack_q4_1_two_pass_f16", stream);
 #endif
 
     kat_quant_linear();

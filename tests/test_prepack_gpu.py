@@ -117,3 +117,93 @@ def test_rejections(cuda_device, nnb200_lib):
     assert lib.nnb200_i8_pack_bytes(0, 32) == 0
     torch.cuda.synchronize()
     assert not blob.any(), "a refused pack wrote nothing"
+
+
+# ---- Q4_1: separated nibble and (d, m) planes ---------------------------------------------------
+
+def _q4_problem(n, k, m, seed, a_dtype=np.float16):
+    from nnops_b200 import synth
+    rng = np.random.default_rng(seed)
+    wb = synth.q4_1_weights(rng, n, k)
+    a = rng.standard_normal((m, k)).astype(a_dtype)
+    return wb, a
+
+
+def test_q4_1_pack_is_a_pure_relayout(cuda_device, nnb200_lib):
+    """Every block's 4-byte (d, m) header and 16 nibble bytes reappear unchanged in the two planes
+    (from a padded source pitch too); pack_bytes follows the stated geometry."""
+    from nnops_b200 import capi
+    for n, k, pad in ((9, 32, 0), (33, 1000, 3), (130, 4096, 0), (17, 4096 + 128, 4)):
+        nblk = (k + 31) // 32
+        wb, _ = _q4_problem(n, k, 1, n + k)
+        src = np.zeros((n, (nblk + pad) * 20), dtype=np.uint8)
+        src[:, : nblk * 20] = wb
+        tw = torch.from_numpy(src).to(cuda_device)[:, : nblk * 20]
+        pk = ops.prepack_q4_1(tw, k)
+        assert pk.blob.numel() == capi.lib().nnb200_q4_1_pack_bytes(n, k) == n * (nblk * 16 + (-(-nblk // 4) * 4) * 4)
+        blocks = wb.reshape(n, nblk, 20)
+        assert np.array_equal(pk.qs.cpu().numpy().reshape(n, nblk, 16), blocks[:, :, 4:])
+        assert np.array_equal(pk.dm.cpu().numpy().reshape(n, nblk, 4), blocks[:, :, :4])
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 11])
+@pytest.mark.parametrize("a_dtype,out_dtype", [("f16", "f32"), ("f16", "f16"), ("f32", "f32")])
+def test_q4_1_packed_gemv(cuda_device, nnb200_lib, m, a_dtype, out_dtype):
+    """The GEMV on packed planes: same values as on the raw stream (the arithmetic is the same,
+    only the loads differ), within the f32 tolerance of the CPU oracle."""
+    n, k = 203, 1024
+    wb, a = _q4_problem(n, k, m, m, np.float16 if a_dtype == "f16" else np.float32)
+    ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device)
+    pk = ops.prepack_q4_1(tw, k)
+    tdt = torch.float32 if out_dtype == "f32" else torch.float16
+    assert ops.q4_1_engine(ta, pk, k, out_dtype=tdt) == 6
+    got = ops.linear_q4_1(ta, pk, k, out_dtype=tdt)
+    raw = ops.linear_q4_1(ta, tw, k, out_dtype=tdt, engine="gemv_dsq")
+    assert torch.equal(got, raw), "packed and raw weights must give identical results"
+    want = oracle.q4_1_matmul(a, wb, k, out_dtype=out_dtype)
+    rtol = 2e-3 if out_dtype == "f32" else 1e-2
+    tol = rtol * np.abs(want.astype(np.float32)) + rtol * float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    assert np.all(np.abs(got.cpu().numpy().astype(np.float32) - want.astype(np.float32)) <= tol)
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 4096, 4096), (1, 5000, 2048 + 128), (2, 37, 12288), (1, 16, 128)])
+def test_q4_1_packed_gemv_shapes(cuda_device, nnb200_lib, shape):
+    m, n, k = shape
+    wb, a = _q4_problem(n, k, m, n + k)
+    ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device)
+    pk = ops.prepack_q4_1(tw, k)
+    got = ops.linear_q4_1(ta, pk, k, out_dtype=torch.float32)
+    raw = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float32, engine="gemv_dsq")
+    assert torch.equal(got, raw)
+    want = oracle.q4_1_matmul(a, wb, k, out_dtype="f32").astype(np.float64)
+    err = np.abs(got.cpu().numpy().astype(np.float64) - want).max() / np.sqrt(np.mean(want ** 2))
+    assert err < 2e-5, err
+
+
+def test_q4_1_packed_two_pass_gemm(cuda_device, nnb200_lib):
+    """A tall call on packed weights expands the planes once and runs the dense GEMM: bit-identical
+    to the same call on the raw stream."""
+    m, n, k = 600, 1100, 320
+    wb, a = _q4_problem(n, k, m, 5)
+    ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device)
+    pk = ops.prepack_q4_1(tw, k)
+    assert ops.q4_1_engine(ta, pk, k, out_dtype=torch.float16) == 5
+    got = ops.linear_q4_1(ta, pk, k, out_dtype=torch.float16)
+    raw = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float16, engine="gemm_two_pass")
+    assert torch.equal(got, raw)
+
+
+def test_q4_1_packed_refusals(cuda_device, nnb200_lib):
+    """Shapes no engine serves on packed weights are refused, not silently mis-read: the fused GEMM
+    and the per-weight GEMV engines only understand the raw stream."""
+    import ctypes as C
+    from nnops_b200 import capi
+    wb, a = _q4_problem(64, 256, 40, 1)
+    ta, tw = torch.from_numpy(a).to(cuda_device), torch.from_numpy(wb).to(cuda_device)
+    pk = ops.prepack_q4_1(tw, 256)
+    out = torch.full((40, 64), 7.0, dtype=torch.float16, device=cuda_device)
+    for engine in ("gemm", "gemv_mma", "gemv_simt"):
+        args = ops.q4_1_args(ta, pk, out, 256, engine=engine)
+        assert capi.lib().nnb200_linear_q4_1(C.byref(args), None) == capi.UNSUPPORTED
+    torch.cuda.synchronize()
+    assert bool((out == 7.0).all())
