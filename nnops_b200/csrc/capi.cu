@@ -234,16 +234,13 @@ int pick_i8_engine(const nnb200_gemm_i8_args* a, const I8Problem& p)
         return (!sharded_out(a) && skinny_i8_supported(p)) ? NNB200_ENGINE_SKINNY : NNB200_ENGINE_GENERIC;
     }
     // Few activation rows: the cost is streaming W once, and what decides is how evenly an engine
-    // spreads that stream over the SMs.  Measured (us) on N=28672,K=8192 / 14336,4096 / 11008,4096 /
-    // 4096,4096:
-    //   * up to 8 rows the streaming warp-MMA engine (16 channels per CTA) wins everywhere;
-    //   * 9..16 rows: it still wins while the layer has at most 96 tiles of 128 channels
-    //     (14.9 against 16.0 / 7.8 against 15.1 on the last two), beyond that the tensor-core engine
-    //     with the weights as the 128-row operand does (16.7 against 20.7 / 46.9 against 58);
+    // spreads that stream over the SMs (crossovers measured on four layer shapes):
+    //   * up to 8 rows the streaming warp-MMA engine (16 channels per CTA);
+    //   * 9..16 rows: the same while the layer has at most 96 tiles of 128 channels, beyond that the
+    //     tensor-core engine with the weights as the 128-row operand;
     //   * 17..128 rows: a layer with so few channels that even 64-wide tiles of the square engine
-    //     leave SMs idle is served best by exactly those (4096 channels: 13.5 against 15.9..22.7);
-    //     otherwise weights-as-rows up to 64 rows, and above while the layer has 256-channel tiles
-    //     for less than half the SMs.
+    //     leave SMs idle is served best by exactly those; otherwise weights-as-rows up to 64 rows,
+    //     and above while the layer has 256-channel tiles for less than half the SMs.
     if (!sharded_out(a)) {
         const bool decode_ok = decode_i8_supported(p);
         const bool skinny_ok = skinny_i8_supported(p);
