@@ -583,10 +583,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the Q4_1 and CPU-baseline side measurements")
-    ap.add_argument("--reassembly", default="multicast", choices=["multicast", "fused", "nccl"],
-                    help="N > 1: the GEMM epilogue stores every tile once through an NVSwitch multicast mapping "
-                         "(multicast; falls back to fused where the fabric has none), or into every rank's output "
-                         "with one peer store per rank (fused), or NCCL all-gather + interleave kernel (nccl)")
+    ap.add_argument("--reassembly", default="fused", choices=["fused", "multicast", "nccl"],
+                    help="N > 1: the GEMM epilogue stores every tile into every rank's output with one peer store per "
+                         "rank (fused, the fastest measured), or once through an NVSwitch multicast mapping (multicast; "
+                         "falls back to fused where the fabric has none), or NCCL all-gather + interleave kernel (nccl)")
     ap.add_argument("--kernel-only", choices=["i8", "gemv", "q4gemm", "q4gemm2", "quant"],
                     help="profiling aid: 3 launches of one kernel (q4gemm = fused form, q4gemm2 = two-pass form, "
                          "quant = QuantizeLinear then DequantizeLinear of an [M, K] f32 tensor, per token; N unused)")
@@ -791,6 +791,18 @@ def main():
     e2e_ms = max_over_ranks(t0.elapsed_time(t1) / e2e_steps)
     e2e_value = total_ops / (e2e_ms * 1e-3) / 1e12
     e2e_check = bool(torch.equal(out_hosts[0], out_hosts[1]))
+    # What the host links give when every rank reads its share back at the same time and nothing
+    # else runs: the floor of the end-to-end step (the read-back is its largest transfer).
+    src_d2h = own_dense[0] if world > 1 else out_dev[0]
+    barrier()
+    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    d0.record()
+    for _ in range(4):
+        out_hosts[0].copy_(src_d2h, non_blocking=True)
+    d1.record()
+    barrier()
+    d2h_ms = max_over_ranks(d0.elapsed_time(d1) / 4)
+    host_link = {"d2h_ms_all_ranks_at_once": d2h_ms, "d2h_gbs_aggregate": d2h / (d2h_ms * 1e-3) / 1e9}
 
     e2e_matches_resident = None
     if world == 1:
@@ -898,7 +910,7 @@ def main():
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "results_identical_across_buffers": e2e_check,
-                    "result_equals_device_resident_run": e2e_matches_resident,
+                    "result_equals_device_resident_run": e2e_matches_resident, "host_link": host_link,
                     "method": "3 streams, double-buffered: H2D of A (at N > 1 each rank uploads M/g rows, then an "
                               "NVLink all-gather), the layer, D2H of each rank's own N/g output columns, every "
                               "step; bytes are totals over the ranks"},
