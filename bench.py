@@ -542,8 +542,11 @@ def run_kernel_only(args):
     """Three launches of one kernel on seeded inputs and nothing else: the command the ncu
     captures under profiles/ are taken from (`--kernel-only i8|gemv|q4gemm|q4gemm2 --shape M N K`)."""
     import torch
-    from nnops_b200 import build, ops, synth
+    from nnops_b200 import build, capi, ops, synth
     build.build()
+    for item in args.knob or []:
+        name, _, value = item.partition("=")
+        capi.set_knob(name.lower(), int(value))
     m, n, k = args.shape
     dev = torch.device("cuda:0")
     rng = np.random.default_rng(0)
@@ -591,6 +594,8 @@ def main():
                     help="profiling aid: 3 launches of one kernel (q4gemm = fused form, q4gemm2 = two-pass form, "
                          "quant = QuantizeLinear then DequantizeLinear of an [M, K] f32 tensor, per token; N unused)")
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=[4096, 28672, 8192])
+    ap.add_argument("--knob", action="append", metavar="NAME=VALUE",
+                    help="with --kernel-only: set a measurement switch first (e.g. i8_pair=1 for the CTA-pair form)")
     args = ap.parse_args()
     if args.kernel_only:
         run_kernel_only(args)

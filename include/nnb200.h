@@ -179,11 +179,76 @@ NNB200_API int nnb200_gemm_i8(const nnb200_gemm_i8_args* args, void* stream);
 NNB200_API int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, void* stream);
 
 /*
+ * int8 Conv2D: a pre-quantised u8/s8 NHWC activation against an s8 HWIO filter, output NHWC.
+ * Replaces conv2d_i8_cuda (src/backend/cuda/conv/conv2d_i8.cu:910-1100; kernel :358-785) and
+ * the packed-filter pair conv_i8_packed_weight_desc / conv_i8_packed_weight_pack
+ * (src/backend/cuda/conv/conv2d_pack.h:30-37).
+ *
+ * out[n][oh][ow][oc] = epilogue( sum_{kh,kw,c} x[n][oh*sh - ph + kh*dh][ow*sw - pw + kw*dw][g*IC/G + c]
+ *                                              * w[kh][kw][c][oc] ),  g = oc / (OC/G),
+ * where a tap outside the image holds the activation's zero point (the real value 0) and the
+ * epilogue is nnb200_gemm_i8's with K = kh*kw*IC/G, a per-tensor activation (scale_x, zp_x) and
+ * per-channel or per-tensor filter parameters: integer destinations S8/U8 (compensation, int32
+ * bias, Relu, requantisation), fp destinations F32/F16 (dequantisation, fp bias, clip,
+ * activation).  An S32 destination answers NNB200_UNSUPPORTED, as in the reference.
+ *
+ * Strides are in ELEMENTS.  The output's channel stride is 1 and its pixels lie at one pitch:
+ * out_stride_h == ow * out_stride_w and, for batch > 1, out_stride_n == oh * out_stride_h
+ * (otherwise NNB200_UNSUPPORTED).  weight_packed != 0: `weight` is a blob written by
+ * nnb200_conv2d_i8_pack for the same kh, kw, IC/G, oc and groups (16-byte aligned); the filter
+ * strides are then ignored and the per-call filter pass is skipped.
+ *
+ * workspace: nnb200_conv2d_i8_workspace_bytes() bytes of 16-byte aligned device scratch: the
+ * gathered activation [groups][pixels][K rounded up to 16] (none for a 1x1, stride-1, unpadded
+ * convolution over a dense activation, which the GEMM reads in place), the k-major filter and
+ * its channel sums (none with a packed filter), and the GEMM's own scratch.
+ */
+typedef struct nnb200_conv2d_i8_args {
+    const void* input;
+    const void* weight;
+    void* out;
+    int64_t batch, ih, iw, ic;
+    int64_t oh, ow, oc;
+    int64_t kh, kw, stride_h, stride_w, dil_h, dil_w, pad_h, pad_w, groups;
+    int64_t in_stride_n, in_stride_h, in_stride_w, in_stride_c;
+    int64_t w_stride_kh, w_stride_kw, w_stride_ic, w_stride_oc;
+    int64_t out_stride_n, out_stride_h, out_stride_w;
+    int32_t weight_packed;
+    int32_t a_unsigned;   /* the activation holds u8 instead of s8 */
+    int32_t out_kind;     /* NNB200_OUT_S8 / U8 / F32 / F16 */
+    const void* bias;     /* [oc]: int32 for integer destinations, out type for fp ones; may be NULL */
+    int32_t relu;
+    int32_t activation;   /* NNB200_ACT_*, fp destinations */
+    float act_alpha, act_beta;
+    float min_clip, max_clip;
+    const float* scale_w;   /* [oc] on the device, or NULL -> scale_w_scalar */
+    const int32_t* zp_w;    /* [oc] on the device, or NULL -> zp_w_scalar */
+    float scale_x, scale_w_scalar;
+    int32_t zp_x, zp_w_scalar;
+    int32_t zp_w_nonzero;   /* 0 = every zp_w[] entry is 0 (skips the activation row sums) */
+    float out_scale;
+    int32_t out_zp;
+    void* workspace;
+    size_t workspace_bytes;
+} nnb200_conv2d_i8_args;
+
+NNB200_API size_t nnb200_conv2d_i8_workspace_bytes(const nnb200_conv2d_i8_args* args);
+NNB200_API int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* args, void* stream);
+
+/* Packed filter: rows [oc][K rounded up to 16] with k contiguous (k = (kh*KW + kw)*IC/G + c),
+ * then, 256-byte aligned, the int32 sum of each row.  pack_bytes is the allocation. */
+NNB200_API size_t nnb200_conv2d_i8_pack_bytes(int64_t kh, int64_t kw, int64_t ic_per_group, int64_t oc);
+NNB200_API int nnb200_conv2d_i8_pack(const void* weight, int64_t w_stride_kh, int64_t w_stride_kw,
+                                     int64_t w_stride_ic, int64_t w_stride_oc, int64_t kh, int64_t kw,
+                                     int64_t ic_per_group, int64_t oc, int64_t groups, void* blob, void* stream);
+
+/*
  * Measurement aid: the int8 tensor rate of this GPU.  Enqueues one launch in which every SM
  * issues iters groups of four tcgen05.mma kind::i8 M128 x N256 x K32 (the int8 GEMM's own
  * instruction) on operand tiles resident in shared memory, with no loads, stores or epilogue;
  * pattern 0 fills the tiles with zeros (the pipe's issue rate), 1 with pseudo-random bytes (the
- * rate the power cap allows once the operands toggle).  *ops receives the integer operations
+ * rate the power cap allows once the operands toggle); adding 2 runs the CTA-pair form of the
+ * instruction (cta_group::2, M256 over two SMs, each holding half of the W tile).  *ops receives the integer operations
  * the launch performs (2 per multiply-add).  The caller times the launch with events on the
  * stream: ops / time is the denominator the GEMM's roofline fraction is quoted against.
  * 1 <= iters <= 2^21.  No counterpart in the reference.

@@ -21,8 +21,8 @@ LIB_DIR = PKG / "lib"
 LIB = LIB_DIR / "libnnb200.so"
 NVCC = os.environ.get("NNB200_NVCC", "/usr/local/cuda/bin/nvcc")
 
-SOURCES = ["capi.cu", "gemm_i8_umma.cu", "gemm_i8_simt.cu", "gemm_i8_decode.cu", "gemm_i8_skinny.cu", "q4_1_gemv.cu", "q4_1_gemv_mma.cu", "q4_1_gemv_dsq.cu", "q4_1_gemm_umma.cu", "gemm_f16_umma.cu", "shard_gather.cu", "quant_linear.cu", "prepack.cu", "static_scratch.cu", "mma_peak.cu"]
-HEADERS = ["ptx.cuh", "epilogue.cuh", "internal.cuh", "q4_1_common.cuh", "../../include/nnb200.h"]
+SOURCES = ["capi.cu", "gemm_i8_umma.cu", "gemm_i8_simt.cu", "gemm_i8_decode.cu", "gemm_i8_skinny.cu", "q4_1_gemv.cu", "q4_1_gemv_mma.cu", "q4_1_gemv_dsq.cu", "q4_1_gemm_umma.cu", "gemm_f16_umma.cu", "shard_gather.cu", "quant_linear.cu", "prepack.cu", "static_scratch.cu", "mma_peak.cu", "conv2d_i8.cu"]
+HEADERS = ["ptx.cuh", "ptx_pair.cuh", "epilogue.cuh", "internal.cuh", "q4_1_common.cuh", "../../include/nnb200.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

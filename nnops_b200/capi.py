@@ -94,6 +94,26 @@ class QuantLinearArgs(C.Structure):
     ]
 
 
+class Conv2dI8Args(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("weight", C.c_void_p), ("out", C.c_void_p),
+        ("batch", C.c_int64), ("ih", C.c_int64), ("iw", C.c_int64), ("ic", C.c_int64),
+        ("oh", C.c_int64), ("ow", C.c_int64), ("oc", C.c_int64),
+        ("kh", C.c_int64), ("kw", C.c_int64), ("stride_h", C.c_int64), ("stride_w", C.c_int64),
+        ("dil_h", C.c_int64), ("dil_w", C.c_int64), ("pad_h", C.c_int64), ("pad_w", C.c_int64), ("groups", C.c_int64),
+        ("in_stride_n", C.c_int64), ("in_stride_h", C.c_int64), ("in_stride_w", C.c_int64), ("in_stride_c", C.c_int64),
+        ("w_stride_kh", C.c_int64), ("w_stride_kw", C.c_int64), ("w_stride_ic", C.c_int64), ("w_stride_oc", C.c_int64),
+        ("out_stride_n", C.c_int64), ("out_stride_h", C.c_int64), ("out_stride_w", C.c_int64),
+        ("weight_packed", C.c_int32), ("a_unsigned", C.c_int32), ("out_kind", C.c_int32),
+        ("bias", C.c_void_p), ("relu", C.c_int32), ("activation", C.c_int32),
+        ("act_alpha", C.c_float), ("act_beta", C.c_float), ("min_clip", C.c_float), ("max_clip", C.c_float),
+        ("scale_w", C.c_void_p), ("zp_w", C.c_void_p),
+        ("scale_x", C.c_float), ("scale_w_scalar", C.c_float), ("zp_x", C.c_int32), ("zp_w_scalar", C.c_int32),
+        ("zp_w_nonzero", C.c_int32), ("out_scale", C.c_float), ("out_zp", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 SYMBOLS = [
     ("nnb200_gemm_i8_workspace_bytes", C.c_size_t, [C.POINTER(GemmI8Args)]),
     ("nnb200_gemm_i8_min_workspace_bytes", C.c_size_t, [C.POINTER(GemmI8Args)]),
@@ -112,6 +132,11 @@ SYMBOLS = [
     ("nnb200_q4_1_pack_bytes", C.c_size_t, [C.c_int64, C.c_int64]),
     ("nnb200_q4_1_pack", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]),
     ("nnb200_q4_1_packed_view", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.POINTER(Q41Packed)]),
+    ("nnb200_conv2d_i8_workspace_bytes", C.c_size_t, [C.POINTER(Conv2dI8Args)]),
+    ("nnb200_conv2d_i8", C.c_int, [C.POINTER(Conv2dI8Args), C.c_void_p]),
+    ("nnb200_conv2d_i8_pack_bytes", C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
+    ("nnb200_conv2d_i8_pack", C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                        C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     ("nnb200_quantize_linear", C.c_int, [C.POINTER(QuantLinearArgs), C.c_void_p]),
     ("nnb200_dequantize_linear", C.c_int, [C.POINTER(QuantLinearArgs), C.c_void_p]),
     ("nnb200_interleave_shards", C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64,

@@ -1040,7 +1040,7 @@ uint64_t nnb200_launch_count(void)
 
 int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double* ops, void* stream)
 {
-    if (iters < 1 || iters > (1 << 21) || pattern < 0 || pattern > 1) {
+    if (iters < 1 || iters > (1 << 21) || pattern < 0 || pattern > 3) {
         return NNB200_INVALID_ARGUMENT;   // the upper bound keeps the launch well inside the bounded wait
     }
     const DeviceInfo* dev = current_device_info();

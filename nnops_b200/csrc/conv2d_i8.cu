@@ -1,0 +1,460 @@
+// int8 Conv2D (NHWC u8/s8 activation x s8 HWIO filter) as a gather pass + the int8 GEMM.
+//
+// Counterpart of the reference's quantized convolution route
+// (src/backend/cuda/conv/conv2d_i8.cu:358-785 kernel, :910-1100 host entry): pixels on M, output
+// channels of one group on N, k = (tap, channel) tap-major.  There the gather runs inside an
+// mma.sync tile kernel; here the product itself belongs to the tcgen05 GEMM (gemm_i8_umma.cu and
+// the small-M engines behind nnb200_gemm_i8), and what is convolution-specific is done by two
+// streaming kernels in front of it:
+//
+//   conv_gather_i8_kernel     activation -> column matrix  col[g][pixel][k], 16 bytes per thread
+//                             where a group's channels allow it.  A tap that falls into the
+//                             padding carries the activation's zero point (the real value 0),
+//                             which is what the reference's CPU and CUDA gathers store
+//                             (conv2d_i8.cu:112-121) so that the zero-point compensation cancels it.
+//   conv_filter_kmajor_kernel HWIO filter -> [g][oc/g][k] with k contiguous (the Linear pose every
+//                             GEMM engine accepts), plus the per-channel sums R_w.  Run per call on
+//                             a raw filter (it is small), or once by nnb200_conv2d_i8_pack.
+//
+// A 1x1 / stride 1 / unpadded convolution over a dense activation needs no gather: the activation
+// IS the [pixels, channels] matrix.  The epilogue is the GEMM's (compensation, int32 bias, Relu,
+// requantisation; or dequantisation, fp bias, clip, activation): the reference's CPU convolution
+// calls the same epilogue routine as its matmul (src/backend/cpu/conv/conv2d_implicit_gemm_i8.cpp:
+// 906-980), and results are compared with that route bit for bit.
+
+#include "internal.cuh"
+
+namespace nnb200 {
+
+namespace {
+
+struct ConvGeom {
+    int64_t batch, ih, iw, ic, oh, ow, oc;
+    int64_t kh, kw, sh, sw, dh, dw, ph, pw, groups;
+    int64_t icg, ocg, k, kp;   // k = kh*kw*icg; kp = k rounded up to 16 (row pitch of the column matrix)
+    int64_t pixels;            // batch * oh * ow
+};
+
+struct GatherParams {
+    const uint8_t* in;
+    uint8_t* col;
+    int64_t in_n, in_h, in_w, in_c;   // element strides of the activation
+    int32_t batch, ih, iw, oh, ow;
+    int32_t kh, kw, sh, sw, dh, dw, ph, pw, groups, icg;
+    int32_t k, kp;
+    int64_t pixels;
+    uint32_t pad_byte;   // the activation's zero point as a byte
+};
+
+// One thread per 16-byte piece of the column matrix: 16 consecutive k of one pixel and group.
+// VEC: the 16 k are 16 consecutive channels of one tap (icg % 16 == 0, dense channel axis,
+// 16-byte aligned rows), one 128-bit load; otherwise each byte finds its own tap.
+template <bool VEC>
+__global__ void __launch_bounds__(256) conv_gather_i8_kernel(const GatherParams p)
+{
+    const int64_t chunks_per_row = p.kp >> 4;
+    const int64_t total = static_cast<int64_t>(p.groups) * p.pixels * chunks_per_row;
+    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t row = idx / chunks_per_row;           // g * pixels + pixel
+        const int32_t chunk = static_cast<int32_t>(idx - row * chunks_per_row);
+        const int32_t g = static_cast<int32_t>(row / p.pixels);
+        const int64_t pixel = row - static_cast<int64_t>(g) * p.pixels;
+        const int32_t ow = static_cast<int32_t>(pixel % p.ow);
+        const int64_t t = pixel / p.ow;
+        const int32_t oh = static_cast<int32_t>(t % p.oh);
+        const int32_t n = static_cast<int32_t>(t / p.oh);
+        const int32_t k0 = chunk << 4;
+        const uint8_t* base = p.in + static_cast<int64_t>(n) * p.in_n + static_cast<int64_t>(g) * p.icg * p.in_c;
+        uint4 v;
+        if constexpr (VEC) {
+            const int32_t tap = k0 / p.icg;
+            const int32_t c0 = k0 - tap * p.icg;
+            const int32_t kh = tap / p.kw;
+            const int32_t kw = tap - kh * p.kw;
+            const int32_t ih = oh * p.sh - p.ph + kh * p.dh;
+            const int32_t iw = ow * p.sw - p.pw + kw * p.dw;
+            const uint32_t pad4 = p.pad_byte * 0x01010101u;
+            v = make_uint4(pad4, pad4, pad4, pad4);
+            if (k0 >= p.k) {
+                v = make_uint4(0u, 0u, 0u, 0u);
+            } else if (static_cast<uint32_t>(ih) < static_cast<uint32_t>(p.ih) &&
+                       static_cast<uint32_t>(iw) < static_cast<uint32_t>(p.iw)) {
+                v = __ldg(reinterpret_cast<const uint4*>(base + static_cast<int64_t>(ih) * p.in_h +
+                                                         static_cast<int64_t>(iw) * p.in_w + c0));
+            }
+        } else {
+            uint32_t w[4] = {0u, 0u, 0u, 0u};
+            int32_t k = k0;
+            int32_t tap = k / p.icg;
+            int32_t c = k - tap * p.icg;
+            int32_t kh = tap / p.kw;
+            int32_t kw = tap - kh * p.kw;
+#pragma unroll
+            for (int j = 0; j < 16; ++j, ++k) {
+                uint32_t byte = 0u;
+                if (k < p.k) {
+                    const int32_t ih = oh * p.sh - p.ph + kh * p.dh;
+                    const int32_t iw = ow * p.sw - p.pw + kw * p.dw;
+                    byte = p.pad_byte;
+                    if (static_cast<uint32_t>(ih) < static_cast<uint32_t>(p.ih) &&
+                        static_cast<uint32_t>(iw) < static_cast<uint32_t>(p.iw)) {
+                        byte = base[static_cast<int64_t>(ih) * p.in_h + static_cast<int64_t>(iw) * p.in_w +
+                                    static_cast<int64_t>(c) * p.in_c];
+                    }
+                }
+                w[j >> 2] |= byte << ((j & 3) * 8);
+                if (++c == p.icg) {
+                    c = 0;
+                    if (++kw == p.kw) {
+                        kw = 0;
+                        ++kh;
+                    }
+                }
+            }
+            v = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        reinterpret_cast<uint4*>(p.col)[idx] = v;
+    }
+}
+
+struct FilterParams {
+    const int8_t* w;       // HWIO, element strides below
+    int8_t* wt;            // [groups][ocg][kp]
+    int32_t* r_w;          // [oc] channel sums, or null
+    int64_t w_kh, w_kw, w_ic, w_oc;
+    int32_t kh, kw, icg, ocg, groups, k, kp;
+};
+
+// One warp per output channel: lanes walk k, so the k-major row is written with coalesced
+// stores; the filter is small (K * OC bytes) and read once.  The warp also reduces the
+// channel's sum.
+__global__ void __launch_bounds__(256) conv_filter_kmajor_kernel(const FilterParams p)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t channel = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t oc = static_cast<int64_t>(p.groups) * p.ocg;
+    if (channel >= oc) {
+        return;
+    }
+    const int8_t* src = p.w + channel * p.w_oc;
+    int8_t* dst = p.wt + channel * p.kp;   // [g][n] rows are consecutive: g * ocg + n == channel
+    int32_t sum = 0;
+    for (int32_t k = lane; k < p.kp; k += 32) {
+        int8_t v = 0;
+        if (k < p.k) {
+            const int32_t tap = k / p.icg;
+            const int32_t c = k - tap * p.icg;
+            const int32_t kh = tap / p.kw;
+            const int32_t kw = tap - kh * p.kw;
+            v = src[kh * p.w_kh + kw * p.w_kw + c * p.w_ic];
+        }
+        dst[k] = v;
+        sum += v;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+    }
+    if (lane == 0 && p.r_w != nullptr) {
+        p.r_w[channel] = sum;
+    }
+}
+
+int64_t round_up_i64(int64_t v, int64_t a)
+{
+    return (v + a - 1) / a * a;
+}
+
+// Fills the derived geometry; false when the arguments do not describe a convolution.
+bool conv_geometry(const nnb200_conv2d_i8_args* a, ConvGeom* g)
+{
+    if (a == nullptr || a->batch < 0 || a->ih <= 0 || a->iw <= 0 || a->ic <= 0 || a->oc <= 0 || a->kh <= 0 ||
+        a->kw <= 0 || a->stride_h <= 0 || a->stride_w <= 0 || a->dil_h <= 0 || a->dil_w <= 0 || a->pad_h < 0 ||
+        a->pad_w < 0 || a->groups <= 0 || a->ic % a->groups != 0 || a->oc % a->groups != 0) {
+        return false;
+    }
+    g->batch = a->batch; g->ih = a->ih; g->iw = a->iw; g->ic = a->ic; g->oc = a->oc;
+    g->kh = a->kh; g->kw = a->kw; g->sh = a->stride_h; g->sw = a->stride_w; g->dh = a->dil_h; g->dw = a->dil_w;
+    g->ph = a->pad_h; g->pw = a->pad_w; g->groups = a->groups;
+    const int64_t span_h = (a->kh - 1) * a->dil_h + 1;
+    const int64_t span_w = (a->kw - 1) * a->dil_w + 1;
+    const int64_t oh = (a->ih + 2 * a->pad_h - span_h) / a->stride_h + 1;
+    const int64_t ow = (a->iw + 2 * a->pad_w - span_w) / a->stride_w + 1;
+    if (a->ih + 2 * a->pad_h < span_h || a->iw + 2 * a->pad_w < span_w || oh != a->oh || ow != a->ow) {
+        return false;
+    }
+    g->oh = oh; g->ow = ow;
+    g->icg = a->ic / a->groups;
+    g->ocg = a->oc / a->groups;
+    g->k = a->kh * a->kw * g->icg;
+    g->kp = round_up_i64(g->k, 16);
+    g->pixels = a->batch * oh * ow;
+    const int64_t lim = int64_t(1) << 31;
+    return g->k < lim && g->pixels < lim && a->ih < 32768 * 16 && a->iw < 32768 * 16;
+}
+
+// The activation can be handed to the GEMM as it lies: 1x1, stride 1, no padding, channels
+// contiguous, one uniform pixel pitch.
+bool pointwise_in_place(const nnb200_conv2d_i8_args* a, const ConvGeom& g)
+{
+    return g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.ph == 0 && g.pw == 0 && a->in_stride_c == 1 &&
+           a->in_stride_h == g.iw * a->in_stride_w && (g.batch == 1 || a->in_stride_n == g.ih * a->in_stride_h) &&
+           a->in_stride_w % 16 == 0 && reinterpret_cast<uintptr_t>(a->input) % 16 == 0 && g.icg % 16 == 0;
+}
+
+struct ConvScratch {
+    size_t col_bytes;      // gathered activation, 0 for the in-place pointwise case
+    size_t filter_bytes;   // k-major filter, 0 when the caller passed a packed one
+    size_t sums_bytes;     // R_w of every channel, 0 when packed or no zero point needs it
+    size_t gemm_bytes;     // what one group's GEMM asks for
+    size_t total;
+};
+
+size_t align256(size_t v)
+{
+    return (v + 255) & ~size_t(255);
+}
+
+// One group's GEMM, as nnb200_gemm_i8 arguments (pointers of group 0; the caller offsets them).
+void group_gemm_args(const nnb200_conv2d_i8_args* a, const ConvGeom& g, bool in_place, nnb200_gemm_i8_args* q)
+{
+    *q = nnb200_gemm_i8_args{};
+    q->m = g.pixels;
+    q->n = g.ocg;
+    q->k = g.k;
+    q->a_stride_m = in_place ? a->in_stride_w : g.kp;
+    q->a_stride_k = 1;
+    q->w_stride_n = g.kp;
+    q->w_stride_k = 1;
+    q->ldc = a->out_stride_w;
+    q->batch = 1;
+    q->a_unsigned = a->a_unsigned;
+    q->out_kind = a->out_kind;
+    q->relu = a->relu;
+    q->activation = a->activation;
+    q->act_alpha = a->act_alpha;
+    q->act_beta = a->act_beta;
+    q->min_clip = a->min_clip;
+    q->max_clip = a->max_clip;
+    q->scale_a_scalar = a->scale_x;
+    q->scale_w_scalar = a->scale_w_scalar;
+    q->zp_a_scalar = a->zp_x;
+    q->zp_w_scalar = a->zp_w_scalar;
+    q->scale_w = a->scale_w;
+    q->zp_w = a->zp_w;
+    q->bias = a->bias;
+    q->zp_w_nonzero = a->zp_w != nullptr ? a->zp_w_nonzero : 0;
+    q->out_scale = a->out_scale;
+    q->out_zp = a->out_zp;
+    q->force_engine = NNB200_ENGINE_AUTO;
+}
+
+bool needs_compensation(const nnb200_conv2d_i8_args* a)
+{
+    return a->zp_x != 0 || a->zp_w_scalar != 0 || (a->zp_w != nullptr && a->zp_w_nonzero != 0);
+}
+
+bool plan_scratch(const nnb200_conv2d_i8_args* a, const ConvGeom& g, bool in_place, ConvScratch* s)
+{
+    s->col_bytes = in_place ? 0 : align256(static_cast<size_t>(g.groups) * static_cast<size_t>(g.pixels) *
+                                           static_cast<size_t>(g.kp));
+    s->filter_bytes = a->weight_packed ? 0 : align256(static_cast<size_t>(g.oc) * static_cast<size_t>(g.kp));
+    s->sums_bytes = a->weight_packed ? 0 : align256(static_cast<size_t>(g.oc) * 4);
+    nnb200_gemm_i8_args q;
+    group_gemm_args(a, g, in_place, &q);
+    // Pointers only decide alignment-dependent engine choices: stand-ins with the alignment the
+    // real operands will have (scratch sections are 256-byte aligned).
+    q.a = in_place ? a->input : reinterpret_cast<const void*>(uintptr_t(4096));
+    q.w = reinterpret_cast<const void*>(uintptr_t(4096));
+    q.out = a->out;
+    s->gemm_bytes = align256(nnb200_gemm_i8_workspace_bytes(&q));
+    s->total = s->col_bytes + s->filter_bytes + s->sums_bytes + s->gemm_bytes;
+    return true;
+}
+
+int out_elem_bytes(int32_t kind)
+{
+    switch (kind) {
+    case NNB200_OUT_S8:
+    case NNB200_OUT_U8: return 1;
+    case NNB200_OUT_F16: return 2;
+    default: return 4;
+    }
+}
+
+}  // namespace
+
+// Byte size of the packed filter: [oc][kp] k-major rows, then int32 sums per channel.
+size_t conv_pack_bytes(int64_t oc, int64_t kp)
+{
+    return align256(static_cast<size_t>(oc) * static_cast<size_t>(kp)) + static_cast<size_t>(oc) * 4;
+}
+
+int launch_conv_filter_kmajor(const void* w, int64_t w_kh, int64_t w_kw, int64_t w_ic, int64_t w_oc, int64_t kh,
+                              int64_t kw, int64_t icg, int64_t ocg, int64_t groups, void* wt, int32_t* r_w,
+                              cudaStream_t stream)
+{
+    FilterParams f;
+    f.w = static_cast<const int8_t*>(w);
+    f.wt = static_cast<int8_t*>(wt);
+    f.r_w = r_w;
+    f.w_kh = w_kh; f.w_kw = w_kw; f.w_ic = w_ic; f.w_oc = w_oc;
+    f.kh = static_cast<int32_t>(kh); f.kw = static_cast<int32_t>(kw);
+    f.icg = static_cast<int32_t>(icg); f.ocg = static_cast<int32_t>(ocg); f.groups = static_cast<int32_t>(groups);
+    f.k = static_cast<int32_t>(kh * kw * icg);
+    f.kp = static_cast<int32_t>(round_up_i64(f.k, 16));
+    const int64_t oc = ocg * groups;
+    const unsigned blocks = static_cast<unsigned>((oc + 7) / 8);
+    conv_filter_kmajor_kernel<<<blocks, 256, 0, stream>>>(f);
+    note_launch();
+    return cuda_status(cudaGetLastError());
+}
+
+}  // namespace nnb200
+
+using namespace nnb200;
+
+extern "C" {
+
+size_t nnb200_conv2d_i8_workspace_bytes(const nnb200_conv2d_i8_args* a)
+{
+    ConvGeom g;
+    if (!conv_geometry(a, &g)) {
+        return 0;
+    }
+    ConvScratch s;
+    plan_scratch(a, g, pointwise_in_place(a, g), &s);
+    return s.total;
+}
+
+size_t nnb200_conv2d_i8_pack_bytes(int64_t kh, int64_t kw, int64_t ic_per_group, int64_t oc)
+{
+    if (kh <= 0 || kw <= 0 || ic_per_group <= 0 || oc <= 0) {
+        return 0;
+    }
+    return conv_pack_bytes(oc, round_up_i64(kh * kw * ic_per_group, 16));
+}
+
+int nnb200_conv2d_i8_pack(const void* weight, int64_t w_stride_kh, int64_t w_stride_kw, int64_t w_stride_ic,
+                          int64_t w_stride_oc, int64_t kh, int64_t kw, int64_t ic_per_group, int64_t oc,
+                          int64_t groups, void* blob, void* stream)
+{
+    if (weight == nullptr || blob == nullptr || kh <= 0 || kw <= 0 || ic_per_group <= 0 || oc <= 0 || groups <= 0 ||
+        oc % groups != 0 || reinterpret_cast<uintptr_t>(blob) % 16 != 0 ||
+        kh * kw * ic_per_group >= (int64_t(1) << 31)) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    const int64_t kp = round_up_i64(kh * kw * ic_per_group, 16);
+    int32_t* sums = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(blob) + align256(static_cast<size_t>(oc * kp)));
+    return launch_conv_filter_kmajor(weight, w_stride_kh, w_stride_kw, w_stride_ic, w_stride_oc, kh, kw, ic_per_group,
+                                     oc / groups, groups, blob, sums, static_cast<cudaStream_t>(stream));
+}
+
+int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* a, void* stream_v)
+{
+    ConvGeom g;
+    if (!conv_geometry(a, &g) || a->input == nullptr || a->weight == nullptr || a->out == nullptr) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if (a->out_kind != NNB200_OUT_S8 && a->out_kind != NNB200_OUT_U8 && a->out_kind != NNB200_OUT_F32 &&
+        a->out_kind != NNB200_OUT_F16) {
+        return NNB200_UNSUPPORTED;   // no s32 destination, as in the reference (conv2d_i8.cu:941-944)
+    }
+    // The GEMM writes [pixels, oc/g] windows at one row pitch.
+    if (a->out_stride_h != g.ow * a->out_stride_w || (g.batch > 1 && a->out_stride_n != g.oh * a->out_stride_h) ||
+        a->out_stride_w < g.oc) {
+        return NNB200_UNSUPPORTED;
+    }
+    if (a->weight_packed && reinterpret_cast<uintptr_t>(a->weight) % 16 != 0) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    if (g.pixels == 0) {
+        return NNB200_OK;
+    }
+    const bool in_place = pointwise_in_place(a, g);
+    ConvScratch plan;
+    plan_scratch(a, g, in_place, &plan);
+    if (plan.total > 0 && (a->workspace == nullptr || a->workspace_bytes < plan.total ||
+                           reinterpret_cast<uintptr_t>(a->workspace) % 16 != 0)) {
+        return NNB200_INVALID_ARGUMENT;
+    }
+    const cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+    uint8_t* col = ws;
+    int8_t* wt = reinterpret_cast<int8_t*>(ws + plan.col_bytes);
+    int32_t* r_w = reinterpret_cast<int32_t*>(ws + plan.col_bytes + plan.filter_bytes);
+    uint8_t* gemm_ws = ws + plan.col_bytes + plan.filter_bytes + plan.sums_bytes;
+    const bool comp = needs_compensation(a);
+
+    if (a->weight_packed) {
+        wt = static_cast<int8_t*>(const_cast<void*>(a->weight));
+        r_w = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(wt) + align256(static_cast<size_t>(g.oc * g.kp)));
+    } else {
+        const int st = launch_conv_filter_kmajor(a->weight, a->w_stride_kh, a->w_stride_kw, a->w_stride_ic,
+                                                 a->w_stride_oc, g.kh, g.kw, g.icg, g.ocg, g.groups, wt,
+                                                 comp ? r_w : nullptr, stream);
+        if (st != NNB200_OK) {
+            return st;
+        }
+    }
+    if (!in_place) {
+        GatherParams p;
+        p.in = static_cast<const uint8_t*>(a->input);
+        p.col = col;
+        p.in_n = a->in_stride_n; p.in_h = a->in_stride_h; p.in_w = a->in_stride_w; p.in_c = a->in_stride_c;
+        p.batch = static_cast<int32_t>(g.batch); p.ih = static_cast<int32_t>(g.ih); p.iw = static_cast<int32_t>(g.iw);
+        p.oh = static_cast<int32_t>(g.oh); p.ow = static_cast<int32_t>(g.ow);
+        p.kh = static_cast<int32_t>(g.kh); p.kw = static_cast<int32_t>(g.kw);
+        p.sh = static_cast<int32_t>(g.sh); p.sw = static_cast<int32_t>(g.sw);
+        p.dh = static_cast<int32_t>(g.dh); p.dw = static_cast<int32_t>(g.dw);
+        p.ph = static_cast<int32_t>(g.ph); p.pw = static_cast<int32_t>(g.pw);
+        p.groups = static_cast<int32_t>(g.groups); p.icg = static_cast<int32_t>(g.icg);
+        p.k = static_cast<int32_t>(g.k); p.kp = static_cast<int32_t>(g.kp);
+        p.pixels = g.pixels;
+        p.pad_byte = static_cast<uint32_t>(a->zp_x) & 0xFFu;
+        const bool vec = g.icg % 16 == 0 && a->in_stride_c == 1 && a->in_stride_w % 16 == 0 && a->in_stride_h % 16 == 0 &&
+                         a->in_stride_n % 16 == 0 && reinterpret_cast<uintptr_t>(a->input) % 16 == 0;
+        const int64_t chunks = g.groups * g.pixels * (g.kp / 16);
+        const DeviceInfo* dev = current_device_info();
+        if (dev == nullptr) {
+            return NNB200_INTERNAL;
+        }
+        int64_t blocks = (chunks + 255) / 256;
+        const int64_t cap = static_cast<int64_t>(dev->sm_count) * 32;
+        blocks = blocks > cap ? cap : blocks;
+        if (vec) {
+            conv_gather_i8_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+        } else {
+            conv_gather_i8_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+        }
+        note_launch();
+        const int st = cuda_status(cudaGetLastError());
+        if (st != NNB200_OK) {
+            return st;
+        }
+    }
+    nnb200_gemm_i8_args q;
+    group_gemm_args(a, g, in_place, &q);
+    q.workspace = plan.gemm_bytes > 0 ? gemm_ws : nullptr;
+    q.workspace_bytes = plan.gemm_bytes;
+    const int64_t out_esz = out_elem_bytes(a->out_kind);
+    const int64_t bias_esz = a->out_kind == NNB200_OUT_F16 ? 2 : 4;
+    for (int64_t grp = 0; grp < g.groups; ++grp) {
+        const int64_t c0 = grp * g.ocg;
+        q.a = in_place ? static_cast<const uint8_t*>(a->input) + grp * g.icg : col + grp * g.pixels * g.kp;
+        q.w = wt + c0 * g.kp;
+        q.out = static_cast<uint8_t*>(a->out) + c0 * out_esz;
+        q.bias = a->bias != nullptr ? static_cast<const uint8_t*>(a->bias) + c0 * bias_esz : nullptr;
+        q.scale_w = a->scale_w != nullptr ? a->scale_w + c0 : nullptr;
+        q.zp_w = a->zp_w != nullptr ? a->zp_w + c0 : nullptr;
+        q.r_w = comp ? r_w + c0 : nullptr;
+        const int st = nnb200_gemm_i8(&q, stream_v);
+        if (st != NNB200_OK) {
+            return st;
+        }
+    }
+    return NNB200_OK;
+}
+
+}  // extern "C"

@@ -365,3 +365,82 @@ def linear_fp_act(a: torch.Tensor, w: torch.Tensor, *, scale_a, zp_a=0, act_dtyp
     out_kind = "f32" if a.dtype == torch.float32 else "f16"
     return gemm_i8(aq, w, out_kind=out_kind, scale_a=scale if per_token else float(scale_a),
                    zp_a=zp if per_token else int(zp_a), **kw)
+
+
+class PackedConvI8:
+    """The k-major filter blob of nnb200_conv2d_i8_pack and the geometry it was cut for."""
+
+    def __init__(self, blob: torch.Tensor, kh: int, kw: int, icg: int, oc: int, groups: int):
+        self.blob, self.kh, self.kw, self.icg, self.oc, self.groups = blob, kh, kw, icg, oc, groups
+
+
+def prepack_conv2d_i8(w: torch.Tensor, groups: int = 1) -> PackedConvI8:
+    """w: s8 HWIO [KH, KW, IC/G, OC] (any strides) on the device."""
+    if not w.is_cuda or w.dtype != torch.int8 or w.dim() != 4:
+        raise RuntimeError("prepack_conv2d_i8 needs a CUDA s8 HWIO filter")
+    kh, kw, icg, oc = w.shape
+    lib = capi.lib()
+    blob = torch.empty(lib.nnb200_conv2d_i8_pack_bytes(kh, kw, icg, oc), dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        capi.check(lib.nnb200_conv2d_i8_pack(w.data_ptr(), w.stride(0), w.stride(1), w.stride(2), w.stride(3), kh, kw,
+                                             icg, oc, groups, blob.data_ptr(), _stream_ptr(w.device)),
+                   "nnb200_conv2d_i8_pack")
+    return PackedConvI8(blob, kh, kw, icg, oc, groups)
+
+
+def conv2d_out_hw(ih, iw, kh, kw, stride=(1, 1), dilation=(1, 1), padding=(0, 0)):
+    oh = (ih + 2 * padding[0] - ((kh - 1) * dilation[0] + 1)) // stride[0] + 1
+    ow = (iw + 2 * padding[1] - ((kw - 1) * dilation[1] + 1)) // stride[1] + 1
+    return oh, ow
+
+
+def conv2d_i8(x: torch.Tensor, w, *, stride=(1, 1), dilation=(1, 1), padding=(0, 0), groups: int = 1,
+              out_kind: str = "s8", out: torch.Tensor | None = None, bias=None, relu=False, activation="none",
+              act_alpha=0.0, act_beta=1.0, min_clip=-math.inf, max_clip=math.inf, scale_x=1.0, zp_x=0, scale_w=1.0,
+              zp_w=0, out_scale=1.0, out_zp=0, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """int8 Conv2D on the current CUDA stream: x [N, IH, IW, IC] u8/s8 (NHWC, any strides), w an s8 HWIO filter
+    [KH, KW, IC/G, OC] or a PackedConvI8; returns [N, OH, OW, OC]."""
+    if not x.is_cuda:
+        raise RuntimeError("nnops_b200.conv2d_i8 needs CUDA tensors; there is no CPU path")
+    dev = x.device
+    packed = isinstance(w, PackedConvI8)
+    n, ih, iw, ic = x.shape
+    if packed:
+        kh, kw, icg, oc = w.kh, w.kw, w.icg, w.oc
+    else:
+        kh, kw, icg, oc = w.shape
+    oh, ow = conv2d_out_hw(ih, iw, kh, kw, stride, dilation, padding)
+    if out is None:
+        out = torch.empty((n, oh, ow, oc), dtype=_OUT_TORCH[out_kind], device=dev)
+    keep: list = []
+    sw, sw0 = _dev_array(scale_w, torch.float32, dev, oc)
+    zw, zw0 = _dev_array(zp_w, torch.int32, dev, oc)
+    if bias is not None:
+        bdt = torch.int32 if out_kind in ("s8", "u8") else _OUT_TORCH[out_kind]
+        bias = torch.as_tensor(bias).to(device=dev, dtype=bdt).contiguous()
+    args = capi.Conv2dI8Args(
+        input=x.data_ptr(), weight=w.blob.data_ptr() if packed else w.data_ptr(), out=out.data_ptr(),
+        batch=n, ih=ih, iw=iw, ic=ic, oh=oh, ow=ow, oc=oc, kh=kh, kw=kw, stride_h=stride[0], stride_w=stride[1],
+        dil_h=dilation[0], dil_w=dilation[1], pad_h=padding[0], pad_w=padding[1], groups=groups,
+        in_stride_n=x.stride(0), in_stride_h=x.stride(1), in_stride_w=x.stride(2), in_stride_c=x.stride(3),
+        w_stride_kh=0 if packed else w.stride(0), w_stride_kw=0 if packed else w.stride(1),
+        w_stride_ic=0 if packed else w.stride(2), w_stride_oc=0 if packed else w.stride(3),
+        out_stride_n=out.stride(0), out_stride_h=out.stride(1), out_stride_w=out.stride(2),
+        weight_packed=int(packed), a_unsigned=int(x.dtype == torch.uint8), out_kind=capi.OUT_KINDS[out_kind],
+        bias=bias.data_ptr() if bias is not None else None, relu=int(bool(relu)),
+        activation=capi.ACTIVATIONS[activation], act_alpha=act_alpha, act_beta=act_beta, min_clip=min_clip,
+        max_clip=max_clip, scale_w=sw.data_ptr() if sw is not None else None,
+        zp_w=zw.data_ptr() if zw is not None else None, scale_x=float(scale_x),
+        scale_w_scalar=1.0 if sw0 is None else float(sw0), zp_x=int(zp_x), zp_w_scalar=0 if zw0 is None else int(zw0),
+        zp_w_nonzero=int(zw is not None and bool((zw != 0).any().item())), out_scale=float(out_scale),
+        out_zp=int(out_zp), workspace=None, workspace_bytes=0)
+    need = capi.lib().nnb200_conv2d_i8_workspace_bytes(C.byref(args))
+    if need:
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        keep.append(workspace)
+        args.workspace = workspace.data_ptr()
+        args.workspace_bytes = workspace.numel()
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nnb200_conv2d_i8(C.byref(args), _stream_ptr(dev)), "nnb200_conv2d_i8")
+    return out

@@ -350,3 +350,75 @@ def linear_fp_act(a: np.ndarray, w: np.ndarray, *, scale_a, zp_a=0, act_dtype=np
     if st != 0:
         raise RuntimeError(f"reference op returned Status {st}")
     return out
+
+
+def conv2d_out_hw(ih: int, iw: int, kh: int, kw: int, stride=(1, 1), dilation=(1, 1), padding=(0, 0)) -> tuple[int, int]:
+    oh = (ih + 2 * padding[0] - ((kh - 1) * dilation[0] + 1)) // stride[0] + 1
+    ow = (iw + 2 * padding[1] - ((kw - 1) * dilation[1] + 1)) // stride[1] + 1
+    return oh, ow
+
+
+def conv2d_i8(x: np.ndarray, w: np.ndarray, *, stride=(1, 1), dilation=(1, 1), padding=(0, 0), groups: int = 1,
+              out_kind: str = "s8", bias: np.ndarray | None = None, relu: bool = False, scale_x: float = 1.0,
+              zp_x: int = 0, scale_w=1.0, zp_w=0, out_scale: float = 1.0, out_zp: int = 0,
+              min_clip: float = -np.inf, max_clip: float = np.inf, impl: str = "port",
+              threads: int | None = None) -> np.ndarray:
+    """int8 Conv2D: ``x`` [N, IH, IW, IC] u8/s8 (NHWC), ``w`` [KH, KW, IC/G, OC] s8 (HWIO) -> [N, OH, OW, OC].
+
+    ``impl="port"`` restates the reference's definition (src/backend/cuda/conv/conv2d_i8.cu:89-141 gather,
+    src/backend/cpu/conv/conv2d_implicit_gemm_i8.cpp:906-980 epilogue): gather the taps of every output
+    pixel, k = (kh, kw, c) tap-major, a tap outside the image holding the activation's zero point, then the
+    int8 matmul epilogue per group with K = KH*KW*IC/G.  ``impl="ref"`` runs the reference's Conv2D CPU route."""
+    assert x.ndim == 4 and w.ndim == 4 and x.dtype in (np.int8, np.uint8) and w.dtype == np.int8
+    n, ih, iw, ic = x.shape
+    kh, kw, icg, oc = w.shape
+    assert ic == icg * groups and oc % groups == 0 and out_kind != "s32"
+    oh, ow = conv2d_out_hw(ih, iw, kh, kw, stride, dilation, padding)
+    ocg = oc // groups
+    if impl == "ref":
+        lib = ref_lib()
+        if lib is None:
+            raise RuntimeError("reference route not available on this host")
+        xc = np.ascontiguousarray(x)
+        wc = np.ascontiguousarray(w)
+        out = np.zeros((n, oh, ow, oc), dtype=_OUT_NP[out_kind])
+        sw = None if np.isscalar(scale_w) else np.ascontiguousarray(scale_w, dtype=np.float32)
+        zw = None if np.isscalar(zp_w) else np.ascontiguousarray(zp_w, dtype=np.int32)
+        if bias is not None:
+            bias = np.ascontiguousarray(bias, dtype=np.int32 if out_kind in ("s8", "u8") else _OUT_NP[out_kind])
+        geom = (C.c_int64 * 16)(n, ih, iw, ic, oc, kh, kw, stride[0], stride[1], dilation[0], dilation[1],
+                                padding[0], padding[1], groups, oh, ow)
+        lib.ref_conv2d_i8.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                      C.POINTER(C.c_int64), C.c_float, C.c_int32, C.c_void_p, C.c_void_p, C.c_float,
+                                      C.c_int32, C.c_float, C.c_int32, C.c_int, C.c_float, C.c_float, C.c_int]
+        lib.ref_conv2d_i8.restype = C.c_int
+        st = lib.ref_conv2d_i8(xc.ctypes.data, int(x.dtype == np.uint8), wc.ctypes.data, _ptr(bias), out.ctypes.data,
+                               OUT_KINDS[out_kind], geom, float(scale_x), int(zp_x), _ptr(sw), _ptr(zw),
+                               float(scale_w if sw is None else 1.0), int(zp_w if zw is None else 0),
+                               float(out_scale), int(out_zp), int(relu), float(min_clip), float(max_clip),
+                               int(threads or ref_threads()))
+        if st != 0:
+            raise RuntimeError(f"reference op returned Status {st}")
+        return out
+
+    # Gather: padded copy filled with the zero point, then one strided slice per tap.
+    ph, pw = padding
+    xp = np.full((n, ih + 2 * ph, iw + 2 * pw, ic), zp_x, dtype=x.dtype)
+    xp[:, ph:ph + ih, pw:pw + iw, :] = x
+    out = np.zeros((n, oh, ow, oc), dtype=_OUT_NP[out_kind])
+    per_channel = lambda v, g: v if np.isscalar(v) else np.asarray(v)[g * ocg:(g + 1) * ocg]
+    for g in range(groups):
+        cols = np.empty((n, oh, ow, kh * kw, icg), dtype=x.dtype)
+        for a in range(kh):
+            for b in range(kw):
+                h0, w0 = a * dilation[0], b * dilation[1]
+                cols[:, :, :, a * kw + b, :] = xp[:, h0:h0 + (oh - 1) * stride[0] + 1:stride[0],
+                                                  w0:w0 + (ow - 1) * stride[1] + 1:stride[1], g * icg:(g + 1) * icg]
+        a_mat = cols.reshape(n * oh * ow, kh * kw * icg)
+        w_mat = np.ascontiguousarray(w[:, :, :, g * ocg:(g + 1) * ocg].reshape(kh * kw * icg, ocg).T)
+        res = gemm_i8(a_mat, w_mat, out_kind=out_kind, bias=None if bias is None else np.asarray(bias)[g * ocg:(g + 1) * ocg],
+                      relu=relu, scale_a=float(scale_x), scale_w=per_channel(scale_w, g), zp_a=int(zp_x),
+                      zp_w=per_channel(zp_w, g), out_scale=out_scale, out_zp=out_zp, min_clip=min_clip,
+                      max_clip=max_clip, impl="port")
+        out[..., g * ocg:(g + 1) * ocg] = res.reshape(n, oh, ow, ocg)
+    return out

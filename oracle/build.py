@@ -24,7 +24,7 @@ CXX = os.environ.get("NNOPS_ORACLE_CXX", "/usr/bin/g++")
 CC = os.environ.get("NNOPS_ORACLE_CC", "/usr/bin/gcc")
 
 # The translation units the Linear/MatMul CPU route needs (reference src/CMakeLists.txt lists
-# ~130; these eleven close the link for ops/linear.cpp + ops/matmul.cpp).
+# ~130; these close the link for ops/linear.cpp, ops/matmul.cpp, ops/quant_linear.cpp and ops/conv2d.cpp).
 REF_SOURCES = [
     "ops/linear.cpp",
     "ops/matmul.cpp",
@@ -39,6 +39,14 @@ REF_SOURCES = [
     "backend/cpu/matmul/linear.cpp",
     "ops/quant_linear.cpp",
     "backend/cpu/quant_linear.cpp",
+    # Conv2D's CPU route (the int8 convolution is checked against it): seven more units close the link.
+    "ops/conv2d.cpp",
+    "ops/depthwise_conv.cpp",
+    "backend/cpu/conv/conv2d_implicit_gemm.cpp",
+    "backend/cpu/conv/conv2d_implicit_gemm_i8.cpp",
+    "backend/cpu/conv/conv2d_winograd.cpp",
+    "backend/cpu/conv/depthwise_conv.cpp",
+    "backend/cpu/conv/depthwise_conv_i8.cpp",
 ]
 
 ISA_VARIANTS = {

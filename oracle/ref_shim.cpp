@@ -5,10 +5,11 @@
 // timed host-CPU baseline ("kind": "reference").  The shipped CUDA path never loads it.
 //
 // Everything here goes through the reference's public operator API exactly as a caller
-// would: Linear::create / MatMul::create(attrs, Backend::CPU) -> compute(out, inputs, ctx),
-// with an OpenMP parallel_for injected through ComputeContext::cpu.
+// would: Linear::create / MatMul::create / Conv2D::create(attrs, Backend::CPU) ->
+// compute(out, inputs, ctx), with an OpenMP parallel_for injected through ComputeContext::cpu.
 
 #include "nnops/core/openmp_backend.hpp"
+#include "nnops/ops/conv2d.hpp"
 #include "nnops/ops/linear.hpp"
 #include "nnops/ops/matmul.hpp"
 #include "nnops/ops/quant_linear.hpp"
@@ -214,6 +215,54 @@ int ref_dequantize_linear(const void* x, int x_is_u8, const int64_t* shape, int 
     const ComputeContext ctx = make_ctx(threads);
     TensorView ins[3] = {xv, sv, zv};
     return int(op->compute(yv, std::span<const TensorView>(ins, 3), ctx, nullptr));
+}
+
+/// int8 Conv2D through the reference op: dense NHWC u8/s8 activation [n, ih, iw, ic], dense s8
+/// HWIO filter [kh, kw, ic/groups, oc], dense NHWC output.  geom = {n, ih, iw, ic, oc, kh, kw,
+/// stride_h, stride_w, dil_h, dil_w, pad_h, pad_w, groups, oh, ow}.  The call pattern is the
+/// reference's own CUDA-vs-CPU test (tests/test_cuda_conv2d.cpp:327-400).
+int ref_conv2d_i8(const void* x, int x_unsigned, const int8_t* w, const void* bias, void* out, int out_kind,
+                  const int64_t* geom, float scale_x, int32_t zp_x, const float* scale_w, const int32_t* zp_w,
+                  float scale_w_scalar, int32_t zp_w_scalar, float out_scale, int32_t out_zp, int relu,
+                  float min_clip, float max_clip, int threads)
+{
+    const int64_t n = geom[0], ih = geom[1], iw = geom[2], ic = geom[3], oc = geom[4], kh = geom[5], kw = geom[6];
+    const int64_t groups = geom[13], oh = geom[14], ow = geom[15];
+    const DataType odt = out_dtype(out_kind);
+    const bool int_out = out_kind <= 2;
+
+    QuantParams qa;
+    qa.scale = scale_x;
+    qa.zero_point = zp_x;
+    QuantParams qw = make_qp(scale_w, zp_w, scale_w_scalar, zp_w_scalar, oc, QuantGranularity::PerChannel);
+    QuantParams qc;
+    qc.scale = out_scale;
+    qc.zero_point = out_zp;
+
+    const int64_t a_shape[4] = {n, ih, iw, ic};
+    const int64_t w_shape[4] = {kh, kw, ic / groups, oc};
+    const int64_t o_shape[4] = {n, oh, ow, oc};
+    const int64_t b_shape[1] = {oc};
+    TensorView av(a_shape, x_unsigned ? DataType::u8 : DataType::s8, const_cast<void*>(x), TensorLayout::NHWC, qa);
+    TensorView wv(w_shape, DataType::s8, const_cast<int8_t*>(w), TensorLayout::HWIO, qw);
+    TensorView ov(o_shape, odt, out, TensorLayout::NHWC, qc);
+    TensorView bv(b_shape, int_out ? DataType::s32 : odt, const_cast<void*>(bias), TensorLayout::Dense);
+
+    Conv2DAttributes attrs;
+    attrs.kernel_size = {kh, kw};
+    attrs.stride = {geom[7], geom[8]};
+    attrs.dilation = {geom[9], geom[10]};
+    attrs.padding = {geom[11], geom[12]};
+    attrs.groups = groups;
+    attrs.output_dtype = odt;
+    attrs.epilogue.type = relu ? EpilogueActivateType::Relu : EpilogueActivateType::None;
+    attrs.epilogue.min_clip = min_clip;
+    attrs.epilogue.max_clip = max_clip;
+
+    auto op = Conv2D::create(attrs, Backend::CPU);
+    const ComputeContext ctx = make_ctx(threads);
+    TensorView ins[3] = {av, wv, bv};
+    return int(op->compute(ov, std::span<const TensorView>(ins, bias ? 3 : 2), ctx, nullptr));
 }
 
 void ref_release_scratch() { release_scratch_memory(); }

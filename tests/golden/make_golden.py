@@ -3,7 +3,7 @@
     python tests/golden/make_golden.py [name-prefix]     (needs oracle/_ref, i.e. the nnops source tree at build time)
 
 Each .npz holds seeded inputs, the reference's output and a JSON `meta` describing the call.
-The reference is driven through its public operator API (Linear / MatMul on Backend::CPU, via
+The reference is driven through its public operator API (Linear / MatMul / Conv2D on Backend::CPU, via
 oracle/ref_shim.cpp).  tests/test_oracle.py checks the C restatement against these files, and
 tests/test_golden_gpu.py checks the CUDA path against them, so parity with the reference stays
 pinned on machines where the reference itself cannot be built.
@@ -109,6 +109,29 @@ def quant_case(name, shape, axis, per, fdt, qdt, *, seed):
          dequantized=dq)
 
 
+def conv_case(name, shape, filt, out_kind, *, seed, stride=(1, 1), dilation=(1, 1), padding=(0, 0), groups=1,
+              a_unsigned=True, relu=True, zp_x=None):
+    """int8 Conv2D through the reference's Conv2D on Backend::CPU: NHWC activation, HWIO filter, per-channel
+    filter scales and zero points, the parameters of the reference's own CUDA-vs-CPU test."""
+    rng = np.random.default_rng(seed)
+    n, ih, iw, ic = shape
+    kh, kw, oc = filt
+    x = rng.integers(0, 256, shape, dtype=np.uint8).view(np.uint8 if a_unsigned else np.int8)
+    w = rng.integers(-127, 128, (kh, kw, ic // groups, oc), dtype=np.int8)
+    scale_w = (0.008 + 0.001 * (np.arange(oc) % 5)).astype(np.float32)
+    zp_w = ((np.arange(oc) % 7) - 3).astype(np.int32)
+    int_out = out_kind in ("s8", "u8")
+    bias = rng.integers(-1000, 1001, oc).astype(np.int32) if int_out else \
+        rng.uniform(-0.5, 0.5, oc).astype(np.float32 if out_kind == "f32" else np.float16)
+    scalars = dict(scale_x=0.0078125, zp_x=int(zp_x if zp_x is not None else (128 if a_unsigned else -6)),
+                   out_scale=0.03, out_zp=110 if out_kind == "u8" else 0)
+    geom = dict(stride=list(stride), dilation=list(dilation), padding=list(padding), groups=groups)
+    out = oracle.conv2d_i8(x, w, out_kind=out_kind, bias=bias, relu=relu, scale_w=scale_w, zp_w=zp_w, impl="ref",
+                           stride=stride, dilation=dilation, padding=padding, groups=groups, **scalars)
+    save(name, dict(op="conv2d_i8", out_kind=out_kind, relu=relu, scalars=scalars, geom=geom), x=x, w=w, bias=bias,
+         scale_w=scale_w, zp_w=zp_w, out=out)
+
+
 if __name__ == "__main__":
     if not oracle.have_ref():
         raise SystemExit("the compiled reference (oracle/_ref) is not available on this machine")
@@ -135,3 +158,10 @@ if __name__ == "__main__":
     quant_case("qdq_per_channel_last_axis_f16_s8", (6, 50), 1, "channel", np.float16, "s8", seed=23)
     fp_act_case("fp_act_f32_per_token", 96, 144, 320, np.float32, seed=30, per_token=True, relu=True)
     fp_act_case("fp_act_f16_per_tensor", 40, 100, 256, np.float16, seed=31, per_token=False, relu=False)
+    conv_case("conv_i8_3x3_u8_s8", (2, 14, 14, 32), (3, 3, 48), "s8", seed=40, padding=(1, 1))
+    conv_case("conv_i8_3x3_groups_stride_u8_u8", (1, 17, 15, 24), (3, 3, 36), "u8", seed=41, padding=(1, 1), stride=(2, 1),
+              groups=3)
+    conv_case("conv_i8_1x1_s8_f32", (2, 12, 12, 64), (1, 1, 40), "f32", seed=42, a_unsigned=False, relu=False)
+    conv_case("conv_i8_5x3_dilated_s8_f16", (1, 16, 18, 16), (5, 3, 24), "f16", seed=43, a_unsigned=False,
+              dilation=(1, 2), padding=(2, 2))
+    conv_case("conv_i8_7x7_stem_u8_s8", (1, 35, 33, 3), (7, 7, 16), "s8", seed=44, stride=(2, 2), padding=(3, 3))

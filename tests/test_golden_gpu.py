@@ -28,6 +28,16 @@ def test_cuda_matches_golden(cuda_device, nnb200_lib, path):
         got = ops.gemm_i8(a, w, out_kind=meta["out_kind"], relu=meta["relu"],
                           activation="relu" if meta["relu"] and meta["out_kind"] in ("f32", "f16") else "none", **kw)
         assert np.array_equal(got.cpu().numpy().view(np.uint8), z["out"].view(np.uint8))
+    elif meta["op"] == "conv2d_i8":
+        g = meta["geom"]
+        fp = meta["out_kind"] in ("f32", "f16")
+        got = ops.conv2d_i8(torch.from_numpy(z["x"]).to(dev), torch.from_numpy(z["w"]).to(dev),
+                            out_kind=meta["out_kind"], bias=torch.from_numpy(z["bias"]), relu=meta["relu"],
+                            activation="relu" if meta["relu"] and fp else "none",
+                            scale_w=torch.from_numpy(z["scale_w"]), zp_w=torch.from_numpy(z["zp_w"]),
+                            stride=tuple(g["stride"]), dilation=tuple(g["dilation"]), padding=tuple(g["padding"]),
+                            groups=g["groups"], **meta["scalars"])
+        assert np.array_equal(got.cpu().numpy().view(np.uint8), z["out"].view(np.uint8))
     elif meta["op"] == "fp_act":
         pt = meta["per_token"]
         got = ops.linear_fp_act(torch.from_numpy(z["a"]).to(dev), torch.from_numpy(z["w"]).to(dev),

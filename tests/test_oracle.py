@@ -118,6 +118,38 @@ def test_port_matches_reference_random():
                 assert np.array_equal(p.view(np.uint8), r.view(np.uint8)), (m, n, k, kind, relu)
 
 
+@pytest.mark.skipif(not oracle.have_ref(), reason="compiled reference not runnable on this host")
+def test_conv_port_matches_reference():
+    """The gather + matmul-epilogue restatement of the int8 convolution against the reference's Conv2D CPU route:
+    strides, dilation, padding with a non-zero activation zero point, groups down to one channel, all four
+    destinations (shapes after tests/test_cuda_conv2d.cpp:268-315)."""
+    rng = np.random.default_rng(17)
+    table = [  # n, ic, ih, iw, oc, kh, kw, stride, dilation, padding, groups, act, out
+        (1, 16, 8, 8, 8, 3, 3, (1, 1), (1, 1), (1, 1), 1, np.uint8, "s8"),
+        (1, 16, 8, 8, 8, 3, 3, (2, 1), (1, 1), (1, 1), 1, np.uint8, "f16"),
+        (1, 16, 8, 8, 8, 3, 3, (1, 1), (2, 1), (1, 1), 1, np.int8, "f16"),
+        (1, 16, 12, 12, 16, 3, 3, (1, 1), (1, 1), (1, 1), 2, np.uint8, "u8"),
+        (1, 16, 8, 8, 16, 3, 3, (1, 1), (1, 1), (1, 1), 16, np.int8, "u8"),
+        (1, 32, 32, 32, 24, 3, 3, (1, 1), (1, 1), (1, 1), 1, np.int8, "s8"),
+        (2, 24, 15, 17, 40, 5, 3, (2, 3), (1, 2), (2, 1), 1, np.uint8, "s8"),
+        (1, 3, 33, 31, 32, 7, 7, (2, 2), (1, 1), (3, 3), 1, np.uint8, "s8"),
+        (1, 64, 9, 9, 32, 1, 1, (1, 1), (1, 1), (0, 0), 1, np.int8, "f32"),
+    ]
+    for (n, ic, ih, iw, oc, kh, kw, stride, dilation, padding, groups, adt, kind) in table:
+        x = rng.integers(0, 256, (n, ih, iw, ic), dtype=np.uint8).view(adt)
+        w = rng.integers(-127, 128, (kh, kw, ic // groups, oc), dtype=np.int8)
+        int_out = kind in ("s8", "u8")
+        bias = rng.integers(-1000, 1001, oc).astype(np.int32) if int_out else \
+            rng.uniform(-0.5, 0.5, oc).astype(np.float32 if kind == "f32" else np.float16)
+        kw_ = dict(stride=stride, dilation=dilation, padding=padding, groups=groups, out_kind=kind, bias=bias, relu=True,
+                   scale_x=0.0078125, zp_x=128 if adt == np.uint8 else -6,
+                   scale_w=(0.008 + 0.001 * (np.arange(oc) % 5)).astype(np.float32),
+                   zp_w=((np.arange(oc) % 7) - 3).astype(np.int32), out_scale=0.03, out_zp=110 if kind == "u8" else 0)
+        p = oracle.conv2d_i8(x, w, impl="port", **kw_)
+        r = oracle.conv2d_i8(x, w, impl="ref", **kw_)
+        assert np.array_equal(p.view(np.uint8), r.view(np.uint8)), (n, ic, ih, iw, oc, kh, kw, groups, kind)
+
+
 def _golden_cases():
     return sorted(GOLDEN.glob("*.npz"))
 
@@ -132,6 +164,13 @@ def test_port_matches_golden(path):
         a = z["a"].T if meta.get("a_transposed") else z["a"]
         w = z["w"].T if meta.get("w_kn") else z["w"]
         out = oracle.gemm_i8(a, w, out_kind=meta["out_kind"], relu=meta["relu"], **kw)
+        assert np.array_equal(out.view(np.uint8), z["out"].view(np.uint8))
+    elif meta["op"] == "conv2d_i8":
+        g = meta["geom"]
+        out = oracle.conv2d_i8(z["x"], z["w"], out_kind=meta["out_kind"], bias=z["bias"], relu=meta["relu"],
+                               scale_w=z["scale_w"], zp_w=z["zp_w"], stride=tuple(g["stride"]),
+                               dilation=tuple(g["dilation"]), padding=tuple(g["padding"]), groups=g["groups"],
+                               **meta["scalars"])
         assert np.array_equal(out.view(np.uint8), z["out"].view(np.uint8))
     elif meta["op"] == "fp_act":
         pt = meta["per_token"]
