@@ -192,6 +192,10 @@ NNB200_API int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, vo
  * bias, Relu, requantisation), fp destinations F32/F16 (dequantisation, fp bias, clip,
  * activation).  An S32 destination answers NNB200_UNSUPPORTED, as in the reference.
  *
+ * pad_h / pad_w are the leading paddings and oh / ow are given by the caller (an auto-padded
+ * convolution pads the trailing edge differently); a window must start inside the image or its
+ * leading padding, else NNB200_INVALID_ARGUMENT.
+ *
  * Strides are in ELEMENTS.  The output's channel stride is 1 and its pixels lie at one pitch:
  * out_stride_h == ow * out_stride_w and, for batch > 1, out_stride_n == oh * out_stride_h
  * (otherwise NNB200_UNSUPPORTED).  weight_packed != 0: `weight` is a blob written by
@@ -263,9 +267,10 @@ NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double
  * INT32_MIN for an unknown knob).
  *   GROUP_M          raster group (m-blocks) of the int8 tensor-core GEMM
  *   I8_BN            force its tile width: 64, 128, 192, 224, 256, 320, 384, 448 or 512
- *   I8_PAIR          0 single-CTA form (default), 1 CTA-pair form where it applies, 2 pair form or an error
+ *   I8_PAIR          0 single-CTA form only, 2 CTA-pair form or an error (default: pair form where it applies);
+ *                    1 / 3 earlier pair forms kept for comparison (one k-block per barrier slot / two commits)
  *   I8_PEER_STAGING  1 / 2 staging tiles per epilogue warp in the sharded write-back
- *   F16_PAIR         as I8_PAIR for the dense f16 GEMM of the Q4_1 two-pass form (default 1)
+ *   F16_PAIR         as I8_PAIR for the dense f16 GEMM of the Q4_1 two-pass form
  *   I8_SHARE_K       0 never share K among SMs in the few-row engine, 2 offer it from 8 K blocks per SM
  *   Q4_GEMV          Q4_1 GEMV engine of the automatic choice: 1 never the deferred-scaling kernel, 2 that
  *                    kernel whenever it can run (default: for a single activation row)

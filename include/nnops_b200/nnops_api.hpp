@@ -103,10 +103,18 @@ struct Epilogue {
     int64_t quant_axis = 0;
 };
 
-/// Dense, plus this backend's packed int8 weight (nnb200_i8_pack's blob).  The reference numbers
-/// its layout tags append-only and 15 is its highest (include/nnops/core/tensor_layout.hpp:100-118);
-/// 16 is the next free value.
-enum class TensorLayout : uint8_t { Dense = 0, PackedI8B200 = 16, PackedQ4_1B200 = 17 };
+/// The layouts this path uses.  nnops numbers its tags append-only (include/nnops/core/tensor_layout.hpp).
+/// Tag values follow include/nnops/core/tensor_layout.hpp of nnops where a tag exists there (NHWC 2,
+/// HWIO 5, Dense 12, PackedHWIOCuda 14); the two packed matmul forms of this backend take the next
+/// free values after the highest one nnops uses (17).
+enum class TensorLayout : uint8_t {
+    NHWC = 2,
+    HWIO = 5,
+    Dense = 12,
+    PackedHWIOCuda = 14,
+    PackedI8B200 = 18,
+    PackedQ4_1B200 = 19,
+};
 
 /// Fixed-capacity dimension list (the reference uses an inline small vector of 8).
 struct Dims {
@@ -233,7 +241,7 @@ struct ComputeContext {
     void* cuda_stream = nullptr;  ///< cudaStream_t, opaque; nullptr = default stream
 };
 
-enum class OpType : uint8_t { Linear = 0, MatMul = 1, QuantizeLinear = 2, DequantizeLinear = 3 };
+enum class OpType : uint8_t { Linear = 0, MatMul = 1, QuantizeLinear = 2, DequantizeLinear = 3, Conv2D = 4 };
 
 class OpBase {
 public:
@@ -394,6 +402,52 @@ private:
     Backend backend_;
 };
 
+enum class ConvAlgorithm : uint8_t { ImplicitGemm = 0, Winograd, Auto };
+
+inline constexpr bool is_quantized_conv2d(DataType weight_dtype) noexcept { return weight_dtype == DataType::s8; }
+
+/// Field for field the attributes of nnops' Conv2D (include/nnops/ops/conv2d.hpp:51-130); this backend
+/// serves the quantized route only (s8 HWIO filter, pre-quantized u8/s8 NHWC activation).
+struct Conv2DAttributes {
+    std::array<int64_t, 2> kernel_size = {1, 1};
+    std::array<int64_t, 2> stride = {1, 1};
+    std::array<int64_t, 2> dilation = {1, 1};
+    std::array<int64_t, 2> padding = {0, 0};
+    int64_t groups = 1;
+    enum class AutoPad : uint8_t { NOTSET = 0, SAME_UPPER, SAME_LOWER, VALID };
+    AutoPad auto_pad = AutoPad::NOTSET;
+    Epilogue epilogue{};
+    bool add_to = false;
+    bool residual_pre_activation = false;
+    DataType output_dtype = DataType::f32;
+    DataType act_quant_dtype = DataType::s8;
+    ConvAlgorithm algorithm = ConvAlgorithm::Auto;
+    int64_t winograd_order = 0;
+};
+
+/// y[N, OH, OW, OC] = epilogue(conv(x[N, IH, IW, IC], w[KH, KW, IC/G, OC]) + bias), channel-last.
+class Conv2D : public OpBase {
+public:
+    static std::unique_ptr<Conv2D> create(const Conv2DAttributes& attrs, Backend backend = Backend::CPU);
+    std::vector<TensorDesc> getOutputTensorDesc(std::span<const TensorDesc> inputs) const override;
+    Status validate(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs) const override;
+    using OpBase::compute;
+    Status compute(std::span<TensorView> outputs, std::span<const TensorView> inputs, const ComputeContext& ctx = {},
+                   void* workspace = nullptr) override;
+    /// s8 HWIO filter on CUDA: the query answers an [OC, bytes / OC] s8 view tagged
+    /// TensorLayout::PackedHWIOCuda; the second call fills it; compute() accepts it in place of the filter.
+    void prepackWeights(std::span<const TensorView> inputs, std::span<TensorView> outputs,
+                        const ComputeContext& ctx = {}) override;
+    OpType getOpType() const override { return OpType::Conv2D; }
+    Backend getBackend() const override { return backend_; }
+    const Conv2DAttributes& attributes() const noexcept { return attrs_; }
+
+private:
+    Conv2D(const Conv2DAttributes& a, Backend b) : attrs_(a), backend_(b) {}
+    Conv2DAttributes attrs_;
+    Backend backend_;
+};
+
 namespace backend::cuda {
 /// The two backend entry points the operator front end dispatches to (the reference declares
 /// them at src/ops/linear.cpp:24 and src/ops/matmul.cpp:35).
@@ -410,6 +464,13 @@ Status quantize_linear_cuda(const QuantLinearAttributes& attrs, TensorView& outp
                             const ComputeContext& ctx, void* workspace);
 Status dequantize_linear_cuda(const QuantLinearAttributes& attrs, TensorView& output,
                               std::span<const TensorView> inputs, const ComputeContext& ctx, void* workspace);
+/// Conv2D's entry (dispatched at src/ops/conv2d.cpp:86-90 of the reference) and the packed-filter pair its
+/// prepackWeights drives (src/backend/cuda/conv/conv2d_pack.h:30-37).
+Status conv2d_cuda(const Conv2DAttributes& attrs, TensorView& output, std::span<const TensorView> inputs,
+                   const ComputeContext& ctx, void* workspace);
+TensorDesc conv_i8_packed_weight_desc(const Conv2DAttributes& attrs, const TensorDesc& weight);
+Status conv_i8_packed_weight_pack(const Conv2DAttributes& attrs, const TensorView& weight, TensorView& out,
+                                  const ComputeContext& ctx);
 }  // namespace backend::cuda
 
 }  // namespace nnops

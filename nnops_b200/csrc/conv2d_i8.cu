@@ -177,11 +177,12 @@ bool conv_geometry(const nnb200_conv2d_i8_args* a, ConvGeom* g)
     g->batch = a->batch; g->ih = a->ih; g->iw = a->iw; g->ic = a->ic; g->oc = a->oc;
     g->kh = a->kh; g->kw = a->kw; g->sh = a->stride_h; g->sw = a->stride_w; g->dh = a->dil_h; g->dw = a->dil_w;
     g->ph = a->pad_h; g->pw = a->pad_w; g->groups = a->groups;
-    const int64_t span_h = (a->kh - 1) * a->dil_h + 1;
-    const int64_t span_w = (a->kw - 1) * a->dil_w + 1;
-    const int64_t oh = (a->ih + 2 * a->pad_h - span_h) / a->stride_h + 1;
-    const int64_t ow = (a->iw + 2 * a->pad_w - span_w) / a->stride_w + 1;
-    if (a->ih + 2 * a->pad_h < span_h || a->iw + 2 * a->pad_w < span_w || oh != a->oh || ow != a->ow) {
+    // pad_h / pad_w are the LEADING paddings; the output extent is the caller's (an auto-padded
+    // convolution pads the trailing edge by a different amount).  Every window must start at or
+    // before the last real row / column; taps beyond any edge read the zero point.
+    const int64_t oh = a->oh, ow = a->ow;
+    if (oh <= 0 || ow <= 0 || (oh - 1) * a->stride_h - a->pad_h > a->ih - 1 ||
+        (ow - 1) * a->stride_w - a->pad_w > a->iw - 1) {
         return false;
     }
     g->oh = oh; g->ow = ow;

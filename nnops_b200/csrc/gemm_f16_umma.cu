@@ -434,8 +434,8 @@ gemm_f16_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 // the smaller stages leave room for a deeper ring.
 //
 // Signalling: TMA loads of both CTAs report their bytes to the LEADER's full barrier; the
-// leader's commits arrive on BOTH CTAs' empty / accumulator-full barriers (one plain commit per
-// destination); the epilogue warps of both CTAs arrive on the leader's accumulator-empty
+// leader's commits arrive on BOTH CTAs' empty / accumulator-full barriers (one instruction with a
+// CTA mask; two k-blocks share a barrier slot, see gemm_i8_umma.cu); the epilogue warps of both CTAs arrive on the leader's accumulator-empty
 // barrier.  A cluster barrier brackets the kernel so neither CTA initialises late or exits early.
 template <int BN>
 struct PairConfig {
@@ -448,7 +448,7 @@ struct PairConfig {
     static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kBarrierBytes;
 };
 
-template <int BN, bool OUT_F16>
+template <int BN, bool OUT_F16, int SUB, bool MC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_f16_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                           void* __restrict__ out, const int64_t ldc, const int m_total, const int n_total,
@@ -456,15 +456,18 @@ gemm_f16_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                           const int vec_ok, const int group_m, int32_t* error_word)
 {
     using Cfg = PairConfig<BN>;
-    constexpr int kStages = Cfg::kStages;
+    // SUB consecutive k-blocks share one pair of barriers (a "slot"): one wait, one expect-tx and
+    // one round of commits per SUB x 4 MMAs.
+    constexpr int kStages = Cfg::kStages / SUB;   // slots in the ring
+    constexpr int kSlotBytes = SUB * Cfg::kStageBytes;
     constexpr int kPairM = 2 * kBlockM;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_base = smem;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
-    uint64_t* empty_bar = full_bar + kStages;
-    uint64_t* acc_full_bar = empty_bar + kStages;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+    uint64_t* empty_bar = full_bar + Cfg::kStages;
+    uint64_t* acc_full_bar = empty_bar + Cfg::kStages;
     uint64_t* acc_empty_bar = acc_full_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -514,21 +517,28 @@ gemm_f16_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
                 const int m0 = tc.m_blk * kPairM + static_cast<int>(rank) * kBlockM;
                 const int n0 = tc.n_blk * BN + static_cast<int>(rank) * (BN / 2);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = 0; kb < num_kb; kb += SUB) {
                     if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         atomicCAS(error_word, 0, kErrProducerWait);
                         ok = false;
                         break;
                     }
-                    uint8_t* a_dst = stage_base + stage * Cfg::kStageBytes;
-                    uint8_t* b_dst = a_dst + Cfg::kATileBytes;
+                    const int nsub = (num_kb - kb) < SUB ? (num_kb - kb) : SUB;
                     if (rank == 0) {
-                        mbar_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+                        mbar_expect_tx(&full_bar[stage], 2 * nsub * Cfg::kStageBytes);
                     }
                     const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
-                    const int wk = w_wrap_k > 0 ? (kb * kBlockK) % w_wrap_k : kb * kBlockK;
-                    tma_load_2d_pair(a_dst, &map_a, leader_full, kb * kBlockK, m0);
-                    tma_load_2d_pair(b_dst, &map_w, leader_full, wk, n0);
+#pragma unroll
+                    for (int j = 0; j < SUB; ++j) {
+                        if (j < nsub) {
+                            uint8_t* a_dst = stage_base + stage * kSlotBytes + j * Cfg::kStageBytes;
+                            uint8_t* b_dst = a_dst + Cfg::kATileBytes;
+                            const int k0 = (kb + j) * kBlockK;
+                            const int wk = w_wrap_k > 0 ? k0 % w_wrap_k : k0;
+                            tma_load_2d_pair(a_dst, &map_a, leader_full, k0, m0);
+                            tma_load_2d_pair(b_dst, &map_w, leader_full, wk, n0);
+                        }
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -553,35 +563,50 @@ gemm_f16_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 256);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = 0; kb < num_kb; kb += SUB) {
                     if (!mbar_wait_cluster(&full_bar[stage], phase, abort_flag)) {
                         atomicCAS(error_word, 0, kErrMmaWait);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(stage_base + stage * Cfg::kStageBytes);
-                    const uint32_t b_addr = a_addr + Cfg::kATileBytes;
-                    const uint64_t a_desc = umma_desc_sw128_kmajor(a_addr);
-                    const uint64_t b_desc = umma_desc_sw128_kmajor(b_addr);
+                    const int nsub = (num_kb - kb) < SUB ? (num_kb - kb) : SUB;
 #pragma unroll
-                    for (int ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
-                        umma_f16_pair(d_tmem, a_desc + static_cast<uint64_t>(ks * 2),
-                                      b_desc + static_cast<uint64_t>(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    for (int j = 0; j < SUB; ++j) {
+                        if (j < nsub) {
+                            const uint32_t a_addr = smem_u32(stage_base + stage * kSlotBytes + j * Cfg::kStageBytes);
+                            const uint32_t b_addr = a_addr + Cfg::kATileBytes;
+                            const uint64_t a_desc = umma_desc_sw128_kmajor(a_addr);
+                            const uint64_t b_desc = umma_desc_sw128_kmajor(b_addr);
+#pragma unroll
+                            for (int ks = 0; ks < kBlockKBytes / kUmmaKBytes; ++ks) {
+                                umma_f16_pair(d_tmem, a_desc + static_cast<uint64_t>(ks * 2),
+                                              b_desc + static_cast<uint64_t>(ks * 2), idesc,
+                                              (kb > 0 || j > 0 || ks > 0) ? 1u : 0u);
+                            }
+                        }
                     }
                     // The slot is free in BOTH CTAs once these MMAs have read it.
-                    const uint32_t e = smem_u32(&empty_bar[stage]);
-                    umma_commit_pair(map_to_cta(e, 0));
-                    umma_commit_pair(map_to_cta(e, 1));
+                    if constexpr (MC) {
+                        umma_commit_pair_mask(&empty_bar[stage], 3);
+                    } else {
+                        const uint32_t e = smem_u32(&empty_bar[stage]);
+                        umma_commit_pair(map_to_cta(e, 0));
+                        umma_commit_pair(map_to_cta(e, 1));
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (ok) {
-                    const uint32_t f = smem_u32(&acc_full_bar[acc]);
-                    umma_commit_pair(map_to_cta(f, 0));
-                    umma_commit_pair(map_to_cta(f, 1));
+                    if constexpr (MC) {
+                        umma_commit_pair_mask(&acc_full_bar[acc], 3);
+                    } else {
+                        const uint32_t f = smem_u32(&acc_full_bar[acc]);
+                        umma_commit_pair(map_to_cta(f, 0));
+                        umma_commit_pair(map_to_cta(f, 1));
+                    }
                 }
             }
         }
@@ -683,12 +708,12 @@ int launch_f16_variant(const nnb200_q4_1_args& q, const F16Operands& op, const F
 
 // CTA-pair launch: 256 x BN tiles, two CTAs per tile.  Returns NNB200_UNSUPPORTED when the device
 // cannot co-schedule a single pair (the caller then uses the single-CTA form).
-template <int BN, bool OUT_F16>
+template <int BN, bool OUT_F16, int SUB, bool MC>
 int launch_f16_pair_variant(const nnb200_q4_1_args& q, const F16Operands& op, const FpEpilogue& ep,
                             const DeviceInfo& dev, cudaStream_t stream)
 {
     using Cfg = PairConfig<BN>;
-    auto kernel = gemm_f16_umma_pair_kernel<BN, OUT_F16>;
+    auto kernel = gemm_f16_umma_pair_kernel<BN, OUT_F16, SUB, MC>;
     static std::once_flag once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
     static int max_pairs[kMaxDevices];
@@ -844,18 +869,21 @@ int launch_q4_1_two_pass(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
         op.k_loop = 2 * kp;
         op.w_wrap_k = kp;
     }
-    // CTA-pair form (256-row tiles over two SMs) for tall problems; measured 1.2 % faster than the
-    // single-CTA form on M=2048, N=14336, K=4096 (208.5 us against 211 us for the whole call).
-    // Knob F16_PAIR = 0 turns it off, 2 makes a device that cannot co-schedule pairs an error.
+    // CTA-pair form (256-row tiles over two SMs) for tall problems: the default there.
+    // Knob F16_PAIR: 0 = never; 2 = the pair form or an error; 1 / 3 = older forms kept for
+    // comparison (one k-block per barrier slot; two k-blocks but one commit per destination CTA).
     const int pair_knob = knob(NNB200_KNOB_F16_PAIR);
-    const char pair_mode = pair_knob < 0 ? '1' : static_cast<char>('0' + (pair_knob > 2 ? 1 : pair_knob));
+    const char pair_mode = pair_knob == 0 ? '0' : (pair_knob == 2 ? '2' : '1');
     if (pair_mode != '0' && q.m >= 4 * kBlockM) {
         // Same width rule with 256-row tiles over sm_count / 2 pairs.
         const int bn2 = pick_bn((static_cast<int>(q.m) + 1) / 2, static_cast<int>(q.n), dev.sm_count / 2);
         int st = NNB200_UNSUPPORTED;
+#define NNB200_F16_PAIR_LAUNCH_V(BNV, SUBV, MCV) \
+    (q.out_f16 ? launch_f16_pair_variant<BNV, true, SUBV, MCV>(q, op, ep, dev, stream) \
+               : launch_f16_pair_variant<BNV, false, SUBV, MCV>(q, op, ep, dev, stream))
 #define NNB200_F16_PAIR_LAUNCH(BNV) \
-    (q.out_f16 ? launch_f16_pair_variant<BNV, true>(q, op, ep, dev, stream) \
-               : launch_f16_pair_variant<BNV, false>(q, op, ep, dev, stream))
+    (pair_knob == 1 ? NNB200_F16_PAIR_LAUNCH_V(BNV, 1, false) \
+     : pair_knob == 3 ? NNB200_F16_PAIR_LAUNCH_V(BNV, 2, false) : NNB200_F16_PAIR_LAUNCH_V(BNV, 2, true))
         if (bn2 >= 256) {
             st = NNB200_F16_PAIR_LAUNCH(256);
         } else if (bn2 >= 224) {
@@ -864,6 +892,7 @@ int launch_q4_1_two_pass(const nnb200_q4_1_args& q, const DeviceInfo& dev, cudaS
             st = NNB200_F16_PAIR_LAUNCH(192);
         }
 #undef NNB200_F16_PAIR_LAUNCH
+#undef NNB200_F16_PAIR_LAUNCH_V
         if (st != NNB200_UNSUPPORTED || pair_mode == '2') {  // '2': the pair form or nothing
             return st;
         }

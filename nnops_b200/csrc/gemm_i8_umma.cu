@@ -628,13 +628,20 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // own 128 rows of A and HALF of the tile's W rows, the pair leader issues tcgen05.mma with
 // cta_group::2 (M = 256 over both SMs' tensor cores and TMEM), and each CTA drains its own 128
 // accumulator rows through the same epilogue.  Per multiply-add the pair moves two thirds of the
-// operand bytes, and -- what pays -- its 32 KB stages give a six-deep ring where the single-CTA
-// form has room for four (a three-deep ring measured 7 % slower than four on the same problem).
+// operand bytes through L2 and shared memory, which under the power cap is worth clock.
+//
+// What the form lives or dies by is how often the tensor pipe is interrupted: every commit is a
+// point the pipe drains to, and every barrier wait a round trip for the issuing thread.  With one
+// 128-byte k-block per barrier slot (4 MMAs between commits, one commit per destination CTA) the
+// pipe was busy 75 % of the cycles and the form LOST to the single-CTA kernel; with two k-blocks
+// per slot (SUB = 2: 8 MMAs between commits) and one commit instruction that arrives on both
+// CTAs' barriers (MC) it is busy about 89 % and wins by 8-9 %.  Three k-blocks per slot leave a
+// ring of two slots, too coarse to hide the loads, and lose again.
 //
 // Signalling: TMA loads of both CTAs report their bytes to the LEADER's full barrier; the
-// leader's commits arrive on BOTH CTAs' empty / accumulator-full barriers (one plain commit per
-// destination); the epilogue warps of both CTAs arrive on the leader's accumulator-empty
-// barrier.  A cluster barrier brackets the kernel so neither CTA initialises late or exits early.
+// leader's commits arrive on BOTH CTAs' empty / accumulator-full barriers; the epilogue warps of
+// both CTAs arrive on the leader's accumulator-empty barrier.  A cluster barrier brackets the
+// kernel so neither CTA initialises late or exits early.
 template <int BN>
 struct PairTileConfig {
     static constexpr int kATileBytes = kBlockM * kBlockKBytes;   // this CTA's 128 rows of A
@@ -647,23 +654,26 @@ struct PairTileConfig {
     static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kColParamBytes + kBarrierBytes;
 };
 
-template <int BN, int KIND>
+template <int BN, int KIND, int SUB, bool MC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const I8Epilogue ep, const int m_total, const int n_total, const int k_total,
                          const uint32_t idesc, const int vec_ok, const int group_m, int32_t* error_word)
 {
     using Cfg = PairTileConfig<BN>;
-    constexpr int kStages = Cfg::kStages;
+    // SUB consecutive 128-byte k-blocks share one pair of barriers (a "slot"): one wait, one
+    // expect-tx and one pair of commits per SUB x 4 MMAs.
+    constexpr int kStages = Cfg::kStages / SUB;           // slots in the ring
+    constexpr int kSlotBytes = SUB * Cfg::kStageBytes;
     constexpr int kPairM = 2 * kBlockM;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_base = smem;
-    int32_t* col_params = reinterpret_cast<int32_t*>(smem + kStages * Cfg::kStageBytes);
+    int32_t* col_params = reinterpret_cast<int32_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(col_params + 4 * 4 * BN);
-    uint64_t* empty_bar = full_bar + kStages;
-    uint64_t* acc_full_bar = empty_bar + kStages;
+    uint64_t* empty_bar = full_bar + Cfg::kStages;
+    uint64_t* acc_full_bar = empty_bar + Cfg::kStages;
     uint64_t* acc_empty_bar = acc_full_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -713,20 +723,26 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
                 const int m0 = tc.m_blk * kPairM + static_cast<int>(rank) * kBlockM;
                 const int n0 = tc.n_blk * BN + static_cast<int>(rank) * (BN / 2);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = 0; kb < num_kb; kb += SUB) {
                     if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         atomicCAS(error_word, 0, kErrProducerWait);
                         ok = false;
                         break;
                     }
-                    uint8_t* a_dst = stage_base + stage * Cfg::kStageBytes;
-                    uint8_t* b_dst = a_dst + Cfg::kATileBytes;
+                    const int nsub = (num_kb - kb) < SUB ? (num_kb - kb) : SUB;
                     if (rank == 0) {
-                        mbar_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+                        mbar_expect_tx(&full_bar[stage], 2 * nsub * Cfg::kStageBytes);
                     }
                     const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
-                    tma_load_2d_pair(a_dst, &map_a, leader_full, kb * kBlockKBytes, m0);
-                    tma_load_2d_pair(b_dst, &map_w, leader_full, kb * kBlockKBytes, n0);
+#pragma unroll
+                    for (int j = 0; j < SUB; ++j) {
+                        if (j < nsub) {
+                            uint8_t* a_dst = stage_base + stage * kSlotBytes + j * Cfg::kStageBytes;
+                            uint8_t* b_dst = a_dst + Cfg::kATileBytes;
+                            tma_load_2d_pair(a_dst, &map_a, leader_full, (kb + j) * kBlockKBytes, m0);
+                            tma_load_2d_pair(b_dst, &map_w, leader_full, (kb + j) * kBlockKBytes, n0);
+                        }
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -751,35 +767,50 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 256);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = 0; kb < num_kb; kb += SUB) {
                     if (!mbar_wait_cluster(&full_bar[stage], phase, abort_flag)) {
                         atomicCAS(error_word, 0, kErrMmaWait);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(stage_base + stage * Cfg::kStageBytes);
-                    const uint32_t b_addr = a_addr + Cfg::kATileBytes;
-                    const uint64_t a_desc = umma_desc_sw128_kmajor(a_addr);
-                    const uint64_t b_desc = umma_desc_sw128_kmajor(b_addr);
+                    const int nsub = (num_kb - kb) < SUB ? (num_kb - kb) : SUB;
 #pragma unroll
-                    for (int ks = 0; ks < kBlockKBytes / kUmmaK; ++ks) {
-                        umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>(ks * 2),
-                                     b_desc + static_cast<uint64_t>(ks * 2), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+                    for (int j = 0; j < SUB; ++j) {
+                        if (j < nsub) {
+                            const uint32_t a_addr = smem_u32(stage_base + stage * kSlotBytes + j * Cfg::kStageBytes);
+                            const uint32_t b_addr = a_addr + Cfg::kATileBytes;
+                            const uint64_t a_desc = umma_desc_sw128_kmajor(a_addr);
+                            const uint64_t b_desc = umma_desc_sw128_kmajor(b_addr);
+#pragma unroll
+                            for (int ks = 0; ks < kBlockKBytes / kUmmaK; ++ks) {
+                                umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>(ks * 2),
+                                             b_desc + static_cast<uint64_t>(ks * 2), idesc,
+                                             (kb > 0 || j > 0 || ks > 0) ? 1u : 0u);
+                            }
+                        }
                     }
                     // The slot is free in BOTH CTAs once these MMAs have read it.
-                    const uint32_t e = smem_u32(&empty_bar[stage]);
-                    umma_commit_pair(map_to_cta(e, 0));
-                    umma_commit_pair(map_to_cta(e, 1));
+                    if constexpr (MC) {
+                        umma_commit_pair_mask(&empty_bar[stage], 3);
+                    } else {
+                        const uint32_t e = smem_u32(&empty_bar[stage]);
+                        umma_commit_pair(map_to_cta(e, 0));
+                        umma_commit_pair(map_to_cta(e, 1));
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (ok) {
-                    const uint32_t f = smem_u32(&acc_full_bar[acc]);
-                    umma_commit_pair(map_to_cta(f, 0));
-                    umma_commit_pair(map_to_cta(f, 1));
+                    if constexpr (MC) {
+                        umma_commit_pair_mask(&acc_full_bar[acc], 3);
+                    } else {
+                        const uint32_t f = smem_u32(&acc_full_bar[acc]);
+                        umma_commit_pair(map_to_cta(f, 0));
+                        umma_commit_pair(map_to_cta(f, 1));
+                    }
                 }
             }
         }
@@ -879,12 +910,12 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
 // CTA-pair launch: 256 x BN tiles, two CTAs per tile.  NNB200_UNSUPPORTED when the device cannot
 // co-schedule a single pair (the caller then uses the single-CTA form).
-template <int BN, int KIND>
+template <int BN, int KIND, int SUB = 1, bool MC = false>
 int launch_pair_variant(const I8Problem& p, const I8Epilogue& ep, int m, int n, int k, uint32_t a_fmt, int vec_ok,
                         const DeviceInfo& dev, cudaStream_t stream)
 {
     using Cfg = PairTileConfig<BN>;
-    auto kernel = gemm_i8_umma_pair_kernel<BN, KIND>;
+    auto kernel = gemm_i8_umma_pair_kernel<BN, KIND, SUB, MC>;
     static std::once_flag once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
     static int max_pairs[kMaxDevices];
@@ -926,16 +957,16 @@ int launch_pair_variant(const I8Problem& p, const I8Epilogue& ep, int m, int n, 
     return cuda_status(cudaGetLastError());
 }
 
-template <int BN>
+template <int BN, int SUB = 1, bool MC = false>
 int launch_pair_bn(const I8Problem& p, const I8Epilogue& ep, int m, int n, int k, uint32_t a_fmt, int vec_ok,
                    const DeviceInfo& dev, cudaStream_t stream)
 {
     switch (ep.out_kind) {
-    case NNB200_OUT_S32: return launch_pair_variant<BN, NNB200_OUT_S32>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
-    case NNB200_OUT_S8: return launch_pair_variant<BN, NNB200_OUT_S8>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
-    case NNB200_OUT_U8: return launch_pair_variant<BN, NNB200_OUT_U8>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
-    case NNB200_OUT_F32: return launch_pair_variant<BN, NNB200_OUT_F32>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
-    case NNB200_OUT_F16: return launch_pair_variant<BN, NNB200_OUT_F16>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_S32: return launch_pair_variant<BN, NNB200_OUT_S32, SUB, MC>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_S8: return launch_pair_variant<BN, NNB200_OUT_S8, SUB, MC>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_U8: return launch_pair_variant<BN, NNB200_OUT_U8, SUB, MC>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_F32: return launch_pair_variant<BN, NNB200_OUT_F32, SUB, MC>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_F16: return launch_pair_variant<BN, NNB200_OUT_F16, SUB, MC>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
     default: return NNB200_UNSUPPORTED;
     }
 }
@@ -1149,15 +1180,17 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
 
     const uint32_t a_fmt = p.a_unsigned ? 0u : 1u;
 
-    // CTA-pair form for tall problems with at least a full wave of 256-row tiles.
-    // Knob I8_PAIR = 0 turns it off, 2 makes a device that cannot co-schedule pairs an error.
+    // CTA-pair form for tall problems with at least a full wave of 256-row tiles: the default there.
+    // Knob I8_PAIR: 0 = never; 2 = the pair form or an error; 1 / 3 = older forms kept for
+    // comparison (one k-block per barrier slot; two k-blocks but one commit per destination CTA).
     {
         const int pair_knob = knob(NNB200_KNOB_I8_PAIR);
-        const char pair_mode = pair_knob < 0 ? '0' : static_cast<char>('0' + (pair_knob > 2 ? 1 : pair_knob));
         const int64_t pair_tiles = static_cast<int64_t>((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + 255) / 256);
-        if (pair_mode != '0' && !sharded && !a_mn && !w_mn && m >= 4 * kBlockM && pair_tiles >= dev.sm_count / 2 && bn == 256) {
-            const int st = launch_pair_bn<256>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
-            if (st != NNB200_UNSUPPORTED || pair_mode == '2') {
+        if (pair_knob != 0 && !sharded && !a_mn && !w_mn && m >= 4 * kBlockM && pair_tiles >= dev.sm_count / 2 && bn == 256) {
+            const int st = pair_knob == 1   ? launch_pair_bn<256, 1, false>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
+                           : pair_knob == 3 ? launch_pair_bn<256, 2, false>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
+                                            : launch_pair_bn<256, 2, true>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+            if (st != NNB200_UNSUPPORTED || pair_knob == 2) {
                 return st;
             }
         }

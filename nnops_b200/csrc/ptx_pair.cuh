@@ -141,4 +141,14 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr)
                  : "memory");
 }
 
+// The same arrival delivered to the barrier at this shared-memory offset in EVERY CTA named by
+// cta_mask (bit i = cluster rank i), with one instruction instead of one commit per destination.
+__device__ __forceinline__ void umma_commit_pair_mask(uint64_t* bar, uint16_t cta_mask)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     smem_u32(bar)),
+                 "h"(cta_mask)
+                 : "memory");
+}
+
 }  // namespace nnb200

@@ -7,7 +7,7 @@ Outputs (all git-ignored, shipped as built files):
   nnops_b200/lib/libnnb200_host.so      operator front end + backend glue against the stand-alone API mirror
   tests/cpp/_bin/test_ops_standalone    operator tests against that library
 and, only where the nnops source tree is present (the directory NNOPS_REFERENCE_ROOT names, else the default below):
-  nnops_b200/lib/libnnops_b200_dropin.so   nnops' own front end (src/ops/linear.cpp, matmul.cpp, quant_linear.cpp) and CPU route,
+  nnops_b200/lib/libnnops_b200_dropin.so   nnops' own front end (src/ops/linear.cpp, matmul.cpp, quant_linear.cpp, conv2d.cpp) and CPU route,
                                            compiled in place with NNOPS_HAS_CUDA, linked against THIS backend
   tests/cpp/_bin/test_ops_dropin           the same tests through the real nnops API, CUDA vs nnops' CPU route
 """
@@ -36,6 +36,10 @@ REF_SOURCES = [
     "backend/cpu/matmul/matmul_helper.cpp", "backend/cpu/matmul/matmul_small.cpp",
     "backend/cpu/matmul/matmul_qblock_fused.cpp", "backend/cpu/matmul/linear.cpp",
     "ops/quant_linear.cpp", "backend/cpu/quant_linear.cpp",
+    # Conv2D's front end and the CPU route its tests compare with.
+    "ops/conv2d.cpp", "ops/depthwise_conv.cpp", "backend/cpu/conv/conv2d_implicit_gemm.cpp",
+    "backend/cpu/conv/conv2d_implicit_gemm_i8.cpp", "backend/cpu/conv/conv2d_winograd.cpp",
+    "backend/cpu/conv/depthwise_conv.cpp", "backend/cpu/conv/depthwise_conv_i8.cpp",
 ]
 COMMON = ["-std=c++23", "-O2", "-fPIC", "-Wall", f"-I{ROOT / 'include'}"]
 
@@ -60,8 +64,8 @@ def _rpath(*dirs):
 def build_standalone(force=False) -> Path:
     lib = lib_build.build()
     out = LIB_DIR / "libnnb200_host.so"
-    srcs = [HOST / "cuda_backend.cpp", HOST / "quant_backend.cpp", HOST / "ops_frontend.cpp"]
-    deps = srcs + [ROOT / "include" / "nnops_b200" / "nnops_api.hpp", ROOT / "include" / "nnb200.h", lib]
+    srcs = [HOST / "cuda_backend.cpp", HOST / "quant_backend.cpp", HOST / "conv_backend.cpp", HOST / "ops_frontend.cpp"]
+    deps = srcs + [HOST / "staging.hpp", ROOT / "include" / "nnops_b200" / "nnops_api.hpp", ROOT / "include" / "nnb200.h", lib]
     if force or _stale(out, deps):
         _run([CXX, *COMMON, "-shared", "-o", out, *srcs, f"-L{LIB_DIR}", "-lnnb200", *_rpath("$ORIGIN")])
     return out
@@ -74,9 +78,9 @@ def build_dropin(force=False) -> Path | None:
         return p if p.exists() else None
     lib = lib_build.build()
     out = LIB_DIR / "libnnops_b200_dropin.so"
-    glue = [HOST / "cuda_backend.cpp", HOST / "quant_backend.cpp"]
+    glue = [HOST / "cuda_backend.cpp", HOST / "quant_backend.cpp", HOST / "conv_backend.cpp", HOST / "not_implemented.cpp"]
     srcs = [REFERENCE_ROOT / "src" / s for s in REF_SOURCES]
-    if not (force or _stale(out, [*glue, lib, ROOT / "include" / "nnb200.h", *srcs])):
+    if not (force or _stale(out, [*glue, HOST / "staging.hpp", lib, ROOT / "include" / "nnb200.h", *srcs])):
         return out
     obj_dir = LIB_DIR / "obj_dropin"
     obj_dir.mkdir(exist_ok=True)

@@ -1,4 +1,4 @@
-// Stand-alone front end of Linear, MatMul, QuantizeLinear and DequantizeLinear for builds
+// Stand-alone front end of Linear, MatMul, QuantizeLinear, DequantizeLinear and Conv2D (quantized route) for builds
 // without the nnops source tree: create / getOutputTensorDesc / validate / compute with the
 // reference's argument checks and status codes (src/ops/linear.cpp:26-120,
 // src/ops/matmul.cpp:36-152, src/ops/quant_linear.cpp:54-175,
@@ -312,6 +312,128 @@ Status DequantizeLinear::compute(std::span<TensorView> outputs, std::span<const 
         return Status::unsupported;
     }
     return backend::cuda::dequantize_linear_cuda(attrs_, outputs[0], inputs, ctx, workspace);
+}
+
+// ---- Conv2D (quantized route) -----------------------------------------------------------
+
+namespace {
+
+int64_t ceil_div_i64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// include/nnops/detail/shape_inference.hpp:55-83.
+int64_t spatial_out(int64_t in, int64_t kernel, int64_t stride, int64_t dilation, int64_t padding, int auto_pad)
+{
+    const int64_t eff = dilation * (kernel - 1) + 1;
+    switch (auto_pad) {
+    case 0: return (in + 2 * padding - eff) / stride + 1;
+    case 1: return ceil_div_i64(in, stride);
+    case 2: return in > 0 ? (in - 1) / stride + 1 : 1;
+    case 3: return (in - eff) / stride + 1;
+    default: return 0;
+    }
+}
+
+// include/nnops/detail/shape_inference.hpp:87-108: only the leading half is a kernel argument.
+int64_t leading_padding(int64_t in, int64_t kernel, int64_t stride, int64_t dilation, int64_t padding, int auto_pad)
+{
+    if (auto_pad == 1 || auto_pad == 2) {
+        const int64_t eff = dilation * (kernel - 1) + 1;
+        const int64_t total = std::max<int64_t>(0, (ceil_div_i64(in, stride) - 1) * stride + eff - in);
+        return auto_pad == 1 ? total / 2 : total - total / 2;
+    }
+    return auto_pad == 3 ? 0 : padding;
+}
+
+}  // namespace
+
+std::unique_ptr<Conv2D> Conv2D::create(const Conv2DAttributes& attrs, Backend backend)
+{
+    return std::unique_ptr<Conv2D>(new Conv2D(attrs, backend));
+}
+
+std::vector<TensorDesc> Conv2D::getOutputTensorDesc(std::span<const TensorDesc> inputs) const
+{
+    const TensorDesc& in = inputs[0];
+    const TensorDesc& wt = inputs[1];
+    const int ap = static_cast<int>(attrs_.auto_pad);
+    TensorDesc out;
+    out.rank = 4;
+    out.layout = in.layout;
+    out.dtype = in.dtype;
+    out.dims[0] = in.dims[0];
+    out.dims[1] = spatial_out(in.dims[1], attrs_.kernel_size[0], attrs_.stride[0], attrs_.dilation[0], attrs_.padding[0], ap);
+    out.dims[2] = spatial_out(in.dims[2], attrs_.kernel_size[1], attrs_.stride[1], attrs_.dilation[1], attrs_.padding[1], ap);
+    // HWIO's last axis is OC; a packed blob's descriptor leads with it.
+    out.dims[3] = wt.layout == TensorLayout::PackedHWIOCuda ? wt.dims[0] : wt.dims[3];
+    if (is_quantized_conv2d(wt.dtype)) {
+        // src/ops/conv2d.cpp:168-178: a pre-quantized activation takes output_dtype.
+        const bool fp_act = in.dtype == DataType::f32 || in.dtype == DataType::f16;
+        const DataType odt = attrs_.output_dtype;
+        const bool int_out = odt == DataType::s8 || odt == DataType::u8;
+        out.dtype = (int_out || !fp_act) ? odt : in.dtype;
+    }
+    return {out};
+}
+
+Status Conv2D::validate(std::span<const TensorDesc> inputs, std::span<const TensorDesc> outputs) const
+{
+    if (check_counts(inputs.size(), outputs.size(), 2, 3, 1) != Status::ok) {
+        return Status::invalid_argument;
+    }
+    if (inputs[0].layout != TensorLayout::NHWC && inputs[0].layout != TensorLayout::Dense) {
+        return Status::invalid_argument;
+    }
+    if (inputs[1].layout != TensorLayout::HWIO && inputs[1].layout != TensorLayout::PackedHWIOCuda) {
+        return Status::invalid_argument;
+    }
+    if (attrs_.add_to && attrs_.residual_pre_activation) {
+        return Status::unsupported;
+    }
+    return Status::ok;
+}
+
+Status Conv2D::compute(std::span<TensorView> outputs, std::span<const TensorView> inputs, const ComputeContext& ctx,
+                       void* workspace)
+{
+    if (const Status s = check_views(outputs, inputs, 2, 3); s != Status::ok) {
+        return s;
+    }
+    if (const Status s = validate_views(*this, outputs, inputs); s != Status::ok) {
+        return s;
+    }
+    if (backend_ != Backend::CUDA) {
+        return Status::unsupported;
+    }
+    // auto_pad lives in the descriptor; the kernel sees explicit leading padding (src/ops/conv2d.cpp:246-256).
+    Conv2DAttributes attrs = attrs_;
+    if (attrs.auto_pad != Conv2DAttributes::AutoPad::NOTSET) {
+        const int ap = static_cast<int>(attrs.auto_pad);
+        attrs.padding[0] = leading_padding(inputs[0].shape(1), attrs.kernel_size[0], attrs.stride[0], attrs.dilation[0],
+                                           attrs.padding[0], ap);
+        attrs.padding[1] = leading_padding(inputs[0].shape(2), attrs.kernel_size[1], attrs.stride[1], attrs.dilation[1],
+                                           attrs.padding[1], ap);
+        attrs.auto_pad = Conv2DAttributes::AutoPad::NOTSET;
+    }
+    return backend::cuda::conv2d_cuda(attrs, outputs[0], inputs, ctx, workspace);
+}
+
+void Conv2D::prepackWeights(std::span<const TensorView> inputs, std::span<TensorView> outputs, const ComputeContext& ctx)
+{
+    if (backend_ != Backend::CUDA || inputs.empty() || outputs.empty()) {
+        return;
+    }
+    const TensorView& weight = inputs[0];
+    const TensorDesc d = backend::cuda::conv_i8_packed_weight_desc(attrs_, weight.desc());
+    if (d.rank == 0) {
+        return;   // no packed form
+    }
+    if (outputs[0].is_empty()) {
+        const int64_t shape[2] = {d.dims[0], d.dims[1]};
+        outputs[0] = TensorView(std::span<const int64_t>(shape, 2), d.dtype, nullptr, d.row_stride_elems, d.layout,
+                                weight.quant_params());
+        return;
+    }
+    (void)backend::cuda::conv_i8_packed_weight_pack(attrs_, weight, outputs[0], ctx);
 }
 
 }  // namespace nnops

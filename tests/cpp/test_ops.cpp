@@ -11,6 +11,7 @@
 //     also run on Backend::CPU (the reference's CPU route) and compared byte for byte.
 
 #ifdef NNB200_USE_NNOPS_HEADERS
+#include "nnops/ops/conv2d.hpp"
 #include "nnops/ops/linear.hpp"
 #include "nnops/ops/matmul.hpp"
 #include "nnops/ops/quant_linear.hpp"
@@ -883,6 +884,224 @@ static void quant_linear_case(const QuantCase& c, const char* name, cudaStream_t
 #endif
 }
 
+// ---- int8 Conv2D (reference tests/test_cuda_conv2d.cpp:252-500) -----------------------------
+
+struct ConvCase {
+    int64_t n, ic, ih, iw, oc, kh, kw, sh, sw, dh, dw, ph, pw, groups;
+    DataType adt, odt;
+    bool bias, relu;
+    int auto_pad;   // 0 = explicit padding, 1 = SAME_UPPER
+    bool packed;    // run a second time through prepackWeights
+};
+
+// Expected value: the gather written out (taps outside the image hold the activation's zero
+// point) and the C oracle's int8 matmul per group.
+static std::vector<uint8_t> conv_expected(const ConvCase& c, int64_t oh, int64_t ow, int64_t ph, int64_t pw,
+                                          const std::vector<uint8_t>& x, const std::vector<int8_t>& w,
+                                          const void* bias_host, int32_t zp_x, const std::vector<float>& sw,
+                                          const std::vector<int32_t>& zw, float out_scale, int32_t out_zp)
+{
+    const int64_t icg = c.ic / c.groups, ocg = c.oc / c.groups, k = c.kh * c.kw * icg, pixels = c.n * oh * ow;
+    const size_t osz = data_type_size(c.odt);
+    const bool int_out = kind_of(c.odt) <= 2;
+    std::vector<uint8_t> want(static_cast<size_t>(pixels * c.oc) * osz, 0);
+    std::vector<uint8_t> col(static_cast<size_t>(pixels * k));
+    std::vector<int8_t> wt(static_cast<size_t>(ocg * k));
+    for (int64_t g = 0; g < c.groups; ++g) {
+        for (int64_t p = 0; p < pixels; ++p) {
+            const int64_t b = p / (oh * ow), y = (p / ow) % oh, xo = p % ow;
+            for (int64_t a = 0; a < c.kh; ++a) {
+                for (int64_t bb = 0; bb < c.kw; ++bb) {
+                    const int64_t iy = y * c.sh - ph + a * c.dh, ix = xo * c.sw - pw + bb * c.dw;
+                    for (int64_t ch = 0; ch < icg; ++ch) {
+                        uint8_t v = static_cast<uint8_t>(zp_x);
+                        if (iy >= 0 && iy < c.ih && ix >= 0 && ix < c.iw) {
+                            v = x[static_cast<size_t>(((b * c.ih + iy) * c.iw + ix) * c.ic + g * icg + ch)];
+                        }
+                        col[static_cast<size_t>(p * k + (a * c.kw + bb) * icg + ch)] = v;
+                    }
+                }
+            }
+        }
+        for (int64_t o = 0; o < ocg; ++o) {
+            for (int64_t kk = 0; kk < k; ++kk) {
+                wt[static_cast<size_t>(o * k + kk)] = w[static_cast<size_t>(kk * c.oc + g * ocg + o)];
+            }
+        }
+        oracle_gemm_i8_args o{};
+        o.a = col.data(); o.w = wt.data();
+        o.out = want.data() + static_cast<size_t>(g * ocg) * osz;
+        o.m = pixels; o.n = ocg; o.k = k;
+        o.a_stride_m = k; o.a_stride_k = 1; o.w_stride_n = k; o.w_stride_k = 1; o.ldc = c.oc;
+        o.a_unsigned = c.adt == DataType::u8;
+        o.out_kind = kind_of(c.odt);
+        o.bias = bias_host ? static_cast<const uint8_t*>(bias_host) + static_cast<size_t>(g * ocg) * (int_out ? 4 : osz) : nullptr;
+        o.relu = c.relu;
+        o.scale_w = sw.data() + g * ocg;
+        o.zp_w = zw.data() + g * ocg;
+        o.scale_a_scalar = 0.0078125f; o.scale_w_scalar = 1.0f;
+        o.zp_a_scalar = zp_x;
+        o.out_scale = out_scale; o.out_zp = out_zp;
+        o.min_clip = -INFINITY; o.max_clip = INFINITY;
+        oracle_gemm_i8(&o);
+    }
+    return want;
+}
+
+static void conv2d_i8_case(const ConvCase& c, const char* name, cudaStream_t stream)
+{
+    g_case = name;
+    std::mt19937_64 rng(c.ic * 977 + c.oc * 31 + c.ih);
+    const int64_t icg = c.ic / c.groups;
+    std::vector<uint8_t> x(static_cast<size_t>(c.n * c.ih * c.iw * c.ic));
+    for (auto& v : x) v = static_cast<uint8_t>(rng() & 0xFF);
+    std::vector<int8_t> w(static_cast<size_t>(c.kh * c.kw * icg * c.oc));
+    for (auto& v : w) v = static_cast<int8_t>(static_cast<int>(rng() % 255) - 127);
+    std::vector<float> sw(c.oc);
+    std::vector<int32_t> zw(c.oc);
+    for (int64_t i = 0; i < c.oc; ++i) {
+        sw[i] = 0.008f + 0.001f * static_cast<float>(i % 5);
+        zw[i] = static_cast<int32_t>(i % 7) - 3;
+    }
+    const bool int_out = kind_of(c.odt) <= 2;
+    const size_t osz = data_type_size(c.odt);
+    std::vector<int32_t> bias_i(c.oc);
+    std::vector<float> bias_f(c.oc);
+    std::vector<uint16_t> bias_h(c.oc);
+    for (int64_t i = 0; i < c.oc; ++i) {
+        bias_i[i] = static_cast<int32_t>(rng() % 2001) - 1000;
+        bias_f[i] = 0.0005f * static_cast<float>(bias_i[i]);
+        bias_h[i] = oracle_f32_to_f16(bias_f[i]);
+    }
+    const void* bias_host = !c.bias ? nullptr
+                            : int_out ? static_cast<const void*>(bias_i.data())
+                                      : (c.odt == DataType::f32 ? static_cast<const void*>(bias_f.data())
+                                                                : static_cast<const void*>(bias_h.data()));
+    const int32_t zp_x = c.adt == DataType::u8 ? 128 : -6;
+    const float out_scale = 0.03f;
+    const int32_t out_zp = c.odt == DataType::u8 ? 110 : 0;
+
+    Conv2DAttributes attrs;
+    attrs.kernel_size = {c.kh, c.kw};
+    attrs.stride = {c.sh, c.sw};
+    attrs.dilation = {c.dh, c.dw};
+    attrs.padding = {c.ph, c.pw};
+    attrs.groups = c.groups;
+    attrs.output_dtype = c.odt;
+    attrs.auto_pad = c.auto_pad == 1 ? Conv2DAttributes::AutoPad::SAME_UPPER : Conv2DAttributes::AutoPad::NOTSET;
+    if (c.relu) attrs.epilogue.type = EpilogueActivateType::Relu;
+
+    QuantParams qa = per_tensor(0.0078125f, zp_x);
+    QuantParams qw = arrays(sw.data(), zw.data(), c.oc, QuantGranularity::PerChannel);   // HOST arrays: the contract
+    const QuantParams qc = per_tensor(out_scale, out_zp);
+    DevBuf dx(x.data(), x.size()), dw(w.data(), w.size());
+    DevBuf dbias(bias_host ? bias_host : static_cast<const void*>(bias_i.data()), static_cast<size_t>(c.oc) * (int_out ? 4 : osz));
+    const int64_t xs[] = {c.n, c.ih, c.iw, c.ic}, ws[] = {c.kh, c.kw, icg, c.oc}, bs[] = {c.oc};
+    TensorView xv(xs, c.adt, dx.p, TensorLayout::NHWC, qa);
+    TensorView wv(ws, DataType::s8, dw.p, TensorLayout::HWIO, qw);
+    TensorView bv(bs, int_out ? DataType::s32 : c.odt, dbias.p);
+
+    auto op = Conv2D::create(attrs, Backend::CUDA);
+    std::vector<TensorDesc> in_d = {xv.desc(), wv.desc()};
+    std::vector<TensorView> ins = {xv, wv};
+    if (c.bias) {
+        in_d.push_back(bv.desc());
+        ins.push_back(bv);
+    }
+    const TensorDesc od = op->getOutputTensorDesc(in_d).front();
+    EXPECT(od.rank == 4 && od.dtype == c.odt && od.dims[0] == c.n && od.dims[3] == c.oc);
+    const int64_t oh = od.dims[1], ow = od.dims[2];
+    int64_t ph = c.ph, pw = c.pw;
+    if (c.auto_pad == 1) {
+        const int64_t th = std::max<int64_t>(0, (oh - 1) * c.sh + (c.kh - 1) * c.dh + 1 - c.ih);
+        const int64_t tw = std::max<int64_t>(0, (ow - 1) * c.sw + (c.kw - 1) * c.dw + 1 - c.iw);
+        ph = th / 2;
+        pw = tw / 2;
+    }
+    const auto want = conv_expected(c, oh, ow, ph, pw, x, w, bias_host, zp_x, sw, zw, out_scale, out_zp);
+    DevBuf dout(want.size(), 0x5A);
+    const int64_t os[] = {c.n, oh, ow, c.oc};
+    TensorView ov(os, c.odt, dout.p, TensorLayout::NHWC, qc);
+    ComputeContext ctx;
+    ctx.expected_backend = Backend::CUDA;
+    ctx.cuda_stream = stream;
+    EXPECT(op->compute(ov, ins, ctx) == Status::ok);
+    const auto got = dout.download<uint8_t>();
+    EXPECT(got == want);
+
+    if (c.packed) {
+        // Two-step prepack: query, allocate, fill; the packed call is bit-identical.
+        TensorView packed;
+        const TensorView pin[] = {wv};
+        TensorView pout[] = {packed};
+        op->prepackWeights(pin, pout, ctx);
+        EXPECT(pout[0].is_empty() && pout[0].rank() == 2 && pout[0].layout() == TensorLayout::PackedHWIOCuda &&
+               pout[0].shape(0) == c.oc);
+        DevBuf blob(static_cast<size_t>(pout[0].numel()));
+        const int64_t pshape[] = {pout[0].shape(0), pout[0].shape(1)};
+        TensorView filled(pshape, DataType::s8, blob.p, pout[0].shape(1), TensorLayout::PackedHWIOCuda, qw);
+        TensorView pout2[] = {filled};
+        op->prepackWeights(pin, pout2, ctx);
+        DevBuf dout2(want.size(), 0x5A);
+        TensorView ov2(os, c.odt, dout2.p, TensorLayout::NHWC, qc);
+        std::vector<TensorView> ins2 = ins;
+        ins2[1] = filled;
+        EXPECT(op->compute(ov2, ins2, ctx) == Status::ok);
+        EXPECT(dout2.download<uint8_t>() == want);
+    }
+
+#ifdef NNB200_USE_NNOPS_HEADERS
+    // The reference's own CPU route on the same bytes.
+    std::vector<uint8_t> cpu(want.size(), 0x5A);
+    TensorView hx(xs, c.adt, x.data(), TensorLayout::NHWC, qa);
+    TensorView hw(ws, DataType::s8, w.data(), TensorLayout::HWIO, qw);
+    TensorView hb(bs, int_out ? DataType::s32 : c.odt, const_cast<void*>(bias_host));
+    TensorView ho(os, c.odt, cpu.data(), TensorLayout::NHWC, qc);
+    std::vector<TensorView> hins = {hx, hw};
+    if (c.bias) hins.push_back(hb);
+    auto cpu_op = Conv2D::create(attrs, Backend::CPU);
+    EXPECT(cpu_op->compute(ho, hins) == Status::ok);
+    EXPECT(cpu == got);
+#endif
+}
+
+static void conv2d_contract_cases()
+{
+    g_case = "conv2d_contract";
+    // An s32 destination has no Conv2D route (tests/test_cuda_conv2d.cpp:503-528); neither has a
+    // Winograd request or a residual add on the quantized route.
+    std::vector<uint8_t> a(1 * 8 * 8 * 4, 1);
+    std::vector<int8_t> w(3 * 3 * 4 * 6, 1);
+    DevBuf da(a.data(), a.size()), dw(w.data(), w.size()), dout(6 * 6 * 6 * 4, 0x5A);
+    const int64_t as[] = {1, 8, 8, 4}, ws[] = {3, 3, 4, 6}, cs[] = {1, 6, 6, 6};
+    TensorView av(as, DataType::u8, da.p, TensorLayout::NHWC, per_tensor(0.01f, 128));
+    TensorView wv(ws, DataType::s8, dw.p, TensorLayout::HWIO, per_tensor(0.01f, 0));
+    ComputeContext ctx;
+    ctx.expected_backend = Backend::CUDA;
+    const TensorView ins[] = {av, wv};
+    {
+        TensorView cv(cs, DataType::s32, dout.p, TensorLayout::NHWC);
+        Conv2DAttributes attrs;
+        attrs.kernel_size = {3, 3};
+        attrs.output_dtype = DataType::s32;
+        auto op = Conv2D::create(attrs, Backend::CUDA);
+        EXPECT(op->compute(cv, ins, ctx) == Status::unsupported);
+    }
+    {
+        TensorView cv(cs, DataType::s8, dout.p, TensorLayout::NHWC, per_tensor(0.05f, 0));
+        Conv2DAttributes attrs;
+        attrs.kernel_size = {3, 3};
+        attrs.output_dtype = DataType::s8;
+        attrs.add_to = true;
+        auto op = Conv2D::create(attrs, Backend::CUDA);
+        EXPECT(op->compute(cv, ins, ctx) == Status::unsupported);
+    }
+    const auto canary = dout.download<uint8_t>();
+    bool untouched = true;
+    for (uint8_t v : canary) untouched = untouched && v == 0x5A;
+    EXPECT(untouched);   // a rejected call writes nothing
+}
+
 int main()
 {
     int dev_count = 0;
@@ -933,6 +1152,19 @@ int main()
     prepack_q4_1_case(3, 260, 1024, true, "prepack_q4_1_gemv_f16", nullptr);
     prepack_q4_1_case(300, 384, 512, true, "prepack_q4_1_two_pass_f16", stream);
 #endif
+
+    conv2d_i8_case({1, 16, 8, 8, 8, 3, 3, 1, 1, 1, 1, 1, 1, 1, DataType::u8, DataType::s8, true, true, 0, true}, "conv2d_i8_3x3_u8_s8", stream);
+    conv2d_i8_case({1, 16, 8, 8, 8, 3, 3, 2, 1, 1, 1, 1, 1, 1, DataType::u8, DataType::f16, true, true, 0, false}, "conv2d_i8_stride_f16", nullptr);
+    conv2d_i8_case({1, 16, 8, 8, 8, 3, 3, 1, 1, 2, 1, 1, 1, 1, DataType::s8, DataType::f16, true, true, 0, false}, "conv2d_i8_dilated_f16", stream);
+    conv2d_i8_case({1, 16, 12, 12, 16, 3, 3, 1, 1, 1, 1, 1, 1, 2, DataType::u8, DataType::u8, true, true, 0, true}, "conv2d_i8_groups_u8", stream);
+    conv2d_i8_case({1, 16, 8, 8, 16, 3, 3, 1, 1, 1, 1, 1, 1, 16, DataType::s8, DataType::u8, true, true, 0, true}, "conv2d_i8_one_channel_groups", nullptr);
+    conv2d_i8_case({2, 64, 28, 28, 128, 1, 1, 1, 1, 1, 1, 0, 0, 1, DataType::s8, DataType::s8, true, false, 0, true}, "conv2d_i8_pointwise", stream);
+    conv2d_i8_case({1, 32, 32, 32, 24, 3, 3, 1, 1, 1, 1, 1, 1, 1, DataType::s8, DataType::s8, true, true, 0, false}, "conv2d_i8_oc24", stream);
+    conv2d_i8_case({1, 256, 14, 14, 256, 3, 3, 1, 1, 1, 1, 1, 1, 1, DataType::s8, DataType::s8, true, true, 0, true}, "conv2d_i8_k2304", stream);
+    conv2d_i8_case({1, 64, 56, 56, 64, 3, 3, 1, 1, 1, 1, 1, 1, 1, DataType::u8, DataType::s8, true, true, 0, false}, "conv2d_i8_3136_pixels", stream);
+    conv2d_i8_case({1, 128, 7, 7, 128, 3, 3, 1, 1, 1, 1, 1, 1, 1, DataType::s8, DataType::f32, false, false, 0, false}, "conv2d_i8_f32_no_bias", nullptr);
+    conv2d_i8_case({2, 3, 33, 31, 32, 7, 7, 2, 2, 1, 1, 0, 0, 1, DataType::u8, DataType::s8, true, true, 1, true}, "conv2d_i8_stem_same_upper", stream);
+    conv2d_contract_cases();
 
     kat_quant_linear();
     quant_linear_case({{64, 4096}, -1, 1, false, false}, "quant_linear_per_tensor_f32_s8", stream);

@@ -173,7 +173,7 @@ def test_refusals_launch_nothing(cuda_device):
 
     before = lib.nnb200_launch_count()
     assert lib.nnb200_conv2d_i8(C.byref(args(out_kind=0)), None) == capi.UNSUPPORTED       # s32 destination
-    assert lib.nnb200_conv2d_i8(C.byref(args(oh=7)), None) == capi.INVALID_ARGUMENT          # shape does not follow
+    assert lib.nnb200_conv2d_i8(C.byref(args(oh=11)), None) == capi.INVALID_ARGUMENT         # windows start below the image
     assert lib.nnb200_conv2d_i8(C.byref(args(groups=3)), None) == capi.INVALID_ARGUMENT
     assert lib.nnb200_conv2d_i8(C.byref(args(out_stride_h=80)), None) == capi.UNSUPPORTED    # rows at two pitches
     assert lib.nnb200_conv2d_i8(C.byref(args(workspace_bytes=16)), None) == capi.INVALID_ARGUMENT

@@ -219,13 +219,15 @@ def test_wide_single_wave_tiles(cuda_device, nnb200_lib, bn, knobs):
     _run_case(cuda_device, 2048, 8192, 128, out_kind="f16", per_channel=True, engine="umma", seed=bn + 2)
 
 
+@pytest.mark.parametrize("form", [2, 1, 3])
 @pytest.mark.parametrize("case", [(1100, 9000, 512, "s8"), (2048, 9472, 256, "s32"), (777, 19000, 384, "f16"),
-                                  (4096, 4736, 640, "u8"), (600, 20000, 96, "f32")])
-def test_cta_pair_form(cuda_device, nnb200_lib, case, knobs):
-    """256-row tiles over clusters of two CTAs (tcgen05.mma cta_group::2): forced ("2" = the pair
-    form or an error), ragged M / N / K, every destination."""
+                                  (4096, 4736, 640, "u8"), (600, 20000, 96, "f32"), (1024, 9728, 128, "s8")])
+def test_cta_pair_form(cuda_device, nnb200_lib, case, form, knobs):
+    """256-row tiles over clusters of two CTAs (tcgen05.mma cta_group::2): forced ("2" = the
+    default pair form or an error; 1 and 3 are its earlier variants), ragged M / N / K including
+    odd and single counts of 128-byte k-blocks (two share a barrier slot), every destination."""
     m, n, k, kind = case
-    knobs("i8_pair", 2)
+    knobs("i8_pair", form)
     _run_case(cuda_device, m, n, k, out_kind=kind, relu=True, per_token=True, per_channel=True, zero_points=True,
               out_scale=0.9, out_zp=0 if kind == "s32" else 3, engine="umma", seed=m + n)
 

@@ -182,6 +182,23 @@ def test_gemm_two_pass_shapes(cuda_device, nnb200_lib, shape, out_dtype):
     _close(got.cpu().numpy(), want, RTOL_F16 if out_dtype == "f16" else RTOL_F32)
 
 
+@pytest.mark.parametrize("shape", [(700, 5000, 1000), (2048, 4096, 64), (1024, 7000, 192), (520, 9500, 96)])
+def test_gemm_two_pass_pair_forms_agree(cuda_device, nnb200_lib, shape, knobs):
+    """The dense pass of the two-pass form has a single-CTA kernel and three CTA-pair variants
+    (knob f16_pair: 0 = single, 1 / 3 = earlier pair forms, default = two k-blocks per barrier
+    slot with one commit): the accumulation order is the same in all of them, so the outputs are
+    bit-identical -- odd and single counts of k-blocks included."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k + 3)
+    ta = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float16)).to(cuda_device)
+    tw = torch.from_numpy(synth.q4_1_weights(rng, n, k)).to(cuda_device)
+    ref = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float16, engine="gemm_two_pass").clone()
+    for form in (0, 1, 3, 2):
+        knobs("f16_pair", form)
+        got = ops.linear_q4_1(ta, tw, k, out_dtype=torch.float16, engine="gemm_two_pass")
+        assert torch.equal(got, ref), form
+
+
 @pytest.mark.parametrize("shape", [(96, 160, 512), (130, 300, 1000), (600, 1100, 320), (2048, 1024, 96)])
 @pytest.mark.parametrize("out_dtype", ["f32", "f16"])
 def test_gemm_two_pass_f32_activations(cuda_device, nnb200_lib, shape, out_dtype):
