@@ -538,6 +538,32 @@ def secondary_i8_poses(torch, dev):
     return out
 
 
+def secondary_i8_conv2d(torch, dev):
+    """int8 Conv2D (u8 NHWC x s8 HWIO -> s8, bias + Relu, per-channel filter scales) on two layer
+    shapes of a ResNet-50 body at batch 32, synthetic values: a 3x3 (gather pass + GEMM) and a 1x1
+    (the GEMM reads the activation in place).  TOP/s counts 2 * pixels * OC * KH*KW*IC."""
+    from nnops_b200 import ops
+    out = {}
+    for name, (n, hw, ic, oc, ks, pad) in {"i8_conv2d_3x3_56x56x256": (32, 56, 256, 256, 3, 1),
+                                            "i8_conv2d_1x1_56x56x256_to_1024": (32, 56, 256, 1024, 1, 0)}.items():
+        x = torch.randint(0, 256, (n, hw, hw, ic), dtype=torch.uint8, device=dev)
+        w = torch.randint(-127, 128, (ks, ks, ic, oc), dtype=torch.int8, device=dev)
+        sw = torch.rand(oc, device=dev) * 0.01 + 0.005
+        bias = torch.randint(-1000, 1001, (oc,), dtype=torch.int32, device=dev)
+        o = torch.empty((n, hw, hw, oc), dtype=torch.int8, device=dev)
+        ws = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+        packed = ops.prepack_conv2d_i8(w)
+        kw = dict(padding=(pad, pad), out_kind="s8", out=o, bias=bias, relu=True, scale_x=0.02, zp_x=128, scale_w=sw,
+                  out_scale=0.05, workspace=ws)
+        us_raw = graph_time_us(torch, lambda: ops.conv2d_i8(x, w, **kw), calls_per_graph=4, replays=5)
+        us_packed = graph_time_us(torch, lambda: ops.conv2d_i8(x, packed, **kw), calls_per_graph=4, replays=5)
+        total_ops = 2.0 * n * hw * hw * oc * ks * ks * ic
+        out[name] = {"tops": total_ops / us_packed / 1e6, "us_per_call": us_packed, "us_per_call_raw_filter": us_raw,
+                     "shape": {"batch": n, "hw": hw, "ic": ic, "oc": oc, "kernel": ks, "padding": pad}}
+        del ws
+    return out
+
+
 def run_kernel_only(args):
     """Three launches of one kernel on seeded inputs and nothing else: the command the ncu
     captures under profiles/ are taken from (`--kernel-only i8|gemv|q4gemm|q4gemm2 --shape M N K`)."""
@@ -821,9 +847,9 @@ def main():
     tp = ROOT / "profiles" / "dram_traffic.json"
     if tp.exists() and world == 1:      # captured for the single-GPU launch only
         try:
-            traffic = json.loads(tp.read_text()).get("gemm_i8_umma_cfg5_bytes_per_launch")
+            traffic = json.loads(tp.read_text()).get("gemm_i8_umma_pair_cfg5_bytes_per_launch")
             traffic_source = ("profiles/dram_traffic.json: dram__bytes_read.sum + dram__bytes_write.sum of one ncu "
-                              "capture of this kernel on this workload (profiles/gemm_i8_umma_config5.md); not "
+                              "capture of this kernel on this workload (profiles/gemm_i8_umma_pair_config5.md); not "
                               "re-measured by this run")
         except (ValueError, OSError):
             traffic = None
@@ -860,6 +886,7 @@ def main():
         extra.update(secondary_q4_1(torch, dev, peaks))
         extra.update(secondary_i8_config2(torch, dev, peaks))
         extra.update(secondary_i8_poses(torch, dev))
+        extra.update(secondary_i8_conv2d(torch, dev))
         extra.update(secondary_quant_linear(torch, dev, peaks))
         extra.update(secondary_i8_decode(torch, dev, peaks, layer.w, layer.kw["scale_w"], layer.kw["bias"]))
         extra["e2e_op"] = operator_level_bench(10, 3)
@@ -924,7 +951,9 @@ def main():
                          "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_source,
                          "peak_source": peak_source, "frac_of_2x_bf16_burst": achieved / derived_peak,
                          "frac_of_nominal_4500": achieved / 4500.0,
-                         "kernel": "gemm_i8_umma_kernel<256,S8>", "kernel_ms": kernel_ms,
+                         "kernel": ("gemm_i8_umma_pair_kernel<256,S8> (CTA pairs, tcgen05.mma cta_group::2)" if world == 1
+                                    else "gemm_i8_umma_kernel<256,S8,peers> (sharded epilogue)"),
+                         "kernel_ms": kernel_ms,
                          "ops_per_launch": per_launch_ops},
             "out_sha256": my_hash, "parity": parity,
             "cpu_baseline": cpu_baseline,

@@ -486,12 +486,19 @@ int nnb200_gemm_i8(const nnb200_gemm_i8_args* a, void* stream_v)
             int32_t* r_a = reinterpret_cast<int32_t*>(ws);
             int32_t* r_w = reinterpret_cast<int32_t*>(ws + ra_bytes);
             const bool have_rw = a->r_w != nullptr && (a->batch == 1 || a->w_batch_stride == 0);
-            const int st = launch_i8_sums(p, r_a, have_rw ? nullptr : r_w, stream);
-            if (st != NNB200_OK) {
-                return st;
+            // R_a only multiplies weight zero points: without any, the sweep over A is skipped.
+            // Likewise R_w only multiplies activation zero points.
+            const bool need_ra = a->zp_w_scalar != 0 || (a->zp_w != nullptr && a->zp_w_nonzero != 0);
+            const bool need_rw = a->zp_a_scalar != 0 || (a->zp_a != nullptr && a->zp_a_nonzero != 0);
+            const bool sweep_w = need_rw && !have_rw;
+            if (need_ra || sweep_w) {
+                const int st = launch_i8_sums(p, need_ra ? r_a : nullptr, sweep_w ? r_w : nullptr, stream);
+                if (st != NNB200_OK) {
+                    return st;
+                }
             }
-            ep.r_a = r_a;
-            ep.r_w = have_rw ? a->r_w : r_w;
+            ep.r_a = need_ra ? r_a : nullptr;
+            ep.r_w = !need_rw ? nullptr : (have_rw ? a->r_w : r_w);
         }
         int st;
         switch (a->batch == 1 ? engine0 : pick_i8_engine(a, p)) {

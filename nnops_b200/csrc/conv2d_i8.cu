@@ -13,8 +13,9 @@
 //                             which is what the reference's CPU and CUDA gathers store
 //                             (conv2d_i8.cu:112-121) so that the zero-point compensation cancels it.
 //   conv_filter_kmajor_kernel HWIO filter -> [g][oc/g][k] with k contiguous (the Linear pose every
-//                             GEMM engine accepts), plus the per-channel sums R_w.  Run per call on
-//                             a raw filter (it is small), or once by nnb200_conv2d_i8_pack.
+//                             GEMM engine accepts); conv_filter_sums_kernel adds the per-channel
+//                             sums R_w.  Run per call on a raw filter (it is small), or once by
+//                             nnb200_conv2d_i8_pack.
 //
 // A 1x1 / stride 1 / unpadded convolution over a dense activation needs no gather: the activation
 // IS the [pixels, channels] matrix.  The epilogue is the GEMM's (compensation, int32 bias, Relu,
@@ -121,43 +122,66 @@ __global__ void __launch_bounds__(256) conv_gather_i8_kernel(const GatherParams 
 struct FilterParams {
     const int8_t* w;       // HWIO, element strides below
     int8_t* wt;            // [groups][ocg][kp]
-    int32_t* r_w;          // [oc] channel sums, or null
     int64_t w_kh, w_kw, w_ic, w_oc;
     int32_t kh, kw, icg, ocg, groups, k, kp;
 };
 
-// One warp per output channel: lanes walk k, so the k-major row is written with coalesced
-// stores; the filter is small (K * OC bytes) and read once.  The warp also reduces the
-// channel's sum.
+// 32 x 32 tiles through shared memory: the HWIO filter is read along oc (its contiguous axis),
+// the k-major rows are written along k.  Columns k >= K of the padded rows are written as zeros.
 __global__ void __launch_bounds__(256) conv_filter_kmajor_kernel(const FilterParams p)
 {
-    const int lane = threadIdx.x & 31;
-    const int64_t channel = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    __shared__ int8_t tile[32][33];
+    const int tx = threadIdx.x & 31;
+    const int ty = threadIdx.x >> 5;   // 0..7
     const int64_t oc = static_cast<int64_t>(p.groups) * p.ocg;
-    if (channel >= oc) {
-        return;
-    }
-    const int8_t* src = p.w + channel * p.w_oc;
-    int8_t* dst = p.wt + channel * p.kp;   // [g][n] rows are consecutive: g * ocg + n == channel
-    int32_t sum = 0;
-    for (int32_t k = lane; k < p.kp; k += 32) {
+    const int k0 = blockIdx.x * 32;
+    const int64_t c0 = static_cast<int64_t>(blockIdx.y) * 32;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int k = k0 + ty * 4 + r;
+        const int64_t channel = c0 + tx;
         int8_t v = 0;
-        if (k < p.k) {
+        if (k < p.k && channel < oc) {
             const int32_t tap = k / p.icg;
             const int32_t c = k - tap * p.icg;
             const int32_t kh = tap / p.kw;
             const int32_t kw = tap - kh * p.kw;
-            v = src[kh * p.w_kh + kw * p.w_kw + c * p.w_ic];
+            v = p.w[kh * p.w_kh + kw * p.w_kw + c * p.w_ic + channel * p.w_oc];
         }
-        dst[k] = v;
-        sum += v;
+        tile[ty * 4 + r][tx] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int64_t channel = c0 + ty * 4 + r;
+        const int k = k0 + tx;
+        if (channel < oc && k < p.kp) {
+            p.wt[channel * p.kp + k] = tile[tx][ty * 4 + r];   // [g][n] rows are consecutive: g * ocg + n == channel
+        }
+    }
+}
+
+// Channel sums of the k-major filter, one warp per channel (coalesced 4-byte reads; kp is a
+// multiple of 16 and the padding is zero).
+__global__ void __launch_bounds__(256) conv_filter_sums_kernel(const int8_t* __restrict__ wt, const int64_t oc,
+                                                               const int32_t kp, int32_t* __restrict__ r_w)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t channel = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (channel >= oc) {
+        return;
+    }
+    const int32_t* row = reinterpret_cast<const int32_t*>(wt + channel * kp);
+    int32_t sum = 0;
+    for (int32_t i = lane; i < kp / 4; i += 32) {
+        sum = __dp4a(row[i], 0x01010101, sum);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
         sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
     }
-    if (lane == 0 && p.r_w != nullptr) {
-        p.r_w[channel] = sum;
+    if (lane == 0) {
+        r_w[channel] = sum;
     }
 }
 
@@ -192,7 +216,7 @@ bool conv_geometry(const nnb200_conv2d_i8_args* a, ConvGeom* g)
     g->kp = round_up_i64(g->k, 16);
     g->pixels = a->batch * oh * ow;
     const int64_t lim = int64_t(1) << 31;
-    return g->k < lim && g->pixels < lim && a->ih < 32768 * 16 && a->iw < 32768 * 16;
+    return g->k < lim && g->pixels < lim && a->ih < 32768 * 16 && a->iw < 32768 * 16 && g->oc < (int64_t(1) << 21);
 }
 
 // The activation can be handed to the GEMM as it lies: 1x1, stride 1, no padding, channels
@@ -299,16 +323,19 @@ int launch_conv_filter_kmajor(const void* w, int64_t w_kh, int64_t w_kw, int64_t
     FilterParams f;
     f.w = static_cast<const int8_t*>(w);
     f.wt = static_cast<int8_t*>(wt);
-    f.r_w = r_w;
     f.w_kh = w_kh; f.w_kw = w_kw; f.w_ic = w_ic; f.w_oc = w_oc;
     f.kh = static_cast<int32_t>(kh); f.kw = static_cast<int32_t>(kw);
     f.icg = static_cast<int32_t>(icg); f.ocg = static_cast<int32_t>(ocg); f.groups = static_cast<int32_t>(groups);
     f.k = static_cast<int32_t>(kh * kw * icg);
     f.kp = static_cast<int32_t>(round_up_i64(f.k, 16));
     const int64_t oc = ocg * groups;
-    const unsigned blocks = static_cast<unsigned>((oc + 7) / 8);
-    conv_filter_kmajor_kernel<<<blocks, 256, 0, stream>>>(f);
+    const dim3 grid(static_cast<unsigned>((f.kp + 31) / 32), static_cast<unsigned>((oc + 31) / 32));
+    conv_filter_kmajor_kernel<<<grid, 256, 0, stream>>>(f);
     note_launch();
+    if (r_w != nullptr) {
+        conv_filter_sums_kernel<<<static_cast<unsigned>((oc + 7) / 8), 256, 0, stream>>>(f.wt, oc, f.kp, r_w);
+        note_launch();
+    }
     return cuda_status(cudaGetLastError());
 }
 
@@ -342,7 +369,7 @@ int nnb200_conv2d_i8_pack(const void* weight, int64_t w_stride_kh, int64_t w_str
                           int64_t groups, void* blob, void* stream)
 {
     if (weight == nullptr || blob == nullptr || kh <= 0 || kw <= 0 || ic_per_group <= 0 || oc <= 0 || groups <= 0 ||
-        oc % groups != 0 || reinterpret_cast<uintptr_t>(blob) % 16 != 0 ||
+        oc % groups != 0 || oc >= (int64_t(1) << 21) || reinterpret_cast<uintptr_t>(blob) % 16 != 0 ||
         kh * kw * ic_per_group >= (int64_t(1) << 31)) {
         return NNB200_INVALID_ARGUMENT;
     }

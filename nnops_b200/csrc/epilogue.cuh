@@ -31,8 +31,8 @@ struct I8Epilogue {
     float scale_a_scalar, scale_w_scalar;
     int32_t zp_a_scalar, zp_w_scalar;
     int32_t compensate;     // any zero point may be non-zero: r_a / r_w are valid
-    const int32_t* r_a;     // [m]  sum_k A[m][k]
-    const int32_t* r_w;     // [n]  sum_k W[n][k]
+    const int32_t* r_a;     // [m]  sum_k A[m][k]; may be null when every weight zero point is 0
+    const int32_t* r_w;     // [n]  sum_k W[n][k]; may be null when every activation zero point is 0
     int32_t k;
     float out_scale;
     int32_t out_zp;
@@ -101,7 +101,7 @@ __device__ __forceinline__ I8RowTerms i8_row_terms(const I8Epilogue& e, int64_t 
 {
     I8RowTerms t;
     t.zpa = e.zp_a != nullptr ? e.zp_a[m] : e.zp_a_scalar;
-    t.ra = e.compensate ? e.r_a[m] : 0;
+    t.ra = (e.compensate && e.r_a != nullptr) ? e.r_a[m] : 0;   // null: every weight zero point is 0
     t.s_a = e.scale_a != nullptr ? e.scale_a[m] : e.scale_a_scalar;
     t.row_k = __fdiv_rn(t.s_a, e.out_scale);
     return t;
@@ -144,7 +144,7 @@ __device__ __forceinline__ void i8_store_element(const I8Epilogue& e, const I8Ro
                                                  int32_t raw)
 {
     const int32_t zpw = e.zp_w != nullptr ? e.zp_w[n] : e.zp_w_scalar;
-    const int32_t rw = e.compensate ? e.r_w[n] : 0;
+    const int32_t rw = (e.compensate && e.r_w != nullptr) ? e.r_w[n] : 0;
     const float s_w = e.scale_w != nullptr ? e.scale_w[n] : e.scale_w_scalar;
     const int64_t idx = m * e.ldc + n;
     if (e.out_kind <= NNB200_OUT_U8) {

@@ -256,17 +256,20 @@ int launch_gemm_i8_narrow(const I8Problem& p, const I8Epilogue& ep, const Device
 
 int launch_i8_sums(const I8Problem& p, int32_t* r_a, int32_t* r_w, cudaStream_t stream)
 {
+    // Either destination may be null: that sweep is skipped.
     const uint8_t* a = static_cast<const uint8_t*>(p.a);
     const uint8_t* w = static_cast<const uint8_t*>(p.w);
-    if (p.a_unsigned) {
-        i8_sums_kernel<true><<<static_cast<unsigned>(p.m), 128, 0, stream>>>(a, p.m, p.k, p.a_stride_m, p.a_stride_k, r_a);
-    } else {
-        i8_sums_kernel<false><<<static_cast<unsigned>(p.m), 128, 0, stream>>>(a, p.m, p.k, p.a_stride_m, p.a_stride_k, r_a);
+    if (r_a != nullptr) {
+        if (p.a_unsigned) {
+            i8_sums_kernel<true><<<static_cast<unsigned>(p.m), 128, 0, stream>>>(a, p.m, p.k, p.a_stride_m, p.a_stride_k, r_a);
+        } else {
+            i8_sums_kernel<false><<<static_cast<unsigned>(p.m), 128, 0, stream>>>(a, p.m, p.k, p.a_stride_m, p.a_stride_k, r_a);
+        }
     }
     if (r_w != nullptr) {
         i8_sums_kernel<false><<<static_cast<unsigned>(p.n), 128, 0, stream>>>(w, p.n, p.k, p.w_stride_n, p.w_stride_k, r_w);
     }
-    note_launch(r_w != nullptr ? 2 : 1);
+    note_launch((r_a != nullptr ? 1 : 0) + (r_w != nullptr ? 1 : 0));
     return cuda_status(cudaGetLastError());
 }
 

@@ -380,7 +380,7 @@ gemm_i8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             const bool n_ok = n < n_total;
             // This channel's terms, in registers for the whole tile.
             const int32_t zpw = (n_ok && ep.zp_w != nullptr) ? ep.zp_w[n] : ep.zp_w_scalar;
-            const int32_t rw = (n_ok && ep.compensate) ? ep.r_w[n] : 0;
+            const int32_t rw = (n_ok && ep.compensate && ep.r_w != nullptr) ? ep.r_w[n] : 0;
             const float s_w = (n_ok && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
             int32_t bias_i = 0;
             float bias_f = 0.0f;

@@ -475,7 +475,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
                 cb[j] = b;
-                cr[j] = (in && ep.compensate) ? ep.r_w[n] : 0;
+                cr[j] = (in && ep.compensate && ep.r_w != nullptr) ? ep.r_w[n] : 0;
                 cz[j] = (in && ep.zp_w != nullptr) ? ep.zp_w[n] : ep.zp_w_scalar;
             }
             __syncwarp();
@@ -849,7 +849,7 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     }
                 }
                 cb[j] = b;
-                cr[j] = (in && ep.compensate) ? ep.r_w[n] : 0;
+                cr[j] = (in && ep.compensate && ep.r_w != nullptr) ? ep.r_w[n] : 0;
                 cz[j] = (in && ep.zp_w != nullptr) ? ep.zp_w[n] : ep.zp_w_scalar;
             }
             __syncwarp();
