@@ -47,75 +47,108 @@ struct GatherParams {
     uint32_t pad_byte;   // the activation's zero point as a byte
 };
 
-// One thread per 16-byte piece of the column matrix: 16 consecutive k of one pixel and group.
+// One thread per 16-byte piece of the column matrix (16 consecutive k of one pixel and group);
+// a block takes `rows_per_block` rows (pixel, group) at a time.  What a piece needs to know about
+// its tap (input offset of the tap, first channel) and about its row (image and group base,
+// window origin) is decoded once per block into shared memory, so the per-piece work is one
+// 32-bit division, two table reads, the bounds test, one load and one store.
 // VEC: the 16 k are 16 consecutive channels of one tap (icg % 16 == 0, dense channel axis,
 // 16-byte aligned rows), one 128-bit load; otherwise each byte finds its own tap.
 template <bool VEC>
-__global__ void __launch_bounds__(256) conv_gather_i8_kernel(const GatherParams p)
+__global__ void __launch_bounds__(256) conv_gather_i8_kernel(const GatherParams p, const int rows_per_block)
 {
-    const int64_t chunks_per_row = p.kp >> 4;
-    const int64_t total = static_cast<int64_t>(p.groups) * p.pixels * chunks_per_row;
-    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t row = idx / chunks_per_row;           // g * pixels + pixel
-        const int32_t chunk = static_cast<int32_t>(idx - row * chunks_per_row);
-        const int32_t g = static_cast<int32_t>(row / p.pixels);
-        const int64_t pixel = row - static_cast<int64_t>(g) * p.pixels;
-        const int32_t ow = static_cast<int32_t>(pixel % p.ow);
-        const int64_t t = pixel / p.ow;
-        const int32_t oh = static_cast<int32_t>(t % p.oh);
-        const int32_t n = static_cast<int32_t>(t / p.oh);
-        const int32_t k0 = chunk << 4;
-        const uint8_t* base = p.in + static_cast<int64_t>(n) * p.in_n + static_cast<int64_t>(g) * p.icg * p.in_c;
-        uint4 v;
-        if constexpr (VEC) {
-            const int32_t tap = k0 / p.icg;
-            const int32_t c0 = k0 - tap * p.icg;
-            const int32_t kh = tap / p.kw;
-            const int32_t kw = tap - kh * p.kw;
-            const int32_t ih = oh * p.sh - p.ph + kh * p.dh;
-            const int32_t iw = ow * p.sw - p.pw + kw * p.dw;
-            const uint32_t pad4 = p.pad_byte * 0x01010101u;
-            v = make_uint4(pad4, pad4, pad4, pad4);
-            if (k0 >= p.k) {
-                v = make_uint4(0u, 0u, 0u, 0u);
-            } else if (static_cast<uint32_t>(ih) < static_cast<uint32_t>(p.ih) &&
-                       static_cast<uint32_t>(iw) < static_cast<uint32_t>(p.iw)) {
-                v = __ldg(reinterpret_cast<const uint4*>(base + static_cast<int64_t>(ih) * p.in_h +
-                                                         static_cast<int64_t>(iw) * p.in_w + c0));
+    extern __shared__ __align__(8) uint8_t gather_smem[];
+    const int cpr = p.kp >> 4;   // pieces per row
+    int64_t* row_base = reinterpret_cast<int64_t*>(gather_smem);          // [rows_per_block]
+    int32_t* row_ih0 = reinterpret_cast<int32_t*>(row_base + rows_per_block);
+    int32_t* row_iw0 = row_ih0 + rows_per_block;
+    int32_t* tap_dh = row_iw0 + rows_per_block;                            // [cpr] of the piece's first k
+    int32_t* tap_dw = tap_dh + cpr;
+    int32_t* tap_c = tap_dw + cpr;
+    int32_t* tap_id = tap_c + cpr;                                         // kh * kw_count + kw (byte-wise path)
+
+    for (int c = threadIdx.x; c < cpr; c += blockDim.x) {
+        const int32_t k0 = c << 4;
+        const int32_t tap = k0 / p.icg;
+        const int32_t kh = tap / p.kw;
+        const int32_t kw = tap - kh * p.kw;
+        tap_dh[c] = kh * p.dh;
+        tap_dw[c] = kw * p.dw;
+        tap_c[c] = k0 - tap * p.icg;
+        tap_id[c] = tap;
+    }
+    const int64_t rows_total = static_cast<int64_t>(p.groups) * p.pixels;
+    const int32_t plane = p.oh * p.ow;
+    for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_block; row0 < rows_total;
+         row0 += static_cast<int64_t>(gridDim.x) * rows_per_block) {
+        __syncthreads();   // the previous batch's readers are done (and the tap table is written)
+        for (int r = threadIdx.x; r < rows_per_block; r += blockDim.x) {
+            const int64_t row = row0 + r;
+            if (row < rows_total) {
+                const int32_t g = static_cast<int32_t>(row / p.pixels);
+                const int32_t pixel = static_cast<int32_t>(row - static_cast<int64_t>(g) * p.pixels);
+                const int32_t n = pixel / plane;
+                const int32_t rem = pixel - n * plane;
+                const int32_t oh = rem / p.ow;
+                const int32_t ow = rem - oh * p.ow;
+                row_base[r] = static_cast<int64_t>(n) * p.in_n + static_cast<int64_t>(g) * p.icg * p.in_c;
+                row_ih0[r] = oh * p.sh - p.ph;
+                row_iw0[r] = ow * p.sw - p.pw;
             }
-        } else {
-            uint32_t w[4] = {0u, 0u, 0u, 0u};
-            int32_t k = k0;
-            int32_t tap = k / p.icg;
-            int32_t c = k - tap * p.icg;
-            int32_t kh = tap / p.kw;
-            int32_t kw = tap - kh * p.kw;
-#pragma unroll
-            for (int j = 0; j < 16; ++j, ++k) {
-                uint32_t byte = 0u;
-                if (k < p.k) {
-                    const int32_t ih = oh * p.sh - p.ph + kh * p.dh;
-                    const int32_t iw = ow * p.sw - p.pw + kw * p.dw;
-                    byte = p.pad_byte;
-                    if (static_cast<uint32_t>(ih) < static_cast<uint32_t>(p.ih) &&
-                        static_cast<uint32_t>(iw) < static_cast<uint32_t>(p.iw)) {
-                        byte = base[static_cast<int64_t>(ih) * p.in_h + static_cast<int64_t>(iw) * p.in_w +
-                                    static_cast<int64_t>(c) * p.in_c];
-                    }
-                }
-                w[j >> 2] |= byte << ((j & 3) * 8);
-                if (++c == p.icg) {
-                    c = 0;
-                    if (++kw == p.kw) {
-                        kw = 0;
-                        ++kh;
-                    }
-                }
-            }
-            v = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        reinterpret_cast<uint4*>(p.col)[idx] = v;
+        __syncthreads();
+        const int pieces = rows_per_block * cpr;
+        for (int t = threadIdx.x; t < pieces; t += blockDim.x) {
+            const int r = t / cpr;
+            const int c = t - r * cpr;
+            const int64_t row = row0 + r;
+            if (row >= rows_total) {
+                break;   // rows are ordered by t: every later piece is past the end as well
+            }
+            const uint8_t* base = p.in + row_base[r];
+            uint4 v;
+            if constexpr (VEC) {
+                const int32_t ih = row_ih0[r] + tap_dh[c];
+                const int32_t iw = row_iw0[r] + tap_dw[c];
+                const uint32_t pad4 = p.pad_byte * 0x01010101u;
+                v = make_uint4(pad4, pad4, pad4, pad4);
+                if (static_cast<uint32_t>(ih) < static_cast<uint32_t>(p.ih) &&
+                    static_cast<uint32_t>(iw) < static_cast<uint32_t>(p.iw)) {
+                    v = __ldg(reinterpret_cast<const uint4*>(base + static_cast<int64_t>(ih) * p.in_h +
+                                                             static_cast<int64_t>(iw) * p.in_w + tap_c[c]));
+                }
+            } else {
+                uint32_t w[4] = {0u, 0u, 0u, 0u};
+                int32_t k = c << 4;
+                int32_t ch = tap_c[c];
+                int32_t kh = tap_id[c] / p.kw;
+                int32_t kw = tap_id[c] - kh * p.kw;
+#pragma unroll
+                for (int j = 0; j < 16; ++j, ++k) {
+                    uint32_t byte = 0u;
+                    if (k < p.k) {
+                        const int32_t ih = row_ih0[r] + kh * p.dh;
+                        const int32_t iw = row_iw0[r] + kw * p.dw;
+                        byte = p.pad_byte;
+                        if (static_cast<uint32_t>(ih) < static_cast<uint32_t>(p.ih) &&
+                            static_cast<uint32_t>(iw) < static_cast<uint32_t>(p.iw)) {
+                            byte = base[static_cast<int64_t>(ih) * p.in_h + static_cast<int64_t>(iw) * p.in_w +
+                                        static_cast<int64_t>(ch) * p.in_c];
+                        }
+                    }
+                    w[j >> 2] |= byte << ((j & 3) * 8);
+                    if (++ch == p.icg) {
+                        ch = 0;
+                        if (++kw == p.kw) {
+                            kw = 0;
+                            ++kh;
+                        }
+                    }
+                }
+                v = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            reinterpret_cast<uint4*>(p.col)[row * cpr + c] = v;
+        }
     }
 }
 
@@ -401,6 +434,9 @@ int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* a, void* stream_v)
         return NNB200_OK;
     }
     const bool in_place = pointwise_in_place(a, g);
+    if (!in_place && g.kp / 16 > 2048) {
+        return NNB200_UNSUPPORTED;   // the gather's tap table is sized for K <= 32768
+    }
     ConvScratch plan;
     plan_scratch(a, g, in_place, &plan);
     if (plan.total > 0 && (a->workspace == nullptr || a->workspace_bytes < plan.total ||
@@ -443,18 +479,23 @@ int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* a, void* stream_v)
         p.pad_byte = static_cast<uint32_t>(a->zp_x) & 0xFFu;
         const bool vec = g.icg % 16 == 0 && a->in_stride_c == 1 && a->in_stride_w % 16 == 0 && a->in_stride_h % 16 == 0 &&
                          a->in_stride_n % 16 == 0 && reinterpret_cast<uintptr_t>(a->input) % 16 == 0;
-        const int64_t chunks = g.groups * g.pixels * (g.kp / 16);
         const DeviceInfo* dev = current_device_info();
         if (dev == nullptr) {
             return NNB200_INTERNAL;
         }
-        int64_t blocks = (chunks + 255) / 256;
-        const int64_t cap = static_cast<int64_t>(dev->sm_count) * 32;
+        // About 2048 pieces (eight per thread) per batch of rows, at most 64 rows.
+        const int64_t cpr = g.kp / 16;
+        int rows_per_block = static_cast<int>(2048 / cpr);
+        rows_per_block = rows_per_block < 1 ? 1 : (rows_per_block > 64 ? 64 : rows_per_block);
+        const int64_t rows_total = g.groups * g.pixels;
+        int64_t blocks = (rows_total + rows_per_block - 1) / rows_per_block;
+        const int64_t cap = static_cast<int64_t>(dev->sm_count) * 8;
         blocks = blocks > cap ? cap : blocks;
+        const size_t smem = static_cast<size_t>(rows_per_block) * 16 + static_cast<size_t>(cpr) * 16;
         if (vec) {
-            conv_gather_i8_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+            conv_gather_i8_kernel<true><<<static_cast<unsigned>(blocks), 256, smem, stream>>>(p, rows_per_block);
         } else {
-            conv_gather_i8_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+            conv_gather_i8_kernel<false><<<static_cast<unsigned>(blocks), 256, smem, stream>>>(p, rows_per_block);
         }
         note_launch();
         const int st = cuda_status(cudaGetLastError());

@@ -42,8 +42,16 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kBlockKBytes = 128;  // one 128-byte swizzle row of K per stage
 constexpr int kUmmaK = 32;         // K per tcgen05.mma for 8-bit operands
-constexpr int kNumThreads = 192;   // TMA warp, MMA warp, 4 epilogue warps
-constexpr int kEpilogueThreads = 128;
+// TMA warp, MMA warp, then the epilogue warps: eight (two per TMEM lane quarter, each draining
+// half of the tile's columns) in the plain kernels, four in the sharded form, whose staging
+// tiles are per warp.  One warp per scheduler issues an instruction every ~4 cycles on the
+// epilogue's dependent chains; with four warps a 128 x 256 tile took ~17k cycles to drain, which
+// hid behind the main loop only from K = 4096 up.
+constexpr int kMaxThreads = 320;
+__host__ __device__ constexpr int epilogue_warps(int peers) { return peers ? 4 : 8; }
+__host__ __device__ constexpr int num_threads(int peers) { return (2 + epilogue_warps(peers)) * 32; }
+// Columns drained by the first of the two warps of a lane quarter (whole 32-column chunks).
+__host__ __device__ constexpr int first_half_cols(int bn, int peers) { return peers ? bn : ((bn / 32 + 1) / 2) * 32; }
 
 // TMA descriptors of the output windows the sharded form writes: [0] this GPU's, then the peers'.
 struct alignas(64) PeerMaps {
@@ -65,7 +73,9 @@ struct TileConfig {
                                                 : ((BN > 128) ? 4 : (BN == 128 ? 6 : 8));
     // Two accumulators BN columns apart (one when BN > 256); a power of two of at least that.
     static constexpr int kTmemCols = BN > 128 ? 512 : 2 * BN;
-    static constexpr int kColParamBytes = 4 * 4 * BN * 4;  // 4 epilogue warps x {scale, bias, r_w, zp_w} x BN x 4 B
+    // Per epilogue warp {scale, bias, r_w, zp_w} of the columns it drains, 4 B each.
+    static constexpr int kHalf0 = first_half_cols(BN, PEERS);
+    static constexpr int kColParamBytes = epilogue_warps(PEERS) * 4 * kHalf0 * 4;
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
     // Sharded form (PEERS = 2): two staging tiles of 32 rows x 128 B per epilogue warp, one being
     // filled while the other is being stored.  With few peers (PEERS = 1, used up to three) the
@@ -98,6 +108,77 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
     return c;
 }
 
+// The per-column terms of the epilogue as one epilogue warp stages them in shared memory.
+struct ColTerms {
+    float scale;     // s_w[n], or (s_a / s_out) * s_w[n] when the row factor is folded in
+    int32_t bias;    // int32 bias (integer destinations) or the fp bias as bits; with fold_comp also -zp_a * R_w[n]
+    int32_t rw;      // R_w[n] when compensation is live
+    int32_t zpw;     // zp_w[n]
+};
+
+// fold_comp: a per-tensor activation zero point against weights whose zero points are all 0 -- the
+// only live compensation term is -zp_a * R_w[n], a column constant, and goes into the bias.
+template <int KIND>
+__device__ __forceinline__ ColTerms load_col_terms(const I8Epilogue& ep, int n, int n_total, bool fold_scale,
+                                                   float folded_row_k, bool fold_comp)
+{
+    ColTerms c;
+    const bool in = n < n_total;
+    const float s_w = (in && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
+    c.scale = fold_scale ? __fmul_rn(folded_row_k, s_w) : s_w;
+    int32_t b = 0;
+    if (in && ep.bias != nullptr) {
+        if constexpr (KIND <= NNB200_OUT_U8) {
+            b = static_cast<const int32_t*>(ep.bias)[n];
+        } else if constexpr (KIND == NNB200_OUT_F32) {
+            b = __float_as_int(static_cast<const float*>(ep.bias)[n]);
+        } else {
+            b = __float_as_int(__half2float(static_cast<const __half*>(ep.bias)[n]));
+        }
+    }
+    c.rw = (in && ep.compensate && ep.r_w != nullptr) ? ep.r_w[n] : 0;
+    c.zpw = (in && ep.zp_w != nullptr) ? ep.zp_w[n] : ep.zp_w_scalar;
+    if (fold_comp) {
+        b = static_cast<int32_t>(static_cast<uint32_t>(b) -
+                                 static_cast<uint32_t>(ep.zp_a_scalar) * static_cast<uint32_t>(c.rw));
+    }
+    c.bias = b;
+    return c;
+}
+
+// Four requantised 8-bit values in one word, first value in the low byte.  Same bytes as four
+// i8_requant() calls, with fewer instructions: that routine clamps x = float(v) * req to
+// [lo - zp, hi - zp], rounds half away from zero as trunc(x + copysign(0.5, x)) and adds zp;
+// the bounds are integers, so clamping before the rounding or saturating after it (and after
+// the zero-point add) gives the same value.  Here the 8-bit saturation rides the packing
+// instruction; with a non-zero zero point x is first kept inside +-32000 so that the add cannot
+// overflow, with ZP0 (out_zp == 0, the usual s8 destination) not even that is needed.
+template <bool U8, bool ZP0>
+__device__ __forceinline__ uint32_t requant_pack4(const int32_t (&v)[4], const float (&req)[4], int32_t zp)
+{
+    int32_t r[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        float x = __fmul_rn(__int2float_rn(v[b]), req[b]);
+        if constexpr (ZP0) {
+            // The conversion itself saturates at the int32 range; nothing is added afterwards.
+            r[b] = __float2int_rz(__fadd_rn(x, copysignf(0.5f, x)));
+        } else {
+            x = fminf(fmaxf(x, -32000.0f), 32000.0f);
+            r[b] = __float2int_rz(__fadd_rn(x, copysignf(0.5f, x))) + zp;
+        }
+    }
+    uint32_t hi, out;
+    if constexpr (U8) {
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(r[3]), "r"(r[2]), "r"(0));
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(r[1]), "r"(r[0]), "r"(hi));
+    } else {
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(r[3]), "r"(r[2]), "r"(0));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(r[1]), "r"(r[0]), "r"(hi));
+    }
+    return out;
+}
+
 // Epilogue of one 32-column chunk of one row.  `acc` holds the raw int32 sums of columns
 // n0..n0+31; col_* point at the chunk's staged per-column terms in shared memory.
 template <int KIND>
@@ -105,8 +186,11 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
                                                int64_t m, bool row_ok, int n0, int n_total,
                                                const float* col_scale, const int32_t* col_bias,
                                                const int32_t* col_rw, const int32_t* col_zpw, int vec,
-                                               bool scale_folded = false)
+                                               bool scale_folded = false, bool plain = false)
 {
+    // plain: no per-element compensation terms are needed -- either every zero point is 0, or
+    // the only live term (-zp_a * R_w[n], a per-tensor activation zero point against symmetric
+    // weights) was folded into the staged column bias.
     // vec: bit 0 = the destination takes 16-byte stores, bit 1 = 32-byte stores as well.
     const bool vec_ok = (vec & 1) != 0;
     const bool vec32 = (vec & 2) != 0;
@@ -140,24 +224,30 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
         const float lo = (KIND == NNB200_OUT_S8 ? -128.0f : 0.0f) - zpf;
         const float hi = (KIND == NNB200_OUT_S8 ? 127.0f : 255.0f) - zpf;
         uint32_t packed[8];
-        if (!e.compensate) {
-            // Common case (every zero point 0): no compensation terms to fetch; with a per-tensor
-            // activation scale the staged column scales already carry (s_a / s_out) * s_w[n].
+        if (!e.compensate || plain) {
+            // Common case: with a per-tensor activation scale the staged column scales already
+            // carry (s_a / s_out) * s_w[n].  The column terms are read four at a time.
+            (void)lo;
+            (void)hi;
+            const bool zp0 = e.out_zp == 0;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-                uint32_t word = 0;
+                const int4 b4 = *reinterpret_cast<const int4*>(col_bias + j);
+                const float4 s4 = *reinterpret_cast<const float4*>(col_scale + j);
+                const int32_t bias4[4] = {b4.x, b4.y, b4.z, b4.w};
+                const float scale4[4] = {s4.x, s4.y, s4.z, s4.w};
+                int32_t v[4];
+                float req[4];
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
-                    int32_t v = static_cast<int32_t>(static_cast<uint32_t>(acc[j + b]) +
-                                                     static_cast<uint32_t>(col_bias[j + b]));
-                    if (e.relu && v < 0) {
-                        v = 0;
+                    v[b] = static_cast<int32_t>(static_cast<uint32_t>(acc[j + b]) + static_cast<uint32_t>(bias4[b]));
+                    if (e.relu && v[b] < 0) {
+                        v[b] = 0;
                     }
-                    const float req = scale_folded ? col_scale[j + b] : __fmul_rn(t.row_k, col_scale[j + b]);
-                    const int32_t q = i8_requant(v, req, lo, hi, e.out_zp);
-                    word |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * b);
+                    req[b] = scale_folded ? scale4[b] : __fmul_rn(t.row_k, scale4[b]);
                 }
-                packed[j / 4] = word;
+                packed[j / 4] = zp0 ? requant_pack4<KIND == NNB200_OUT_U8, true>(v, req, 0)
+                                    : requant_pack4<KIND == NNB200_OUT_U8, false>(v, req, e.out_zp);
             }
         } else {
 #pragma unroll
@@ -253,7 +343,7 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
 }
 
 template <int BN, int KIND, int PEERS>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(kMaxThreads, 1)
 gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ PeerMaps peer_maps, const I8Epilogue ep, const int m_total,
                     const int n_total, const int k_total, const uint32_t idesc, const int vec_ok, const int group_m,
@@ -269,7 +359,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // Per-column epilogue terms, one private copy per epilogue warp (no cross-warp barrier).
     uint8_t* peer_stage = smem + kStages * Cfg::kStageBytes;  // 1024-byte aligned (PEERS only)
     int32_t* col_params = reinterpret_cast<int32_t*>(peer_stage + Cfg::kPeerStageBytes);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(col_params + 4 * 4 * BN);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(col_params + Cfg::kColParamBytes / 4);
     uint64_t* empty_bar = full_bar + kStages;
     uint64_t* acc_full_bar = empty_bar + kStages;
     uint64_t* acc_empty_bar = acc_full_bar + 2;
@@ -294,7 +384,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full_bar[a], 1);
-            mbar_init(&acc_empty_bar[a], kEpilogueThreads / 32);
+            mbar_init(&acc_empty_bar[a], epilogue_warps(PEERS));
         }
         *abort_flag = 0;
         mbar_init_fence();
@@ -444,10 +534,22 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // once per column instead of once per element).  The sharded form keeps the plain scales.
         const bool fold_scale = !PEERS && (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) && ep.scale_a == nullptr;
         const float folded_row_k = __fdiv_rn(ep.scale_a_scalar, ep.out_scale);
-        float* cs = reinterpret_cast<float*>(col_params + (warp - 2) * 4 * BN);
-        int32_t* cb = reinterpret_cast<int32_t*>(cs) + BN;
-        int32_t* cr = cb + BN;
-        int32_t* cz = cr + BN;
+        const bool fold_comp = !PEERS && (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) && ep.compensate != 0 &&
+                               ep.zp_a == nullptr && ep.r_a == nullptr;
+        // The next tile's column terms are loaded into registers before this tile is drained,
+        // so their latency is not paid between tiles (up to four per lane and term).
+        constexpr int kTermIters = (Cfg::kHalf0 + 31) / 32;
+        constexpr bool kPrefetch = !PEERS && kTermIters <= 4;
+        ColTerms next_terms[kPrefetch ? kTermIters : 1];
+        // Two warps per lane quarter: the first drains columns [0, kHalf0), the second the rest.
+        constexpr int kHalf0 = Cfg::kHalf0;
+        const int half = PEERS ? 0 : ((warp - 2) >> 2);
+        const int col0 = half * kHalf0;
+        const int ncols = half ? BN - kHalf0 : kHalf0;
+        float* cs = reinterpret_cast<float*>(col_params + (warp - 2) * 4 * kHalf0);
+        int32_t* cb = reinterpret_cast<int32_t*>(cs) + kHalf0;
+        int32_t* cr = cb + kHalf0;
+        int32_t* cz = cr + kHalf0;
         int stage_turn = 0;  // sharded form: which of the warp's two staging tiles is next
         (void)stage_turn;
         int local_tile = 0;
@@ -455,28 +557,23 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
             const int acc = Cfg::kNSplit > 1 ? 0 : (local_tile & 1);
             const uint32_t acc_phase = Cfg::kNSplit > 1 ? (local_tile & 1u) : ((local_tile >> 1) & 1u);
-            const int n_base = tc.n_blk * BN;
+            const int n_base = tc.n_blk * BN + col0;   // first column this warp drains
 
-            // Stage this tile's per-column terms (hidden behind the tile's main loop).
+            // This tile's per-column terms: fetched while the previous tile was being drained
+            // (kPrefetch), or now, hidden behind the tile's main loop.
             __syncwarp();  // previous tile's reads of the staging are done
-            for (int j = lane; j < BN; j += 32) {
-                const int n = n_base + j;
-                const bool in = n < n_total;
-                const float s_w = (in && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
-                cs[j] = fold_scale ? __fmul_rn(folded_row_k, s_w) : s_w;
-                int32_t b = 0;
-                if (in && ep.bias != nullptr) {
-                    if constexpr (KIND <= NNB200_OUT_U8) {
-                        b = static_cast<const int32_t*>(ep.bias)[n];
-                    } else if constexpr (KIND == NNB200_OUT_F32) {
-                        b = __float_as_int(static_cast<const float*>(ep.bias)[n]);
-                    } else {
-                        b = __float_as_int(__half2float(static_cast<const __half*>(ep.bias)[n]));
-                    }
+#pragma unroll
+            for (int i = 0; i < kTermIters; ++i) {
+                const int j = lane + i * 32;
+                if (j < ncols) {
+                    const ColTerms ct = (kPrefetch && local_tile > 0)
+                                            ? next_terms[kPrefetch ? i : 0]
+                                            : load_col_terms<KIND>(ep, n_base + j, n_total, fold_scale, folded_row_k, fold_comp);
+                    cs[j] = ct.scale;
+                    cb[j] = ct.bias;
+                    cr[j] = ct.rw;
+                    cz[j] = ct.zpw;
                 }
-                cb[j] = b;
-                cr[j] = (in && ep.compensate && ep.r_w != nullptr) ? ep.r_w[n] : 0;
-                cz[j] = (in && ep.zp_w != nullptr) ? ep.zp_w[n] : ep.zp_w_scalar;
             }
             __syncwarp();
 
@@ -498,8 +595,20 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             tc_fence_after_sync();
 
+            if constexpr (kPrefetch) {
+                const int next = tile + static_cast<int>(gridDim.x);
+                if (next < num_tiles) {
+                    const int next_base = tile_coord(next, num_m, num_n, group_m).n_blk * BN + col0;
+#pragma unroll
+                    for (int i = 0; i < kTermIters; ++i) {
+                        next_terms[i] = load_col_terms<KIND>(ep, next_base + lane + i * 32, n_total, fold_scale,
+                                                             folded_row_k, fold_comp);
+                    }
+                }
+            }
+
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(acc * BN);
+                                   static_cast<uint32_t>(acc * BN + col0);
             if constexpr (PEERS && (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8)) {
                 // Sharded write-back: 128 columns at a time through a per-warp staging tile.
                 const float zpf = static_cast<float>(ep.out_zp);
@@ -583,16 +692,16 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             } else {
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < ncols / 32; ++c) {
                     const int n0 = n_base + c * 32;
                     if (n0 >= n_total) {
-                        break;  // uniform across the CTA's epilogue warps
+                        break;  // uniform across the warp
                     }
                     uint32_t v[32];
                     tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                     tmem_ld_wait();
                     epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
-                                         cz + c * 32, vec_ok, fold_scale);
+                                         cz + c * 32, vec_ok, fold_scale, fold_comp);
                 }
             }
             // Accumulator drained: hand it back to the MMA warp.
@@ -647,7 +756,8 @@ struct PairTileConfig {
     static constexpr int kATileBytes = kBlockM * kBlockKBytes;   // this CTA's 128 rows of A
     static constexpr int kBTileBytes = (BN / 2) * kBlockKBytes;  // this CTA's half of the W rows
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
-    static constexpr int kColParamBytes = 4 * 4 * BN * 4;
+    static constexpr int kHalf0 = first_half_cols(BN, 0);
+    static constexpr int kColParamBytes = epilogue_warps(0) * 4 * kHalf0 * 4;
     static constexpr int kStages = (208 * 1024 - kColParamBytes) / kStageBytes;  // 256: 6, 224: 6, 192: 7
     static constexpr int kTmemCols = 512;
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
@@ -655,7 +765,7 @@ struct PairTileConfig {
 };
 
 template <int BN, int KIND, int SUB, bool MC>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMaxThreads, 1)
 gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const I8Epilogue ep, const int m_total, const int n_total, const int k_total,
                          const uint32_t idesc, const int vec_ok, const int group_m, int32_t* error_word)
@@ -671,7 +781,7 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_base = smem;
     int32_t* col_params = reinterpret_cast<int32_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(col_params + 4 * 4 * BN);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(col_params + Cfg::kColParamBytes / 4);
     uint64_t* empty_bar = full_bar + Cfg::kStages;
     uint64_t* acc_full_bar = empty_bar + Cfg::kStages;
     uint64_t* acc_empty_bar = acc_full_bar + 2;
@@ -695,7 +805,7 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full_bar[a], 1);
-            mbar_init(&acc_empty_bar[a], 2 * kEpilogueThreads / 32);  // the leader's: 4 warps of each CTA
+            mbar_init(&acc_empty_bar[a], 2 * epilogue_warps(0));  // the leader's: the epilogue warps of both CTAs
         }
         *abort_flag = 0;
         mbar_init_fence();
@@ -820,37 +930,40 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int quarter = warp & 3;
         const bool fold_scale = (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) && ep.scale_a == nullptr;
         const float folded_row_k = __fdiv_rn(ep.scale_a_scalar, ep.out_scale);
-        float* cs = reinterpret_cast<float*>(col_params + (warp - 2) * 4 * BN);
-        int32_t* cb = reinterpret_cast<int32_t*>(cs) + BN;
-        int32_t* cr = cb + BN;
-        int32_t* cz = cr + BN;
+        const bool fold_comp = (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) && ep.compensate != 0 &&
+                               ep.zp_a == nullptr && ep.r_a == nullptr;
+        constexpr int kTermIters = (Cfg::kHalf0 + 31) / 32;   // 4 for 256-wide tiles
+        ColTerms next_terms[kTermIters];
+        constexpr int kHalf0 = Cfg::kHalf0;
+        const int half = (warp - 2) >> 2;   // two warps per lane quarter, half of the columns each
+        const int col0 = half * kHalf0;
+        const int ncols = half ? BN - kHalf0 : kHalf0;
+        float* cs = reinterpret_cast<float*>(col_params + (warp - 2) * 4 * kHalf0);
+        int32_t* cb = reinterpret_cast<int32_t*>(cs) + kHalf0;
+        int32_t* cr = cb + kHalf0;
+        int32_t* cz = cr + kHalf0;
         int local_tile = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
             const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
             const int acc = local_tile & 1;
             const uint32_t acc_phase = (local_tile >> 1) & 1u;
-            const int n_base = tc.n_blk * BN;
+            const int n_base = tc.n_blk * BN + col0;   // first column this warp drains
 
-            // Stage this tile's per-column terms (hidden behind the tile's main loop).
+            // This tile's per-column terms: fetched while the previous tile was being drained, or
+            // (first tile) now, hidden behind the tile's main loop.
             __syncwarp();
-            for (int j = lane; j < BN; j += 32) {
-                const int n = n_base + j;
-                const bool in = n < n_total;
-                const float s_w = (in && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
-                cs[j] = fold_scale ? __fmul_rn(folded_row_k, s_w) : s_w;
-                int32_t b = 0;
-                if (in && ep.bias != nullptr) {
-                    if constexpr (KIND <= NNB200_OUT_U8) {
-                        b = static_cast<const int32_t*>(ep.bias)[n];
-                    } else if constexpr (KIND == NNB200_OUT_F32) {
-                        b = __float_as_int(static_cast<const float*>(ep.bias)[n]);
-                    } else {
-                        b = __float_as_int(__half2float(static_cast<const __half*>(ep.bias)[n]));
-                    }
+#pragma unroll
+            for (int i = 0; i < kTermIters; ++i) {
+                const int j = lane + i * 32;
+                if (j < ncols) {
+                    const ColTerms ct = local_tile > 0 ? next_terms[i]
+                                                       : load_col_terms<KIND>(ep, n_base + j, n_total, fold_scale,
+                                                                              folded_row_k, fold_comp);
+                    cs[j] = ct.scale;
+                    cb[j] = ct.bias;
+                    cr[j] = ct.rw;
+                    cz[j] = ct.zpw;
                 }
-                cb[j] = b;
-                cr[j] = (in && ep.compensate && ep.r_w != nullptr) ? ep.r_w[n] : 0;
-                cz[j] = (in && ep.zp_w != nullptr) ? ep.zp_w[n] : ep.zp_w_scalar;
             }
             __syncwarp();
 
@@ -877,19 +990,32 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
             tc_fence_after_sync();
 
+            {
+                // The next tile's column terms, in flight while this tile is drained.
+                const int next = tile + num_pairs;
+                if (next < num_tiles) {
+                    const int next_base = tile_coord(next, num_m, num_n, group_m).n_blk * BN + col0;
+#pragma unroll
+                    for (int i = 0; i < kTermIters; ++i) {
+                        next_terms[i] = load_col_terms<KIND>(ep, next_base + lane + i * 32, n_total, fold_scale,
+                                                             folded_row_k, fold_comp);
+                    }
+                }
+            }
+
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>(acc * 256);
+                                   static_cast<uint32_t>(acc * 256 + col0);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < ncols / 32; ++c) {
                 const int n0 = n_base + c * 32;
                 if (n0 >= n_total) {
-                    break;  // uniform across the CTA's epilogue warps
+                    break;  // uniform across the warp
                 }
                 uint32_t v[32];
                 tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                 tmem_ld_wait();
                 epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
-                                     cz + c * 32, vec_ok, fold_scale);
+                                     cz + c * 32, vec_ok, fold_scale, fold_comp);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -925,7 +1051,7 @@ int launch_pair_variant(const I8Problem& p, const I8Epilogue& ep, int m, int n, 
         if (attr_err[dev.device] == cudaSuccess) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(static_cast<unsigned>(dev.sm_count & ~1));
-            cfg.blockDim = dim3(kNumThreads);
+            cfg.blockDim = dim3(num_threads(0));
             cfg.dynamicSmemBytes = Cfg::kSmemBytes;
             int count = 0;
             if (cudaOccupancyMaxActiveClusters(&count, kernel, &cfg) == cudaSuccess) {
@@ -950,7 +1076,7 @@ int launch_pair_variant(const I8Problem& p, const I8Epilogue& ep, int m, int n, 
     const int pairs = num_tiles < max_pairs[dev.device] ? num_tiles : max_pairs[dev.device];
     int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(2 * kBlockM) * (k > 0 ? k : 1)));
     group_m = group_m < 2 ? 2 : group_m;
-    kernel<<<2 * pairs, kNumThreads, Cfg::kSmemBytes, stream>>>(map_a, map_w, ep, m, n, k,
+    kernel<<<2 * pairs, num_threads(0), Cfg::kSmemBytes, stream>>>(map_a, map_w, ep, m, n, k,
                                                                umma_idesc(2, a_fmt, 1, 2 * kBlockM, BN), vec_ok, group_m,
                                                                dev.error_word);
     note_launch();
@@ -1007,7 +1133,7 @@ int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8E
     if (knob(NNB200_KNOB_GROUP_M) > 0) {
         group_m = knob(NNB200_KNOB_GROUP_M);
     }
-    kernel<<<grid, kNumThreads, kSmem, stream>>>(map_a, map_w, maps, ep, m, n, k, idesc, vec_ok, group_m,
+    kernel<<<grid, num_threads(PEERS), kSmem, stream>>>(map_a, map_w, maps, ep, m, n, k, idesc, vec_ok, group_m,
                                                  dev.error_word);
     note_launch();
     return cuda_status(cudaGetLastError());

@@ -80,10 +80,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
+// The same probe, allowed to suspend the thread in hardware for up to `ns` nanoseconds while the
+// phase is incomplete (it still returns as soon as the phase completes).  Used inside the wait
+// loops: a role that polls without the hint takes issue slots from the epilogue warps that share
+// its scheduler.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Upper bound on any single pipeline wait, in SM clock cycles (~2 s at 2 GHz).  A healthy
 // kernel waits microseconds; the bound only exists so a mis-programmed pipeline returns an
 // error instead of hanging the GPU.
 constexpr long long kWaitLimitCycles = 4'000'000'000LL;
+// How long one probe inside a wait loop may keep the thread suspended.
+constexpr uint32_t kWaitSuspendNs = 20000;
 
 // Wait for `parity` on `bar`.  Returns false if the wait ran out or another role already
 // aborted (`*abort_flag` != 0); on running out it raises the flag itself.
@@ -96,10 +117,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     const long long t0 = clock64();
     uint32_t spins = 0;
     for (;;) {
-        if (mbar_try_wait(bar, parity)) {
+        if (mbar_try_wait_suspend(bar, parity, kWaitSuspendNs)) {
             return true;
         }
-        if ((++spins & 0xFFu) == 0) {
+        if ((++spins & 0xFu) == 0) {
             if (*abort_flag != 0) {
                 return false;
             }

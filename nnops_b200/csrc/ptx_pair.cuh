@@ -53,6 +53,22 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
     return ok != 0;
 }
 
+// The same with a suspend-time hint (see mbar_try_wait_suspend).
+__device__ __forceinline__ bool mbar_try_wait_cluster_suspend(uint64_t* bar, uint32_t parity, uint32_t ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait, as mbar_wait, with the cluster-scope probe.
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag)
 {
@@ -62,10 +78,10 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
     const long long t0 = clock64();
     uint32_t spins = 0;
     for (;;) {
-        if (mbar_try_wait_cluster(bar, parity)) {
+        if (mbar_try_wait_cluster_suspend(bar, parity, kWaitSuspendNs)) {
             return true;
         }
-        if ((++spins & 0xFFu) == 0) {
+        if ((++spins & 0xFu) == 0) {
             if (*abort_flag != 0) {
                 return false;
             }
