@@ -585,6 +585,17 @@ def run_kernel_only(args):
         for _ in range(3):
             ops.quantize_linear(x, scale, zp, out=q)
             ops.dequantize_linear(q, scale, zp, out=y)
+    elif args.kernel_only == "conv":
+        # --shape N HW C: batch, plane edge and channel count (in = out) of a 3x3, padding-1 layer.
+        n_img, hw, ch = m, n, k
+        x = torch.from_numpy(rng.integers(0, 256, (n_img, hw, hw, ch), dtype=np.uint8)).to(dev)
+        w = torch.from_numpy(rng.integers(-127, 128, (3, 3, ch, ch), dtype=np.int8)).to(dev)
+        sw = torch.from_numpy(rng.uniform(0.005, 0.015, ch).astype(np.float32)).to(dev)
+        bias = torch.from_numpy(rng.integers(-1000, 1001, ch).astype(np.int32)).to(dev)
+        out = torch.empty((n_img, hw, hw, ch), dtype=torch.int8, device=dev)
+        for _ in range(3):
+            ops.conv2d_i8(x, w, padding=(1, 1), out_kind="s8", out=out, bias=bias, relu=True, scale_x=0.02, zp_x=128,
+                          scale_w=sw, out_scale=0.05)
     elif args.kernel_only == "i8":
         a = torch.from_numpy(synth.s8_uniform(rng, (m, k))).to(dev)
         w = torch.from_numpy(synth.s8_uniform(rng, (n, k))).to(dev)
@@ -616,12 +627,13 @@ def main():
                     help="N > 1: the GEMM epilogue stores every tile into every rank's output with one peer store per "
                          "rank (fused, the fastest measured), or once through an NVSwitch multicast mapping (multicast; "
                          "falls back to fused where the fabric has none), or NCCL all-gather + interleave kernel (nccl)")
-    ap.add_argument("--kernel-only", choices=["i8", "gemv", "q4gemm", "q4gemm2", "quant"],
+    ap.add_argument("--kernel-only", choices=["i8", "gemv", "q4gemm", "q4gemm2", "quant", "conv"],
                     help="profiling aid: 3 launches of one kernel (q4gemm = fused form, q4gemm2 = two-pass form, "
-                         "quant = QuantizeLinear then DequantizeLinear of an [M, K] f32 tensor, per token; N unused)")
+                         "quant = QuantizeLinear then DequantizeLinear of an [M, K] f32 tensor, per token; N unused; "
+                         "conv = int8 3x3 Conv2D, --shape BATCH EDGE CHANNELS)")
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), default=[4096, 28672, 8192])
     ap.add_argument("--knob", action="append", metavar="NAME=VALUE",
-                    help="with --kernel-only: set a measurement switch first (e.g. i8_pair=1 for the CTA-pair form)")
+                    help="set a measurement switch of the library first (e.g. i8_pair=0 for the single-CTA GEMM)")
     args = ap.parse_args()
     if args.kernel_only:
         run_kernel_only(args)
@@ -647,6 +659,9 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     build.build()
+    for item in args.knob or []:   # measurement switches, every rank
+        name, _, value = item.partition("=")
+        capi.set_knob(name.lower(), int(value))
     lib = capi.lib()
     peaks = read_peaks()
 

@@ -68,7 +68,7 @@ struct TileConfig {
     static constexpr int kBTileBytes = BN * kBlockKBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     // Ring depth: as many stages as fit beside the epilogue staging in ~200 KB.
-    static constexpr int kStages = PEERS ? ((BN == 256) ? (PEERS == 1 ? 4 : 3) : (BN == 224 ? 4 : 5))
+    static constexpr int kStages = PEERS ? ((BN == 256) ? (PEERS == 1 ? 4 : 3) : (BN == 224 ? 4 : (PEERS == 3 ? 4 : 5)))
                                    : (BN > 256) ? (BN > 384 ? 2 : 3)
                                                 : ((BN > 128) ? 4 : (BN == 128 ? 6 : 8));
     // Two accumulators BN columns apart (one when BN > 256); a power of two of at least that.
@@ -81,8 +81,11 @@ struct TileConfig {
     // filled while the other is being stored.  With few peers (PEERS = 1, used up to three) the
     // stores are not what saturates first and the main loop decides: one staging tile per warp,
     // and the shared memory that frees keeps the ring at four stages.
-    static constexpr int kStageTiles = PEERS == 1 ? 1 : 2;
-    static constexpr int kPeerStageBytes = PEERS ? 4 * kStageTiles * 32 * 128 : 0;
+    // PEERS = 3 (measurement): one staging tile of 32 rows x 256 B per warp, not swizzled, stored
+    // with 256-byte rows per bulk store (half as many link packets per byte, if the link cares).
+    static constexpr int kStageTiles = PEERS == 2 ? 2 : 1;
+    static constexpr int kStageGroupCols = PEERS == 3 ? 256 : 128;   // columns per staging tile
+    static constexpr int kPeerStageBytes = PEERS ? 4 * kStageTiles * 32 * kStageGroupCols : 0;
     static constexpr int kSmemBytes =
         1024 /*alignment slack*/ + kStages * kStageBytes + kPeerStageBytes + kColParamBytes + kBarrierBytes;
 };
@@ -617,24 +620,27 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int row0 = tc.m_blk * kBlockM + quarter * 32;
                 const int num_dst = 1 + ep.num_peers;
                 const bool multicast = ep.mc_out != nullptr;
+                constexpr int kGroupCols = Cfg::kStageGroupCols;       // 128 (swizzled tile) or 256 (plain tile)
+                constexpr int kGroupChunks = kGroupCols / 32;
 #pragma unroll 1
-                for (int c4 = 0; c4 < (BN + 127) / 128; ++c4) {
-                    const int n128 = n_base + c4 * 128;
+                for (int c4 = 0; c4 < (BN + kGroupCols - 1) / kGroupCols; ++c4) {
+                    const int n128 = n_base + c4 * kGroupCols;
                     if (n128 >= n_total) {
                         break;  // uniform across the warp
                     }
                     // Two staging tiles per warp, used alternately: before refilling one, its
                     // previous bulk stores must have finished READING it (they may still be in flight
                     // on the wire).  Only lane 0 issues bulk stores, so only lane 0 has groups to wait on.
-                    uint8_t* stage = peer_stage + ((warp - 2) * Cfg::kStageTiles + (stage_turn % Cfg::kStageTiles)) * (32 * 128);
+                    uint8_t* stage = peer_stage + ((warp - 2) * Cfg::kStageTiles + (stage_turn % Cfg::kStageTiles)) *
+                                                      (32 * kGroupCols);
                     ++stage_turn;
                     if (lane == 0) {
                         bulk_wait_group_read<Cfg::kStageTiles - 1>();
                     }
                     __syncwarp();
 #pragma unroll 1
-                    for (int cc = 0; cc < 4; ++cc) {
-                        const int c = c4 * 4 + cc;
+                    for (int cc = 0; cc < kGroupChunks; ++cc) {
+                        const int c = c4 * kGroupChunks + cc;
                         if (c >= BN / 32) {
                             break;  // a 224-wide tile ends inside its second 128-column group
                         }
@@ -655,12 +661,13 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             }
                             packed[j / 4] = word;
                         }
-                        // This lane's row in the 128-byte-swizzled tile: 16-byte pieces 2cc and 2cc+1.
-                        uint4* srow = reinterpret_cast<uint4*>(stage + lane * 128);
-                        srow[(2 * cc) ^ (lane & 7)] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        srow[(2 * cc + 1) ^ (lane & 7)] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        // This lane's row of the tile: 16-byte pieces 2cc and 2cc+1 (swizzled in the 128-byte form).
+                        uint4* srow = reinterpret_cast<uint4*>(stage + lane * kGroupCols);
+                        const int sw = PEERS == 3 ? 0 : (lane & 7);
+                        srow[(2 * cc) ^ sw] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        srow[(2 * cc + 1) ^ sw] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                     }
-                    if (multicast) {
+                    if (PEERS != 3 && multicast) {
                         // One store per tile for all ranks: the staged rows go out as 16-byte
                         // multimem stores, eight lanes covering one 128-byte row, four rows per
                         // pass, and the switch replicates them into every rank's copy.
@@ -1107,11 +1114,12 @@ int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8E
     PeerMaps maps;
     std::memset(&maps, 0, sizeof(maps));
     if constexpr (PEERS) {
-        // Output windows as 2-D byte tensors [m][n] with the caller's pitch; 128 x 32 boxes.
+        // Output windows as 2-D byte tensors [m][n] with the caller's pitch; 128 x 32 boxes
+        // (128-byte swizzle), or 256 x 32 plain boxes in the wide-row form.
         for (int d = 0; d <= ep.num_peers; ++d) {
             const void* base = d == 0 ? ep.out : ep.peer_out[d - 1];
             if (!make_tma_2d(&maps.m[d], base, 1, static_cast<uint64_t>(n), static_cast<uint64_t>(m),
-                             static_cast<uint64_t>(ep.ldc), 128, 32)) {
+                             static_cast<uint64_t>(ep.ldc), Cfg::kStageGroupCols, 32, PEERS != 3)) {
                 return NNB200_INTERNAL;
             }
         }
@@ -1153,6 +1161,17 @@ int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, cons
         bool single = ep.num_peers <= 3;
         if (const int staging = knob(NNB200_KNOB_I8_PEER_STAGING); staging == 1 || staging == 2) {
             single = staging == 1;
+        }
+        if constexpr (BN == 256) {
+            // knob I8_PEER_STAGING = 3: 256-byte rows per bulk store (measurement).
+            if (knob(NNB200_KNOB_I8_PEER_STAGING) == 3 && ep.mc_out == nullptr) {
+                if (kind == NNB200_OUT_S8) {
+                    return launch_variant<BN, NNB200_OUT_S8, 3>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+                }
+                if (kind == NNB200_OUT_U8) {
+                    return launch_variant<BN, NNB200_OUT_U8, 3>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
+                }
+            }
         }
         if constexpr (BN == 256 || BN == 128) {
             if (kind == NNB200_OUT_S8) {
