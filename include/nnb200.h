@@ -267,7 +267,8 @@ NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double
  * INT32_MIN for an unknown knob).
  *   GROUP_M          raster group (m-blocks) of the int8 tensor-core GEMM
  *   I8_BN            force its tile width: 64, 128, 192, 224, 256, 320, 384, 448 or 512
- *   I8_PAIR          0 single-CTA form only, 2 CTA-pair form or an error (default: pair form where it applies);
+ *   I8_PAIR          0 single-CTA form only, 2 CTA-pair form whatever the shape, or an error (default: pair form
+ *                    where it pays);
  *                    1 / 3 earlier pair forms kept for comparison (one k-block per barrier slot / two commits)
  *   I8_PEER_STAGING  1 / 2 staging tiles per epilogue warp in the sharded write-back
  *   F16_PAIR         as I8_PAIR for the dense f16 GEMM of the Q4_1 two-pass form

@@ -97,13 +97,20 @@ __global__ void __launch_bounds__(256) conv_gather_i8_kernel(const GatherParams 
             }
         }
         __syncthreads();
-        const int pieces = rows_per_block * cpr;
-        for (int t = threadIdx.x; t < pieces; t += blockDim.x) {
-            const int r = t / cpr;
-            const int c = t - r * cpr;
+        // A warp walks the pieces of one row at a time (lanes = consecutive pieces: coalesced and
+        // no division); rows shorter than a warp share one, `rows_per_warp` at a time.
+        const int lane = threadIdx.x & 31;
+        const int warp = threadIdx.x >> 5;
+        const int rows_per_warp = cpr >= 32 ? 1 : 32 / cpr;
+        const int sub_row = cpr >= 32 ? 0 : lane / cpr;
+        const int c_first = cpr >= 32 ? lane : lane - sub_row * cpr;
+        const int c_step = cpr >= 32 ? 32 : cpr;   // short rows: one piece per lane, the loop below runs once
+        for (int r = warp * rows_per_warp + sub_row; r < rows_per_block && sub_row < rows_per_warp;
+             r += 8 * rows_per_warp) {
+          for (int c = c_first; c < cpr; c += c_step) {
             const int64_t row = row0 + r;
             if (row >= rows_total) {
-                break;   // rows are ordered by t: every later piece is past the end as well
+                break;
             }
             const uint8_t* base = p.in + row_base[r];
             uint4 v;
@@ -148,6 +155,7 @@ __global__ void __launch_bounds__(256) conv_gather_i8_kernel(const GatherParams 
                 v = make_uint4(w[0], w[1], w[2], w[3]);
             }
             reinterpret_cast<uint4*>(p.col)[row * cpr + c] = v;
+          }
         }
     }
 }

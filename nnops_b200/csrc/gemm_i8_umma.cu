@@ -68,7 +68,7 @@ struct TileConfig {
     static constexpr int kBTileBytes = BN * kBlockKBytes;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     // Ring depth: as many stages as fit beside the epilogue staging in ~200 KB.
-    static constexpr int kStages = PEERS ? ((BN == 256) ? (PEERS == 1 ? 4 : 3) : (BN == 224 ? 4 : (PEERS == 3 ? 4 : 5)))
+    static constexpr int kStages = PEERS ? ((BN == 256) ? (PEERS == 1 ? 4 : 3) : (BN == 224 ? 4 : 5))
                                    : (BN > 256) ? (BN > 384 ? 2 : 3)
                                                 : ((BN > 128) ? 4 : (BN == 128 ? 6 : 8));
     // Two accumulators BN columns apart (one when BN > 256); a power of two of at least that.
@@ -81,10 +81,10 @@ struct TileConfig {
     // filled while the other is being stored.  With few peers (PEERS = 1, used up to three) the
     // stores are not what saturates first and the main loop decides: one staging tile per warp,
     // and the shared memory that frees keeps the ring at four stages.
-    // PEERS = 3 (measurement): one staging tile of 32 rows x 256 B per warp, not swizzled, stored
-    // with 256-byte rows per bulk store (half as many link packets per byte, if the link cares).
+    // (Rows of 256 bytes per bulk store from a plain 32 x 256 tile were tried: no change on four
+    // GPUs at the same ring depth.)
     static constexpr int kStageTiles = PEERS == 2 ? 2 : 1;
-    static constexpr int kStageGroupCols = PEERS == 3 ? 256 : 128;   // columns per staging tile
+    static constexpr int kStageGroupCols = 128;   // columns per staging tile
     static constexpr int kPeerStageBytes = PEERS ? 4 * kStageTiles * 32 * kStageGroupCols : 0;
     static constexpr int kSmemBytes =
         1024 /*alignment slack*/ + kStages * kStageBytes + kPeerStageBytes + kColParamBytes + kBarrierBytes;
@@ -663,11 +663,11 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                         // This lane's row of the tile: 16-byte pieces 2cc and 2cc+1 (swizzled in the 128-byte form).
                         uint4* srow = reinterpret_cast<uint4*>(stage + lane * kGroupCols);
-                        const int sw = PEERS == 3 ? 0 : (lane & 7);
+                        const int sw = lane & 7;
                         srow[(2 * cc) ^ sw] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                         srow[(2 * cc + 1) ^ sw] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                     }
-                    if (PEERS != 3 && multicast) {
+                    if (multicast) {
                         // One store per tile for all ranks: the staged rows go out as 16-byte
                         // multimem stores, eight lanes covering one 128-byte row, four rows per
                         // pass, and the switch replicates them into every rank's copy.
@@ -1114,12 +1114,11 @@ int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8E
     PeerMaps maps;
     std::memset(&maps, 0, sizeof(maps));
     if constexpr (PEERS) {
-        // Output windows as 2-D byte tensors [m][n] with the caller's pitch; 128 x 32 boxes
-        // (128-byte swizzle), or 256 x 32 plain boxes in the wide-row form.
+        // Output windows as 2-D byte tensors [m][n] with the caller's pitch; 128 x 32 boxes.
         for (int d = 0; d <= ep.num_peers; ++d) {
             const void* base = d == 0 ? ep.out : ep.peer_out[d - 1];
             if (!make_tma_2d(&maps.m[d], base, 1, static_cast<uint64_t>(n), static_cast<uint64_t>(m),
-                             static_cast<uint64_t>(ep.ldc), Cfg::kStageGroupCols, 32, PEERS != 3)) {
+                             static_cast<uint64_t>(ep.ldc), Cfg::kStageGroupCols, 32)) {
                 return NNB200_INTERNAL;
             }
         }
@@ -1155,23 +1154,13 @@ int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, cons
         // Sharded write-back exists for the 8-bit destinations: 256- and 128-wide tiles, and --
         // multicast stores only, whose pieces need not be whole 128-byte boxes -- 224-wide ones.
         // knob I8_PEER_STAGING = 1 / 2 forces the staging depth (measurement aid).
-        // Up to three peers (measured at one and three: 0.380 -> 0.346 and 0.262 -> 0.237 ms per step) the
-        // deeper ring pays; from four on the stores dominate and the measured form, two staging tiles, stays.
-        // Multicast stores leave the SM as ordinary stores: one staging tile per warp is all they need.
-        bool single = ep.num_peers <= 3;
+        // One staging tile per warp and the fourth ring stage it leaves room for: measured faster than
+        // two tiles and three stages at every size (per step, one / three / seven peers:
+        // 0.380 -> 0.346, 0.262 -> 0.237 and 0.255 -> 0.238 ms).  Multicast stores leave the SM as
+        // ordinary stores: one staging tile per warp is all they need.
+        bool single = true;
         if (const int staging = knob(NNB200_KNOB_I8_PEER_STAGING); staging == 1 || staging == 2) {
             single = staging == 1;
-        }
-        if constexpr (BN == 256) {
-            // knob I8_PEER_STAGING = 3: 256-byte rows per bulk store (measurement).
-            if (knob(NNB200_KNOB_I8_PEER_STAGING) == 3 && ep.mc_out == nullptr) {
-                if (kind == NNB200_OUT_S8) {
-                    return launch_variant<BN, NNB200_OUT_S8, 3>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
-                }
-                if (kind == NNB200_OUT_U8) {
-                    return launch_variant<BN, NNB200_OUT_U8, 3>(map_a, map_w, ep, m, n, k, idesc, vec_ok, dev, stream);
-                }
-            }
         }
         if constexpr (BN == 256 || BN == 128) {
             if (kind == NNB200_OUT_S8) {
@@ -1325,17 +1314,25 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceIn
 
     const uint32_t a_fmt = p.a_unsigned ? 0u : 1u;
 
-    // CTA-pair form for tall problems with at least a full wave of 256-row tiles: the default there.
-    // Knob I8_PAIR: 0 = never; 2 = the pair form or an error; 1 / 3 = older forms kept for
-    // comparison (one k-block per barrier slot; two k-blocks but one commit per destination CTA).
+    // CTA-pair form for tall problems with at least a full wave of 256-row tiles and a K of 2048 or
+    // more (below that the per-tile hand-overs of the pair cost more than its main loop saves:
+    // measured 103 against 116 us at K = 256, 68 against 71 at 1024, 64 against 60 at 2304).
+    // Knob I8_PAIR: 0 = never; 2 = the pair form whatever the shape, or an error; 1 / 3 = older
+    // forms kept for comparison (one k-block per barrier slot; two k-blocks but one commit per
+    // destination CTA), forced likewise.
     {
         const int pair_knob = knob(NNB200_KNOB_I8_PAIR);
         const int64_t pair_tiles = static_cast<int64_t>((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + 255) / 256);
-        if (pair_knob != 0 && !sharded && !a_mn && !w_mn && m >= 4 * kBlockM && pair_tiles >= dev.sm_count / 2 && bn == 256) {
+        const bool forced = pair_knob >= 1 && pair_knob <= 3;   // 1, 2, 3: a pair form or an error
+        if (forced && (sharded || a_mn || w_mn)) {
+            return NNB200_UNSUPPORTED;
+        }
+        if (pair_knob != 0 && !sharded && !a_mn && !w_mn &&
+            (forced || (m >= 4 * kBlockM && k >= 2048 && pair_tiles >= dev.sm_count / 2 && bn == 256))) {
             const int st = pair_knob == 1   ? launch_pair_bn<256, 1, false>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
                            : pair_knob == 3 ? launch_pair_bn<256, 2, false>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
                                             : launch_pair_bn<256, 2, true>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
-            if (st != NNB200_UNSUPPORTED || pair_knob == 2) {
+            if (st != NNB200_UNSUPPORTED || forced) {
                 return st;
             }
         }
