@@ -44,6 +44,10 @@ struct I8Epilogue {
     // The same window inside a multicast mapping bound to every rank's copy (this rank's too):
     // tiles are stored once with multimem.st and replicated by the switch; peer_out is unused.
     void* mc_out;
+    // Set by the tensor-core launcher, not by callers: this many entries of peer_out are written
+    // with plain 32-byte stores from the ordinary epilogue (two-rank shards on the CTA-pair
+    // kernel), and num_peers is 0.
+    int32_t direct_peers;
 };
 
 __device__ __forceinline__ float act_apply(int32_t act, float alpha, float beta, float x)

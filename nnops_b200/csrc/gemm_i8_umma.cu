@@ -274,6 +274,12 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
         if (full && vec32) {
             // The lane's 32 values are exactly one 32-byte sector of its row.
             st_global_32(dst, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
+            // Two-rank shards: the same sector into the other rank's copy, over the link (the
+            // launcher has checked that every chunk is full and every pointer 32-byte aligned).
+            for (int d = 0; d < e.direct_peers; ++d) {
+                st_global_32(static_cast<uint8_t*>(e.peer_out[d]) + m * e.ldc + n0, packed[0], packed[1], packed[2],
+                             packed[3], packed[4], packed[5], packed[6], packed[7]);
+            }
         } else if (full && vec_ok) {
             *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             *reinterpret_cast<uint4*>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
@@ -718,6 +724,9 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 mbar_arrive(&acc_empty_bar[acc]);
             }
         }
+        if (!PEERS && ep.direct_peers > 0) {
+            __threadfence_system();  // this warp's stores into the peer's copy are performed before the kernel completes
+        }
         if constexpr (PEERS) {
             if (ep.mc_out != nullptr) {
                 __threadfence_system();  // this warp's multicast stores are performed before the kernel completes
@@ -1030,6 +1039,9 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty_bar[acc]), 0));
             }
         }
+        if (ep.direct_peers > 0) {
+            __threadfence_system();  // stores into the other rank's copy are performed before the kernel completes
+        }
     }
 
     // ---------------- teardown ----------------
@@ -1216,11 +1228,27 @@ bool umma_i8_supported(const I8Problem& p)
     return operand_ok(p.a, p.a_stride_m, p.a_stride_k, p.m, p.k) && operand_ok(p.w, p.w_stride_n, p.w_stride_k, p.n, p.k);
 }
 
-int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream)
+int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep_in, const DeviceInfo& dev, cudaStream_t stream)
 {
     const int m = static_cast<int>(p.m);
     const int n = static_cast<int>(p.n);
     const int k = static_cast<int>(p.k);
+
+    // A shard with ONE peer (two ranks) is bound by its GEMM, not by the link: it runs the
+    // ordinary kernels -- the CTA-pair form where that applies -- whose epilogue stores each
+    // 32-byte sector a second time, into the peer's copy, instead of the staged bulk stores of
+    // the sharded form.  Needs whole 32-column chunks and 32-byte aligned destinations.
+    I8Epilogue ep = ep_in;
+    {
+        const auto mis32 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31u) != 0; };
+        const uint64_t pitch = static_cast<uint64_t>(ep.ldc);   // 8-bit destinations: bytes
+        if (ep.num_peers == 1 && ep.mc_out == nullptr && knob(NNB200_KNOB_I8_PEER_STAGING) <= 0 &&
+            (ep.out_kind == NNB200_OUT_S8 || ep.out_kind == NNB200_OUT_U8) && p.a_stride_k == 1 && p.w_stride_k == 1 &&
+            m >= 4 * kBlockM && k >= 2048 && n % 32 == 0 && pitch % 32 == 0 && !mis32(ep.out) && !mis32(ep.peer_out[0])) {
+            ep.direct_peers = 1;
+            ep.num_peers = 0;
+        }
+    }
 
     // Tile width.  When even the widest tile gives every SM work, take the width with the least
     // padded work over whole waves (waves x width; ties to the wider tile); narrow problems
