@@ -193,8 +193,8 @@ NNB200_API int nnb200_gemm_i8_static_scratch(const nnb200_gemm_i8_args* args, vo
  * activation).  An S32 destination answers NNB200_UNSUPPORTED, as in the reference.
  *
  * pad_h / pad_w are the leading paddings and oh / ow are given by the caller (an auto-padded
- * convolution pads the trailing edge differently); a window must start inside the image or its
- * leading padding, else NNB200_INVALID_ARGUMENT.
+ * convolution pads the trailing edge differently); an extent whose last window would start more
+ * than the leading padding plus one filter span past the image answers NNB200_INVALID_ARGUMENT.
  *
  * Strides are in ELEMENTS.  The output's channel stride is 1 and its pixels lie at one pitch:
  * out_stride_h == ow * out_stride_w and, for batch > 1, out_stride_n == oh * out_stride_h
@@ -275,6 +275,7 @@ NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double
  *   I8_SHARE_K       0 never share K among SMs in the few-row engine, 2 offer it from 8 K blocks per SM
  *   Q4_GEMV          Q4_1 GEMV engine of the automatic choice: 1 never the deferred-scaling kernel, 2 that
  *                    kernel whenever it can run (default: for a single activation row)
+ *   CONV_FORM        1 = nnb200_conv2d_i8 never takes its implicit-GEMM form (gather pass + GEMM always)
  */
 #define NNB200_KNOB_GROUP_M 0
 #define NNB200_KNOB_I8_BN 1
@@ -283,7 +284,8 @@ NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double
 #define NNB200_KNOB_F16_PAIR 4
 #define NNB200_KNOB_I8_SHARE_K 5
 #define NNB200_KNOB_Q4_GEMV 6
-#define NNB200_KNOB_COUNT 7
+#define NNB200_KNOB_CONV_FORM 7
+#define NNB200_KNOB_COUNT 8
 NNB200_API int nnb200_set_knob(int knob, int value);
 NNB200_API int nnb200_get_knob(int knob);
 

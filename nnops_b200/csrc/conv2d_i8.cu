@@ -17,13 +17,24 @@
 //                             sums R_w.  Run per call on a raw filter (it is small), or once by
 //                             nnb200_conv2d_i8_pack.
 //
+// Stride-1 convolutions over whole 128-channel blocks per group with symmetric weights skip the
+// gather altogether (the implicit-GEMM form, launch_conv_i8_umma in gemm_i8_umma.cu): the GEMM's
+// producer reads the activation itself, one 4-D TMA box {128 channels, bw, bh, 1 image} per
+// k-block (tap, channel block) at the patch's origin shifted by the tap -- out-of-image parts are
+// filled with zeros by the copy engine -- and the epilogue adds the zero point's share back for
+// rows whose window overhangs: zp_x times the filter's channel sums over the lost taps, one of a
+// few rows of a small table (conv_border_table_kernel) picked by the row's border class.
+//
 // A 1x1 / stride 1 / unpadded convolution over a dense activation needs no gather: the activation
 // IS the [pixels, channels] matrix.  The epilogue is the GEMM's (compensation, int32 bias, Relu,
 // requantisation; or dequantisation, fp bias, clip, activation): the reference's CPU convolution
 // calls the same epilogue routine as its matmul (src/backend/cpu/conv/conv2d_implicit_gemm_i8.cpp:
 // 906-980), and results are compared with that route bit for bit.
 
+#include <cstring>
+
 #include "internal.cuh"
+#include "epilogue.cuh"
 
 namespace nnb200 {
 
@@ -226,6 +237,58 @@ __global__ void __launch_bounds__(256) conv_filter_sums_kernel(const int8_t* __r
     }
 }
 
+// Per-tap channel sums of the k-major filter: wtap[tap][channel] = sum over the tap's icg
+// weights.  The implicit-GEMM form adds zp_x * wtap back for taps that fall outside the image.
+__global__ void __launch_bounds__(256) conv_filter_tap_sums_kernel(const int8_t* __restrict__ wt, const int64_t oc,
+                                                                   const int32_t kp, const int32_t icg, const int32_t taps,
+                                                                   int32_t* __restrict__ wtap)
+{
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= oc * taps) {
+        return;
+    }
+    const int64_t channel = idx / taps;
+    const int32_t tap = static_cast<int32_t>(idx - channel * taps);
+    const int8_t* src = wt + channel * kp + static_cast<int64_t>(tap) * icg;
+    int32_t sum = 0;
+    for (int32_t c = 0; c < icg; ++c) {
+        sum += src[c];
+    }
+    wtap[static_cast<int64_t>(tap) * oc + channel] = sum;
+}
+
+// Border-class table of the implicit-GEMM form: row (i, j) = sum of the per-tap channel sums
+// over the taps (a, b) with a in mask_h[i - 1] or b in mask_w[j - 1] (index 0 = no tap lost).
+struct BorderParams {
+    const int32_t* wtap;   // [kh * kw][oc]
+    int32_t* table;        // [(nh + 1) * (nw + 1)][oc]
+    int32_t oc, kh, kw, nh, nw;
+    uint32_t mask_h[8], mask_w[8];
+};
+
+__global__ void __launch_bounds__(256) conv_border_table_kernel(const BorderParams p)
+{
+    const int classes = (p.nh + 1) * (p.nw + 1);
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<int64_t>(classes) * p.oc) {
+        return;
+    }
+    const int cls = static_cast<int>(idx / p.oc);
+    const int ch = static_cast<int>(idx - static_cast<int64_t>(cls) * p.oc);
+    const int i = cls / (p.nw + 1), j = cls - i * (p.nw + 1);
+    const uint32_t mh = i > 0 ? p.mask_h[i - 1] : 0u;
+    const uint32_t mw = j > 0 ? p.mask_w[j - 1] : 0u;
+    int32_t sum = 0;
+    for (int a = 0; a < p.kh; ++a) {
+        for (int b = 0; b < p.kw; ++b) {
+            if (((mh >> a) | (mw >> b)) & 1u) {
+                sum += p.wtap[static_cast<int64_t>(a * p.kw + b) * p.oc + ch];
+            }
+        }
+    }
+    p.table[idx] = sum;
+}
+
 int64_t round_up_i64(int64_t v, int64_t a)
 {
     return (v + a - 1) / a * a;
@@ -243,11 +306,13 @@ bool conv_geometry(const nnb200_conv2d_i8_args* a, ConvGeom* g)
     g->kh = a->kh; g->kw = a->kw; g->sh = a->stride_h; g->sw = a->stride_w; g->dh = a->dil_h; g->dw = a->dil_w;
     g->ph = a->pad_h; g->pw = a->pad_w; g->groups = a->groups;
     // pad_h / pad_w are the LEADING paddings; the output extent is the caller's (an auto-padded
-    // convolution pads the trailing edge by a different amount).  Every window must start at or
-    // before the last real row / column; taps beyond any edge read the zero point.
+    // convolution pads the trailing edge by a different amount).  Taps beyond any edge read the
+    // zero point; an output extent whose last window would start more than the leading padding
+    // plus one filter span past the image is not a convolution of this input.
     const int64_t oh = a->oh, ow = a->ow;
-    if (oh <= 0 || ow <= 0 || (oh - 1) * a->stride_h - a->pad_h > a->ih - 1 ||
-        (ow - 1) * a->stride_w - a->pad_w > a->iw - 1) {
+    const int64_t span_h = (a->kh - 1) * a->dil_h + 1, span_w = (a->kw - 1) * a->dil_w + 1;
+    if (oh <= 0 || ow <= 0 || (oh - 1) * a->stride_h - a->pad_h > a->ih - 1 + a->pad_h + span_h ||
+        (ow - 1) * a->stride_w - a->pad_w > a->iw - 1 + a->pad_w + span_w) {
         return false;
     }
     g->oh = oh; g->ow = ow;
@@ -270,12 +335,44 @@ bool pointwise_in_place(const nnb200_conv2d_i8_args* a, const ConvGeom& g)
 }
 
 struct ConvScratch {
-    size_t col_bytes;      // gathered activation, 0 for the in-place pointwise case
+    size_t col_bytes;      // gathered activation, 0 for the in-place pointwise case and the implicit form
     size_t filter_bytes;   // k-major filter, 0 when the caller passed a packed one
-    size_t sums_bytes;     // R_w of every channel, 0 when packed or no zero point needs it
+    size_t sums_bytes;     // R_w of every channel and the per-tap sums, 0 when packed
     size_t gemm_bytes;     // what one group's GEMM asks for
     size_t total;
 };
+
+// The implicit-GEMM form (no gathered copy; launch_conv_i8_umma) takes stride-1 convolutions
+// over whole 128-channel blocks per group whose weights have no zero points, when TMA can
+// address the activation (dense channels, 16-byte aligned pitches and base).
+bool implicit_form(const nnb200_conv2d_i8_args* a, const ConvGeom& g)
+{
+    if (knob(NNB200_KNOB_CONV_FORM) == 1) {
+        return false;   // measurement switch: always the gather pass + GEMM
+    }
+    const bool zp_w_zero = a->zp_w_scalar == 0 && (a->zp_w == nullptr || a->zp_w_nonzero == 0);
+    // Patches of 128 pixels must not pad a small image by more than half again of its pixels.
+    int64_t padded = 0;
+    conv_patch_log2(static_cast<int>(g.oh), static_cast<int>(g.ow), &padded);
+    // ... and small planes (14 x 14 measured a little slower than the gather form, 28 x 28 the
+    // same, 56 x 56 1.4x and 112 x 112 1.7x faster) stay on the gather form.
+    if (g.oh > 65536 || g.ow > 65536 || padded * 2 > g.oh * g.ow * 3 || g.oh * g.ow < 700) {
+        return false;
+    }
+    if (a->zp_x != 0 && g.kh <= 32 && g.kw <= 32) {
+        uint32_t masks[8];
+        if (conv_border_masks(static_cast<int>(g.oh), static_cast<int>(g.ih), static_cast<int>(g.kh), static_cast<int>(g.dh),
+                              static_cast<int>(g.ph), masks) < 0 ||
+            conv_border_masks(static_cast<int>(g.ow), static_cast<int>(g.iw), static_cast<int>(g.kw), static_cast<int>(g.dw),
+                              static_cast<int>(g.pw), masks) < 0) {
+            return false;   // more than eight kinds of overhang along an axis
+        }
+    }
+    return g.sh == 1 && g.sw == 1 && g.icg % 128 == 0 && g.kh <= 32 && g.kw <= 32 && zp_w_zero && a->in_stride_c == 1 &&
+           a->in_stride_w % 16 == 0 && a->in_stride_h % 16 == 0 && a->in_stride_n % 16 == 0 &&
+           reinterpret_cast<uintptr_t>(a->input) % 16 == 0 && a->in_stride_w >= g.ic && g.oh <= 65536 && g.ow <= 65536 &&
+           (g.kh - 1) * g.dh < 32768 && (g.kw - 1) * g.dw < 32768 && g.ph < 32768 && g.pw < 32768;
+}
 
 size_t align256(size_t v)
 {
@@ -323,10 +420,18 @@ bool needs_compensation(const nnb200_conv2d_i8_args* a)
 
 bool plan_scratch(const nnb200_conv2d_i8_args* a, const ConvGeom& g, bool in_place, ConvScratch* s)
 {
-    s->col_bytes = in_place ? 0 : align256(static_cast<size_t>(g.groups) * static_cast<size_t>(g.pixels) *
-                                           static_cast<size_t>(g.kp));
+    const bool implicit = !in_place && implicit_form(a, g);
+    s->col_bytes = (in_place || implicit) ? 0 : align256(static_cast<size_t>(g.groups) * static_cast<size_t>(g.pixels) *
+                                                         static_cast<size_t>(g.kp));
     s->filter_bytes = a->weight_packed ? 0 : align256(static_cast<size_t>(g.oc) * static_cast<size_t>(g.kp));
-    s->sums_bytes = a->weight_packed ? 0 : align256(static_cast<size_t>(g.oc) * 4);
+    s->sums_bytes = a->weight_packed ? 0 : align256(static_cast<size_t>(g.oc) * 4) +
+                                               align256(static_cast<size_t>(g.oc) * static_cast<size_t>(g.kh * g.kw) * 4);
+    if (implicit) {
+        // gemm_bytes holds the border-class table here: at most 9 x 9 rows of oc sums.
+        s->gemm_bytes = a->zp_x != 0 ? align256(static_cast<size_t>(81) * static_cast<size_t>(g.oc) * 4) : 0;
+        s->total = s->filter_bytes + s->sums_bytes + s->gemm_bytes;
+        return true;
+    }
     nnb200_gemm_i8_args q;
     group_gemm_args(a, g, in_place, &q);
     // Pointers only decide alignment-dependent engine choices: stand-ins with the alignment the
@@ -351,15 +456,17 @@ int out_elem_bytes(int32_t kind)
 
 }  // namespace
 
-// Byte size of the packed filter: [oc][kp] k-major rows, then int32 sums per channel.
-size_t conv_pack_bytes(int64_t oc, int64_t kp)
+// Byte size of the packed filter: [oc][kp] k-major rows, then (each section 256-byte aligned)
+// int32 sums per channel and int32 sums per (tap, channel).
+size_t conv_pack_bytes(int64_t oc, int64_t kp, int64_t taps)
 {
-    return align256(static_cast<size_t>(oc) * static_cast<size_t>(kp)) + static_cast<size_t>(oc) * 4;
+    return align256(static_cast<size_t>(oc) * static_cast<size_t>(kp)) + align256(static_cast<size_t>(oc) * 4) +
+           static_cast<size_t>(oc) * static_cast<size_t>(taps) * 4;
 }
 
 int launch_conv_filter_kmajor(const void* w, int64_t w_kh, int64_t w_kw, int64_t w_ic, int64_t w_oc, int64_t kh,
                               int64_t kw, int64_t icg, int64_t ocg, int64_t groups, void* wt, int32_t* r_w,
-                              cudaStream_t stream)
+                              int32_t* wtap, cudaStream_t stream)
 {
     FilterParams f;
     f.w = static_cast<const int8_t*>(w);
@@ -375,6 +482,12 @@ int launch_conv_filter_kmajor(const void* w, int64_t w_kh, int64_t w_kw, int64_t
     note_launch();
     if (r_w != nullptr) {
         conv_filter_sums_kernel<<<static_cast<unsigned>((oc + 7) / 8), 256, 0, stream>>>(f.wt, oc, f.kp, r_w);
+        note_launch();
+    }
+    if (wtap != nullptr) {
+        const int64_t items = oc * kh * kw;
+        conv_filter_tap_sums_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, stream>>>(
+            f.wt, oc, f.kp, f.icg, static_cast<int32_t>(kh * kw), wtap);
         note_launch();
     }
     return cuda_status(cudaGetLastError());
@@ -402,7 +515,7 @@ size_t nnb200_conv2d_i8_pack_bytes(int64_t kh, int64_t kw, int64_t ic_per_group,
     if (kh <= 0 || kw <= 0 || ic_per_group <= 0 || oc <= 0) {
         return 0;
     }
-    return conv_pack_bytes(oc, round_up_i64(kh * kw * ic_per_group, 16));
+    return conv_pack_bytes(oc, round_up_i64(kh * kw * ic_per_group, 16), kh * kw);
 }
 
 int nnb200_conv2d_i8_pack(const void* weight, int64_t w_stride_kh, int64_t w_stride_kw, int64_t w_stride_ic,
@@ -415,9 +528,11 @@ int nnb200_conv2d_i8_pack(const void* weight, int64_t w_stride_kh, int64_t w_str
         return NNB200_INVALID_ARGUMENT;
     }
     const int64_t kp = round_up_i64(kh * kw * ic_per_group, 16);
-    int32_t* sums = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(blob) + align256(static_cast<size_t>(oc * kp)));
+    uint8_t* after = static_cast<uint8_t*>(blob) + align256(static_cast<size_t>(oc * kp));
+    int32_t* sums = reinterpret_cast<int32_t*>(after);
+    int32_t* wtap = reinterpret_cast<int32_t*>(after + align256(static_cast<size_t>(oc) * 4));
     return launch_conv_filter_kmajor(weight, w_stride_kh, w_stride_kw, w_stride_ic, w_stride_oc, kh, kw, ic_per_group,
-                                     oc / groups, groups, blob, sums, static_cast<cudaStream_t>(stream));
+                                     oc / groups, groups, blob, sums, wtap, static_cast<cudaStream_t>(stream));
 }
 
 int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* a, void* stream_v)
@@ -442,7 +557,8 @@ int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* a, void* stream_v)
         return NNB200_OK;
     }
     const bool in_place = pointwise_in_place(a, g);
-    if (!in_place && g.kp / 16 > 2048) {
+    const bool implicit = !in_place && implicit_form(a, g);   // the same decision plan_scratch takes
+    if (!in_place && !implicit && g.kp / 16 > 2048) {
         return NNB200_UNSUPPORTED;   // the gather's tap table is sized for K <= 32768
     }
     ConvScratch plan;
@@ -456,19 +572,112 @@ int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* a, void* stream_v)
     uint8_t* col = ws;
     int8_t* wt = reinterpret_cast<int8_t*>(ws + plan.col_bytes);
     int32_t* r_w = reinterpret_cast<int32_t*>(ws + plan.col_bytes + plan.filter_bytes);
+    int32_t* wtap = reinterpret_cast<int32_t*>(ws + plan.col_bytes + plan.filter_bytes + align256(static_cast<size_t>(g.oc) * 4));
     uint8_t* gemm_ws = ws + plan.col_bytes + plan.filter_bytes + plan.sums_bytes;
     const bool comp = needs_compensation(a);
 
     if (a->weight_packed) {
         wt = static_cast<int8_t*>(const_cast<void*>(a->weight));
-        r_w = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(wt) + align256(static_cast<size_t>(g.oc * g.kp)));
+        uint8_t* after = reinterpret_cast<uint8_t*>(wt) + align256(static_cast<size_t>(g.oc * g.kp));
+        r_w = reinterpret_cast<int32_t*>(after);
+        wtap = reinterpret_cast<int32_t*>(after + align256(static_cast<size_t>(g.oc) * 4));
     } else {
         const int st = launch_conv_filter_kmajor(a->weight, a->w_stride_kh, a->w_stride_kw, a->w_stride_ic,
                                                  a->w_stride_oc, g.kh, g.kw, g.icg, g.ocg, g.groups, wt,
-                                                 comp ? r_w : nullptr, stream);
+                                                 comp ? r_w : nullptr, (implicit && a->zp_x != 0) ? wtap : nullptr, stream);
         if (st != NNB200_OK) {
             return st;
         }
+    }
+    if (implicit) {
+        // One launch per group on the tensor-core engine, the activation read in place.
+        const DeviceInfo* dev = current_device_info();
+        if (dev == nullptr) {
+            return NNB200_INTERNAL;
+        }
+        if (dev->cc_major != 10) {
+            return NNB200_UNSUPPORTED;
+        }
+        const bool int_out = a->out_kind <= NNB200_OUT_U8;
+        const int64_t out_esz = out_elem_bytes(a->out_kind);
+        const int64_t bias_esz = a->out_kind == NNB200_OUT_F16 ? 2 : 4;
+        BorderParams bp;
+        std::memset(&bp, 0, sizeof(bp));
+        int32_t* border = reinterpret_cast<int32_t*>(gemm_ws);
+        if (a->zp_x != 0) {
+            bp.wtap = wtap;
+            bp.table = border;
+            bp.oc = static_cast<int32_t>(g.oc);
+            bp.kh = static_cast<int32_t>(g.kh);
+            bp.kw = static_cast<int32_t>(g.kw);
+            bp.nh = conv_border_masks(static_cast<int>(g.oh), static_cast<int>(g.ih), bp.kh, static_cast<int>(g.dh),
+                                      static_cast<int>(g.ph), bp.mask_h);
+            bp.nw = conv_border_masks(static_cast<int>(g.ow), static_cast<int>(g.iw), bp.kw, static_cast<int>(g.dw),
+                                      static_cast<int>(g.pw), bp.mask_w);
+            if (bp.nh < 0 || bp.nw < 0) {
+                return NNB200_INTERNAL;   // implicit_form() admits only geometries with at most eight classes
+            }
+            const int64_t items = static_cast<int64_t>(bp.nh + 1) * (bp.nw + 1) * g.oc;
+            conv_border_table_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, stream>>>(bp);
+            note_launch();
+            if (cudaGetLastError() != cudaSuccess) {
+                return NNB200_INTERNAL;
+            }
+        }
+        for (int64_t grp = 0; grp < g.groups; ++grp) {
+            const int64_t c0 = grp * g.ocg;
+            I8Epilogue ep;
+            std::memset(&ep, 0, sizeof(ep));
+            ep.out = static_cast<uint8_t*>(a->out) + c0 * out_esz;
+            ep.ldc = a->out_stride_w;
+            ep.out_kind = a->out_kind;
+            ep.bias = a->bias != nullptr ? static_cast<const uint8_t*>(a->bias) + c0 * bias_esz : nullptr;
+            ep.relu = int_out ? (a->relu != 0) : 0;
+            ep.activation = int_out ? NNB200_ACT_NONE : a->activation;
+            ep.act_alpha = a->act_alpha;
+            ep.act_beta = a->act_beta;
+            ep.min_clip = a->min_clip;
+            ep.max_clip = a->max_clip;
+            ep.scale_w = a->scale_w != nullptr ? a->scale_w + c0 : nullptr;
+            ep.zp_w = nullptr;                       // every weight zero point is 0 in this form
+            ep.scale_a_scalar = a->scale_x;
+            ep.scale_w_scalar = a->scale_w_scalar;
+            ep.zp_a_scalar = a->zp_x;
+            ep.zp_w_scalar = 0;
+            ep.compensate = a->zp_x != 0 ? 1 : 0;
+            ep.r_a = nullptr;
+            ep.r_w = a->zp_x != 0 ? r_w + c0 : nullptr;
+            ep.k = static_cast<int32_t>(g.k);
+            ep.out_scale = a->out_scale;
+            ep.out_zp = a->out_zp;
+            ConvUmmaArgs c;
+            c.x = a->input;
+            c.in_n = a->in_stride_n; c.in_h = a->in_stride_h; c.in_w = a->in_stride_w;
+            c.batch = static_cast<int32_t>(g.batch); c.ih = static_cast<int32_t>(g.ih); c.iw = static_cast<int32_t>(g.iw);
+            c.ic_total = static_cast<int32_t>(g.ic); c.oh = static_cast<int32_t>(g.oh); c.ow = static_cast<int32_t>(g.ow);
+            c.kh = static_cast<int32_t>(g.kh); c.kw = static_cast<int32_t>(g.kw);
+            c.dh = static_cast<int32_t>(g.dh); c.dw = static_cast<int32_t>(g.dw);
+            c.ph = static_cast<int32_t>(g.ph); c.pw = static_cast<int32_t>(g.pw);
+            c.c_base = static_cast<int32_t>(grp * g.icg); c.icg = static_cast<int32_t>(g.icg);
+            c.wt = wt + c0 * g.kp;
+            c.ldw = g.kp;
+            c.ocg = static_cast<int32_t>(g.ocg); c.k = static_cast<int32_t>(g.k);
+            c.zp_x = a->zp_x;
+            c.wtap_ld = static_cast<int32_t>(g.oc);
+            c.nh = bp.nh;
+            c.nw = bp.nw;
+            for (int q = 0; q < 8; ++q) {
+                c.mask_h[q] = bp.mask_h[q];
+                c.mask_w[q] = bp.mask_w[q];
+            }
+            c.border = a->zp_x != 0 ? border + c0 : nullptr;
+            c.a_unsigned = a->a_unsigned;
+            const int st = launch_conv_i8_umma(c, ep, *dev, stream);
+            if (st != NNB200_OK) {
+                return st;
+            }
+        }
+        return NNB200_OK;
     }
     if (!in_place) {
         GatherParams p;

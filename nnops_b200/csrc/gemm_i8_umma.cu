@@ -58,6 +58,27 @@ struct alignas(64) PeerMaps {
     CUtensorMap m[8];
 };
 
+// Geometry of the implicit-GEMM convolution (CONV kernels): an M tile is a patch of bh x bw
+// output pixels of one image, its A operand for the k-block (tap, 128 channels) one 4-D TMA
+// box of the NHWC activation shifted by the tap -- what lies outside the image is filled with
+// zeros, and rows whose window overhangs get the zero point's share added back in the epilogue.
+struct ConvTile {
+    int32_t oh, ow, ih, iw;
+    int32_t kh, kw, dh, dw, ph, pw;
+    int32_t bw_log2, bh;           // patch: bh rows x (1 << bw_log2) columns, 128 pixels
+    int32_t tiles_w, tiles_h;      // patches per image
+    int32_t c_base;                // first channel of this group in the activation
+    int32_t kb_per_tap;            // 128-channel k-blocks per tap
+    int32_t zp_x;                  // activation zero point (0: no correction)
+    int32_t wtap_ld;               // output channels of the whole filter (row length of the tables)
+    // Border classes: the distinct masks of out-of-image taps along each axis (at most eight
+    // each); class (i, j) -- i, j = 1 + index of the row's masks, 0 = none -- has a table row
+    // holding the sum of the per-tap channel sums of the filter over the taps it loses.
+    int32_t nh, nw;
+    uint32_t mask_h[8], mask_w[8];
+    const int32_t* border;         // [(nh + 1) * (nw + 1)][wtap_ld], at this group's first column
+};
+
 template <int BN, int PEERS = 0>
 struct TileConfig {
     // Tiles wider than 256 columns (single-wave form, see launch_gemm_i8_umma) are issued as two
@@ -351,13 +372,14 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
     }
 }
 
-template <int BN, int KIND, int PEERS>
+template <int BN, int KIND, int PEERS, bool CONV = false>
 __global__ void __launch_bounds__(kMaxThreads, 1)
 gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ PeerMaps peer_maps, const I8Epilogue ep, const int m_total,
                     const int n_total, const int k_total, const uint32_t idesc, const int vec_ok, const int group_m,
-                    int32_t* error_word)
+                    int32_t* error_word, const ConvTile conv)
 {
+    static_assert(!CONV || PEERS == 0, "the convolution form has no sharded epilogue");
     using Cfg = TileConfig<BN, PEERS>;
     constexpr int kStages = Cfg::kStages;
 
@@ -430,7 +452,19 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     uint8_t* a_dst = stage_base + stage * Cfg::kStageBytes;
                     uint8_t* b_dst = a_dst + Cfg::kATileBytes;
                     mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-                    if (pose & 1) {
+                    if constexpr (CONV) {
+                        // Patch (image, th, tw) shifted by the k-block's tap; 128 channels of it.
+                        const int tw = tc.m_blk % conv.tiles_w;
+                        const int t2 = tc.m_blk / conv.tiles_w;
+                        const int th = t2 % conv.tiles_h;
+                        const int img = t2 / conv.tiles_h;
+                        const int tap = kb / conv.kb_per_tap;
+                        const int c0 = (kb - tap * conv.kb_per_tap) * kBlockKBytes;
+                        const int ta = tap / conv.kw;
+                        const int tb = tap - ta * conv.kw;
+                        tma_load_4d(a_dst, &map_a, &full_bar[stage], conv.c_base + c0,
+                                    (tw << conv.bw_log2) - conv.pw + tb * conv.dw, th * conv.bh - conv.ph + ta * conv.dh, img);
+                    } else if (pose & 1) {
                         // A stored [K][M]: the box is 128 k-rows of 128 m-bytes.
                         tma_load_2d(a_dst, &map_a, &full_bar[stage], tc.m_blk * kBlockM, kb * kBlockKBytes);
                     } else {
@@ -586,8 +620,39 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             __syncwarp();
 
-            const int64_t m = static_cast<int64_t>(tc.m_blk) * kBlockM + quarter * 32 + lane;
-            const bool row_ok = m < m_total;
+            int64_t m = static_cast<int64_t>(tc.m_blk) * kBlockM + quarter * 32 + lane;
+            bool row_ok = m < m_total;
+            uint32_t bad_h = 0, bad_w = 0;   // CONV: the row's border class along each axis (0: every tap inside)
+            if constexpr (CONV) {
+                // Row r of the tile is pixel (r >> bw_log2, r & (bw - 1)) of the patch.
+                const int r = quarter * 32 + lane;
+                const int tw = tc.m_blk % conv.tiles_w;
+                const int t2 = tc.m_blk / conv.tiles_w;
+                const int th = t2 % conv.tiles_h;
+                const int img = t2 / conv.tiles_h;
+                const int y = th * conv.bh + (r >> conv.bw_log2);
+                const int x = (tw << conv.bw_log2) + (r & ((1 << conv.bw_log2) - 1));
+                row_ok = y < conv.oh && x < conv.ow;
+                m = (static_cast<int64_t>(img) * conv.oh + y) * conv.ow + x;
+                if (conv.zp_x != 0 && row_ok) {
+                    uint32_t lost_h = 0, lost_w = 0;
+                    for (int a = 0; a < conv.kh; ++a) {
+                        const int iy = y - conv.ph + a * conv.dh;
+                        lost_h |= (iy < 0 || iy >= conv.ih) ? (1u << a) : 0u;
+                    }
+                    for (int b = 0; b < conv.kw; ++b) {
+                        const int ix = x - conv.pw + b * conv.dw;
+                        lost_w |= (ix < 0 || ix >= conv.iw) ? (1u << b) : 0u;
+                    }
+                    // bad_h / bad_w: 1 + index of the mask among the axis's classes (0 = no tap lost).
+                    for (int q = 0; q < conv.nh; ++q) {
+                        bad_h = (lost_h != 0 && conv.mask_h[q] == lost_h) ? static_cast<uint32_t>(q + 1) : bad_h;
+                    }
+                    for (int q = 0; q < conv.nw; ++q) {
+                        bad_w = (lost_w != 0 && conv.mask_w[q] == lost_w) ? static_cast<uint32_t>(q + 1) : bad_w;
+                    }
+                }
+            }
             I8RowTerms rt;
             rt.zpa = 0;
             rt.ra = 0;
@@ -713,6 +778,31 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     uint32_t v[32];
                     tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                     tmem_ld_wait();
+                    if constexpr (CONV) {
+                        // A tap outside the image was loaded as 0 where the reference's gather holds
+                        // the zero point: add zp_x * (that tap's channel sum of the filter) back.
+                        if ((bad_h | bad_w) != 0) {
+                            const int32_t* tb = conv.border +
+                                                static_cast<int64_t>(bad_h * (conv.nw + 1) + bad_w) * conv.wtap_ld + n0;
+                            if (n0 + 32 <= n_total && (reinterpret_cast<uintptr_t>(tb) & 15u) == 0) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4) {
+                                    const int4 t4 = __ldg(reinterpret_cast<const int4*>(tb + j));
+                                    v[j] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.x);
+                                    v[j + 1] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.y);
+                                    v[j + 2] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.z);
+                                    v[j + 3] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.w);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    if (n0 + j < n_total) {
+                                        v[j] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(tb[j]);
+                                    }
+                                }
+                            }
+                        }
+                    }
                     epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
                                          cz + c * 32, vec_ok, fold_scale, fold_comp);
                 }
@@ -1153,7 +1243,7 @@ int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8E
         group_m = knob(NNB200_KNOB_GROUP_M);
     }
     kernel<<<grid, num_threads(PEERS), kSmem, stream>>>(map_a, map_w, maps, ep, m, n, k, idesc, vec_ok, group_m,
-                                                 dev.error_word);
+                                                 dev.error_word, ConvTile{});
     note_launch();
     return cuda_status(cudaGetLastError());
 }
@@ -1207,6 +1297,109 @@ int launch_bn(int kind, const CUtensorMap& map_a, const CUtensorMap& map_w, cons
 }
 
 }  // namespace
+
+namespace {
+
+template <int BN, int KIND>
+int launch_conv_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m_tiles, int n,
+                        int k, uint32_t idesc, int vec_ok, const ConvTile& conv, const DeviceInfo& dev,
+                        cudaStream_t stream)
+{
+    using Cfg = TileConfig<BN, 0>;
+    auto kernel = gemm_i8_umma_kernel<BN, KIND, 0, true>;
+    static std::once_flag once[kMaxDevices];
+    static cudaError_t attr_err[kMaxDevices];
+    std::call_once(once[dev.device], [&] {
+        attr_err[dev.device] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    });
+    if (attr_err[dev.device] != cudaSuccess) {
+        return NNB200_INTERNAL;
+    }
+    PeerMaps maps;
+    std::memset(&maps, 0, sizeof(maps));
+    const int num_tiles = m_tiles * ((n + BN - 1) / BN);
+    const int grid = num_tiles < dev.sm_count ? num_tiles : dev.sm_count;
+    int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(kBlockM) * (k > 0 ? k : 1)));
+    group_m = group_m < 4 ? 4 : group_m;
+    kernel<<<grid, num_threads(0), Cfg::kSmemBytes, stream>>>(map_a, map_w, maps, ep, m_tiles * kBlockM, n, k, idesc, vec_ok,
+                                                            group_m, dev.error_word, conv);
+    note_launch();
+    return cuda_status(cudaGetLastError());
+}
+
+template <int BN>
+int launch_conv_bn(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m_tiles, int n, int k,
+                   uint32_t idesc, int vec_ok, const ConvTile& conv, const DeviceInfo& dev, cudaStream_t stream)
+{
+    switch (ep.out_kind) {
+    case NNB200_OUT_S8: return launch_conv_variant<BN, NNB200_OUT_S8>(map_a, map_w, ep, m_tiles, n, k, idesc, vec_ok, conv, dev, stream);
+    case NNB200_OUT_U8: return launch_conv_variant<BN, NNB200_OUT_U8>(map_a, map_w, ep, m_tiles, n, k, idesc, vec_ok, conv, dev, stream);
+    case NNB200_OUT_F32: return launch_conv_variant<BN, NNB200_OUT_F32>(map_a, map_w, ep, m_tiles, n, k, idesc, vec_ok, conv, dev, stream);
+    case NNB200_OUT_F16: return launch_conv_variant<BN, NNB200_OUT_F16>(map_a, map_w, ep, m_tiles, n, k, idesc, vec_ok, conv, dev, stream);
+    default: return NNB200_UNSUPPORTED;
+    }
+}
+
+}  // namespace
+
+// Implicit-GEMM convolution of one group: output pixels are tiled in patches of 128 (bh rows x
+// bw columns of one image, bw a power of two chosen for the least padding), the activation is
+// read through a 4-D tensor map {c, w, h, n} whose boxes are those patches shifted by the tap.
+int launch_conv_i8_umma(const ConvUmmaArgs& c, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream)
+{
+    ConvTile t;
+    std::memset(&t, 0, sizeof(t));
+    const int best = conv_patch_log2(c.oh, c.ow, nullptr);
+    t.oh = c.oh; t.ow = c.ow; t.ih = c.ih; t.iw = c.iw;
+    t.kh = c.kh; t.kw = c.kw; t.dh = c.dh; t.dw = c.dw; t.ph = c.ph; t.pw = c.pw;
+    t.bw_log2 = best;
+    t.bh = 128 >> best;
+    t.tiles_w = (c.ow + (1 << best) - 1) >> best;
+    t.tiles_h = (c.oh + t.bh - 1) / t.bh;
+    t.c_base = c.c_base;
+    t.kb_per_tap = c.icg / kBlockKBytes;
+    t.zp_x = c.zp_x;
+    t.wtap_ld = c.wtap_ld;
+    t.nh = c.nh;
+    t.nw = c.nw;
+    for (int q = 0; q < 8; ++q) {
+        t.mask_h[q] = c.mask_h[q];
+        t.mask_w[q] = c.mask_w[q];
+    }
+    t.border = c.border;
+    const int64_t m_tiles64 = static_cast<int64_t>(c.batch) * t.tiles_h * t.tiles_w;
+    if (m_tiles64 > (INT32_MAX / kBlockM)) {
+        return NNB200_UNSUPPORTED;
+    }
+    const int m_tiles = static_cast<int>(m_tiles64);
+    const int n = c.ocg, k = c.k;
+    int bn = 256;
+    if (static_cast<int64_t>(m_tiles) * ((n + 255) / 256) < dev.sm_count || n <= 128) {
+        bn = 128;
+        if (static_cast<int64_t>(m_tiles) * ((n + 127) / 128) < dev.sm_count || n <= 64) {
+            bn = 64;
+        }
+    }
+    CUtensorMap map_a, map_w;
+    if (!make_tma_nhwc_u8(&map_a, c.x, static_cast<uint64_t>(c.ic_total), static_cast<uint64_t>(c.iw),
+                          static_cast<uint64_t>(c.ih), static_cast<uint64_t>(c.batch), static_cast<uint64_t>(c.in_w),
+                          static_cast<uint64_t>(c.in_h), static_cast<uint64_t>(c.in_n), kBlockKBytes, 1u << best,
+                          static_cast<uint32_t>(t.bh)) ||
+        !make_tma_2d(&map_w, c.wt, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(c.ldw),
+                     kBlockKBytes, static_cast<uint32_t>(bn))) {
+        return NNB200_INTERNAL;
+    }
+    const int elem = ep.out_kind == NNB200_OUT_S32 || ep.out_kind == NNB200_OUT_F32 ? 4 : (ep.out_kind == NNB200_OUT_F16 ? 2 : 1);
+    const uint64_t pitch_bytes = static_cast<uint64_t>(ep.ldc) * elem;
+    const int vec_ok = (((reinterpret_cast<uintptr_t>(ep.out) & 15u) == 0 && (pitch_bytes & 15u) == 0) ? 1 : 0) |
+                       (((reinterpret_cast<uintptr_t>(ep.out) & 31u) == 0 && (pitch_bytes & 31u) == 0) ? 2 : 0);
+    const uint32_t idesc = umma_idesc(2, c.a_unsigned ? 0u : 1u, 1, kBlockM, bn);
+    switch (bn) {
+    case 256: return launch_conv_bn<256>(map_a, map_w, ep, m_tiles, n, k, idesc, vec_ok, t, dev, stream);
+    case 128: return launch_conv_bn<128>(map_a, map_w, ep, m_tiles, n, k, idesc, vec_ok, t, dev, stream);
+    default: return launch_conv_bn<64>(map_a, map_w, ep, m_tiles, n, k, idesc, vec_ok, t, dev, stream);
+    }
+}
 
 bool umma_i8_supported(const I8Problem& p)
 {

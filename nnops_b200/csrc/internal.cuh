@@ -51,6 +51,10 @@ void note_launch(int n = 1);
 bool make_tma_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t cols, uint64_t rows,
                  uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, bool swizzle128 = true);
 
+bool make_tma_nhwc_u8(CUtensorMap* map, const void* base, uint64_t c, uint64_t w, uint64_t h, uint64_t n,
+                      uint64_t stride_w, uint64_t stride_h, uint64_t stride_n, uint32_t box_c, uint32_t box_w,
+                      uint32_t box_h);
+
 // One 2-D int8 problem (a single batch element), Linear pose: A [m,k] and W [n,k] both
 // k-contiguous.  lda / ldw are row pitches in bytes.
 struct I8Problem {
@@ -66,6 +70,83 @@ struct I8Problem {
 bool umma_i8_supported(const I8Problem& p);
 
 int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
+// One group of an int8 convolution on the tensor-core engine without a gathered copy of the
+// activation (stride 1, a multiple of 128 channels per group, symmetric weights): see
+// gemm_i8_umma.cu.  Strides in bytes (8-bit elements).
+struct ConvUmmaArgs {
+    const void* x;              // NHWC activation, all channels
+    int64_t in_n, in_h, in_w;
+    int32_t batch, ih, iw, ic_total, oh, ow;
+    int32_t kh, kw, dh, dw, ph, pw;
+    int32_t c_base, icg;        // this group's channels
+    const void* wt;             // k-major filter rows of this group [ocg][ldw], k = (tap, channel)
+    int64_t ldw;
+    int32_t ocg, k;
+    int32_t zp_x;
+    int32_t wtap_ld;            // output channels of the whole filter: row length of `border`
+    // Border classes (zp_x != 0): the distinct masks of out-of-image taps per axis and, per pair
+    // of classes, the sum of the filter's per-tap channel sums over the taps the pair loses.
+    int32_t nh, nw;
+    uint32_t mask_h[8], mask_w[8];
+    const int32_t* border;      // [(nh + 1) * (nw + 1)][wtap_ld], at this group's first column
+    int32_t a_unsigned;
+};
+int launch_conv_i8_umma(const ConvUmmaArgs& c, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
+// Which taps of one filter axis fall outside the image, as a bit mask, for the output coordinate
+// `o` (stride 1): bit t set when o - pad + t * dil is not in [0, extent_in).
+inline uint32_t conv_bad_taps(int o, int pad, int dil, int taps, int extent_in)
+{
+    uint32_t bad = 0;
+    for (int t = 0; t < taps; ++t) {
+        const int i = o - pad + t * dil;
+        bad |= (i < 0 || i >= extent_in) ? (1u << t) : 0u;
+    }
+    return bad;
+}
+// The distinct non-zero masks over all output coordinates of an axis, into masks[0..7]; returns
+// their number, or -1 when there are more than eight.
+inline int conv_border_masks(int extent_out, int extent_in, int taps, int dil, int pad, uint32_t* masks)
+{
+    int count = 0;
+    for (int o = 0; o < extent_out; ++o) {
+        const uint32_t bad = conv_bad_taps(o, pad, dil, taps, extent_in);
+        if (bad == 0) {
+            continue;
+        }
+        bool seen = false;
+        for (int q = 0; q < count; ++q) {
+            seen = seen || masks[q] == bad;
+        }
+        if (!seen) {
+            if (count == 8) {
+                return -1;
+            }
+            masks[count++] = bad;
+        }
+    }
+    return count;
+}
+
+// The patch of 128 output pixels an M tile of that form covers: (128 >> lg) rows x (1 << lg)
+// columns, lg in 3..7, chosen for the fewest padded pixels per image (ties: the wider patch).
+// *padded = pixels per image the tiles cover.
+inline int conv_patch_log2(int oh, int ow, int64_t* padded)
+{
+    int best = 3;
+    int64_t best_cost = -1;
+    for (int lg = 3; lg <= 7; ++lg) {
+        const int bw = 1 << lg, bh = 128 >> lg;
+        const int64_t cost = static_cast<int64_t>((ow + bw - 1) / bw) * bw * ((oh + bh - 1) / bh) * bh;
+        if (best_cost < 0 || cost <= best_cost) {
+            best_cost = cost;
+            best = lg;
+        }
+    }
+    if (padded != nullptr) {
+        *padded = best_cost;
+    }
+    return best;
+}
 int launch_gemm_i8_generic(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
 int launch_gemm_i8_narrow(const I8Problem& p, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
 bool narrow_i8_supported(const I8Problem& p);

@@ -162,6 +162,18 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// 4-D tiled load (an NHWC activation as {c, w, h, n}): x, the innermost coordinate, must make
+// x * elem_size a multiple of 16 bytes; the others may be negative or past the end, and the
+// part of the box outside the tensor is filled with zeros.
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t x, int32_t y,
+                                            int32_t z, int32_t w)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+
 // 2-D tiled store shared -> global (the destination may be a peer GPU's memory: stores, unlike
 // multicast loads, are fine there).  Tracked by the issuing thread's bulk async-groups.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int32_t x, int32_t y)

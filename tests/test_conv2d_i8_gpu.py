@@ -50,7 +50,17 @@ CASES = [
     (2, 3, 33, 31, 32, 7, 7, 2, 2, 1, 1, 3, 3, 1, U8, "s8", True, True, None, False),
     (4, 48, 9, 9, 21, 3, 3, 1, 1, 1, 1, 0, 0, 3, S8, "f16", True, False, None, False),
     (2, 64, 28, 28, 96, 1, 1, 2, 2, 1, 1, 0, 0, 1, U8, "u8", True, True, None, False),
+    # Shapes the implicit-GEMM form takes (stride 1, whole 128-channel blocks per group, symmetric
+    # weights): zero points against padding (the border correction), dilation, groups, a 1x1 with
+    # padding, patches that overhang the image on both axes, every destination.
+    (2, 128, 20, 20, 160, 3, 3, 1, 1, 1, 1, 1, 1, 1, U8, "s8", True, True, 128, True),
+    (1, 256, 28, 28, 96, 3, 3, 1, 1, 2, 2, 2, 2, 1, S8, "u8", True, True, -6, True),
+    (2, 256, 17, 13, 64, 5, 3, 1, 1, 1, 1, 2, 0, 2, U8, "f16", True, True, None, True),
+    (1, 128, 30, 30, 40, 1, 1, 1, 1, 1, 1, 1, 1, 1, U8, "f32", True, False, 128, True),
+    (3, 128, 9, 40, 256, 3, 3, 1, 1, 1, 1, 1, 1, 1, S8, "s8", True, True, 0, True),
+    (1, 384, 56, 56, 128, 3, 3, 1, 1, 1, 1, 1, 1, 1, U8, "s8", True, True, 77, True),
 ]
+IMPLICIT = list(range(len(CASES) - 6, len(CASES)))
 
 
 def _make(case, seed):
@@ -98,7 +108,21 @@ def test_conv2d_i8_matches_cpu_route(cuda_device, idx):
     _same(got, want)
 
 
-@pytest.mark.parametrize("idx", [3, 11, 16, 18, 21, 23, 24])
+@pytest.mark.parametrize("idx", IMPLICIT + [17])
+def test_implicit_form_equals_gather_form(cuda_device, idx, knobs):
+    """The implicit-GEMM form (4-D TMA boxes of the activation, zeros outside the image, the zero
+    point's share added back for overhanging windows) against the gather pass + GEMM on the same
+    bytes, and its workspace: no gathered copy."""
+    import ctypes as C
+    x, w, kwargs = _make(CASES[idx], 300 + idx)
+    x_t, w_t = torch.from_numpy(x).to(cuda_device), torch.from_numpy(w).to(cuda_device)
+    implicit = _gpu(x_t, w_t, kwargs)
+    knobs("conv_form", 1)
+    _same(_gpu(x_t, w_t, kwargs), implicit)
+    _same(implicit, oracle.conv2d_i8(x, w, **kwargs))
+
+
+@pytest.mark.parametrize("idx", [3, 11, 16, 18, 21, 23, 24] + IMPLICIT[:3])
 def test_packed_filter_is_bit_identical(cuda_device, idx):
     """The packed filter holds the bytes the per-call filter pass would write: same output
     (tests/test_cuda_conv2d.cpp:531-650, `cuda_conv2d_i8_packed_filter`)."""
@@ -173,7 +197,7 @@ def test_refusals_launch_nothing(cuda_device):
 
     before = lib.nnb200_launch_count()
     assert lib.nnb200_conv2d_i8(C.byref(args(out_kind=0)), None) == capi.UNSUPPORTED       # s32 destination
-    assert lib.nnb200_conv2d_i8(C.byref(args(oh=11)), None) == capi.INVALID_ARGUMENT         # windows start below the image
+    assert lib.nnb200_conv2d_i8(C.byref(args(oh=16)), None) == capi.INVALID_ARGUMENT         # windows start far below the image
     assert lib.nnb200_conv2d_i8(C.byref(args(groups=3)), None) == capi.INVALID_ARGUMENT
     assert lib.nnb200_conv2d_i8(C.byref(args(out_stride_h=80)), None) == capi.UNSUPPORTED    # rows at two pitches
     assert lib.nnb200_conv2d_i8(C.byref(args(workspace_bytes=16)), None) == capi.INVALID_ARGUMENT
