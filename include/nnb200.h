@@ -275,7 +275,8 @@ NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double
  *   I8_SHARE_K       0 never share K among SMs in the few-row engine, 2 offer it from 8 K blocks per SM
  *   Q4_GEMV          Q4_1 GEMV engine of the automatic choice: 1 never the deferred-scaling kernel, 2 that
  *                    kernel whenever it can run (default: for a single activation row)
- *   CONV_FORM        1 = nnb200_conv2d_i8 never takes its implicit-GEMM form (gather pass + GEMM always)
+ *   CONV_FORM        1 = nnb200_conv2d_i8 never takes its implicit-GEMM form (gather pass + GEMM always),
+ *                    2 = that form wherever it can run, small and heavily padded planes included
  */
 #define NNB200_KNOB_GROUP_M 0
 #define NNB200_KNOB_I8_BN 1

@@ -238,23 +238,32 @@ __global__ void __launch_bounds__(256) conv_filter_sums_kernel(const int8_t* __r
 }
 
 // Per-tap channel sums of the k-major filter: wtap[tap][channel] = sum over the tap's icg
-// weights.  The implicit-GEMM form adds zp_x * wtap back for taps that fall outside the image.
+// weights (icg a multiple of 4: the implicit-GEMM form, which is what reads them, has whole
+// 128-channel blocks).  One warp per channel, coalesced 4-byte reads, one reduction per tap.
 __global__ void __launch_bounds__(256) conv_filter_tap_sums_kernel(const int8_t* __restrict__ wt, const int64_t oc,
                                                                    const int32_t kp, const int32_t icg, const int32_t taps,
                                                                    int32_t* __restrict__ wtap)
 {
-    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= oc * taps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t channel = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (channel >= oc) {
         return;
     }
-    const int64_t channel = idx / taps;
-    const int32_t tap = static_cast<int32_t>(idx - channel * taps);
-    const int8_t* src = wt + channel * kp + static_cast<int64_t>(tap) * icg;
-    int32_t sum = 0;
-    for (int32_t c = 0; c < icg; ++c) {
-        sum += src[c];
+    const int32_t* row = reinterpret_cast<const int32_t*>(wt + channel * kp);
+    const int32_t words = icg >> 2;
+    for (int32_t tap = 0; tap < taps; ++tap) {
+        int32_t sum = 0;
+        for (int32_t i = lane; i < words; i += 32) {
+            sum = __dp4a(row[tap * words + i], 0x01010101, sum);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+        }
+        if (lane == 0) {
+            wtap[static_cast<int64_t>(tap) * oc + channel] = sum;
+        }
     }
-    wtap[static_cast<int64_t>(tap) * oc + channel] = sum;
 }
 
 // Border-class table of the implicit-GEMM form: row (i, j) = sum of the per-tap channel sums
@@ -350,13 +359,14 @@ bool implicit_form(const nnb200_conv2d_i8_args* a, const ConvGeom& g)
     if (knob(NNB200_KNOB_CONV_FORM) == 1) {
         return false;   // measurement switch: always the gather pass + GEMM
     }
+    const bool any_size = knob(NNB200_KNOB_CONV_FORM) == 2;   // ... or this form wherever it can run
     const bool zp_w_zero = a->zp_w_scalar == 0 && (a->zp_w == nullptr || a->zp_w_nonzero == 0);
     // Patches of 128 pixels must not pad a small image by more than half again of its pixels.
     int64_t padded = 0;
     conv_patch_log2(static_cast<int>(g.oh), static_cast<int>(g.ow), &padded);
     // ... and small planes (14 x 14 measured a little slower than the gather form, 28 x 28 the
     // same, 56 x 56 1.4x and 112 x 112 1.7x faster) stay on the gather form.
-    if (g.oh > 65536 || g.ow > 65536 || padded * 2 > g.oh * g.ow * 3 || g.oh * g.ow < 700) {
+    if (g.oh > 65536 || g.ow > 65536 || (!any_size && (padded * 2 > g.oh * g.ow * 3 || g.oh * g.ow < 700))) {
         return false;
     }
     if (a->zp_x != 0 && g.kh <= 32 && g.kw <= 32) {
@@ -485,8 +495,7 @@ int launch_conv_filter_kmajor(const void* w, int64_t w_kh, int64_t w_kw, int64_t
         note_launch();
     }
     if (wtap != nullptr) {
-        const int64_t items = oc * kh * kw;
-        conv_filter_tap_sums_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, stream>>>(
+        conv_filter_tap_sums_kernel<<<static_cast<unsigned>((oc + 7) / 8), 256, 0, stream>>>(
             f.wt, oc, f.kp, f.icg, static_cast<int32_t>(kh * kw), wtap);
         note_launch();
     }
@@ -531,8 +540,10 @@ int nnb200_conv2d_i8_pack(const void* weight, int64_t w_stride_kh, int64_t w_str
     uint8_t* after = static_cast<uint8_t*>(blob) + align256(static_cast<size_t>(oc * kp));
     int32_t* sums = reinterpret_cast<int32_t*>(after);
     int32_t* wtap = reinterpret_cast<int32_t*>(after + align256(static_cast<size_t>(oc) * 4));
+    // The per-tap sums serve the implicit-GEMM form only (whole 128-channel blocks per group).
     return launch_conv_filter_kmajor(weight, w_stride_kh, w_stride_kw, w_stride_ic, w_stride_oc, kh, kw, ic_per_group,
-                                     oc / groups, groups, blob, sums, wtap, static_cast<cudaStream_t>(stream));
+                                     oc / groups, groups, blob, sums, ic_per_group % 128 == 0 ? wtap : nullptr,
+                                     static_cast<cudaStream_t>(stream));
 }
 
 int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* a, void* stream_v)

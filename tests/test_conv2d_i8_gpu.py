@@ -116,8 +116,28 @@ def test_implicit_form_equals_gather_form(cuda_device, idx, knobs):
     import ctypes as C
     x, w, kwargs = _make(CASES[idx], 300 + idx)
     x_t, w_t = torch.from_numpy(x).to(cuda_device), torch.from_numpy(w).to(cuda_device)
+    lib = capi.lib()
+
+    def scratch():
+        n, ih, iw, ic = x.shape
+        kh, kw, icg, oc = w.shape
+        oh, ow = ops.conv2d_out_hw(ih, iw, kh, kw, kwargs["stride"], kwargs["dilation"], kwargs["padding"])
+        a = capi.Conv2dI8Args(input=x_t.data_ptr(), weight=w_t.data_ptr(), out=x_t.data_ptr(), batch=n, ih=ih, iw=iw, ic=ic,
+                              oh=oh, ow=ow, oc=oc, kh=kh, kw=kw, stride_h=1, stride_w=1, dil_h=kwargs["dilation"][0],
+                              dil_w=kwargs["dilation"][1], pad_h=kwargs["padding"][0], pad_w=kwargs["padding"][1],
+                              groups=kwargs["groups"], in_stride_n=ih * iw * ic, in_stride_h=iw * ic, in_stride_w=ic,
+                              in_stride_c=1, w_stride_kh=kw * icg * oc, w_stride_kw=icg * oc, w_stride_ic=oc, w_stride_oc=1,
+                              out_stride_n=oh * ow * oc, out_stride_h=ow * oc, out_stride_w=oc, out_kind=1,
+                              zp_x=kwargs["zp_x"])
+        return lib.nnb200_conv2d_i8_workspace_bytes(C.byref(a)), n * oh * ow * kh * kw * icg * kwargs["groups"]
+
+    knobs("conv_form", 2)         # the implicit form wherever it can run, whatever the plane size
+    need, col = scratch()
+    assert need < col             # no gathered copy in the plan
     implicit = _gpu(x_t, w_t, kwargs)
-    knobs("conv_form", 1)
+    knobs("conv_form", 1)         # never
+    need, col = scratch()
+    assert need >= col
     _same(_gpu(x_t, w_t, kwargs), implicit)
     _same(implicit, oracle.conv2d_i8(x, w, **kwargs))
 
