@@ -564,6 +564,13 @@ int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* a, void* stream_v)
     if (a->weight_packed && reinterpret_cast<uintptr_t>(a->weight) % 16 != 0) {
         return NNB200_INVALID_ARGUMENT;
     }
+    // Natural alignment of the arrays the kernels read as 2- or 4-byte words: refused here
+    // instead of faulting on the GPU.
+    const auto misaligned = [](const void* q, uintptr_t to) { return (reinterpret_cast<uintptr_t>(q) & (to - 1)) != 0; };
+    if (misaligned(a->scale_w, 4) || misaligned(a->zp_w, 4) ||
+        misaligned(a->bias, a->out_kind == NNB200_OUT_F16 ? 2 : 4)) {
+        return NNB200_INVALID_ARGUMENT;
+    }
     if (g.pixels == 0) {
         return NNB200_OK;
     }

@@ -80,3 +80,33 @@ def test_knobs_round_trip(nnb200_lib):
     assert capi.set_knob("i8_bn", -5) == 192
     assert nnb200_lib.nnb200_get_knob(capi.KNOBS["i8_bn"]) == -1
     assert nnb200_lib.nnb200_set_knob(99, 1) == -(2 ** 31)
+
+
+def test_conv_arguments_are_checked_before_any_launch(nnb200_lib):
+    """nnb200_conv2d_i8 without a GPU: geometry that is no convolution, null or misaligned pointers and a
+    missing workspace are refused with a status, nothing is launched."""
+    from nnops_b200 import capi
+    base = 0x7000_0000_1000            # never dereferenced: validation comes first
+
+    def block(**over):
+        a = capi.Conv2dI8Args(input=base, weight=base + 0x10000, out=base + 0x20000, batch=1, ih=8, iw=8, ic=16, oh=8,
+                              ow=8, oc=8, kh=3, kw=3, stride_h=1, stride_w=1, dil_h=1, dil_w=1, pad_h=1, pad_w=1,
+                              groups=1, in_stride_n=1024, in_stride_h=128, in_stride_w=16, in_stride_c=1,
+                              w_stride_kh=384, w_stride_kw=128, w_stride_ic=8, w_stride_oc=1, out_stride_n=512,
+                              out_stride_h=64, out_stride_w=8, out_kind=1, scale_x=1.0, scale_w_scalar=1.0, out_scale=1.0)
+        for k, v in over.items():
+            setattr(a, k, v)
+        return a
+
+    before = nnb200_lib.nnb200_launch_count()
+    assert nnb200_lib.nnb200_conv2d_i8_workspace_bytes(C.byref(block())) > 0
+    assert nnb200_lib.nnb200_conv2d_i8(C.byref(block()), None) == capi.INVALID_ARGUMENT            # no workspace given
+    assert nnb200_lib.nnb200_conv2d_i8(C.byref(block(groups=3)), None) == capi.INVALID_ARGUMENT
+    assert nnb200_lib.nnb200_conv2d_i8(C.byref(block(input=None)), None) == capi.INVALID_ARGUMENT
+    assert nnb200_lib.nnb200_conv2d_i8(C.byref(block(out_kind=0)), None) == capi.UNSUPPORTED        # s32 destination
+    assert nnb200_lib.nnb200_conv2d_i8(C.byref(block(bias=base + 2)), None) == capi.INVALID_ARGUMENT
+    assert nnb200_lib.nnb200_conv2d_i8(C.byref(block(scale_w=base + 1)), None) == capi.INVALID_ARGUMENT
+    assert nnb200_lib.nnb200_conv2d_i8(C.byref(block(batch=0)), None) == capi.OK                    # empty output
+    assert nnb200_lib.nnb200_conv2d_i8_pack(None, 1, 1, 1, 1, 3, 3, 16, 8, 1, None, None) == capi.INVALID_ARGUMENT
+    assert nnb200_lib.nnb200_conv2d_i8_pack_bytes(3, 3, 16, 8) >= 8 * 144 + 8 * 4
+    assert nnb200_lib.nnb200_launch_count() == before
