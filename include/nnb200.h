@@ -269,7 +269,8 @@ NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double
  *   I8_BN            force its tile width: 64, 128, 192, 224, 256, 320, 384, 448 or 512
  *   I8_PAIR          0 single-CTA form only, 2 CTA-pair form whatever the shape, or an error (default: pair form
  *                    where it pays);
- *                    1 / 3 earlier pair forms kept for comparison (one k-block per barrier slot / two commits)
+ *                    1 / 3 earlier pair forms kept for comparison (one k-block per barrier slot / two commits);
+ *                    0 also keeps the implicit-GEMM convolution on single CTAs
  *   I8_PEER_STAGING  1 / 2 staging tiles per epilogue warp in the sharded write-back
  *   F16_PAIR         as I8_PAIR for the dense f16 GEMM of the Q4_1 two-pass form
  *   I8_SHARE_K       0 never share K among SMs in the few-row engine, 2 offer it from 8 K blocks per SM
@@ -277,6 +278,8 @@ NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double
  *                    kernel whenever it can run (default: for a single activation row)
  *   CONV_FORM        1 = nnb200_conv2d_i8 never takes its implicit-GEMM form (gather pass + GEMM always),
  *                    2 = that form wherever it can run, small and heavily padded planes included
+ *   I8_K_ROTATE      tile t of the int8 tensor-core GEMM starts its walk over the 128-byte K blocks at block
+ *                    (t * value) mod blocks; 0 = every tile at block 0 (default: 5 up to 4096 weight rows, else 0)
  */
 #define NNB200_KNOB_GROUP_M 0
 #define NNB200_KNOB_I8_BN 1
@@ -286,7 +289,8 @@ NNB200_API int nnb200_measure_i8_mma_peak(int32_t iters, int32_t pattern, double
 #define NNB200_KNOB_I8_SHARE_K 5
 #define NNB200_KNOB_Q4_GEMV 6
 #define NNB200_KNOB_CONV_FORM 7
-#define NNB200_KNOB_COUNT 8
+#define NNB200_KNOB_I8_K_ROTATE 8
+#define NNB200_KNOB_COUNT 9
 NNB200_API int nnb200_set_knob(int knob, int value);
 NNB200_API int nnb200_get_knob(int knob);
 

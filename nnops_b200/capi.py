@@ -22,7 +22,7 @@ Q4_ENGINES = {"auto": 0, "gemm": 1, "gemv": 2, "gemv_simt": 3, "gemv_mma": 4, "g
 STATIC_SCRATCH_BYTES = 1 << 20
 # Measurement / test switches (NNB200_KNOB_* in nnb200.h); process-wide, negative = default.
 KNOBS = {"group_m": 0, "i8_bn": 1, "i8_pair": 2, "i8_peer_staging": 3, "f16_pair": 4, "i8_share_k": 5, "q4_gemv": 6,
-         "conv_form": 7}
+         "conv_form": 7, "i8_k_rotate": 8}
 
 
 class GemmI8Args(C.Structure):

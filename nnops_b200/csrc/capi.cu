@@ -118,7 +118,7 @@ PeerPoison peer_poison_for_current_device(bool create)
 }
 
 namespace {
-std::atomic<int> g_knobs[NNB200_KNOB_COUNT] = {{-1}, {-1}, {-1}, {-1}, {-1}, {-1}, {-1}, {-1}};
+std::atomic<int> g_knobs[NNB200_KNOB_COUNT] = {{-1}, {-1}, {-1}, {-1}, {-1}, {-1}, {-1}, {-1}, {-1}};
 }
 
 int knob(int id)

@@ -29,6 +29,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 #include <mutex>
 
 #include "internal.cuh"
@@ -77,7 +78,91 @@ struct ConvTile {
     int32_t nh, nw;
     uint32_t mask_h[8], mask_w[8];
     const int32_t* border;         // [(nh + 1) * (nw + 1)][wtap_ld], at this group's first column
+    int32_t m_tiles;               // patches in all (batch * tiles_h * tiles_w)
 };
+
+// Patch m_blk = (image, th, tw); a patch index past m_tiles (the second half of an odd pair)
+// decodes to an image past the batch: its loads are all fill, its rows are not stored.
+struct ConvPatch {
+    int img, th, tw;
+};
+
+__device__ __forceinline__ ConvPatch conv_patch(const ConvTile& conv, int m_blk)
+{
+    ConvPatch p;
+    p.tw = m_blk % conv.tiles_w;
+    const int t2 = m_blk / conv.tiles_w;
+    p.th = t2 % conv.tiles_h;
+    p.img = t2 / conv.tiles_h;
+    return p;
+}
+
+// Row r of a patch: its output pixel's flat index, whether it exists, and -- with a non-zero
+// activation zero point -- the row's border class along each axis (0: every tap inside).
+struct ConvRow {
+    int64_t m;
+    bool ok;
+    uint32_t bad_h, bad_w;
+};
+
+__device__ __forceinline__ ConvRow conv_row(const ConvTile& conv, int m_blk, int r)
+{
+    const ConvPatch p = conv_patch(conv, m_blk);
+    const int y = p.th * conv.bh + (r >> conv.bw_log2);
+    const int x = (p.tw << conv.bw_log2) + (r & ((1 << conv.bw_log2) - 1));
+    ConvRow o;
+    o.ok = m_blk < conv.m_tiles && y < conv.oh && x < conv.ow;
+    o.m = (static_cast<int64_t>(p.img) * conv.oh + y) * conv.ow + x;
+    o.bad_h = 0;
+    o.bad_w = 0;
+    if (conv.zp_x != 0 && o.ok) {
+        uint32_t lost_h = 0, lost_w = 0;
+        for (int a = 0; a < conv.kh; ++a) {
+            const int iy = y - conv.ph + a * conv.dh;
+            lost_h |= (iy < 0 || iy >= conv.ih) ? (1u << a) : 0u;
+        }
+        for (int b = 0; b < conv.kw; ++b) {
+            const int ix = x - conv.pw + b * conv.dw;
+            lost_w |= (ix < 0 || ix >= conv.iw) ? (1u << b) : 0u;
+        }
+        // 1 + index of the mask among the axis's classes (0 = no tap lost).
+        for (int q = 0; q < conv.nh; ++q) {
+            o.bad_h = (lost_h != 0 && conv.mask_h[q] == lost_h) ? static_cast<uint32_t>(q + 1) : o.bad_h;
+        }
+        for (int q = 0; q < conv.nw; ++q) {
+            o.bad_w = (lost_w != 0 && conv.mask_w[q] == lost_w) ? static_cast<uint32_t>(q + 1) : o.bad_w;
+        }
+    }
+    return o;
+}
+
+// A tap outside the image was loaded as 0 where the reference's gather holds the zero point:
+// add zp_x * (that tap's channel sum of the filter) back, from the row's class in the table.
+__device__ __forceinline__ void conv_border_fix(const ConvTile& conv, uint32_t (&v)[32], uint32_t bad_h, uint32_t bad_w,
+                                                int n0, int n_total)
+{
+    if ((bad_h | bad_w) == 0) {
+        return;
+    }
+    const int32_t* tb = conv.border + static_cast<int64_t>(bad_h * (conv.nw + 1) + bad_w) * conv.wtap_ld + n0;
+    if (n0 + 32 <= n_total && (reinterpret_cast<uintptr_t>(tb) & 15u) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const int4 t4 = __ldg(reinterpret_cast<const int4*>(tb + j));
+            v[j] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.x);
+            v[j + 1] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.y);
+            v[j + 2] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.z);
+            v[j + 3] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.w);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (n0 + j < n_total) {
+                v[j] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(tb[j]);
+            }
+        }
+    }
+}
 
 template <int BN, int PEERS = 0>
 struct TileConfig {
@@ -116,21 +201,60 @@ struct TileCoord {
     int n_blk;
 };
 
+// Where a tile's walk over the K blocks starts.  Integer accumulation does not depend on the order
+// of the K blocks, so each tile may start somewhere else: CTAs that share an operand tile (every
+// CTA of a wave when N is one tile wide, as in a convolution's GEMM) then ask the L2 for
+// different lines at any one time instead of all for the same ones.  k_rot == 0 keeps 0.
+__device__ __forceinline__ int k_rotation(int tile, int k_rot, int num_kb)
+{
+    return k_rot == 0 ? 0 : static_cast<int>((static_cast<unsigned>(tile) * static_cast<unsigned>(k_rot)) % static_cast<unsigned>(num_kb));
+}
+
+// Division of a number below 2^31 by a fixed divisor as a multiply and a shift (the GPU has no
+// integer divider: a plain `/` is a chain of some thirty dependent instructions, and the tile
+// walk below needs three of them per tile in every role's loop).
+struct FastDiv {
+    uint32_t mul, shift;
+    __device__ __forceinline__ void init(uint32_t d)
+    {
+        shift = d > 1 ? 32u - static_cast<uint32_t>(__clz(static_cast<int>(d - 1))) : 0u;
+        mul = static_cast<uint32_t>(((static_cast<uint64_t>(1) << 32) * ((static_cast<uint64_t>(1) << shift) - d)) / d + 1);
+    }
+    __device__ __forceinline__ uint32_t div(uint32_t n) const { return (__umulhi(n, mul) + n) >> shift; }
+};
+
 // Tiles are walked m-fastest inside groups of `group_m` m-blocks, groups n-fastest: the CTAs of
 // one wave then share a band of A (kept in L2 for the whole pass over N) while W streams by once
-// per group.
-__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int group_m)
-{
-    const int group_size = group_m * num_n;
-    const int group = tile / group_size;
-    const int first_m = group * group_m;
-    const int gm = min(num_m - first_m, group_m);
-    const int in_group = tile - group * group_size;
-    TileCoord c;
-    c.m_blk = first_m + in_group % gm;
-    c.n_blk = in_group / gm;
-    return c;
-}
+// per group.  The last group may hold fewer m-blocks.
+struct TileWalk {
+    int num_m, group_m, group_size, last_gm;
+    FastDiv by_group, by_gm, by_last_gm;
+    __device__ __forceinline__ TileWalk(int num_m_, int num_n, int group_m_)
+    {
+        num_m = num_m_;
+        group_m = group_m_ < num_m_ ? group_m_ : (num_m_ > 0 ? num_m_ : 1);
+        group_size = group_m * num_n;
+        const int groups = (num_m + group_m - 1) / group_m;
+        last_gm = num_m - (groups - 1) * group_m;
+        last_gm = last_gm > 0 ? last_gm : 1;
+        by_group.init(static_cast<uint32_t>(group_size > 0 ? group_size : 1));
+        by_gm.init(static_cast<uint32_t>(group_m));
+        by_last_gm.init(static_cast<uint32_t>(last_gm));
+    }
+    __device__ __forceinline__ TileCoord operator()(int tile) const
+    {
+        const int group = static_cast<int>(by_group.div(static_cast<uint32_t>(tile)));
+        const int first_m = group * group_m;
+        const int in_group = tile - group * group_size;
+        const bool last = num_m - first_m < group_m;
+        const int gm = last ? last_gm : group_m;
+        TileCoord c;
+        c.n_blk = static_cast<int>(last ? by_last_gm.div(static_cast<uint32_t>(in_group))
+                                        : by_gm.div(static_cast<uint32_t>(in_group)));
+        c.m_blk = first_m + in_group - c.n_blk * gm;
+        return c;
+    }
+};
 
 // The per-column terms of the epilogue as one epilogue warp stages them in shared memory.
 struct ColTerms {
@@ -140,33 +264,56 @@ struct ColTerms {
     int32_t zpw;     // zp_w[n]
 };
 
-// fold_comp: a per-tensor activation zero point against weights whose zero points are all 0 -- the
-// only live compensation term is -zp_a * R_w[n], a column constant, and goes into the bias.
+// The loads only, so that they can be issued a tile ahead: nothing here depends on a loaded
+// value (an f16 bias stays as its 16 bits).  finish_col_terms() does the arithmetic when the
+// terms are staged.
 template <int KIND>
-__device__ __forceinline__ ColTerms load_col_terms(const I8Epilogue& ep, int n, int n_total, bool fold_scale,
-                                                   float folded_row_k, bool fold_comp)
+__device__ __forceinline__ ColTerms load_col_terms(const I8Epilogue& ep, int n, int n_total)
 {
     ColTerms c;
     const bool in = n < n_total;
-    const float s_w = (in && ep.scale_w != nullptr) ? ep.scale_w[n] : ep.scale_w_scalar;
-    c.scale = fold_scale ? __fmul_rn(folded_row_k, s_w) : s_w;
-    int32_t b = 0;
+    c.scale = ep.scale_w_scalar;
+    if (in && ep.scale_w != nullptr) {
+        c.scale = ep.scale_w[n];
+    }
+    c.bias = 0;
     if (in && ep.bias != nullptr) {
         if constexpr (KIND <= NNB200_OUT_U8) {
-            b = static_cast<const int32_t*>(ep.bias)[n];
+            c.bias = static_cast<const int32_t*>(ep.bias)[n];
         } else if constexpr (KIND == NNB200_OUT_F32) {
-            b = __float_as_int(static_cast<const float*>(ep.bias)[n]);
+            c.bias = __float_as_int(static_cast<const float*>(ep.bias)[n]);
         } else {
-            b = __float_as_int(__half2float(static_cast<const __half*>(ep.bias)[n]));
+            c.bias = static_cast<int32_t>(static_cast<const uint16_t*>(ep.bias)[n]);
         }
     }
-    c.rw = (in && ep.compensate && ep.r_w != nullptr) ? ep.r_w[n] : 0;
-    c.zpw = (in && ep.zp_w != nullptr) ? ep.zp_w[n] : ep.zp_w_scalar;
-    if (fold_comp) {
-        b = static_cast<int32_t>(static_cast<uint32_t>(b) -
-                                 static_cast<uint32_t>(ep.zp_a_scalar) * static_cast<uint32_t>(c.rw));
+    c.rw = 0;
+    if (in && ep.compensate && ep.r_w != nullptr) {
+        c.rw = ep.r_w[n];
     }
-    c.bias = b;
+    c.zpw = ep.zp_w_scalar;
+    if (in && ep.zp_w != nullptr) {
+        c.zpw = ep.zp_w[n];
+    }
+    return c;
+}
+
+// fold_scale: the per-tensor row factor s_a / s_out goes into the column scale.
+// fold_comp: a per-tensor activation zero point against weights whose zero points are all 0 -- the
+// only live compensation term is -zp_a * R_w[n], a column constant, and goes into the bias.
+template <int KIND>
+__device__ __forceinline__ ColTerms finish_col_terms(const I8Epilogue& ep, ColTerms c, bool fold_scale, float folded_row_k,
+                                                     bool fold_comp)
+{
+    if (fold_scale) {
+        c.scale = __fmul_rn(folded_row_k, c.scale);
+    }
+    if constexpr (KIND == NNB200_OUT_F16) {
+        c.bias = __float_as_int(__half2float(__ushort_as_half(static_cast<unsigned short>(c.bias))));
+    }
+    if (fold_comp) {
+        c.bias = static_cast<int32_t>(static_cast<uint32_t>(c.bias) -
+                                      static_cast<uint32_t>(ep.zp_a_scalar) * static_cast<uint32_t>(c.rw));
+    }
     return c;
 }
 
@@ -253,25 +400,34 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
             // carry (s_a / s_out) * s_w[n].  The column terms are read four at a time.
             (void)lo;
             (void)hi;
-            const bool zp0 = e.out_zp == 0;
+            // Branch-free per element: the run-time switches become operands (a lower bound for
+            // the ReLU, a row factor of exactly 1 when the scale is already folded -- x * 1.0f is
+            // x), and the zero-point variant is chosen once per chunk.
+            const int32_t relu_lo = e.relu ? 0 : INT32_MIN;
+            const float row_k = scale_folded ? 1.0f : t.row_k;
+            const auto body = [&](auto zp0_tag) {
+                constexpr bool kZp0 = decltype(zp0_tag)::value;
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-                const int4 b4 = *reinterpret_cast<const int4*>(col_bias + j);
-                const float4 s4 = *reinterpret_cast<const float4*>(col_scale + j);
-                const int32_t bias4[4] = {b4.x, b4.y, b4.z, b4.w};
-                const float scale4[4] = {s4.x, s4.y, s4.z, s4.w};
-                int32_t v[4];
-                float req[4];
+                for (int j = 0; j < 32; j += 4) {
+                    const int4 b4 = *reinterpret_cast<const int4*>(col_bias + j);
+                    const float4 s4 = *reinterpret_cast<const float4*>(col_scale + j);
+                    const int32_t bias4[4] = {b4.x, b4.y, b4.z, b4.w};
+                    const float scale4[4] = {s4.x, s4.y, s4.z, s4.w};
+                    int32_t v[4];
+                    float req[4];
 #pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    v[b] = static_cast<int32_t>(static_cast<uint32_t>(acc[j + b]) + static_cast<uint32_t>(bias4[b]));
-                    if (e.relu && v[b] < 0) {
-                        v[b] = 0;
+                    for (int b = 0; b < 4; ++b) {
+                        v[b] = max(static_cast<int32_t>(static_cast<uint32_t>(acc[j + b]) + static_cast<uint32_t>(bias4[b])),
+                                   relu_lo);
+                        req[b] = __fmul_rn(row_k, scale4[b]);
                     }
-                    req[b] = scale_folded ? scale4[b] : __fmul_rn(t.row_k, scale4[b]);
+                    packed[j / 4] = requant_pack4<KIND == NNB200_OUT_U8, kZp0>(v, req, e.out_zp);
                 }
-                packed[j / 4] = zp0 ? requant_pack4<KIND == NNB200_OUT_U8, true>(v, req, 0)
-                                    : requant_pack4<KIND == NNB200_OUT_U8, false>(v, req, e.out_zp);
+            };
+            if (e.out_zp == 0) {
+                body(std::true_type{});
+            } else {
+                body(std::false_type{});
             }
         } else {
 #pragma unroll
@@ -376,7 +532,7 @@ template <int BN, int KIND, int PEERS, bool CONV = false>
 __global__ void __launch_bounds__(kMaxThreads, 1)
 gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ PeerMaps peer_maps, const I8Epilogue ep, const int m_total,
-                    const int n_total, const int k_total, const uint32_t idesc, const int vec_ok, const int group_m,
+                    const int n_total, const int k_total, const uint32_t idesc, const int vec_ok, const int group_m, const int k_rot,
                     int32_t* error_word, const ConvTile conv)
 {
     static_assert(!CONV || PEERS == 0, "the convolution form has no sharded epilogue");
@@ -407,6 +563,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int num_n = (n_total + BN - 1) / BN;
     const int num_tiles = num_m * num_n;
     const int num_kb = (k_total + kBlockKBytes - 1) / kBlockKBytes;
+    const TileWalk walk(num_m, num_n, group_m);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -442,8 +599,10 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t armed_phase = 0;  // bit s: parity of the phase slot s was last armed in
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const TileCoord tc = walk(tile);
+                const int rot = k_rotation(tile, k_rot, num_kb);
+                for (int step = 0; step < num_kb; ++step) {
+                    const int kb = step + rot < num_kb ? step + rot : step + rot - num_kb;
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         atomicCAS(error_word, 0, kErrProducerWait);
                         ok = false;
@@ -454,16 +613,14 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
                     if constexpr (CONV) {
                         // Patch (image, th, tw) shifted by the k-block's tap; 128 channels of it.
-                        const int tw = tc.m_blk % conv.tiles_w;
-                        const int t2 = tc.m_blk / conv.tiles_w;
-                        const int th = t2 % conv.tiles_h;
-                        const int img = t2 / conv.tiles_h;
+                        const ConvPatch pt = conv_patch(conv, tc.m_blk);
                         const int tap = kb / conv.kb_per_tap;
                         const int c0 = (kb - tap * conv.kb_per_tap) * kBlockKBytes;
                         const int ta = tap / conv.kw;
                         const int tb = tap - ta * conv.kw;
                         tma_load_4d(a_dst, &map_a, &full_bar[stage], conv.c_base + c0,
-                                    (tw << conv.bw_log2) - conv.pw + tb * conv.dw, th * conv.bh - conv.ph + ta * conv.dh, img);
+                                    (pt.tw << conv.bw_log2) - conv.pw + tb * conv.dw,
+                                    pt.th * conv.bh - conv.ph + ta * conv.dh, pt.img);
                     } else if (pose & 1) {
                         // A stored [K][M]: the box is 128 k-rows of 128 m-bytes.
                         tma_load_2d(a_dst, &map_a, &full_bar[stage], tc.m_blk * kBlockM, kb * kBlockKBytes);
@@ -597,7 +754,7 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         (void)stage_turn;
         int local_tile = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
-            const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
+            const TileCoord tc = walk(tile);
             const int acc = Cfg::kNSplit > 1 ? 0 : (local_tile & 1);
             const uint32_t acc_phase = Cfg::kNSplit > 1 ? (local_tile & 1u) : ((local_tile >> 1) & 1u);
             const int n_base = tc.n_blk * BN + col0;   // first column this warp drains
@@ -609,9 +766,9 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int i = 0; i < kTermIters; ++i) {
                 const int j = lane + i * 32;
                 if (j < ncols) {
-                    const ColTerms ct = (kPrefetch && local_tile > 0)
-                                            ? next_terms[kPrefetch ? i : 0]
-                                            : load_col_terms<KIND>(ep, n_base + j, n_total, fold_scale, folded_row_k, fold_comp);
+                    const ColTerms ct = finish_col_terms<KIND>(
+                        ep, (kPrefetch && local_tile > 0) ? next_terms[kPrefetch ? i : 0] : load_col_terms<KIND>(ep, n_base + j, n_total),
+                        fold_scale, folded_row_k, fold_comp);
                     cs[j] = ct.scale;
                     cb[j] = ct.bias;
                     cr[j] = ct.rw;
@@ -624,34 +781,11 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool row_ok = m < m_total;
             uint32_t bad_h = 0, bad_w = 0;   // CONV: the row's border class along each axis (0: every tap inside)
             if constexpr (CONV) {
-                // Row r of the tile is pixel (r >> bw_log2, r & (bw - 1)) of the patch.
-                const int r = quarter * 32 + lane;
-                const int tw = tc.m_blk % conv.tiles_w;
-                const int t2 = tc.m_blk / conv.tiles_w;
-                const int th = t2 % conv.tiles_h;
-                const int img = t2 / conv.tiles_h;
-                const int y = th * conv.bh + (r >> conv.bw_log2);
-                const int x = (tw << conv.bw_log2) + (r & ((1 << conv.bw_log2) - 1));
-                row_ok = y < conv.oh && x < conv.ow;
-                m = (static_cast<int64_t>(img) * conv.oh + y) * conv.ow + x;
-                if (conv.zp_x != 0 && row_ok) {
-                    uint32_t lost_h = 0, lost_w = 0;
-                    for (int a = 0; a < conv.kh; ++a) {
-                        const int iy = y - conv.ph + a * conv.dh;
-                        lost_h |= (iy < 0 || iy >= conv.ih) ? (1u << a) : 0u;
-                    }
-                    for (int b = 0; b < conv.kw; ++b) {
-                        const int ix = x - conv.pw + b * conv.dw;
-                        lost_w |= (ix < 0 || ix >= conv.iw) ? (1u << b) : 0u;
-                    }
-                    // bad_h / bad_w: 1 + index of the mask among the axis's classes (0 = no tap lost).
-                    for (int q = 0; q < conv.nh; ++q) {
-                        bad_h = (lost_h != 0 && conv.mask_h[q] == lost_h) ? static_cast<uint32_t>(q + 1) : bad_h;
-                    }
-                    for (int q = 0; q < conv.nw; ++q) {
-                        bad_w = (lost_w != 0 && conv.mask_w[q] == lost_w) ? static_cast<uint32_t>(q + 1) : bad_w;
-                    }
-                }
+                const ConvRow cr_ = conv_row(conv, tc.m_blk, quarter * 32 + lane);
+                m = cr_.m;
+                row_ok = cr_.ok;
+                bad_h = cr_.bad_h;
+                bad_w = cr_.bad_w;
             }
             I8RowTerms rt;
             rt.zpa = 0;
@@ -672,11 +806,10 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if constexpr (kPrefetch) {
                 const int next = tile + static_cast<int>(gridDim.x);
                 if (next < num_tiles) {
-                    const int next_base = tile_coord(next, num_m, num_n, group_m).n_blk * BN + col0;
+                    const int next_base = walk(next).n_blk * BN + col0;
 #pragma unroll
                     for (int i = 0; i < kTermIters; ++i) {
-                        next_terms[i] = load_col_terms<KIND>(ep, next_base + lane + i * 32, n_total, fold_scale,
-                                                             folded_row_k, fold_comp);
+                        next_terms[i] = load_col_terms<KIND>(ep, next_base + lane + i * 32, n_total);
                     }
                 }
             }
@@ -769,42 +902,36 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             } else {
-#pragma unroll 1
-                for (int c = 0; c < ncols / 32; ++c) {
+                // Chunks of 32 columns, two register sets: the load of the next chunk is in flight
+                // while this one is requantised and stored.
+                const int left = n_total - n_base;   // columns of the matrix from this warp's first one
+                const int nch = left <= 0 ? 0 : min(ncols / 32, (left + 31) / 32);   // uniform across the warp
+                const auto finish = [&](int c, uint32_t (&v)[32]) {
                     const int n0 = n_base + c * 32;
-                    if (n0 >= n_total) {
-                        break;  // uniform across the warp
-                    }
-                    uint32_t v[32];
-                    tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
-                    tmem_ld_wait();
                     if constexpr (CONV) {
-                        // A tap outside the image was loaded as 0 where the reference's gather holds
-                        // the zero point: add zp_x * (that tap's channel sum of the filter) back.
-                        if ((bad_h | bad_w) != 0) {
-                            const int32_t* tb = conv.border +
-                                                static_cast<int64_t>(bad_h * (conv.nw + 1) + bad_w) * conv.wtap_ld + n0;
-                            if (n0 + 32 <= n_total && (reinterpret_cast<uintptr_t>(tb) & 15u) == 0) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 4) {
-                                    const int4 t4 = __ldg(reinterpret_cast<const int4*>(tb + j));
-                                    v[j] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.x);
-                                    v[j + 1] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.y);
-                                    v[j + 2] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.z);
-                                    v[j + 3] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(t4.w);
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) {
-                                    if (n0 + j < n_total) {
-                                        v[j] += static_cast<uint32_t>(conv.zp_x) * static_cast<uint32_t>(tb[j]);
-                                    }
-                                }
-                            }
-                        }
+                        conv_border_fix(conv, v, bad_h, bad_w, n0, n_total);
                     }
                     epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
                                          cz + c * 32, vec_ok, fold_scale, fold_comp);
+                };
+                uint32_t va[32], vb[32];
+                if (nch > 0) {
+                    tmem_ld_32x32(t_row, va);
+                }
+#pragma unroll 1
+                for (int c = 0; c < nch; c += 2) {
+                    tmem_ld_wait();
+                    if (c + 1 < nch) {
+                        tmem_ld_32x32(t_row + static_cast<uint32_t>((c + 1) * 32), vb);
+                    }
+                    finish(c, va);
+                    if (c + 1 < nch) {
+                        tmem_ld_wait();
+                        if (c + 2 < nch) {
+                            tmem_ld_32x32(t_row + static_cast<uint32_t>((c + 2) * 32), va);
+                        }
+                        finish(c + 1, vb);
+                    }
                 }
             }
             // Accumulator drained: hand it back to the MMA warp.
@@ -870,11 +997,12 @@ struct PairTileConfig {
     static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kColParamBytes + kBarrierBytes;
 };
 
-template <int BN, int KIND, int SUB, bool MC>
+template <int BN, int KIND, int SUB, bool MC, bool CONV = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMaxThreads, 1)
 gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const I8Epilogue ep, const int m_total, const int n_total, const int k_total,
-                         const uint32_t idesc, const int vec_ok, const int group_m, int32_t* error_word)
+                         const uint32_t idesc, const int vec_ok, const int group_m, const int k_rot,
+                         int32_t* error_word, const ConvTile conv)
 {
     using Cfg = PairTileConfig<BN>;
     // SUB consecutive 128-byte k-blocks share one pair of barriers (a "slot"): one wait, one
@@ -903,6 +1031,7 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int num_n = (n_total + BN - 1) / BN;
     const int num_tiles = num_m * num_n;
     const int num_kb = (k_total + kBlockKBytes - 1) / kBlockKBytes;
+    const TileWalk walk(num_m, num_n, group_m);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -936,9 +1065,10 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-                const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
+                const TileCoord tc = walk(tile);
                 const int m0 = tc.m_blk * kPairM + static_cast<int>(rank) * kBlockM;
                 const int n0 = tc.n_blk * BN + static_cast<int>(rank) * (BN / 2);
+                const int rot = k_rotation(tile, k_rot, num_kb);
                 for (int kb = 0; kb < num_kb; kb += SUB) {
                     if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1u, abort_flag)) {
                         atomicCAS(error_word, 0, kErrProducerWait);
@@ -955,8 +1085,21 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         if (j < nsub) {
                             uint8_t* a_dst = stage_base + stage * kSlotBytes + j * Cfg::kStageBytes;
                             uint8_t* b_dst = a_dst + Cfg::kATileBytes;
-                            tma_load_2d_pair(a_dst, &map_a, leader_full, (kb + j) * kBlockKBytes, m0);
-                            tma_load_2d_pair(b_dst, &map_w, leader_full, (kb + j) * kBlockKBytes, n0);
+                            const int kx = kb + j + rot < num_kb ? kb + j + rot : kb + j + rot - num_kb;
+                            if constexpr (CONV) {
+                                // This CTA's patch of the pair (2 * m_blk + rank), shifted by the k-block's tap.
+                                const ConvPatch pt = conv_patch(conv, 2 * tc.m_blk + static_cast<int>(rank));
+                                const int tap = kx / conv.kb_per_tap;
+                                const int c0 = (kx - tap * conv.kb_per_tap) * kBlockKBytes;
+                                const int ta = tap / conv.kw;
+                                const int tb = tap - ta * conv.kw;
+                                tma_load_4d_pair(a_dst, &map_a, leader_full, conv.c_base + c0,
+                                                 (pt.tw << conv.bw_log2) - conv.pw + tb * conv.dw,
+                                                 pt.th * conv.bh - conv.ph + ta * conv.dh, pt.img);
+                            } else {
+                                tma_load_2d_pair(a_dst, &map_a, leader_full, kx * kBlockKBytes, m0);
+                            }
+                            tma_load_2d_pair(b_dst, &map_w, leader_full, kx * kBlockKBytes, n0);
                         }
                     }
                     if (++stage == kStages) {
@@ -1050,7 +1193,7 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         int32_t* cz = cr + kHalf0;
         int local_tile = 0;
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
-            const TileCoord tc = tile_coord(tile, num_m, num_n, group_m);
+            const TileCoord tc = walk(tile);
             const int acc = local_tile & 1;
             const uint32_t acc_phase = (local_tile >> 1) & 1u;
             const int n_base = tc.n_blk * BN + col0;   // first column this warp drains
@@ -1062,9 +1205,9 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             for (int i = 0; i < kTermIters; ++i) {
                 const int j = lane + i * 32;
                 if (j < ncols) {
-                    const ColTerms ct = local_tile > 0 ? next_terms[i]
-                                                       : load_col_terms<KIND>(ep, n_base + j, n_total, fold_scale,
-                                                                              folded_row_k, fold_comp);
+                    const ColTerms ct = finish_col_terms<KIND>(
+                        ep, local_tile > 0 ? next_terms[i] : load_col_terms<KIND>(ep, n_base + j, n_total), fold_scale,
+                        folded_row_k, fold_comp);
                     cs[j] = ct.scale;
                     cb[j] = ct.bias;
                     cr[j] = ct.rw;
@@ -1073,9 +1216,17 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
             __syncwarp();
 
-            const int64_t m = static_cast<int64_t>(tc.m_blk) * kPairM + static_cast<int64_t>(rank) * kBlockM +
-                              quarter * 32 + lane;
-            const bool row_ok = m < m_total;
+            int64_t m = static_cast<int64_t>(tc.m_blk) * kPairM + static_cast<int64_t>(rank) * kBlockM +
+                        quarter * 32 + lane;
+            bool row_ok = m < m_total;
+            uint32_t bad_h = 0, bad_w = 0;   // CONV: the row's border class along each axis
+            if constexpr (CONV) {
+                const ConvRow cr_ = conv_row(conv, 2 * tc.m_blk + static_cast<int>(rank), quarter * 32 + lane);
+                m = cr_.m;
+                row_ok = cr_.ok;
+                bad_h = cr_.bad_h;
+                bad_w = cr_.bad_w;
+            }
             I8RowTerms rt;
             rt.zpa = 0;
             rt.ra = 0;
@@ -1100,28 +1251,46 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 // The next tile's column terms, in flight while this tile is drained.
                 const int next = tile + num_pairs;
                 if (next < num_tiles) {
-                    const int next_base = tile_coord(next, num_m, num_n, group_m).n_blk * BN + col0;
+                    const int next_base = walk(next).n_blk * BN + col0;
 #pragma unroll
                     for (int i = 0; i < kTermIters; ++i) {
-                        next_terms[i] = load_col_terms<KIND>(ep, next_base + lane + i * 32, n_total, fold_scale,
-                                                             folded_row_k, fold_comp);
+                        next_terms[i] = load_col_terms<KIND>(ep, next_base + lane + i * 32, n_total);
                     }
                 }
             }
 
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(acc * 256 + col0);
-#pragma unroll 1
-            for (int c = 0; c < ncols / 32; ++c) {
+            // Chunks of 32 columns, two register sets: the load of the next chunk is in flight while
+            // this one is requantised and stored.
+            const int left = n_total - n_base;
+            const int nch = left <= 0 ? 0 : min(ncols / 32, (left + 31) / 32);   // uniform across the warp
+            const auto finish = [&](int c, uint32_t (&v)[32]) {
                 const int n0 = n_base + c * 32;
-                if (n0 >= n_total) {
-                    break;  // uniform across the warp
+                if constexpr (CONV) {
+                    conv_border_fix(conv, v, bad_h, bad_w, n0, n_total);
                 }
-                uint32_t v[32];
-                tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
-                tmem_ld_wait();
                 epilogue_chunk<KIND>(ep, rt, v, m, row_ok, n0, n_total, cs + c * 32, cb + c * 32, cr + c * 32,
                                      cz + c * 32, vec_ok, fold_scale, fold_comp);
+            };
+            uint32_t va[32], vb[32];
+            if (nch > 0) {
+                tmem_ld_32x32(t_row, va);
+            }
+#pragma unroll 1
+            for (int c = 0; c < nch; c += 2) {
+                tmem_ld_wait();
+                if (c + 1 < nch) {
+                    tmem_ld_32x32(t_row + static_cast<uint32_t>((c + 1) * 32), vb);
+                }
+                finish(c, va);
+                if (c + 1 < nch) {
+                    tmem_ld_wait();
+                    if (c + 2 < nch) {
+                        tmem_ld_32x32(t_row + static_cast<uint32_t>((c + 2) * 32), va);
+                    }
+                    finish(c + 1, vb);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -1145,6 +1314,16 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
 // CTA-pair launch: 256 x BN tiles, two CTAs per tile.  NNB200_UNSUPPORTED when the device cannot
 // co-schedule a single pair (the caller then uses the single-CTA form).
+// Step of the per-tile K rotation (see k_rotation).  Default: 5 blocks per tile index where the
+// weight has at most 4096 rows -- few column tiles, so many CTAs of a wave share each W tile
+// (measured +3..10 % there, -2 % at 8192 rows); knob I8_K_ROTATE sets it, 0 = every tile starts
+// at block 0.
+inline int k_rotation_step(int n)
+{
+    const int kn = knob(NNB200_KNOB_I8_K_ROTATE);
+    return kn >= 0 ? kn : (n <= 4096 ? 5 : 0);
+}
+
 template <int BN, int KIND, int SUB = 1, bool MC = false>
 int launch_pair_variant(const I8Problem& p, const I8Epilogue& ep, int m, int n, int k, uint32_t a_fmt, int vec_ok,
                         const DeviceInfo& dev, cudaStream_t stream)
@@ -1187,7 +1366,7 @@ int launch_pair_variant(const I8Problem& p, const I8Epilogue& ep, int m, int n, 
     group_m = group_m < 2 ? 2 : group_m;
     kernel<<<2 * pairs, num_threads(0), Cfg::kSmemBytes, stream>>>(map_a, map_w, ep, m, n, k,
                                                                umma_idesc(2, a_fmt, 1, 2 * kBlockM, BN), vec_ok, group_m,
-                                                               dev.error_word);
+                                                               k_rotation_step(n), dev.error_word, ConvTile{});
     note_launch();
     return cuda_status(cudaGetLastError());
 }
@@ -1243,7 +1422,7 @@ int launch_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8E
         group_m = knob(NNB200_KNOB_GROUP_M);
     }
     kernel<<<grid, num_threads(PEERS), kSmem, stream>>>(map_a, map_w, maps, ep, m, n, k, idesc, vec_ok, group_m,
-                                                 dev.error_word, ConvTile{});
+                                                 k_rotation_step(n), dev.error_word, ConvTile{});
     note_launch();
     return cuda_status(cudaGetLastError());
 }
@@ -1322,9 +1501,65 @@ int launch_conv_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, cons
     int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(kBlockM) * (k > 0 ? k : 1)));
     group_m = group_m < 4 ? 4 : group_m;
     kernel<<<grid, num_threads(0), Cfg::kSmemBytes, stream>>>(map_a, map_w, maps, ep, m_tiles * kBlockM, n, k, idesc, vec_ok,
-                                                            group_m, dev.error_word, conv);
+                                                            group_m, k_rotation_step(n), dev.error_word, conv);
     note_launch();
     return cuda_status(cudaGetLastError());
+}
+
+// The CTA-pair form of the same: two patches per 256 x 256 tile, each CTA loading its own patch
+// and half of the filter rows.  NNB200_UNSUPPORTED when the device cannot co-schedule a pair.
+template <int KIND>
+int launch_conv_pair_variant(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m_tiles, int n,
+                             int k, uint32_t a_fmt, int vec_ok, const ConvTile& conv, const DeviceInfo& dev,
+                             cudaStream_t stream)
+{
+    constexpr int BN = 256;
+    using Cfg = PairTileConfig<BN>;
+    auto kernel = gemm_i8_umma_pair_kernel<BN, KIND, 2, true, true>;
+    static std::once_flag once[kMaxDevices];
+    static cudaError_t attr_err[kMaxDevices];
+    static int max_pairs[kMaxDevices];
+    std::call_once(once[dev.device], [&] {
+        attr_err[dev.device] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        max_pairs[dev.device] = 0;
+        if (attr_err[dev.device] == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(static_cast<unsigned>(dev.sm_count & ~1));
+            cfg.blockDim = dim3(num_threads(0));
+            cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+            int count = 0;
+            if (cudaOccupancyMaxActiveClusters(&count, kernel, &cfg) == cudaSuccess) {
+                max_pairs[dev.device] = count;
+            }
+        }
+    });
+    if (attr_err[dev.device] != cudaSuccess) {
+        return NNB200_INTERNAL;
+    }
+    if (max_pairs[dev.device] < 1) {
+        return NNB200_UNSUPPORTED;
+    }
+    const int num_tiles = ((m_tiles + 1) / 2) * ((n + BN - 1) / BN);
+    const int pairs = num_tiles < max_pairs[dev.device] ? num_tiles : max_pairs[dev.device];
+    int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(2 * kBlockM) * (k > 0 ? k : 1)));
+    group_m = group_m < 2 ? 2 : group_m;
+    kernel<<<2 * pairs, num_threads(0), Cfg::kSmemBytes, stream>>>(map_a, map_w, ep, m_tiles * kBlockM, n, k,
+                                                               umma_idesc(2, a_fmt, 1, 2 * kBlockM, BN), vec_ok, group_m,
+                                                               k_rotation_step(n), dev.error_word, conv);
+    note_launch();
+    return cuda_status(cudaGetLastError());
+}
+
+int launch_conv_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const I8Epilogue& ep, int m_tiles, int n, int k,
+                     uint32_t a_fmt, int vec_ok, const ConvTile& conv, const DeviceInfo& dev, cudaStream_t stream)
+{
+    switch (ep.out_kind) {
+    case NNB200_OUT_S8: return launch_conv_pair_variant<NNB200_OUT_S8>(map_a, map_w, ep, m_tiles, n, k, a_fmt, vec_ok, conv, dev, stream);
+    case NNB200_OUT_U8: return launch_conv_pair_variant<NNB200_OUT_U8>(map_a, map_w, ep, m_tiles, n, k, a_fmt, vec_ok, conv, dev, stream);
+    case NNB200_OUT_F32: return launch_conv_pair_variant<NNB200_OUT_F32>(map_a, map_w, ep, m_tiles, n, k, a_fmt, vec_ok, conv, dev, stream);
+    case NNB200_OUT_F16: return launch_conv_pair_variant<NNB200_OUT_F16>(map_a, map_w, ep, m_tiles, n, k, a_fmt, vec_ok, conv, dev, stream);
+    default: return NNB200_UNSUPPORTED;
+    }
 }
 
 template <int BN>
@@ -1372,6 +1607,7 @@ int launch_conv_i8_umma(const ConvUmmaArgs& c, const I8Epilogue& ep, const Devic
         return NNB200_UNSUPPORTED;
     }
     const int m_tiles = static_cast<int>(m_tiles64);
+    t.m_tiles = m_tiles;
     const int n = c.ocg, k = c.k;
     int bn = 256;
     if (static_cast<int64_t>(m_tiles) * ((n + 255) / 256) < dev.sm_count || n <= 128) {
@@ -1393,6 +1629,22 @@ int launch_conv_i8_umma(const ConvUmmaArgs& c, const I8Epilogue& ep, const Devic
     const uint64_t pitch_bytes = static_cast<uint64_t>(ep.ldc) * elem;
     const int vec_ok = (((reinterpret_cast<uintptr_t>(ep.out) & 15u) == 0 && (pitch_bytes & 15u) == 0) ? 1 : 0) |
                        (((reinterpret_cast<uintptr_t>(ep.out) & 31u) == 0 && (pitch_bytes & 31u) == 0) ? 2 : 0);
+    // CTA pairs (two patches per tile, half of the filter rows per CTA) where there are enough
+    // pair tiles to fill the device: a single CTA's 128 x 256 tile asks its SM for more operand
+    // bytes per clock than the L2 delivers to one SM, the pair's halves do not.  Knob I8_PAIR = 0
+    // keeps the single-CTA form.
+    if (bn == 256 && knob(NNB200_KNOB_I8_PAIR) != 0 &&
+        static_cast<int64_t>((m_tiles + 1) / 2) * ((n + 255) / 256) >= dev.sm_count / 2) {
+        CUtensorMap map_wh;
+        if (!make_tma_2d(&map_wh, c.wt, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(c.ldw),
+                         kBlockKBytes, 128u)) {
+            return NNB200_INTERNAL;
+        }
+        const int st = launch_conv_pair(map_a, map_wh, ep, m_tiles, n, k, c.a_unsigned ? 0u : 1u, vec_ok, t, dev, stream);
+        if (st != NNB200_UNSUPPORTED) {
+            return st;
+        }
+    }
     const uint32_t idesc = umma_idesc(2, c.a_unsigned ? 0u : 1u, 1, kBlockM, bn);
     switch (bn) {
     case 256: return launch_conv_bn<256>(map_a, map_w, ep, m_tiles, n, k, idesc, vec_ok, t, dev, stream);

@@ -105,6 +105,18 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
         : "memory");
 }
 
+// The same for a 4-D tensor map (an NHWC activation: {c, w, h, n}); coordinates may lie outside
+// the tensor, where the load delivers the fill value.
+__device__ __forceinline__ void tma_load_4d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int32_t x, int32_t y, int32_t z, int32_t w)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+
 // TMEM allocation for the pair: one warp of EACH of the two CTAs executes these.
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t ncols)
 {

@@ -59,8 +59,12 @@ CASES = [
     (1, 128, 30, 30, 40, 1, 1, 1, 1, 1, 1, 1, 1, 1, U8, "f32", True, False, 128, True),
     (3, 128, 9, 40, 256, 3, 3, 1, 1, 1, 1, 1, 1, 1, S8, "s8", True, True, 0, True),
     (1, 384, 56, 56, 128, 3, 3, 1, 1, 1, 1, 1, 1, 1, U8, "s8", True, True, 77, True),
+    # Enough 256-wide tiles for the CTA-pair form: an odd number of patches (the last pair's second
+    # half is past the batch), and a second column of tiles with a ragged edge.
+    (17, 128, 24, 40, 256, 3, 3, 1, 1, 1, 1, 1, 1, 1, U8, "s8", True, True, 128, True),
+    (5, 128, 56, 56, 320, 3, 3, 1, 1, 2, 2, 2, 2, 1, S8, "f16", True, True, -6, True),
 ]
-IMPLICIT = list(range(len(CASES) - 6, len(CASES)))
+IMPLICIT = list(range(len(CASES) - 8, len(CASES)))
 
 
 def _make(case, seed):
@@ -135,6 +139,9 @@ def test_implicit_form_equals_gather_form(cuda_device, idx, knobs):
     need, col = scratch()
     assert need < col             # no gathered copy in the plan
     implicit = _gpu(x_t, w_t, kwargs)
+    knobs("i8_pair", 0)           # one CTA per tile where the default pairs them
+    _same(_gpu(x_t, w_t, kwargs), implicit)
+    knobs("i8_pair", -1)
     knobs("conv_form", 1)         # never
     need, col = scratch()
     assert need >= col

@@ -232,6 +232,20 @@ def test_cta_pair_form(cuda_device, nnb200_lib, case, form, knobs):
               out_scale=0.9, out_zp=0 if kind == "s32" else 3, engine="umma", seed=m + n)
 
 
+@pytest.mark.parametrize("pair", [0, 2])
+@pytest.mark.parametrize("case", [(1100, 9000, 512 + 128 * 3, "s8", 1), (2048, 9472, 640, "s32", 5), (1024, 9728, 128, "u8", 7),
+                                  (640, 20000, 96, "f16", 3)])
+def test_k_blocks_walked_from_a_rotated_start(cuda_device, nnb200_lib, case, pair, knobs):
+    """Tiles may start their walk over the K blocks at different blocks (integer sums do not depend
+    on the order): same bytes as the oracle for single-CTA and pair tiles, odd block counts, a
+    single block, a ragged last block."""
+    m, n, k, kind, step = case
+    knobs("i8_pair", pair)
+    knobs("i8_k_rotate", step)
+    _run_case(cuda_device, m, n, k, out_kind=kind, relu=True, per_token=True, per_channel=True, zero_points=True,
+              out_scale=0.9, out_zp=0 if kind == "s32" else 3, engine="umma", seed=m + k)
+
+
 def test_transposed_poses_off_the_tma_rule_use_generic(cuda_device, nnb200_lib):
     """[K, M] activations and [K, N] weights whose row pitch is not a multiple of 16 bytes cannot
     be addressed by TMA: the generic engine serves them."""
