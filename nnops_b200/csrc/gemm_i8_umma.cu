@@ -430,18 +430,26 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
                 body(std::false_type{});
             }
         } else {
+            // Compensation live (zero points on both sides, or per-row ones): the integer terms, then
+            // the same packed requantisation, one loop for every zero point (more code here slows
+            // the common path above measurably).
+            (void)lo;
+            (void)hi;
+            const int32_t relu_lo = e.relu ? 0 : INT32_MIN;
+            const float row_k = scale_folded ? 1.0f : t.row_k;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-                uint32_t word = 0;
+                int32_t v[4];
+                float req[4];
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
-                    const int32_t v = i8_int_value(e, t, static_cast<int32_t>(acc[j + b]), col_zpw[j + b],
-                                                   col_rw[j + b], col_bias[j + b]);
-                    const float req = scale_folded ? col_scale[j + b] : __fmul_rn(t.row_k, col_scale[j + b]);
-                    const int32_t q = i8_requant(v, req, lo, hi, e.out_zp);
-                    word |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * b);
+                    const int32_t c = i8_compensate(static_cast<int32_t>(acc[j + b]), t.zpa, col_zpw[j + b], t.ra,
+                                                    col_rw[j + b], e.k);
+                    v[b] = max(static_cast<int32_t>(static_cast<uint32_t>(c) + static_cast<uint32_t>(col_bias[j + b])),
+                               relu_lo);
+                    req[b] = __fmul_rn(row_k, col_scale[j + b]);
                 }
-                packed[j / 4] = word;
+                packed[j / 4] = requant_pack4<KIND == NNB200_OUT_U8, false>(v, req, e.out_zp);
             }
         }
         if (!row_ok) {
@@ -468,60 +476,100 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
                 }
             }
         }
-    } else if constexpr (KIND == NNB200_OUT_F32) {
+    } else {  // F32 / F16
+        // One loop per (compensation live?, activation class): the run-time switches are taken
+        // once per chunk, not once per element.  With a per-tensor activation scale the staged
+        // column scale already carries s_a * s_w[n] (row factor exactly 1: x * 1.0f is x).
+        const float row_s = scale_folded ? 1.0f : t.s_a;
         float o[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            o[j] = i8_fp_value(e, t, static_cast<int32_t>(acc[j]), col_zpw[j], col_rw[j], col_scale[j],
-                               __int_as_float(col_bias[j]));
-        }
-        if (!row_ok) {
-            return;
-        }
-        float* dst = static_cast<float*>(e.out) + m * e.ldc + n0;
-        if (full && vec_ok) {
+        const auto body = [&](auto comp_tag, auto act_tag) {
+            constexpr bool kComp = decltype(comp_tag)::value;
+            constexpr int kAct = decltype(act_tag)::value;   // 0 none, 1 Relu, 2 any other
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-                *reinterpret_cast<float4*>(dst + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
-            }
-        } else {
+                const int4 b4 = *reinterpret_cast<const int4*>(col_bias + j);
+                const float4 s4 = *reinterpret_cast<const float4*>(col_scale + j);
+                const float bias4[4] = {__int_as_float(b4.x), __int_as_float(b4.y), __int_as_float(b4.z), __int_as_float(b4.w)};
+                const float scale4[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                if (n0 + j < n_total) {
-                    dst[j] = o[j];
+                for (int b = 0; b < 4; ++b) {
+                    int32_t v = static_cast<int32_t>(acc[j + b]);
+                    if constexpr (kComp) {
+                        v = i8_compensate(v, t.zpa, col_zpw[j + b], t.ra, col_rw[j + b], e.k);
+                    }
+                    float f = __fmul_rn(__int2float_rn(v), __fmul_rn(row_s, scale4[b]));
+                    const float fb = __fadd_rn(f, bias4[b]);
+                    f = bias4[b] != 0.0f ? fb : f;   // a zero bias is not added (-0 stays -0)
+                    f = fminf(fmaxf(f, e.min_clip), e.max_clip);
+                    if constexpr (kAct == 1) {
+                        f = fmaxf(f, 0.0f);
+                    } else if constexpr (kAct == 2) {
+                        f = act_apply(e.activation, e.act_alpha, e.act_beta, f);
+                    }
+                    o[j + b] = f;
                 }
             }
-        }
-    } else {  // F16
-        uint32_t packed[16];
-#pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-            const float f0 = i8_fp_value(e, t, static_cast<int32_t>(acc[j]), col_zpw[j], col_rw[j], col_scale[j],
-                                         __int_as_float(col_bias[j]));
-            const float f1 = i8_fp_value(e, t, static_cast<int32_t>(acc[j + 1]), col_zpw[j + 1], col_rw[j + 1],
-                                         col_scale[j + 1], __int_as_float(col_bias[j + 1]));
-            packed[j / 2] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f0))) |
-                            (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f1))) << 16);
+        };
+        const int act_class = e.activation == NNB200_ACT_NONE ? 0 : (e.activation == NNB200_ACT_RELU ? 1 : 2);
+        if (e.compensate) {
+            if (act_class == 0) {
+                body(std::true_type{}, std::integral_constant<int, 0>{});
+            } else if (act_class == 1) {
+                body(std::true_type{}, std::integral_constant<int, 1>{});
+            } else {
+                body(std::true_type{}, std::integral_constant<int, 2>{});
+            }
+        } else {
+            if (act_class == 0) {
+                body(std::false_type{}, std::integral_constant<int, 0>{});
+            } else if (act_class == 1) {
+                body(std::false_type{}, std::integral_constant<int, 1>{});
+            } else {
+                body(std::false_type{}, std::integral_constant<int, 2>{});
+            }
         }
         if (!row_ok) {
             return;
         }
-        uint16_t* dst = static_cast<uint16_t*>(e.out) + m * e.ldc + n0;
-        if (full && vec32) {
-            st_global_32(dst, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
-            st_global_32(dst + 16, packed[8], packed[9], packed[10], packed[11], packed[12], packed[13], packed[14],
-                         packed[15]);
-        } else if (full && vec_ok) {
+        if constexpr (KIND == NNB200_OUT_F32) {
+            float* dst = static_cast<float*>(e.out) + m * e.ldc + n0;
+            if (full && vec_ok) {
 #pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-                *reinterpret_cast<uint4*>(dst + 2 * j) =
-                    make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+                for (int j = 0; j < 32; j += 4) {
+                    *reinterpret_cast<float4*>(dst + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (n0 + j < n_total) {
+                        dst[j] = o[j];
+                    }
+                }
             }
         } else {
+            uint32_t packed[16];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                if (n0 + j < n_total) {
-                    dst[j] = static_cast<uint16_t>(packed[j / 2] >> (16 * (j % 2)));
+            for (int j = 0; j < 32; j += 2) {
+                packed[j / 2] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(o[j]))) |
+                                (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(o[j + 1]))) << 16);
+            }
+            uint16_t* dst = static_cast<uint16_t*>(e.out) + m * e.ldc + n0;
+            if (full && vec32) {
+                st_global_32(dst, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
+                st_global_32(dst + 16, packed[8], packed[9], packed[10], packed[11], packed[12], packed[13], packed[14],
+                             packed[15]);
+            } else if (full && vec_ok) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                    *reinterpret_cast<uint4*>(dst + 2 * j) =
+                        make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (n0 + j < n_total) {
+                        dst[j] = static_cast<uint16_t>(packed[j / 2] >> (16 * (j % 2)));
+                    }
                 }
             }
         }
@@ -732,8 +780,10 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // 8-bit destinations with a per-tensor activation scale: the row factor s_a / s_out is the
         // same for every row, so it is folded into the staged column scales (same two roundings,
         // once per column instead of once per element).  The sharded form keeps the plain scales.
-        const bool fold_scale = !PEERS && (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) && ep.scale_a == nullptr;
-        const float folded_row_k = __fdiv_rn(ep.scale_a_scalar, ep.out_scale);
+        // fp destinations: the row factor is s_a itself.
+        const bool fold_scale = !PEERS && KIND != NNB200_OUT_S32 && ep.scale_a == nullptr;
+        const float folded_row_k = (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8)
+                                       ? __fdiv_rn(ep.scale_a_scalar, ep.out_scale) : ep.scale_a_scalar;
         const bool fold_comp = !PEERS && (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) && ep.compensate != 0 &&
                                ep.zp_a == nullptr && ep.r_a == nullptr;
         // The next tile's column terms are loaded into registers before this tile is drained,
@@ -821,6 +871,8 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const float zpf = static_cast<float>(ep.out_zp);
                 const float lo = (KIND == NNB200_OUT_S8 ? -128.0f : 0.0f) - zpf;
                 const float hi = (KIND == NNB200_OUT_S8 ? 127.0f : 255.0f) - zpf;
+                (void)lo;
+                (void)hi;
                 const int row0 = tc.m_blk * kBlockM + quarter * 32;
                 const int num_dst = 1 + ep.num_peers;
                 const bool multicast = ep.mc_out != nullptr;
@@ -851,19 +903,39 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         uint32_t v[32];
                         tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
                         tmem_ld_wait();
+                        // No branch per element: the ReLU is a lower bound, compensation is chosen
+                        // once per chunk, saturation rides the packing instruction.
                         uint32_t packed[8];
+                        const int32_t relu_lo = ep.relu ? 0 : INT32_MIN;
+                        if (ep.compensate) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            uint32_t word = 0;
+                            for (int j = 0; j < 32; j += 4) {
+                                int32_t vv[4];
+                                float rq[4];
 #pragma unroll
-                            for (int b = 0; b < 4; ++b) {
-                                const int col = c * 32 + j + b;
-                                const int32_t val = i8_int_value(ep, rt, static_cast<int32_t>(v[j + b]), cz[col], cr[col],
-                                                                 cb[col]);
-                                const int32_t q = i8_requant(val, __fmul_rn(rt.row_k, cs[col]), lo, hi, ep.out_zp);
-                                word |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * b);
+                                for (int b = 0; b < 4; ++b) {
+                                    const int col = c * 32 + j + b;
+                                    const int32_t x = i8_compensate(static_cast<int32_t>(v[j + b]), rt.zpa, cz[col], rt.ra,
+                                                                    cr[col], ep.k);
+                                    vv[b] = max(static_cast<int32_t>(static_cast<uint32_t>(x) + static_cast<uint32_t>(cb[col])),
+                                                relu_lo);
+                                    rq[b] = __fmul_rn(rt.row_k, cs[col]);
+                                }
+                                packed[j / 4] = requant_pack4<KIND == NNB200_OUT_U8, false>(vv, rq, ep.out_zp);
                             }
-                            packed[j / 4] = word;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                int32_t vv[4];
+                                float rq[4];
+#pragma unroll
+                                for (int b = 0; b < 4; ++b) {
+                                    const int col = c * 32 + j + b;
+                                    vv[b] = max(static_cast<int32_t>(v[j + b] + static_cast<uint32_t>(cb[col])), relu_lo);
+                                    rq[b] = __fmul_rn(rt.row_k, cs[col]);
+                                }
+                                packed[j / 4] = requant_pack4<KIND == NNB200_OUT_U8, false>(vv, rq, ep.out_zp);
+                            }
                         }
                         // This lane's row of the tile: 16-byte pieces 2cc and 2cc+1 (swizzled in the 128-byte form).
                         uint4* srow = reinterpret_cast<uint4*>(stage + lane * kGroupCols);
@@ -1177,8 +1249,9 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     } else {
         // ---------------- epilogue warps (each CTA drains its own 128 rows) ----------------
         const int quarter = warp & 3;
-        const bool fold_scale = (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) && ep.scale_a == nullptr;
-        const float folded_row_k = __fdiv_rn(ep.scale_a_scalar, ep.out_scale);
+        const bool fold_scale = KIND != NNB200_OUT_S32 && ep.scale_a == nullptr;
+        const float folded_row_k = (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8)
+                                       ? __fdiv_rn(ep.scale_a_scalar, ep.out_scale) : ep.scale_a_scalar;
         const bool fold_comp = (KIND == NNB200_OUT_S8 || KIND == NNB200_OUT_U8) && ep.compensate != 0 &&
                                ep.zp_a == nullptr && ep.r_a == nullptr;
         constexpr int kTermIters = (Cfg::kHalf0 + 31) / 32;   // 4 for 256-wide tiles

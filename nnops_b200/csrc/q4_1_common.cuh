@@ -50,6 +50,59 @@ __device__ __forceinline__ float fp_epilogue_value(const FpEpilogue& e, float ac
     return act_apply(e.activation, e.act_alpha, e.act_beta, v);
 }
 
+// The same value with the run-time switches turned into operands, for loops over many elements:
+// alpha is always multiplied in (x * 1.0f is x), a missing bias adds -0.0f (x + -0.0f is x for
+// every x, -0 included), and the activation class -- 0 none, 1 Relu, 2 any other -- is a
+// template argument chosen once outside the loop.
+template <bool OUT_F16, int ACT>
+__device__ __forceinline__ float fp_epilogue_value_flat(const FpEpilogue& e, float acc, int64_t n)
+{
+    float b = -0.0f;
+    if (e.bias != nullptr) {
+        b = OUT_F16 ? __half2float(static_cast<const __half*>(e.bias)[n]) : static_cast<const float*>(e.bias)[n];
+    }
+    float v = __fadd_rn(__fmul_rn(acc, e.alpha), b);
+    v = fminf(fmaxf(v, e.min_clip), e.max_clip);
+    if constexpr (ACT == 1) {
+        v = fmaxf(v, 0.0f);
+    } else if constexpr (ACT == 2) {
+        v = act_apply(e.activation, e.act_alpha, e.act_beta, v);
+    }
+    return v;
+}
+
+// 32 consecutive columns of one row: accumulator bits in, output values (f32) out.  `identity`
+// (fp_epilogue_is_identity, tested once per tile by the caller) passes the accumulator through.
+template <bool OUT_F16>
+__device__ __forceinline__ void fp_epilogue_chunk(const FpEpilogue& e, bool identity, const uint32_t (&v)[32], int n0,
+                                                  int n_total, float (&o)[32])
+{
+    if (identity) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            o[j] = __uint_as_float(v[j]);
+        }
+        return;
+    }
+    const int act_class = e.activation == NNB200_ACT_NONE ? 0 : (e.activation == NNB200_ACT_RELU ? 1 : 2);
+    if (act_class == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            o[j] = fp_epilogue_value_flat<OUT_F16, 0>(e, __uint_as_float(v[j]), min(n0 + j, n_total - 1));
+        }
+    } else if (act_class == 1) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            o[j] = fp_epilogue_value_flat<OUT_F16, 1>(e, __uint_as_float(v[j]), min(n0 + j, n_total - 1));
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            o[j] = fp_epilogue_value_flat<OUT_F16, 2>(e, __uint_as_float(v[j]), min(n0 + j, n_total - 1));
+        }
+    }
+}
+
 // Two nibble-carrying words (8 bytes of qs) -> 8 consecutive f16 weights of the low nibbles
 // and 8 of the high nibbles, each as a uint4 of four half2.
 __device__ __forceinline__ void dequant_word_pair(uint32_t w0, uint32_t w1, __half2 d2, __half2 m2, uint4& lo,

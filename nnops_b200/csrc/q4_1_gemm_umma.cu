@@ -265,16 +265,13 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
                 tmem_ld_wait();
                 const bool full = n0 + 32 <= n_total;
                 if constexpr (OUT_F16) {
+                    float o[32];
+                    fp_epilogue_chunk<true>(ep, identity, v, n0, n_total, o);
                     uint32_t packed[16];
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
-                        const float f0 = identity ? __uint_as_float(v[j])
-                                                  : fp_epilogue_value<true>(ep, __uint_as_float(v[j]), min(n0 + j, n_total - 1));
-                        const float f1 = identity ? __uint_as_float(v[j + 1])
-                                                  : fp_epilogue_value<true>(ep, __uint_as_float(v[j + 1]),
-                                                                            min(n0 + j + 1, n_total - 1));
-                        packed[j / 2] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f0))) |
-                                        (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(f1))) << 16);
+                        packed[j / 2] = static_cast<uint32_t>(__half_as_ushort(__float2half_rn(o[j]))) |
+                                        (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(o[j + 1]))) << 16);
                     }
                     if (row_ok) {
                         uint16_t* dst = static_cast<uint16_t*>(out) + m * ldc + n0;
@@ -295,11 +292,7 @@ q4_1_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const uint8_t* 
                     }
                 } else {
                     float o[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        o[j] = identity ? __uint_as_float(v[j])
-                                        : fp_epilogue_value<false>(ep, __uint_as_float(v[j]), min(n0 + j, n_total - 1));
-                    }
+                    fp_epilogue_chunk<false>(ep, identity, v, n0, n_total, o);
                     if (row_ok) {
                         float* dst = static_cast<float*>(out) + m * ldc + n0;
                         if (full && vec_ok) {
