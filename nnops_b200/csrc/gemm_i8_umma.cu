@@ -378,7 +378,15 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
             return;
         }
         int32_t* dst = static_cast<int32_t*>(e.out) + m * e.ldc + n0;
-        if (full && vec_ok) {
+        if (full && vec32) {
+            // The lane's 128 bytes as four 256-bit stores (whole 32-byte sectors).
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                st_global_32(dst + j, static_cast<uint32_t>(o[j]), static_cast<uint32_t>(o[j + 1]), static_cast<uint32_t>(o[j + 2]),
+                             static_cast<uint32_t>(o[j + 3]), static_cast<uint32_t>(o[j + 4]), static_cast<uint32_t>(o[j + 5]),
+                             static_cast<uint32_t>(o[j + 6]), static_cast<uint32_t>(o[j + 7]));
+            }
+        } else if (full && vec_ok) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
                 *reinterpret_cast<int4*>(dst + j) = make_int4(o[j], o[j + 1], o[j + 2], o[j + 3]);
@@ -484,7 +492,7 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
         float o[32];
         const auto body = [&](auto comp_tag, auto act_tag) {
             constexpr bool kComp = decltype(comp_tag)::value;
-            constexpr int kAct = decltype(act_tag)::value;   // 0 none, 1 Relu, 2 any other
+            constexpr int kAct = decltype(act_tag)::value;   // 0 none, 1 Relu, 2 any other, 3 Gelu
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
                 const int4 b4 = *reinterpret_cast<const int4*>(col_bias + j);
@@ -505,12 +513,18 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
                         f = fmaxf(f, 0.0f);
                     } else if constexpr (kAct == 2) {
                         f = act_apply(e.activation, e.act_alpha, e.act_beta, f);
+                    } else if constexpr (kAct == 3) {
+                        f = act_apply(NNB200_ACT_GELU, e.act_alpha, e.act_beta, f);   // the switch folds away
                     }
                     o[j + b] = f;
                 }
             }
         };
-        const int act_class = e.activation == NNB200_ACT_NONE ? 0 : (e.activation == NNB200_ACT_RELU ? 1 : 2);
+        // Gelu (the usual partner of a Linear) gets a loop of its own; the remaining activations
+        // share one with the switch inside.
+        const int act_class = e.activation == NNB200_ACT_NONE ? 0
+                              : e.activation == NNB200_ACT_RELU ? 1
+                              : e.activation == NNB200_ACT_GELU ? 3 : 2;
         if (e.compensate) {
             if (act_class == 0) {
                 body(std::true_type{}, std::integral_constant<int, 0>{});
@@ -524,6 +538,8 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
                 body(std::false_type{}, std::integral_constant<int, 0>{});
             } else if (act_class == 1) {
                 body(std::false_type{}, std::integral_constant<int, 1>{});
+            } else if (act_class == 3) {
+                body(std::false_type{}, std::integral_constant<int, 3>{});
             } else {
                 body(std::false_type{}, std::integral_constant<int, 2>{});
             }
@@ -533,7 +549,14 @@ __device__ __forceinline__ void epilogue_chunk(const I8Epilogue& e, const I8RowT
         }
         if constexpr (KIND == NNB200_OUT_F32) {
             float* dst = static_cast<float*>(e.out) + m * e.ldc + n0;
-            if (full && vec_ok) {
+            if (full && vec32) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    st_global_32(dst + j, __float_as_uint(o[j]), __float_as_uint(o[j + 1]), __float_as_uint(o[j + 2]),
+                                 __float_as_uint(o[j + 3]), __float_as_uint(o[j + 4]), __float_as_uint(o[j + 5]),
+                                 __float_as_uint(o[j + 6]), __float_as_uint(o[j + 7]));
+                }
+            } else if (full && vec_ok) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
                     *reinterpret_cast<float4*>(dst + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
