@@ -120,6 +120,13 @@ def build_tests(force=False) -> list[Path]:
         _run([CXX, *COMMON, "-o", out, src, f"-L{LIB_DIR}", "-lnnb200_host", "-lnnb200", f"-L{oracle_lib.parent}",
               "-lnnops_oracle", *cuda, *_rpath(LIB_DIR, oracle_lib.parent, CUDA_HOME / "lib64")])
     outs.append(out)
+    # The C++ sharded layer (header-only over the C ABI) and its forked-ranks test.
+    shard_src = ROOT / "tests" / "cpp" / "test_sharded.cpp"
+    out = BIN_DIR / "test_sharded"
+    if force or _stale(out, [shard_src, ROOT / "include" / "nnops_b200" / "sharded_linear.hpp", lib_build.LIB]):
+        _run([CXX, *COMMON, "-o", out, shard_src, f"-L{LIB_DIR}", "-lnnb200", *cuda, "-lrt", "-pthread",
+              *_rpath(LIB_DIR, CUDA_HOME / "lib64")])
+    outs.append(out)
     bench_src = ROOT / "tests" / "cpp" / "bench_linear_op.cpp"
     out = BIN_DIR / "bench_linear_op_standalone"
     if force or _stale(out, [bench_src, host_lib]):
