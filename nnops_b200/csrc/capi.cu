@@ -156,16 +156,17 @@ bool make_tma_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t co
 // w, h, n; box = {box_c, box_w, box_h, 1}, 128-byte swizzle, zero fill outside the tensor.
 bool make_tma_nhwc_u8(CUtensorMap* map, const void* base, uint64_t c, uint64_t w, uint64_t h, uint64_t n,
                       uint64_t stride_w, uint64_t stride_h, uint64_t stride_n, uint32_t box_c, uint32_t box_w,
-                      uint32_t box_h)
+                      uint32_t box_h, uint32_t step_w, uint32_t step_h)
 {
     EncodeTiledFn fn = encode_tiled_fn();
-    if (fn == nullptr) {
+    if (fn == nullptr || box_w * step_w > 256 || box_h * step_h > 256) {
         return false;
     }
     const cuuint64_t dims[4] = {c, w, h, n};
     const cuuint64_t strides[3] = {stride_w, stride_h, stride_n};
-    const cuuint32_t box[4] = {box_c, box_w, box_h, 1};
-    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    // The box is given as the span it covers in the tensor; the element strides thin it out.
+    const cuuint32_t box[4] = {box_c, box_w * step_w, box_h * step_h, 1};
+    const cuuint32_t elem_strides[4] = {1, step_w, step_h, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, elem_strides,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -17,7 +17,7 @@
 //                             sums R_w.  Run per call on a raw filter (it is small), or once by
 //                             nnb200_conv2d_i8_pack.
 //
-// Stride-1 convolutions over whole 128-channel blocks per group with symmetric weights skip the
+// Convolutions with strides of 1 or 2 over whole 128-channel blocks per group with symmetric weights skip the
 // gather altogether (the implicit-GEMM form, launch_conv_i8_umma in gemm_i8_umma.cu): the GEMM's
 // producer reads the activation itself, one 4-D TMA box {128 channels, bw, bh, 1 image} per
 // k-block (tap, channel block) at the patch's origin shifted by the tap -- out-of-image parts are
@@ -351,8 +351,8 @@ struct ConvScratch {
     size_t total;
 };
 
-// The implicit-GEMM form (no gathered copy; launch_conv_i8_umma) takes stride-1 convolutions
-// over whole 128-channel blocks per group whose weights have no zero points, when TMA can
+// The implicit-GEMM form (no gathered copy; launch_conv_i8_umma) takes convolutions with strides of
+// 1 or 2 (a stride is the tensor map's element stride along that axis) over whole 128-channel blocks per group whose weights have no zero points, when TMA can
 // address the activation (dense channels, 16-byte aligned pitches and base).
 bool implicit_form(const nnb200_conv2d_i8_args* a, const ConvGeom& g)
 {
@@ -371,14 +371,14 @@ bool implicit_form(const nnb200_conv2d_i8_args* a, const ConvGeom& g)
     }
     if (a->zp_x != 0 && g.kh <= 32 && g.kw <= 32) {
         uint32_t masks[8];
-        if (conv_border_masks(static_cast<int>(g.oh), static_cast<int>(g.ih), static_cast<int>(g.kh), static_cast<int>(g.dh),
-                              static_cast<int>(g.ph), masks) < 0 ||
-            conv_border_masks(static_cast<int>(g.ow), static_cast<int>(g.iw), static_cast<int>(g.kw), static_cast<int>(g.dw),
-                              static_cast<int>(g.pw), masks) < 0) {
+        if (conv_border_masks(static_cast<int>(g.oh), static_cast<int>(g.ih), static_cast<int>(g.kh), static_cast<int>(g.sh),
+                              static_cast<int>(g.dh), static_cast<int>(g.ph), masks) < 0 ||
+            conv_border_masks(static_cast<int>(g.ow), static_cast<int>(g.iw), static_cast<int>(g.kw), static_cast<int>(g.sw),
+                              static_cast<int>(g.dw), static_cast<int>(g.pw), masks) < 0) {
             return false;   // more than eight kinds of overhang along an axis
         }
     }
-    return g.sh == 1 && g.sw == 1 && g.icg % 128 == 0 && g.kh <= 32 && g.kw <= 32 && zp_w_zero && a->in_stride_c == 1 &&
+    return g.sh >= 1 && g.sh <= 2 && g.sw >= 1 && g.sw <= 2 && g.icg % 128 == 0 && g.kh <= 32 && g.kw <= 32 && zp_w_zero && a->in_stride_c == 1 &&
            a->in_stride_w % 16 == 0 && a->in_stride_h % 16 == 0 && a->in_stride_n % 16 == 0 &&
            reinterpret_cast<uintptr_t>(a->input) % 16 == 0 && a->in_stride_w >= g.ic && g.oh <= 65536 && g.ow <= 65536 &&
            (g.kh - 1) * g.dh < 32768 && (g.kw - 1) * g.dw < 32768 && g.ph < 32768 && g.pw < 32768;
@@ -628,10 +628,10 @@ int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* a, void* stream_v)
             bp.oc = static_cast<int32_t>(g.oc);
             bp.kh = static_cast<int32_t>(g.kh);
             bp.kw = static_cast<int32_t>(g.kw);
-            bp.nh = conv_border_masks(static_cast<int>(g.oh), static_cast<int>(g.ih), bp.kh, static_cast<int>(g.dh),
-                                      static_cast<int>(g.ph), bp.mask_h);
-            bp.nw = conv_border_masks(static_cast<int>(g.ow), static_cast<int>(g.iw), bp.kw, static_cast<int>(g.dw),
-                                      static_cast<int>(g.pw), bp.mask_w);
+            bp.nh = conv_border_masks(static_cast<int>(g.oh), static_cast<int>(g.ih), bp.kh, static_cast<int>(g.sh),
+                                      static_cast<int>(g.dh), static_cast<int>(g.ph), bp.mask_h);
+            bp.nw = conv_border_masks(static_cast<int>(g.ow), static_cast<int>(g.iw), bp.kw, static_cast<int>(g.sw),
+                                      static_cast<int>(g.dw), static_cast<int>(g.pw), bp.mask_w);
             if (bp.nh < 0 || bp.nw < 0) {
                 return NNB200_INTERNAL;   // implicit_form() admits only geometries with at most eight classes
             }
@@ -676,6 +676,7 @@ int nnb200_conv2d_i8(const nnb200_conv2d_i8_args* a, void* stream_v)
             c.kh = static_cast<int32_t>(g.kh); c.kw = static_cast<int32_t>(g.kw);
             c.dh = static_cast<int32_t>(g.dh); c.dw = static_cast<int32_t>(g.dw);
             c.ph = static_cast<int32_t>(g.ph); c.pw = static_cast<int32_t>(g.pw);
+            c.sh = static_cast<int32_t>(g.sh); c.sw = static_cast<int32_t>(g.sw);
             c.c_base = static_cast<int32_t>(grp * g.icg); c.icg = static_cast<int32_t>(g.icg);
             c.wt = wt + c0 * g.kp;
             c.ldw = g.kp;

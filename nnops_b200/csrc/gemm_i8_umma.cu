@@ -66,6 +66,7 @@ struct alignas(64) PeerMaps {
 struct ConvTile {
     int32_t oh, ow, ih, iw;
     int32_t kh, kw, dh, dw, ph, pw;
+    int32_t sh, sw;                // window strides (1 or 2): the tensor map's element strides along h and w
     int32_t bw_log2, bh;           // patch: bh rows x (1 << bw_log2) columns, 128 pixels
     int32_t tiles_w, tiles_h;      // patches per image
     int32_t c_base;                // first channel of this group in the activation
@@ -118,11 +119,11 @@ __device__ __forceinline__ ConvRow conv_row(const ConvTile& conv, int m_blk, int
     if (conv.zp_x != 0 && o.ok) {
         uint32_t lost_h = 0, lost_w = 0;
         for (int a = 0; a < conv.kh; ++a) {
-            const int iy = y - conv.ph + a * conv.dh;
+            const int iy = y * conv.sh - conv.ph + a * conv.dh;
             lost_h |= (iy < 0 || iy >= conv.ih) ? (1u << a) : 0u;
         }
         for (int b = 0; b < conv.kw; ++b) {
-            const int ix = x - conv.pw + b * conv.dw;
+            const int ix = x * conv.sw - conv.pw + b * conv.dw;
             lost_w |= (ix < 0 || ix >= conv.iw) ? (1u << b) : 0u;
         }
         // 1 + index of the mask among the axis's classes (0 = no tap lost).
@@ -690,8 +691,8 @@ gemm_i8_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         const int ta = tap / conv.kw;
                         const int tb = tap - ta * conv.kw;
                         tma_load_4d(a_dst, &map_a, &full_bar[stage], conv.c_base + c0,
-                                    (pt.tw << conv.bw_log2) - conv.pw + tb * conv.dw,
-                                    pt.th * conv.bh - conv.ph + ta * conv.dh, pt.img);
+                                    (pt.tw << conv.bw_log2) * conv.sw - conv.pw + tb * conv.dw,
+                                    pt.th * conv.bh * conv.sh - conv.ph + ta * conv.dh, pt.img);
                     } else if (pose & 1) {
                         // A stored [K][M]: the box is 128 k-rows of 128 m-bytes.
                         tma_load_2d(a_dst, &map_a, &full_bar[stage], tc.m_blk * kBlockM, kb * kBlockKBytes);
@@ -1189,8 +1190,8 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                                 const int ta = tap / conv.kw;
                                 const int tb = tap - ta * conv.kw;
                                 tma_load_4d_pair(a_dst, &map_a, leader_full, conv.c_base + c0,
-                                                 (pt.tw << conv.bw_log2) - conv.pw + tb * conv.dw,
-                                                 pt.th * conv.bh - conv.ph + ta * conv.dh, pt.img);
+                                                 (pt.tw << conv.bw_log2) * conv.sw - conv.pw + tb * conv.dw,
+                                                 pt.th * conv.bh * conv.sh - conv.ph + ta * conv.dh, pt.img);
                             } else {
                                 tma_load_2d_pair(a_dst, &map_a, leader_full, kx * kBlockKBytes, m0);
                             }
@@ -1683,6 +1684,7 @@ int launch_conv_i8_umma(const ConvUmmaArgs& c, const I8Epilogue& ep, const Devic
     const int best = conv_patch_log2(c.oh, c.ow, nullptr);
     t.oh = c.oh; t.ow = c.ow; t.ih = c.ih; t.iw = c.iw;
     t.kh = c.kh; t.kw = c.kw; t.dh = c.dh; t.dw = c.dw; t.ph = c.ph; t.pw = c.pw;
+    t.sh = c.sh; t.sw = c.sw;
     t.bw_log2 = best;
     t.bh = 128 >> best;
     t.tiles_w = (c.ow + (1 << best) - 1) >> best;
@@ -1716,7 +1718,7 @@ int launch_conv_i8_umma(const ConvUmmaArgs& c, const I8Epilogue& ep, const Devic
     if (!make_tma_nhwc_u8(&map_a, c.x, static_cast<uint64_t>(c.ic_total), static_cast<uint64_t>(c.iw),
                           static_cast<uint64_t>(c.ih), static_cast<uint64_t>(c.batch), static_cast<uint64_t>(c.in_w),
                           static_cast<uint64_t>(c.in_h), static_cast<uint64_t>(c.in_n), kBlockKBytes, 1u << best,
-                          static_cast<uint32_t>(t.bh)) ||
+                          static_cast<uint32_t>(t.bh), static_cast<uint32_t>(c.sw), static_cast<uint32_t>(c.sh)) ||
         !make_tma_2d(&map_w, c.wt, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(c.ldw),
                      kBlockKBytes, static_cast<uint32_t>(bn))) {
         return NNB200_INTERNAL;

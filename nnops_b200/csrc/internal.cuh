@@ -51,9 +51,11 @@ void note_launch(int n = 1);
 bool make_tma_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t cols, uint64_t rows,
                  uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, bool swizzle128 = true);
 
+// box_w / box_h count the pixels a box DELIVERS; step_w / step_h (1 or 2) the distance between
+// them in the tensor (the map's element strides), so the box spans box * step pixels.
 bool make_tma_nhwc_u8(CUtensorMap* map, const void* base, uint64_t c, uint64_t w, uint64_t h, uint64_t n,
                       uint64_t stride_w, uint64_t stride_h, uint64_t stride_n, uint32_t box_c, uint32_t box_w,
-                      uint32_t box_h);
+                      uint32_t box_h, uint32_t step_w = 1, uint32_t step_h = 1);
 
 // One 2-D int8 problem (a single batch element), Linear pose: A [m,k] and W [n,k] both
 // k-contiguous.  lda / ldw are row pitches in bytes.
@@ -78,6 +80,7 @@ struct ConvUmmaArgs {
     int64_t in_n, in_h, in_w;
     int32_t batch, ih, iw, ic_total, oh, ow;
     int32_t kh, kw, dh, dw, ph, pw;
+    int32_t sh, sw;             // window strides (1 or 2)
     int32_t c_base, icg;        // this group's channels
     const void* wt;             // k-major filter rows of this group [ocg][ldw], k = (tap, channel)
     int64_t ldw;
@@ -93,23 +96,23 @@ struct ConvUmmaArgs {
 };
 int launch_conv_i8_umma(const ConvUmmaArgs& c, const I8Epilogue& ep, const DeviceInfo& dev, cudaStream_t stream);
 // Which taps of one filter axis fall outside the image, as a bit mask, for the output coordinate
-// `o` (stride 1): bit t set when o - pad + t * dil is not in [0, extent_in).
-inline uint32_t conv_bad_taps(int o, int pad, int dil, int taps, int extent_in)
+// `o`: bit t set when o * stride - pad + t * dil is not in [0, extent_in).
+inline uint32_t conv_bad_taps(int o, int stride, int pad, int dil, int taps, int extent_in)
 {
     uint32_t bad = 0;
     for (int t = 0; t < taps; ++t) {
-        const int i = o - pad + t * dil;
+        const int i = o * stride - pad + t * dil;
         bad |= (i < 0 || i >= extent_in) ? (1u << t) : 0u;
     }
     return bad;
 }
 // The distinct non-zero masks over all output coordinates of an axis, into masks[0..7]; returns
 // their number, or -1 when there are more than eight.
-inline int conv_border_masks(int extent_out, int extent_in, int taps, int dil, int pad, uint32_t* masks)
+inline int conv_border_masks(int extent_out, int extent_in, int taps, int stride, int dil, int pad, uint32_t* masks)
 {
     int count = 0;
     for (int o = 0; o < extent_out; ++o) {
-        const uint32_t bad = conv_bad_taps(o, pad, dil, taps, extent_in);
+        const uint32_t bad = conv_bad_taps(o, stride, pad, dil, taps, extent_in);
         if (bad == 0) {
             continue;
         }

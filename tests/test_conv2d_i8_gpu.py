@@ -63,8 +63,14 @@ CASES = [
     # half is past the batch), and a second column of tiles with a ragged edge.
     (17, 128, 24, 40, 256, 3, 3, 1, 1, 1, 1, 1, 1, 1, U8, "s8", True, True, 128, True),
     (5, 128, 56, 56, 320, 3, 3, 1, 1, 2, 2, 2, 2, 1, S8, "f16", True, True, -6, True),
+    # Strides of 2 (the tensor map's element strides): a downsampling 3x3 over an odd plane, a
+    # 1x1 projection, unequal strides, and one with enough tiles for CTA pairs.
+    (2, 128, 57, 57, 160, 3, 3, 2, 2, 1, 1, 1, 1, 1, U8, "s8", True, True, 128, True),
+    (1, 256, 56, 56, 64, 1, 1, 2, 2, 1, 1, 0, 0, 1, S8, "u8", True, True, -6, True),
+    (2, 128, 40, 33, 96, 3, 3, 2, 1, 1, 1, 1, 1, 1, U8, "f16", True, True, None, True),
+    (22, 128, 56, 56, 256, 3, 3, 2, 2, 1, 1, 1, 1, 1, U8, "s8", True, True, 128, True),
 ]
-IMPLICIT = list(range(len(CASES) - 8, len(CASES)))
+IMPLICIT = list(range(len(CASES) - 12, len(CASES)))
 
 
 def _make(case, seed):
@@ -127,7 +133,8 @@ def test_implicit_form_equals_gather_form(cuda_device, idx, knobs):
         kh, kw, icg, oc = w.shape
         oh, ow = ops.conv2d_out_hw(ih, iw, kh, kw, kwargs["stride"], kwargs["dilation"], kwargs["padding"])
         a = capi.Conv2dI8Args(input=x_t.data_ptr(), weight=w_t.data_ptr(), out=x_t.data_ptr(), batch=n, ih=ih, iw=iw, ic=ic,
-                              oh=oh, ow=ow, oc=oc, kh=kh, kw=kw, stride_h=1, stride_w=1, dil_h=kwargs["dilation"][0],
+                              oh=oh, ow=ow, oc=oc, kh=kh, kw=kw, stride_h=kwargs["stride"][0], stride_w=kwargs["stride"][1],
+                              dil_h=kwargs["dilation"][0],
                               dil_w=kwargs["dilation"][1], pad_h=kwargs["padding"][0], pad_w=kwargs["padding"][1],
                               groups=kwargs["groups"], in_stride_n=ih * iw * ic, in_stride_h=iw * ic, in_stride_w=ic,
                               in_stride_c=1, w_stride_kh=kw * icg * oc, w_stride_kw=icg * oc, w_stride_ic=oc, w_stride_oc=1,
