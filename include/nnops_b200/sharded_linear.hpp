@@ -188,15 +188,16 @@ public:
             if (flags && g == 1) {
                 break;
             }
-            Buffer b;
-            b.mapped.assign(static_cast<size_t>(g), nullptr);
+            if (!flags) {
+                outs_.emplace_back();
+            }
+            Buffer& slot = flags ? flag_ : outs_.back();   // owned from here on: release() frees it on any exit
+            slot.mapped.assign(static_cast<size_t>(g), nullptr);
             const size_t bytes = flags ? NNB200_RANK_FLAG_BYTES : static_cast<size_t>(m) * static_cast<size_t>(n_total_);
-            int st = nnb200_peer_buffer_alloc(&b.own, bytes);
+            int st = nnb200_peer_buffer_alloc(&slot.own, bytes);
             if (st != NNB200_OK) {
                 return st;
             }
-            (flags ? flag_ : outs_.emplace_back()) = b;
-            Buffer& slot = flags ? flag_ : outs_.back();
             slot.mapped[static_cast<size_t>(me)] = slot.own;
             if (flags) {
                 // Zeroed once, before anyone can write into it: the exchange below orders that.
