@@ -1885,9 +1885,15 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep_in, const Devic
 
     const uint32_t a_fmt = p.a_unsigned ? 0u : 1u;
 
-    // CTA-pair form for tall problems with at least a full wave of 256-row tiles and a K of 2048 or
-    // more (below that the per-tile hand-overs of the pair cost more than its main loop saves:
-    // measured 103 against 116 us at K = 256, 68 against 71 at 1024, 64 against 60 at 2304).
+    // CTA-pair form from 256 rows up, with a K of 2048 or more (below that single CTAs are level or
+    // ahead: 22.3 against 23.7 us at 4096 x 4096 x 1024, 35.6 against 37.4 at 8192 x 4096 x 1024) and at
+    // least 24 tiles of 256 x 256.  CUDA-graph timings, single / pair: 512 x 4096 x 4096 (32 tiles)
+    // 24.9 / 16.6 us, 256 x 8192 x 8192 (32) 45.3 / 26.1, 384 x 8192 x 4096 (64) 26.9 / 17.0, 512 x 4096 x 11008
+    // (32) 58.3 / 31.9; with 16 tiles or fewer they are level or single CTAs ahead (256 x 4096 x 4096:
+    // 14.9 / 16.3).  With more tiles than SM pairs, where the single-CTA form would pick a narrower
+    // tile to fill its waves, the pairs' own waves must be at least three quarters full
+    // (2048 x 8192 x 2048, 256 tiles on 74 pairs: 30.9 / 28.5; not 640 x 8192 x 4096, 96 tiles: 22.5 / 27.2;
+    // not M = 512, N = 11008, 86 tiles: 22.3 / 27.3).
     // Knob I8_PAIR: 0 = never; 2 = the pair form whatever the shape, or an error; 1 / 3 = older
     // forms kept for comparison (one k-block per barrier slot; two k-blocks but one commit per
     // destination CTA), forced likewise.
@@ -1895,11 +1901,14 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep_in, const Devic
         const int pair_knob = knob(NNB200_KNOB_I8_PAIR);
         const int64_t pair_tiles = static_cast<int64_t>((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + 255) / 256);
         const bool forced = pair_knob >= 1 && pair_knob <= 3;   // 1, 2, 3: a pair form or an error
+        const int64_t pairs = dev.sm_count / 2 > 0 ? dev.sm_count / 2 : 1;
+        const bool pair_waves_full = pair_tiles * 4 >= ((pair_tiles + pairs - 1) / pairs) * pairs * 3;
         if (forced && (sharded || a_mn || w_mn)) {
             return NNB200_UNSUPPORTED;
         }
         if (pair_knob != 0 && !sharded && !a_mn && !w_mn &&
-            (forced || (m >= 4 * kBlockM && k >= 2048 && pair_tiles >= dev.sm_count / 2 && bn == 256))) {
+            (forced || (m >= 2 * kBlockM && k >= 2048 && pair_tiles >= 24 &&
+                        (pair_tiles <= pairs || bn == 256 || pair_waves_full)))) {
             const int st = pair_knob == 1   ? launch_pair_bn<256, 1, false>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
                            : pair_knob == 3 ? launch_pair_bn<256, 2, false>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
                                             : launch_pair_bn<256, 2, true>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
