@@ -1093,7 +1093,7 @@ struct PairTileConfig {
     static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kColParamBytes + kBarrierBytes;
 };
 
-template <int BN, int KIND, int SUB, bool MC, bool CONV = false>
+template <int BN, int KIND, int SUB, bool MC, bool CONV = false, int POSE = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMaxThreads, 1)
 gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const I8Epilogue ep, const int m_total, const int n_total, const int k_total,
@@ -1192,10 +1192,18 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                                 tma_load_4d_pair(a_dst, &map_a, leader_full, conv.c_base + c0,
                                                  (pt.tw << conv.bw_log2) * conv.sw - conv.pw + tb * conv.dw,
                                                  pt.th * conv.bh * conv.sh - conv.ph + ta * conv.dh, pt.img);
+                            } else if constexpr ((POSE & 1) != 0) {
+                                // A stored [K][M]: 128 k-rows of this CTA's 128 m-bytes.
+                                tma_load_2d_pair(a_dst, &map_a, leader_full, m0, kx * kBlockKBytes);
                             } else {
                                 tma_load_2d_pair(a_dst, &map_a, leader_full, kx * kBlockKBytes, m0);
                             }
-                            tma_load_2d_pair(b_dst, &map_w, leader_full, kx * kBlockKBytes, n0);
+                            if constexpr ((POSE & 2) != 0) {
+                                // W stored [K][N]: 128 k-rows of this CTA's 128 n-bytes (BN = 256).
+                                tma_load_2d_pair(b_dst, &map_w, leader_full, n0, kx * kBlockKBytes);
+                            } else {
+                                tma_load_2d_pair(b_dst, &map_w, leader_full, kx * kBlockKBytes, n0);
+                            }
                         }
                     }
                     if (++stage == kStages) {
@@ -1235,12 +1243,18 @@ gemm_i8_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         if (j < nsub) {
                             const uint32_t a_addr = smem_u32(stage_base + stage * kSlotBytes + j * Cfg::kStageBytes);
                             const uint32_t b_addr = a_addr + Cfg::kATileBytes;
-                            const uint64_t a_desc = umma_desc_sw128_kmajor(a_addr);
-                            const uint64_t b_desc = umma_desc_sw128_kmajor(b_addr);
+                            // MN-major tiles (POSE bits): 32 k-rows of 128 bytes per K step instead of 32 bytes
+                            // along the row, as in the single-CTA kernel.
+                            const uint64_t a_desc = (POSE & 1) ? umma_desc_sw128_mnmajor(a_addr, 128 * kBlockKBytes)
+                                                               : umma_desc_sw128_kmajor(a_addr);
+                            const uint64_t b_desc = (POSE & 2) ? umma_desc_sw128_mnmajor(b_addr, 128 * kBlockKBytes)
+                                                               : umma_desc_sw128_kmajor(b_addr);
+                            constexpr uint64_t a_step = (POSE & 1) ? 256u : 2u;
+                            constexpr uint64_t b_step = (POSE & 2) ? 256u : 2u;
 #pragma unroll
                             for (int ks = 0; ks < kBlockKBytes / kUmmaK; ++ks) {
-                                umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>(ks * 2),
-                                             b_desc + static_cast<uint64_t>(ks * 2), idesc,
+                                umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>(ks) * a_step,
+                                             b_desc + static_cast<uint64_t>(ks) * b_step, idesc,
                                              (kb > 0 || j > 0 || ks > 0) ? 1u : 0u);
                             }
                         }
@@ -1421,12 +1435,13 @@ inline int k_rotation_step(int n)
     return kn >= 0 ? kn : (n <= 4096 ? 5 : 0);
 }
 
-template <int BN, int KIND, int SUB = 1, bool MC = false>
+template <int BN, int KIND, int SUB = 1, bool MC = false, int POSE = 0>
 int launch_pair_variant(const I8Problem& p, const I8Epilogue& ep, int m, int n, int k, uint32_t a_fmt, int vec_ok,
                         const DeviceInfo& dev, cudaStream_t stream)
 {
+    static_assert(POSE == 0 || BN == 256, "an MN-major W half is one 128-column block");
     using Cfg = PairTileConfig<BN>;
-    auto kernel = gemm_i8_umma_pair_kernel<BN, KIND, SUB, MC>;
+    auto kernel = gemm_i8_umma_pair_kernel<BN, KIND, SUB, MC, false, POSE>;
     static std::once_flag once[kMaxDevices];
     static cudaError_t attr_err[kMaxDevices];
     static int max_pairs[kMaxDevices];
@@ -1451,33 +1466,41 @@ int launch_pair_variant(const I8Problem& p, const I8Epilogue& ep, int m, int n, 
         return NNB200_UNSUPPORTED;
     }
     CUtensorMap map_a, map_w;
-    if (!make_tma_2d(&map_a, p.a, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(m),
-                     static_cast<uint64_t>(p.a_stride_m), kBlockKBytes, kBlockM) ||
-        !make_tma_2d(&map_w, p.w, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
-                     static_cast<uint64_t>(p.w_stride_n), kBlockKBytes, BN / 2)) {
+    const bool map_a_ok =
+        (POSE & 1) ? make_tma_2d(&map_a, p.a, 1, static_cast<uint64_t>(m), static_cast<uint64_t>(k),
+                                 static_cast<uint64_t>(p.a_stride_k), kBlockM, kBlockKBytes)
+                   : make_tma_2d(&map_a, p.a, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(m),
+                                 static_cast<uint64_t>(p.a_stride_m), kBlockKBytes, kBlockM);
+    const bool map_w_ok =
+        (POSE & 2) ? make_tma_2d(&map_w, p.w, 1, static_cast<uint64_t>(n), static_cast<uint64_t>(k),
+                                 static_cast<uint64_t>(p.w_stride_k), 128, kBlockKBytes)
+                   : make_tma_2d(&map_w, p.w, 1, static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                                 static_cast<uint64_t>(p.w_stride_n), kBlockKBytes, BN / 2);
+    if (!map_a_ok || !map_w_ok) {
         return NNB200_INTERNAL;
     }
     const int num_tiles = ((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + BN - 1) / BN);
     const int pairs = num_tiles < max_pairs[dev.device] ? num_tiles : max_pairs[dev.device];
     int group_m = static_cast<int>((40ll << 20) / (static_cast<int64_t>(2 * kBlockM) * (k > 0 ? k : 1)));
     group_m = group_m < 2 ? 2 : group_m;
+    constexpr uint32_t major_bits = ((POSE & 1) ? kUmmaAMajorMN : 0u) | ((POSE & 2) ? kUmmaBMajorMN : 0u);
     kernel<<<2 * pairs, num_threads(0), Cfg::kSmemBytes, stream>>>(map_a, map_w, ep, m, n, k,
-                                                               umma_idesc(2, a_fmt, 1, 2 * kBlockM, BN), vec_ok, group_m,
+                                                               umma_idesc(2, a_fmt, 1, 2 * kBlockM, BN) | major_bits, vec_ok, group_m,
                                                                k_rotation_step(n), dev.error_word, ConvTile{});
     note_launch();
     return cuda_status(cudaGetLastError());
 }
 
-template <int BN, int SUB = 1, bool MC = false>
+template <int BN, int SUB = 1, bool MC = false, int POSE = 0>
 int launch_pair_bn(const I8Problem& p, const I8Epilogue& ep, int m, int n, int k, uint32_t a_fmt, int vec_ok,
                    const DeviceInfo& dev, cudaStream_t stream)
 {
     switch (ep.out_kind) {
-    case NNB200_OUT_S32: return launch_pair_variant<BN, NNB200_OUT_S32, SUB, MC>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
-    case NNB200_OUT_S8: return launch_pair_variant<BN, NNB200_OUT_S8, SUB, MC>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
-    case NNB200_OUT_U8: return launch_pair_variant<BN, NNB200_OUT_U8, SUB, MC>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
-    case NNB200_OUT_F32: return launch_pair_variant<BN, NNB200_OUT_F32, SUB, MC>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
-    case NNB200_OUT_F16: return launch_pair_variant<BN, NNB200_OUT_F16, SUB, MC>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_S32: return launch_pair_variant<BN, NNB200_OUT_S32, SUB, MC, POSE>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_S8: return launch_pair_variant<BN, NNB200_OUT_S8, SUB, MC, POSE>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_U8: return launch_pair_variant<BN, NNB200_OUT_U8, SUB, MC, POSE>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_F32: return launch_pair_variant<BN, NNB200_OUT_F32, SUB, MC, POSE>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
+    case NNB200_OUT_F16: return launch_pair_variant<BN, NNB200_OUT_F16, SUB, MC, POSE>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
     default: return NNB200_UNSUPPORTED;
     }
 }
@@ -1903,14 +1926,19 @@ int launch_gemm_i8_umma(const I8Problem& p, const I8Epilogue& ep_in, const Devic
         const bool forced = pair_knob >= 1 && pair_knob <= 3;   // 1, 2, 3: a pair form or an error
         const int64_t pairs = dev.sm_count / 2 > 0 ? dev.sm_count / 2 : 1;
         const bool pair_waves_full = pair_tiles * 4 >= ((pair_tiles + pairs - 1) / pairs) * pairs * 3;
-        if (forced && (sharded || a_mn || w_mn)) {
+        const bool mn = a_mn || w_mn;   // MN-major operands: the default pair form only (knob 1 / 3: K-major)
+        if (forced && (sharded || (mn && pair_knob != 2))) {
             return NNB200_UNSUPPORTED;
         }
-        if (pair_knob != 0 && !sharded && !a_mn && !w_mn &&
+        if (pair_knob != 0 && !sharded &&
             (forced || (m >= 2 * kBlockM && k >= 2048 && pair_tiles >= 24 &&
                         (pair_tiles <= pairs || bn == 256 || pair_waves_full)))) {
+            const int pose = (a_mn ? 1 : 0) | (w_mn ? 2 : 0);
             const int st = pair_knob == 1   ? launch_pair_bn<256, 1, false>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
                            : pair_knob == 3 ? launch_pair_bn<256, 2, false>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
+                           : pose == 1      ? launch_pair_bn<256, 2, true, 1>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
+                           : pose == 2      ? launch_pair_bn<256, 2, true, 2>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
+                           : pose == 3      ? launch_pair_bn<256, 2, true, 3>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream)
                                             : launch_pair_bn<256, 2, true>(p, ep, m, n, k, a_fmt, vec_ok, dev, stream);
             if (st != NNB200_UNSUPPORTED || forced) {
                 return st;

@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import oracle
-from nnops_b200 import ops, synth
+from nnops_b200 import capi, ops, synth
 
 pytestmark = pytest.mark.gpu
 
@@ -263,7 +263,8 @@ def test_transposed_poses_off_the_tma_rule_use_generic(cuda_device, nnb200_lib):
 
 
 @pytest.mark.parametrize("pose", ["nn", "tn", "tt", "nt"])          # (transpose_a, transpose_b) of MatMul: n = no, t = yes
-@pytest.mark.parametrize("shape", [(256, 512, 384), (144, 272, 208), (1008, 4112, 96), (2048, 9008, 640), (144, 144, 144)])
+@pytest.mark.parametrize("shape", [(256, 512, 384), (144, 272, 208), (1008, 4112, 96), (2048, 9008, 640), (144, 144, 144),
+                                   (528, 4112, 2080)])   # the last one: CTA pairs (K >= 2048, 51 tiles of 256 x 256)
 @pytest.mark.parametrize("out_kind", ["s32", "s8", "f16"])
 def test_matmul_poses_on_the_tensor_core_engine(cuda_device, nnb200_lib, pose, shape, out_kind):
     """MatMul's four operand poses on the tcgen05 engine (reference: one tile kernel templated on
@@ -294,6 +295,33 @@ def test_matmul_poses_on_the_tensor_core_engine(cuda_device, nnb200_lib, pose, s
     if not np.array_equal(got.view(np.uint8), want.view(np.uint8)):
         bad = np.argwhere(got != want)
         raise AssertionError(f"{len(bad)} mismatches of {got.size}; first {bad[:5].tolist()}")
+
+
+@pytest.mark.parametrize("pose", ["nn", "tn", "tt"])
+def test_matmul_poses_on_cta_pairs(cuda_device, nnb200_lib, pose, knobs):
+    """MN-major operands on the CTA-pair kernel (forced on a small ragged shape, an odd count of
+    k-blocks): same bytes as on single CTAs and as the oracle."""
+    m, n, k = 304, 528, 2192
+    rng = np.random.default_rng(17 + len(pose))
+    a_t, b_t = pose[0] == "t", pose[1] == "t"
+    a_store = rng.integers(-127, 128, (k, m) if a_t else (m, k), dtype=np.int8)
+    b_store = rng.integers(-127, 128, (n, k) if b_t else (k, n), dtype=np.int8)
+    a_log = a_store.T if a_t else a_store
+    w_log = b_store if b_t else b_store.T
+    kw = dict(out_kind="s8", scale_w=rng.uniform(0.001, 0.02, n).astype(np.float32), scale_a=0.02, out_scale=1.7,
+              bias=rng.integers(-500, 501, n).astype(np.int32), relu=True)
+    want = oracle.gemm_i8(a_log, w_log, **kw)
+    ta = torch.from_numpy(a_store).to(cuda_device)
+    tb = torch.from_numpy(b_store).to(cuda_device)
+    ta = ta.t() if a_t else ta
+    tw = tb if b_t else tb.t()
+    knobs("i8_pair", 2)
+    got = ops.gemm_i8(ta, tw, engine="umma", **kw)
+    torch.cuda.synchronize()
+    assert capi.take_device_error() == 0
+    assert np.array_equal(got.cpu().numpy(), want)
+    knobs("i8_pair", 0)
+    assert torch.equal(ops.gemm_i8(ta, tw, engine="umma", **kw), got)
 
 
 def test_matmul_default_pose_takes_the_tensor_core_engine_by_itself(cuda_device, nnb200_lib):
