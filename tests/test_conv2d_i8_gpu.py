@@ -69,8 +69,10 @@ CASES = [
     (1, 256, 56, 56, 64, 1, 1, 2, 2, 1, 1, 0, 0, 1, S8, "u8", True, True, -6, True),
     (2, 128, 40, 33, 96, 3, 3, 2, 1, 1, 1, 1, 1, 1, U8, "f16", True, True, None, True),
     (22, 128, 56, 56, 256, 3, 3, 2, 2, 1, 1, 1, 1, 1, U8, "s8", True, True, 128, True),
+    (2, 128, 41, 45, 64, 3, 5, 2, 2, 2, 2, 2, 4, 1, U8, "s8", True, True, 77, True),     # stride 2 with dilation 2
+    (3, 256, 31, 29, 48, 3, 3, 1, 2, 1, 1, 1, 1, 2, S8, "f32", True, False, -6, True),   # stride along w only, two groups
 ]
-IMPLICIT = list(range(len(CASES) - 12, len(CASES)))
+IMPLICIT = list(range(len(CASES) - 14, len(CASES)))
 
 
 def _make(case, seed):
