@@ -538,6 +538,39 @@ def secondary_i8_poses(torch, dev):
     return out
 
 
+def secondary_i8_epilogue_bound(torch, dev, peaks):
+    """Two int8 Linear calls whose time is the epilogue's, not the main loop's: a short K with an s8
+    destination (the GEMM of a 1x1 convolution: M = 100352, N = 1024, K = 256, bias + ReLU +
+    per-channel requant), and f16 / f32 destinations (dequantising epilogue with an f16 bias) at
+    M = 32768, N = 4096, K = 256; and the headline-sized 8192^3 into f16.  Synthetic values."""
+    from nnops_b200 import ops
+    out = {}
+
+    def case(key, m, n, k, kind, **kw):
+        a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev)
+        w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev)
+        sw = torch.rand(n, device=dev) * 0.02 + 0.001
+        dt = {"s8": torch.int8, "f16": torch.float16, "f32": torch.float32}[kind]
+        o = torch.empty((m, n), dtype=dt, device=dev)
+        if kind == "s8":
+            extra = dict(bias=torch.randint(-1000, 1001, (n,), dtype=torch.int32, device=dev), relu=True, out_scale=0.05)
+        else:
+            extra = dict(bias=(torch.rand(n, device=dev) - 0.5).to(dt))
+        extra.update(kw)
+        us = graph_time_us(torch, lambda: ops.gemm_i8(a, w, out_kind=kind, out=o, scale_a=0.02, scale_w=sw, **extra))
+        nbytes = m * k + n * k + m * n * o.element_size()
+        out[key] = {"tops": 2.0 * m * n * k / us / 1e6, "us_per_call": us, "gbs": nbytes / us / 1e3,
+                    "frac_of_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"], "shape": [m, n, k], "out": kind}
+        del a, w, o
+
+    case("i8_linear_k256_s8", 100352, 1024, 256, "s8")
+    case("i8_linear_k256_f16", 32768, 4096, 256, "f16")
+    case("i8_linear_k256_f16_gelu", 32768, 4096, 256, "f16", activation="gelu")
+    case("i8_linear_k256_f32", 32768, 4096, 256, "f32")
+    case("i8_linear_8192_f16", 8192, 8192, 8192, "f16")
+    return out
+
+
 def secondary_i8_conv2d(torch, dev):
     """int8 Conv2D (u8 NHWC x s8 HWIO -> s8, bias + Relu, per-channel filter scales) on two layer
     shapes of a ResNet-50 body at batch 32, synthetic values: a 3x3 (gather pass + GEMM) and a 1x1
@@ -902,6 +935,7 @@ def main():
         extra.update(secondary_i8_config2(torch, dev, peaks))
         extra.update(secondary_i8_poses(torch, dev))
         extra.update(secondary_i8_conv2d(torch, dev))
+        extra.update(secondary_i8_epilogue_bound(torch, dev, peaks))
         extra.update(secondary_quant_linear(torch, dev, peaks))
         extra.update(secondary_i8_decode(torch, dev, peaks, layer.w, layer.kw["scale_w"], layer.kw["bias"]))
         extra["e2e_op"] = operator_level_bench(10, 3)
