@@ -177,6 +177,9 @@ public:
     int alloc_outputs(int64_t m, int count)
     {
         const int g = ex_.world(), me = ex_.rank();
+        if (!outs_.empty() || flag_.own != nullptr) {
+            return NNB200_INVALID_ARGUMENT;   // one allocation per layer: close() first
+        }
         if (g < 1 || g > kMaxShardRanks || count < 1 || m < 1 || shard_.n * g != n_total_ ||
             (shard_.out_kind != NNB200_OUT_S8 && shard_.out_kind != NNB200_OUT_U8)) {
             return NNB200_INVALID_ARGUMENT;
