@@ -246,6 +246,61 @@ def test_k_blocks_walked_from_a_rotated_start(cuda_device, nnb200_lib, case, pai
               out_scale=0.9, out_zp=0 if kind == "s32" else 3, engine="umma", seed=m + k)
 
 
+def _np_activation(name, x, alpha, beta):
+    """The activations of the fp epilogue (act_apply in csrc/epilogue.cuh; reference:
+    include/nnops/core/epilogue.hpp), in float64."""
+    x = x.astype(np.float64)
+    if name == "relu":
+        return np.maximum(x, 0)
+    if name == "relu6":
+        return np.minimum(np.maximum(x, 0), 6)
+    if name == "leaky_relu":
+        return np.where(x > 0, x, alpha * x)
+    if name == "sigmoid":
+        return 1 / (1 + np.exp(-x))
+    if name == "tanh":
+        return np.tanh(x)
+    if name == "gelu":
+        return 0.5 * x * (1 + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+    if name == "silu":
+        return x / (1 + np.exp(-x))
+    if name == "hard_swish":
+        return x * np.minimum(np.maximum(x + 3, 0), 6) * (beta / 6)
+    if name == "elu":
+        return np.where(x > 0, x, alpha * (np.exp(np.minimum(x, 0)) - 1))
+    raise KeyError(name)
+
+
+@pytest.mark.parametrize("engine", ["umma", "generic"])
+@pytest.mark.parametrize("zero_points", [False, True])
+@pytest.mark.parametrize("out_kind", ["f32", "f16"])
+@pytest.mark.parametrize("act", ["relu", "gelu", "sigmoid", "tanh", "leaky_relu", "silu", "hard_swish", "elu", "relu6"])
+def test_fp_destinations_apply_every_activation(cuda_device, nnb200_lib, act, out_kind, zero_points, engine):
+    """fp destinations: dequantise, bias, clip, then the activation.  The tensor-core epilogue has
+    a loop per (compensation live, activation class); each must give what the activation applied
+    to the SAME call's un-activated f32 output gives (that output is bit-exact against the oracle
+    elsewhere), to f32 / f16 rounding and the accuracy of the device's exp / tanh."""
+    m, n, k = 200, 328, 256
+    rng = np.random.default_rng(len(act) * 7 + (1 if zero_points else 0))
+    a = torch.from_numpy(rng.integers(-127, 128, (m, k), dtype=np.int8)).to(cuda_device)
+    w = torch.from_numpy(rng.integers(-127, 128, (n, k), dtype=np.int8)).to(cuda_device)
+    kw = dict(scale_a=0.004, scale_w=rng.uniform(0.0005, 0.002, n).astype(np.float32), engine=engine,
+              bias=rng.uniform(-1, 1, n).astype(np.float32), min_clip=-5.0, max_clip=7.0)
+    if zero_points:
+        kw.update(zp_a=5, zp_w=rng.integers(-4, 5, n).astype(np.int32))
+    base = ops.gemm_i8(a, w, out_kind="f32", **kw).cpu().numpy()
+    assert np.abs(base).max() > 1.0 and (base < 0).any() and (base > 0).any()
+    if out_kind == "f16":
+        kw["bias"] = kw["bias"].astype(np.float16)
+        base = ops.gemm_i8(a, w, out_kind="f32", **{**kw, "bias": kw["bias"].astype(np.float32)}).cpu().numpy()
+    got = ops.gemm_i8(a, w, out_kind=out_kind, activation=act, act_alpha=0.1, act_beta=1.5, **kw)
+    torch.cuda.synchronize()
+    want = _np_activation(act, base, 0.1, 1.5)
+    err = np.abs(got.cpu().numpy().astype(np.float64) - want)
+    tol = (2e-6 + 2e-6 * np.abs(want)) if out_kind == "f32" else (1e-3 + 1e-3 * np.abs(want))
+    assert (err <= tol).all(), (act, float(err.max()), float(np.abs(want).max()))
+
+
 def test_transposed_poses_off_the_tma_rule_use_generic(cuda_device, nnb200_lib):
     """[K, M] activations and [K, N] weights whose row pitch is not a multiple of 16 bytes cannot
     be addressed by TMA: the generic engine serves them."""
