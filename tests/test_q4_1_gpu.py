@@ -251,6 +251,38 @@ def test_gemm_epilogue_bias_relu(cuda_device, nnb200_lib):
         _close(got.cpu().numpy(), want, RTOL_F16)
 
 
+@pytest.mark.parametrize("engine", ["gemm", "gemm_two_pass"])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("act", ["none", "relu", "gelu", "silu", "hard_swish"])
+def test_gemm_epilogue_alpha_bias_clip_activation(cuda_device, nnb200_lib, engine, out_dtype, act):
+    """alpha, bias, clip and every activation class of the tensor-core GEMMs' drain (one loop per
+    class): what the same arithmetic in float64 gives on the SAME engine's plain f32 product."""
+    rng = np.random.default_rng(11)
+    m, n, k = 256, 392, 256
+    wb = torch.from_numpy(synth.q4_1_weights(rng, n, k)).to(cuda_device)
+    a = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float16)).to(cuda_device)
+    bias = rng.uniform(-2, 2, n).astype(np.float32)
+    plain = ops.linear_q4_1(a, wb, k, out_dtype=torch.float32, engine=engine).cpu().numpy().astype(np.float64)
+    b_t = torch.from_numpy(bias.astype(np.float16 if out_dtype == torch.float16 else np.float32)).to(cuda_device)
+    got = ops.linear_q4_1(a, wb, k, out_dtype=out_dtype, bias=b_t, alpha=0.75, min_clip=-6.0, max_clip=9.0,
+                          activation=act, act_alpha=0.1, act_beta=1.5, engine=engine)
+    torch.cuda.synchronize()
+    x = np.clip(plain * 0.75 + b_t.cpu().numpy().astype(np.float64), -6.0, 9.0)
+    if act == "relu":
+        want = np.maximum(x, 0)
+    elif act == "gelu":
+        want = 0.5 * x * (1 + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+    elif act == "silu":
+        want = x / (1 + np.exp(-x))
+    elif act == "hard_swish":
+        want = x * np.clip(x + 3, 0, 6) * (1.5 / 6)
+    else:
+        want = x
+    err = np.abs(got.cpu().numpy().astype(np.float64) - want)
+    tol = (1e-5 + 1e-5 * np.abs(want)) if out_dtype == torch.float32 else (2e-3 + 2e-3 * np.abs(want))
+    assert (err <= tol).all(), (act, float(err.max()))
+
+
 def _close_abs_rms(got, ref, rtol, atol_rms):
     """|got - ref| <= atol_rms * rms(ref) + rtol * |ref| elementwise."""
     got = got.astype(np.float32)
