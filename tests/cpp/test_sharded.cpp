@@ -205,52 +205,89 @@ int gpu_rank(int rank, int world, const std::string& name)
     CUDA_OK(cudaMemcpy(d_scale, scale.data(), scale.size() * 4, cudaMemcpyHostToDevice));
     CUDA_OK(cudaMemcpy(d_bias, bias.data(), bias.size() * 4, cudaMemcpyHostToDevice));
 
-    nnb200_gemm_i8_args full;
-    std::memset(&full, 0, sizeof(full));
-    full.a = d_a; full.w = d_w; full.out = d_ref;
-    full.m = m; full.n = n; full.k = k;
-    full.a_stride_m = k; full.a_stride_k = 1; full.w_stride_n = k; full.w_stride_k = 1;
-    full.ldc = n; full.batch = 1;
-    full.out_kind = NNB200_OUT_S8;
-    full.bias = d_bias; full.relu = 1;
-    full.scale_w = d_scale; full.scale_a_scalar = 0.02f; full.scale_w_scalar = 1.0f;
-    full.out_scale = 0.9f;
-    full.min_clip = -INFINITY; full.max_clip = INFINITY;
-    NNB_OK(nnb200_gemm_i8(&full, nullptr));
+    // Per-channel weight zero points for the second variant.
+    std::vector<int32_t> zpw(static_cast<size_t>(n));
+    for (auto& v : zpw) v = static_cast<int32_t>(next() % 9u) - 4;
+    int32_t* d_zpw = nullptr;
+    CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&d_zpw), zpw.size() * 4));
+    CUDA_OK(cudaMemcpy(d_zpw, zpw.data(), zpw.size() * 4, cudaMemcpyHostToDevice));
 
-    nnb200_gemm_i8_args shard = full;
-    shard.w = d_w + static_cast<int64_t>(rank) * n_per * k;
-    shard.bias = d_bias + static_cast<int64_t>(rank) * n_per;
-    shard.scale_w = d_scale + static_cast<int64_t>(rank) * n_per;
-    shard.n = n_per;
-    shard.out = nullptr;
-
-    ShardedLinearI8 layer(ex, shard, n);
-    NNB_OK(layer.alloc_outputs(m, 2));
-    std::vector<int8_t> want(static_cast<size_t>(m * n)), got(want.size());
-    CUDA_OK(cudaDeviceSynchronize());
-    CUDA_OK(cudaMemcpy(want.data(), d_ref, want.size(), cudaMemcpyDeviceToHost));
     int mismatches = 0;
-    for (int round = 0; round < 3; ++round) {
-        const int oi = round & 1;
-        NNB_OK(layer.begin_step());
-        CUDA_OK(cudaMemset(layer.output(oi), 0x55, want.size()));
+    // Variant 0: symmetric, s8 destination, ReLU (the benchmark's epilogue).  Variant 1: zero points
+    // on both sides (compensation live in the sharded epilogue), u8 destination with a zero point.
+    for (int variant = 0; variant < 2; ++variant) {
+        nnb200_gemm_i8_args full;
+        std::memset(&full, 0, sizeof(full));
+        full.a = d_a; full.w = d_w; full.out = d_ref;
+        full.m = m; full.n = n; full.k = k;
+        full.a_stride_m = k; full.a_stride_k = 1; full.w_stride_n = k; full.w_stride_k = 1;
+        full.ldc = n; full.batch = 1;
+        full.out_kind = variant == 0 ? NNB200_OUT_S8 : NNB200_OUT_U8;
+        full.bias = d_bias; full.relu = variant == 0 ? 1 : 0;
+        full.scale_w = d_scale; full.scale_a_scalar = 0.02f; full.scale_w_scalar = 1.0f;
+        full.out_scale = 0.9f;
+        full.min_clip = -INFINITY; full.max_clip = INFINITY;
+        if (variant == 1) {
+            full.zp_a_scalar = 5;
+            full.zp_w = d_zpw;
+            full.zp_w_nonzero = 1;
+            full.out_zp = 117;
+        }
+        void *ws_full = nullptr, *ws_shard = nullptr;
+        full.workspace_bytes = nnb200_gemm_i8_workspace_bytes(&full);
+        if (full.workspace_bytes > 0) {
+            CUDA_OK(cudaMalloc(&ws_full, full.workspace_bytes));
+            full.workspace = ws_full;
+        }
+        NNB_OK(nnb200_gemm_i8(&full, nullptr));
+
+        nnb200_gemm_i8_args shard = full;
+        shard.w = d_w + static_cast<int64_t>(rank) * n_per * k;
+        shard.bias = d_bias + static_cast<int64_t>(rank) * n_per;
+        shard.scale_w = d_scale + static_cast<int64_t>(rank) * n_per;
+        shard.zp_w = variant == 1 ? d_zpw + static_cast<int64_t>(rank) * n_per : nullptr;
+        shard.n = n_per;
+        shard.workspace = nullptr;
+        shard.workspace_bytes = nnb200_gemm_i8_workspace_bytes(&shard);   // asked with a valid destination in place
+        shard.out = nullptr;
+        if (shard.workspace_bytes > 0) {
+            CUDA_OK(cudaMalloc(&ws_shard, shard.workspace_bytes));
+            shard.workspace = ws_shard;
+        }
+
+        ShardedLinearI8 layer(ex, shard, n);
+        NNB_OK(layer.alloc_outputs(m, 2));
+        if (layer.alloc_outputs(m, 1) != NNB200_INVALID_ARGUMENT) {   // one allocation per layer
+            return 14;
+        }
+        std::vector<int8_t> want(static_cast<size_t>(m * n)), got(want.size());
         CUDA_OK(cudaDeviceSynchronize());
-        if (!ex.barrier()) {   // nobody's stores arrive before everybody's fill is done
-            return 12;
+        CUDA_OK(cudaMemcpy(want.data(), d_ref, want.size(), cudaMemcpyDeviceToHost));
+        for (int round = 0; round < 3; ++round) {
+            const int oi = round & 1;
+            NNB_OK(layer.begin_step());
+            CUDA_OK(cudaMemset(layer.output(oi), 0x55, want.size()));
+            CUDA_OK(cudaDeviceSynchronize());
+            if (!ex.barrier()) {   // nobody's stores arrive before everybody's fill is done
+                return 12;
+            }
+            NNB_OK(layer.forward(d_a, k, oi, nullptr, round == 2));
+            NNB_OK(layer.check());
+            CUDA_OK(cudaMemcpy(got.data(), layer.output(oi), got.size(), cudaMemcpyDeviceToHost));
+            if (std::memcmp(got.data(), want.data(), got.size()) != 0) {
+                ++mismatches;
+                std::fprintf(stderr, "rank %d variant %d round %d: output differs from the single-GPU result\n", rank,
+                             variant, round);
+            }
+            if (!ex.barrier()) {   // everyone has read its copy before the next round overwrites it
+                return 13;
+            }
         }
-        NNB_OK(layer.forward(d_a, k, oi, nullptr, round == 2));
-        NNB_OK(layer.check());
-        CUDA_OK(cudaMemcpy(got.data(), layer.output(oi), got.size(), cudaMemcpyDeviceToHost));
-        if (std::memcmp(got.data(), want.data(), got.size()) != 0) {
-            ++mismatches;
-            std::fprintf(stderr, "rank %d round %d: output differs from the single-GPU result\n", rank, round);
-        }
-        if (!ex.barrier()) {   // everyone has read its copy before the next round overwrites it
-            return 13;
-        }
+        NNB_OK(layer.close());
+        cudaFree(ws_full);
+        cudaFree(ws_shard);
     }
-    NNB_OK(layer.close());
+    cudaFree(d_zpw);
     cudaFree(d_a); cudaFree(d_w); cudaFree(d_ref); cudaFree(d_scale); cudaFree(d_bias);
     return mismatches == 0 ? 0 : 1;
 }
